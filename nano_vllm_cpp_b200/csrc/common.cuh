@@ -1,0 +1,64 @@
+// Shared helpers of the hand-written sm_100a kernels.
+//
+// Every launcher is an extern "C" function that takes raw device pointers, sizes and a
+// cudaStream_t, launches on that stream and returns 0 or a negative NV_ERR_* / positive
+// cudaError_t code.  Nothing here allocates device memory: the caller owns every buffer.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define NV_DT_F32 0
+#define NV_DT_BF16 1
+
+#define NV_OK 0
+#define NV_ERR_BAD_DTYPE (-2)
+#define NV_ERR_BAD_SIZE (-3)
+#define NV_ERR_UNSUPPORTED (-4)
+
+#define NV_API extern "C" __attribute__((visibility("default")))
+
+#define NV_RETURN_LAST()                          \
+  do {                                            \
+    cudaError_t e__ = cudaGetLastError();         \
+    return e__ == cudaSuccess ? NV_OK : (int)e__; \
+  } while (0)
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(bf16 v) { return __bfloat162float(v); }
+
+template <typename T>
+__device__ __forceinline__ T from_f32(float v);
+template <>
+__device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+// Load / store with a run-time dtype code: the plain kernels take it where a template
+// parameter would multiply instantiations without making anything faster that matters.
+__device__ __forceinline__ float ld_dt(const void* p, int dt, size_t i) {
+  return dt == NV_DT_F32 ? ((const float*)p)[i] : __bfloat162float(((const bf16*)p)[i]);
+}
+__device__ __forceinline__ void st_dt(void* p, int dt, size_t i, float v) {
+  if (dt == NV_DT_F32) ((float*)p)[i] = v;
+  else ((bf16*)p)[i] = __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// SiLU(g) * u exactly as the reference writes it: g / (1 + expf(-g)) * u  (src/hip_ops.hip:419-429).
+__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
+
+static inline int dt_ok(int dt) { return dt == NV_DT_F32 || dt == NV_DT_BF16; }

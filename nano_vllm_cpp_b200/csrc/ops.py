@@ -1,0 +1,284 @@
+"""ctypes binding of the CUDA library: one Python function per launcher.
+
+Every function takes torch CUDA tensors, checks what the kernel assumes (dtype, contiguity,
+sizes), launches on torch's current stream and raises ``KernelError`` on a refusal or a
+CUDA error.  There is no CPU fallback: on a machine without the library (and without nvcc to
+build it) importing the ops fails with the reason.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_int, c_float, c_longlong, c_void_p
+
+import torch
+
+from . import build as _build
+
+F32, BF16 = 0, 1
+_DT = {torch.float32: F32, torch.bfloat16: BF16}
+_ERR = {-2: "unsupported dtype", -3: "bad size", -4: "size not supported by this kernel",
+        -5: "kernel set-up failed"}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        path = _build.library_path()
+        try:
+            _lib = ctypes.CDLL(path)
+        except OSError as e:
+            raise KernelError(f"cannot load the CUDA library {path}: {e}") from None
+    return _lib
+
+
+def _check(code: int, what: str) -> None:
+    if code == 0:
+        return
+    if code < 0:
+        raise KernelError(f"{what}: {_ERR.get(code, f'error {code}')}")
+    raise KernelError(f"{what}: CUDA error {code} ({_cuda_error_name(code)})")
+
+
+def _cuda_error_name(code: int) -> str:
+    try:
+        f = lib().nv_error_string
+        f.restype = ctypes.c_char_p
+        return f(c_int(code)).decode()
+    except Exception:
+        return "?"
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _p(t) -> c_void_p:
+    if t is None:
+        return c_void_p(0)
+    return c_void_p(t.data_ptr())
+
+
+def dt(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise KernelError(f"dtype {t.dtype} is not supported (float32 or bfloat16)") from None
+
+
+def _need(cond: bool, msg: str) -> None:
+    if not cond:
+        raise KernelError(msg)
+
+
+def _cuda_contig(*ts) -> None:
+    for t in ts:
+        if t is None:
+            continue
+        _need(t.is_cuda, "tensor is not on a CUDA device")
+        _need(t.is_contiguous(), "tensor is not contiguous")
+
+
+def _i32(*ts) -> None:
+    for t in ts:
+        if t is not None:
+            _need(t.dtype == torch.int32, f"index tensor must be int32, found {t.dtype}")
+
+
+# ----------------------------------------------------------------------------- error flag
+class ErrorFlag:
+    """A device int that kernels set (to 1 + the offending row) instead of trapping."""
+
+    def __init__(self, device):
+        self.t = torch.zeros(1, dtype=torch.int32, device=device)
+
+    def check(self, what: str) -> None:
+        v = int(self.t.item())
+        if v:
+            self.t.zero_()
+            raise KernelError(f"{what}: a kernel reported a bad index at row/pair {v - 1}")
+
+
+# ----------------------------------------------------------------------------- plain ops
+def embedding(ids, table, out, err: ErrorFlag) -> None:
+    _cuda_contig(ids, table, out)
+    _i32(ids)
+    T, (V, H) = ids.numel(), table.shape
+    _need(out.dtype == torch.float32 and out.shape == (T, H), "embedding: out must be float32 [T, H]")
+    _check(lib().nv_embedding(_p(ids), _p(table), c_int(dt(table)), _p(out), c_int(T), c_int(H), c_int(V),
+                              _p(err.t), _stream()), "embedding")
+
+
+def add_rmsnorm(x, branch, w, eps: float, out, out32=None) -> None:
+    """x (+= branch); out = rmsnorm(x) * w; optional float32 copy of out."""
+    _cuda_contig(x, branch, w, out, out32)
+    T, H = x.shape
+    _need(x.dtype == torch.float32, "add_rmsnorm: the residual stream is float32")
+    _need(branch is None or (branch.dtype == torch.float32 and branch.shape == x.shape),
+          "add_rmsnorm: branch must be float32 and shaped like x")
+    _need(w.numel() == H and out.shape == x.shape, "add_rmsnorm: shape mismatch")
+    _need(out32 is None or (out32.dtype == torch.float32 and out32.shape == x.shape), "add_rmsnorm: out32")
+    _check(lib().nv_add_rmsnorm(_p(x), _p(branch), _p(w), c_int(dt(w)), c_float(eps), _p(out), c_int(dt(out)),
+                                _p(out32), c_int(T), c_int(H), _stream()), "add_rmsnorm")
+
+
+def gemm_plain(a, w, out, *, bias=None, a_rows=None, swiglu=False, M=None, tiles=None) -> None:
+    """out[m, :] = a[a_rows[m] or m, :] @ w.T (+ bias), or silu(gate) * up with ``swiglu``.
+
+    ``tiles`` = (tile_expert, tile_row0, tile_rows, num_tiles) selects the grouped form, where w is
+    [E, rows, K]."""
+    _cuda_contig(w, bias, a_rows)
+    _need(a.stride(-1) == 1 and out.stride(-1) == 1, "gemm: rows must be dense")
+    K = a.shape[1]
+    grouped = tiles is not None
+    n_rows_w = w.shape[-2]
+    _need(w.shape[-1] == K, f"gemm: inner sizes differ ({K} vs {w.shape[-1]})")
+    N = n_rows_w // 2 if swiglu else n_rows_w
+    _need(not swiglu or n_rows_w % 2 == 0, "gemm: swiglu needs an even number of weight rows")
+    if M is None:
+        M = a_rows.numel() if a_rows is not None else a.shape[0]
+    _need(out.shape[0] >= M and out.shape[1] == N, f"gemm: out is {tuple(out.shape)}, need [{M}, {N}]")
+    _i32(a_rows)
+    if grouped:
+        te, tr0, tr, nt = tiles
+        _i32(te, tr0, tr, nt)
+        stride = w.stride(0)
+        max_tiles = te.numel()
+    else:
+        te = tr0 = tr = nt = None
+        stride = 0
+        max_tiles = 0
+    if bias is not None:
+        _need(bias.numel() == N, "gemm: bias length")
+    _check(lib().nv_gemm_plain(_p(a), c_int(dt(a)), c_longlong(a.stride(0)), _p(a_rows),
+                               _p(w), c_int(dt(w)), c_longlong(stride),
+                               _p(bias), c_int(dt(bias) if bias is not None else 0),
+                               _p(out), c_int(dt(out)), c_longlong(out.stride(0)),
+                               c_int(M), c_int(N), c_int(K), c_int(1 if swiglu else 0),
+                               _p(te), _p(tr0), _p(tr), _p(nt), c_int(max_tiles), _stream()), "gemm_plain")
+
+
+def gemm_plain_tile_m() -> int:
+    return int(lib().nv_gemm_plain_tile_m())
+
+
+def rope_store(qkv, positions, inv_freq, rotary_dim: int, k_cache, v_cache, block_table, row_entry,
+               Hq: int, Hkv: int, D: int, write_kv: bool, err: ErrorFlag) -> None:
+    _cuda_contig(qkv, positions, inv_freq, k_cache, v_cache, block_table, row_entry)
+    _i32(positions, block_table, row_entry)
+    T = qkv.shape[0]
+    _need(qkv.shape[1] == (Hq + 2 * Hkv) * D, "rope_store: qkv width")
+    _need(inv_freq.dtype == torch.float32 and inv_freq.numel() >= rotary_dim // 2, "rope_store: inv_freq")
+    page = k_cache.shape[2]
+    _need(k_cache.shape[1:] == (Hkv, page, D) and v_cache.shape == k_cache.shape, "rope_store: cache shape")
+    _check(lib().nv_rope_store(_p(qkv), c_int(dt(qkv)), _p(positions), _p(inv_freq), c_int(rotary_dim),
+                               _p(k_cache), _p(v_cache), c_int(dt(k_cache)), _p(block_table),
+                               c_int(block_table.shape[1]), _p(row_entry), c_int(T), c_int(Hq), c_int(Hkv),
+                               c_int(D), c_int(page), c_int(1 if write_kv else 0), _p(err.t), _stream()),
+           "rope_store")
+
+
+def paged_attention_plain(qkv, k_cache, v_cache, block_table, row_entry, positions, scale: float, window: int,
+                          out, Hq: int, Hkv: int, D: int) -> None:
+    _cuda_contig(qkv, k_cache, v_cache, block_table, row_entry, positions, out)
+    _i32(block_table, row_entry, positions)
+    T = qkv.shape[0]
+    page = k_cache.shape[2]
+    _need(out.shape == (T, Hq * D), "attention: out shape")
+    _check(lib().nv_paged_attention_plain(_p(qkv), c_int(dt(qkv)), c_int(qkv.shape[1]), _p(k_cache), _p(v_cache),
+                                          c_int(dt(k_cache)), _p(block_table), c_int(block_table.shape[1]),
+                                          _p(row_entry), _p(positions), c_float(scale), c_int(window), _p(out),
+                                          c_int(dt(out)), c_int(T), c_int(Hq), c_int(Hkv), c_int(D), c_int(page),
+                                          _stream()), "paged_attention_plain")
+
+
+def router_topk(logits, K: int, renorm: bool, idx, score) -> None:
+    _cuda_contig(logits, idx, score)
+    T, E = logits.shape
+    _need(logits.dtype == torch.float32 and score.dtype == torch.float32, "router: float32 logits and scores")
+    _i32(idx)
+    _need(idx.shape == (T, K) and score.shape == (T, K), "router: output shapes")
+    _check(lib().nv_router_topk(_p(logits), c_int(T), c_int(E), c_int(K), c_int(1 if renorm else 0), _p(idx),
+                                _p(score), _stream()), "router_topk")
+
+
+class MoeAlignment:
+    """Device buffers of one expert permutation (sizes fixed by T*K and E)."""
+
+    def __init__(self, TK: int, E: int, tile_m: int, device):
+        i32 = dict(dtype=torch.int32, device=device)
+        self.TK, self.E, self.tile_m = TK, E, tile_m
+        self.max_tiles = (TK + tile_m - 1) // tile_m + E
+        self.counts = torch.empty(E, **i32)
+        self.offsets = torch.empty(E + 1, **i32)
+        self.cursor = torch.empty(E, **i32)
+        self.sorted_token = torch.empty(max(TK, 1), **i32)
+        self.pair_pos = torch.empty(max(TK, 1), **i32)
+        self.tile_expert = torch.empty(self.max_tiles, **i32)
+        self.tile_row0 = torch.empty(self.max_tiles, **i32)
+        self.tile_rows = torch.empty(self.max_tiles, **i32)
+        self.num_tiles = torch.zeros(1, **i32)
+
+    @property
+    def tiles(self):
+        return (self.tile_expert, self.tile_row0, self.tile_rows, self.num_tiles)
+
+
+def moe_align(idx, K: int, al: MoeAlignment, err: ErrorFlag) -> None:
+    _cuda_contig(idx)
+    _i32(idx)
+    T = idx.numel() // K
+    _need(T * K == al.TK, "moe_align: buffers were sized for another batch")
+    _check(lib().nv_moe_align(_p(idx), c_int(T), c_int(K), c_int(al.E), c_int(al.tile_m), _p(al.counts),
+                              _p(al.offsets), _p(al.cursor), _p(al.sorted_token), _p(al.pair_pos),
+                              _p(al.tile_expert), _p(al.tile_row0), _p(al.tile_rows), _p(al.num_tiles), _p(err.t),
+                              _stream()), "moe_align")
+
+
+def moe_combine(y, pair_pos, score, shared, gate_logit, out) -> None:
+    _cuda_contig(y, pair_pos, score, shared, gate_logit, out)
+    T, K = score.shape
+    H = out.shape[1]
+    for t in (y, score, shared, gate_logit, out):
+        _need(t is None or t.dtype == torch.float32, "moe_combine: float32 tensors")
+    _check(lib().nv_moe_combine(_p(y), _p(pair_pos), _p(score), _p(shared), _p(gate_logit), _p(out), c_int(T),
+                                c_int(K), c_int(H), _stream()), "moe_combine")
+
+
+def silu_mul(gu, out) -> None:
+    _cuda_contig(gu, out)
+    rows, I2 = gu.shape
+    _need(out.shape == (rows, I2 // 2), "silu_mul: out shape")
+    _check(lib().nv_silu_mul(_p(gu), c_int(dt(gu)), _p(out), c_int(dt(out)), c_longlong(rows), c_int(I2 // 2),
+                             _stream()), "silu_mul")
+
+
+def gather_rows(src, rows, dst) -> None:
+    _cuda_contig(src, rows, dst)
+    _i32(rows)
+    _need(src.dtype == dst.dtype and dst.shape == (rows.numel(), src.shape[1]), "gather_rows: shapes")
+    _check(lib().nv_gather_rows(_p(src), c_int(dt(src)), _p(rows), _p(dst), c_int(rows.numel()),
+                                c_int(src.shape[1]), _stream()), "gather_rows")
+
+
+def sample(logits, temperature, u, out) -> None:
+    """One token per row: greedy where temperature <= 0, else inverse-CDF with the given u in [0,1)."""
+    _cuda_contig(logits, temperature, u, out)
+    R, V = logits.shape
+    _need(logits.dtype == torch.float32 and temperature.dtype == torch.float32 and u.dtype == torch.float64,
+          "sample: logits/temperature float32, u float64")
+    _i32(out)
+    _need(temperature.numel() == R and u.numel() == R and out.numel() == R, "sample: one entry per row")
+    _check(lib().nv_sample(_p(logits), c_int(R), c_int(V), _p(temperature), _p(u), _p(out), _stream()), "sample")
+
+
+# ----------------------------------------------------------------------------- fast products
+def gemm_fast_usable(a, w, out, *, bias=None, a_rows=None, swiglu=False, grouped=False) -> bool:
+    """Whether the tensor-core product takes these operands; the plain product takes all."""
+    return False

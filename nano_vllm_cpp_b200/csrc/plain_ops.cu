@@ -1,0 +1,484 @@
+// Plain kernels: one simple, checkable implementation of every op of the model that is not a
+// matrix product.  They are the float32 path's kernels, the bfloat16 path's kernels for every
+// op that has no faster form yet, and the twins that the fast kernels are tested against.
+// Softmax, norms, router probabilities, rotation angles and the residual sum are 32-bit (the
+// router's softmax is 64-bit, as in the reference) whatever the storage type is.
+#include "common.cuh"
+
+namespace {
+
+// ------------------------------------------------------------------ embedding
+// out[t,:] = float(table[ids[t],:])                       (src/hip_ops.hip:553-563)
+__global__ void embedding_kernel(const int* __restrict__ ids, const void* __restrict__ table, int dt,
+                                 float* __restrict__ out, int H, int V, int* __restrict__ err) {
+  int t = blockIdx.x;
+  int id = ids[t];
+  if (id < 0 || id >= V) {
+    if (threadIdx.x == 0) atomicExch(err, 1 + t);
+    id = 0;
+  }
+  for (int i = threadIdx.x; i < H; i += blockDim.x) out[(size_t)t * H + i] = ld_dt(table, dt, (size_t)id * H + i);
+}
+
+// ---------------------------------------------------------- residual add + RMSNorm
+// x += branch (if given); y = x * rsqrt(mean(x^2) + eps) * w     (src/hip_ops.hip:395-417)
+// One block per row.  The sum of squares is taken in a fixed order (a thread's strided
+// elements, then a tree), so a row's result does not depend on the batch.
+__global__ void __launch_bounds__(256) add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ branch,
+                                                          const void* __restrict__ w, int w_dt, float eps,
+                                                          void* __restrict__ out, int out_dt,
+                                                          float* __restrict__ out32, int H) {
+  __shared__ float red[256];
+  size_t base = (size_t)blockIdx.x * H;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += 256) {
+    float v = x[base + i];
+    if (branch) {
+      v += branch[base + i];
+      x[base + i] = v;
+    }
+    ss = fmaf(v, v, ss);
+  }
+  red[threadIdx.x] = ss;
+  __syncthreads();
+  for (int s = 128; s > 0; s >>= 1) {
+    if (threadIdx.x < s) red[threadIdx.x] += red[threadIdx.x + s];
+    __syncthreads();
+  }
+  float inv = rsqrtf(red[0] / (float)H + eps);
+  for (int i = threadIdx.x; i < H; i += 256) {
+    float y = x[base + i] * inv * ld_dt(w, w_dt, i);
+    st_dt(out, out_dt, base + i, y);
+    if (out32) out32[base + i] = y;
+  }
+}
+
+// ------------------------------------------------ rotary position encoding + cache write
+// NeoX pairing (d, d + R/2) over the first R = rotary_dim elements of each head:
+//   ang = float(pos) * inv_freq[d];  o[d] = x[d] cos - x[d+R/2] sin;  o[d+R/2] = x[d+R/2] cos + x[d] sin
+// (src/hip_ops.hip:431-450).  q is rotated in place; k is rotated and written to its page; v is
+// copied to its page (src/hip_ops.hip:452-466).  One block per (row, head of q|k|v).
+// Cache layout: [page][kv head][slot in page][D].
+__global__ void rope_store_kernel(void* __restrict__ qkv, int dt, const int* __restrict__ positions,
+                                  const float* __restrict__ inv_freq, int rotary_dim,
+                                  void* __restrict__ kc, void* __restrict__ vc, int cache_dt,
+                                  const int* __restrict__ block_table, int max_blocks,
+                                  const int* __restrict__ row_entry, int Hq, int Hkv, int D, int page,
+                                  int write_kv, int* __restrict__ err) {
+  const int t = blockIdx.x, h = blockIdx.y;
+  const int width = (Hq + 2 * Hkv) * D;
+  const size_t base = (size_t)t * width + (size_t)h * D;
+  const int pos = positions[t];
+  size_t cbase = 0;
+  const bool is_q = h < Hq, is_k = !is_q && h < Hq + Hkv;
+  if (!is_q) {
+    if (!write_kv) return;
+    int blk = block_table[(size_t)row_entry[t] * max_blocks + pos / page];
+    if (blk < 0) {
+      if (threadIdx.x == 0) atomicExch(err, 1 + t);
+      return;
+    }
+    int kvh = is_k ? h - Hq : h - Hq - Hkv;
+    cbase = (((size_t)blk * Hkv + kvh) * page + pos % page) * D;
+  }
+  if (is_q || is_k) {
+    const int half = rotary_dim / 2;
+    // a thread owns whole pairs, so rotating q in place needs no barrier
+    for (int f = threadIdx.x; f < half; f += blockDim.x) {
+      float ang = (float)pos * inv_freq[f];
+      float c = cosf(ang), s = sinf(ang);
+      float x1 = ld_dt(qkv, dt, base + f), x2 = ld_dt(qkv, dt, base + f + half);
+      float o1 = x1 * c - x2 * s, o2 = x2 * c + x1 * s;
+      if (is_q) {
+        st_dt(qkv, dt, base + f, o1);
+        st_dt(qkv, dt, base + f + half, o2);
+      } else {
+        st_dt(kc, cache_dt, cbase + f, o1);
+        st_dt(kc, cache_dt, cbase + f + half, o2);
+      }
+    }
+    if (is_k)
+      for (int d = rotary_dim + threadIdx.x; d < D; d += blockDim.x)
+        st_dt(kc, cache_dt, cbase + d, ld_dt(qkv, dt, base + d));
+  } else {
+    for (int d = threadIdx.x; d < D; d += blockDim.x) st_dt(vc, cache_dt, cbase + d, ld_dt(qkv, dt, base + d));
+  }
+}
+
+// --------------------------------------------------------------- paged attention (plain)
+// One block per (row, query head).  Row t with position p sees keys [lo, p] where
+// lo = max(0, p + 1 - window) (window 0 = all).  Keys are taken in chunks of 128 from lo
+// upward with an online softmax; everything is fp32 (src/hip_ops.hip:473-551).
+constexpr int ATT_THREADS = 128;
+__global__ void __launch_bounds__(ATT_THREADS) paged_attention_plain_kernel(
+    const void* __restrict__ qkv, int dt, int q_stride, const void* __restrict__ kc, const void* __restrict__ vc,
+    int cache_dt, const int* __restrict__ block_table, int max_blocks, const int* __restrict__ row_entry,
+    const int* __restrict__ positions, float scale, int window, void* __restrict__ out, int out_dt,
+    int Hq, int Hkv, int D, int page) {
+  __shared__ float q[256];
+  __shared__ float p[ATT_THREADS];
+  __shared__ int pslot[ATT_THREADS];   // element offset / D of each key of the chunk
+  __shared__ float red[ATT_THREADS];
+  const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+  const int kvh = h / (Hq / Hkv);
+  const int n = positions[t] + 1;
+  const int lo = window > 0 ? max(0, n - window) : 0;
+  const int* bt = block_table + (size_t)row_entry[t] * max_blocks;
+  for (int d = tid; d < D; d += ATT_THREADS) q[d] = ld_dt(qkv, dt, (size_t)t * q_stride + (size_t)h * D + d);
+  __syncthreads();
+  float m = -1e30f, l = 0.f;
+  float o0 = 0.f, o1 = 0.f;  // this thread's output elements d = tid and tid + 128
+  for (int c0 = lo; c0 < n; c0 += ATT_THREADS) {
+    const int j = c0 + tid;
+    float s = -1e30f;
+    if (j < n) {
+      int blk = bt[j / page];
+      size_t slot = ((size_t)blk * Hkv + kvh) * page + j % page;
+      pslot[tid] = (int)slot;
+      float acc = 0.f;
+      for (int d = 0; d < D; ++d) acc = fmaf(q[d], ld_dt(kc, cache_dt, slot * D + d), acc);
+      s = acc * scale;
+    }
+    red[tid] = s;
+    __syncthreads();
+    for (int st = ATT_THREADS / 2; st > 0; st >>= 1) {
+      if (tid < st) red[tid] = fmaxf(red[tid], red[tid + st]);
+      __syncthreads();
+    }
+    const float m_new = fmaxf(m, red[0]);
+    __syncthreads();
+    const float e = j < n ? expf(s - m_new) : 0.f;
+    p[tid] = e;
+    red[tid] = e;
+    __syncthreads();
+    for (int st = ATT_THREADS / 2; st > 0; st >>= 1) {
+      if (tid < st) red[tid] += red[tid + st];
+      __syncthreads();
+    }
+    const float alpha = expf(m - m_new);
+    l = l * alpha + red[0];
+    m = m_new;
+    const int cnt = min(ATT_THREADS, n - c0);
+    o0 *= alpha;
+    o1 *= alpha;
+    if (tid < D) {
+      for (int i = 0; i < cnt; ++i) o0 = fmaf(p[i], ld_dt(vc, cache_dt, (size_t)pslot[i] * D + tid), o0);
+    }
+    if (tid + ATT_THREADS < D) {
+      for (int i = 0; i < cnt; ++i)
+        o1 = fmaf(p[i], ld_dt(vc, cache_dt, (size_t)pslot[i] * D + tid + ATT_THREADS), o1);
+    }
+    __syncthreads();
+  }
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+  const size_t ob = (size_t)t * Hq * D + (size_t)h * D;
+  if (tid < D) st_dt(out, out_dt, ob + tid, o0 * inv);
+  if (tid + ATT_THREADS < D) st_dt(out, out_dt, ob + tid + ATT_THREADS, o1 * inv);
+}
+
+// ----------------------------------------------------------------------- router
+// One warp per row: p = softmax(logits) over all E in double, then K rounds of "largest
+// remaining, lowest index on a tie", optional renormalisation of the K weights in double
+// (src/hip_ops.hip:813-841).
+__global__ void router_topk_kernel(const float* __restrict__ logits, int T, int E, int K, int renorm,
+                                   int* __restrict__ idx, float* __restrict__ score) {
+  extern __shared__ double sm[];
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int t = blockIdx.x * (blockDim.x / 32) + warp;
+  if (t >= T) return;
+  double* pr = sm + (size_t)warp * E;
+  const float* r = logits + (size_t)t * E;
+  float mx = -INFINITY;
+  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, r[e]);
+  mx = warp_max(mx);
+  double s = 0.0;
+  for (int e = lane; e < E; e += 32) {
+    double v = exp((double)r[e] - (double)mx);
+    pr[e] = v;
+    s += v;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  __syncwarp();
+  for (int e = lane; e < E; e += 32) pr[e] /= s;
+  __syncwarp();
+  double wsum = 0.0;
+  double mine = 0.0;  // lane k keeps the k-th weight (K <= 32 is checked by the launcher)
+  for (int k = 0; k < K; ++k) {
+    double best = -1.0;
+    int bi = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      double v = pr[e];
+      if (v > best) { best = v; bi = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      double ob = __shfl_xor_sync(0xffffffffu, best, o);
+      int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+    }
+    if (lane == k) { mine = best; idx[(size_t)t * K + k] = bi; }
+    wsum += best;
+    if (lane == 0) pr[bi] = -2.0;
+    __syncwarp();
+  }
+  if (lane < K) score[(size_t)t * K + lane] = (float)(renorm ? mine / wsum : mine);
+}
+
+// ------------------------------------------------------------- expert permutation
+// From idx[T*K] build, for the grouped products: counts and offsets per expert, the list of
+// (row, k) pairs sorted by expert (sorted_token = source row of x for each sorted position,
+// pair_pos = sorted position of each pair) and the list of M-tiles (expert, first row, rows).
+// One block.  The order of pairs inside an expert's segment comes from atomics and may differ
+// from run to run; it decides only where a pair's row sits, never a sum's order.
+__global__ void __launch_bounds__(1024) moe_align_kernel(const int* __restrict__ idx, int TK, int K, int E,
+                                                         int tile_m, int* __restrict__ counts,
+                                                         int* __restrict__ offsets, int* __restrict__ cursor,
+                                                         int* __restrict__ sorted_token, int* __restrict__ pair_pos,
+                                                         int* __restrict__ tile_expert, int* __restrict__ tile_row0,
+                                                         int* __restrict__ tile_rows, int* __restrict__ num_tiles,
+                                                         int* __restrict__ err) {
+  const int tid = threadIdx.x;
+  for (int e = tid; e < E; e += 1024) counts[e] = 0;
+  __syncthreads();
+  for (int i = tid; i < TK; i += 1024) {
+    int e = idx[i];
+    if (e < 0 || e >= E) { atomicExch(err, 1 + i); continue; }
+    atomicAdd(&counts[e], 1);
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int off = 0, nt = 0;
+    for (int e = 0; e < E; ++e) {
+      offsets[e] = off;
+      cursor[e] = off;
+      int c = counts[e];
+      for (int r = 0; r < c; r += tile_m) {
+        tile_expert[nt] = e;
+        tile_row0[nt] = off + r;
+        tile_rows[nt] = min(tile_m, c - r);
+        ++nt;
+      }
+      off += c;
+    }
+    offsets[E] = off;
+    *num_tiles = nt;
+  }
+  __syncthreads();
+  for (int i = tid; i < TK; i += 1024) {
+    int e = idx[i];
+    if (e < 0 || e >= E) continue;
+    int p = atomicAdd(&cursor[e], 1);
+    sorted_token[p] = i / K;
+    pair_pos[i] = p;
+  }
+}
+
+// ------------------------------------------------------------------------ combine
+// out[t,:] = sigmoid(gate_logit[t]) * shared[t,:] + sum_k score[t,k] * y[pair_pos[t*K+k],:]
+// with the routed sum taken for k = 0..K-1 in that order, then added to the shared term
+// (src/hip_ops.hip:873-892, 926-934; src/model.cpp:803-811).
+__global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ pair_pos,
+                                   const float* __restrict__ score, const float* __restrict__ shared,
+                                   const float* __restrict__ gate_logit, float* __restrict__ out, int K, int H) {
+  const int t = blockIdx.x;
+  float g = 1.f;
+  if (gate_logit) g = 1.f / (1.f + expf(-gate_logit[t]));
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < H; i += gridDim.y * blockDim.x) {
+    float r = 0.f;
+    for (int k = 0; k < K; ++k) {
+      float w = score[(size_t)t * K + k];
+      r = fmaf(w, y[(size_t)pair_pos[(size_t)t * K + k] * H + i], r);
+    }
+    float sh = shared ? shared[(size_t)t * H + i] * g : 0.f;
+    out[(size_t)t * H + i] = sh + r;
+  }
+}
+
+// ------------------------------------------------------------------------ silu_mul
+// out[r,c] = silu(gu[r,c]) * gu[r,I+c]   (src/hip_ops.hip:419-429) — for callers whose product
+// could not fuse it.
+__global__ void silu_mul_kernel(const void* __restrict__ gu, int dt, void* __restrict__ out, int out_dt,
+                                long long rows, int I) {
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows * I) return;
+  long long r = i / I;
+  int c = (int)(i % I);
+  st_dt(out, out_dt, i, silu_mul(ld_dt(gu, dt, r * 2 * I + c), ld_dt(gu, dt, r * 2 * I + I + c)));
+}
+
+// ------------------------------------------------------------------------ gather rows
+__global__ void gather_rows_kernel(const void* __restrict__ src, int dt, const int* __restrict__ rows,
+                                   void* __restrict__ dst, int H) {
+  int r = rows[blockIdx.x];
+  for (int i = threadIdx.x; i < H; i += blockDim.x)
+    st_dt(dst, dt, (size_t)blockIdx.x * H + i, ld_dt(src, dt, (size_t)r * H + i));
+}
+
+// ------------------------------------------------------------------------ sampling
+// temperature <= 0: the first largest logit.  Otherwise p_i = exp((l_i - max) / T) in double,
+// target = u * sum p, answer = first i whose running sum exceeds target, V-1 if none
+// (include/nanovllm/sampler.hpp:10-34).  One block per row; a thread owns a contiguous run of
+// the vocabulary, so the running sum is taken in index order.
+constexpr int SAMPLE_THREADS = 1024;
+__global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const float* __restrict__ logits, int V,
+                                                                const float* __restrict__ temperature,
+                                                                const double* __restrict__ u,
+                                                                int* __restrict__ out) {
+  __shared__ float fmx[SAMPLE_THREADS];
+  __shared__ int fidx[SAMPLE_THREADS];
+  __shared__ double part[SAMPLE_THREADS];
+  __shared__ int answer;
+  const int row = blockIdx.x, tid = threadIdx.x;
+  const float* l = logits + (size_t)row * V;
+  const int per = (V + SAMPLE_THREADS - 1) / SAMPLE_THREADS;
+  const int b = min(V, tid * per), e = min(V, b + per);
+  float mx = -INFINITY;
+  int mi = 0x7fffffff;
+  for (int i = b; i < e; ++i)
+    if (l[i] > mx) { mx = l[i]; mi = i; }
+  fmx[tid] = mx;
+  fidx[tid] = mi;
+  __syncthreads();
+  for (int s = SAMPLE_THREADS / 2; s > 0; s >>= 1) {
+    if (tid < s) {
+      float o = fmx[tid + s];
+      int oi = fidx[tid + s];
+      if (o > fmx[tid] || (o == fmx[tid] && oi < fidx[tid])) { fmx[tid] = o; fidx[tid] = oi; }
+    }
+    __syncthreads();
+  }
+  const float T = temperature[row];
+  if (T <= 0.f) {
+    if (tid == 0) out[row] = fidx[0] == 0x7fffffff ? 0 : fidx[0];
+    return;
+  }
+  const double mxd = (double)fmx[0], inv_t = 1.0 / (double)T;
+  double s = 0.0;
+  for (int i = b; i < e; ++i) s += exp(((double)l[i] - mxd) * inv_t);
+  part[tid] = s;
+  if (tid == 0) answer = V - 1;
+  __syncthreads();
+  // exclusive prefix over 1024 partial sums: Hillis-Steele on shared memory
+  for (int off = 1; off < SAMPLE_THREADS; off <<= 1) {
+    double v = tid >= off ? part[tid - off] : 0.0;
+    __syncthreads();
+    part[tid] += v;
+    __syncthreads();
+  }
+  const double total = part[SAMPLE_THREADS - 1];
+  const double target = u[row] * total;
+  const double before = tid ? part[tid - 1] : 0.0;
+  if (before <= target && part[tid] > target) {
+    double cum = before;
+    int a = -1;
+    for (int i = b; i < e; ++i) {
+      cum += exp(((double)l[i] - mxd) * inv_t);
+      if (cum > target) { a = i; break; }
+    }
+    atomicMin(&answer, a >= 0 ? a : max(b, e - 1));
+  }
+  __syncthreads();
+  if (tid == 0) out[row] = answer;
+}
+
+}  // namespace
+
+// =============================================================================== launchers
+
+NV_API const char* nv_error_string(int code) { return cudaGetErrorString((cudaError_t)code); }
+
+NV_API int nv_embedding(const int* ids, const void* table, int table_dt, float* out, int T, int H, int V,
+                        int* err, cudaStream_t s) {
+  if (!dt_ok(table_dt)) return NV_ERR_BAD_DTYPE;
+  if (T == 0) return NV_OK;
+  embedding_kernel<<<T, 256, 0, s>>>(ids, table, table_dt, out, H, V, err);
+  NV_RETURN_LAST();
+}
+
+NV_API int nv_add_rmsnorm(float* x, const float* branch, const void* w, int w_dt, float eps, void* out,
+                          int out_dt, float* out32, int T, int H, cudaStream_t s) {
+  if (!dt_ok(w_dt) || !dt_ok(out_dt)) return NV_ERR_BAD_DTYPE;
+  if (T == 0) return NV_OK;
+  add_rmsnorm_kernel<<<T, 256, 0, s>>>(x, branch, w, w_dt, eps, out, out_dt, out32, H);
+  NV_RETURN_LAST();
+}
+
+NV_API int nv_rope_store(void* qkv, int dt, const int* positions, const float* inv_freq, int rotary_dim,
+                         void* kc, void* vc, int cache_dt, const int* block_table, int max_blocks,
+                         const int* row_entry, int T, int Hq, int Hkv, int D, int page, int write_kv, int* err,
+                         cudaStream_t s) {
+  if (!dt_ok(dt) || !dt_ok(cache_dt)) return NV_ERR_BAD_DTYPE;
+  if (rotary_dim < 0 || rotary_dim > D || rotary_dim % 2) return NV_ERR_BAD_SIZE;
+  if (T == 0) return NV_OK;
+  dim3 grid(T, Hq + 2 * Hkv);
+  int threads = D <= 32 ? 32 : (D <= 64 ? 64 : (D <= 128 ? 128 : 256));
+  if (D > 256 || D % 2) return NV_ERR_UNSUPPORTED;
+  rope_store_kernel<<<grid, threads, 0, s>>>(qkv, dt, positions, inv_freq, rotary_dim, kc, vc, cache_dt,
+                                             block_table, max_blocks, row_entry, Hq, Hkv, D, page, write_kv, err);
+  NV_RETURN_LAST();
+}
+
+NV_API int nv_paged_attention_plain(const void* qkv, int dt, int q_stride, const void* kc, const void* vc,
+                                    int cache_dt, const int* block_table, int max_blocks, const int* row_entry,
+                                    const int* positions, float scale, int window, void* out, int out_dt, int T,
+                                    int Hq, int Hkv, int D, int page, cudaStream_t s) {
+  if (!dt_ok(dt) || !dt_ok(cache_dt) || !dt_ok(out_dt)) return NV_ERR_BAD_DTYPE;
+  if (D > 256 || D <= 0 || Hkv <= 0 || Hq % Hkv) return NV_ERR_UNSUPPORTED;
+  if (T == 0) return NV_OK;
+  dim3 grid(T, Hq);
+  paged_attention_plain_kernel<<<grid, ATT_THREADS, 0, s>>>(qkv, dt, q_stride, kc, vc, cache_dt, block_table,
+                                                            max_blocks, row_entry, positions, scale, window, out,
+                                                            out_dt, Hq, Hkv, D, page);
+  NV_RETURN_LAST();
+}
+
+NV_API int nv_router_topk(const float* logits, int T, int E, int K, int renorm, int* idx, float* score,
+                          cudaStream_t s) {
+  if (K < 1 || K > E || K > 32) return NV_ERR_UNSUPPORTED;
+  if (T == 0) return NV_OK;
+  const int warps = 4;
+  size_t smem = (size_t)warps * E * sizeof(double);
+  if (smem > 48 * 1024) return NV_ERR_UNSUPPORTED;  // E <= 1536
+  router_topk_kernel<<<(T + warps - 1) / warps, warps * 32, smem, s>>>(logits, T, E, K, renorm, idx, score);
+  NV_RETURN_LAST();
+}
+
+NV_API int nv_moe_align(const int* idx, int T, int K, int E, int tile_m, int* counts, int* offsets, int* cursor,
+                        int* sorted_token, int* pair_pos, int* tile_expert, int* tile_row0, int* tile_rows,
+                        int* num_tiles, int* err, cudaStream_t s) {
+  if (tile_m <= 0 || K <= 0 || E <= 0) return NV_ERR_BAD_SIZE;
+  moe_align_kernel<<<1, 1024, 0, s>>>(idx, T * K, K, E, tile_m, counts, offsets, cursor, sorted_token, pair_pos,
+                                      tile_expert, tile_row0, tile_rows, num_tiles, err);
+  NV_RETURN_LAST();
+}
+
+NV_API int nv_moe_combine(const float* y, const int* pair_pos, const float* score, const float* shared,
+                          const float* gate_logit, float* out, int T, int K, int H, cudaStream_t s) {
+  if (T == 0) return NV_OK;
+  dim3 grid(T, (H + 1023) / 1024);
+  moe_combine_kernel<<<grid, 256, 0, s>>>(y, pair_pos, score, shared, gate_logit, out, K, H);
+  NV_RETURN_LAST();
+}
+
+NV_API int nv_silu_mul(const void* gu, int dt, void* out, int out_dt, long long rows, int I, cudaStream_t s) {
+  if (!dt_ok(dt) || !dt_ok(out_dt)) return NV_ERR_BAD_DTYPE;
+  long long n = rows * I;
+  if (n == 0) return NV_OK;
+  silu_mul_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(gu, dt, out, out_dt, rows, I);
+  NV_RETURN_LAST();
+}
+
+NV_API int nv_gather_rows(const void* src, int dt, const int* rows, void* dst, int R, int H, cudaStream_t s) {
+  if (!dt_ok(dt)) return NV_ERR_BAD_DTYPE;
+  if (R == 0) return NV_OK;
+  gather_rows_kernel<<<R, 256, 0, s>>>(src, dt, rows, dst, H);
+  NV_RETURN_LAST();
+}
+
+NV_API int nv_sample(const float* logits, int R, int V, const float* temperature, const double* u, int* out,
+                     cudaStream_t s) {
+  if (R == 0) return NV_OK;
+  sample_kernel<<<R, SAMPLE_THREADS, 0, s>>>(logits, V, temperature, u, out);
+  NV_RETURN_LAST();
+}

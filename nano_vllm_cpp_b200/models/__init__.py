@@ -1,0 +1,1 @@
+"""Architectures: each module turns its typed configuration into a ``ModelSpec`` and registers itself."""

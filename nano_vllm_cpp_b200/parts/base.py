@@ -1,0 +1,106 @@
+"""Interfaces of the parts a layer is put together from.
+
+A part knows its own sizes and constants and the names of its own tensors (relative to a
+prefix that the model gives it); it does not know which model or which layer it is in.
+
+===================  =======================================================================
+part                 what it must provide
+===================  =======================================================================
+``Norm``             ``forward(x, branch, want_f32)``: add ``branch`` (or nothing) to the
+                     float32 residual stream ``x`` in place, return the normalised rows in the
+                     run's activation dtype and, if asked, a float32 copy of them
+``PositionEncoding`` ``rotary_dim`` and ``inv_freq()``: what the rotation kernel needs; a part
+                     with ``rotary_dim == 0`` encodes nothing
+``Mixer``            ``cache_spec()``: what it keeps per request (pages of keys and values, a
+                     fixed-size state, or nothing); ``forward(h, batch, cache)`` -> float32
+                     ``[T, hidden]`` branch output
+``FeedForward``      ``wants_f32_input``; ``forward(h, h32, batch)`` -> float32 ``[T, hidden]``
+===================  =======================================================================
+
+All parts also provide ``tensor_specs(available)`` (name -> shape and how to draw it at
+random) and ``load(fetch, ctx)``, which binds device tensors fetched by name.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Callable, Optional
+
+import torch
+
+
+@dataclass(frozen=True)
+class TensorSpec:
+    shape: tuple
+    init: str = "normal"      # "normal": N(0, std) | "ones": 1 (+ N(0, norm_std) if asked) | "zeros"
+    kind: str = "matrix"      # "matrix" | "vector": vectors are held in float32 on the device
+
+
+@dataclass(frozen=True)
+class KVCacheSpec:
+    """Keys and values in pages; ``window`` > 0: only the last ``window`` positions are read."""
+    num_kv_heads: int
+    head_dim: int
+    window: int = 0
+
+
+@dataclass(frozen=True)
+class StateCacheSpec:
+    """A fixed-size state per request, zeroed when a request gets its slot."""
+    shape: tuple
+    dtype: torch.dtype = torch.float32
+
+
+@dataclass
+class RunContext:
+    """What a part needs from the run it is loaded into."""
+    device: torch.device
+    act_dtype: torch.dtype           # float32 or bfloat16: storage type of activations and caches
+    err: object = None               # csrc.ops.ErrorFlag
+    page_size: int = 16
+    fast_kernels: bool = True        # False: plain kernels everywhere (the twin path of the tests)
+
+
+Fetch = Callable[[str], torch.Tensor]
+
+
+class Part:
+    def tensor_specs(self, available=None) -> dict:
+        """``available(name) -> bool`` tells which of several accepted layouts a file holds."""
+        return {}
+
+    def load(self, fetch: Fetch, ctx: RunContext) -> None:
+        self.ctx = ctx
+
+
+class Norm(Part):
+    def forward(self, x, branch, want_f32: bool = False):
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    rotary_dim: int = 0
+
+    def inv_freq(self):
+        raise NotImplementedError
+
+
+class Mixer(Part):
+    def cache_spec(self):
+        return None
+
+    def forward(self, h, batch, cache):
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    wants_f32_input: bool = False
+
+    def forward(self, h, h32, batch):
+        raise NotImplementedError
+
+
+@dataclass
+class PartSpec:
+    """A part as data: its registered kind and the parameters of its constructor."""
+    kind: str
+    params: dict = field(default_factory=dict)

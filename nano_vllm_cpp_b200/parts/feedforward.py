@@ -1,0 +1,132 @@
+"""Feed-forward parts: the dense SwiGLU MLP and the sparse mixture of SwiGLU experts with a
+softmax router, top-k routing and an optional sigmoid-gated shared expert."""
+from __future__ import annotations
+
+import torch
+
+from ..csrc import ops
+from .base import FeedForward, TensorSpec
+from .linear import linear, grouped_linear
+from .registry import register_part
+
+
+class DenseSwiGLU(FeedForward):
+    """``down(silu(gate(h)) * up(h))`` (src/model.cpp:828-832; src/hip_ops.hip:419-429)."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int):
+        self.hidden, self.inter = hidden_size, intermediate_size
+
+    def tensor_specs(self, available=None):
+        H, I = self.hidden, self.inter
+        return {"gate_proj.weight": TensorSpec((I, H)), "up_proj.weight": TensorSpec((I, H)),
+                "down_proj.weight": TensorSpec((H, I))}
+
+    def load(self, fetch, ctx):
+        self.ctx = ctx
+        # gate rows then up rows in one matrix (src/model.cpp:589-596)
+        self.gate_up = _cat([fetch("gate_proj.weight"), fetch("up_proj.weight")])
+        self.down = fetch("down_proj.weight")
+
+    def forward(self, h, h32, batch):
+        act = linear(self.ctx, h, self.gate_up, self.ctx.act_dtype, swiglu=True)
+        return linear(self.ctx, act, self.down, torch.float32)
+
+
+class SparseMoeSwiGLU(FeedForward):
+    """Per row (src/model.cpp:789-827; src/hip_ops.hip:813-893, 926-934):
+
+    router logits ``r = h Wg^T`` in float32; ``p = softmax(r)`` over all experts; the ``top_k``
+    largest (ties to the lower index) with weights ``p`` or ``p / sum`` (``renormalize``);
+    ``routed = sum_k w_k * down_e(silu(gate_e(h)) * up_e(h))`` for k in rank order;
+    ``shared = sigmoid(h . w_gate) * down_s(silu(gate_s(h)) * up_s(h))`` if there is a shared
+    expert; the result is ``shared + routed``.
+    """
+    wants_f32_input = True
+
+    def __init__(self, hidden_size: int, num_experts: int, top_k: int, intermediate_size: int,
+                 shared_intermediate_size: int = 0, renormalize: bool = False):
+        if not (1 <= top_k <= num_experts):
+            raise ValueError("top_k must lie in 1..num_experts")
+        if top_k > 32 or num_experts > 1536:
+            raise ValueError("the router kernel takes up to 32 experts per row out of up to 1536")
+        self.hidden, self.E, self.K = hidden_size, num_experts, top_k
+        self.inter, self.shared_inter, self.renorm = intermediate_size, shared_intermediate_size, renormalize
+        self._align = {}
+
+    def tensor_specs(self, available=None):
+        H, I, E, SI = self.hidden, self.inter, self.E, self.shared_inter
+        s = {"gate.weight": TensorSpec((E, H))}
+        if available is not None and available("experts.gate_up_proj"):  # stacked form, src/model.cpp:274-281
+            s["experts.gate_up_proj"] = TensorSpec((E, 2 * I, H))
+            s["experts.down_proj"] = TensorSpec((E, H, I))
+        else:
+            for e in range(E):
+                s[f"experts.{e}.gate_proj.weight"] = TensorSpec((I, H))
+                s[f"experts.{e}.up_proj.weight"] = TensorSpec((I, H))
+                s[f"experts.{e}.down_proj.weight"] = TensorSpec((H, I))
+        if SI > 0:
+            s["shared_expert.gate_proj.weight"] = TensorSpec((SI, H))
+            s["shared_expert.up_proj.weight"] = TensorSpec((SI, H))
+            s["shared_expert.down_proj.weight"] = TensorSpec((H, SI))
+            s["shared_expert_gate.weight"] = TensorSpec((1, H))
+        return s
+
+    def load(self, fetch, ctx):
+        self.ctx = ctx
+        H, I, E = self.hidden, self.inter, self.E
+        self.router = fetch("gate.weight")
+        if fetch.has("experts.gate_up_proj"):
+            self.w_gate_up = fetch("experts.gate_up_proj").contiguous()
+            self.w_down = fetch("experts.down_proj").contiguous()
+        else:
+            first = fetch("experts.0.gate_proj.weight")
+            # every expert's [gate; up] rows and down matrix in one block each, indexed by expert
+            self.w_gate_up = torch.empty((E, 2 * I, H), dtype=first.dtype, device=first.device)
+            self.w_down = torch.empty((E, H, I), dtype=first.dtype, device=first.device)
+            for e in range(E):
+                self.w_gate_up[e, :I].copy_(first if e == 0 else fetch(f"experts.{e}.gate_proj.weight"))
+                self.w_gate_up[e, I:].copy_(fetch(f"experts.{e}.up_proj.weight"))
+                self.w_down[e].copy_(fetch(f"experts.{e}.down_proj.weight"))
+            del first
+        if self.shared_inter > 0:
+            self.sh_gate_up = _cat([fetch("shared_expert.gate_proj.weight"), fetch("shared_expert.up_proj.weight")])
+            self.sh_down = fetch("shared_expert.down_proj.weight")
+            self.sh_gate = fetch("shared_expert_gate.weight")
+
+    def _alignment(self, TK, device):
+        tile_m = ops.gemm_plain_tile_m()
+        key = (TK, tile_m)
+        if key not in self._align:
+            self._align[key] = ops.MoeAlignment(TK, self.E, tile_m, device)
+        return self._align[key]
+
+    def forward(self, h, h32, batch):
+        ctx = self.ctx
+        T = h.shape[0]
+        dev = h.device
+        logits = linear(ctx, h32, self.router, torch.float32)
+        idx = torch.empty((T, self.K), dtype=torch.int32, device=dev)
+        score = torch.empty((T, self.K), dtype=torch.float32, device=dev)
+        ops.router_topk(logits, self.K, self.renorm, idx, score)
+        al = self._alignment(T * self.K, dev)
+        ops.moe_align(idx, self.K, al, ctx.err)
+        act = grouped_linear(ctx, h, self.w_gate_up, ctx.act_dtype, al, a_rows=al.sorted_token, swiglu=True)
+        y = grouped_linear(ctx, act, self.w_down, torch.float32, al)
+        shared = gate_logit = None
+        if self.shared_inter > 0:
+            sact = linear(ctx, h, self.sh_gate_up, ctx.act_dtype, swiglu=True)
+            shared = linear(ctx, sact, self.sh_down, torch.float32)
+            gate_logit = linear(ctx, h32, self.sh_gate, torch.float32)
+        out = torch.empty((T, self.hidden), dtype=torch.float32, device=dev)
+        ops.moe_combine(y, al.pair_pos, score, shared, gate_logit, out)
+        return out
+
+
+def _cat(ts):
+    if len({t.dtype for t in ts}) > 1:
+        ts = [t.float() for t in ts]
+    return torch.cat(ts, dim=0).contiguous()
+
+
+register_part("feed_forward", "dense_swiglu", DenseSwiGLU)
+register_part("feed_forward", "sparse_moe_swiglu", SparseMoeSwiGLU)

@@ -1,0 +1,43 @@
+"""Matrix products of the parts: picks the kernel for a product's types and sizes.
+
+float32 anywhere in the operands -> the plain FFMA kernel (true 32-bit, no tensor cores).
+bfloat16 x bfloat16 -> the tcgen05 kernel when its size rules hold, else the plain kernel.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..csrc import ops
+
+
+def linear(ctx, a, w, out_dtype, *, bias=None, a_rows=None, swiglu=False, M=None, out=None):
+    """``out = a[a_rows] @ w.T (+ bias)``; with ``swiglu`` w is [2N, K] (gate rows, then up rows)
+    and ``out = silu(a @ gate.T) * (a @ up.T)``."""
+    rows_w = w.shape[0]
+    N = rows_w // 2 if swiglu else rows_w
+    if M is None:
+        M = a_rows.numel() if a_rows is not None else a.shape[0]
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    if M == 0:
+        return out
+    if ctx.fast_kernels and ops.gemm_fast_usable(a, w, out, bias=bias, a_rows=a_rows, swiglu=swiglu):
+        ops.gemm_fast(a, w, out, bias=bias, a_rows=a_rows, swiglu=swiglu, M=M)
+    else:
+        ops.gemm_plain(a, w, out, bias=bias, a_rows=a_rows, swiglu=swiglu, M=M)
+    return out
+
+
+def grouped_linear(ctx, a, w, out_dtype, align, *, a_rows=None, swiglu=False):
+    """Per-expert product over an expert-sorted row list: row r of the output belongs to the expert
+    whose segment of ``align`` holds r and is ``a[a_rows[r]] @ w[expert].T``."""
+    rows_w = w.shape[1]
+    N = rows_w // 2 if swiglu else rows_w
+    out = torch.empty((align.TK, N), dtype=out_dtype, device=a.device)
+    if align.TK == 0:
+        return out
+    if ctx.fast_kernels and ops.gemm_fast_usable(a, w, out, a_rows=a_rows, swiglu=swiglu, grouped=True):
+        ops.gemm_fast_grouped(a, w, out, align, a_rows=a_rows, swiglu=swiglu)
+    else:
+        ops.gemm_plain(a, w, out, a_rows=a_rows, swiglu=swiglu, M=align.TK, tiles=align.tiles)
+    return out

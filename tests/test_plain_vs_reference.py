@@ -1,0 +1,48 @@
+"""The plain implementation against the reference's own CPU forward pass (recorded output of
+tools/ref_top5.cpp, see tests/golden/make_golden.py): top-5 ids and logits of the last position
+and the routed experts and weights of the last token."""
+import json
+import os
+import sys
+
+import pytest
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(HERE, "golden"))
+import make_golden  # noqa: E402
+import plain_model  # noqa: E402
+
+with open(os.path.join(HERE, "golden", "ref_top5.json")) as f:
+    GOLD = json.load(f)
+
+
+@pytest.mark.parametrize("key", sorted(GOLD))
+def test_plain_matches_reference_cpu(key, tmp_path):
+    cname, _ = key.split("/")
+    mdir = make_golden.tiny_model(make_golden.CASES[cname], str(tmp_path / cname))
+    cfg, W = plain_model.read_folder(mdir)
+    g = GOLD[key]
+    logits = plain_model.forward(cfg, W, g["ids"])[-1]
+    top = torch.topk(logits, 5)
+    assert [int(i) for i in top.indices] == [t[0] for t in g["top5"]]
+    for v, (_, want) in zip(top.values, g["top5"]):
+        assert abs(float(v) - want) <= 6e-4          # the reference prints three decimals
+    # routing of the last token in every sparse layer
+    eps = cfg["rms_norm_eps"]
+    x = plain_model.embedding(W["model.embed_tokens.weight"], g["ids"])
+    for l in range(cfg["num_hidden_layers"]):
+        p = f"model.layers.{l}."
+        h = plain_model.rms_norm(x, W[p + "input_layernorm.weight"], eps)
+        x = x + plain_model.attention_layer(h, W, p + "self_attn.", cfg, l, list(range(len(g["ids"]))))
+        h = plain_model.rms_norm(x, W[p + "post_attention_layernorm.weight"], eps)
+        if plain_model.layer_is_sparse(cfg, l):
+            idx, w = plain_model.route(h, W[p + "mlp.gate.weight"], cfg["num_experts_per_tok"], cfg["norm_topk_prob"])
+            want = g["routes"][str(l)]
+            assert [int(i) for i in idx[-1]] == [r[0] for r in want]
+            for a, r in zip(w[-1], want):
+                assert abs(float(a) - r[1]) <= 6e-5  # four decimals
+            x = x + plain_model.sparse_mlp(h, W, p + "mlp.", cfg)
+        else:
+            assert str(l) not in g["routes"]
+            x = x + plain_model.dense_mlp(h, W, p + "mlp.")
