@@ -1,0 +1,85 @@
+"""Device side of the cache: the page pools of keys and values and the per-request state arrays.
+
+For every call of the model's order that owns a cache entry there is either a pair of tensors
+``k, v`` shaped ``[pages, kv_heads, page_size, head_dim]`` — a page's rows of one head are
+contiguous — or a state tensor ``[slots, *shape]``.  Calls whose attention has the same window
+form a group and share page ids (the same page index addresses the same slice in each of
+them, as in the reference's pool: src/model.cpp:642-645).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from ..parts.base import KVCacheSpec, StateCacheSpec
+
+
+@dataclass
+class CacheView:
+    kind: str                      # "kv" | "state" | "none"
+    group: int = -1
+    k: Optional[torch.Tensor] = None
+    v: Optional[torch.Tensor] = None
+    state: Optional[torch.Tensor] = None
+    write: bool = True
+    page_size: int = 0
+
+
+class DeviceCache:
+    def __init__(self, cache_specs: list, page_size: int, max_slots: int, device, dtype):
+        self.page_size, self.device, self.dtype, self.max_slots = page_size, device, dtype, max_slots
+        self.specs = cache_specs
+        self.windows: list = []                    # one per group
+        self.entry_group: list = []
+        for s in cache_specs:
+            if isinstance(s, KVCacheSpec):
+                if s.window not in self.windows:
+                    self.windows.append(s.window)
+                self.entry_group.append(self.windows.index(s.window))
+            else:
+                self.entry_group.append(-1)
+        self.views: list = []
+        self.num_pages: list = []
+
+    def bytes_per_page(self) -> list:
+        """Per group: bytes of one page over all its entries."""
+        item = torch.empty((), dtype=self.dtype).element_size()
+        out = [0] * len(self.windows)
+        for s, g in zip(self.specs, self.entry_group):
+            if isinstance(s, KVCacheSpec):
+                out[g] += 2 * s.num_kv_heads * self.page_size * s.head_dim * item
+        return out
+
+    def allocate(self, num_pages) -> None:
+        if isinstance(num_pages, int):
+            num_pages = [num_pages] * len(self.windows)
+        self.num_pages = list(num_pages)
+        self.views = []
+        for s, g in zip(self.specs, self.entry_group):
+            if isinstance(s, KVCacheSpec):
+                shape = (max(1, num_pages[g]), s.num_kv_heads, self.page_size, s.head_dim)
+                k = torch.zeros(shape, dtype=self.dtype, device=self.device)
+                v = torch.zeros(shape, dtype=self.dtype, device=self.device)
+                self.views.append(CacheView("kv", g, k, v, None, True, self.page_size))
+            elif isinstance(s, StateCacheSpec):
+                st = torch.zeros((self.max_slots, *s.shape), dtype=s.dtype, device=self.device)
+                self.views.append(CacheView("state", -1, None, None, st, True, self.page_size))
+            elif isinstance(s, tuple) and s[0] == "shared":
+                self.views.append(None)
+            else:
+                self.views.append(CacheView("none"))
+        for i, s in enumerate(self.specs):
+            if isinstance(s, tuple) and s[0] == "shared":
+                o = self.views[s[1]]
+                self.views[i] = CacheView(o.kind, o.group, o.k, o.v, o.state, False, o.page_size)
+
+    def view(self, call_index: int) -> CacheView:
+        return self.views[call_index]
+
+    def reset_slot(self, slot: int) -> None:
+        """A request has just been given this slot: its states start from zero."""
+        for v in self.views:
+            if v.kind == "state" and v.write:
+                v.state[slot].zero_()

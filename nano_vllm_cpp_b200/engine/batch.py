@@ -1,0 +1,109 @@
+"""The flat arrays of one step: a packed batch of (request, its next tokens).
+
+The reference fills the same information into ``Context`` per step (include/nanovllm/context.hpp:10-24,
+built in src/model_runner.cpp:43-128) but for either prompt chunks or decode tokens; here any mix
+is one batch.  All index arrays travel to the device in one copy of one pinned int32 buffer.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import numpy as np
+import torch
+
+
+@dataclass
+class StepEntry:
+    """The next tokens of one request and the places among them whose logits are wanted."""
+    rid: object
+    tokens: list
+    want: list = field(default_factory=list)
+
+
+@dataclass
+class EntryInfo:
+    rid: object
+    slot: int       # state slot of the request
+    pos0: int       # position of the entry's first row
+    length: int
+    row0: int       # first row of the entry in the batch
+
+
+@dataclass
+class StepBatch:
+    T: int                          # rows (tokens) in the batch
+    S: int                          # entries (requests) in the batch
+    input_ids: torch.Tensor         # [T] int32
+    positions: torch.Tensor         # [T] int32
+    row_entry: torch.Tensor         # [T] int32: entry of each row
+    cu_rows: torch.Tensor           # [S+1] int32: first row of each entry, then T
+    entry_pos0: torch.Tensor        # [S] int32
+    entry_slot: torch.Tensor        # [S] int32
+    want_rows: torch.Tensor         # [n_want] int32
+    block_tables: list              # per group: [S, max_blocks] int32, -1 = no page
+    entries: list                   # list[EntryInfo] (host)
+    max_rows: int                   # longest entry
+    max_context: int                # largest pos0 + length
+    decode_only: bool               # every entry has one row
+
+
+def _align4(n: int) -> int:
+    return (n + 3) & ~3
+
+
+def build_batch(entries: list, infos: list, tables: list, max_blocks: int, device) -> StepBatch:
+    """``infos``: EntryInfo per entry; ``tables``: per group, per entry, the list of page ids."""
+    S = len(entries)
+    T = sum(len(e.tokens) for e in entries)
+    n_want = sum(len(e.want) for e in entries)
+    G = len(tables)
+    seg = {}
+    off = 0
+    for name, n in (("ids", T), ("pos", T), ("row_entry", T), ("cu", S + 1), ("pos0", S), ("slot", S),
+                    ("want", n_want)):
+        seg[name] = (off, n)
+        off = _align4(off + n)
+    for g in range(G):
+        seg[f"bt{g}"] = (off, S * max_blocks)
+        off = _align4(off + S * max_blocks)
+    host = np.full(max(off, 4), -1, dtype=np.int32)
+
+    def put(name, values):
+        o, n = seg[name]
+        host[o:o + n] = values
+
+    ids, pos, row_entry, cu, want = [], [], [], [0], []
+    for i, (e, info) in enumerate(zip(entries, infos)):
+        n = len(e.tokens)
+        ids.extend(e.tokens)
+        pos.extend(range(info.pos0, info.pos0 + n))
+        row_entry.extend([i] * n)
+        for w in e.want:
+            if not (0 <= w < n):
+                raise ValueError(f"request {e.rid!r}: wanted place {w} is not among its {n} tokens")
+            want.append(info.row0 + w)
+        cu.append(cu[-1] + n)
+    put("ids", ids), put("pos", pos), put("row_entry", row_entry), put("cu", cu)
+    put("pos0", [i.pos0 for i in infos]), put("slot", [i.slot for i in infos]), put("want", want)
+    for g in range(G):
+        o, _ = seg[f"bt{g}"]
+        for i, table in enumerate(tables[g]):
+            if len(table) > max_blocks:
+                raise ValueError("a request holds more pages than the block table is wide")
+            host[o + i * max_blocks:o + i * max_blocks + len(table)] = table
+    pinned = torch.from_numpy(host)
+    if torch.device(device).type == "cuda":
+        pinned = pinned.pin_memory()
+    dev = pinned.to(device, non_blocking=True)
+
+    def view(name):
+        o, n = seg[name]
+        return dev[o:o + n]
+
+    return StepBatch(
+        T=T, S=S, input_ids=view("ids"), positions=view("pos"), row_entry=view("row_entry"), cu_rows=view("cu"),
+        entry_pos0=view("pos0"), entry_slot=view("slot"), want_rows=view("want"),
+        block_tables=[view(f"bt{g}").view(S, max_blocks) for g in range(G)], entries=list(infos),
+        max_rows=max((i.length for i in infos), default=0),
+        max_context=max((i.pos0 + i.length for i in infos), default=0),
+        decode_only=all(i.length == 1 for i in infos))

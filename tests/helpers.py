@@ -1,0 +1,100 @@
+"""Shared pieces of the tests: the two tiny configurations, model folders in temporary places,
+plain-implementation logits, and a replay driver over the engine's step function."""
+import os
+import sys
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(HERE, "golden"))
+import make_golden  # noqa: E402
+import plain_model  # noqa: E402
+
+CASES = make_golden.CASES
+
+# Tolerances, fixed before the first GPU run.  float32: sums of at most a few hundred float32
+# products against float64 -> 1e-5 absolute on logits of order one.  bfloat16: activations are
+# rounded to 8 bits of mantissa (2^-9 relative) a few times per layer; over the layers of the
+# tiny models that gives errors of the order of one percent of the largest logit.
+TOL = {"float32": dict(abs=1e-5, rel=1e-5), "bfloat16": dict(abs=2e-2, rel=3e-2)}
+
+
+def model_folder(case_name, tmp_path_factory_or_dir):
+    d = tmp_path_factory_or_dir
+    if hasattr(d, "mktemp"):
+        d = str(d.mktemp(f"model_{case_name}"))
+    return make_golden.tiny_model(CASES[case_name], os.path.join(str(d), case_name))
+
+
+def prompt(case_name, n, salt=0):
+    rs = np.random.RandomState(7000 + ord(case_name[0]) * 131 + n * 17 + salt)
+    return [int(x) for x in rs.randint(0, CASES[case_name]["config"]["vocab_size"], size=n)]
+
+
+_plain_cache = {}
+
+
+def plain_logits(mdir, ids):
+    """float64 logits [T, V] of the plain implementation for one whole sequence (cached)."""
+    key = (mdir, tuple(ids))
+    if key not in _plain_cache:
+        if mdir not in _plain_cache:
+            _plain_cache[mdir] = plain_model.read_folder(mdir)
+        cfg, W = _plain_cache[mdir]
+        _plain_cache[key] = plain_model.forward(cfg, W, list(ids))
+    return _plain_cache[key]
+
+
+def assert_close(got, want, dtype, what=""):
+    got = torch.as_tensor(got, dtype=torch.float64).cpu()
+    want = torch.as_tensor(want, dtype=torch.float64).cpu()
+    assert got.shape == want.shape, f"{what}: shape {tuple(got.shape)} vs {tuple(want.shape)}"
+    tol = TOL[dtype]
+    bound = tol["abs"] + tol["rel"] * want.abs().max()
+    err = (got - want).abs()
+    if not bool((err <= bound).all()):
+        bad = torch.nonzero(err > bound)
+        first = bad[0].tolist()
+        raise AssertionError(f"{what}: {len(bad)} of {err.numel()} values differ by more than {float(bound):.3g}; "
+                             f"max {float(err.max()):.3g}; first at {first}: got {float(got[tuple(first)]):.6g}, "
+                             f"want {float(want[tuple(first)]):.6g}")
+
+
+class Replay:
+    """Drives ModelRunner.step with a schedule and collects logits per (request, position)."""
+
+    def __init__(self, runner):
+        from nano_vllm_cpp_b200.engine.batch import StepEntry
+        self.runner, self.StepEntry = runner, StepEntry
+        self.fed = {}          # rid -> tokens fed so far
+        self.logits = {}       # (rid, position) -> float32 row
+
+    def step(self, parts, end=()):
+        """parts: list of (rid, tokens, want_all or list of places)."""
+        entries = []
+        for rid, toks, want in parts:
+            places = list(range(len(toks))) if want is True else list(want)
+            entries.append(self.StepEntry(rid, list(toks), places))
+        out = self.runner.step(entries).float().cpu()
+        r = 0
+        for e in entries:
+            if e.rid not in self.fed:      # a new request under an id used before: forget the old rows
+                for key in [k for k in self.logits if k[0] == e.rid]:
+                    del self.logits[key]
+            base = self.fed.get(e.rid, 0)
+            for w in e.want:
+                self.logits[(e.rid, base + w)] = out[r]
+                r += 1
+            self.fed[e.rid] = base + len(e.tokens)
+        for rid in end:
+            self.runner.close(rid)
+            self.fed.pop(rid, None)
+        self.runner.manager.check()
+
+    def compare(self, rid, ids, mdir, dtype, what):
+        want = plain_logits(mdir, ids)
+        pos = sorted(p for (r, p) in self.logits if r == rid)
+        assert pos, f"{what}: no logits were collected for {rid}"
+        got = torch.stack([self.logits[(rid, p)] for p in pos])
+        assert_close(got, want[pos], dtype, f"{what} request {rid}")

@@ -1,0 +1,135 @@
+"""The engine against the plain implementation, for every way of cutting the work into steps:
+whole, last 32 tokens one by one, portions of changing size, and mixed batches on a pool so small
+that pages are used again.  Both tiny configurations, float32 and bfloat16."""
+import pytest
+import torch
+
+import helpers
+from helpers import Replay, prompt
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = {"A": [5, 17, 33, 70], "B": [1, 9, 24, 40, 70]}
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    return {c: helpers.model_folder(c, tmp_path_factory) for c in ("A", "B")}
+
+
+def make_runner(mdir, dtype, max_tokens, max_requests=4):
+    from nano_vllm_cpp_b200.engine.runner import ModelRunner
+    return ModelRunner(mdir, dtype=dtype, max_tokens=max_tokens, max_requests=max_requests)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("case", ["A", "B"])
+def test_whole(case, dtype, folders):
+    runner = make_runner(folders[case], dtype, 128)
+    rp = Replay(runner)
+    for n in LENGTHS[case]:
+        ids = prompt(case, n)
+        rp.step([(f"r{n}", ids, True)], end=[f"r{n}"])
+        rp.compare(f"r{n}", ids, folders[case], dtype, f"whole {case} n={n}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("case", ["A", "B"])
+def test_last_32_one_by_one(case, dtype, folders):
+    runner = make_runner(folders[case], dtype, 128)
+    rp = Replay(runner)
+    for n in (40, 70, 100):
+        ids = prompt(case, n, salt=1)
+        head = n - 32
+        rp.step([("x", ids[:head], [head - 1])])
+        for t in range(head, n):
+            rp.step([("x", ids[t:t + 1], [0])])
+        rp.compare("x", ids, folders[case], dtype, f"decode {case} n={n}")
+        rp.step([], end=["x"])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("case", ["A", "B"])
+def test_portions_of_changing_size(case, dtype, folders):
+    runner = make_runner(folders[case], dtype, 128)
+    rp = Replay(runner)
+    ids = prompt(case, 101, salt=2)
+    sizes = [7, 2, 16, 1, 3, 31, 2, 17, 2, 5, 15]
+    assert sum(sizes) == 101
+    at = 0
+    for s in sizes:
+        rp.step([("p", ids[at:at + s], True)])
+        at += s
+    rp.compare("p", ids, folders[case], dtype, f"portions {case}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("case", ["A", "B"])
+def test_mixed_with_page_reuse(case, dtype, folders):
+    """Up to four live requests; portions of some beside decode tokens of others; the pool holds 192
+    tokens while the requests need 5 x 64 in turn, so finished requests' pages are used again."""
+    runner = make_runner(folders[case], dtype, 192)
+    rp = Replay(runner)
+    L = {"a": 50, "b": 37, "c": 64, "d": 20, "e": 61, "f": 33}
+    ids = {r: prompt(case, n, salt=ord(r)) for r, n in L.items()}
+    at = {r: 0 for r in L}
+
+    def take(r, n, want=True):
+        toks = ids[r][at[r]:at[r] + n]
+        at[r] += len(toks)
+        return (r, toks, want)
+
+    rp.step([take("a", 30), take("b", 2)])
+    rp.step([take("a", 1), take("b", 20), take("c", 7)])
+    rp.step([take("a", 1), take("b", 1), take("c", 40)])
+    rp.step([take("a", 18), take("b", 14), take("c", 1)], end=["a", "b"])   # a, b finished: 50, 37
+    rp.step([take("c", 1), take("d", 20), take("e", 3)], end=["d"])
+    rp.step([take("c", 15), take("e", 2), take("f", 30)], end=["c"])
+    rp.step([take("e", 56), take("f", 1)])
+    rp.step([take("f", 2)], end=["e", "f"])
+    for r in L:
+        assert at[r] == L[r]
+        rp.compare(r, ids[r], folders[case], dtype, f"mixed {case}")
+    for pool in runner.manager.pools:
+        assert pool.num_free() == pool.num_pages
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_first_tokens_and_long_decoding(dtype, folders):
+    """Positions 0, 1, 2 alone, then 150 tokens one by one (beyond several pages and the window)."""
+    case = "B"
+    runner = make_runner(folders[case], dtype, 192)
+    rp = Replay(runner)
+    ids = prompt(case, 150, salt=3)
+    for t in range(150):
+        rp.step([("l", ids[t:t + 1], [0])])
+    rp.compare("l", ids, folders[case], dtype, "long decode")
+
+
+def test_trace_run_program(folders, tmp_path):
+    """bin/trace_run as a user starts it: JSON lines in, <step>.f32 files and 'done' lines out."""
+    import json, os, subprocess, sys
+    import numpy as np
+    case, dtype = "A", "float32"
+    ids = prompt(case, 40, salt=4)
+    ids2 = prompt(case, 9, salt=5)
+    steps = [
+        {"step": 0, "entries": [{"id": "a", "tokens": ids[:10], "want": [9]}], "end": []},
+        {"step": 1, "entries": [{"id": "a", "tokens": ids[10:38], "want": []}, {"id": "b", "tokens": ids2, "want": [0, 8]}], "end": ["b"]},
+        {"step": 2, "entries": [{"id": "a", "tokens": ids[38:], "want": [0, 1]}], "end": ["a"]},
+    ]
+    out = tmp_path / "out"
+    exe = os.path.join(os.path.dirname(helpers.HERE), "bin", "trace_run")
+    r = subprocess.run([sys.executable, exe, "--model", folders[case], "--dtype", dtype, "--out", str(out),
+                        "--max-tokens", "128"], input="\n".join(json.dumps(s) for s in steps) + "\n",
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [l for l in r.stdout.splitlines() if l.startswith("done")] == ["done 0", "done 1", "done 2"]
+    V = helpers.CASES[case]["config"]["vocab_size"]
+    ref_a, ref_b = helpers.plain_logits(folders[case], ids), helpers.plain_logits(folders[case], ids2)
+    s0 = np.fromfile(out / "0.f32", dtype="<f4").reshape(-1, V)
+    s1 = np.fromfile(out / "1.f32", dtype="<f4").reshape(-1, V)
+    s2 = np.fromfile(out / "2.f32", dtype="<f4").reshape(-1, V)
+    helpers.assert_close(s0, ref_a[[9]], dtype, "step 0")
+    helpers.assert_close(s1, ref_b[[0, 8]], dtype, "step 1")
+    helpers.assert_close(s2, ref_a[[38, 39]], dtype, "step 2")
