@@ -1,0 +1,151 @@
+"""The Python entry point, in the reference's manner (include/nanovllm/llm_engine.hpp:20-38):
+
+    engine = LLMEngine(model_dir, max_model_len=4096, num_kv_blocks=0)
+    outs = engine.generate([[1, 2, 3], [4, 5]], SamplingParams(temperature=0.0, max_tokens=16))
+
+``generate`` takes prompts as lists of token ids (the tokenizer is outside this engine) and returns
+one ``{"token_ids": [...]}`` per prompt, ordered by request id as the reference's does
+(src/llm_engine.cpp:120-133).  ``add_request`` / ``step`` / ``is_finished`` drive it by hand.
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass, field
+
+from ..config.engine_config import EngineConfig, SamplingParams
+from ..sampling import Sampler, uniform
+from .batch import StepEntry
+from .runner import ModelRunner
+from .scheduler import Scheduler
+from .sequence import Sequence
+
+
+@dataclass
+class StepOutput:
+    finished: list                                  # [(seq_id, completion token ids)]
+    num_prefill_tokens: int = 0
+    num_decode_tokens: int = 0
+    new_tokens: list = field(default_factory=list)  # [(seq_id, token)] for every token drawn this step
+
+
+class LLMEngine:
+    def __init__(self, model: str, max_model_len: int = 4096, num_kv_blocks: int = 0, **kwargs):
+        cfg = EngineConfig(model=model, max_model_len=max_model_len,
+                           num_kvcache_blocks=num_kv_blocks if num_kv_blocks else -1)
+        random_weights = kwargs.pop("random_weights", False)
+        norm_std = kwargs.pop("norm_std", 0.0)
+        std = kwargs.pop("std", None)
+        for k, v in kwargs.items():
+            if not hasattr(cfg, k):
+                raise TypeError(f"unknown engine option {k!r}")
+            setattr(cfg, k, v)
+        cfg.validate()
+        self.config = cfg
+        self.runner = ModelRunner(
+            model, dtype=cfg.dtype, page_size=cfg.kvcache_block_size,
+            num_pages=cfg.num_kvcache_blocks if cfg.num_kvcache_blocks > 0 else None,
+            max_requests=cfg.max_num_seqs, max_model_len=cfg.max_model_len, device=cfg.device,
+            random_seed=cfg.seed if random_weights else None, norm_std=norm_std, std=std,
+            gpu_memory_utilization=cfg.gpu_memory_utilization, prefix_caching=cfg.enable_prefix_caching)
+        mc = self.runner.config
+        max_pos = getattr(mc, "max_position_embeddings", None)
+        if max_pos:                                              # include/nanovllm/config.hpp:269
+            cfg.max_model_len = min(cfg.max_model_len, max_pos)
+        cfg.max_model_len = min(cfg.max_model_len, self.runner.max_model_len)
+        if cfg.eos < 0:
+            cfg.eos = self._eos_from_files(model, getattr(mc, "eos_token_id", -1))
+        self.scheduler = Scheduler(self.runner.manager, max_num_seqs=cfg.max_num_seqs,
+                                   max_num_batched_tokens=cfg.max_num_batched_tokens,
+                                   max_model_len=cfg.max_model_len, eos=cfg.eos, prefill_chunk=cfg.prefill_chunk)
+        self.sampler = Sampler(self.runner.device)
+
+    @staticmethod
+    def _eos_from_files(model_dir: str, from_config: int) -> int:
+        """generation_config.json's ``eos_token_id`` (first of a list) wins over config.json's, as in
+        include/nanovllm/config.hpp:213-232; -1 = no stop token."""
+        import json
+        path = os.path.join(model_dir, "generation_config.json")
+        try:
+            with open(path) as f:
+                e = json.load(f).get("eos_token_id")
+            if isinstance(e, list) and e:
+                return int(e[0])
+            if isinstance(e, int):
+                return e
+        except (OSError, ValueError):
+            pass
+        return from_config
+
+    # ------------------------------------------------------------------ requests
+    @property
+    def vocab_size(self) -> int:
+        return self.runner.vocab_size
+
+    @property
+    def eos_token(self) -> int:
+        return self.config.eos
+
+    def add_request(self, prompt_ids, sampling: SamplingParams | None = None) -> int:
+        sp = sampling or SamplingParams()
+        sp.validate()
+        ids = [int(t) for t in prompt_ids]
+        if not ids:
+            raise ValueError("empty prompt token ids")
+        if len(ids) + sp.max_tokens > self.config.max_model_len:      # src/llm_engine.cpp:71
+            raise ValueError("prompt + max_tokens exceeds max_model_len")
+        bad = [t for t in ids if not (0 <= t < self.vocab_size)]
+        if bad:
+            raise ValueError(f"token id {bad[0]} is outside the vocabulary [0, {self.vocab_size})")
+        seq = Sequence(ids, sp, base_seed=self.config.seed)
+        self.scheduler.add(seq)
+        return seq.seq_id
+
+    def is_finished(self) -> bool:
+        return self.scheduler.is_finished()
+
+    # ------------------------------------------------------------------ one step
+    def step(self) -> StepOutput:
+        scheduled = self.scheduler.schedule()
+        if not scheduled:
+            return StepOutput([])
+        entries, temps, us, sampled_seqs = [], [], [], []
+        n_prefill = n_decode = 0
+        for s in scheduled:
+            toks = s.seq.token_ids[s.start:s.start + s.count]
+            entries.append(StepEntry(s.seq.seq_id, toks, [s.count - 1] if s.samples else []))
+            if s.samples:
+                temps.append(s.seq.temperature)
+                us.append(uniform(s.seq.seed, s.seq.num_completion_tokens))
+                sampled_seqs.append(s.seq)
+            if s.count == 1 and s.start >= s.seq.num_prompt_tokens:
+                n_decode += 1
+            else:
+                n_prefill += s.count
+        logits = self.runner.step(entries)
+        tokens = self.sampler.sample(logits, temps, us)
+        sampled = {seq.seq_id: tok for seq, tok in zip(sampled_seqs, tokens)}
+        finished = self.scheduler.postprocess(scheduled, sampled)
+        return StepOutput([(q.seq_id, q.completion_token_ids) for q in finished], n_prefill, n_decode,
+                          list(sampled.items()))
+
+    # ------------------------------------------------------------------ generate
+    def generate(self, prompts, sampling_params=None) -> list:
+        """``prompts``: list of token-id lists.  ``sampling_params``: one for all or one per prompt."""
+        if sampling_params is None or isinstance(sampling_params, SamplingParams):
+            sps = [sampling_params or SamplingParams()] * len(prompts)
+        else:
+            sps = list(sampling_params)
+            if len(sps) != len(prompts):
+                raise ValueError("prompts and sampling params size mismatch")      # src/llm_engine.cpp:107
+        for p, sp in zip(prompts, sps):
+            if isinstance(p, str):
+                raise TypeError("this engine takes token ids; tokenize outside it")
+            self.add_request(p, sp)
+        completed = {}
+        while not self.is_finished():
+            for seq_id, toks in self.step().finished:
+                completed[seq_id] = toks
+        return [{"token_ids": completed[k]} for k in sorted(completed)]
+
+
+LLM = LLMEngine

@@ -26,7 +26,7 @@ from __future__ import annotations
 from collections import deque
 from dataclasses import dataclass
 
-from ..cache import CacheManager
+from ..cache import CacheManager, NoFreePages
 from .sequence import Sequence, SequenceStatus
 
 
@@ -80,12 +80,18 @@ class Scheduler:
         budget = self.max_num_batched_tokens
 
         # 1. one token for every running sequence, oldest first
+        preempted_before = self.num_preemptions
         kept: deque = deque()
         while self.running and len(out) < self.max_num_seqs and budget > 0:
             seq = self.running.popleft()
             n = self._cached(seq)
             ok = True
-            while not self.manager.can_extend(seq.seq_id, n, n + 1):
+            while True:
+                try:
+                    self.manager.extend(seq.seq_id, n, n + 1)   # takes the page now (src/scheduler.cpp:75)
+                    break
+                except NoFreePages:
+                    pass
                 if self.running:
                     self.preempt(self.running.pop())
                 elif kept and kept[-1] is not seq:
@@ -106,7 +112,8 @@ class Scheduler:
         self.running = kept
 
         # 2. prompt portions from the waiting queue, in order
-        while self.waiting and len(out) < self.max_num_seqs and budget > 0:
+        while (self.waiting and len(out) < self.max_num_seqs and budget > 0
+               and self.num_preemptions == preempted_before):   # no admission in a step that had to preempt
             seq = self.waiting[0]
             opened_here = False
             if not self.manager.has(seq.seq_id):
@@ -125,7 +132,9 @@ class Scheduler:
                 opened_here = True
             start = self._cached(seq)
             count = min(seq.num_tokens - start, budget, self.prefill_chunk or budget)
-            if not self.manager.can_extend(seq.seq_id, start, start + count):
+            try:
+                self.manager.extend(seq.seq_id, start, start + count)
+            except NoFreePages:
                 if opened_here:
                     self.manager.close(seq.seq_id)
                 break

@@ -1,0 +1,281 @@
+"""The cache manager and the scheduler on the host: no page lost, held twice or freed twice under
+random orders of requests; windows give pages back; prefix pages are shared; the scheduler's
+decisions under a token budget and when pages run out."""
+import random
+
+import pytest
+
+from nano_vllm_cpp_b200.cache import BlockPool, CacheManager, NoFreePages, NoFreeSlot, chain_hash
+from nano_vllm_cpp_b200.config import SamplingParams
+from nano_vllm_cpp_b200.engine.scheduler import Scheduler, SchedulerError
+from nano_vllm_cpp_b200.engine.sequence import Sequence
+
+
+# ------------------------------------------------------------------------------- block pool
+def test_pool_order_and_double_release():
+    p = BlockPool(4, 16)
+    a, b = p.allocate(), p.allocate()
+    assert (a, b) == (0, 1)                      # fresh pages come from the front
+    p.release(a)
+    assert p.allocate() == 2 and p.allocate() == 3 and p.allocate() == 0   # a freed page goes to the back
+    with pytest.raises(NoFreePages):
+        p.allocate()
+    p.release(b)
+    with pytest.raises(RuntimeError):
+        p.release(b)                             # freed twice
+    p.check()
+
+
+def test_pool_hash_revival():
+    p = BlockPool(3, 4)
+    a = p.allocate()
+    h = chain_hash([1, 2, 3, 4], None)
+    p.set_hash(a, h, [1, 2, 3, 4])
+    p.release(a)
+    assert p.lookup(h, [1, 2, 3, 4]) == a        # a freed page keeps its hash ...
+    assert p.lookup(h, [1, 2, 3, 5]) is None
+    p.share(a)                                   # ... and can be revived
+    assert p.ref_count[a] == 1 and p.num_free() == 2
+    p.release(a)
+    p.allocate(), p.allocate()
+    assert p.allocate() == a and p.lookup(h, [1, 2, 3, 4]) is None   # handed out again: hash forgotten
+    assert chain_hash([1, 2], None) != chain_hash([1, 2], 7) != chain_hash([2, 1], 7)
+
+
+# ------------------------------------------------------------------------------- cache manager
+def test_manager_pages_and_slots():
+    m = CacheManager([0], 8, 16, max_requests=2)
+    m.open("a")
+    m.extend("a", 0, 17)
+    assert len(m.get("a").tables[0]) == 2
+    m.commit("a", 17)
+    m.extend("a", 17, 32)
+    assert len(m.get("a").tables[0]) == 2        # position 31 still lies in the second page
+    m.commit("a", 32)
+    m.extend("a", 32, 33)
+    assert len(m.get("a").tables[0]) == 3
+    with pytest.raises(RuntimeError):
+        m.extend("a", 40, 41)                    # rows must continue where the cache ends
+    m.open("b")
+    with pytest.raises(NoFreeSlot):
+        m.open("c")
+    assert m.pages_needed("b", 0, 16 * 5) == [5] and m.can_extend("b", 0, 16 * 5)
+    assert not m.can_extend("b", 0, 16 * 5 + 1)
+    with pytest.raises(NoFreePages):
+        m.extend("b", 0, 16 * 5 + 1)
+    m.check()
+    m.close("a")
+    m.close("b")
+    m.check()
+    assert m.pools[0].num_free() == 8 and m.free_slots() == 2
+
+
+def test_windowed_group_gives_pages_back():
+    m = CacheManager([0, 16], [16, 6], 16, max_requests=1)
+    m.open("r")
+    n = 0
+    for step in [5, 30, 1, 1, 40, 1, 1, 64, 1]:
+        m.extend("r", n, n + step)
+        n += step
+        m.commit("r", n)
+        full, win = m.get("r").tables
+        assert all(p >= 0 for p in full) and len(full) == (n + 15) // 16
+        live = [i for i, p in enumerate(win) if p >= 0]
+        # the next row (position n) reads keys n-15 .. n: pages from (n-15)//16 on are still there
+        assert all(win[i] >= 0 for i in range(max(0, n - 15) // 16, len(win)))
+        m.check()
+    m.extend("r", n, n + 1)
+    win = m.get("r").tables[1]
+    assert sum(1 for p in win if p >= 0) <= 2    # one page of history plus the page being written
+    # a portion too long for the windowed pool is refused: its own rows need the pages at once
+    m.close("r")
+    m.open("s")
+    with pytest.raises(NoFreePages):
+        m.extend("s", 0, 16 * 6 + 1)
+    m.close("s")
+    m.check()
+
+
+def test_random_request_orders_lose_no_page():
+    rng = random.Random(0)
+    for trial in range(30):
+        windows = rng.choice([[0], [0, 16], [0, 8, 32]])
+        m = CacheManager(windows, rng.choice([6, 12, 40]), 16, max_requests=4)
+        live, next_id = {}, 0
+        for _ in range(300):
+            op = rng.random()
+            if op < 0.25 and len(live) < 4:
+                m.open(next_id)
+                live[next_id] = 0
+                next_id += 1
+            elif op < 0.35 and live:
+                rid = rng.choice(list(live))
+                m.close(rid)
+                del live[rid]
+            elif live:
+                rid = rng.choice(list(live))
+                n = rng.choice([1, 1, 1, 2, 7, 16, 33])
+                start = live[rid]
+                if m.can_extend(rid, start, start + n):
+                    m.extend(rid, start, start + n)
+                    m.commit(rid, start + n)
+                    live[rid] = start + n
+                else:
+                    with pytest.raises(NoFreePages):
+                        m.extend(rid, start, start + n)
+            m.check()
+        for rid in list(live):
+            m.close(rid)
+        m.check()
+        assert all(p.num_free() == p.num_pages for p in m.pools) and m.free_slots() == 4
+
+
+def test_prefix_pages_are_shared_and_never_the_last():
+    m = CacheManager([0], 16, 4, max_requests=4, prefix_caching=True)
+    toks = list(range(100, 111))                 # 11 tokens: two full pages and a part
+    m.open("a")
+    m.extend("a", 0, 11)
+    m.commit("a", 11, toks)
+    assert m.get("a").hashed_pages == 2
+    matched = m.match_prefix(toks)               # the same prompt again: both full pages hit
+    assert [p for p, _ in matched] == m.get("a").tables[0][:2]
+    assert len(m.match_prefix(toks[:8])) == 1    # 8 tokens = exactly two pages: the last one is left to run
+    assert m.match_prefix([1] + toks[1:]) == []
+    m.open("b")
+    assert m.adopt_prefix("b", matched) == 8
+    m.extend("b", 8, 11)
+    assert m.get("b").tables[0][:2] == m.get("a").tables[0][:2] and m.get("b").tables[0][2] != m.get("a").tables[0][2]
+    m.check()
+    m.close("a")
+    m.check()                                    # shared pages stay with b
+    m.close("b")
+    matched = m.match_prefix(toks)               # both gone, hashes kept: revival
+    assert len(matched) == 2 and m.new_pages_for(11, matched) == 3
+    m.open("c")
+    m.adopt_prefix("c", matched)
+    m.check()
+    # windows switch prefix sharing off: a hit must be a hit in every group
+    assert not CacheManager([0, 16], 8, 4, 2, prefix_caching=True).prefix_caching
+
+
+# ------------------------------------------------------------------------------- scheduler
+def drive(sched, seqs, rng, max_steps=10000, check=None):
+    """Runs the scheduler with a stand-in for the model (random tokens); returns per-step records."""
+    for s in seqs:
+        sched.add(s)
+    records = []
+    for _ in range(max_steps):
+        if sched.is_finished():
+            return records
+        out = sched.schedule()
+        assert out, "an unfinished scheduler must schedule something"
+        assert len({s.seq.seq_id for s in out}) == len(out)
+        assert sum(s.count for s in out) <= sched.max_num_batched_tokens
+        assert len(out) <= sched.max_num_seqs
+        for s in out:                               # the runner's view: pages are there for every row
+            rc = sched.manager.get(s.seq.seq_id)
+            assert rc.num_tokens == s.start
+            assert all(len(t) * sched.manager.page_size >= s.start + s.count for t in rc.tables)
+            assert s.samples == (s.start + s.count == s.seq.num_tokens)
+        sched.manager.check()
+        sampled = {s.seq.seq_id: rng.randrange(2, 50) for s in out if s.samples}
+        records.append([(s.seq.seq_id, s.start, s.count, s.samples) for s in out])
+        sched.postprocess(out, sampled)
+        sched.manager.check()
+        if check:
+            check(out)
+    raise AssertionError("the scheduler did not finish")
+
+
+def make_sched(pages, *, windows=(0,), budget=64, max_seqs=8, prefix=False, chunk=0, max_len=4096, eos=-1):
+    m = CacheManager(list(windows), pages, 16, max_requests=max_seqs, prefix_caching=prefix)
+    return Scheduler(m, max_num_seqs=max_seqs, max_num_batched_tokens=budget, max_model_len=max_len, eos=eos,
+                     prefill_chunk=chunk)
+
+
+def test_budget_portions_and_mixed_steps():
+    rng = random.Random(1)
+    sched = make_sched(64, budget=32)
+    seqs = [Sequence(list(range(2, 2 + n)), SamplingParams(max_tokens=6, ignore_eos=True)) for n in (70, 5, 40)]
+    rec = drive(sched, seqs, rng)
+    a = seqs[0].seq_id
+    # the 70-token prompt is cut into 32 + 32 + 6; the rest of the third step's budget goes to the next prompt
+    assert rec[0] == [(a, 0, 32, False)] and rec[1] == [(a, 32, 32, False)]
+    assert rec[2][0] == (a, 64, 6, True) and rec[2][1][:3] == (seqs[1].seq_id, 0, 5)
+    # later steps hold decode tokens of running sequences beside prompt portions of waiting ones
+    assert any(any(c == 1 and st >= 70 for (_, st, c, _) in step) and any(c > 1 for (_, _, c, _) in step) for step in rec)
+    assert all(s.is_finished and s.num_completion_tokens == 6 for s in seqs)
+    assert all(p.num_free() == p.num_pages for p in sched.manager.pools)
+
+
+def test_prefill_chunk_cap():
+    sched = make_sched(64, budget=64, chunk=10)
+    seq = Sequence(list(range(2, 27)), SamplingParams(max_tokens=1))
+    rec = drive(sched, [seq], random.Random(2))
+    assert [r[0][2] for r in rec] == [10, 10, 5]
+
+
+def test_eos_max_tokens_and_max_model_len():
+    sched = make_sched(64, eos=7, max_len=12)
+    s1 = Sequence([2, 3, 4], SamplingParams(max_tokens=50))
+    s2 = Sequence([2, 3, 4], SamplingParams(max_tokens=50, ignore_eos=True))
+    sched.add(s1), sched.add(s2)
+    out = sched.schedule()
+    sched.postprocess(out, {s1.seq_id: 7, s2.seq_id: 7})
+    assert s1.is_finished and not s2.is_finished          # the stop token ends s1 only
+    while not sched.is_finished():
+        out = sched.schedule()
+        sched.postprocess(out, {s.seq.seq_id: 9 for s in out})
+    assert s2.num_tokens == 12                            # stopped by max_model_len
+
+
+def test_out_of_pages_preempts_newest_and_everything_finishes():
+    rng = random.Random(3)
+    # 3 requests x (20 prompt + 30 new) = 150 tokens -> 12 pages needed at the end; the pool has 8
+    sched = make_sched(8, budget=64)
+    seqs = [Sequence(list(range(2, 22)), SamplingParams(max_tokens=30, ignore_eos=True)) for _ in range(3)]
+    rec = drive(sched, seqs, rng)
+    assert sched.num_preemptions > 0
+    assert seqs[0].num_preemptions == 0                   # the oldest request is never the victim here
+    assert all(s.is_finished and s.num_completion_tokens == 30 for s in seqs)
+    # a preempted request comes back with prompt and generated tokens as one prefill from position 0
+    victim = max(seqs, key=lambda s: s.num_preemptions)
+    again = [e for step in rec for e in step if e[0] == victim.seq_id and e[1] == 0]
+    assert len(again) >= 2 and again[-1][2] > 20
+    assert all(p.num_free() == p.num_pages for p in sched.manager.pools)
+
+
+def test_random_workloads_with_tight_pools():
+    rng = random.Random(4)
+    for trial in range(25):
+        windows = rng.choice([(0,), (0, 16)])
+        sched = make_sched(rng.choice([8, 10, 16]), windows=windows, budget=rng.choice([16, 48, 200]),
+                           max_seqs=rng.choice([2, 4, 8]), prefix=rng.random() < 0.5, chunk=rng.choice([0, 0, 7]))
+        seqs = []
+        for _ in range(rng.randrange(1, 9)):
+            n = rng.choice([1, 3, 16, 17, 40, 64])
+            base = rng.choice([100, 200])                 # common prefixes on purpose
+            seqs.append(Sequence([base + i for i in range(n)], SamplingParams(max_tokens=rng.choice([1, 5, 30]), ignore_eos=True)))
+        drive(sched, seqs, rng)
+        assert all(s.is_finished for s in seqs)
+        assert all(p.num_free() == p.num_pages for p in sched.manager.pools)
+        assert sched.manager.free_slots() == sched.max_num_seqs
+
+
+def test_pool_smaller_than_one_request_is_an_error():
+    sched = make_sched(2, budget=64)
+    sched.add(Sequence(list(range(2, 42)), SamplingParams(max_tokens=4)))
+    with pytest.raises(SchedulerError, match="could not make progress"):
+        for _ in range(10):
+            out = sched.schedule()
+            sched.postprocess(out, {s.seq.seq_id: 5 for s in out if s.samples})
+
+
+def test_prefix_hit_skips_cached_pages():
+    sched = make_sched(32, budget=256, prefix=True)
+    p = list(range(2, 50))                                # 48 tokens = 3 full pages
+    s1 = Sequence(p, SamplingParams(max_tokens=2, ignore_eos=True))
+    drive(sched, [s1], random.Random(5))
+    s2 = Sequence(p + [60, 61], SamplingParams(max_tokens=2, ignore_eos=True))
+    rec = drive(sched, [s2], random.Random(5))
+    assert rec[0] == [(s2.seq_id, 48, 2, True)]           # the three cached pages are not run again
