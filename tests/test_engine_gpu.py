@@ -1,0 +1,115 @@
+"""Generation through the Python entry point and the command line: greedy tokens equal the plain
+implementation's, sampled tokens equal the plain sampler's on the engine's logits, a preempted
+request resumes with the same tokens, and batch composition does not change a request's tokens."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import helpers
+from helpers import prompt
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    return {c: helpers.model_folder(c, tmp_path_factory) for c in ("A", "B")}
+
+
+def engine(mdir, **kw):
+    from nano_vllm_cpp_b200 import LLMEngine
+    kw.setdefault("dtype", "float32")
+    kw.setdefault("max_num_seqs", 8)
+    return LLMEngine(mdir, kw.pop("max_model_len", 128), kw.pop("num_kv_blocks", 64), **kw)
+
+
+def plain_greedy(mdir, ids, n):
+    cfg, W = helpers.plain_model.read_folder(mdir)
+    return helpers.plain_model.greedy_generate(cfg, W, ids, n)
+
+
+@pytest.mark.parametrize("case", ["A", "B"])
+def test_greedy_generation_equals_plain(case, folders):
+    from nano_vllm_cpp_b200 import SamplingParams
+    lengths = {"A": [5, 17, 33], "B": [1, 9, 24]}[case]
+    prompts = [prompt(case, n, salt=9) for n in lengths]
+    eng = engine(folders[case])
+    outs = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True))
+    for p, o in zip(prompts, outs):
+        assert o["token_ids"] == plain_greedy(folders[case], p, 12)
+
+
+def test_temperature_sampling_is_reproducible_and_follows_the_plain_sampler(folders):
+    from nano_vllm_cpp_b200 import SamplingParams
+    from nano_vllm_cpp_b200.sampling import uniform
+    case = "B"
+    prompts = [prompt(case, n, salt=10) for n in (1, 9, 24, 40, 70)]
+    sps = [SamplingParams(temperature=0.8, max_tokens=24, ignore_eos=True, seed=100 + i) for i in range(5)]
+    a = engine(folders[case], max_model_len=128).generate(prompts, sps)
+    b = engine(folders[case], max_model_len=128, max_num_batched_tokens=16, max_num_seqs=2).generate(prompts, sps)
+    assert [o["token_ids"] for o in a] == [o["token_ids"] for o in b]      # same seeds, other batching
+    # every token is the plain sampler's choice on the plain logits of its prefix with the same u
+    cfg, W = helpers.plain_model.read_folder(folders[case])
+    ids = list(prompts[1])
+    for k, tok in enumerate(a[1]["token_ids"][:8]):
+        logits = helpers.plain_model.forward(cfg, W, ids)[-1].float().numpy()
+        assert helpers.plain_model.sample(logits, 0.8, uniform(101, k)) == tok
+        ids.append(tok)
+
+
+def test_preempted_request_resumes_with_the_same_tokens(folders):
+    from nano_vllm_cpp_b200 import SamplingParams
+    case = "A"
+    prompts = [prompt(case, 20, salt=20 + i) for i in range(3)]
+    sp = [SamplingParams(temperature=0.7, max_tokens=30, ignore_eos=True, seed=5 + i) for i in range(3)]
+    roomy = engine(folders[case], num_kv_blocks=64)
+    want = [o["token_ids"] for o in roomy.generate(prompts, sp)]
+    tight = engine(folders[case], num_kv_blocks=8)          # 150 tokens needed at the end, 128 fit
+    got = [o["token_ids"] for o in tight.generate(prompts, sp)]
+    assert tight.scheduler.num_preemptions > 0
+    assert got == want
+
+
+def test_sample_kernel_against_plain_sampler():
+    from nano_vllm_cpp_b200.csrc import ops
+    g = torch.Generator().manual_seed(0)
+    for V in (5, 384, 1000, 151936):
+        R = 6
+        logits = (torch.randn(R, V, generator=g) * 3).cuda()
+        temps = torch.tensor([0.0, 0.5, 1.0, 2.0, 0.01, 1.3])
+        us = torch.tensor([0.3, 0.0, 0.999999, 0.5, 0.7, 0.123], dtype=torch.float64)
+        out = torch.empty(R, dtype=torch.int32, device="cuda")
+        ops.sample(logits, temps.cuda(), us.cuda(), out)
+        want = [helpers.plain_model.sample(logits[r].cpu().numpy(), float(temps[r]), float(us[r])) for r in range(R)]
+        assert out.tolist() == want
+    tie = torch.zeros(2, 100).cuda()
+    tie[0, 7] = tie[0, 50] = 3.0
+    out = torch.empty(2, dtype=torch.int32, device="cuda")
+    ops.sample(tie, torch.zeros(2).cuda(), torch.zeros(2, dtype=torch.float64).cuda(), out)
+    assert out.tolist() == [7, 0]                            # the first largest logit
+
+
+def test_command_line(folders):
+    exe = os.path.join(os.path.dirname(helpers.HERE), "bin", "nanovllm")
+    ids = prompt("A", 5, salt=9)
+    r = subprocess.run([sys.executable, exe, folders["A"], "--tokens", ",".join(map(str, ids)), "--max-tokens", "6",
+                        "--temperature", "0", "--dtype", "float32", "--max-model-len", "64", "--num-kv-blocks", "8",
+                        "--ignore-eos"], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    line = [l for l in r.stdout.splitlines() if l.startswith("token_ids:")][0]
+    assert [int(x) for x in line.split()[1:]] == plain_greedy(folders["A"], ids, 6)
+    r = subprocess.run([sys.executable, exe, "--bench", folders["A"], "--num-seqs", "3", "--max-tokens", "4",
+                        "--max-model-len", "128", "--num-kv-blocks", "32"], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert "PP: 192 tokens" in r.stdout and "decode:" in r.stdout
+    r = subprocess.run([sys.executable, exe, folders["A"], "hello"], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 2 and "token ids" in r.stderr
+
+
+def test_smoke_entry():
+    sys.path.insert(0, os.path.dirname(helpers.HERE))
+    import __graft_entry__
+    __graft_entry__.smoke()
