@@ -38,7 +38,17 @@ def lib() -> ctypes.CDLL:
     return _lib
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """How many launcher calls have been made so far (each launches this library's kernels)."""
+    return _launches
+
+
 def _check(code: int, what: str) -> None:
+    global _launches
+    _launches += 1
     if code == 0:
         return
     if code < 0:

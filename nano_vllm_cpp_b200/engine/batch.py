@@ -45,6 +45,7 @@ class StepBatch:
     max_rows: int                   # longest entry
     max_context: int                # largest pos0 + length
     decode_only: bool               # every entry has one row
+    h2d_bytes: int = 0              # bytes of index arrays copied to the device for this step
 
 
 def _align4(n: int) -> int:
@@ -106,4 +107,4 @@ def build_batch(entries: list, infos: list, tables: list, max_blocks: int, devic
         block_tables=[view(f"bt{g}").view(S, max_blocks) for g in range(G)], entries=list(infos),
         max_rows=max((i.length for i in infos), default=0),
         max_context=max((i.pos0 + i.length for i in infos), default=0),
-        decode_only=all(i.length == 1 for i in infos))
+        decode_only=all(i.length == 1 for i in infos), h2d_bytes=int(host.nbytes))

@@ -56,6 +56,7 @@ class ModelRunner:
         self.manager = CacheManager(self.cache.windows or [0], num_pages, page_size, max_requests,
                                     prefix_caching=prefix_caching)
         self.num_pages = num_pages
+        self.last_h2d_bytes = 0
 
     def _pages_from_free_memory(self, utilization: float) -> int:
         free, total = torch.cuda.mem_get_info(self.device)
@@ -98,15 +99,20 @@ class ModelRunner:
             infos.append(EntryInfo(e.rid, rc.slot, start, len(e.tokens), row0))
             row0 += len(e.tokens)
         tables = [[self.manager.get(e.rid).tables[g] for e in entries] for g in range(len(self.manager.pools))]
-        return build_batch(entries, infos, tables, self.max_blocks, self.device)
+        batch = build_batch(entries, infos, tables, self.max_blocks, self.device)
+        self.last_h2d_bytes = batch.h2d_bytes
+        return batch
 
     @torch.no_grad()
-    def step(self, entries: list) -> torch.Tensor:
+    def step(self, entries: list, check: bool = True) -> torch.Tensor:
+        """``check=False`` skips reading the kernels' error flag back (one device-to-host copy); the
+        caller then reads it later with ``ctx.err.check``."""
         if not entries:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
         batch = self.prepare(entries)
         logits = self.model.forward(batch, self.cache)
-        self.ctx.err.check("step")
+        if check:
+            self.ctx.err.check("step")
         for info in batch.entries:
             self.manager.commit(info.rid, info.pos0 + info.length)
         return logits

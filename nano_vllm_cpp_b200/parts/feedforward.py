@@ -52,6 +52,7 @@ class SparseMoeSwiGLU(FeedForward):
         self.hidden, self.E, self.K = hidden_size, num_experts, top_k
         self.inter, self.shared_inter, self.renorm = intermediate_size, shared_intermediate_size, renormalize
         self._align = {}
+        self.last_alignment = None      # the permutation buffers of the latest forward (for statistics)
 
     def tensor_specs(self, available=None):
         H, I, E, SI = self.hidden, self.inter, self.E, self.shared_inter
@@ -110,6 +111,7 @@ class SparseMoeSwiGLU(FeedForward):
         ops.router_topk(logits, self.K, self.renorm, idx, score)
         al = self._alignment(T * self.K, dev)
         ops.moe_align(idx, self.K, al, ctx.err)
+        self.last_alignment = al
         act = grouped_linear(ctx, h, self.w_gate_up, ctx.act_dtype, al, a_rows=al.sorted_token, swiglu=True)
         y = grouped_linear(ctx, act, self.w_down, torch.float32, al)
         shared = gate_logit = None
