@@ -112,6 +112,8 @@ class ErrorFlag:
         v = int(self.t.item())
         if v:
             self.t.zero_()
+            if v >= 0x7000:
+                raise KernelError(f"{what}: a kernel gave up waiting on a barrier (code {v:#x}); its output is invalid")
             raise KernelError(f"{what}: a kernel reported a bad index at row/pair {v - 1}")
 
 
@@ -289,6 +291,91 @@ def sample(logits, temperature, u, out) -> None:
 
 
 # ----------------------------------------------------------------------------- fast products
+_num_sms = None
+
+
+def num_sms() -> int:
+    global _num_sms
+    if _num_sms is None:
+        _num_sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+    return _num_sms
+
+
+def _tma_ok(t) -> bool:
+    return (t.dtype == torch.bfloat16 and t.stride(-1) == 1 and t.data_ptr() % 16 == 0
+            and all(st % 8 == 0 for st in t.stride()[:-1]))
+
+
 def gemm_fast_usable(a, w, out, *, bias=None, a_rows=None, swiglu=False, grouped=False) -> bool:
-    """Whether the tensor-core product takes these operands; the plain product takes all."""
-    return False
+    """Whether the tensor-core product takes these operands; the plain product takes all.
+
+    Both operands bfloat16 with K a multiple of 8 (TMA moves 16-byte units), output float32 or
+    bfloat16."""
+    if not (_tma_ok(a) and _tma_ok(w) and w.is_contiguous()):
+        return False
+    if a.shape[-1] % 8 or out.dtype not in _DT or out.stride(-1) != 1:
+        return False
+    return True
+
+
+def grouped_token_tile(TK: int, E: int) -> int:
+    """Token tile of the grouped tensor-core product for TK (row, expert) pairs over E experts."""
+    avg = (TK + E - 1) // E
+    return 16 if avg <= 12 else (32 if avg <= 24 else 64)
+
+
+def permute_rows(src, rows, R=None):
+    """bfloat16 rows of ``src`` gathered in the order of ``rows``."""
+    R = rows.numel() if R is None else R
+    dst = torch.empty((R, src.shape[1]), dtype=src.dtype, device=src.device)
+    _check(lib().nv_permute_rows_bf16(_p(src), _p(rows), _p(dst), c_int(R), c_int(src.shape[1]), _stream()),
+           "permute_rows")
+    return dst
+
+
+def gemm_fast(a, w, out, *, bias=None, a_rows=None, swiglu=False, M=None, err=None, splits=None) -> None:
+    """Tensor-core form of ``gemm_plain`` (dense)."""
+    if a_rows is not None:
+        a = permute_rows(a, a_rows, M)
+    M = a.shape[0] if M is None else M
+    K = a.shape[1]
+    rows_w = w.shape[0]
+    N = rows_w // 2 if swiglu else rows_w
+    L = lib()
+    n_tile = L.nv_tc_gemm_token_tile(c_int(M), c_int(1 if swiglu else 0))
+    if splits is None:
+        splits = L.nv_tc_gemm_splits(c_int(M), c_int(N), c_int(K), c_int(n_tile), c_int(num_sms()))
+    scratch = None
+    if splits > 1:
+        scratch = torch.empty((splits, M, 2 * N if swiglu else N), dtype=torch.float32, device=a.device)
+    _check(L.nv_tc_gemm(_p(a), c_longlong(a.stride(0)), c_int(M), _p(w), c_int(rows_w), c_int(N), c_int(K),
+                        _p(bias), c_int(dt(bias) if bias is not None else 0), _p(out), c_int(dt(out)),
+                        c_longlong(out.stride(0)), c_int(1 if swiglu else 0), c_int(n_tile), c_int(splits),
+                        _p(scratch), _p(None), _p(None), _p(None), _p(None), c_int(0), c_int(0),
+                        _p(err.t if err is not None else _global_err().t), _stream()), "tc_gemm")
+
+
+def gemm_fast_grouped(a, w, out, align, *, a_rows=None, swiglu=False, err=None) -> None:
+    """Tensor-core form of the grouped ``gemm_plain``: ``align.tile_m`` must be the token tile."""
+    if a_rows is not None:
+        a = permute_rows(a, a_rows, align.TK)
+    K = a.shape[1]
+    E, rows_w = w.shape[0], w.shape[1]
+    N = rows_w // 2 if swiglu else rows_w
+    _need(align.tile_m in (16, 32, 64, 128), "grouped product: token tile must be 16, 32, 64 or 128")
+    _check(lib().nv_tc_gemm(_p(a), c_longlong(a.stride(0)), c_int(align.TK), _p(w), c_int(E * rows_w), c_int(N),
+                            c_int(K), _p(None), c_int(0), _p(out), c_int(dt(out)), c_longlong(out.stride(0)),
+                            c_int(1 if swiglu else 0), c_int(align.tile_m), c_int(1), _p(None), _p(align.tile_expert),
+                            _p(align.tile_row0), _p(align.tile_rows), _p(align.num_tiles), c_int(align.max_tiles),
+                            c_int(rows_w), _p(err.t if err is not None else _global_err().t), _stream()),
+           "tc_gemm_grouped")
+
+
+_gerr = None
+
+
+def _global_err() -> "ErrorFlag":
+    global _gerr
+    if _gerr is None:
+        _gerr = ErrorFlag(torch.device("cuda", torch.cuda.current_device()))
+    return _gerr

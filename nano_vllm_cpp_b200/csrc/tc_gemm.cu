@@ -1,0 +1,463 @@
+// bfloat16 matrix products on the 5th-generation tensor cores: tcgen05.mma with the accumulator in
+// tensor memory (TMEM), operands staged in shared memory by TMA through an mbarrier ring.
+//
+//   out[t, n] = sum_k X[t, k] * W[n, k]        X: [tokens, K] bf16   W: [rows, K] bf16 (K contiguous)
+//
+// The weight matrix is the M operand of the instruction (128 rows per CTA) and the tokens are
+// the N operand (16..256 per CTA), so one kernel serves decoding (a handful of tokens: the
+// tile is 128 weights x 16 tokens and the kernel streams weights at memory speed) and
+// prefill (128 x 256 tiles).  Options:
+//   swiglu    W holds gate rows [0, N) and up rows [N, 2N); two accumulators share the token
+//             operand and the epilogue writes silu(gate) * up
+//   grouped   W is [E, rows, K]; token tiles come from a list (expert, first row, rows) over an
+//             expert-sorted row list, as built by nv_moe_align with tile_m = the token tile
+//   split-K   grid.z CTAs each sum a range of k; raw float32 partial sums go to a scratch
+//             buffer and nv_tc_gemm_finish adds them in split order, then bias / swiglu / cast
+//
+// Warp roles: warp 0 issues TMA loads, warp 1 allocates TMEM and issues the MMAs, warps 2-5
+// read the accumulator back (tcgen05.ld) and store.  Every wait on an mbarrier is bounded: after
+// about two seconds a waiter records the fact in the error flag and goes on, so the kernel always
+// ends and frees its TMEM; its output is then garbage and the host raises.
+#include "common.cuh"
+
+#include <cuda.h>
+#include <mutex>
+#include <unordered_map>
+
+namespace {
+
+constexpr int TILE_W = 128;     // weight rows per CTA (M of the instruction)
+constexpr int BLOCK_K = 64;     // elements of K per stage: 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int MAX_STAGES = 8;
+constexpr int NUM_THREADS = 192;
+constexpr long long WAIT_CYCLES = 4000000000LL;   // ~2 s at 2 GHz
+
+struct TcArgs {
+  void* out;
+  float* partial;
+  const void* bias;
+  const int* tile_expert;
+  const int* tile_row0;
+  const int* tile_rows;
+  const int* num_tiles;
+  int* err;
+  long long ldo;
+  int out_dt, bias_dt;
+  int M_tok;            // rows of X that exist (dense); grouped: total sorted rows
+  int N;                // output features (rows of W per matrix; W has 2N rows with swiglu)
+  int rows_per_expert;  // rows of W per expert (grouped), N or 2N
+  int k_steps_total, k_steps_per_split, splits;
+  int n_tile, swiglu, stages;
+  int tmem_cols;
+};
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false after the limit; the caller records it and carries on.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err, int code) {
+  if (mbar_try(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!mbar_try(bar, parity)) {
+    if (clock64() - t0 > WAIT_CYCLES) {
+      atomicExch(err, code);
+      return false;
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* tm, uint64_t* bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"((uint64_t)tm), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)), "r"(cols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+
+// D[tmem] (+)= A[smem desc] * B[smem desc]; issued by one thread
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// the mbarrier gets one arrival when every MMA issued so far by this thread has finished
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory operand descriptor: K-major tile of rows x 64 bf16 (128 bytes per row), written by TMA with
+// the 128-byte swizzle; 8-row groups are 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3FFF);        // start address
+  d |= (uint64_t)1 << 16;                        // leading byte offset (unused with swizzle): 16 B
+  d |= (uint64_t)(1024 >> 4) << 32;              // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;                        // descriptor version of this architecture
+  d |= (uint64_t)2 << 61;                        // 128-byte swizzle
+  return d;
+}
+
+// Instruction descriptor: bf16 x bf16 -> f32, both operands K-major, M = 128, N = n.
+__device__ __forceinline__ uint32_t instr_desc(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TILE_W >> 4) << 24);
+}
+
+// ------------------------------------------------------------------ the kernel
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, TcArgs a) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  __shared__ uint64_t full_bar[MAX_STAGES], empty_bar[MAX_STAGES], acc_bar;
+  __shared__ uint32_t tmem_base_s;
+
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int nb = blockIdx.x;                       // block of 128 output features
+  int row0, rows_here, w_row_base;
+  if (a.tile_expert) {
+    if ((int)blockIdx.y >= *a.num_tiles) return;   // the whole CTA leaves before touching barriers or TMEM
+    row0 = a.tile_row0[blockIdx.y];
+    rows_here = a.tile_rows[blockIdx.y];
+    w_row_base = a.tile_expert[blockIdx.y] * a.rows_per_expert;
+  } else {
+    row0 = blockIdx.y * a.n_tile;
+    rows_here = min(a.n_tile, a.M_tok - row0);
+    w_row_base = 0;
+  }
+  const int k_begin = blockIdx.z * a.k_steps_per_split;
+  const int k_end = min(a.k_steps_total, k_begin + a.k_steps_per_split);
+  const int n_steps = k_end - k_begin;
+
+  // stage layout: [A gate 16 KB][A up 16 KB if swiglu][X n_tile*128 B], every piece 1024-aligned
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const uint32_t a_bytes = TILE_W * 128, x_bytes = a.n_tile * 128;
+  const uint32_t stage_bytes = a_bytes * (a.swiglu ? 2 : 1) + x_bytes;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < a.stages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(&acc_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(&tmem_base_s, a.tmem_cols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_s;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      for (int it = 0; it < n_steps; ++it) {
+        const int s = it % a.stages;
+        const uint32_t ph = (it / a.stages) & 1;
+        mbar_wait(&empty_bar[s], ph ^ 1, a.err, 0x7001);
+        uint8_t* st = smem + (size_t)s * stage_bytes;
+        mbar_expect_tx(&full_bar[s], stage_bytes);
+        const int kc = (k_begin + it) * BLOCK_K;
+        tma_load_2d(st, &tm_w, &full_bar[s], kc, w_row_base + nb * TILE_W);
+        if (a.swiglu) tma_load_2d(st + a_bytes, &tm_w, &full_bar[s], kc, w_row_base + a.N + nb * TILE_W);
+        tma_load_2d(st + a_bytes * (a.swiglu ? 2 : 1), &tm_x, &full_bar[s], kc, row0);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = instr_desc(a.n_tile);
+      for (int it = 0; it < n_steps; ++it) {
+        const int s = it % a.stages;
+        const uint32_t ph = (it / a.stages) & 1;
+        mbar_wait(&full_bar[s], ph, a.err, 0x7002);
+        tc_fence_after();
+        const uint32_t sa = smem_u32(smem + (size_t)s * stage_bytes);
+        const uint64_t da = smem_desc_sw128(sa);
+        const uint64_t du = smem_desc_sw128(sa + a_bytes);
+        const uint64_t dx = smem_desc_sw128(sa + a_bytes * (a.swiglu ? 2 : 1));
+#pragma unroll
+        for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+          const uint64_t adv = (uint64_t)(k * UMMA_K * 2 >> 4);   // 32 bytes per k-slice inside the swizzle row
+          const uint32_t acc = (it > 0 || k > 0) ? 1u : 0u;
+          umma_bf16(tmem_base, da + adv, dx + adv, idesc, acc);
+          if (a.swiglu) umma_bf16(tmem_base + a.n_tile, du + adv, dx + adv, idesc, acc);
+        }
+        umma_commit(&empty_bar[s]);     // the stage may be refilled once these MMAs have read it
+      }
+      umma_commit(&acc_bar);            // the accumulator is complete
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue: warps 2..5
+    const int q = warp % 4;                        // a warp may read TMEM lanes [32q, 32q + 32) only
+    const int n = nb * TILE_W + q * 32 + lane;     // this thread's output feature
+    const bool n_ok = n < a.N;
+    if (n_steps > 0) mbar_wait(&acc_bar, 0, a.err, 0x7003);
+    tc_fence_after();
+    float bias = 0.f;
+    if (a.bias && n_ok && a.splits == 1) bias = ld_dt(a.bias, a.bias_dt, n);
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+    for (int c0 = 0; c0 < a.n_tile; c0 += 16) {
+      if (c0 >= rows_here) break;                  // uniform over the warp
+      float g[16], u[16];
+      if (n_steps > 0) {
+        tmem_ld16(lane_addr + c0, g);
+        if (a.swiglu) tmem_ld16(lane_addr + a.n_tile + c0, u);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) g[j] = u[j] = 0.f;
+      }
+      if (!n_ok) continue;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        if (c0 + j >= rows_here) break;
+        const size_t t = (size_t)(row0 + c0 + j);
+        if (a.splits > 1) {
+          const int width = a.swiglu ? 2 * a.N : a.N;
+          float* p = a.partial + ((size_t)blockIdx.z * a.M_tok + t) * width;
+          p[n] = g[j];
+          if (a.swiglu) p[a.N + n] = u[j];
+        } else {
+          float v = a.swiglu ? silu_mul(g[j], u[j]) : g[j];
+          st_dt(a.out, a.out_dt, t * a.ldo + n, v + bias);
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, a.tmem_cols);
+}
+
+// Adds split-K partial sums in split order and finishes: bias, swiglu, cast.
+__global__ void tc_gemm_finish_kernel(const float* __restrict__ partial, int splits, int M_tok, int N, int swiglu,
+                                      const void* __restrict__ bias, int bias_dt, void* __restrict__ out, int out_dt,
+                                      long long ldo) {
+  const int width = swiglu ? 2 * N : N;
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)M_tok * N) return;
+  const long long t = i / N;
+  const int n = (int)(i % N);
+  float g = 0.f, u = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float* p = partial + ((size_t)s * M_tok + t) * width;
+    g += p[n];
+    if (swiglu) u += p[N + n];
+  }
+  float v = swiglu ? silu_mul(g, u) : g;
+  if (bias) v += ld_dt(bias, bias_dt, n);
+  st_dt(out, out_dt, t * ldo + n, v);
+}
+
+// out[r, :] = src[rows[r], :] for bf16 rows (the expert-sorted copy of the activations)
+__global__ void permute_rows_bf16_kernel(const bf16* __restrict__ src, const int* __restrict__ rows,
+                                         bf16* __restrict__ dst, int H) {
+  const int r = blockIdx.x;
+  const uint4* s = (const uint4*)(src + (size_t)rows[r] * H);
+  uint4* d = (uint4*)(dst + (size_t)r * H);
+  for (int i = threadIdx.x; i < H / 8; i += blockDim.x) d[i] = s[i];
+}
+
+// ------------------------------------------------------------------ host side: tensor maps
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  });
+  return fn;
+}
+
+struct MapKey {
+  const void* ptr;
+  long long rows, cols, ld;
+  int box_rows;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = (size_t)k.ptr;
+    h = h * 1000003u ^ (size_t)k.rows;
+    h = h * 1000003u ^ (size_t)k.cols;
+    h = h * 1000003u ^ (size_t)k.ld;
+    return h * 1000003u ^ (size_t)k.box_rows;
+  }
+};
+
+// A row-major bf16 matrix [rows, cols] with row stride ld elements; boxes of box_rows x 64, 128-byte swizzle,
+// zero fill outside.
+int get_map(const void* ptr, long long rows, long long cols, long long ld, int box_rows, CUtensorMap* out) {
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  static std::mutex mu;
+  MapKey key{ptr, rows, cols, ld, box_rows};
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) {
+    *out = it->second;
+    return NV_OK;
+  }
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return -5;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BLOCK_K, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMap m;
+  CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return -5;
+  if (cache.size() > 8192) cache.clear();
+  cache[key] = m;
+  *out = m;
+  return NV_OK;
+}
+
+int pow2_at_least(int v) {
+  int p = 32;
+  while (p < v) p <<= 1;
+  return p;
+}
+
+}  // namespace
+
+// Token tile the product will use for `rows` tokens (dense) or for the largest expected expert segment
+// (grouped): the N of the instruction, 16..256.
+NV_API int nv_tc_gemm_token_tile(int rows, int swiglu) {
+  int cap = swiglu ? 128 : 256;   // two accumulators of n_tile columns must fit 512 TMEM columns with room to spare
+  int t = 16;
+  while (t < rows && t < cap) t <<= 1;
+  return t;
+}
+
+// Bytes of float32 scratch a call needs for its split-K partial sums (0 when it does not split).
+NV_API long long nv_tc_gemm_scratch_bytes(int M_tok, int N, int swiglu, int splits) {
+  if (splits <= 1) return 0;
+  return (long long)splits * M_tok * (swiglu ? 2 * N : N) * 4;
+}
+
+// How many ways to split K so that a small grid still fills the GPU.  1 for large grids.
+NV_API int nv_tc_gemm_splits(int M_tok, int N, int K, int n_tile, int num_sms) {
+  int ctas = ((N + TILE_W - 1) / TILE_W) * ((M_tok + n_tile - 1) / n_tile);
+  int k_steps = (K + BLOCK_K - 1) / BLOCK_K;
+  if (ctas >= num_sms || k_steps < 8) return 1;
+  int s = num_sms / ctas;
+  if (s > k_steps / 4) s = k_steps / 4;
+  if (s > 16) s = 16;
+  return s < 1 ? 1 : s;
+}
+
+NV_API int nv_tc_gemm(const void* X, long long ldx, int M_tok, const void* W, int w_rows_total, int N, int K,
+                      const void* bias, int bias_dt, void* out, int out_dt, long long ldo, int swiglu, int n_tile,
+                      int splits, float* scratch, const int* tile_expert, const int* tile_row0,
+                      const int* tile_rows, const int* num_tiles, int max_tiles, int rows_per_expert, int* err,
+                      cudaStream_t stream) {
+  if (!dt_ok(out_dt) || (bias && !dt_ok(bias_dt))) return NV_ERR_BAD_DTYPE;
+  if (K % 8 || ldx % 8 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return NV_ERR_UNSUPPORTED;  // TMA: 16-byte rules
+  if (n_tile < 16 || n_tile > 256 || (n_tile & (n_tile - 1)) || (swiglu && n_tile > 128)) return NV_ERR_BAD_SIZE;
+  if (M_tok <= 0 || N <= 0) return NV_OK;
+  const bool grouped = tile_expert != nullptr;
+  if (grouped && splits != 1) return NV_ERR_UNSUPPORTED;
+  if (splits > 1 && !scratch) return NV_ERR_BAD_SIZE;
+
+  CUtensorMap tm_w, tm_x;
+  int rc = get_map(W, w_rows_total, K, K, TILE_W, &tm_w);
+  if (rc) return rc;
+  rc = get_map(X, M_tok, K, ldx, n_tile, &tm_x);
+  if (rc) return rc;
+
+  TcArgs a;
+  a.out = out; a.partial = scratch; a.bias = bias; a.tile_expert = tile_expert; a.tile_row0 = tile_row0;
+  a.tile_rows = tile_rows; a.num_tiles = num_tiles; a.err = err; a.ldo = ldo; a.out_dt = out_dt; a.bias_dt = bias_dt;
+  a.M_tok = M_tok; a.N = N; a.rows_per_expert = rows_per_expert;
+  a.k_steps_total = (K + BLOCK_K - 1) / BLOCK_K;
+  a.splits = splits < 1 ? 1 : splits;
+  a.k_steps_per_split = (a.k_steps_total + a.splits - 1) / a.splits;
+  a.n_tile = n_tile; a.swiglu = swiglu ? 1 : 0;
+  const int stage_bytes = TILE_W * 128 * (swiglu ? 2 : 1) + n_tile * 128;
+  int stages = (200 * 1024) / stage_bytes;
+  if (stages > MAX_STAGES) stages = MAX_STAGES;
+  if (stages > a.k_steps_per_split) stages = a.k_steps_per_split < 2 ? 2 : a.k_steps_per_split;
+  a.stages = stages;
+  a.tmem_cols = pow2_at_least(n_tile * (swiglu ? 2 : 1));
+  const size_t smem = (size_t)stages * stage_bytes + 1024;
+
+  static std::once_flag once;
+  static cudaError_t attr_rc = cudaSuccess;
+  std::call_once(once, [] {
+    attr_rc = cudaFuncSetAttribute(tc_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+  });
+  if (attr_rc != cudaSuccess) return (int)attr_rc;
+
+  dim3 grid((N + TILE_W - 1) / TILE_W, grouped ? max_tiles : (M_tok + n_tile - 1) / n_tile, a.splits);
+  tc_gemm_kernel<<<grid, NUM_THREADS, smem, stream>>>(tm_w, tm_x, a);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return (int)e;
+  if (a.splits > 1) {
+    long long total = (long long)M_tok * N;
+    tc_gemm_finish_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(scratch, a.splits, M_tok, N, a.swiglu,
+                                                                              bias, bias_dt, out, out_dt, ldo);
+  }
+  NV_RETURN_LAST();
+}
+
+NV_API int nv_permute_rows_bf16(const void* src, const int* rows, void* dst, int R, int H, cudaStream_t stream) {
+  if (H % 8 || ((uintptr_t)src & 15) || ((uintptr_t)dst & 15)) return NV_ERR_UNSUPPORTED;
+  if (R == 0) return NV_OK;
+  permute_rows_bf16_kernel<<<R, 128, 0, stream>>>((const bf16*)src, rows, (bf16*)dst, H);
+  NV_RETURN_LAST();
+}

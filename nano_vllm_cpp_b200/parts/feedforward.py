@@ -94,8 +94,8 @@ class SparseMoeSwiGLU(FeedForward):
             self.sh_down = fetch("shared_expert.down_proj.weight")
             self.sh_gate = fetch("shared_expert_gate.weight")
 
-    def _alignment(self, TK, device):
-        tile_m = ops.gemm_plain_tile_m()
+    def _alignment(self, TK, device, fast):
+        tile_m = ops.grouped_token_tile(TK, self.E) if fast else ops.gemm_plain_tile_m()
         key = (TK, tile_m)
         if key not in self._align:
             self._align[key] = ops.MoeAlignment(TK, self.E, tile_m, device)
@@ -109,7 +109,9 @@ class SparseMoeSwiGLU(FeedForward):
         idx = torch.empty((T, self.K), dtype=torch.int32, device=dev)
         score = torch.empty((T, self.K), dtype=torch.float32, device=dev)
         ops.router_topk(logits, self.K, self.renorm, idx, score)
-        al = self._alignment(T * self.K, dev)
+        fast = (ctx.fast_kernels and h.dtype == torch.bfloat16 and self.w_gate_up.dtype == torch.bfloat16
+                and self.w_down.dtype == torch.bfloat16 and self.hidden % 8 == 0 and self.inter % 8 == 0)
+        al = self._alignment(T * self.K, dev, fast)
         ops.moe_align(idx, self.K, al, ctx.err)
         self.last_alignment = al
         act = grouped_linear(ctx, h, self.w_gate_up, ctx.act_dtype, al, a_rows=al.sorted_token, swiglu=True)

@@ -22,7 +22,7 @@ def linear(ctx, a, w, out_dtype, *, bias=None, a_rows=None, swiglu=False, M=None
     if M == 0:
         return out
     if ctx.fast_kernels and ops.gemm_fast_usable(a, w, out, bias=bias, a_rows=a_rows, swiglu=swiglu):
-        ops.gemm_fast(a, w, out, bias=bias, a_rows=a_rows, swiglu=swiglu, M=M)
+        ops.gemm_fast(a, w, out, bias=bias, a_rows=a_rows, swiglu=swiglu, M=M, err=ctx.err)
     else:
         ops.gemm_plain(a, w, out, bias=bias, a_rows=a_rows, swiglu=swiglu, M=M)
     return out
@@ -37,7 +37,7 @@ def grouped_linear(ctx, a, w, out_dtype, align, *, a_rows=None, swiglu=False):
     if align.TK == 0:
         return out
     if ctx.fast_kernels and ops.gemm_fast_usable(a, w, out, a_rows=a_rows, swiglu=swiglu, grouped=True):
-        ops.gemm_fast_grouped(a, w, out, align, a_rows=a_rows, swiglu=swiglu)
+        ops.gemm_fast_grouped(a, w, out, align, a_rows=a_rows, swiglu=swiglu, err=ctx.err)
     else:
         ops.gemm_plain(a, w, out, a_rows=a_rows, swiglu=swiglu, M=align.TK, tiles=align.tiles)
     return out
