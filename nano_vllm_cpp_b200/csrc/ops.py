@@ -176,6 +176,36 @@ def gemm_plain(a, w, out, *, bias=None, a_rows=None, swiglu=False, M=None, tiles
                                _p(te), _p(tr0), _p(tr), _p(nt), c_int(max_tiles), _stream()), "gemm_plain")
 
 
+def rowdot(a, w, out) -> None:
+    """out[t, n] = a[t, :] . w[n, :] for float32 rows and a short matrix (float32 or bfloat16), float32 out."""
+    _cuda_contig(w, out)
+    _need(a.dtype == torch.float32 and out.dtype == torch.float32 and a.stride(1) == 1, "rowdot: float32 rows")
+    T, K = a.shape
+    N = w.shape[0]
+    _need(w.shape[1] == K and out.shape == (T, N), "rowdot: shapes")
+    _check(lib().nv_rowdot(_p(a), c_longlong(a.stride(0)), _p(w), c_int(dt(w)), _p(out), c_int(T), c_int(N),
+                           c_int(K), _stream()), "rowdot")
+
+
+def attention_decode(qkv, k_cache, v_cache, block_table, row_entry, positions, scale: float, window: int, out,
+                     Hq: int, Hkv: int, D: int, max_context: int, rows=None) -> None:
+    """One query row per request (``rows``: which batch rows; None = all) against its paged keys."""
+    _cuda_contig(qkv, k_cache, v_cache, block_table, row_entry, positions, out, rows)
+    _i32(block_table, row_entry, positions, rows)
+    R = qkv.shape[0] if rows is None else rows.numel()
+    page = k_cache.shape[2]
+    L = lib()
+    splits = L.nv_attention_decode_splits(c_int(R), c_int(Hq), c_int(Hkv), c_int(max_context), c_int(num_sms()))
+    scratch = None
+    if splits > 1:
+        scratch = torch.empty(R * Hq * splits * (D + 2), dtype=torch.float32, device=qkv.device)
+    _check(L.nv_attention_decode(_p(qkv), c_int(dt(qkv)), c_int(qkv.shape[1]), _p(k_cache), _p(v_cache),
+                                 c_int(dt(k_cache)), _p(block_table), c_int(block_table.shape[1]), _p(row_entry),
+                                 _p(positions), _p(rows), c_int(R), c_float(scale), c_int(window), _p(out),
+                                 c_int(dt(out)), c_int(Hq), c_int(Hkv), c_int(D), c_int(page), c_int(splits),
+                                 _p(scratch), _stream()), "attention_decode")
+
+
 def gemm_plain_tile_m() -> int:
     return int(lib().nv_gemm_plain_tile_m())
 

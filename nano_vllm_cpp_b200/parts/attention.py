@@ -70,6 +70,12 @@ class PagedAttention(Mixer):
         return linear(ctx, att, self.o_weight, torch.float32)
 
     def _attend(self, qkv, cache, bt, batch, att):
+        # bfloat16 runs take the split-key kernel for batches of single rows; float32 runs keep the
+        # plain kernel everywhere, so that their sums have one order however the work is cut
+        if self.ctx.fast_kernels and self.ctx.act_dtype == torch.bfloat16 and batch.decode_only:
+            ops.attention_decode(qkv, cache.k, cache.v, bt, batch.row_entry, batch.positions, self.scale,
+                                 self.window, att, self.Hq, self.Hkv, self.D, batch.max_context)
+            return
         ops.paged_attention_plain(qkv, cache.k, cache.v, bt, batch.row_entry, batch.positions, self.scale,
                                   self.window, att, self.Hq, self.Hkv, self.D)
 

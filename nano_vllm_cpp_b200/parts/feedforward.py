@@ -6,7 +6,7 @@ import torch
 
 from ..csrc import ops
 from .base import FeedForward, TensorSpec
-from .linear import linear, grouped_linear
+from .linear import linear, grouped_linear, small_linear
 from .registry import register_part
 
 
@@ -105,7 +105,7 @@ class SparseMoeSwiGLU(FeedForward):
         ctx = self.ctx
         T = h.shape[0]
         dev = h.device
-        logits = linear(ctx, h32, self.router, torch.float32)
+        logits = small_linear(ctx, h32, self.router)
         idx = torch.empty((T, self.K), dtype=torch.int32, device=dev)
         score = torch.empty((T, self.K), dtype=torch.float32, device=dev)
         ops.router_topk(logits, self.K, self.renorm, idx, score)
@@ -120,7 +120,7 @@ class SparseMoeSwiGLU(FeedForward):
         if self.shared_inter > 0:
             sact = linear(ctx, h, self.sh_gate_up, ctx.act_dtype, swiglu=True)
             shared = linear(ctx, sact, self.sh_down, torch.float32)
-            gate_logit = linear(ctx, h32, self.sh_gate, torch.float32)
+            gate_logit = small_linear(ctx, h32, self.sh_gate)
         out = torch.empty((T, self.hidden), dtype=torch.float32, device=dev)
         ops.moe_combine(y, al.pair_pos, score, shared, gate_logit, out)
         return out

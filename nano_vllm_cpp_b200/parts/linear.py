@@ -28,6 +28,14 @@ def linear(ctx, a, w, out_dtype, *, bias=None, a_rows=None, swiglu=False, M=None
     return out
 
 
+def small_linear(ctx, a32, w):
+    """float32 rows times a short matrix, float32 out: router logits and gate logits."""
+    out = torch.empty((a32.shape[0], w.shape[0]), dtype=torch.float32, device=a32.device)
+    if a32.shape[0]:
+        ops.rowdot(a32, w, out)
+    return out
+
+
 def grouped_linear(ctx, a, w, out_dtype, align, *, a_rows=None, swiglu=False):
     """Per-expert product over an expert-sorted row list: row r of the output belongs to the expert
     whose segment of ``align`` holds r and is ``a[a_rows[r]] @ w[expert].T``."""

@@ -174,3 +174,211 @@ def test_tc_gemm_grouped(T, E, K):
     close(res[False], want, 2e-2, "plain grouped")
     close(res[True], want, 2e-2, "tc grouped")
     close(res[True], res[False], 2e-2, "tc vs plain grouped")
+
+
+# ------------------------------------------------------------------------------- small products, router
+@pytest.mark.parametrize("T,N,K", [(1, 1, 64), (8, 60, 2048), (33, 7, 100), (5, 64, 3000)])
+@pytest.mark.parametrize("tw", [torch.float32, torch.bfloat16])
+def test_rowdot(T, N, K, tw):
+    o = ops()
+    a, w = rnd(T, K), rnd(N, K, dtype=tw, seed=1)
+    out = torch.empty(T, N, device=DEV)
+    o.rowdot(a, w, out)
+    close(out, a.double() @ w.double().T, 2e-6, "rowdot")
+    one = torch.empty(1, N, device=DEV)
+    o.rowdot(a[T - 1:T].contiguous(), w, one)
+    assert torch.equal(one[0], out[T - 1])          # a row does not depend on the batch
+
+
+@pytest.mark.parametrize("T,E,K,renorm", [(9, 60, 4, False), (4, 6, 3, True), (130, 8, 2, True), (3, 100, 8, False)])
+def test_router_topk(T, E, K, renorm):
+    o = ops()
+    logits = rnd(T, E, scale=2.0)
+    logits[0, :] = 0.5                                # an exact tie: the lowest indices win
+    idx = torch.empty(T, K, dtype=torch.int32, device=DEV)
+    sc = torch.empty(T, K, device=DEV)
+    o.router_topk(logits, K, renorm, idx, sc)
+    p = torch.softmax(logits.double(), -1).cpu()
+    for t in range(T):
+        order = sorted(range(E), key=lambda e: (-float(p[t, e]), e))[:K]
+        assert idx[t].tolist() == order
+        w = p[t, order]
+        if renorm:
+            w = w / w.sum()
+        close(sc[t], w, 1e-6, "router weights")
+    assert idx[0].tolist() == list(range(K))
+
+
+def test_moe_align_and_combine():
+    o = ops()
+    T, K, E, H = 37, 3, 10, 72
+    g = torch.Generator().manual_seed(3)
+    idx = torch.stack([torch.randperm(E, generator=g)[:K] for _ in range(T)]).to(torch.int32).to(DEV)
+    err = o.ErrorFlag(DEV)
+    al = o.MoeAlignment(T * K, E, 16, DEV)
+    o.moe_align(idx, K, al, err)
+    err.check("align")
+    counts = torch.bincount(idx.flatten().long().cpu(), minlength=E)
+    assert al.counts.cpu().tolist() == counts.tolist()
+    assert al.offsets.cpu().tolist() == [0] + torch.cumsum(counts, 0).tolist()
+    pos = al.pair_pos.cpu().long()
+    assert sorted(pos.tolist()) == list(range(T * K))                 # a permutation
+    assert al.sorted_token.cpu()[pos].tolist() == [i // K for i in range(T * K)]
+    off = al.offsets.cpu()
+    for i in range(T * K):                                            # every pair sits in its expert's segment
+        e = int(idx.flatten()[i])
+        assert off[e] <= pos[i] < off[e + 1]
+    nt = int(al.num_tiles)
+    assert nt == sum((int(c) + 15) // 16 for c in counts)
+    covered = []
+    for i in range(nt):
+        e, r0, r = int(al.tile_expert[i]), int(al.tile_row0[i]), int(al.tile_rows[i])
+        assert off[e] <= r0 and r0 + r <= off[e + 1] and 1 <= r <= 16
+        covered += list(range(r0, r0 + r))
+    assert sorted(covered) == list(range(T * K))
+    y, score, sh, gl = rnd(T * K, H), rnd(T, K, seed=1).abs(), rnd(T, H, seed=2), rnd(T, seed=3)
+    out = torch.empty(T, H, device=DEV)
+    o.moe_combine(y, al.pair_pos, score, sh, gl, out)
+    want = torch.sigmoid(gl.double())[:, None] * sh.double()
+    yy = y.double()[al.pair_pos.long()].reshape(T, K, H)
+    want = want + (score.double()[:, :, None] * yy).sum(1)
+    close(out, want, 2e-6, "combine")
+    o.moe_combine(y, al.pair_pos, score, None, None, out)
+    close(out, (score.double()[:, :, None] * yy).sum(1), 2e-6, "combine without shared expert")
+    bad = idx.clone()
+    bad[5, 1] = E
+    o.moe_align(bad, K, al, err)
+    with pytest.raises(o.KernelError):
+        err.check("align")
+
+
+# ------------------------------------------------------------------------------- rotary + cache write, attention
+def paged_setup(lens, Hkv, D, page, dtype, seed=0, shuffle=True):
+    """Random keys/values for requests of the given lengths, scattered over shuffled pages."""
+    g = torch.Generator().manual_seed(seed)
+    n_pages = sum((n + page - 1) // page for n in lens) + 3
+    perm = torch.randperm(n_pages, generator=g).tolist() if shuffle else list(range(n_pages))
+    max_blocks = max((n + page - 1) // page for n in lens) + 1
+    bt = torch.full((len(lens), max_blocks), -1, dtype=torch.int32)
+    kc = torch.zeros(n_pages, Hkv, page, D, dtype=dtype)
+    vc = torch.zeros_like(kc)
+    ks, vs = [], []
+    for i, n in enumerate(lens):
+        k = (torch.randn(n, Hkv, D, generator=g)).to(dtype)
+        v = (torch.randn(n, Hkv, D, generator=g)).to(dtype)
+        ks.append(k), vs.append(v)
+        for b in range((n + page - 1) // page):
+            p = perm.pop()
+            bt[i, b] = p
+            seg = slice(b * page, min(n, (b + 1) * page))
+            kc[p, :, :seg.stop - seg.start] = k[seg].transpose(0, 1)
+            vc[p, :, :seg.stop - seg.start] = v[seg].transpose(0, 1)
+    return kc.to(DEV), vc.to(DEV), bt.to(DEV), ks, vs
+
+
+def attention_reference(q, k, v, pos, scale, window):
+    """q: [Hq, D] at position pos; k, v: [n, Hkv, D] -> [Hq, D] in float64."""
+    Hq, Hkv = q.shape[0], k.shape[1]
+    lo = max(0, pos + 1 - window) if window > 0 else 0
+    out = torch.zeros(Hq, q.shape[1], dtype=torch.float64)
+    for h in range(Hq):
+        kh = h // (Hq // Hkv)
+        s = (k[lo:pos + 1, kh].double() @ q[h].double()) * scale
+        out[h] = torch.softmax(s, 0) @ v[lo:pos + 1, kh].double()
+    return out
+
+
+@pytest.mark.parametrize("Hq,Hkv,D,page", [(3, 1, 32, 16), (4, 4, 16, 16), (6, 2, 48, 32), (14, 2, 128, 16), (2, 1, 256, 16)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window", [0, 20])
+def test_attention_plain_and_decode(Hq, Hkv, D, page, dtype, window):
+    o = ops()
+    lens = [1, 16, 17, 200, 333]
+    kc, vc, bt, ks, vs = paged_setup(lens, Hkv, D, page, dtype, seed=D)
+    T = len(lens)
+    width = (Hq + 2 * Hkv) * D
+    qkv = rnd(T, width, dtype=dtype, seed=7)
+    pos = torch.tensor([n - 1 for n in lens], dtype=torch.int32, device=DEV)
+    row_entry = torch.arange(T, dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(D)
+    want = torch.stack([attention_reference(qkv[i, :Hq * D].reshape(Hq, D).cpu(), ks[i], vs[i], lens[i] - 1, scale, window)
+                        for i in range(T)]).reshape(T, Hq * D)
+    tol = 2e-5 if dtype == torch.float32 else 1.5e-2
+    out = torch.empty(T, Hq * D, dtype=dtype, device=DEV)
+    o.paged_attention_plain(qkv, kc, vc, bt, row_entry, pos, scale, window, out, Hq, Hkv, D)
+    close(out, want, tol, "plain attention")
+    out2 = torch.full_like(out, float("nan"))
+    o.attention_decode(qkv, kc, vc, bt, row_entry, pos, scale, window, out2, Hq, Hkv, D, max(lens))
+    close(out2, want, tol, "decode attention")
+    rows = torch.tensor([3, 0], dtype=torch.int32, device=DEV)        # a subset of the rows, in another order
+    out3 = torch.zeros_like(out)
+    o.attention_decode(qkv, kc, vc, bt, row_entry, pos, scale, window, out3, Hq, Hkv, D, 4096, rows=rows)
+    close(out3[[0, 3]], want[[0, 3]], tol, "decode attention on a row subset")
+    assert float(out3[[1, 2, 4]].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("kernel", ["plain", "decode"])
+def test_attention_finds_one_far_key(kernel):
+    """Among 700 keys one far key matches the query; its value must dominate the output.  With a window
+    that excludes it, it must not."""
+    o = ops()
+    Hq = Hkv = 2
+    D, page, n, far = 64, 16, 700, 37
+    kc, vc, bt, ks, vs = paged_setup([n], Hkv, D, page, torch.bfloat16, seed=1)
+    q = torch.zeros(1, (Hq + 2 * Hkv) * D, dtype=torch.bfloat16)
+    key = ks[0][far, 1].float()
+    q[0, D:2 * D] = (key / key.norm() * 40).to(torch.bfloat16)        # head 1 looks for that key
+    q = q.to(DEV)
+    pos = torch.tensor([n - 1], dtype=torch.int32, device=DEV)
+    ent = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for window, hit in ((0, True), (n - far, True), (n - far - 1, False)):
+        out = torch.empty(1, Hq * D, dtype=torch.bfloat16, device=DEV)
+        if kernel == "plain":
+            o.paged_attention_plain(q, kc, vc, bt, ent, pos, 1.0, window, out, Hq, Hkv, D)
+        else:
+            o.attention_decode(q, kc, vc, bt, ent, pos, 1.0, window, out, Hq, Hkv, D, n)
+        want = attention_reference(q[0, :Hq * D].reshape(Hq, D).cpu(), ks[0], vs[0], n - 1, 1.0, window)
+        close(out[0], want.reshape(-1), 1.5e-2, f"window {window}")
+        near = float((out[0, D:].float().cpu() - vs[0][far, 1].float()).abs().max())
+        assert (near < 0.1) == hit
+
+
+@pytest.mark.parametrize("Hq,Hkv,D,rot", [(3, 1, 32, 32), (4, 2, 16, 16), (2, 2, 48, 32), (2, 1, 128, 128)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rope_store(Hq, Hkv, D, rot, dtype):
+    o = ops()
+    page, T = 16, 6
+    positions = [0, 1, 15, 16, 100, 4095]
+    qkv = rnd(T, (Hq + 2 * Hkv) * D, dtype=dtype)
+    orig = qkv.clone()
+    inv = torch.tensor([1.0 / (10000.0 ** (2.0 * i / rot)) for i in range(rot // 2)], dtype=torch.float64).float().to(DEV)
+    n_pages = 4096 // page + 1
+    kc = torch.zeros(n_pages, Hkv, page, D, dtype=dtype, device=DEV)
+    vc = torch.zeros_like(kc)
+    bt = torch.arange(n_pages, dtype=torch.int32).flip(0).reshape(1, -1).to(DEV).contiguous()   # page i -> n_pages-1-i
+    ent = torch.zeros(T, dtype=torch.int32, device=DEV)
+    err = o.ErrorFlag(DEV)
+    o.rope_store(qkv, torch.tensor(positions, dtype=torch.int32, device=DEV), inv, rot, kc, vc, bt, ent, Hq, Hkv, D,
+                 True, err)
+    err.check("rope")
+
+    def rotate(x, p):
+        x = x.double()
+        ang = (torch.tensor(float(p), dtype=torch.float32) * inv.cpu()).double()
+        c, s = torch.cos(ang), torch.sin(ang)
+        x1, x2 = x[..., :rot // 2], x[..., rot // 2:rot]
+        return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s, x[..., rot:]], -1)
+
+    tol = 3e-6 if dtype == torch.float32 else 2 ** -8
+    for i, p in enumerate(positions):
+        heads = orig[i].reshape(Hq + 2 * Hkv, D).cpu()
+        close(qkv[i, :Hq * D].reshape(Hq, D), rotate(heads[:Hq], p), tol, "q")
+        page_id = n_pages - 1 - p // page
+        close(kc[page_id, :, p % page], rotate(heads[Hq:Hq + Hkv], p), tol, "k")
+        assert torch.equal(vc[page_id, :, p % page].cpu(), heads[Hq + Hkv:])
+    assert torch.equal(qkv[:, Hq * D:], orig[:, Hq * D:])           # k and v stay as they were in the buffer
+    bt[0, 0] = -1                                                      # the page of position 4095 is missing
+    o.rope_store(qkv, torch.tensor(positions, dtype=torch.int32, device=DEV), inv, rot, kc, vc, bt, ent, Hq, Hkv, D,
+                 True, err)
+    with pytest.raises(o.KernelError):
+        err.check("rope")
