@@ -46,6 +46,12 @@ def launch_count() -> int:
     return _launches
 
 
+def add_launches(n: int) -> None:
+    """Launches replayed from a CUDA graph, counted at its capture."""
+    global _launches
+    _launches += n
+
+
 def _check(code: int, what: str) -> None:
     global _launches
     _launches += 1
@@ -204,6 +210,21 @@ def attention_decode(qkv, k_cache, v_cache, block_table, row_entry, positions, s
                                  _p(positions), _p(rows), c_int(R), c_float(scale), c_int(window), _p(out),
                                  c_int(dt(out)), c_int(Hq), c_int(Hkv), c_int(D), c_int(page), c_int(splits),
                                  _p(scratch), _stream()), "attention_decode")
+
+
+def attention_prefill(qkv, k_cache, v_cache, block_table, cu_rows, entry_pos0, max_tiles: int, scale: float,
+                      window: int, out, Hq: int, Hkv: int, D: int) -> None:
+    """bfloat16 rows of any mix of portions against their paged keys (tensor cores)."""
+    _cuda_contig(qkv, k_cache, v_cache, block_table, cu_rows, entry_pos0, out)
+    _i32(block_table, cu_rows, entry_pos0)
+    _need(qkv.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16,
+          "attention_prefill: bfloat16 only")
+    _need(out.shape == (qkv.shape[0], Hq * D), "attention_prefill: out shape")
+    S = entry_pos0.numel()
+    _check(lib().nv_attention_prefill(_p(qkv), c_int(qkv.shape[1]), _p(k_cache), _p(v_cache), _p(block_table),
+                                      c_int(block_table.shape[1]), _p(cu_rows), _p(entry_pos0), c_int(S),
+                                      c_int(max_tiles), c_float(scale), c_int(window), _p(out), c_int(Hq), c_int(Hkv),
+                                      c_int(D), c_int(k_cache.shape[2]), _stream()), "attention_prefill")
 
 
 def gemm_plain_tile_m() -> int:

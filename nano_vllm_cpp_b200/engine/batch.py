@@ -52,12 +52,47 @@ def _align4(n: int) -> int:
     return (n + 3) & ~3
 
 
-def build_batch(entries: list, infos: list, tables: list, max_blocks: int, device) -> StepBatch:
-    """``infos``: EntryInfo per entry; ``tables``: per group, per entry, the list of page ids."""
-    S = len(entries)
-    T = sum(len(e.tokens) for e in entries)
-    n_want = sum(len(e.want) for e in entries)
-    G = len(tables)
+class BatchStager:
+    """A small ring of pinned host buffers for the index arrays, so that a step allocates no pinned
+    memory and the host never overwrites a buffer whose copy to the device may still be queued."""
+
+    def __init__(self, device, depth: int = 4):
+        self.device = torch.device(device)
+        self.depth = depth
+        self.bufs = [None] * depth
+        self.events = [None] * depth
+        self.at = 0
+
+    def stage(self, host: np.ndarray, static_dev=None) -> torch.Tensor:
+        """Copies ``host`` (int32) to the device: into ``static_dev`` if given, else into a new tensor."""
+        n = host.shape[0]
+        if self.device.type != "cuda":
+            t = torch.from_numpy(host.copy())
+            if static_dev is not None:
+                static_dev[:n].copy_(t)
+                return static_dev
+            return t
+        i = self.at
+        self.at = (self.at + 1) % self.depth
+        if self.events[i] is not None:
+            self.events[i].synchronize()
+        if self.bufs[i] is None or self.bufs[i].numel() < n:
+            self.bufs[i] = torch.empty(max(n, 1024), dtype=torch.int32).pin_memory()
+        pinned = self.bufs[i]
+        pinned.numpy()[:n] = host
+        if static_dev is not None:
+            static_dev[:n].copy_(pinned[:n], non_blocking=True)
+            dev = static_dev
+        else:
+            dev = pinned[:n].to(self.device, non_blocking=True)
+        if self.events[i] is None:
+            self.events[i] = torch.cuda.Event()
+        self.events[i].record()
+        return dev
+
+
+def batch_layout(S: int, T: int, n_want: int, G: int, max_blocks: int):
+    """Offsets of the index arrays inside the one int32 buffer of a step: name -> (offset, length)."""
     seg = {}
     off = 0
     for name, n in (("ids", T), ("pos", T), ("row_entry", T), ("cu", S + 1), ("pos0", S), ("slot", S),
@@ -67,7 +102,20 @@ def build_batch(entries: list, infos: list, tables: list, max_blocks: int, devic
     for g in range(G):
         seg[f"bt{g}"] = (off, S * max_blocks)
         off = _align4(off + S * max_blocks)
-    host = np.full(max(off, 4), -1, dtype=np.int32)
+    return seg, max(off, 4)
+
+
+def build_batch(entries: list, infos: list, tables: list, max_blocks: int, device, stager=None,
+                static_dev=None) -> StepBatch:
+    """``infos``: EntryInfo per entry; ``tables``: per group, per entry, the list of page ids.
+    With ``static_dev`` the arrays are written into that device buffer (whose layout must be the one
+    of ``batch_layout`` for these sizes) instead of a fresh one."""
+    S = len(entries)
+    T = sum(len(e.tokens) for e in entries)
+    n_want = sum(len(e.want) for e in entries)
+    G = len(tables)
+    seg, total = batch_layout(S, T, n_want, G, max_blocks)
+    host = np.full(total, -1, dtype=np.int32)
 
     def put(name, values):
         o, n = seg[name]
@@ -92,10 +140,9 @@ def build_batch(entries: list, infos: list, tables: list, max_blocks: int, devic
             if len(table) > max_blocks:
                 raise ValueError("a request holds more pages than the block table is wide")
             host[o + i * max_blocks:o + i * max_blocks + len(table)] = table
-    pinned = torch.from_numpy(host)
-    if torch.device(device).type == "cuda":
-        pinned = pinned.pin_memory()
-    dev = pinned.to(device, non_blocking=True)
+    if stager is None:
+        stager = BatchStager(device, depth=1)
+    dev = stager.stage(host, static_dev)
 
     def view(name):
         o, n = seg[name]

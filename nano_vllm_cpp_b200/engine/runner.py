@@ -16,7 +16,7 @@ from ..cache import CacheManager, DeviceCache
 from ..csrc import ops
 from ..parts.base import RunContext, KVCacheSpec
 from ..weights.loader import load_model
-from .batch import StepEntry, EntryInfo, build_batch
+from .batch import StepEntry, EntryInfo, build_batch, batch_layout, BatchStager
 
 _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32, "bf16": torch.bfloat16, "fp32": torch.float32}
 
@@ -30,7 +30,7 @@ class ModelRunner:
                  max_tokens: int | None = None, max_requests: int = 4, max_model_len: int | None = None,
                  device: str = "cuda:0", random_seed: int | None = None, norm_std: float = 0.0,
                  std: float | None = None, gpu_memory_utilization: float = 0.9, prefix_caching: bool = False,
-                 fast_kernels: bool = True):
+                 fast_kernels: bool = True, cuda_graphs: bool = True):
         if not torch.cuda.is_available():
             raise StepError("no CUDA device: this engine runs on the GPU only (there is no CPU fallback)")
         if dtype not in _DTYPES:
@@ -57,6 +57,10 @@ class ModelRunner:
                                     prefix_caching=prefix_caching)
         self.num_pages = num_pages
         self.last_h2d_bytes = 0
+        self.stager = BatchStager(self.device)
+        self.cuda_graphs = cuda_graphs and self.model.graph_safe
+        self._graphs: dict = {}        # decode batch size -> captured step
+        self._seen: dict = {}
 
     def _pages_from_free_memory(self, utilization: float) -> int:
         free, total = torch.cuda.mem_get_info(self.device)
@@ -79,7 +83,7 @@ class ModelRunner:
         return self.manager.get(rid).num_tokens
 
     # ------------------------------------------------------------------ the step
-    def prepare(self, entries: list):
+    def prepare(self, entries: list, static_dev=None):
         """Takes pages for the entries' positions and builds the batch arrays."""
         infos, row0 = [], 0
         seen = set()
@@ -99,7 +103,7 @@ class ModelRunner:
             infos.append(EntryInfo(e.rid, rc.slot, start, len(e.tokens), row0))
             row0 += len(e.tokens)
         tables = [[self.manager.get(e.rid).tables[g] for e in entries] for g in range(len(self.manager.pools))]
-        batch = build_batch(entries, infos, tables, self.max_blocks, self.device)
+        batch = build_batch(entries, infos, tables, self.max_blocks, self.device, self.stager, static_dev)
         self.last_h2d_bytes = batch.h2d_bytes
         return batch
 
@@ -109,10 +113,44 @@ class ModelRunner:
         caller then reads it later with ``ctx.err.check``."""
         if not entries:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
-        batch = self.prepare(entries)
-        logits = self.model.forward(batch, self.cache)
+        logits = batch = None
+        if self.cuda_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
+            logits, batch = self._graph_step(entries)
+        if batch is None:
+            batch = self.prepare(entries)
+            logits = self.model.forward(batch, self.cache)
         if check:
             self.ctx.err.check("step")
         for info in batch.entries:
             self.manager.commit(info.rid, info.pos0 + info.length)
         return logits
+
+    # ------------------------------------------------------------------ decode steps as CUDA graphs
+    def _graph_step(self, entries: list):
+        """A batch of single rows that all want their logits always launches the same kernels with the
+        same sizes; only the index arrays differ.  Such a step is captured once per batch size and
+        replayed afterwards: the arrays are copied into the buffer the graph reads, and the graph's
+        logits tensor is returned (valid until the next step of the same size)."""
+        S = len(entries)
+        g = self._graphs.get(S)
+        if g is None:
+            self._seen[S] = self._seen.get(S, 0) + 1
+            if self._seen[S] < 2 or len(self._graphs) >= 24:
+                return None, None          # a size seen once is not worth a capture
+            seg, total = batch_layout(S, S, S, len(self.manager.pools), self.max_blocks)
+            static_dev = torch.full((total,), -1, dtype=torch.int32, device=self.device)
+            batch = self.prepare(entries, static_dev)
+            batch.max_context = self.max_model_len        # the split of the keys must not depend on the step
+            logits = self.model.forward(batch, self.cache)       # warms up; also this step's result
+            torch.cuda.synchronize(self.device)
+            before = ops.launch_count()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                static_logits = self.model.forward(batch, self.cache)
+            self._graphs[S] = (graph, static_dev, static_logits, ops.launch_count() - before)
+            return logits, batch
+        graph, static_dev, static_logits, launches = g
+        batch = self.prepare(entries, static_dev)
+        graph.replay()
+        ops.add_launches(launches)
+        return static_logits, batch

@@ -72,9 +72,14 @@ class PagedAttention(Mixer):
     def _attend(self, qkv, cache, bt, batch, att):
         # bfloat16 runs take the split-key kernel for batches of single rows; float32 runs keep the
         # plain kernel everywhere, so that their sums have one order however the work is cut
-        if self.ctx.fast_kernels and self.ctx.act_dtype == torch.bfloat16 and batch.decode_only:
-            ops.attention_decode(qkv, cache.k, cache.v, bt, batch.row_entry, batch.positions, self.scale,
-                                 self.window, att, self.Hq, self.Hkv, self.D, batch.max_context)
+        if self.ctx.fast_kernels and self.ctx.act_dtype == torch.bfloat16 and cache.k.dtype == torch.bfloat16:
+            if batch.decode_only:
+                ops.attention_decode(qkv, cache.k, cache.v, bt, batch.row_entry, batch.positions, self.scale,
+                                     self.window, att, self.Hq, self.Hkv, self.D, batch.max_context)
+            else:
+                tiles = sum((e.length + 63) // 64 for e in batch.entries)
+                ops.attention_prefill(qkv, cache.k, cache.v, bt, batch.cu_rows, batch.entry_pos0, tiles, self.scale,
+                                      self.window, att, self.Hq, self.Hkv, self.D)
             return
         ops.paged_attention_plain(qkv, cache.k, cache.v, bt, batch.row_entry, batch.positions, self.scale,
                                   self.window, att, self.Hq, self.Hkv, self.D)

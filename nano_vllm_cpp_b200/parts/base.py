@@ -64,6 +64,10 @@ Fetch = Callable[[str], torch.Tensor]
 
 
 class Part:
+    # False for a part whose forward does per-step work on the host (reads ``batch.entries``, branches on
+    # values): steps of a model with such a part are never captured into a CUDA graph.
+    graph_safe: bool = True
+
     def tensor_specs(self, available=None) -> dict:
         """``available(name) -> bool`` tells which of several accepted layouts a file holds."""
         return {}

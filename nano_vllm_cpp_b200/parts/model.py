@@ -72,6 +72,10 @@ class Model:
             if c.cache_of is not None and not (0 <= c.cache_of < i and self.calls[c.cache_of].cache_of is None):
                 raise ValueError(f"call {i}: cache_of must name an earlier call that owns its cache entry")
 
+    @property
+    def graph_safe(self) -> bool:
+        return all(part.graph_safe for _, part in self._named_parts())
+
     # ------------------------------------------------------------------ tensors
     def _named_parts(self):
         for i, layer in enumerate(self.layers):

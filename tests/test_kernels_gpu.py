@@ -382,3 +382,36 @@ def test_rope_store(Hq, Hkv, D, rot, dtype):
                  True, err)
     with pytest.raises(o.KernelError):
         err.check("rope")
+
+
+@pytest.mark.parametrize("Hq,Hkv,D,page", [(3, 1, 32, 16), (4, 4, 16, 16), (6, 2, 48, 32), (4, 2, 128, 16), (2, 1, 256, 16),
+                                           (5, 5, 80, 16)])
+@pytest.mark.parametrize("window", [0, 20, 100])
+def test_attention_prefill_against_plain(Hq, Hkv, D, page, window):
+    """Portions of several requests in one batch: a whole prompt, a portion that continues a cached
+    prefix, a single decode row, a two-row portion, a portion longer than two tiles."""
+    o = ops()
+    ctx_len = [0, 130, 75, 31, 5]        # tokens already in the cache
+    new = [70, 40, 1, 2, 150]            # rows of this step
+    lens = [c + n for c, n in zip(ctx_len, new)]
+    kc, vc, bt, ks, vs = paged_setup(lens, Hkv, D, page, torch.bfloat16, seed=D + window)
+    T = sum(new)
+    qkv = rnd(T, (Hq + 2 * Hkv) * D, dtype=torch.bfloat16, seed=11)
+    cu = [0]
+    for n in new:
+        cu.append(cu[-1] + n)
+    pos = torch.tensor([c + i for c, n in zip(ctx_len, new) for i in range(n)], dtype=torch.int32, device=DEV)
+    row_entry = torch.tensor([e for e, n in enumerate(new) for _ in range(n)], dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(D)
+    ref = torch.empty(T, Hq * D, dtype=torch.bfloat16, device=DEV)
+    o.paged_attention_plain(qkv, kc, vc, bt, row_entry, pos, scale, window, ref, Hq, Hkv, D)
+    out = torch.full_like(ref, float("nan"))
+    tiles = sum((n + 63) // 64 for n in new)
+    o.attention_prefill(qkv, kc, vc, bt, torch.tensor(cu, dtype=torch.int32, device=DEV),
+                        torch.tensor(ctx_len, dtype=torch.int32, device=DEV), tiles, scale, window, out, Hq, Hkv, D)
+    close(out, ref, 1.5e-2, "prefill vs plain")
+    # and a few rows against float64
+    for r in (0, 69, 70, 109, 110, 112, T - 1):
+        e = int(row_entry[r])
+        want = attention_reference(qkv[r, :Hq * D].reshape(Hq, D).cpu(), ks[e], vs[e], int(pos[r]), scale, window)
+        close(out[r], want.reshape(-1), 1.5e-2, f"row {r}")
