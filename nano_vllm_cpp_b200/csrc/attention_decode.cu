@@ -296,3 +296,47 @@ NV_API int nv_attention_decode(const void* qkv, int q_dt, int q_stride, const vo
   }
   NV_RETURN_LAST();
 }
+
+// ------------------------------------------------------------------------------------------------
+// The variant that allocates nothing (declared and described in no_alloc.h).
+#include "no_alloc.h"
+
+namespace {
+
+// Partial results of the key splits.  In host code this name is only a stand-in for the symbol, not
+// a device address: the address is looked up once per device below and that pointer goes to the kernel.
+static __device__ __align__(256) float g_noalloc_scratch[NV_NOALLOC_SCRATCH_FLOATS];
+
+constexpr int MAX_DEVICES = 64;
+float* g_noalloc_ptr[MAX_DEVICES] = {};   // device address of the array, per device, once looked up
+
+}  // namespace
+
+NV_API int nv_attention_decode_noalloc_max_rows(int Hq, int D, int splits) {
+  if (Hq <= 0 || D <= 0) return 0;
+  if (splits <= 1) return 0x7fffffff;      // one split writes its result directly and needs no scratch
+  return (int)((long long)NV_NOALLOC_SCRATCH_FLOATS / ((long long)Hq * splits * (D + 2)));
+}
+
+NV_API int nv_attention_decode_noalloc(const void* qkv, int q_dt, int q_stride, const void* kc, const void* vc,
+                                       int cache_dt, const int* block_table, int max_blocks, const int* row_entry,
+                                       const int* positions, const int* rows, int R, float scale, int window,
+                                       void* out, int out_dt, int Hq, int Hkv, int D, int page, int splits,
+                                       cudaStream_t stream) {
+  if (splits < 1) splits = 1;
+  if (nv_attention_decode_scratch_floats(R, Hq, D, splits) > (long long)NV_NOALLOC_SCRATCH_FLOATS)
+    return NV_ERR_NOALLOC_TOO_LARGE;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= MAX_DEVICES) return NV_ERR_UNSUPPORTED;
+  if (!g_noalloc_ptr[dev]) {               // set-up, once per device, with that device current
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_noalloc_scratch);
+    if (e != cudaSuccess) return (int)e;
+    g_noalloc_ptr[dev] = p;
+  }
+  return nv_attention_decode(qkv, q_dt, q_stride, kc, vc, cache_dt, block_table, max_blocks, row_entry, positions,
+                             rows, R, scale, window, out, out_dt, Hq, Hkv, D, page, splits, g_noalloc_ptr[dev],
+                             stream);
+}

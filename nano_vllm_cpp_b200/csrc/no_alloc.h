@@ -1,0 +1,47 @@
+// Decode attention for callers that cannot allocate device memory.
+//
+// This entry point has no counterpart in the reference project; it exists for this library's users.
+//
+// Who needs it: the engine gives nearly all free device memory to the key/value page pool when it
+// starts, so a later cudaMalloc (the split-key partial results of nv_attention_decode are such a
+// buffer, and torch's allocator falls back to cudaMalloc when its cache is empty) can fail or stall
+// exactly when the server is busiest; and a host thread that drives the GPU from a latency-critical
+// loop must not run into cudaMalloc / cudaFree, which synchronise the whole device.  Such callers
+// pass only inputs and outputs; the partial results live in a fixed array inside the library.
+//
+//   * The array is file-scope device memory of NV_NOALLOC_SCRATCH_FLOATS floats (4 MiB).  Every GPU
+//     that loads the library holds it from the load until the process exits.
+//   * A call whose partial results would not fit — rows * Hq * splits * (D + 2) floats — is refused
+//     with NV_ERR_NOALLOC_TOO_LARGE and launches nothing.  nv_attention_decode_noalloc_max_rows tells
+//     how many rows fit for given sizes.
+//   * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with that
+//     device current) and keeps it; make that first call before any stream capture.  Later calls do
+//     no set-up.  No call allocates or frees anything, on the device or through a library.
+//   * All calls share the one array, and it keeps the last call's contents.  Nothing in it has to
+//     start at zero: every slot a call reads was written by that call first.  Two calls that overlap
+//     on the GPU (different streams, no ordering between them) race on the array; order them.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#define NV_NOALLOC_SCRATCH_FLOATS (1 << 20)
+#define NV_ERR_NOALLOC_TOO_LARGE (-6)
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// Same arguments and result as nv_attention_decode without `scratch`; `splits` >= 1 as chosen by the caller
+// (nv_attention_decode_splits gives the library's own choice).  Returns 0, a negative NV_ERR_* code or a
+// cudaError_t.
+int nv_attention_decode_noalloc(const void* qkv, int q_dt, int q_stride, const void* kc, const void* vc, int cache_dt,
+                                const int* block_table, int max_blocks, const int* row_entry, const int* positions,
+                                const int* rows, int R, float scale, int window, void* out, int out_dt, int Hq,
+                                int Hkv, int D, int page, int splits, cudaStream_t stream);
+
+// Largest number of rows one call can take for these sizes (0 if not even one fits).
+int nv_attention_decode_noalloc_max_rows(int Hq, int D, int splits);
+
+#ifdef __cplusplus
+}
+#endif
