@@ -1,0 +1,345 @@
+"""The parts of a layer one by one against the plain implementation, at sizes of their own; the
+order list (a layer run twice, a call that reads another call's cache); and a toy mixer with a
+per-request state that is defined here, registered, built from a config.json and stepped through the
+engine without any change to the package."""
+import json
+import os
+from dataclasses import dataclass
+
+import numpy as np
+import pytest
+import torch
+
+import helpers
+import plain_model as pm
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def ctx_for(dtype):
+    from nano_vllm_cpp_b200.csrc import ops
+    from nano_vllm_cpp_b200.parts import RunContext
+    return RunContext(device=torch.device(DEV), act_dtype=dtype, err=ops.ErrorFlag(DEV), page_size=16)
+
+
+class DictFetch:
+    """Hands a part its tensors from a dict of float64 CPU tensors, in the run's storage types."""
+
+    def __init__(self, tensors, dtype):
+        self.t, self.dtype = tensors, dtype
+
+    def __call__(self, name):
+        t = self.t[name]
+        return t.to(torch.float32 if t.dim() == 1 else self.dtype).to(DEV)
+
+    def has(self, name):
+        return name in self.t
+
+
+def rand_tensors(specs, seed, std=0.1, dtype=torch.bfloat16):
+    """Random values already rounded to bfloat16, as float64 (so both runs and the plain code see the same)."""
+    g = torch.Generator().manual_seed(seed)
+    out = {}
+    for name, s in specs.items():
+        t = torch.randn(s.shape, generator=g) * std
+        if s.init == "ones":
+            t = t + 1.0
+        out[name] = t.to(torch.bfloat16).double()
+    return out
+
+
+def tol(dtype):
+    return 2e-5 if dtype == torch.float32 else 2e-2
+
+
+def close(got, want, rel, what):
+    got, want = got.double().cpu(), want.double().cpu()
+    err = float((got - want).abs().max())
+    bound = rel * max(1e-3, float(want.abs().max()))
+    assert err <= bound, f"{what}: max error {err:.3g} > {bound:.3g}"
+
+
+# ------------------------------------------------------------------------------- parts alone
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rmsnorm_part(dtype):
+    from nano_vllm_cpp_b200.parts import build_part, PartSpec
+    H = 200
+    part = build_part("norm", PartSpec("rmsnorm", dict(size=H, eps=1e-5)))
+    W = rand_tensors(part.tensor_specs(), 1)
+    part.load(DictFetch(W, dtype), ctx_for(dtype))
+    x = torch.randn(9, H, generator=torch.Generator().manual_seed(2))
+    br = torch.randn(9, H, generator=torch.Generator().manual_seed(3))
+    xd = x.to(DEV)
+    out, out32 = part.forward(xd, br.to(DEV), want_f32=True)
+    want = pm.rms_norm(x.double() + br.double(), W["weight"], 1e-5)
+    close(xd, x.double() + br.double(), 1e-6, "stream")
+    close(out32, want, 2e-6, "float32 copy")
+    close(out, want, tol(dtype) if dtype == torch.bfloat16 else 2e-6, "normalised rows")
+    assert out.dtype == dtype
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_dense_swiglu_part(dtype):
+    from nano_vllm_cpp_b200.parts import build_part, PartSpec
+    H, I = 136, 200
+    part = build_part("feed_forward", PartSpec("dense_swiglu", dict(hidden_size=H, intermediate_size=I)))
+    W = rand_tensors(part.tensor_specs(), 4)
+    part.load(DictFetch(W, dtype), ctx_for(dtype))
+    h = (torch.randn(21, H, generator=torch.Generator().manual_seed(5))).to(torch.bfloat16)
+    out = part.forward(h.to(dtype).to(DEV), None, None)
+    want = pm.dense_mlp(h.double(), W, "")
+    assert out.dtype == torch.float32
+    close(out, want, tol(dtype), "dense mlp")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("E,K,renorm,SI", [(10, 3, True, 72), (5, 5, False, 0), (60, 4, False, 264)])
+def test_sparse_moe_part(dtype, E, K, renorm, SI):
+    from nano_vllm_cpp_b200.parts import build_part, PartSpec
+    H, I = 136, 56
+    part = build_part("feed_forward", PartSpec("sparse_moe_swiglu", dict(
+        hidden_size=H, num_experts=E, top_k=K, intermediate_size=I, shared_intermediate_size=SI, renormalize=renorm)))
+    W = rand_tensors(part.tensor_specs(), 6, std=0.2)
+    ctx = ctx_for(dtype)
+    part.load(DictFetch(W, dtype), ctx)
+    h = (torch.randn(37, H, generator=torch.Generator().manual_seed(7))).to(torch.bfloat16)
+    hd = h.to(dtype).to(DEV)
+    out = part.forward(hd, h.float().to(DEV), None)
+    ctx.err.check("moe")
+    cfg = dict(num_experts=E, num_experts_per_tok=K, norm_topk_prob=renorm, shared_expert_intermediate_size=SI,
+               moe_intermediate_size=I)
+    want = pm.sparse_mlp(h.double(), W, "", cfg)
+    close(out, want, tol(dtype), "sparse mlp")
+    # the stacked layout of the expert tensors gives the same layer
+    stacked = {k: v for k, v in W.items() if not k.startswith("experts.")}
+    stacked["experts.gate_up_proj"] = torch.stack([torch.cat([W[f"experts.{e}.gate_proj.weight"], W[f"experts.{e}.up_proj.weight"]]) for e in range(E)])
+    stacked["experts.down_proj"] = torch.stack([W[f"experts.{e}.down_proj.weight"] for e in range(E)])
+    part2 = build_part("feed_forward", PartSpec("sparse_moe_swiglu", dict(
+        hidden_size=H, num_experts=E, top_k=K, intermediate_size=I, shared_intermediate_size=SI, renormalize=renorm)))
+    assert set(part2.tensor_specs(lambda n: n in stacked)) == set(stacked)
+    part2.load(DictFetch(stacked, dtype), ctx)
+    assert torch.equal(part2.forward(hd, h.float().to(DEV), None), out)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("Hq,Hkv,D,window,bias", [(6, 2, 32, 0, True), (3, 3, 48, 10, False), (5, 1, 16, 33, True)])
+def test_attention_part_in_portions(dtype, Hq, Hkv, D, window, bias):
+    """Two requests; the first runs whole, the second in a portion, then both get one more row."""
+    from nano_vllm_cpp_b200.parts import build_part, PartSpec
+    from nano_vllm_cpp_b200.cache import DeviceCache
+    H = 72
+    part = build_part("mixer", PartSpec("paged_attention", dict(
+        hidden_size=H, num_heads=Hq, num_kv_heads=Hkv, head_dim=D, bias=bias, window=window,
+        position=PartSpec("rotary_neox", dict(rotary_dim=D, theta=5000.0)))))
+    W = rand_tensors(part.tensor_specs(), 8, std=0.15)
+    ctx = ctx_for(dtype)
+    part.load(DictFetch(W, dtype), ctx)
+    cache = DeviceCache([part.cache_spec()], 16, 4, DEV, dtype)
+    cache.allocate(16)
+    g = torch.Generator().manual_seed(9)
+    xa = torch.randn(40, H, generator=g).to(torch.bfloat16)
+    xb = torch.randn(50, H, generator=g).to(torch.bfloat16)
+    cfg = dict(num_attention_heads=Hq, num_key_value_heads=Hkv, head_dim=D, rope_theta=5000.0,
+               use_sliding_window=window > 0, sliding_window=window, max_window_layers=0)
+    want_a = pm.attention_layer(xa.double(), W, "", cfg, 0, list(range(40)))
+    want_b = pm.attention_layer(xb.double(), W, "", cfg, 0, list(range(50)))
+    # step 1: a whole minus one row (39 rows), b's first 20 rows.  Pages: a -> 0..2, b -> 3..6
+    from nano_vllm_cpp_b200.engine.batch import StepEntry, EntryInfo, build_batch
+    ta, tb = [0, 1, 2], [3, 4, 5, 6]
+
+    def run(parts):
+        ses, infos, tabs, rows, row0 = [], [], [], [], 0
+        for slot, (x, table, p0, n) in enumerate(parts):
+            ses.append(StepEntry(slot, [0] * n, []))
+            infos.append(EntryInfo(slot, slot, p0, n, row0))
+            tabs.append(table)
+            rows.append(x[p0:p0 + n])
+            row0 += n
+        batch = build_batch(ses, infos, [tabs], 8, DEV)
+        out = part.forward(torch.cat(rows).to(dtype).to(DEV), batch, cache.view(0))
+        ctx.err.check("attention")
+        return out
+
+    o1 = run([(xa, ta, 0, 39), (xb, tb, 0, 20)])
+    close(o1[:39], want_a[:39], tol(dtype), "a rows 0..38")
+    close(o1[39:], want_b[:20], tol(dtype), "b rows 0..19")
+    o2 = run([(xa, ta, 39, 1), (xb, tb, 20, 29)])
+    close(o2[:1], want_a[39:], tol(dtype), "a row 39")
+    close(o2[1:], want_b[20:49], tol(dtype), "b rows 20..48")
+    o3 = run([(xb, tb, 49, 1)])
+    close(o3, want_b[49:], tol(dtype), "b row 49 (decode kernel in bfloat16)")
+
+
+def test_part_constructors_refuse_what_the_kernels_cannot_take():
+    from nano_vllm_cpp_b200.parts import build_part, PartSpec
+    pos = PartSpec("none", {})
+    with pytest.raises(ValueError, match="head_dim"):
+        build_part("mixer", PartSpec("paged_attention", dict(hidden_size=64, num_heads=2, num_kv_heads=2, head_dim=24, bias=False, position=pos)))
+    with pytest.raises(ValueError, match="head_dim"):
+        build_part("mixer", PartSpec("paged_attention", dict(hidden_size=64, num_heads=2, num_kv_heads=2, head_dim=512, bias=False, position=pos)))
+    with pytest.raises(ValueError, match="multiple"):
+        build_part("mixer", PartSpec("paged_attention", dict(hidden_size=64, num_heads=3, num_kv_heads=2, head_dim=16, bias=False, position=pos)))
+    with pytest.raises(ValueError, match="top_k"):
+        build_part("feed_forward", PartSpec("sparse_moe_swiglu", dict(hidden_size=64, num_experts=4, top_k=5, intermediate_size=8)))
+    with pytest.raises(KeyError, match="no mixer part"):
+        build_part("mixer", PartSpec("does_not_exist", {}))
+
+
+# ------------------------------------------------------------------------------- the order list
+def plain_with_order(cfg, W, ids, order):
+    """plain_model.forward with an explicit list of (layer, cache_of) calls: a call with cache_of reads the
+    keys and values that the named earlier call made and makes none of its own."""
+    T = len(ids)
+    eps = cfg["rms_norm_eps"]
+    x = pm.embedding(W["model.embed_tokens.weight"], ids)
+    Hq, Hkv, D = cfg["num_attention_heads"], cfg["num_key_value_heads"], pm.head_dim(cfg)
+    kv = {}
+    for ci, (l, cache_of) in enumerate(order):
+        p = f"model.layers.{l}."
+        h = pm.rms_norm(x, W[p + "input_layernorm.weight"], eps)
+        proj = lambda n, heads: (h @ W[p + f"self_attn.{n}.weight"].T + W[p + f"self_attn.{n}.bias"]).reshape(T, heads, D)
+        q = pm.rope_neox(proj("q_proj", Hq), list(range(T)), cfg["rope_theta"])
+        if cache_of is None:
+            kv[ci] = (pm.rope_neox(proj("k_proj", Hkv), list(range(T)), cfg["rope_theta"]), proj("v_proj", Hkv))
+            k, v = kv[ci]
+        else:
+            k, v = kv[cache_of]
+        a = pm.causal_attention(q, k, v, 1.0 / np.sqrt(D), pm.layer_window(cfg, l))
+        x = x + a.reshape(T, Hq * D) @ W[p + "self_attn.o_proj.weight"].T
+        h = pm.rms_norm(x, W[p + "post_attention_layernorm.weight"], eps)
+        x = x + (pm.sparse_mlp(h, W, p + "mlp.", cfg) if pm.layer_is_sparse(cfg, l) else pm.dense_mlp(h, W, p + "mlp."))
+    return pm.rms_norm(x, W["model.norm.weight"], eps) @ W["lm_head.weight"].T
+
+
+def test_order_list_repeats_a_layer_and_shares_a_cache(tmp_path):
+    from nano_vllm_cpp_b200.config import register_architecture, Qwen2MoeConfig
+    from nano_vllm_cpp_b200.models.qwen2_moe import build_spec
+    from nano_vllm_cpp_b200.parts import LayerCall
+    from nano_vllm_cpp_b200.engine.runner import ModelRunner
+    order = [(0, None), (1, None), (1, None), (0, 0)]
+
+    def build(cfg):
+        spec = build_spec(cfg)
+        spec.order = [LayerCall(l, c) for l, c in order]
+        return spec
+
+    register_architecture("ToyOrderForCausalLM", Qwen2MoeConfig.from_dict, build)
+    mdir = helpers.model_folder("A", str(tmp_path))
+    cfg = json.load(open(os.path.join(mdir, "config.json")))
+    cfg["architectures"] = ["ToyOrderForCausalLM"]
+    json.dump(cfg, open(os.path.join(mdir, "config.json"), "w"))
+    pcfg, W = pm.read_folder(mdir)
+    ids = helpers.prompt("A", 45, salt=30)
+    want = plain_with_order(pcfg, W, ids, order)
+    runner = ModelRunner(mdir, dtype="float32", max_tokens=128)
+    assert len(runner.cache.views) == 4 and runner.cache.views[3].k is runner.cache.views[0].k
+    assert runner.cache.views[2].k is not runner.cache.views[1].k and not runner.cache.views[3].write
+    rp = helpers.Replay(runner)
+    for a, b in ((0, 20), (20, 22), (22, 44), (44, 45)):
+        rp.step([("o", ids[a:b], True)])
+    got = torch.stack([rp.logits[("o", p)] for p in range(45)])
+    helpers.assert_close(got, want, "float32", "order list")
+
+
+# ------------------------------------------------------------------------------- a toy mixer with state
+@dataclass
+class ToyConfig:
+    vocab_size: int
+    hidden_size: int
+    num_hidden_layers: int
+    intermediate_size: int
+    rms_norm_eps: float
+    decay: float
+
+    @classmethod
+    def from_dict(cls, d):
+        return cls(d["vocab_size"], d["hidden_size"], d["num_hidden_layers"], d["intermediate_size"],
+                   d["rms_norm_eps"], d["decay"])
+
+
+def define_toy():
+    """A mixer that keeps one vector per request: s_t = decay * s_{t-1} + h_t, out_t = W s_t."""
+    from nano_vllm_cpp_b200.parts import Mixer, TensorSpec, StateCacheSpec, PartSpec, LayerSpec, ModelSpec, register_part
+    from nano_vllm_cpp_b200.config import register_architecture
+
+    class DecayingSum(Mixer):
+        graph_safe = False                      # walks the entries on the host
+
+        def __init__(self, hidden_size, decay):
+            self.hidden, self.decay = hidden_size, decay
+
+        def tensor_specs(self, available=None):
+            return {"mix.weight": TensorSpec((self.hidden, self.hidden))}
+
+        def load(self, fetch, ctx):
+            self.ctx = ctx
+            self.w = fetch("mix.weight").float()
+
+        def cache_spec(self):
+            return StateCacheSpec((self.hidden,), torch.float32)
+
+        def forward(self, h, batch, cache):
+            out = torch.empty((batch.T, self.hidden), dtype=torch.float32, device=h.device)
+            for e in batch.entries:
+                s = cache.state[e.slot]
+                for r in range(e.row0, e.row0 + e.length):
+                    s = self.decay * s + h[r].float()
+                    out[r] = self.w @ s
+                cache.state[e.slot] = s
+            return out
+
+    register_part("mixer", "toy_decaying_sum", DecayingSum)
+
+    def build(cfg):
+        norm = PartSpec("rmsnorm", dict(size=cfg.hidden_size, eps=cfg.rms_norm_eps))
+
+        def layer():
+            return LayerSpec(
+                norm1=norm, mixer=PartSpec("toy_decaying_sum", dict(hidden_size=cfg.hidden_size, decay=cfg.decay)),
+                norm2=norm, feed_forward=PartSpec("dense_swiglu", dict(hidden_size=cfg.hidden_size,
+                                                                       intermediate_size=cfg.intermediate_size)),
+                names={"norm1": "ln1.", "mixer": "toy.", "norm2": "ln2.", "feed_forward": "mlp."})
+
+        return ModelSpec(vocab_size=cfg.vocab_size, hidden_size=cfg.hidden_size,
+                         layers=[layer() for _ in range(cfg.num_hidden_layers)], final_norm=norm,
+                         tie_word_embeddings=True, init_std=0.1)
+
+    register_architecture("ToyStateForCausalLM", ToyConfig.from_dict, build)
+
+
+def toy_plain(cfg, W, ids):
+    x = pm.embedding(W["model.embed_tokens.weight"], ids)
+    for l in range(cfg["num_hidden_layers"]):
+        p = f"model.layers.{l}."
+        h = pm.rms_norm(x, W[p + "ln1.weight"], cfg["rms_norm_eps"])
+        s = torch.zeros(cfg["hidden_size"], dtype=torch.float64)
+        out = []
+        for t in range(len(ids)):
+            s = cfg["decay"] * s + h[t]
+            out.append(W[p + "toy.mix.weight"] @ s)
+        x = x + torch.stack(out)
+        h = pm.rms_norm(x, W[p + "ln2.weight"], cfg["rms_norm_eps"])
+        x = x + pm.dense_mlp(h, W, p + "mlp.")
+    return pm.rms_norm(x, W["model.norm.weight"], cfg["rms_norm_eps"]) @ W["model.embed_tokens.weight"].T
+
+
+def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
+    from nano_vllm_cpp_b200.weights import write_model_folder
+    from nano_vllm_cpp_b200.engine.runner import ModelRunner
+    define_toy()
+    cfg = dict(architectures=["ToyStateForCausalLM"], vocab_size=90, hidden_size=40, num_hidden_layers=2,
+               intermediate_size=56, rms_norm_eps=1e-5, decay=0.9)
+    mdir = write_model_folder(cfg, str(tmp_path / "toy"), seed=3, norm_std=0.1, dtype="float32")
+    _, W = pm.read_folder(mdir)
+    runner = ModelRunner(mdir, dtype="float32", max_tokens=64, max_requests=2)
+    assert [v.kind for v in runner.cache.views] == ["state", "state"] and not runner.cuda_graphs
+    g = np.random.RandomState(0)
+    ids = {r: [int(t) for t in g.randint(0, 90, size=n)] for r, n in (("a", 23), ("b", 9), ("c", 12))}
+    rp = helpers.Replay(runner)
+    rp.step([("a", ids["a"][:10], True), ("b", ids["b"][:2], True)])
+    rp.step([("a", ids["a"][10:11], True), ("b", ids["b"][2:], True)], end=["b"])
+    rp.step([("a", ids["a"][11:], True), ("c", ids["c"], True)])      # c takes b's slot: its state starts from zero
+    for r in ids:
+        got = torch.stack([rp.logits[(r, p)] for p in range(len(ids[r]))])
+        helpers.assert_close(got, toy_plain(cfg, W, ids[r]), "float32", f"toy request {r}")
