@@ -42,6 +42,11 @@ int nv_attention_decode_noalloc(const void* qkv, int q_dt, int q_stride, const v
 // Largest number of rows one call can take for these sizes (0 if not even one fits).
 int nv_attention_decode_noalloc_max_rows(int Hq, int D, int splits);
 
+// 0 while no kernel launched through this entry point has reported trouble on the current device (a block
+// table without a page it needed, a copy that never arrived).  Reading it waits for the device; it is
+// meant for tests and for diagnosis, not for the serving loop.
+int nv_attention_decode_noalloc_status(void);
+
 #ifdef __cplusplus
 }
 #endif

@@ -184,17 +184,22 @@ def gemm_plain(a, w, out, *, bias=None, a_rows=None, swiglu=False, M=None, tiles
 
 def rowdot(a, w, out) -> None:
     """out[t, n] = a[t, :] . w[n, :] for float32 rows and a short matrix (float32 or bfloat16), float32 out."""
-    _cuda_contig(w, out)
-    _need(a.dtype == torch.float32 and out.dtype == torch.float32 and a.stride(1) == 1, "rowdot: float32 rows")
+    _cuda_contig(w)
+    _need(a.dtype == torch.float32 and out.dtype == torch.float32 and a.stride(1) == 1 and out.stride(1) == 1,
+          "rowdot: float32 rows")
     T, K = a.shape
     N = w.shape[0]
     _need(w.shape[1] == K and out.shape == (T, N), "rowdot: shapes")
-    _check(lib().nv_rowdot(_p(a), c_longlong(a.stride(0)), _p(w), c_int(dt(w)), _p(out), c_int(T), c_int(N),
-                           c_int(K), _stream()), "rowdot")
+    _check(lib().nv_rowdot(_p(a), c_longlong(a.stride(0)), _p(w), c_int(dt(w)), _p(out), c_longlong(out.stride(0)),
+                           c_int(T), c_int(N), c_int(K), _stream()), "rowdot")
+
+
+def attention_decode_usable(k_cache, D: int) -> bool:
+    return bool(lib().nv_attention_decode_usable(c_int(D), c_int(k_cache.shape[2]), c_int(dt(k_cache))))
 
 
 def attention_decode(qkv, k_cache, v_cache, block_table, row_entry, positions, scale: float, window: int, out,
-                     Hq: int, Hkv: int, D: int, max_context: int, rows=None) -> None:
+                     Hq: int, Hkv: int, D: int, max_context: int, rows=None, err=None) -> None:
     """One query row per request (``rows``: which batch rows; None = all) against its paged keys."""
     _cuda_contig(qkv, k_cache, v_cache, block_table, row_entry, positions, out, rows)
     _i32(block_table, row_entry, positions, rows)
@@ -209,7 +214,8 @@ def attention_decode(qkv, k_cache, v_cache, block_table, row_entry, positions, s
                                  c_int(dt(k_cache)), _p(block_table), c_int(block_table.shape[1]), _p(row_entry),
                                  _p(positions), _p(rows), c_int(R), c_float(scale), c_int(window), _p(out),
                                  c_int(dt(out)), c_int(Hq), c_int(Hkv), c_int(D), c_int(page), c_int(splits),
-                                 _p(scratch), _stream()), "attention_decode")
+                                 _p(scratch), _p(err.t if err is not None else _global_err().t), _stream()),
+           "attention_decode")
 
 
 def attention_prefill(qkv, k_cache, v_cache, block_table, cu_rows, entry_pos0, max_tiles: int, scale: float,
@@ -262,13 +268,15 @@ def paged_attention_plain(qkv, k_cache, v_cache, block_table, row_entry, positio
 
 
 def router_topk(logits, K: int, renorm: bool, idx, score) -> None:
-    _cuda_contig(logits, idx, score)
+    """``logits`` may be a column slice of a wider float32 matrix (rows ``stride(0)`` apart)."""
+    _cuda_contig(idx, score)
+    _need(logits.is_cuda and logits.stride(1) == 1, "router: logits rows must be dense")
     T, E = logits.shape
     _need(logits.dtype == torch.float32 and score.dtype == torch.float32, "router: float32 logits and scores")
     _i32(idx)
     _need(idx.shape == (T, K) and score.shape == (T, K), "router: output shapes")
-    _check(lib().nv_router_topk(_p(logits), c_int(T), c_int(E), c_int(K), c_int(1 if renorm else 0), _p(idx),
-                                _p(score), _stream()), "router_topk")
+    _check(lib().nv_router_topk(_p(logits), c_longlong(logits.stride(0)), c_int(T), c_int(E), c_int(K),
+                                c_int(1 if renorm else 0), _p(idx), _p(score), _stream()), "router_topk")
 
 
 class MoeAlignment:
@@ -277,7 +285,7 @@ class MoeAlignment:
     def __init__(self, TK: int, E: int, tile_m: int, device):
         i32 = dict(dtype=torch.int32, device=device)
         self.TK, self.E, self.tile_m = TK, E, tile_m
-        self.max_tiles = (TK + tile_m - 1) // tile_m + E
+        self.max_tiles = max(1, min(TK, (TK + tile_m - 1) // tile_m + E))
         self.counts = torch.empty(E, **i32)
         self.offsets = torch.empty(E + 1, **i32)
         self.cursor = torch.empty(E, **i32)
@@ -305,13 +313,15 @@ def moe_align(idx, K: int, al: MoeAlignment, err: ErrorFlag) -> None:
 
 
 def moe_combine(y, pair_pos, score, shared, gate_logit, out) -> None:
-    _cuda_contig(y, pair_pos, score, shared, gate_logit, out)
+    """``gate_logit``: [T] or a [T, 1] column slice of a wider float32 matrix."""
+    _cuda_contig(y, pair_pos, score, shared, out)
     T, K = score.shape
+    gate_ld = 1 if gate_logit is None else (gate_logit.stride(0) if gate_logit.dim() >= 1 else 1)
     H = out.shape[1]
     for t in (y, score, shared, gate_logit, out):
         _need(t is None or t.dtype == torch.float32, "moe_combine: float32 tensors")
-    _check(lib().nv_moe_combine(_p(y), _p(pair_pos), _p(score), _p(shared), _p(gate_logit), _p(out), c_int(T),
-                                c_int(K), c_int(H), _stream()), "moe_combine")
+    _check(lib().nv_moe_combine(_p(y), _p(pair_pos), _p(score), _p(shared), _p(gate_logit), c_longlong(gate_ld),
+                                _p(out), c_int(T), c_int(K), c_int(H), _stream()), "moe_combine")
 
 
 def silu_mul(gu, out) -> None:

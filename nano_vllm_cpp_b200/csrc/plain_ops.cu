@@ -57,51 +57,64 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(float* __restrict__ x,
 // NeoX pairing (d, d + R/2) over the first R = rotary_dim elements of each head:
 //   ang = float(pos) * inv_freq[d];  o[d] = x[d] cos - x[d+R/2] sin;  o[d+R/2] = x[d+R/2] cos + x[d] sin
 // (src/hip_ops.hip:431-450).  q is rotated in place; k is rotated and written to its page; v is
-// copied to its page (src/hip_ops.hip:452-466).  One block per (row, head of q|k|v).
+// copied to its page (src/hip_ops.hip:452-466).  One block per row and group of four heads: the angles are taken once per block.
 // Cache layout: [page][kv head][slot in page][D].
-__global__ void rope_store_kernel(void* __restrict__ qkv, int dt, const int* __restrict__ positions,
+constexpr int ROPE_HEADS_PER_BLOCK = 4;
+__global__ void __launch_bounds__(128) rope_store_kernel(void* __restrict__ qkv, int dt, const int* __restrict__ positions,
                                   const float* __restrict__ inv_freq, int rotary_dim,
                                   void* __restrict__ kc, void* __restrict__ vc, int cache_dt,
                                   const int* __restrict__ block_table, int max_blocks,
                                   const int* __restrict__ row_entry, int Hq, int Hkv, int D, int page,
                                   int write_kv, int* __restrict__ err) {
-  const int t = blockIdx.x, h = blockIdx.y;
+  __shared__ float cs[128], sn[128];        // cos and sin of this row's angles, once for the block's heads
+  const int t = blockIdx.x;
+  const int h_begin = blockIdx.y * ROPE_HEADS_PER_BLOCK;                 // heads in the order q.., k.., v..
+  const int h_end = min(Hq + 2 * Hkv, h_begin + ROPE_HEADS_PER_BLOCK);
+  if (!write_kv && h_begin >= Hq) return;
   const int width = (Hq + 2 * Hkv) * D;
-  const size_t base = (size_t)t * width + (size_t)h * D;
   const int pos = positions[t];
-  size_t cbase = 0;
-  const bool is_q = h < Hq, is_k = !is_q && h < Hq + Hkv;
-  if (!is_q) {
-    if (!write_kv) return;
-    int blk = block_table[(size_t)row_entry[t] * max_blocks + pos / page];
-    if (blk < 0) {
-      if (threadIdx.x == 0) atomicExch(err, 1 + t);
-      return;
-    }
-    int kvh = is_k ? h - Hq : h - Hq - Hkv;
-    cbase = (((size_t)blk * Hkv + kvh) * page + pos % page) * D;
-  }
-  if (is_q || is_k) {
-    const int half = rotary_dim / 2;
-    // a thread owns whole pairs, so rotating q in place needs no barrier
+  const int half = rotary_dim / 2;
+  if (h_begin < Hq + Hkv)
     for (int f = threadIdx.x; f < half; f += blockDim.x) {
       float ang = (float)pos * inv_freq[f];
-      float c = cosf(ang), s = sinf(ang);
-      float x1 = ld_dt(qkv, dt, base + f), x2 = ld_dt(qkv, dt, base + f + half);
-      float o1 = x1 * c - x2 * s, o2 = x2 * c + x1 * s;
-      if (is_q) {
-        st_dt(qkv, dt, base + f, o1);
-        st_dt(qkv, dt, base + f + half, o2);
-      } else {
-        st_dt(kc, cache_dt, cbase + f, o1);
-        st_dt(kc, cache_dt, cbase + f + half, o2);
-      }
+      cs[f] = cosf(ang);
+      sn[f] = sinf(ang);
     }
-    if (is_k)
-      for (int d = rotary_dim + threadIdx.x; d < D; d += blockDim.x)
-        st_dt(kc, cache_dt, cbase + d, ld_dt(qkv, dt, base + d));
-  } else {
-    for (int d = threadIdx.x; d < D; d += blockDim.x) st_dt(vc, cache_dt, cbase + d, ld_dt(qkv, dt, base + d));
+  int blk = 0;
+  if (h_end > Hq && write_kv) {
+    blk = block_table[(size_t)row_entry[t] * max_blocks + pos / page];
+    if (blk < 0) {
+      if (threadIdx.x == 0) atomicExch(err, 1 + t);
+      write_kv = 0;
+    }
+  }
+  __syncthreads();
+  const size_t row = (size_t)t * width;
+  for (int h = h_begin; h < h_end; ++h) {
+    const size_t base = row + (size_t)h * D;
+    if (h < Hq + Hkv) {
+      const bool is_q = h < Hq;
+      if (!is_q && !write_kv) continue;
+      const size_t cbase = is_q ? 0 : (((size_t)blk * Hkv + (h - Hq)) * page + pos % page) * D;
+      // a thread owns whole pairs (f, f + half), so rotating q in place needs no barrier
+      for (int f = threadIdx.x; f < half; f += blockDim.x) {
+        const float x1 = ld_dt(qkv, dt, base + f), x2 = ld_dt(qkv, dt, base + f + half);
+        const float o1 = x1 * cs[f] - x2 * sn[f], o2 = x2 * cs[f] + x1 * sn[f];
+        if (is_q) {
+          st_dt(qkv, dt, base + f, o1);
+          st_dt(qkv, dt, base + f + half, o2);
+        } else {
+          st_dt(kc, cache_dt, cbase + f, o1);
+          st_dt(kc, cache_dt, cbase + f + half, o2);
+        }
+      }
+      if (!is_q)
+        for (int d = rotary_dim + threadIdx.x; d < D; d += blockDim.x)
+          st_dt(kc, cache_dt, cbase + d, ld_dt(qkv, dt, base + d));
+    } else if (write_kv) {
+      const size_t cbase = (((size_t)blk * Hkv + (h - Hq - Hkv)) * page + pos % page) * D;
+      for (int d = threadIdx.x; d < D; d += blockDim.x) st_dt(vc, cache_dt, cbase + d, ld_dt(qkv, dt, base + d));
+    }
   }
 }
 
@@ -180,14 +193,14 @@ __global__ void __launch_bounds__(ATT_THREADS) paged_attention_plain_kernel(
 // One warp per row: p = softmax(logits) over all E in double, then K rounds of "largest
 // remaining, lowest index on a tie", optional renormalisation of the K weights in double
 // (src/hip_ops.hip:813-841).
-__global__ void router_topk_kernel(const float* __restrict__ logits, int T, int E, int K, int renorm,
+__global__ void router_topk_kernel(const float* __restrict__ logits, long long ld, int T, int E, int K, int renorm,
                                    int* __restrict__ idx, float* __restrict__ score) {
   extern __shared__ double sm[];
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const int t = blockIdx.x * (blockDim.x / 32) + warp;
   if (t >= T) return;
   double* pr = sm + (size_t)warp * E;
-  const float* r = logits + (size_t)t * E;
+  const float* r = logits + (size_t)t * ld;
   float mx = -INFINITY;
   for (int e = lane; e < E; e += 32) mx = fmaxf(mx, r[e]);
   mx = warp_max(mx);
@@ -238,37 +251,47 @@ __global__ void __launch_bounds__(1024) moe_align_kernel(const int* __restrict__
                                                          int* __restrict__ tile_expert, int* __restrict__ tile_row0,
                                                          int* __restrict__ tile_rows, int* __restrict__ num_tiles,
                                                          int* __restrict__ err) {
+  extern __shared__ int al_s[];            // counts[E], cursor[E], tile_base[E]
+  int* cnt = al_s;
+  int* cur = al_s + E;
+  int* tbase = al_s + 2 * E;
   const int tid = threadIdx.x;
-  for (int e = tid; e < E; e += 1024) counts[e] = 0;
+  for (int e = tid; e < E; e += 1024) cnt[e] = 0;
   __syncthreads();
   for (int i = tid; i < TK; i += 1024) {
     int e = idx[i];
     if (e < 0 || e >= E) { atomicExch(err, 1 + i); continue; }
-    atomicAdd(&counts[e], 1);
+    atomicAdd(&cnt[e], 1);
   }
   __syncthreads();
-  if (tid == 0) {
+  if (tid == 0) {                           // E is small: a serial scan over shared memory
     int off = 0, nt = 0;
     for (int e = 0; e < E; ++e) {
-      offsets[e] = off;
-      cursor[e] = off;
-      int c = counts[e];
-      for (int r = 0; r < c; r += tile_m) {
-        tile_expert[nt] = e;
-        tile_row0[nt] = off + r;
-        tile_rows[nt] = min(tile_m, c - r);
-        ++nt;
-      }
-      off += c;
+      cur[e] = off;
+      tbase[e] = nt;
+      off += cnt[e];
+      nt += (cnt[e] + tile_m - 1) / tile_m;
     }
     offsets[E] = off;
     *num_tiles = nt;
   }
   __syncthreads();
+  for (int e = tid; e < E; e += 1024) {
+    const int c = cnt[e], off = cur[e];
+    counts[e] = c;
+    offsets[e] = off;
+    cursor[e] = off + c;
+    for (int r = 0, t = tbase[e]; r < c; r += tile_m, ++t) {
+      tile_expert[t] = e;
+      tile_row0[t] = off + r;
+      tile_rows[t] = min(tile_m, c - r);
+    }
+  }
+  __syncthreads();
   for (int i = tid; i < TK; i += 1024) {
     int e = idx[i];
     if (e < 0 || e >= E) continue;
-    int p = atomicAdd(&cursor[e], 1);
+    int p = atomicAdd(&cur[e], 1);
     sorted_token[p] = i / K;
     pair_pos[i] = p;
   }
@@ -280,10 +303,11 @@ __global__ void __launch_bounds__(1024) moe_align_kernel(const int* __restrict__
 // (src/hip_ops.hip:873-892, 926-934; src/model.cpp:803-811).
 __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ pair_pos,
                                    const float* __restrict__ score, const float* __restrict__ shared,
-                                   const float* __restrict__ gate_logit, float* __restrict__ out, int K, int H) {
+                                   const float* __restrict__ gate_logit, long long gate_ld,
+                                   float* __restrict__ out, int K, int H) {
   const int t = blockIdx.x;
   float g = 1.f;
-  if (gate_logit) g = 1.f / (1.f + expf(-gate_logit[t]));
+  if (gate_logit) g = 1.f / (1.f + expf(-gate_logit[(size_t)t * gate_ld]));
   for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < H; i += gridDim.y * blockDim.x) {
     float r = 0.f;
     for (int k = 0; k < K; ++k) {
@@ -411,10 +435,9 @@ NV_API int nv_rope_store(void* qkv, int dt, const int* positions, const float* i
   if (!dt_ok(dt) || !dt_ok(cache_dt)) return NV_ERR_BAD_DTYPE;
   if (rotary_dim < 0 || rotary_dim > D || rotary_dim % 2) return NV_ERR_BAD_SIZE;
   if (T == 0) return NV_OK;
-  dim3 grid(T, Hq + 2 * Hkv);
-  int threads = D <= 32 ? 32 : (D <= 64 ? 64 : (D <= 128 ? 128 : 256));
   if (D > 256 || D % 2) return NV_ERR_UNSUPPORTED;
-  rope_store_kernel<<<grid, threads, 0, s>>>(qkv, dt, positions, inv_freq, rotary_dim, kc, vc, cache_dt,
+  dim3 grid(T, (Hq + 2 * Hkv + ROPE_HEADS_PER_BLOCK - 1) / ROPE_HEADS_PER_BLOCK);
+  rope_store_kernel<<<grid, 128, 0, s>>>(qkv, dt, positions, inv_freq, rotary_dim, kc, vc, cache_dt,
                                              block_table, max_blocks, row_entry, Hq, Hkv, D, page, write_kv, err);
   NV_RETURN_LAST();
 }
@@ -433,14 +456,14 @@ NV_API int nv_paged_attention_plain(const void* qkv, int dt, int q_stride, const
   NV_RETURN_LAST();
 }
 
-NV_API int nv_router_topk(const float* logits, int T, int E, int K, int renorm, int* idx, float* score,
-                          cudaStream_t s) {
+NV_API int nv_router_topk(const float* logits, long long ld, int T, int E, int K, int renorm, int* idx,
+                          float* score, cudaStream_t s) {
   if (K < 1 || K > E || K > 32) return NV_ERR_UNSUPPORTED;
   if (T == 0) return NV_OK;
   const int warps = 4;
   size_t smem = (size_t)warps * E * sizeof(double);
   if (smem > 48 * 1024) return NV_ERR_UNSUPPORTED;  // E <= 1536
-  router_topk_kernel<<<(T + warps - 1) / warps, warps * 32, smem, s>>>(logits, T, E, K, renorm, idx, score);
+  router_topk_kernel<<<(T + warps - 1) / warps, warps * 32, smem, s>>>(logits, ld, T, E, K, renorm, idx, score);
   NV_RETURN_LAST();
 }
 
@@ -448,16 +471,18 @@ NV_API int nv_moe_align(const int* idx, int T, int K, int E, int tile_m, int* co
                         int* sorted_token, int* pair_pos, int* tile_expert, int* tile_row0, int* tile_rows,
                         int* num_tiles, int* err, cudaStream_t s) {
   if (tile_m <= 0 || K <= 0 || E <= 0) return NV_ERR_BAD_SIZE;
-  moe_align_kernel<<<1, 1024, 0, s>>>(idx, T * K, K, E, tile_m, counts, offsets, cursor, sorted_token, pair_pos,
+  if (E > 4000) return NV_ERR_UNSUPPORTED;   // three int arrays of E in shared memory
+  moe_align_kernel<<<1, 1024, 3 * E * sizeof(int), s>>>(idx, T * K, K, E, tile_m, counts, offsets, cursor, sorted_token, pair_pos,
                                       tile_expert, tile_row0, tile_rows, num_tiles, err);
   NV_RETURN_LAST();
 }
 
 NV_API int nv_moe_combine(const float* y, const int* pair_pos, const float* score, const float* shared,
-                          const float* gate_logit, float* out, int T, int K, int H, cudaStream_t s) {
+                          const float* gate_logit, long long gate_ld, float* out, int T, int K, int H,
+                          cudaStream_t s) {
   if (T == 0) return NV_OK;
   dim3 grid(T, (H + 1023) / 1024);
-  moe_combine_kernel<<<grid, 256, 0, s>>>(y, pair_pos, score, shared, gate_logit, out, K, H);
+  moe_combine_kernel<<<grid, 256, 0, s>>>(y, pair_pos, score, shared, gate_logit, gate_ld, out, K, H);
   NV_RETURN_LAST();
 }
 

@@ -4,24 +4,25 @@
 namespace {
 
 // out[t, n] = sum_k a[t, k] * w[n, k] for float32 rows a and a short, wide matrix w (router logits,
-// the shared expert's gate): one warp per (row, four outputs).  A lane sums its strided elements in
-// ascending order, then the lanes are added by a fixed xor tree, so a row's result does not
-// depend on the batch.  Float32 throughout (src/model.cpp:797 computes the router logits in float32 too).
+// the shared expert's gate): one block per (row, four outputs); its 8 warps take the 128-element
+// chunks of k in turn (warp w: chunks w, w + 8, ...), a lane sums its 4 elements of each chunk in
+// ascending order, lanes are added by a fixed xor tree and the 8 warp sums in warp order.  The order
+// is the same whatever the batch is, so a row's result does not depend on it.  Float32 throughout
+// (src/model.cpp:797 computes the router logits in float32 too).
 template <typename TW>
 __global__ void __launch_bounds__(256) rowdot_kernel(const float* __restrict__ a, long long lda,
-                                                     const TW* __restrict__ w, float* __restrict__ out, int T,
-                                                     int N, int K) {
-  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) / 32, lane = threadIdx.x % 32;
-  const int nq = (N + 3) / 4;
-  if (warp >= T * nq) return;
-  const int t = warp / nq, n0 = (warp % nq) * 4;
+                                                     const TW* __restrict__ w, float* __restrict__ out,
+                                                     long long ldo, int N, int K) {
+  __shared__ float part[8][4];
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int t = blockIdx.x, n0 = blockIdx.y * 4;
   const float* ar = a + (size_t)t * lda;
   float s[4] = {0.f, 0.f, 0.f, 0.f};
   const TW* wr[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) wr[i] = w + (size_t)min(n0 + i, N - 1) * K;
   if (K % 4 == 0 && ((uintptr_t)ar & 15) == 0 && ((uintptr_t)w & 15) == 0) {
-    for (int k = lane * 4; k < K; k += 128) {
+    for (int k = warp * 128 + lane * 4; k < K; k += 1024) {
       const float4 av = *(const float4*)(ar + k);
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -40,28 +41,36 @@ __global__ void __launch_bounds__(256) rowdot_kernel(const float* __restrict__ a
       }
     }
   } else {
-    for (int k = lane; k < K; k += 32) {
-      const float av = ar[k];
+    for (int k0 = warp * 128; k0 < K; k0 += 1024)
+      for (int k = k0 + lane; k < min(K, k0 + 128); k += 32) {
+        const float av = ar[k];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) s[i] = fmaf(av, to_f32(wr[i][k]), s[i]);
-    }
+        for (int i = 0; i < 4; ++i) s[i] = fmaf(av, to_f32(wr[i][k]), s[i]);
+      }
   }
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     s[i] = warp_sum(s[i]);
-    if (lane == 0 && n0 + i < N) out[(size_t)t * N + n0 + i] = s[i];
+    if (lane == 0) part[warp][i] = s[i];
+  }
+  __syncthreads();
+  if (threadIdx.x < 4 && n0 + threadIdx.x < N) {
+    float v = 0.f;
+#pragma unroll
+    for (int wi = 0; wi < 8; ++wi) v += part[wi][threadIdx.x];
+    out[(size_t)t * ldo + n0 + threadIdx.x] = v;
   }
 }
 
 }  // namespace
 
-NV_API int nv_rowdot(const float* a, long long lda, const void* w, int w_dt, float* out, int T, int N, int K,
-                     cudaStream_t s) {
+NV_API int nv_rowdot(const float* a, long long lda, const void* w, int w_dt, float* out, long long ldo, int T,
+                     int N, int K, cudaStream_t s) {
   if (!dt_ok(w_dt)) return NV_ERR_BAD_DTYPE;
   if (T == 0 || N == 0) return NV_OK;
-  const long long warps = (long long)T * ((N + 3) / 4);
-  const unsigned blocks = (unsigned)((warps + 7) / 8);
-  if (w_dt == NV_DT_F32) rowdot_kernel<float><<<blocks, 256, 0, s>>>(a, lda, (const float*)w, out, T, N, K);
-  else rowdot_kernel<bf16><<<blocks, 256, 0, s>>>(a, lda, (const bf16*)w, out, T, N, K);
+  if ((N + 3) / 4 > 65535) return NV_ERR_BAD_SIZE;
+  dim3 grid(T, (N + 3) / 4);
+  if (w_dt == NV_DT_F32) rowdot_kernel<float><<<grid, 256, 0, s>>>(a, lda, (const float*)w, out, ldo, N, K);
+  else rowdot_kernel<bf16><<<grid, 256, 0, s>>>(a, lda, (const bf16*)w, out, ldo, N, K);
   NV_RETURN_LAST();
 }

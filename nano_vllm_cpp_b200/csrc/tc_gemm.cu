@@ -18,7 +18,7 @@
 // read the accumulator back (tcgen05.ld) and store.  Every wait on an mbarrier is bounded: after
 // about two seconds a waiter records the fact in the error flag and goes on, so the kernel always
 // ends and frees its TMEM; its output is then garbage and the host raises.
-#include "common.cuh"
+#include "pipeline.cuh"
 
 #include <cuda.h>
 #include <mutex>
@@ -31,7 +31,6 @@ constexpr int BLOCK_K = 64;     // elements of K per stage: 128 bytes = one swiz
 constexpr int UMMA_K = 16;
 constexpr int MAX_STAGES = 8;
 constexpr int NUM_THREADS = 192;
-constexpr long long WAIT_CYCLES = 4000000000LL;   // ~2 s at 2 GHz
 
 struct TcArgs {
   void* out;
@@ -52,39 +51,7 @@ struct TcArgs {
   int tmem_cols;
 };
 
-// ------------------------------------------------------------------ PTX wrappers
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.b32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait.  Returns false after the limit; the caller records it and carries on.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err, int code) {
-  if (mbar_try(bar, parity)) return true;
-  const long long t0 = clock64();
-  while (!mbar_try(bar, parity)) {
-    if (clock64() - t0 > WAIT_CYCLES) {
-      atomicExch(err, code);
-      return false;
-    }
-  }
-  return true;
-}
-
+// ------------------------------------------------------------------ PTX wrappers (mbarriers: pipeline.cuh)
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* tm, uint64_t* bar, int c0, int c1) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
@@ -150,7 +117,7 @@ __device__ __forceinline__ uint32_t instr_desc(int n) {
 }
 
 // ------------------------------------------------------------------ the kernel
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(NUM_THREADS, 2)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, TcArgs a) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   __shared__ uint64_t full_bar[MAX_STAGES], empty_bar[MAX_STAGES], acc_bar;
@@ -179,12 +146,14 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   const uint32_t stage_bytes = a_bytes * (a.swiglu ? 2 : 1) + x_bytes;
 
   if (threadIdx.x == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&tm_w) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&tm_x) : "memory");
     for (int s = 0; s < a.stages; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
     mbar_init(&acc_bar, 1);
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    mbar_fence_init();
   }
   if (warp == 1) tmem_alloc(&tmem_base_s, a.tmem_cols);
   tc_fence_before();
@@ -429,7 +398,10 @@ NV_API int nv_tc_gemm(const void* X, long long ldx, int M_tok, const void* W, in
   a.k_steps_per_split = (a.k_steps_total + a.splits - 1) / a.splits;
   a.n_tile = n_tile; a.swiglu = swiglu ? 1 : 0;
   const int stage_bytes = TILE_W * 128 * (swiglu ? 2 : 1) + n_tile * 128;
-  int stages = (200 * 1024) / stage_bytes;
+  // Small stages (few tokens): keep a CTA under half of the shared memory so that two CTAs share an SM and
+  // one's start-up and epilogue overlap the other's streaming.  Large stages: one CTA per SM, deep ring.
+  const int budget = stage_bytes * 4 <= 104 * 1024 ? 104 * 1024 : 200 * 1024;
+  int stages = budget / stage_bytes;
   if (stages > MAX_STAGES) stages = MAX_STAGES;
   if (stages > a.k_steps_per_split) stages = a.k_steps_per_split < 2 ? 2 : a.k_steps_per_split;
   a.stages = stages;

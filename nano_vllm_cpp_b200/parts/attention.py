@@ -73,9 +73,9 @@ class PagedAttention(Mixer):
         # bfloat16 runs take the split-key kernel for batches of single rows; float32 runs keep the
         # plain kernel everywhere, so that their sums have one order however the work is cut
         if self.ctx.fast_kernels and self.ctx.act_dtype == torch.bfloat16 and cache.k.dtype == torch.bfloat16:
-            if batch.decode_only:
+            if batch.decode_only and ops.attention_decode_usable(cache.k, self.D):
                 ops.attention_decode(qkv, cache.k, cache.v, bt, batch.row_entry, batch.positions, self.scale,
-                                     self.window, att, self.Hq, self.Hkv, self.D, batch.max_context)
+                                     self.window, att, self.Hq, self.Hkv, self.D, batch.max_context, err=self.ctx.err)
             else:
                 tiles = sum((e.length + 63) // 64 for e in batch.entries)
                 ops.attention_prefill(qkv, cache.k, cache.v, bt, batch.cu_rows, batch.entry_pos0, tiles, self.scale,

@@ -52,6 +52,7 @@ class SparseMoeSwiGLU(FeedForward):
         self.hidden, self.E, self.K = hidden_size, num_experts, top_k
         self.inter, self.shared_inter, self.renorm = intermediate_size, shared_intermediate_size, renormalize
         self._align = {}
+        self.router_and_gate = None
         self.last_alignment = None      # the permutation buffers of the latest forward (for statistics)
 
     def tensor_specs(self, available=None):
@@ -93,6 +94,9 @@ class SparseMoeSwiGLU(FeedForward):
             self.sh_gate_up = _cat([fetch("shared_expert.gate_proj.weight"), fetch("shared_expert.up_proj.weight")])
             self.sh_down = fetch("shared_expert.down_proj.weight")
             self.sh_gate = fetch("shared_expert_gate.weight")
+            # the gate's single row rides along with the router's rows: one product gives both logits
+            if self.sh_gate.dtype == self.router.dtype:
+                self.router_and_gate = torch.cat([self.router, self.sh_gate.reshape(1, -1)], dim=0).contiguous()
 
     def _alignment(self, TK, device, fast):
         tile_m = ops.grouped_token_tile(TK, self.E) if fast else ops.gemm_plain_tile_m()
@@ -105,7 +109,12 @@ class SparseMoeSwiGLU(FeedForward):
         ctx = self.ctx
         T = h.shape[0]
         dev = h.device
-        logits = small_linear(ctx, h32, self.router)
+        gate_logit = None
+        if self.router_and_gate is not None:
+            both = small_linear(ctx, h32, self.router_and_gate)
+            logits, gate_logit = both[:, :self.E], both[:, self.E:]
+        else:
+            logits = small_linear(ctx, h32, self.router)
         idx = torch.empty((T, self.K), dtype=torch.int32, device=dev)
         score = torch.empty((T, self.K), dtype=torch.float32, device=dev)
         ops.router_topk(logits, self.K, self.renorm, idx, score)
@@ -116,11 +125,12 @@ class SparseMoeSwiGLU(FeedForward):
         self.last_alignment = al
         act = grouped_linear(ctx, h, self.w_gate_up, ctx.act_dtype, al, a_rows=al.sorted_token, swiglu=True)
         y = grouped_linear(ctx, act, self.w_down, torch.float32, al)
-        shared = gate_logit = None
+        shared = None
         if self.shared_inter > 0:
             sact = linear(ctx, h, self.sh_gate_up, ctx.act_dtype, swiglu=True)
             shared = linear(ctx, sact, self.sh_down, torch.float32)
-            gate_logit = small_linear(ctx, h32, self.sh_gate)
+            if gate_logit is None:
+                gate_logit = small_linear(ctx, h32, self.sh_gate)
         out = torch.empty((T, self.hidden), dtype=torch.float32, device=dev)
         ops.moe_combine(y, al.pair_pos, score, shared, gate_logit, out)
         return out

@@ -45,6 +45,7 @@ def _call(lib, name, qkv, kc, vc, bt, ent, pos, out, Hq, Hkv, D, page, splits, s
             c_int(Hq), c_int(Hkv), c_int(D), c_int(page), c_int(splits)]
     if scratch is not None:
         args.append(c_void_p(scratch.data_ptr()))
+        args.append(c_void_p(0))            # the ordinary entry point also takes an error flag; none here
     args.append(stream)
     return fn(*args)
 
@@ -79,3 +80,5 @@ def test_no_alloc_decode_attention_matches_the_ordinary_entry_point():
     assert _call(lib, "nv_attention_decode_noalloc", qkv[:most], kc, vc, bt, ent, pos, out[:most], Hq, Hkv, D, page,
                  splits) == 0
     torch.cuda.synchronize()
+    lib.nv_attention_decode_noalloc_status.restype = c_int
+    assert lib.nv_attention_decode_noalloc_status() == 0
