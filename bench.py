@@ -216,7 +216,8 @@ def main() -> int:
         launches = ops.launch_count() - launches0
         runner.ctx.err.check("decode")
         ms = a.elapsed_time(b) / steps
-        distinct = [int((p.last_alignment.counts > 0).sum()) for p in moe_parts() if p.last_alignment is not None]
+        distinct = [int((p.last_alignment.counts[:cfg["num_experts"]] > 0).sum()) for p in moe_parts()
+                    if p.last_alignment is not None]
         ctxs = [runner.num_cached(r) for r in rids]
         for r in rids:
             runner.close(r)

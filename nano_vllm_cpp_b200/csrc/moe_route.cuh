@@ -1,0 +1,112 @@
+// Routing of a mixture of experts: per-row top-k of the router's softmax, and the permutation of
+// (row, expert) pairs into expert order that the grouped products work on.  Device functions shared
+// by the stand-alone kernels (plain_ops.cu) and the fused small-batch kernel (small_ops.cu).
+#pragma once
+
+#include "common.cuh"
+
+// One warp routes one row: p = softmax(logits) over all E in double, then K rounds of "largest
+// remaining, lowest index on a tie", optional renormalisation of the K weights in double
+// (src/hip_ops.hip:813-841).  `pr` is E doubles of scratch for this warp.  With C > 0 the row also
+// gets C "always on" experts E .. E+C-1 with weight sigmoid(gate_logit): the chunks of a shared
+// expert that is computed as C more experts (src/model.cpp:803-811 computes it separately).
+// idx and score rows are K + C wide.
+__device__ __forceinline__ void route_row(const float* __restrict__ r, int E, int K, int renorm, double* pr,
+                                          int lane, int* __restrict__ idx_row, float* __restrict__ score_row,
+                                          int C, const float* gate_logit) {
+  float mx = -INFINITY;
+  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, r[e]);
+  mx = warp_max(mx);
+  double s = 0.0;
+  for (int e = lane; e < E; e += 32) {
+    double v = exp((double)r[e] - (double)mx);
+    pr[e] = v;
+    s += v;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  __syncwarp();
+  for (int e = lane; e < E; e += 32) pr[e] /= s;
+  __syncwarp();
+  double wsum = 0.0;
+  double mine = 0.0;  // lane k keeps the k-th weight (K <= 32)
+  for (int k = 0; k < K; ++k) {
+    double best = -1.0;
+    int bi = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      double v = pr[e];
+      if (v > best) { best = v; bi = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      double ob = __shfl_xor_sync(0xffffffffu, best, o);
+      int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+    }
+    if (lane == k) { mine = best; idx_row[k] = bi; }
+    wsum += best;
+    if (lane == 0) pr[bi] = -2.0;
+    __syncwarp();
+  }
+  if (lane < K) score_row[lane] = (float)(renorm ? mine / wsum : mine);
+  if (lane < C) {
+    idx_row[K + lane] = E + lane;
+    score_row[K + lane] = 1.f / (1.f + expf(-gate_logit[0]));
+  }
+}
+
+// From idx[TK] (expert of every (row, k) pair; K pairs per row) build, for the grouped products:
+// counts and offsets per expert, the pairs sorted by expert (sorted_token = source row of each sorted
+// position, pair_pos = sorted position of each pair) and the list of tiles (expert, first row, rows)
+// of at most tile_m rows.  One block of 1024 threads; `al_s` is 3 * E ints of shared memory.  The
+// order of pairs inside an expert's segment comes from atomics and may differ from run to run; it
+// decides only where a pair's row sits, never a sum's order.
+__device__ __forceinline__ void align_block(const int* __restrict__ idx, int TK, int K, int E, int tile_m,
+                                            int* __restrict__ counts, int* __restrict__ offsets,
+                                            int* __restrict__ sorted_token, int* __restrict__ pair_pos,
+                                            int* __restrict__ tile_expert, int* __restrict__ tile_row0,
+                                            int* __restrict__ tile_rows, int* __restrict__ num_tiles,
+                                            int* __restrict__ err, int* al_s) {
+  int* cnt = al_s;
+  int* cur = al_s + E;
+  int* tbase = al_s + 2 * E;
+  const int tid = threadIdx.x, nthr = blockDim.x;
+  for (int e = tid; e < E; e += nthr) cnt[e] = 0;
+  __syncthreads();
+  for (int i = tid; i < TK; i += nthr) {
+    int e = idx[i];
+    if (e < 0 || e >= E) { atomicExch(err, 1 + i); continue; }
+    atomicAdd(&cnt[e], 1);
+  }
+  __syncthreads();
+  if (tid == 0) {                           // E is small: a serial scan over shared memory
+    int off = 0, nt = 0;
+    for (int e = 0; e < E; ++e) {
+      cur[e] = off;
+      tbase[e] = nt;
+      off += cnt[e];
+      nt += (cnt[e] + tile_m - 1) / tile_m;
+    }
+    offsets[E] = off;
+    *num_tiles = nt;
+  }
+  __syncthreads();
+  for (int e = tid; e < E; e += nthr) {
+    const int c = cnt[e], off = cur[e];
+    counts[e] = c;
+    offsets[e] = off;
+    for (int r = 0, t = tbase[e]; r < c; r += tile_m, ++t) {
+      tile_expert[t] = e;
+      tile_row0[t] = off + r;
+      tile_rows[t] = min(tile_m, c - r);
+    }
+  }
+  __syncthreads();
+  for (int i = tid; i < TK; i += nthr) {
+    int e = idx[i];
+    if (e < 0 || e >= E) continue;
+    int p = atomicAdd(&cur[e], 1);
+    sorted_token[p] = i / K;
+    pair_pos[i] = p;
+  }
+}

@@ -267,16 +267,20 @@ def paged_attention_plain(qkv, k_cache, v_cache, block_table, row_entry, positio
                                           _stream()), "paged_attention_plain")
 
 
-def router_topk(logits, K: int, renorm: bool, idx, score) -> None:
-    """``logits`` may be a column slice of a wider float32 matrix (rows ``stride(0)`` apart)."""
+def router_topk(logits, K: int, renorm: bool, idx, score, C: int = 0, gate_logit=None) -> None:
+    """``logits`` may be a column slice of a wider float32 matrix (rows ``stride(0)`` apart).  With ``C`` the
+    rows of ``idx``/``score`` are K + C wide: C always-on experts E..E+C-1 weighted sigmoid(gate_logit)."""
     _cuda_contig(idx, score)
     _need(logits.is_cuda and logits.stride(1) == 1, "router: logits rows must be dense")
     T, E = logits.shape
     _need(logits.dtype == torch.float32 and score.dtype == torch.float32, "router: float32 logits and scores")
     _i32(idx)
-    _need(idx.shape == (T, K) and score.shape == (T, K), "router: output shapes")
+    _need(idx.shape == (T, K + C) and score.shape == (T, K + C), "router: output shapes")
+    _need(C == 0 or (gate_logit is not None and gate_logit.dtype == torch.float32), "router: gate logits")
     _check(lib().nv_router_topk(_p(logits), c_longlong(logits.stride(0)), c_int(T), c_int(E), c_int(K),
-                                c_int(1 if renorm else 0), _p(idx), _p(score), _stream()), "router_topk")
+                                c_int(1 if renorm else 0), _p(idx), _p(score), c_int(C), _p(gate_logit),
+                                c_longlong(gate_logit.stride(0) if gate_logit is not None else 0), _stream()),
+           "router_topk")
 
 
 class MoeAlignment:
@@ -288,7 +292,6 @@ class MoeAlignment:
         self.max_tiles = max(1, min(TK, (TK + tile_m - 1) // tile_m + E))
         self.counts = torch.empty(E, **i32)
         self.offsets = torch.empty(E + 1, **i32)
-        self.cursor = torch.empty(E, **i32)
         self.sorted_token = torch.empty(max(TK, 1), **i32)
         self.pair_pos = torch.empty(max(TK, 1), **i32)
         self.tile_expert = torch.empty(self.max_tiles, **i32)
@@ -307,9 +310,34 @@ def moe_align(idx, K: int, al: MoeAlignment, err: ErrorFlag) -> None:
     T = idx.numel() // K
     _need(T * K == al.TK, "moe_align: buffers were sized for another batch")
     _check(lib().nv_moe_align(_p(idx), c_int(T), c_int(K), c_int(al.E), c_int(al.tile_m), _p(al.counts),
-                              _p(al.offsets), _p(al.cursor), _p(al.sorted_token), _p(al.pair_pos),
+                              _p(al.offsets), _p(al.sorted_token), _p(al.pair_pos),
                               _p(al.tile_expert), _p(al.tile_row0), _p(al.tile_rows), _p(al.num_tiles), _p(err.t),
                               _stream()), "moe_align")
+
+
+def moe_route_small_usable(T: int, E: int, K: int, C: int, H: int) -> bool:
+    return bool(lib().nv_moe_route_small_usable(c_int(T), c_int(E), c_int(K), c_int(C), c_int(H)))
+
+
+def moe_route_small(logits, K: int, renorm: bool, C: int, gate_logit, idx, score, al: "MoeAlignment", err, x=None):
+    """Top-k, expert permutation and (with ``x``, bfloat16 rows) the expert-sorted copy of x, in one launch.
+    Returns the sorted copy or None."""
+    T, E = logits.shape
+    KT = K + C
+    _need(idx.shape == (T, KT) and score.shape == (T, KT) and al.TK == T * KT and al.E == E + C, "route: sizes")
+    xs = None
+    H = 8
+    if x is not None:
+        _need(x.dtype == torch.bfloat16 and x.is_contiguous(), "route: bfloat16 rows")
+        H = x.shape[1]
+        xs = torch.empty((T * KT, H), dtype=x.dtype, device=x.device)
+    _check(lib().nv_moe_route_small(_p(logits), c_longlong(logits.stride(0)), c_int(T), c_int(E), c_int(K),
+                                    c_int(1 if renorm else 0), c_int(C), _p(gate_logit),
+                                    c_longlong(gate_logit.stride(0) if gate_logit is not None else 0), _p(idx),
+                                    _p(score), c_int(al.tile_m), _p(al.counts), _p(al.offsets), _p(al.sorted_token),
+                                    _p(al.pair_pos), _p(al.tile_expert), _p(al.tile_row0), _p(al.tile_rows),
+                                    _p(al.num_tiles), _p(err.t), _p(x), _p(xs), c_int(H), _stream()), "moe_route_small")
+    return xs
 
 
 def moe_combine(y, pair_pos, score, shared, gate_logit, out) -> None:

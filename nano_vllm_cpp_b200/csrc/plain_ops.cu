@@ -4,6 +4,7 @@
 // Softmax, norms, router probabilities, rotation angles and the residual sum are 32-bit (the
 // router's softmax is 64-bit, as in the reference) whatever the storage type is.
 #include "common.cuh"
+#include "moe_route.cuh"
 
 namespace {
 
@@ -189,112 +190,29 @@ __global__ void __launch_bounds__(ATT_THREADS) paged_attention_plain_kernel(
   if (tid + ATT_THREADS < D) st_dt(out, out_dt, ob + tid + ATT_THREADS, o1 * inv);
 }
 
-// ----------------------------------------------------------------------- router
-// One warp per row: p = softmax(logits) over all E in double, then K rounds of "largest
-// remaining, lowest index on a tie", optional renormalisation of the K weights in double
-// (src/hip_ops.hip:813-841).
+// ----------------------------------------------------------------------- router, expert permutation
+// (the work is in moe_route.cuh)
 __global__ void router_topk_kernel(const float* __restrict__ logits, long long ld, int T, int E, int K, int renorm,
-                                   int* __restrict__ idx, float* __restrict__ score) {
+                                   int* __restrict__ idx, float* __restrict__ score, int C,
+                                   const float* __restrict__ gate_logit, long long gate_ld) {
   extern __shared__ double sm[];
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const int t = blockIdx.x * (blockDim.x / 32) + warp;
   if (t >= T) return;
-  double* pr = sm + (size_t)warp * E;
-  const float* r = logits + (size_t)t * ld;
-  float mx = -INFINITY;
-  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, r[e]);
-  mx = warp_max(mx);
-  double s = 0.0;
-  for (int e = lane; e < E; e += 32) {
-    double v = exp((double)r[e] - (double)mx);
-    pr[e] = v;
-    s += v;
-  }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-  __syncwarp();
-  for (int e = lane; e < E; e += 32) pr[e] /= s;
-  __syncwarp();
-  double wsum = 0.0;
-  double mine = 0.0;  // lane k keeps the k-th weight (K <= 32 is checked by the launcher)
-  for (int k = 0; k < K; ++k) {
-    double best = -1.0;
-    int bi = 0x7fffffff;
-    for (int e = lane; e < E; e += 32) {
-      double v = pr[e];
-      if (v > best) { best = v; bi = e; }
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      double ob = __shfl_xor_sync(0xffffffffu, best, o);
-      int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
-    }
-    if (lane == k) { mine = best; idx[(size_t)t * K + k] = bi; }
-    wsum += best;
-    if (lane == 0) pr[bi] = -2.0;
-    __syncwarp();
-  }
-  if (lane < K) score[(size_t)t * K + lane] = (float)(renorm ? mine / wsum : mine);
+  route_row(logits + (size_t)t * ld, E, K, renorm, sm + (size_t)warp * E, lane, idx + (size_t)t * (K + C),
+            score + (size_t)t * (K + C), C, C ? gate_logit + (size_t)t * gate_ld : nullptr);
 }
 
-// ------------------------------------------------------------- expert permutation
-// From idx[T*K] build, for the grouped products: counts and offsets per expert, the list of
-// (row, k) pairs sorted by expert (sorted_token = source row of x for each sorted position,
-// pair_pos = sorted position of each pair) and the list of M-tiles (expert, first row, rows).
-// One block.  The order of pairs inside an expert's segment comes from atomics and may differ
-// from run to run; it decides only where a pair's row sits, never a sum's order.
 __global__ void __launch_bounds__(1024) moe_align_kernel(const int* __restrict__ idx, int TK, int K, int E,
                                                          int tile_m, int* __restrict__ counts,
-                                                         int* __restrict__ offsets, int* __restrict__ cursor,
+                                                         int* __restrict__ offsets,
                                                          int* __restrict__ sorted_token, int* __restrict__ pair_pos,
                                                          int* __restrict__ tile_expert, int* __restrict__ tile_row0,
                                                          int* __restrict__ tile_rows, int* __restrict__ num_tiles,
                                                          int* __restrict__ err) {
-  extern __shared__ int al_s[];            // counts[E], cursor[E], tile_base[E]
-  int* cnt = al_s;
-  int* cur = al_s + E;
-  int* tbase = al_s + 2 * E;
-  const int tid = threadIdx.x;
-  for (int e = tid; e < E; e += 1024) cnt[e] = 0;
-  __syncthreads();
-  for (int i = tid; i < TK; i += 1024) {
-    int e = idx[i];
-    if (e < 0 || e >= E) { atomicExch(err, 1 + i); continue; }
-    atomicAdd(&cnt[e], 1);
-  }
-  __syncthreads();
-  if (tid == 0) {                           // E is small: a serial scan over shared memory
-    int off = 0, nt = 0;
-    for (int e = 0; e < E; ++e) {
-      cur[e] = off;
-      tbase[e] = nt;
-      off += cnt[e];
-      nt += (cnt[e] + tile_m - 1) / tile_m;
-    }
-    offsets[E] = off;
-    *num_tiles = nt;
-  }
-  __syncthreads();
-  for (int e = tid; e < E; e += 1024) {
-    const int c = cnt[e], off = cur[e];
-    counts[e] = c;
-    offsets[e] = off;
-    cursor[e] = off + c;
-    for (int r = 0, t = tbase[e]; r < c; r += tile_m, ++t) {
-      tile_expert[t] = e;
-      tile_row0[t] = off + r;
-      tile_rows[t] = min(tile_m, c - r);
-    }
-  }
-  __syncthreads();
-  for (int i = tid; i < TK; i += 1024) {
-    int e = idx[i];
-    if (e < 0 || e >= E) continue;
-    int p = atomicAdd(&cur[e], 1);
-    sorted_token[p] = i / K;
-    pair_pos[i] = p;
-  }
+  extern __shared__ int al_s[];
+  align_block(idx, TK, K, E, tile_m, counts, offsets, sorted_token, pair_pos, tile_expert, tile_row0, tile_rows,
+              num_tiles, err, al_s);
 }
 
 // ------------------------------------------------------------------------ combine
@@ -457,22 +375,23 @@ NV_API int nv_paged_attention_plain(const void* qkv, int dt, int q_stride, const
 }
 
 NV_API int nv_router_topk(const float* logits, long long ld, int T, int E, int K, int renorm, int* idx,
-                          float* score, cudaStream_t s) {
-  if (K < 1 || K > E || K > 32) return NV_ERR_UNSUPPORTED;
+                          float* score, int C, const float* gate_logit, long long gate_ld, cudaStream_t s) {
+  if (K < 1 || K > E || K > 32 || C < 0 || C > 32 || (C > 0 && !gate_logit)) return NV_ERR_UNSUPPORTED;
   if (T == 0) return NV_OK;
   const int warps = 4;
   size_t smem = (size_t)warps * E * sizeof(double);
   if (smem > 48 * 1024) return NV_ERR_UNSUPPORTED;  // E <= 1536
-  router_topk_kernel<<<(T + warps - 1) / warps, warps * 32, smem, s>>>(logits, ld, T, E, K, renorm, idx, score);
+  router_topk_kernel<<<(T + warps - 1) / warps, warps * 32, smem, s>>>(logits, ld, T, E, K, renorm, idx, score, C,
+                                                                       gate_logit, gate_ld);
   NV_RETURN_LAST();
 }
 
-NV_API int nv_moe_align(const int* idx, int T, int K, int E, int tile_m, int* counts, int* offsets, int* cursor,
+NV_API int nv_moe_align(const int* idx, int T, int K, int E, int tile_m, int* counts, int* offsets,
                         int* sorted_token, int* pair_pos, int* tile_expert, int* tile_row0, int* tile_rows,
                         int* num_tiles, int* err, cudaStream_t s) {
   if (tile_m <= 0 || K <= 0 || E <= 0) return NV_ERR_BAD_SIZE;
   if (E > 4000) return NV_ERR_UNSUPPORTED;   // three int arrays of E in shared memory
-  moe_align_kernel<<<1, 1024, 3 * E * sizeof(int), s>>>(idx, T * K, K, E, tile_m, counts, offsets, cursor, sorted_token, pair_pos,
+  moe_align_kernel<<<1, 1024, 3 * E * sizeof(int), s>>>(idx, T * K, K, E, tile_m, counts, offsets, sorted_token, pair_pos,
                                       tile_expert, tile_row0, tile_rows, num_tiles, err);
   NV_RETURN_LAST();
 }

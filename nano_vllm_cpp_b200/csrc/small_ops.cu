@@ -1,5 +1,6 @@
 // Small fast kernels around the big products.
 #include "common.cuh"
+#include "moe_route.cuh"
 
 namespace {
 
@@ -62,6 +63,37 @@ __global__ void __launch_bounds__(256) rowdot_kernel(const float* __restrict__ a
   }
 }
 
+// Routing of a small batch in one launch: top-k of every row, the expert permutation, and the
+// expert-sorted copy of the (bfloat16) activations.  One block of 1024 threads; for batches whose
+// T * (K + C) pairs and rows fit one block's reach (the launcher checks).
+__global__ void __launch_bounds__(1024) moe_route_small_kernel(
+    const float* __restrict__ logits, long long ld, int T, int E, int K, int renorm, int C,
+    const float* __restrict__ gate_logit, long long gate_ld, int* __restrict__ idx, float* __restrict__ score,
+    int tile_m, int* __restrict__ counts, int* __restrict__ offsets, int* __restrict__ sorted_token,
+    int* __restrict__ pair_pos, int* __restrict__ tile_expert, int* __restrict__ tile_row0,
+    int* __restrict__ tile_rows, int* __restrict__ num_tiles, int* __restrict__ err,
+    const bf16* __restrict__ x, bf16* __restrict__ x_sorted, int H) {
+  extern __shared__ double rs_smem[];
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int KT = K + C;
+  for (int t = warp; t < T; t += 32)
+    route_row(logits + (size_t)t * ld, E, K, renorm, rs_smem + (size_t)warp * E, lane, idx + (size_t)t * KT,
+              score + (size_t)t * KT, C, C ? gate_logit + (size_t)t * gate_ld : nullptr);
+  __threadfence_block();
+  __syncthreads();
+  int* al_s = (int*)(rs_smem + (size_t)32 * E);
+  align_block(idx, T * KT, KT, E + C, tile_m, counts, offsets, sorted_token, pair_pos, tile_expert, tile_row0,
+              tile_rows, num_tiles, err, al_s);
+  if (!x_sorted) return;
+  __threadfence_block();
+  __syncthreads();
+  for (int p = warp; p < T * KT; p += 32) {
+    const uint4* src = (const uint4*)(x + (size_t)sorted_token[p] * H);
+    uint4* dst = (uint4*)(x_sorted + (size_t)p * H);
+    for (int i = lane; i < H / 8; i += 32) dst[i] = src[i];
+  }
+}
+
 }  // namespace
 
 NV_API int nv_rowdot(const float* a, long long lda, const void* w, int w_dt, float* out, long long ldo, int T,
@@ -72,5 +104,25 @@ NV_API int nv_rowdot(const float* a, long long lda, const void* w, int w_dt, flo
   dim3 grid(T, (N + 3) / 4);
   if (w_dt == NV_DT_F32) rowdot_kernel<float><<<grid, 256, 0, s>>>(a, lda, (const float*)w, out, ldo, N, K);
   else rowdot_kernel<bf16><<<grid, 256, 0, s>>>(a, lda, (const bf16*)w, out, ldo, N, K);
+  NV_RETURN_LAST();
+}
+
+// Largest batch the fused routing kernel takes: rows and pairs one block can walk in a few microseconds.
+NV_API int nv_moe_route_small_usable(int T, int E, int K, int C, int H) {
+  const size_t smem = (size_t)32 * E * sizeof(double) + (size_t)3 * (E + C) * sizeof(int);
+  return T <= 64 && T * (K + C) <= 1024 && smem <= 48 * 1024 && H % 8 == 0 && K <= 32 && C <= 32;
+}
+
+NV_API int nv_moe_route_small(const float* logits, long long ld, int T, int E, int K, int renorm, int C,
+                              const float* gate_logit, long long gate_ld, int* idx, float* score, int tile_m,
+                              int* counts, int* offsets, int* sorted_token, int* pair_pos, int* tile_expert,
+                              int* tile_row0, int* tile_rows, int* num_tiles, int* err, const void* x,
+                              void* x_sorted, int H, cudaStream_t s) {
+  if (!nv_moe_route_small_usable(T, E, K, C, H) || K < 1 || K > E || (C > 0 && !gate_logit)) return NV_ERR_UNSUPPORTED;
+  if (T == 0) return NV_OK;
+  const size_t smem = (size_t)32 * E * sizeof(double) + (size_t)3 * (E + C) * sizeof(int);
+  moe_route_small_kernel<<<1, 1024, smem, s>>>(logits, ld, T, E, K, renorm, C, gate_logit, gate_ld, idx, score, tile_m,
+                                               counts, offsets, sorted_token, pair_pos, tile_expert, tile_row0,
+                                               tile_rows, num_tiles, err, (const bf16*)x, (bf16*)x_sorted, H);
   NV_RETURN_LAST();
 }

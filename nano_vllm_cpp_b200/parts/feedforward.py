@@ -75,64 +75,95 @@ class SparseMoeSwiGLU(FeedForward):
 
     def load(self, fetch, ctx):
         self.ctx = ctx
-        H, I, E = self.hidden, self.inter, self.E
+        H, I, E, SI = self.hidden, self.inter, self.E, self.shared_inter
         self.router = fetch("gate.weight")
-        if fetch.has("experts.gate_up_proj"):
-            self.w_gate_up = fetch("experts.gate_up_proj").contiguous()
-            self.w_down = fetch("experts.down_proj").contiguous()
+        stacked = fetch.has("experts.gate_up_proj")
+        first = fetch("experts.gate_up_proj") if stacked else fetch("experts.0.gate_proj.weight")
+        # The shared expert as C more experts that every row visits: possible when its width is a whole
+        # number of expert widths.  Its chunks then ride in the grouped products and need no launches of
+        # their own.  Only the tensor-core path does this; the plain path keeps the shared expert apart.
+        C = SI // I if (SI > 0 and SI % I == 0 and SI // I <= 32) else 0
+        self.virtual = C if (ctx.fast_kernels and ctx.act_dtype == torch.bfloat16 and first.dtype == torch.bfloat16
+                             and H % 8 == 0 and I % 8 == 0) else 0
+        EC = E + self.virtual
+        # every expert's [gate; up] rows and down matrix in one block each, indexed by expert
+        self.w_gate_up = torch.empty((EC, 2 * I, H), dtype=first.dtype, device=first.device)
+        self.w_down = torch.empty((EC, H, I), dtype=first.dtype, device=first.device)
+        if stacked:
+            self.w_gate_up[:E].copy_(first)
+            self.w_down[:E].copy_(fetch("experts.down_proj"))
         else:
-            first = fetch("experts.0.gate_proj.weight")
-            # every expert's [gate; up] rows and down matrix in one block each, indexed by expert
-            self.w_gate_up = torch.empty((E, 2 * I, H), dtype=first.dtype, device=first.device)
-            self.w_down = torch.empty((E, H, I), dtype=first.dtype, device=first.device)
             for e in range(E):
                 self.w_gate_up[e, :I].copy_(first if e == 0 else fetch(f"experts.{e}.gate_proj.weight"))
                 self.w_gate_up[e, I:].copy_(fetch(f"experts.{e}.up_proj.weight"))
                 self.w_down[e].copy_(fetch(f"experts.{e}.down_proj.weight"))
-            del first
-        if self.shared_inter > 0:
-            self.sh_gate_up = _cat([fetch("shared_expert.gate_proj.weight"), fetch("shared_expert.up_proj.weight")])
-            self.sh_down = fetch("shared_expert.down_proj.weight")
+        del first
+        if SI > 0:
+            sg, su = fetch("shared_expert.gate_proj.weight"), fetch("shared_expert.up_proj.weight")
+            sd = fetch("shared_expert.down_proj.weight")
             self.sh_gate = fetch("shared_expert_gate.weight")
             # the gate's single row rides along with the router's rows: one product gives both logits
             if self.sh_gate.dtype == self.router.dtype:
                 self.router_and_gate = torch.cat([self.router, self.sh_gate.reshape(1, -1)], dim=0).contiguous()
+            if self.virtual and sg.dtype == su.dtype == sd.dtype == self.w_gate_up.dtype and self.router_and_gate is not None:
+                for c in range(self.virtual):
+                    self.w_gate_up[E + c, :I].copy_(sg[c * I:(c + 1) * I])
+                    self.w_gate_up[E + c, I:].copy_(su[c * I:(c + 1) * I])
+                    self.w_down[E + c].copy_(sd[:, c * I:(c + 1) * I])
+            else:
+                if self.virtual:                       # mixed storage types: keep the shared expert apart
+                    self.w_gate_up, self.w_down = self.w_gate_up[:E].clone(), self.w_down[:E].clone()
+                    self.virtual = 0
+                self.sh_gate_up = _cat([sg, su])
+                self.sh_down = sd
+        else:
+            self.virtual = 0
 
-    def _alignment(self, TK, device, fast):
-        tile_m = ops.grouped_token_tile(TK, self.E) if fast else ops.gemm_plain_tile_m()
-        key = (TK, tile_m)
+    def _alignment(self, TK, n_experts, device, fast):
+        tile_m = ops.grouped_token_tile(TK, n_experts) if fast else ops.gemm_plain_tile_m()
+        key = (TK, n_experts, tile_m)
         if key not in self._align:
-            self._align[key] = ops.MoeAlignment(TK, self.E, tile_m, device)
+            self._align[key] = ops.MoeAlignment(TK, n_experts, tile_m, device)
         return self._align[key]
 
     def forward(self, h, h32, batch):
         ctx = self.ctx
         T = h.shape[0]
         dev = h.device
+        C = self.virtual
+        KT = self.K + C
         gate_logit = None
         if self.router_and_gate is not None:
             both = small_linear(ctx, h32, self.router_and_gate)
             logits, gate_logit = both[:, :self.E], both[:, self.E:]
         else:
             logits = small_linear(ctx, h32, self.router)
-        idx = torch.empty((T, self.K), dtype=torch.int32, device=dev)
-        score = torch.empty((T, self.K), dtype=torch.float32, device=dev)
-        ops.router_topk(logits, self.K, self.renorm, idx, score)
+        idx = torch.empty((T, KT), dtype=torch.int32, device=dev)
+        score = torch.empty((T, KT), dtype=torch.float32, device=dev)
         fast = (ctx.fast_kernels and h.dtype == torch.bfloat16 and self.w_gate_up.dtype == torch.bfloat16
                 and self.w_down.dtype == torch.bfloat16 and self.hidden % 8 == 0 and self.inter % 8 == 0)
-        al = self._alignment(T * self.K, dev, fast)
-        ops.moe_align(idx, self.K, al, ctx.err)
+        al = self._alignment(T * KT, self.E + C, dev, fast)
+        x_sorted = None
+        if fast and ops.moe_route_small_usable(T, self.E, self.K, C, self.hidden):
+            x_sorted = ops.moe_route_small(logits, self.K, self.renorm, C, gate_logit, idx, score, al, ctx.err,
+                                           x=h if T * KT <= 128 else None)
+        else:
+            ops.router_topk(logits, self.K, self.renorm, idx, score, C, gate_logit)
+            ops.moe_align(idx, KT, al, ctx.err)
         self.last_alignment = al
-        act = grouped_linear(ctx, h, self.w_gate_up, ctx.act_dtype, al, a_rows=al.sorted_token, swiglu=True)
+        if x_sorted is not None:
+            act = grouped_linear(ctx, x_sorted, self.w_gate_up, ctx.act_dtype, al, swiglu=True)
+        else:
+            act = grouped_linear(ctx, h, self.w_gate_up, ctx.act_dtype, al, a_rows=al.sorted_token, swiglu=True)
         y = grouped_linear(ctx, act, self.w_down, torch.float32, al)
         shared = None
-        if self.shared_inter > 0:
+        if self.shared_inter > 0 and not C:
             sact = linear(ctx, h, self.sh_gate_up, ctx.act_dtype, swiglu=True)
             shared = linear(ctx, sact, self.sh_down, torch.float32)
             if gate_logit is None:
                 gate_logit = small_linear(ctx, h32, self.sh_gate)
         out = torch.empty((T, self.hidden), dtype=torch.float32, device=dev)
-        ops.moe_combine(y, al.pair_pos, score, shared, gate_logit, out)
+        ops.moe_combine(y, al.pair_pos, score, shared, gate_logit if shared is not None else None, out)
         return out
 
 
