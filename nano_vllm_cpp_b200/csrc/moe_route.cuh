@@ -58,7 +58,8 @@ __device__ __forceinline__ void route_row(const float* __restrict__ r, int E, in
 // From idx[TK] (expert of every (row, k) pair; K pairs per row) build, for the grouped products:
 // counts and offsets per expert, the pairs sorted by expert (sorted_token = source row of each sorted
 // position, pair_pos = sorted position of each pair) and the list of tiles (expert, first row, rows)
-// of at most tile_m rows.  One block of 1024 threads; `al_s` is 3 * E ints of shared memory.  The
+// of at most tile_m rows — and a second list cut by tile_m2, for a product that prefers another tile
+// (t2 == nullptr: none).  One block of 1024 threads; `al_s` is 4 * E ints of shared memory.  The
 // order of pairs inside an expert's segment comes from atomics and may differ from run to run; it
 // decides only where a pair's row sits, never a sum's order.
 __device__ __forceinline__ void align_block(const int* __restrict__ idx, int TK, int K, int E, int tile_m,
@@ -66,10 +67,13 @@ __device__ __forceinline__ void align_block(const int* __restrict__ idx, int TK,
                                             int* __restrict__ sorted_token, int* __restrict__ pair_pos,
                                             int* __restrict__ tile_expert, int* __restrict__ tile_row0,
                                             int* __restrict__ tile_rows, int* __restrict__ num_tiles,
-                                            int* __restrict__ err, int* al_s) {
+                                            int* __restrict__ err, int* al_s, int tile_m2 = 0,
+                                            int* __restrict__ t2_expert = nullptr, int* __restrict__ t2_row0 = nullptr,
+                                            int* __restrict__ t2_rows = nullptr, int* __restrict__ num_tiles2 = nullptr) {
   int* cnt = al_s;
   int* cur = al_s + E;
   int* tbase = al_s + 2 * E;
+  int* tbase2 = al_s + 3 * E;
   const int tid = threadIdx.x, nthr = blockDim.x;
   for (int e = tid; e < E; e += nthr) cnt[e] = 0;
   __syncthreads();
@@ -80,15 +84,18 @@ __device__ __forceinline__ void align_block(const int* __restrict__ idx, int TK,
   }
   __syncthreads();
   if (tid == 0) {                           // E is small: a serial scan over shared memory
-    int off = 0, nt = 0;
+    int off = 0, nt = 0, nt2 = 0;
     for (int e = 0; e < E; ++e) {
       cur[e] = off;
       tbase[e] = nt;
+      tbase2[e] = nt2;
       off += cnt[e];
       nt += (cnt[e] + tile_m - 1) / tile_m;
+      if (tile_m2) nt2 += (cnt[e] + tile_m2 - 1) / tile_m2;
     }
     offsets[E] = off;
     *num_tiles = nt;
+    if (tile_m2) *num_tiles2 = nt2;
   }
   __syncthreads();
   for (int e = tid; e < E; e += nthr) {
@@ -100,6 +107,12 @@ __device__ __forceinline__ void align_block(const int* __restrict__ idx, int TK,
       tile_row0[t] = off + r;
       tile_rows[t] = min(tile_m, c - r);
     }
+    if (tile_m2)
+      for (int r = 0, t = tbase2[e]; r < c; r += tile_m2, ++t) {
+        t2_expert[t] = e;
+        t2_row0[t] = off + r;
+        t2_rows[t] = min(tile_m2, c - r);
+      }
   }
   __syncthreads();
   for (int i = tid; i < TK; i += nthr) {

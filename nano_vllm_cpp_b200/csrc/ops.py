@@ -283,25 +283,54 @@ def router_topk(logits, K: int, renorm: bool, idx, score, C: int = 0, gate_logit
            "router_topk")
 
 
-class MoeAlignment:
-    """Device buffers of one expert permutation (sizes fixed by T*K and E)."""
+class TileList:
+    """Tiles (expert, first row, rows) over an expert-sorted row list, cut by ``tile_m`` rows."""
 
     def __init__(self, TK: int, E: int, tile_m: int, device):
         i32 = dict(dtype=torch.int32, device=device)
-        self.TK, self.E, self.tile_m = TK, E, tile_m
+        self.tile_m = tile_m
         self.max_tiles = max(1, min(TK, (TK + tile_m - 1) // tile_m + E))
-        self.counts = torch.empty(E, **i32)
-        self.offsets = torch.empty(E + 1, **i32)
-        self.sorted_token = torch.empty(max(TK, 1), **i32)
-        self.pair_pos = torch.empty(max(TK, 1), **i32)
         self.tile_expert = torch.empty(self.max_tiles, **i32)
         self.tile_row0 = torch.empty(self.max_tiles, **i32)
         self.tile_rows = torch.empty(self.max_tiles, **i32)
         self.num_tiles = torch.zeros(1, **i32)
 
     @property
-    def tiles(self):
+    def arrays(self):
         return (self.tile_expert, self.tile_row0, self.tile_rows, self.num_tiles)
+
+
+class MoeAlignment:
+    """Device buffers of one expert permutation (sizes fixed by T*K and E): counts and offsets per expert,
+    the sorted pairs, and one or two tile lists over them (``tile_m2``: a second list cut by another tile
+    size, for a product that prefers it; 0 = none)."""
+
+    def __init__(self, TK: int, E: int, tile_m: int, device, tile_m2: int = 0):
+        i32 = dict(dtype=torch.int32, device=device)
+        self.TK, self.E = TK, E
+        self.primary = TileList(TK, E, tile_m, device)
+        self.secondary = TileList(TK, E, tile_m2, device) if tile_m2 and tile_m2 != tile_m else None
+        self.counts = torch.empty(E, **i32)
+        self.offsets = torch.empty(E + 1, **i32)
+        self.sorted_token = torch.empty(max(TK, 1), **i32)
+        self.pair_pos = torch.empty(max(TK, 1), **i32)
+
+    # the primary list under the names the kernels' wrappers use
+    tile_m = property(lambda self: self.primary.tile_m)
+    max_tiles = property(lambda self: self.primary.max_tiles)
+    tile_expert = property(lambda self: self.primary.tile_expert)
+    tile_row0 = property(lambda self: self.primary.tile_row0)
+    tile_rows = property(lambda self: self.primary.tile_rows)
+    num_tiles = property(lambda self: self.primary.num_tiles)
+
+    @property
+    def tiles(self):
+        return self.primary.arrays
+
+    def list_for(self, tile_m: int) -> TileList:
+        if self.secondary is not None and self.secondary.tile_m == tile_m:
+            return self.secondary
+        return self.primary
 
 
 def moe_align(idx, K: int, al: MoeAlignment, err: ErrorFlag) -> None:
@@ -309,10 +338,13 @@ def moe_align(idx, K: int, al: MoeAlignment, err: ErrorFlag) -> None:
     _i32(idx)
     T = idx.numel() // K
     _need(T * K == al.TK, "moe_align: buffers were sized for another batch")
+    s2 = al.secondary
     _check(lib().nv_moe_align(_p(idx), c_int(T), c_int(K), c_int(al.E), c_int(al.tile_m), _p(al.counts),
                               _p(al.offsets), _p(al.sorted_token), _p(al.pair_pos),
                               _p(al.tile_expert), _p(al.tile_row0), _p(al.tile_rows), _p(al.num_tiles), _p(err.t),
-                              _stream()), "moe_align")
+                              c_int(s2.tile_m if s2 else 0), _p(s2.tile_expert if s2 else None), _p(s2.tile_row0 if s2 else None),
+                              _p(s2.tile_rows if s2 else None), _p(s2.num_tiles if s2 else None), _stream()),
+           "moe_align")
 
 
 def moe_route_small_usable(T: int, E: int, K: int, C: int, H: int) -> bool:
@@ -325,6 +357,7 @@ def moe_route_small(logits, K: int, renorm: bool, C: int, gate_logit, idx, score
     T, E = logits.shape
     KT = K + C
     _need(idx.shape == (T, KT) and score.shape == (T, KT) and al.TK == T * KT and al.E == E + C, "route: sizes")
+    _need(al.secondary is None, "route: the one-launch routing builds one tile list")
     xs = None
     H = 8
     if x is not None:
@@ -407,10 +440,17 @@ def gemm_fast_usable(a, w, out, *, bias=None, a_rows=None, swiglu=False, grouped
     return True
 
 
-def grouped_token_tile(TK: int, E: int) -> int:
-    """Token tile of the grouped tensor-core product for TK (row, expert) pairs over E experts."""
+def grouped_token_tile(TK: int, E: int, swiglu: bool = False) -> int:
+    """Token tile of the grouped tensor-core product for TK (row, expert) pairs over E experts.  With many
+    rows per expert a wide token tile wins (two weight tiles per token tile, fewer operand bytes per flop)
+    even though more of an expert's last tile is padding.  ``swiglu`` lets the two products of an expert
+    layer choose differently; at present they agree."""
     avg = (TK + E - 1) // E
-    return 16 if avg <= 12 else (32 if avg <= 24 else 64)
+    if avg <= 12:
+        return 16
+    if avg <= 24:
+        return 32
+    return 128 if avg >= 96 else 64
 
 
 def permute_rows(src, rows, R=None):
@@ -444,18 +484,20 @@ def gemm_fast(a, w, out, *, bias=None, a_rows=None, swiglu=False, M=None, err=No
                         _p(err.t if err is not None else _global_err().t), _stream()), "tc_gemm")
 
 
-def gemm_fast_grouped(a, w, out, align, *, a_rows=None, swiglu=False, err=None) -> None:
-    """Tensor-core form of the grouped ``gemm_plain``: ``align.tile_m`` must be the token tile."""
+def gemm_fast_grouped(a, w, out, align, *, a_rows=None, swiglu=False, err=None, tiles=None) -> None:
+    """Tensor-core form of the grouped ``gemm_plain``; ``tiles`` (a TileList of ``align``) picks the token tile."""
     if a_rows is not None:
         a = permute_rows(a, a_rows, align.TK)
     K = a.shape[1]
     E, rows_w = w.shape[0], w.shape[1]
     N = rows_w // 2 if swiglu else rows_w
-    _need(align.tile_m in (16, 32, 64, 128), "grouped product: token tile must be 16, 32, 64 or 128")
+    tl = tiles if tiles is not None else align.primary
+    _need(tl.tile_m in (16, 32, 64, 128) or (tl.tile_m == 256 and not swiglu),
+          "grouped product: token tile must be 16, 32, 64, 128 (or 256 without swiglu)")
     _check(lib().nv_tc_gemm(_p(a), c_longlong(a.stride(0)), c_int(align.TK), _p(w), c_int(E * rows_w), c_int(N),
                             c_int(K), _p(None), c_int(0), _p(out), c_int(dt(out)), c_longlong(out.stride(0)),
-                            c_int(1 if swiglu else 0), c_int(align.tile_m), c_int(1), _p(None), _p(align.tile_expert),
-                            _p(align.tile_row0), _p(align.tile_rows), _p(align.num_tiles), c_int(align.max_tiles),
+                            c_int(1 if swiglu else 0), c_int(tl.tile_m), c_int(1), _p(None), _p(tl.tile_expert),
+                            _p(tl.tile_row0), _p(tl.tile_rows), _p(tl.num_tiles), c_int(tl.max_tiles),
                             c_int(rows_w), _p(err.t if err is not None else _global_err().t), _stream()),
            "tc_gemm_grouped")
 

@@ -109,7 +109,7 @@ NV_API int nv_rowdot(const float* a, long long lda, const void* w, int w_dt, flo
 
 // Largest batch the fused routing kernel takes: rows and pairs one block can walk in a few microseconds.
 NV_API int nv_moe_route_small_usable(int T, int E, int K, int C, int H) {
-  const size_t smem = (size_t)32 * E * sizeof(double) + (size_t)3 * (E + C) * sizeof(int);
+  const size_t smem = (size_t)32 * E * sizeof(double) + (size_t)4 * (E + C) * sizeof(int);
   return T <= 64 && T * (K + C) <= 1024 && smem <= 48 * 1024 && H % 8 == 0 && K <= 32 && C <= 32;
 }
 
@@ -120,7 +120,7 @@ NV_API int nv_moe_route_small(const float* logits, long long ld, int T, int E, i
                               void* x_sorted, int H, cudaStream_t s) {
   if (!nv_moe_route_small_usable(T, E, K, C, H) || K < 1 || K > E || (C > 0 && !gate_logit)) return NV_ERR_UNSUPPORTED;
   if (T == 0) return NV_OK;
-  const size_t smem = (size_t)32 * E * sizeof(double) + (size_t)3 * (E + C) * sizeof(int);
+  const size_t smem = (size_t)32 * E * sizeof(double) + (size_t)4 * (E + C) * sizeof(int);
   moe_route_small_kernel<<<1, 1024, smem, s>>>(logits, ld, T, E, K, renorm, C, gate_logit, gate_ld, idx, score, tile_m,
                                                counts, offsets, sorted_token, pair_pos, tile_expert, tile_row0,
                                                tile_rows, num_tiles, err, (const bf16*)x, (bf16*)x_sorted, H);

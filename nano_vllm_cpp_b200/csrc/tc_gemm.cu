@@ -11,6 +11,8 @@
 //             operand and the epilogue writes silu(gate) * up
 //   grouped   W is [E, rows, K]; token tiles come from a list (expert, first row, rows) over an
 //             expert-sorted row list, as built by nv_moe_align with tile_m = the token tile
+//   dual      (chosen by the launcher for many tokens) a CTA takes 256 weight rows as two tiles with two
+//             accumulators over one token tile: a third fewer operand bytes per flop than one tile
 //   split-K   grid.z CTAs each sum a range of k; raw float32 partial sums go to a scratch
 //             buffer and nv_tc_gemm_finish adds them in split order, then bias / swiglu / cast
 //
@@ -47,7 +49,8 @@ struct TcArgs {
   int N;                // output features (rows of W per matrix; W has 2N rows with swiglu)
   int rows_per_expert;  // rows of W per expert (grouped), N or 2N
   int k_steps_total, k_steps_per_split, splits;
-  int n_tile, swiglu, stages;
+  int n_tile, swiglu, dual, stages;   // swiglu and dual both mean two weight tiles per stage
+  int w_per_cta;                      // output features per CTA: 128, or 256 with dual
   int tmem_cols;
 };
 
@@ -140,10 +143,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   const int k_end = min(a.k_steps_total, k_begin + a.k_steps_per_split);
   const int n_steps = k_end - k_begin;
 
-  // stage layout: [A gate 16 KB][A up 16 KB if swiglu][X n_tile*128 B], every piece 1024-aligned
+  // stage layout: [W tile 16 KB][second W tile 16 KB if swiglu or dual][X n_tile*128 B], each 1024-aligned
+  const int two = (a.swiglu || a.dual) ? 1 : 0;
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const uint32_t a_bytes = TILE_W * 128, x_bytes = a.n_tile * 128;
-  const uint32_t stage_bytes = a_bytes * (a.swiglu ? 2 : 1) + x_bytes;
+  const uint32_t stage_bytes = a_bytes * (two ? 2 : 1) + x_bytes;
 
   if (threadIdx.x == 0) {
     asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&tm_w) : "memory");
@@ -171,9 +175,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         uint8_t* st = smem + (size_t)s * stage_bytes;
         mbar_expect_tx(&full_bar[s], stage_bytes);
         const int kc = (k_begin + it) * BLOCK_K;
-        tma_load_2d(st, &tm_w, &full_bar[s], kc, w_row_base + nb * TILE_W);
-        if (a.swiglu) tma_load_2d(st + a_bytes, &tm_w, &full_bar[s], kc, w_row_base + a.N + nb * TILE_W);
-        tma_load_2d(st + a_bytes * (a.swiglu ? 2 : 1), &tm_x, &full_bar[s], kc, row0);
+        tma_load_2d(st, &tm_w, &full_bar[s], kc, w_row_base + nb * a.w_per_cta);
+        if (two)     // swiglu: the up rows of the same features; dual: the next 128 features
+          tma_load_2d(st + a_bytes, &tm_w, &full_bar[s], kc, w_row_base + nb * a.w_per_cta + (a.swiglu ? a.N : TILE_W));
+        tma_load_2d(st + a_bytes * (two ? 2 : 1), &tm_x, &full_bar[s], kc, row0);
       }
     }
   } else if (warp == 1) {
@@ -188,13 +193,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         const uint32_t sa = smem_u32(smem + (size_t)s * stage_bytes);
         const uint64_t da = smem_desc_sw128(sa);
         const uint64_t du = smem_desc_sw128(sa + a_bytes);
-        const uint64_t dx = smem_desc_sw128(sa + a_bytes * (a.swiglu ? 2 : 1));
+        const uint64_t dx = smem_desc_sw128(sa + a_bytes * (two ? 2 : 1));
 #pragma unroll
         for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
           const uint64_t adv = (uint64_t)(k * UMMA_K * 2 >> 4);   // 32 bytes per k-slice inside the swizzle row
           const uint32_t acc = (it > 0 || k > 0) ? 1u : 0u;
           umma_bf16(tmem_base, da + adv, dx + adv, idesc, acc);
-          if (a.swiglu) umma_bf16(tmem_base + a.n_tile, du + adv, dx + adv, idesc, acc);
+          if (two) umma_bf16(tmem_base + a.n_tile, du + adv, dx + adv, idesc, acc);
         }
         umma_commit(&empty_bar[s]);     // the stage may be refilled once these MMAs have read it
       }
@@ -203,19 +208,23 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   } else {
     // ---------------------------------------------------------------- epilogue: warps 2..5
     const int q = warp % 4;                        // a warp may read TMEM lanes [32q, 32q + 32) only
-    const int n = nb * TILE_W + q * 32 + lane;     // this thread's output feature
-    const bool n_ok = n < a.N;
+    const int n = nb * a.w_per_cta + q * 32 + lane;    // this thread's output feature (dual: and n + 128)
+    const int n2 = n + TILE_W;
+    const bool n_ok = n < a.N, n2_ok = a.dual && n2 < a.N;
     if (n_steps > 0) mbar_wait(&acc_bar, 0, a.err, 0x7003);
     tc_fence_after();
-    float bias = 0.f;
-    if (a.bias && n_ok && a.splits == 1) bias = ld_dt(a.bias, a.bias_dt, n);
+    float bias = 0.f, bias2 = 0.f;
+    if (a.bias && a.splits == 1) {
+      if (n_ok) bias = ld_dt(a.bias, a.bias_dt, n);
+      if (n2_ok) bias2 = ld_dt(a.bias, a.bias_dt, n2);
+    }
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
     for (int c0 = 0; c0 < a.n_tile; c0 += 16) {
       if (c0 >= rows_here) break;                  // uniform over the warp
       float g[16], u[16];
       if (n_steps > 0) {
         tmem_ld16(lane_addr + c0, g);
-        if (a.swiglu) tmem_ld16(lane_addr + a.n_tile + c0, u);
+        if (two) tmem_ld16(lane_addr + a.n_tile + c0, u);
       } else {
 #pragma unroll
         for (int j = 0; j < 16; ++j) g[j] = u[j] = 0.f;
@@ -230,9 +239,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
           float* p = a.partial + ((size_t)blockIdx.z * a.M_tok + t) * width;
           p[n] = g[j];
           if (a.swiglu) p[a.N + n] = u[j];
+          if (n2_ok) p[n2] = u[j];
         } else {
           float v = a.swiglu ? silu_mul(g[j], u[j]) : g[j];
           st_dt(a.out, a.out_dt, t * a.ldo + n, v + bias);
+          if (n2_ok) st_dt(a.out, a.out_dt, t * a.ldo + n2, u[j] + bias2);
         }
       }
     }
@@ -347,7 +358,7 @@ int pow2_at_least(int v) {
 // Token tile the product will use for `rows` tokens (dense) or for the largest expected expert segment
 // (grouped): the N of the instruction, 16..256.
 NV_API int nv_tc_gemm_token_tile(int rows, int swiglu) {
-  int cap = swiglu ? 128 : 256;   // two accumulators of n_tile columns must fit 512 TMEM columns with room to spare
+  int cap = swiglu ? 128 : 256;   // SwiGLU keeps two accumulators per feature tile: a narrower token tile suits it
   int t = 16;
   while (t < rows && t < cap) t <<= 1;
   return t;
@@ -377,7 +388,7 @@ NV_API int nv_tc_gemm(const void* X, long long ldx, int M_tok, const void* W, in
                       cudaStream_t stream) {
   if (!dt_ok(out_dt) || (bias && !dt_ok(bias_dt))) return NV_ERR_BAD_DTYPE;
   if (K % 8 || ldx % 8 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return NV_ERR_UNSUPPORTED;  // TMA: 16-byte rules
-  if (n_tile < 16 || n_tile > 256 || (n_tile & (n_tile - 1)) || (swiglu && n_tile > 128)) return NV_ERR_BAD_SIZE;
+  if (n_tile < 16 || n_tile > 256 || (n_tile & (n_tile - 1))) return NV_ERR_BAD_SIZE;
   if (M_tok <= 0 || N <= 0) return NV_OK;
   const bool grouped = tile_expert != nullptr;
   if (grouped && splits != 1) return NV_ERR_UNSUPPORTED;
@@ -397,7 +408,15 @@ NV_API int nv_tc_gemm(const void* X, long long ldx, int M_tok, const void* W, in
   a.splits = splits < 1 ? 1 : splits;
   a.k_steps_per_split = (a.k_steps_total + a.splits - 1) / a.splits;
   a.n_tile = n_tile; a.swiglu = swiglu ? 1 : 0;
-  const int stage_bytes = TILE_W * 128 * (swiglu ? 2 : 1) + n_tile * 128;
+  // Many tokens per tile and enough features: two weight tiles per CTA.  The operands then cost 2*16 KB + X
+  // per k-step for twice the flops, which is what the shared-memory fill rate, the limit here, rewards.
+  // ... provided the halved grid still covers the GPU (measured: a half-empty GPU loses more than the tile gains)
+  const bool many_tokens = tile_expert ? n_tile >= 128
+                                       : (M_tok >= 256 && (long long)((N + 255) / 256) * ((M_tok + n_tile - 1) / n_tile) >= 120);
+  a.dual = (!swiglu && many_tokens && N >= 2 * TILE_W && a.splits == 1) ? 1 : 0;
+  a.w_per_cta = a.dual ? 2 * TILE_W : TILE_W;
+  const int two = (swiglu || a.dual) ? 1 : 0;
+  const int stage_bytes = TILE_W * 128 * (two ? 2 : 1) + n_tile * 128;
   // Small stages (few tokens): keep a CTA under half of the shared memory so that two CTAs share an SM and
   // one's start-up and epilogue overlap the other's streaming.  Large stages: one CTA per SM, deep ring.
   const int budget = stage_bytes * 4 <= 104 * 1024 ? 104 * 1024 : 200 * 1024;
@@ -405,7 +424,7 @@ NV_API int nv_tc_gemm(const void* X, long long ldx, int M_tok, const void* W, in
   if (stages > MAX_STAGES) stages = MAX_STAGES;
   if (stages > a.k_steps_per_split) stages = a.k_steps_per_split < 2 ? 2 : a.k_steps_per_split;
   a.stages = stages;
-  a.tmem_cols = pow2_at_least(n_tile * (swiglu ? 2 : 1));
+  a.tmem_cols = pow2_at_least(n_tile * (two ? 2 : 1));
   const size_t smem = (size_t)stages * stage_bytes + 1024;
 
   static std::once_flag once;
@@ -415,7 +434,7 @@ NV_API int nv_tc_gemm(const void* X, long long ldx, int M_tok, const void* W, in
   });
   if (attr_rc != cudaSuccess) return (int)attr_rc;
 
-  dim3 grid((N + TILE_W - 1) / TILE_W, grouped ? max_tiles : (M_tok + n_tile - 1) / n_tile, a.splits);
+  dim3 grid((N + a.w_per_cta - 1) / a.w_per_cta, grouped ? max_tiles : (M_tok + n_tile - 1) / n_tile, a.splits);
   tc_gemm_kernel<<<grid, NUM_THREADS, smem, stream>>>(tm_w, tm_x, a);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;

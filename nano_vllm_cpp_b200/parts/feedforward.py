@@ -120,10 +120,13 @@ class SparseMoeSwiGLU(FeedForward):
             self.virtual = 0
 
     def _alignment(self, TK, n_experts, device, fast):
-        tile_m = ops.grouped_token_tile(TK, n_experts) if fast else ops.gemm_plain_tile_m()
-        key = (TK, n_experts, tile_m)
+        if fast:    # the down product's tile is the primary list, the SwiGLU product may want a wider one
+            tile_m, tile_m2 = ops.grouped_token_tile(TK, n_experts), ops.grouped_token_tile(TK, n_experts, swiglu=True)
+        else:
+            tile_m, tile_m2 = ops.gemm_plain_tile_m(), 0
+        key = (TK, n_experts, tile_m, tile_m2)
         if key not in self._align:
-            self._align[key] = ops.MoeAlignment(TK, n_experts, tile_m, device)
+            self._align[key] = ops.MoeAlignment(TK, n_experts, tile_m, device, tile_m2)
         return self._align[key]
 
     def forward(self, h, h32, batch):
@@ -144,17 +147,19 @@ class SparseMoeSwiGLU(FeedForward):
                 and self.w_down.dtype == torch.bfloat16 and self.hidden % 8 == 0 and self.inter % 8 == 0)
         al = self._alignment(T * KT, self.E + C, dev, fast)
         x_sorted = None
-        if fast and ops.moe_route_small_usable(T, self.E, self.K, C, self.hidden):
+        if fast and al.secondary is None and ops.moe_route_small_usable(T, self.E, self.K, C, self.hidden):
             x_sorted = ops.moe_route_small(logits, self.K, self.renorm, C, gate_logit, idx, score, al, ctx.err,
                                            x=h if T * KT <= 128 else None)
         else:
             ops.router_topk(logits, self.K, self.renorm, idx, score, C, gate_logit)
             ops.moe_align(idx, KT, al, ctx.err)
         self.last_alignment = al
+        wide = al.secondary                      # the tile list of the SwiGLU product, if it has one of its own
         if x_sorted is not None:
-            act = grouped_linear(ctx, x_sorted, self.w_gate_up, ctx.act_dtype, al, swiglu=True)
+            act = grouped_linear(ctx, x_sorted, self.w_gate_up, ctx.act_dtype, al, swiglu=True, tiles=wide)
         else:
-            act = grouped_linear(ctx, h, self.w_gate_up, ctx.act_dtype, al, a_rows=al.sorted_token, swiglu=True)
+            act = grouped_linear(ctx, h, self.w_gate_up, ctx.act_dtype, al, a_rows=al.sorted_token, swiglu=True,
+                                 tiles=wide)
         y = grouped_linear(ctx, act, self.w_down, torch.float32, al)
         shared = None
         if self.shared_inter > 0 and not C:
