@@ -1,9 +1,9 @@
 // Prefill attention: portions of prompts (any number of rows per request, any mix of requests) against
 // the paged keys and values, bfloat16, on the tensor cores.
 //
-// grid = (row tiles, query heads).  A CTA takes 64 consecutive rows of one request (its portion is cut
-// into tiles of 64; the CTA finds its tile by walking the entries' row offsets) and one query head;
-// each of its 4 warps owns 16 rows.  Keys and values are gathered page by page into shared memory in
+// grid = (row tiles, query heads).  A CTA takes 128 consecutive rows of one request (its portion is cut
+// into tiles of 128; the CTA finds its tile by walking the entries' row offsets) and one query head;
+// each of its 8 warps owns 16 rows.  Keys and values are gathered page by page into shared memory in
 // tiles of 64 keys with cp.async (double-buffered), S = Q K^T and O += P V run as m16n8k16 bf16
 // MMAs with float32 accumulators, and the softmax is the online form in float32 registers.
 // Row at position p sees keys [max(0, p + 1 - window), p]; the mask is applied per element, so
@@ -15,7 +15,7 @@
 
 namespace {
 
-constexpr int BM = 64, BN = 64, PF_THREADS = 128;
+constexpr int BM = 128, BN = 64, PF_THREADS = 256;   // 8 warps of 16 rows share every tile of keys
 
 struct PfArgs {
   const bf16* qkv;
@@ -71,7 +71,7 @@ __global__ void __launch_bounds__(PF_THREADS) attention_prefill_kernel(PfArgs a)
   const int h = blockIdx.y, kvh = h / (a.Hq / a.Hkv);
   const int D = a.D, chunks = D / 8;
 
-  if (tid == 0) {                                  // which (entry, tile of 64 rows) is this CTA's?
+  if (tid == 0) {                                  // which (entry, tile of BM rows) is this CTA's?
     int left = blockIdx.x, e = 0, found = -1;
     for (; e < a.S; ++e) {
       int n = a.cu_rows[e + 1] - a.cu_rows[e];
@@ -146,6 +146,12 @@ __global__ void __launch_bounds__(PF_THREADS) attention_prefill_kernel(PfArgs a)
     const bf16* vb = Vs + buf * BN * LDS;
     const int j0 = kv0 + t * BN;
 
+    // a warp whose 16 rows see none of this tile's keys (all later than its last row, or all before its
+    // first row's window) only keeps the barriers
+    const int warp_p_hi = pos0 + warp * 16 + 15, warp_p_lo = pos0 + warp * 16;
+    const bool warp_sees = j0 <= warp_p_hi && (a.window <= 0 || j0 + BN - 1 >= warp_p_lo + 1 - a.window) &&
+                           warp * 16 < nrows;
+    if (warp_sees) {
     // ---- S = Q K^T for this warp's 16 rows x 64 keys
     float s[BN / 8][4];
 #pragma unroll
@@ -224,6 +230,7 @@ __global__ void __launch_bounds__(PF_THREADS) attention_prefill_kernel(PfArgs a)
         }
       }
     }
+    }
     __syncthreads();                                // everyone is done with this buffer before it is refilled
   }
   cp_wait<0>();
@@ -262,8 +269,10 @@ int launch_prefill(const PfArgs& a, int max_tiles, cudaStream_t s) {
 
 }  // namespace
 
-// bfloat16 only; head_dim a multiple of 16 up to 256.  `max_tiles` >= sum over entries of ceil(rows / 64);
-// surplus CTAs leave at once.
+// bfloat16 only; head_dim a multiple of 16 up to 256.  `max_tiles` >= sum over entries of
+// ceil(rows / nv_attention_prefill_tile_rows()); surplus CTAs leave at once.
+NV_API int nv_attention_prefill_tile_rows() { return BM; }
+
 NV_API int nv_attention_prefill(const void* qkv, int q_stride, const void* kc, const void* vc,
                                 const int* block_table, int max_blocks, const int* cu_rows, const int* entry_pos0,
                                 int S, int max_tiles, float scale, int window, void* out, int Hq, int Hkv, int D,

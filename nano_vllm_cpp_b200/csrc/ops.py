@@ -218,6 +218,10 @@ def attention_decode(qkv, k_cache, v_cache, block_table, row_entry, positions, s
            "attention_decode")
 
 
+def attention_prefill_tile_rows() -> int:
+    return int(lib().nv_attention_prefill_tile_rows())
+
+
 def attention_prefill(qkv, k_cache, v_cache, block_table, cu_rows, entry_pos0, max_tiles: int, scale: float,
                       window: int, out, Hq: int, Hkv: int, D: int) -> None:
     """bfloat16 rows of any mix of portions against their paged keys (tensor cores)."""

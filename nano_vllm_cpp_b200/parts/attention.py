@@ -77,7 +77,8 @@ class PagedAttention(Mixer):
                 ops.attention_decode(qkv, cache.k, cache.v, bt, batch.row_entry, batch.positions, self.scale,
                                      self.window, att, self.Hq, self.Hkv, self.D, batch.max_context, err=self.ctx.err)
             else:
-                tiles = sum((e.length + 63) // 64 for e in batch.entries)
+                tm = ops.attention_prefill_tile_rows()
+                tiles = sum((e.length + tm - 1) // tm for e in batch.entries)
                 ops.attention_prefill(qkv, cache.k, cache.v, bt, batch.cu_rows, batch.entry_pos0, tiles, self.scale,
                                       self.window, att, self.Hq, self.Hkv, self.D)
             return
