@@ -59,7 +59,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 
 // DP: head dimension rounded up to 32, 64, 128 or 256 (sizes the shared memory and the accumulators).
 template <int DP>
-__global__ void __launch_bounds__(PF_THREADS) attention_prefill_kernel(PfArgs a) {
+__global__ void __launch_bounds__(PF_THREADS, DP <= 128 ? 2 : 1) attention_prefill_kernel(PfArgs a) {
   constexpr int LDS = DP + 8;                      // row stride (elements): 16 bytes of padding against bank conflicts
   extern __shared__ __align__(16) uint8_t pf_smem[];
   bf16* Qs = (bf16*)pf_smem;
@@ -72,7 +72,8 @@ __global__ void __launch_bounds__(PF_THREADS) attention_prefill_kernel(PfArgs a)
   const int D = a.D, chunks = D / 8;
 
   if (tid == 0) {                                  // which (entry, tile of BM rows) is this CTA's?
-    int left = blockIdx.x, e = 0, found = -1;
+    // later tiles of a portion see more keys: hand them out first so that the long ones start early
+    int left = (int)(gridDim.x - 1 - blockIdx.x), e = 0, found = -1;
     for (; e < a.S; ++e) {
       int n = a.cu_rows[e + 1] - a.cu_rows[e];
       int tiles = (n + BM - 1) / BM;
@@ -95,6 +96,8 @@ __global__ void __launch_bounds__(PF_THREADS) attention_prefill_kernel(PfArgs a)
   const int kv0 = lo / 16 * 16;
   const int n_tiles = (hi - kv0 + BN - 1) / BN;
   const int* bt = a.block_table + (size_t)e * a.max_blocks;
+  const bool pow2_page = (a.page & (a.page - 1)) == 0;
+  const int page_shift = 31 - __clz(a.page);
 
   // ---- Q tile -> shared memory (rows beyond nrows are zero)
   for (int c = tid; c < BM * chunks; c += PF_THREADS) {
@@ -108,12 +111,16 @@ __global__ void __launch_bounds__(PF_THREADS) attention_prefill_kernel(PfArgs a)
     bf16* kd = Ks + buf * BN * LDS;
     bf16* vd = Vs + buf * BN * LDS;
     for (int c = tid; c < BN * chunks; c += PF_THREADS) {
-      const int r = c / chunks, ch = c % chunks;
+      const int r = c / chunks, ch = c - r * chunks;
       const int j = j0 + r;
-      int blk = -1;
-      if (j < hi) blk = bt[j / a.page];
+      int blk = -1, slot = 0;
+      if (j < hi) {
+        const int pg = pow2_page ? (j >> page_shift) : j / a.page;
+        slot = j - pg * a.page;
+        blk = bt[pg];
+      }
       if (blk >= 0) {
-        const size_t off = (((size_t)blk * a.Hkv + kvh) * a.page + j % a.page) * D + ch * 8;
+        const size_t off = (((size_t)blk * a.Hkv + kvh) * a.page + slot) * D + ch * 8;
         cp_async16(kd + r * LDS + ch * 8, a.kc + off);
         cp_async16(vd + r * LDS + ch * 8, a.vc + off);
       } else {
@@ -172,18 +179,25 @@ __global__ void __launch_bounds__(PF_THREADS) attention_prefill_kernel(PfArgs a)
         }
       }
     }
-    // ---- mask, online softmax
+    // ---- mask (only on tiles that some row of the warp sees partly), online softmax
+    const bool whole = j0 + BN - 1 <= warp_p_lo && (a.window <= 0 || j0 >= warp_p_hi + 1 - a.window) &&
+                       warp * 16 + 15 < nrows;
     float mx_lo = -INFINITY, mx_hi = -INFINITY;
+    if (!whole) {
+#pragma unroll
+      for (int nt = 0; nt < BN / 8; ++nt) {
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const int j = j0 + nt * 8 + 2 * tq + c;
+          if (!(live_lo && j <= p_lo && j >= w_lo_lo)) s[nt][c] = -INFINITY;
+          if (!(live_hi && j <= p_hi && j >= w_lo_hi)) s[nt][2 + c] = -INFINITY;
+        }
+      }
+    }
 #pragma unroll
     for (int nt = 0; nt < BN / 8; ++nt) {
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        const int j = j0 + nt * 8 + 2 * tq + c;
-        if (!(live_lo && j <= p_lo && j >= w_lo_lo)) s[nt][c] = -INFINITY;
-        if (!(live_hi && j <= p_hi && j >= w_lo_hi)) s[nt][2 + c] = -INFINITY;
-        mx_lo = fmaxf(mx_lo, s[nt][c]);
-        mx_hi = fmaxf(mx_hi, s[nt][2 + c]);
-      }
+      mx_lo = fmaxf(mx_lo, fmaxf(s[nt][0], s[nt][1]));
+      mx_hi = fmaxf(mx_hi, fmaxf(s[nt][2], s[nt][3]));
     }
     mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
     mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));

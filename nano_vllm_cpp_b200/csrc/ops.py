@@ -182,8 +182,9 @@ def gemm_plain(a, w, out, *, bias=None, a_rows=None, swiglu=False, M=None, tiles
                                _p(te), _p(tr0), _p(tr), _p(nt), c_int(max_tiles), _stream()), "gemm_plain")
 
 
-def rowdot(a, w, out) -> None:
-    """out[t, n] = a[t, :] . w[n, :] for float32 rows and a short matrix (float32 or bfloat16), float32 out."""
+def rowdot(a, w, out, wide: bool = False) -> None:
+    """out[t, n] = a[t, :] . w[n, :] for float32 rows and a short matrix (float32 or bfloat16), float32 out.
+    ``wide``: the many-rows kernel (another summation order; see small_ops.cu)."""
     _cuda_contig(w)
     _need(a.dtype == torch.float32 and out.dtype == torch.float32 and a.stride(1) == 1 and out.stride(1) == 1,
           "rowdot: float32 rows")
@@ -191,7 +192,7 @@ def rowdot(a, w, out) -> None:
     N = w.shape[0]
     _need(w.shape[1] == K and out.shape == (T, N), "rowdot: shapes")
     _check(lib().nv_rowdot(_p(a), c_longlong(a.stride(0)), _p(w), c_int(dt(w)), _p(out), c_longlong(out.stride(0)),
-                           c_int(T), c_int(N), c_int(K), _stream()), "rowdot")
+                           c_int(T), c_int(N), c_int(K), c_int(1 if wide else 0), _stream()), "rowdot")
 
 
 def attention_decode_usable(k_cache, D: int) -> bool:

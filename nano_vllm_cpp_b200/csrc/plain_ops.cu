@@ -58,19 +58,19 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(float* __restrict__ x,
 // NeoX pairing (d, d + R/2) over the first R = rotary_dim elements of each head:
 //   ang = float(pos) * inv_freq[d];  o[d] = x[d] cos - x[d+R/2] sin;  o[d+R/2] = x[d+R/2] cos + x[d] sin
 // (src/hip_ops.hip:431-450).  q is rotated in place; k is rotated and written to its page; v is
-// copied to its page (src/hip_ops.hip:452-466).  One block per row and group of four heads: the angles are taken once per block.
+// copied to its page (src/hip_ops.hip:452-466).  
 // Cache layout: [page][kv head][slot in page][D].
-constexpr int ROPE_HEADS_PER_BLOCK = 4;
-__global__ void __launch_bounds__(128) rope_store_kernel(void* __restrict__ qkv, int dt, const int* __restrict__ positions,
+// One block per (row, group of `hpb` heads in the order q.., k.., v..): the angles are taken once per block.
+__global__ void __launch_bounds__(256) rope_store_kernel(void* __restrict__ qkv, int dt, const int* __restrict__ positions,
                                   const float* __restrict__ inv_freq, int rotary_dim,
                                   void* __restrict__ kc, void* __restrict__ vc, int cache_dt,
                                   const int* __restrict__ block_table, int max_blocks,
                                   const int* __restrict__ row_entry, int Hq, int Hkv, int D, int page,
-                                  int write_kv, int* __restrict__ err) {
-  __shared__ float cs[128], sn[128];        // cos and sin of this row's angles, once for the block's heads
+                                  int write_kv, int hpb, int* __restrict__ err) {
+  __shared__ float cs[128], sn[128];
   const int t = blockIdx.x;
-  const int h_begin = blockIdx.y * ROPE_HEADS_PER_BLOCK;                 // heads in the order q.., k.., v..
-  const int h_end = min(Hq + 2 * Hkv, h_begin + ROPE_HEADS_PER_BLOCK);
+  const int h_begin = blockIdx.y * hpb;
+  const int h_end = min(Hq + 2 * Hkv, h_begin + hpb);
   if (!write_kv && h_begin >= Hq) return;
   const int width = (Hq + 2 * Hkv) * D;
   const int pos = positions[t];
@@ -91,31 +91,39 @@ __global__ void __launch_bounds__(128) rope_store_kernel(void* __restrict__ qkv,
   }
   __syncthreads();
   const size_t row = (size_t)t * width;
-  for (int h = h_begin; h < h_end; ++h) {
-    const size_t base = row + (size_t)h * D;
-    if (h < Hq + Hkv) {
-      const bool is_q = h < Hq;
-      if (!is_q && !write_kv) continue;
-      const size_t cbase = is_q ? 0 : (((size_t)blk * Hkv + (h - Hq)) * page + pos % page) * D;
-      // a thread owns whole pairs (f, f + half), so rotating q in place needs no barrier
-      for (int f = threadIdx.x; f < half; f += blockDim.x) {
-        const float x1 = ld_dt(qkv, dt, base + f), x2 = ld_dt(qkv, dt, base + f + half);
-        const float o1 = x1 * cs[f] - x2 * sn[f], o2 = x2 * cs[f] + x1 * sn[f];
-        if (is_q) {
-          st_dt(qkv, dt, base + f, o1);
-          st_dt(qkv, dt, base + f + half, o2);
-        } else {
-          st_dt(kc, cache_dt, cbase + f, o1);
-          st_dt(kc, cache_dt, cbase + f + half, o2);
-        }
+  const size_t slot = (size_t)(pos % page);
+  // rotated heads (q, and k when the cache is written): the block's (head, pair) items flattened; a thread
+  // owns whole pairs (f, f + half), so rotating q in place needs no barrier
+  const int rot_end = min(h_end, write_kv ? Hq + Hkv : Hq);
+  if (half > 0)
+    for (int i = threadIdx.x; i < (rot_end - h_begin) * half; i += blockDim.x) {
+      const int h = h_begin + i / half, f = i % half;
+      const size_t base = row + (size_t)h * D;
+      const float x1 = ld_dt(qkv, dt, base + f), x2 = ld_dt(qkv, dt, base + f + half);
+      const float o1 = x1 * cs[f] - x2 * sn[f], o2 = x2 * cs[f] + x1 * sn[f];
+      if (h < Hq) {
+        st_dt(qkv, dt, base + f, o1);
+        st_dt(qkv, dt, base + f + half, o2);
+      } else {
+        const size_t cbase = (((size_t)blk * Hkv + (h - Hq)) * page + slot) * D;
+        st_dt(kc, cache_dt, cbase + f, o1);
+        st_dt(kc, cache_dt, cbase + f + half, o2);
       }
-      if (!is_q)
-        for (int d = rotary_dim + threadIdx.x; d < D; d += blockDim.x)
-          st_dt(kc, cache_dt, cbase + d, ld_dt(qkv, dt, base + d));
-    } else if (write_kv) {
-      const size_t cbase = (((size_t)blk * Hkv + (h - Hq - Hkv)) * page + pos % page) * D;
-      for (int d = threadIdx.x; d < D; d += blockDim.x) st_dt(vc, cache_dt, cbase + d, ld_dt(qkv, dt, base + d));
     }
+  if (!write_kv) return;
+  // what is copied as it is: the part of k beyond the rotated dimensions, and v
+  const int tail = D - rotary_dim;
+  const int k_lo = max(h_begin, Hq), k_hi = min(h_end, Hq + Hkv);
+  for (int i = threadIdx.x; i < (k_hi - k_lo) * tail; i += blockDim.x) {
+    const int h = k_lo + i / tail, d = rotary_dim + i % tail;
+    const size_t cbase = (((size_t)blk * Hkv + (h - Hq)) * page + slot) * D;
+    st_dt(kc, cache_dt, cbase + d, ld_dt(qkv, dt, row + (size_t)h * D + d));
+  }
+  const int v_lo = max(h_begin, Hq + Hkv);
+  for (int i = threadIdx.x; i < (h_end - v_lo) * D; i += blockDim.x) {
+    const int h = v_lo + i / D, d = i % D;
+    const size_t cbase = (((size_t)blk * Hkv + (h - Hq - Hkv)) * page + slot) * D;
+    st_dt(vc, cache_dt, cbase + d, ld_dt(qkv, dt, row + (size_t)h * D + d));
   }
 }
 
@@ -356,9 +364,12 @@ NV_API int nv_rope_store(void* qkv, int dt, const int* positions, const float* i
   if (rotary_dim < 0 || rotary_dim > D || rotary_dim % 2) return NV_ERR_BAD_SIZE;
   if (T == 0) return NV_OK;
   if (D > 256 || D % 2) return NV_ERR_UNSUPPORTED;
-  dim3 grid(T, (Hq + 2 * Hkv + ROPE_HEADS_PER_BLOCK - 1) / ROPE_HEADS_PER_BLOCK);
-  rope_store_kernel<<<grid, 128, 0, s>>>(qkv, dt, positions, inv_freq, rotary_dim, kc, vc, cache_dt,
-                                             block_table, max_blocks, row_entry, Hq, Hkv, D, page, write_kv, err);
+  // few rows: many small blocks (latency); many rows: one block per row does all heads (the angles once)
+  const int heads = Hq + 2 * Hkv;
+  const int hpb = T >= 256 ? heads : 4;
+  dim3 grid(T, (heads + hpb - 1) / hpb);
+  rope_store_kernel<<<grid, T >= 256 ? 256 : 128, 0, s>>>(qkv, dt, positions, inv_freq, rotary_dim, kc, vc, cache_dt,
+                                             block_table, max_blocks, row_entry, Hq, Hkv, D, page, write_kv, hpb, err);
   NV_RETURN_LAST();
 }
 

@@ -63,6 +63,60 @@ __global__ void __launch_bounds__(256) rowdot_kernel(const float* __restrict__ a
   }
 }
 
+// The same product for many rows: one block per row keeps the row in shared memory and its 8 warps walk the
+// outputs four at a time, each warp summing all of k itself.  Fewer, fatter blocks and a fraction of the
+// loads; the order of the sum differs from rowdot_kernel's, so a run uses one of the two for a given op
+// and batch shape only where rounding-level differences between batch shapes are accepted (bfloat16 runs).
+template <typename TW>
+__global__ void __launch_bounds__(256) rowdot_wide_kernel(const float* __restrict__ a, long long lda,
+                                                          const TW* __restrict__ w, float* __restrict__ out,
+                                                          long long ldo, int N, int K) {
+  extern __shared__ float row_s[];
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int t = blockIdx.x;
+  const float* ar = a + (size_t)t * lda;
+  for (int k = threadIdx.x; k < K; k += 256) row_s[k] = ar[k];
+  __syncthreads();
+  const bool vec = K % 4 == 0 && ((uintptr_t)w & 15) == 0;
+  for (int n0 = warp * 4; n0 < N; n0 += 32) {
+    float s[4] = {0.f, 0.f, 0.f, 0.f};
+    const TW* wr[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) wr[i] = w + (size_t)min(n0 + i, N - 1) * K;
+    if (vec) {
+      for (int k = lane * 4; k < K; k += 128) {
+        const float4 av = *(const float4*)(row_s + k);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float w0, w1, w2, w3;
+          if (sizeof(TW) == 4) {
+            const float4 wv = *(const float4*)((const float*)wr[i] + k);
+            w0 = wv.x; w1 = wv.y; w2 = wv.z; w3 = wv.w;
+          } else {
+            const uint2 raw = *(const uint2*)((const bf16*)wr[i] + k);
+            const float2 lo = __bfloat1622float2(*(const __nv_bfloat162*)&raw.x);
+            const float2 hi = __bfloat1622float2(*(const __nv_bfloat162*)&raw.y);
+            w0 = lo.x; w1 = lo.y; w2 = hi.x; w3 = hi.y;
+          }
+          s[i] = fmaf(av.x, w0, s[i]); s[i] = fmaf(av.y, w1, s[i]);
+          s[i] = fmaf(av.z, w2, s[i]); s[i] = fmaf(av.w, w3, s[i]);
+        }
+      }
+    } else {
+      for (int k = lane; k < K; k += 32) {
+        const float av = row_s[k];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) s[i] = fmaf(av, to_f32(wr[i][k]), s[i]);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      s[i] = warp_sum(s[i]);
+      if (lane == 0 && n0 + i < N) out[(size_t)t * ldo + n0 + i] = s[i];
+    }
+  }
+}
+
 // Routing of a small batch in one launch: top-k of every row, the expert permutation, and the
 // expert-sorted copy of the (bfloat16) activations.  One block of 1024 threads; for batches whose
 // T * (K + C) pairs and rows fit one block's reach (the launcher checks).
@@ -97,9 +151,16 @@ __global__ void __launch_bounds__(1024) moe_route_small_kernel(
 }  // namespace
 
 NV_API int nv_rowdot(const float* a, long long lda, const void* w, int w_dt, float* out, long long ldo, int T,
-                     int N, int K, cudaStream_t s) {
+                     int N, int K, int wide, cudaStream_t s) {
   if (!dt_ok(w_dt)) return NV_ERR_BAD_DTYPE;
   if (T == 0 || N == 0) return NV_OK;
+  if (wide && (size_t)K * 4 <= 48 * 1024) {
+    if (w_dt == NV_DT_F32)
+      rowdot_wide_kernel<float><<<T, 256, (size_t)K * 4, s>>>(a, lda, (const float*)w, out, ldo, N, K);
+    else
+      rowdot_wide_kernel<bf16><<<T, 256, (size_t)K * 4, s>>>(a, lda, (const bf16*)w, out, ldo, N, K);
+    NV_RETURN_LAST();
+  }
   if ((N + 3) / 4 > 65535) return NV_ERR_BAD_SIZE;
   dim3 grid(T, (N + 3) / 4);
   if (w_dt == NV_DT_F32) rowdot_kernel<float><<<grid, 256, 0, s>>>(a, lda, (const float*)w, out, ldo, N, K);

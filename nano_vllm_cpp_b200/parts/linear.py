@@ -32,7 +32,8 @@ def small_linear(ctx, a32, w):
     """float32 rows times a short matrix, float32 out: router logits and gate logits."""
     out = torch.empty((a32.shape[0], w.shape[0]), dtype=torch.float32, device=a32.device)
     if a32.shape[0]:
-        ops.rowdot(a32, w, out)
+        # float32 runs keep one kernel whatever the batch is; bfloat16 runs take the many-rows kernel for prompts
+        ops.rowdot(a32, w, out, wide=ctx.fast_kernels and ctx.act_dtype == torch.bfloat16 and a32.shape[0] >= 64)
     return out
 
 

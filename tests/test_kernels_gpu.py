@@ -185,6 +185,9 @@ def test_rowdot(T, N, K, tw):
     out = torch.empty(T, N, device=DEV)
     o.rowdot(a, w, out)
     close(out, a.double() @ w.double().T, 2e-6, "rowdot")
+    wide = torch.empty(T, N, device=DEV)
+    o.rowdot(a, w, wide, wide=True)                  # the many-rows kernel: same values up to rounding
+    close(wide, a.double() @ w.double().T, 2e-6, "rowdot wide")
     one = torch.empty(1, N, device=DEV)
     o.rowdot(a[T - 1:T].contiguous(), w, one)
     assert torch.equal(one[0], out[T - 1])          # a row does not depend on the batch
