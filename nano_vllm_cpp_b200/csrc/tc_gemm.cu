@@ -16,8 +16,10 @@
 //   split-K   grid.z CTAs each sum a range of k; raw float32 partial sums go to a scratch
 //             buffer and nv_tc_gemm_finish adds them in split order, then bias / swiglu / cast
 //
-// Warp roles: warp 0 issues TMA loads, warp 1 allocates TMEM and issues the MMAs, warps 2-5
-// read the accumulator back (tcgen05.ld) and store.  Every wait on an mbarrier is bounded: after
+// The kernel is persistent (one or two CTAs per SM walk the tile list) with two accumulator sets in
+// TMEM, so a tile's epilogue overlaps the next tile's products.  Warp roles: warp 0 issues TMA
+// loads, warp 1 allocates TMEM and issues the MMAs, warps 2-5 read the accumulator back (tcgen05.ld)
+// and store.  Every wait on an mbarrier is bounded: after
 // about two seconds a waiter records the fact in the error flag and goes on, so the kernel always
 // ends and frees its TMEM; its output is then garbage and the host raises.
 #include "pipeline.cuh"
@@ -51,6 +53,8 @@ struct TcArgs {
   int k_steps_total, k_steps_per_split, splits;
   int n_tile, swiglu, dual, stages;   // swiglu and dual both mean two weight tiles per stage
   int w_per_cta;                      // output features per CTA: 128, or 256 with dual
+  int n_blocks;                       // blocks of w_per_cta features
+  int acc_bufs;                       // accumulator sets in TMEM: 2 when two fit, else 1
   int tmem_cols;
 };
 
@@ -120,34 +124,51 @@ __device__ __forceinline__ uint32_t instr_desc(int n) {
 }
 
 // ------------------------------------------------------------------ the kernel
+// Persistent: the grid is as many CTAs as fit the GPU at once and every CTA walks the tile list
+// tile = blockIdx.x, blockIdx.x + gridDim.x, ...  A tile is (block of output features, token tile,
+// k split), features fastest so that CTAs running together share token tiles in L2.  The operand
+// ring and the barriers' phases run on across tiles, and the accumulator is double-buffered in
+// TMEM (when two fit), so the epilogue of one tile overlaps the products of the next.
+struct Tile {
+  int nb, row0, rows_here, w_row_base, z, n_steps, k_begin;
+};
+
+__device__ __forceinline__ bool get_tile(const TcArgs& a, int tile_id, int y_tiles, Tile& t) {
+  const int total = a.n_blocks * y_tiles * a.splits;
+  if (tile_id >= total) return false;
+  t.nb = tile_id % a.n_blocks;
+  const int rest = tile_id / a.n_blocks;
+  const int y = rest % y_tiles;
+  t.z = rest / y_tiles;
+  if (a.tile_expert) {
+    t.row0 = a.tile_row0[y];
+    t.rows_here = a.tile_rows[y];
+    t.w_row_base = a.tile_expert[y] * a.rows_per_expert;
+  } else {
+    t.row0 = y * a.n_tile;
+    t.rows_here = min(a.n_tile, a.M_tok - t.row0);
+    t.w_row_base = 0;
+  }
+  t.k_begin = t.z * a.k_steps_per_split;
+  t.n_steps = max(0, min(a.k_steps_total, t.k_begin + a.k_steps_per_split) - t.k_begin);
+  return true;
+}
+
 __global__ void __launch_bounds__(NUM_THREADS, 2)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, TcArgs a) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  __shared__ uint64_t full_bar[MAX_STAGES], empty_bar[MAX_STAGES], acc_bar;
+  __shared__ uint64_t full_bar[MAX_STAGES], empty_bar[MAX_STAGES], acc_full[2], acc_empty[2];
   __shared__ uint32_t tmem_base_s;
 
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-  const int nb = blockIdx.x;                       // block of 128 output features
-  int row0, rows_here, w_row_base;
-  if (a.tile_expert) {
-    if ((int)blockIdx.y >= *a.num_tiles) return;   // the whole CTA leaves before touching barriers or TMEM
-    row0 = a.tile_row0[blockIdx.y];
-    rows_here = a.tile_rows[blockIdx.y];
-    w_row_base = a.tile_expert[blockIdx.y] * a.rows_per_expert;
-  } else {
-    row0 = blockIdx.y * a.n_tile;
-    rows_here = min(a.n_tile, a.M_tok - row0);
-    w_row_base = 0;
-  }
-  const int k_begin = blockIdx.z * a.k_steps_per_split;
-  const int k_end = min(a.k_steps_total, k_begin + a.k_steps_per_split);
-  const int n_steps = k_end - k_begin;
+  const int y_tiles = a.tile_expert ? *a.num_tiles : (a.M_tok + a.n_tile - 1) / a.n_tile;
 
   // stage layout: [W tile 16 KB][second W tile 16 KB if swiglu or dual][X n_tile*128 B], each 1024-aligned
   const int two = (a.swiglu || a.dual) ? 1 : 0;
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const uint32_t a_bytes = TILE_W * 128, x_bytes = a.n_tile * 128;
   const uint32_t stage_bytes = a_bytes * (two ? 2 : 1) + x_bytes;
+  const int acc_cols = a.n_tile * (two ? 2 : 1);   // TMEM columns of one accumulator set
 
   if (threadIdx.x == 0) {
     asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&tm_w) : "memory");
@@ -156,7 +177,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
-    mbar_init(&acc_bar, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 4);                 // one arrival per epilogue warp
+    }
     mbar_fence_init();
   }
   if (warp == 1) tmem_alloc(&tmem_base_s, a.tmem_cols);
@@ -168,84 +192,105 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
-      for (int it = 0; it < n_steps; ++it) {
-        const int s = it % a.stages;
-        const uint32_t ph = (it / a.stages) & 1;
-        mbar_wait(&empty_bar[s], ph ^ 1, a.err, 0x7001);
-        uint8_t* st = smem + (size_t)s * stage_bytes;
-        mbar_expect_tx(&full_bar[s], stage_bytes);
-        const int kc = (k_begin + it) * BLOCK_K;
-        tma_load_2d(st, &tm_w, &full_bar[s], kc, w_row_base + nb * a.w_per_cta);
-        if (two)     // swiglu: the up rows of the same features; dual: the next 128 features
-          tma_load_2d(st + a_bytes, &tm_w, &full_bar[s], kc, w_row_base + nb * a.w_per_cta + (a.swiglu ? a.N : TILE_W));
-        tma_load_2d(st + a_bytes * (two ? 2 : 1), &tm_x, &full_bar[s], kc, row0);
+      int it = 0;                                  // k-steps issued so far, over all tiles
+      Tile t;
+      for (int tile = blockIdx.x; get_tile(a, tile, y_tiles, t); tile += gridDim.x) {
+        for (int k = 0; k < t.n_steps; ++k, ++it) {
+          const int s = it % a.stages;
+          mbar_wait(&empty_bar[s], ((it / a.stages) & 1) ^ 1, a.err, 0x7001);
+          uint8_t* st = smem + (size_t)s * stage_bytes;
+          mbar_expect_tx(&full_bar[s], stage_bytes);
+          const int kc = (t.k_begin + k) * BLOCK_K;
+          const int wr = t.w_row_base + t.nb * a.w_per_cta;
+          tma_load_2d(st, &tm_w, &full_bar[s], kc, wr);
+          if (two)     // swiglu: the up rows of the same features; dual: the next 128 features
+            tma_load_2d(st + a_bytes, &tm_w, &full_bar[s], kc, wr + (a.swiglu ? a.N : TILE_W));
+          tma_load_2d(st + a_bytes * (two ? 2 : 1), &tm_x, &full_bar[s], kc, t.row0);
+        }
       }
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       const uint32_t idesc = instr_desc(a.n_tile);
-      for (int it = 0; it < n_steps; ++it) {
-        const int s = it % a.stages;
-        const uint32_t ph = (it / a.stages) & 1;
-        mbar_wait(&full_bar[s], ph, a.err, 0x7002);
+      int it = 0, n = 0;                           // k-steps consumed, tiles done
+      Tile t;
+      for (int tile = blockIdx.x; get_tile(a, tile, y_tiles, t); tile += gridDim.x, ++n) {
+        const int b = a.acc_bufs == 2 ? (n & 1) : 0;
+        const int use = a.acc_bufs == 2 ? (n >> 1) : n;          // how often this buffer was used before
+        mbar_wait(&acc_empty[b], (use & 1) ^ 1, a.err, 0x7004);  // the epilogue has drained it
         tc_fence_after();
-        const uint32_t sa = smem_u32(smem + (size_t)s * stage_bytes);
-        const uint64_t da = smem_desc_sw128(sa);
-        const uint64_t du = smem_desc_sw128(sa + a_bytes);
-        const uint64_t dx = smem_desc_sw128(sa + a_bytes * (two ? 2 : 1));
+        const uint32_t acc_addr = tmem_base + b * acc_cols;
+        for (int k = 0; k < t.n_steps; ++k, ++it) {
+          const int s = it % a.stages;
+          mbar_wait(&full_bar[s], (it / a.stages) & 1, a.err, 0x7002);
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + (size_t)s * stage_bytes);
+          const uint64_t da = smem_desc_sw128(sa);
+          const uint64_t du = smem_desc_sw128(sa + a_bytes);
+          const uint64_t dx = smem_desc_sw128(sa + a_bytes * (two ? 2 : 1));
 #pragma unroll
-        for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
-          const uint64_t adv = (uint64_t)(k * UMMA_K * 2 >> 4);   // 32 bytes per k-slice inside the swizzle row
-          const uint32_t acc = (it > 0 || k > 0) ? 1u : 0u;
-          umma_bf16(tmem_base, da + adv, dx + adv, idesc, acc);
-          if (two) umma_bf16(tmem_base + a.n_tile, du + adv, dx + adv, idesc, acc);
+          for (int kk = 0; kk < BLOCK_K / UMMA_K; ++kk) {
+            const uint64_t adv = (uint64_t)(kk * UMMA_K * 2 >> 4);   // 32 bytes per k-slice inside the swizzle row
+            const uint32_t acc = (k > 0 || kk > 0) ? 1u : 0u;
+            umma_bf16(acc_addr, da + adv, dx + adv, idesc, acc);
+            if (two) umma_bf16(acc_addr + a.n_tile, du + adv, dx + adv, idesc, acc);
+          }
+          umma_commit(&empty_bar[s]);     // the stage may be refilled once these MMAs have read it
         }
-        umma_commit(&empty_bar[s]);     // the stage may be refilled once these MMAs have read it
+        umma_commit(&acc_full[b]);        // the accumulator is complete (at once if the tile had no k-steps)
       }
-      umma_commit(&acc_bar);            // the accumulator is complete
     }
   } else {
     // ---------------------------------------------------------------- epilogue: warps 2..5
     const int q = warp % 4;                        // a warp may read TMEM lanes [32q, 32q + 32) only
-    const int n = nb * a.w_per_cta + q * 32 + lane;    // this thread's output feature (dual: and n + 128)
-    const int n2 = n + TILE_W;
-    const bool n_ok = n < a.N, n2_ok = a.dual && n2 < a.N;
-    if (n_steps > 0) mbar_wait(&acc_bar, 0, a.err, 0x7003);
-    tc_fence_after();
-    float bias = 0.f, bias2 = 0.f;
-    if (a.bias && a.splits == 1) {
-      if (n_ok) bias = ld_dt(a.bias, a.bias_dt, n);
-      if (n2_ok) bias2 = ld_dt(a.bias, a.bias_dt, n2);
-    }
-    const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
-    for (int c0 = 0; c0 < a.n_tile; c0 += 16) {
-      if (c0 >= rows_here) break;                  // uniform over the warp
-      float g[16], u[16];
-      if (n_steps > 0) {
-        tmem_ld16(lane_addr + c0, g);
-        if (two) tmem_ld16(lane_addr + a.n_tile + c0, u);
-      } else {
-#pragma unroll
-        for (int j = 0; j < 16; ++j) g[j] = u[j] = 0.f;
+    int n_done = 0;
+    Tile t;
+    for (int tile = blockIdx.x; get_tile(a, tile, y_tiles, t); tile += gridDim.x, ++n_done) {
+      const int b = a.acc_bufs == 2 ? (n_done & 1) : 0;
+      const int use = a.acc_bufs == 2 ? (n_done >> 1) : n_done;
+      const int n = t.nb * a.w_per_cta + q * 32 + lane;   // this thread's output feature (dual: and n + 128)
+      const int n2 = n + TILE_W;
+      const bool n_ok = n < a.N, n2_ok = a.dual && n2 < a.N;
+      mbar_wait(&acc_full[b], use & 1, a.err, 0x7003);
+      tc_fence_after();
+      float bias = 0.f, bias2 = 0.f;
+      if (a.bias && a.splits == 1) {
+        if (n_ok) bias = ld_dt(a.bias, a.bias_dt, n);
+        if (n2_ok) bias2 = ld_dt(a.bias, a.bias_dt, n2);
       }
-      if (!n_ok) continue;
-#pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        if (c0 + j >= rows_here) break;
-        const size_t t = (size_t)(row0 + c0 + j);
-        if (a.splits > 1) {
-          const int width = a.swiglu ? 2 * a.N : a.N;
-          float* p = a.partial + ((size_t)blockIdx.z * a.M_tok + t) * width;
-          p[n] = g[j];
-          if (a.swiglu) p[a.N + n] = u[j];
-          if (n2_ok) p[n2] = u[j];
+      const uint32_t lane_addr = tmem_base + b * acc_cols + ((uint32_t)(q * 32) << 16);
+      for (int c0 = 0; c0 < a.n_tile; c0 += 16) {
+        if (c0 >= t.rows_here) break;                // uniform over the warp
+        float g[16], u[16];
+        if (t.n_steps > 0) {
+          tmem_ld16(lane_addr + c0, g);
+          if (two) tmem_ld16(lane_addr + a.n_tile + c0, u);
         } else {
-          float v = a.swiglu ? silu_mul(g[j], u[j]) : g[j];
-          st_dt(a.out, a.out_dt, t * a.ldo + n, v + bias);
-          if (n2_ok) st_dt(a.out, a.out_dt, t * a.ldo + n2, u[j] + bias2);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) g[j] = u[j] = 0.f;
+        }
+        if (!n_ok) continue;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          if (c0 + j >= t.rows_here) break;
+          const size_t row = (size_t)(t.row0 + c0 + j);
+          if (a.splits > 1) {
+            const int width = a.swiglu ? 2 * a.N : a.N;
+            float* p = a.partial + ((size_t)t.z * a.M_tok + row) * width;
+            p[n] = g[j];
+            if (a.swiglu) p[a.N + n] = u[j];
+            if (n2_ok) p[n2] = u[j];
+          } else {
+            float v = a.swiglu ? silu_mul(g[j], u[j]) : g[j];
+            st_dt(a.out, a.out_dt, row * a.ldo + n, v + bias);
+            if (n2_ok) st_dt(a.out, a.out_dt, row * a.ldo + n2, u[j] + bias2);
+          }
         }
       }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[b]);   // this warp has read all it needs from the buffer
     }
   }
   tc_fence_before();
@@ -417,30 +462,43 @@ NV_API int nv_tc_gemm(const void* X, long long ldx, int M_tok, const void* W, in
   a.w_per_cta = a.dual ? 2 * TILE_W : TILE_W;
   const int two = (swiglu || a.dual) ? 1 : 0;
   const int stage_bytes = TILE_W * 128 * (two ? 2 : 1) + n_tile * 128;
+  a.n_blocks = (N + a.w_per_cta - 1) / a.w_per_cta;
+  const int acc_cols = n_tile * (two ? 2 : 1);
+  a.acc_bufs = acc_cols <= 256 ? 2 : 1;
+  a.tmem_cols = pow2_at_least(acc_cols * a.acc_bufs);
   // Small stages (few tokens): keep a CTA under half of the shared memory so that two CTAs share an SM and
-  // one's start-up and epilogue overlap the other's streaming.  Large stages: one CTA per SM, deep ring.
-  const int budget = stage_bytes * 4 <= 104 * 1024 ? 104 * 1024 : 200 * 1024;
+  // one's start-up and epilogue overlap the other's streaming.  Large stages, or more than half of the
+  // TMEM columns: one CTA per SM, deep ring.
+  const bool pair = stage_bytes * 4 <= 104 * 1024 && a.tmem_cols <= 256;
+  const int budget = pair ? 104 * 1024 : 200 * 1024;
   int stages = budget / stage_bytes;
   if (stages > MAX_STAGES) stages = MAX_STAGES;
-  if (stages > a.k_steps_per_split) stages = a.k_steps_per_split < 2 ? 2 : a.k_steps_per_split;
+  if (stages < 2) return NV_ERR_UNSUPPORTED;
   a.stages = stages;
-  a.tmem_cols = pow2_at_least(n_tile * (two ? 2 : 1));
-  const size_t smem = (size_t)stages * stage_bytes + 1024;
+  size_t smem = (size_t)stages * stage_bytes + 1024;
+  if (!pair && smem < 120 * 1024) smem = 120 * 1024;   // more than half an SM's shared memory: no second CTA
 
   static std::once_flag once;
   static cudaError_t attr_rc = cudaSuccess;
+  static int num_sms = 0;
   std::call_once(once, [] {
     attr_rc = cudaFuncSetAttribute(tc_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+    int dev = 0;
+    if (attr_rc == cudaSuccess) attr_rc = cudaGetDevice(&dev);
+    if (attr_rc == cudaSuccess) attr_rc = cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
   });
   if (attr_rc != cudaSuccess) return (int)attr_rc;
 
-  dim3 grid((N + a.w_per_cta - 1) / a.w_per_cta, grouped ? max_tiles : (M_tok + n_tile - 1) / n_tile, a.splits);
+  const long long y_tiles = grouped ? max_tiles : (M_tok + n_tile - 1) / n_tile;
+  const long long total = (long long)a.n_blocks * y_tiles * a.splits;     // an upper bound when grouped
+  const long long resident = (long long)num_sms * (pair ? 2 : 1);
+  dim3 grid((unsigned)(total < resident ? total : resident));
   tc_gemm_kernel<<<grid, NUM_THREADS, smem, stream>>>(tm_w, tm_x, a);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
   if (a.splits > 1) {
-    long long total = (long long)M_tok * N;
-    tc_gemm_finish_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(scratch, a.splits, M_tok, N, a.swiglu,
+    const long long outputs = (long long)M_tok * N;
+    tc_gemm_finish_kernel<<<(unsigned)((outputs + 255) / 256), 256, 0, stream>>>(scratch, a.splits, M_tok, N, a.swiglu,
                                                                               bias, bias_dt, out, out_dt, ldo);
   }
   NV_RETURN_LAST();
