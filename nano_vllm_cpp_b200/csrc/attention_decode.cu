@@ -16,10 +16,13 @@
 // Reference twin: nv_paged_attention_plain.  (The reference's kernel: src/hip_ops.hip:473-551.)
 #include "pipeline.cuh"
 
+#include <cstdlib>
+
 namespace {
 
 constexpr int WARPS = 4;                // consumer warps; one more warp produces
-constexpr int MAX_STAGES = 8;
+constexpr int MAX_STAGES = 16;
+constexpr int BT_CACHE = 1024;           // block-table entries of a split kept in shared memory
 constexpr int LPK = 8;                 // lanes per key
 constexpr int KEYS_PER_WARP = 32 / LPK;
 constexpr int KEYS_PER_PASS = WARPS * KEYS_PER_WARP;   // 16
@@ -71,6 +74,7 @@ __global__ void __launch_bounds__((WARPS + 1) * 32) attention_decode_kernel(DecA
   __shared__ float mrg_o[WARPS][GB][256];
   __shared__ float mrg_m[WARPS][GB], mrg_l[WARPS][GB];
   __shared__ uint64_t full_bar[MAX_STAGES], empty_bar[MAX_STAGES];
+  __shared__ int bt_s[BT_CACHE];          // this split's block-table entries, fetched once up front
 
   const int r = blockIdx.x;
   const int t = a.rows ? a.rows[r] : r;
@@ -104,9 +108,10 @@ __global__ void __launch_bounds__((WARPS + 1) * 32) attention_decode_kernel(DecA
     int g = i / D, d = i % D;
     q_s[g][d] = ld_dt(a.qkv, a.q_dt, (size_t)t * a.q_stride + (size_t)(kvh * G + g0 + g) * D + d) * a.scale;
   }
-  __syncthreads();
-
   const int* bt = a.block_table + (size_t)a.row_entry[t] * a.max_blocks;
+  // the producer must not wait for a block-table entry per page: that load's latency would bound the stream
+  for (int i = threadIdx.x; i < min(n_pages, BT_CACHE); i += (WARPS + 1) * 32) bt_s[i] = bt[pb + i];
+  __syncthreads();
 
   if (warp == WARPS) {
     // ---------------------------------------------------------------- producer: one lane issues the copies
@@ -114,7 +119,7 @@ __global__ void __launch_bounds__((WARPS + 1) * 32) attention_decode_kernel(DecA
       for (int i = 0; i < n_pages; ++i) {
         const int s = i % a.stages;
         mbar_wait(&empty_bar[s], ((i / a.stages) & 1) ^ 1, a.err, 0x7101);
-        const int blk = bt[pb + i];
+        const int blk = i < BT_CACHE ? bt_s[i] : bt[pb + i];
         uint8_t* st = dec_smem + (size_t)s * 2 * chunk_bytes;
         if (blk < 0) {                       // a page that should be there is not: report, let the consumers pass
           if (a.err) atomicExch(a.err, 1 + t);
@@ -138,6 +143,16 @@ __global__ void __launch_bounds__((WARPS + 1) * 32) attention_decode_kernel(DecA
       for (int c = 0; c < CPL; ++c)
 #pragma unroll
         for (int e = 0; e < 8; ++e) acc[g][c][e] = 0.f;
+    }
+    // with one query head per block its chunks of q live in registers; otherwise they are read from shared memory
+    float qr[GB == 1 ? CPL : 1][8];
+    if (GB == 1) {
+#pragma unroll
+      for (int c = 0; c < CPL; ++c) {
+        const int ch = li + c * LPK;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) qr[c][e] = ch < chunks ? q_s[0][ch * 8 + e] : 0.f;
+      }
     }
     for (int i = 0; i < n_pages; ++i) {
       const int s = i % a.stages;
@@ -166,7 +181,10 @@ __global__ void __launch_bounds__((WARPS + 1) * 32) attention_decode_kernel(DecA
 #pragma unroll
           for (int c = 0; c < CPL; ++c) {
             const int ch = li + c * LPK;
-            if (ch < chunks) {
+            if (GB == 1) {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) sc = fmaf(qr[c][e], kf[c][e], sc);     // kf is zero beyond the head
+            } else if (ch < chunks) {
               const float4 qa = *(const float4*)&q_s[g][ch * 8], qb = *(const float4*)&q_s[g][ch * 8 + 4];
               sc = fmaf(qa.x, kf[c][0], sc); sc = fmaf(qa.y, kf[c][1], sc); sc = fmaf(qa.z, kf[c][2], sc);
               sc = fmaf(qa.w, kf[c][3], sc); sc = fmaf(qb.x, kf[c][4], sc); sc = fmaf(qb.y, kf[c][5], sc);
@@ -177,14 +195,21 @@ __global__ void __launch_bounds__((WARPS + 1) * 32) attention_decode_kernel(DecA
           sc += __shfl_xor_sync(0xffffffffu, sc, 2);
           sc += __shfl_xor_sync(0xffffffffu, sc, 4);
           if (live) {
-            const float m_new = fmaxf(m[g], sc);
-            const float alpha = __expf(m[g] - m_new), p = __expf(sc - m_new);
-            l[g] = l[g] * alpha + p;
-            m[g] = m_new;
+            if (sc > m[g]) {                       // a new maximum (rare after the first keys): rescale what was summed
+              const float alpha = __expf(m[g] - sc);
+              l[g] *= alpha;
+#pragma unroll
+              for (int c = 0; c < CPL; ++c)
+#pragma unroll
+                for (int e = 0; e < 8; ++e) acc[g][c][e] *= alpha;
+              m[g] = sc;
+            }
+            const float p = __expf(sc - m[g]);
+            l[g] += p;
 #pragma unroll
             for (int c = 0; c < CPL; ++c)
 #pragma unroll
-              for (int e = 0; e < 8; ++e) acc[g][c][e] = fmaf(p, vf[c][e], acc[g][c][e] * alpha);
+              for (int e = 0; e < 8; ++e) acc[g][c][e] = fmaf(p, vf[c][e], acc[g][c][e]);
           }
         }
       }
@@ -254,6 +279,263 @@ __global__ void __launch_bounds__((WARPS + 1) * 32) attention_decode_kernel(DecA
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// The tensor-core form, for bfloat16 caches whose head dimension is a multiple of 64.
+//
+// The lane-per-chunk kernel above spends a few hundred instructions per key and page, and on this
+// GPU the instruction issue rate, not memory, then bounds it at about half of the memory speed.
+// Here a warp takes a whole page: S = Q K^T and O += P V are m16n8k16 bf16 MMAs whose 16 rows are
+// the query heads that share the kv head (rows beyond them are zero), about ninety instructions per
+// page.  Pages arrive by tiled TMA copies (boxes of `page` keys x 64 elements, 128-byte swizzle) so
+// that ldmatrix reads them without bank conflicts; the ring, the split over keys and the merges are
+// those of the kernel above.
+__device__ __forceinline__ void ldsm4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *(uint32_t*)&v;
+}
+
+constexpr int TC_ROWS = 16;      // query heads per block (rows of the MMA)
+
+// D: head dimension, a multiple of 64 (compile time: it sizes the fragments).
+template <int D>
+__global__ void __launch_bounds__((WARPS + 1) * 32, D <= 128 ? 3 : 1)
+attention_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                           DecArgs a) {
+  extern __shared__ __align__(1024) uint8_t dec_smem_raw[];
+  constexpr int QLD = D + 8;                         // padded row of q in shared memory
+  __shared__ __align__(16) bf16 q_s[TC_ROWS * QLD];
+  __shared__ uint64_t full_bar[MAX_STAGES], empty_bar[MAX_STAGES];
+  __shared__ int bt_s[BT_CACHE];
+  __shared__ float mrg_m[WARPS][TC_ROWS], mrg_l[WARPS][TC_ROWS];
+
+  uint8_t* dec_smem = (uint8_t*)(((uintptr_t)dec_smem_raw + 1023) & ~(uintptr_t)1023);
+  const int r = blockIdx.x;
+  const int t = a.rows ? a.rows[r] : r;
+  const int G = a.Hq / a.Hkv;
+  const int groups = (G + TC_ROWS - 1) / TC_ROWS;
+  const int kvh = blockIdx.y / groups;
+  const int g0 = (blockIdx.y % groups) * TC_ROWS;
+  const int ng = min(TC_ROWS, G - g0);
+  const int split = blockIdx.z;
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+
+  const int n = a.positions[t] + 1;
+  const int lo = a.window > 0 ? max(0, n - a.window) : 0;
+  const int p_lo = lo / a.page, p_hi = (n - 1) / a.page + 1;
+  const int per = (p_hi - p_lo + a.splits - 1) / a.splits;
+  const int pb = p_lo + split * per;
+  const int n_pages = max(0, min(p_hi, pb + per) - pb);
+  const uint32_t box_bytes = (uint32_t)a.page * 128;           // one box: `page` keys x 64 elements
+  const uint32_t half_stage = box_bytes * (D / 64);            // keys of one page; values follow
+  const uint32_t stage_bytes = 2 * half_stage;
+
+  if (threadIdx.x == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&tm_k) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&tm_v) : "memory");
+    for (int s = 0; s < a.stages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);                   // a stage is read by one warp
+    }
+    mbar_fence_init();
+  }
+  for (int i = threadIdx.x; i < TC_ROWS * D; i += (WARPS + 1) * 32) {
+    const int g = i / D, d = i % D;
+    float v = 0.f;
+    if (g < ng) v = ld_dt(a.qkv, a.q_dt, (size_t)t * a.q_stride + (size_t)(kvh * G + g0 + g) * D + d);
+    q_s[g * QLD + d] = __float2bfloat16_rn(v);
+  }
+  const int* bt = a.block_table + (size_t)a.row_entry[t] * a.max_blocks;
+  for (int i = threadIdx.x; i < min(n_pages, BT_CACHE); i += (WARPS + 1) * 32) bt_s[i] = bt[pb + i];
+  __syncthreads();
+
+  const int g = lane / 4, tq = lane % 4;
+  float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
+  float o[D / 8][4];
+
+  if (warp == WARPS) {
+    // ---------------------------------------------------------------- producer
+    if (lane == 0) {
+      for (int i = 0; i < n_pages; ++i) {
+        const int s = i % a.stages;
+        mbar_wait(&empty_bar[s], ((i / a.stages) & 1) ^ 1, a.err, 0x7111);
+        const int blk = i < BT_CACHE ? bt_s[i] : bt[pb + i];
+        uint8_t* st = dec_smem + (size_t)s * stage_bytes;
+        if (blk < 0) {
+          if (a.err) atomicExch(a.err, 1 + t);
+          mbar_arrive(&full_bar[s]);
+          continue;
+        }
+        const int row = (blk * a.Hkv + kvh) * a.page;          // first row of the page in the [rows, D] view
+        mbar_expect_tx(&full_bar[s], stage_bytes);
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c) {
+          tma_load_2d(st + c * box_bytes, &tm_k, &full_bar[s], c * 64, row);
+          tma_load_2d(st + half_stage + c * box_bytes, &tm_v, &full_bar[s], c * 64, row);
+        }
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- consumers: warp w takes pages w, w+4, ...
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    uint32_t qa[D / 16][4];
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk)
+      ldsm4(smem_u32(q_s + ((lane % 8) + 8 * ((lane / 8) % 2)) * QLD + kk * 16 + 8 * (lane / 16)), qa[kk][0], qa[kk][1],
+            qa[kk][2], qa[kk][3]);
+    for (int i = warp; i < n_pages; i += WARPS) {
+      const int s = i % a.stages;
+      mbar_wait(&full_bar[s], (i / a.stages) & 1, a.err, 0x7112);
+      const uint32_t kbase = smem_u32(dec_smem + (size_t)s * stage_bytes);
+      const uint32_t vbase = kbase + half_stage;
+      const int j_page = (pb + i) * a.page;
+      for (int kb = 0; kb < a.page / 16; ++kb) {
+        const int j0 = j_page + kb * 16;
+        if (j0 >= n || j0 + 15 < lo) continue;                 // uniform: no visible key in these 16
+        float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+        {
+          const int key = kb * 16 + (lane % 8) + 8 * (lane / 16);
+          const uint32_t rowaddr = kbase + key * 128;
+          const int half8 = (lane / 8) % 2;                    // which 8-element half of the 16-wide k block
+          // fragments are fetched four k-blocks at a time before their products, so that the latency of
+          // ldmatrix is paid once per batch and not once per product
+#pragma unroll
+          for (int k4 = 0; k4 < D / 64; ++k4) {
+            uint32_t b[4][4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int chunk = u * 2 + half8;                  // 16-byte chunk inside the 128-byte row of box k4
+              ldsm4(rowaddr + k4 * box_bytes + ((chunk ^ (key & 7)) << 4), b[u][0], b[u][1], b[u][2], b[u][3]);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              mma16816(s0, qa[k4 * 4 + u], b[u][0], b[u][1]);
+              mma16816(s1, qa[k4 * 4 + u], b[u][2], b[u][3]);
+            }
+          }
+        }
+        // mask keys outside [lo, n): all rows of a decode step share the range
+        if (j0 < lo || j0 + 15 >= n) {
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            const int ja = j0 + 2 * tq + c, jb = ja + 8;
+            if (ja < lo || ja >= n) s0[c] = s0[2 + c] = -INFINITY;
+            if (jb < lo || jb >= n) s1[c] = s1[2 + c] = -INFINITY;
+          }
+        }
+        float mx_lo = fmaxf(fmaxf(s0[0], s0[1]), fmaxf(s1[0], s1[1]));
+        float mx_hi = fmaxf(fmaxf(s0[2], s0[3]), fmaxf(s1[2], s1[3]));
+        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+        const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+        const float ms_lo = mn_lo == -INFINITY ? 0.f : mn_lo * a.scale, ms_hi = mn_hi == -INFINITY ? 0.f : mn_hi * a.scale;
+        const float al_lo = exp2f(m_lo * a.scale - ms_lo), al_hi = exp2f(m_hi * a.scale - ms_hi);
+        m_lo = mn_lo;
+        m_hi = mn_hi;
+        s0[0] = exp2f(s0[0] * a.scale - ms_lo); s0[1] = exp2f(s0[1] * a.scale - ms_lo);
+        s1[0] = exp2f(s1[0] * a.scale - ms_lo); s1[1] = exp2f(s1[1] * a.scale - ms_lo);
+        s0[2] = exp2f(s0[2] * a.scale - ms_hi); s0[3] = exp2f(s0[3] * a.scale - ms_hi);
+        s1[2] = exp2f(s1[2] * a.scale - ms_hi); s1[3] = exp2f(s1[3] * a.scale - ms_hi);
+        l_lo = l_lo * al_lo + (s0[0] + s0[1] + s1[0] + s1[1]);
+        l_hi = l_hi * al_hi + (s0[2] + s0[3] + s1[2] + s1[3]);
+        if (al_lo != 1.f || al_hi != 1.f) {
+#pragma unroll
+          for (int i2 = 0; i2 < D / 8; ++i2) {
+            o[i2][0] *= al_lo; o[i2][1] *= al_lo; o[i2][2] *= al_hi; o[i2][3] *= al_hi;
+          }
+        }
+        uint32_t pa[4] = {pack_bf16(s0[0], s0[1]), pack_bf16(s0[2], s0[3]), pack_bf16(s1[0], s1[1]),
+                          pack_bf16(s1[2], s1[3])};
+        {
+          const int key = kb * 16 + (lane % 8) + 8 * ((lane / 8) % 2);
+          const uint32_t rowaddr = vbase + key * 128;
+          const int half8 = lane / 16;
+#pragma unroll
+          for (int d4 = 0; d4 < D / 64; ++d4) {
+            uint32_t b[4][4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int chunk = u * 2 + half8;
+              ldsm4_t(rowaddr + d4 * box_bytes + ((chunk ^ (key & 7)) << 4), b[u][0], b[u][1], b[u][2], b[u][3]);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              mma16816(o[2 * (d4 * 4 + u)], pa, b[u][0], b[u][1]);
+              mma16816(o[2 * (d4 * 4 + u) + 1], pa, b[u][2], b[u][3]);
+            }
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty_bar[s]);
+    }
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+  }
+  __syncthreads();          // every page has been read: the ring's memory is free for the merge
+  float* mrg_o = (float*)dec_smem;                              // [WARPS][ng][D]
+  if (warp < WARPS) {
+    if (tq == 0) {
+      if (g < ng) { mrg_m[warp][g] = m_lo; mrg_l[warp][g] = l_lo; }
+      if (g + 8 < ng) { mrg_m[warp][g + 8] = m_hi; mrg_l[warp][g + 8] = l_hi; }
+    }
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      const int d = i * 8 + 2 * tq;
+      if (g < ng) { mrg_o[((size_t)warp * ng + g) * D + d] = o[i][0]; mrg_o[((size_t)warp * ng + g) * D + d + 1] = o[i][1]; }
+      if (g + 8 < ng) {
+        mrg_o[((size_t)warp * ng + g + 8) * D + d] = o[i][2];
+        mrg_o[((size_t)warp * ng + g + 8) * D + d + 1] = o[i][3];
+      }
+    }
+  }
+  __syncthreads();
+  // merge the warps (fixed order) and write this split's result; scores are in log2 units here
+  for (int i = threadIdx.x; i < ng * D; i += (WARPS + 1) * 32) {
+    const int gg = i / D, d = i % D;
+    float mm = mrg_m[0][gg];
+#pragma unroll
+    for (int w = 1; w < WARPS; ++w) mm = fmaxf(mm, mrg_m[w][gg]);
+    const float mms = mm == -INFINITY ? 0.f : mm * a.scale;
+    float ll = 0.f, ov = 0.f;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) {
+      const float sc = exp2f(mrg_m[w][gg] * a.scale - mms);
+      ll = fmaf(mrg_l[w][gg], sc, ll);
+      ov = fmaf(mrg_o[((size_t)w * ng + gg) * D + d], sc, ov);
+    }
+    const int h = kvh * G + g0 + gg;
+    if (a.splits == 1) {
+      st_dt(a.out, a.out_dt, ((size_t)t * a.Hq + h) * D + d, ll > 0.f ? ov / ll : 0.f);
+    } else {
+      const size_t pi = ((size_t)r * a.Hq + h) * a.splits + split;
+      a.part_o[pi * D + d] = ov;
+      if (d == 0) {                                             // the merge kernel works in natural-log units
+        a.part_ml[pi * 2] = mm == -INFINITY ? -1e30f : mms * 0.6931471805599453f;
+        a.part_ml[pi * 2 + 1] = ll;
+      }
+    }
+  }
+}
+
 // Combines the splits of one (row, head) in split order.
 __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                               const int* __restrict__ rows, void* __restrict__ out, int out_dt,
@@ -292,10 +574,36 @@ int launch_decode(const DecArgs& a, int R, int G, size_t smem, cudaStream_t s) {
   return G == 1 ? launch_decode_g<TC, CPL, 1>(a, R, G, smem, s) : launch_decode_g<TC, CPL, 4>(a, R, G, smem, s);
 }
 
+template <int D>
+int launch_decode_tc(DecArgs a, int R, const void* kc, const void* vc, int num_pages, float scale, cudaStream_t s) {
+  const int G = a.Hq / a.Hkv;
+  CUtensorMap tm_k, tm_v;
+  const long long rows = (long long)num_pages * a.Hkv * a.page;
+  int rc = nv_tensor_map_bf16(kc, rows, D, D, a.page, &tm_k);
+  if (rc) return rc;
+  rc = nv_tensor_map_bf16(vc, rows, D, D, a.page, &tm_v);
+  if (rc) return rc;
+  a.scale = scale * 1.4426950408889634f;            // the kernel works in log2 units
+  const size_t ring = (size_t)a.stages * 2 * a.page * D * 2;
+  const size_t merge = (size_t)WARPS * TC_ROWS * D * sizeof(float);
+  const size_t smem = (ring > merge ? ring : merge) + 1024;
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         160 * 1024);
+    if (e != cudaSuccess) return (int)e;
+    attr_done = true;
+  }
+  dim3 grid(R, a.Hkv * ((G + TC_ROWS - 1) / TC_ROWS), a.splits);
+  attention_decode_tc_kernel<D><<<grid, (WARPS + 1) * 32, smem, s>>>(tm_k, tm_v, a);
+  NV_RETURN_LAST();
+}
+
 // Stages of the page ring for a page of `page` keys of `D` elements of `esize` bytes: as many as fit in
 // 64 KB (two CTAs per SM and more), at least 2 within 160 KB, else 0 (refused).
 int decode_stages(int page, int D, int esize) {
   const long long stage = 2LL * page * D * esize;
+  if (const char* e = getenv("NV_DEC_STAGES")) return atoi(e);      // experiments only
   long long s = (64 * 1024) / stage;
   if (s >= 2) return (int)(s > MAX_STAGES ? MAX_STAGES : s);
   return 2 * stage <= 160 * 1024 ? 2 : 0;
@@ -317,7 +625,7 @@ NV_API int nv_attention_decode_usable(int D, int page, int cache_dt) {
 // Number of splits that fills `num_sms` multiprocessors a few times over for this many rows.
 NV_API int nv_attention_decode_splits(int rows, int Hq, int Hkv, int max_context, int num_sms) {
   int G = Hq / Hkv;
-  int blocks = rows * Hkv * (G == 1 ? 1 : (G + 3) / 4);
+  int blocks = rows * Hkv * ((G + 15) / 16);
   int want = (4 * num_sms + blocks - 1) / blocks;
   int most = (max_context + 255) / 256;          // at least 256 keys per split
   int s = want < most ? want : most;
@@ -328,7 +636,7 @@ NV_API int nv_attention_decode_splits(int rows, int Hq, int Hkv, int max_context
 NV_API int nv_attention_decode(const void* qkv, int q_dt, int q_stride, const void* kc, const void* vc, int cache_dt,
                                const int* block_table, int max_blocks, const int* row_entry, const int* positions,
                                const int* rows, int R, float scale, int window, void* out, int out_dt, int Hq,
-                               int Hkv, int D, int page, int splits, float* scratch, int* err,
+                               int Hkv, int D, int page, int num_pages, int splits, float* scratch, int* err,
                                cudaStream_t stream) {
   if (!dt_ok(q_dt) || !dt_ok(cache_dt) || !dt_ok(out_dt)) return NV_ERR_BAD_DTYPE;
   if (D <= 0 || D > 256 || D % 8 || Hkv <= 0 || Hq % Hkv || page % 16) return NV_ERR_UNSUPPORTED;
@@ -350,7 +658,19 @@ NV_API int nv_attention_decode(const void* qkv, int q_dt, int q_stride, const vo
   const size_t smem = (size_t)stages * 2 * page * D * esize;
   const int G = Hq / Hkv;
   int rc;
-  if (cache_dt == NV_DT_BF16) {
+  // The tensor-core form gives every stage of the ring to one warp (stage s to warp s % 4), so that the waits
+  // of a warp on a barrier are for consecutive uses of it; that needs a ring of a multiple of four stages.
+  int tc_stages = stages / WARPS * WARPS;
+  if (tc_stages > WARPS && (long long)WARPS * 2 * page * D * esize >= 32 * 1024) tc_stages = WARPS;   // more CTAs per SM beat a deeper ring
+  if (cache_dt == NV_DT_BF16 && D % 64 == 0 && page <= 256 && num_pages > 0 && tc_stages >= WARPS &&
+      !getenv("NV_DECODE_ATTENTION_SIMT")) {
+    a.stages = tc_stages;
+    // tensor-core form (a page of keys per warp); its blocks take up to 16 query heads of a kv head
+    rc = D == 64 ? launch_decode_tc<64>(a, R, kc, vc, num_pages, scale, stream)
+       : D == 128 ? launch_decode_tc<128>(a, R, kc, vc, num_pages, scale, stream)
+       : D == 192 ? launch_decode_tc<192>(a, R, kc, vc, num_pages, scale, stream)
+                  : launch_decode_tc<256>(a, R, kc, vc, num_pages, scale, stream);
+  } else if (cache_dt == NV_DT_BF16) {
     rc = D <= 64 ? launch_decode<bf16, 1>(a, R, G, smem, stream)
                  : (D <= 128 ? launch_decode<bf16, 2>(a, R, G, smem, stream)
                              : launch_decode<bf16, 4>(a, R, G, smem, stream));
@@ -395,8 +715,8 @@ NV_API int nv_attention_decode_noalloc_max_rows(int Hq, int D, int splits) {
 NV_API int nv_attention_decode_noalloc(const void* qkv, int q_dt, int q_stride, const void* kc, const void* vc,
                                        int cache_dt, const int* block_table, int max_blocks, const int* row_entry,
                                        const int* positions, const int* rows, int R, float scale, int window,
-                                       void* out, int out_dt, int Hq, int Hkv, int D, int page, int splits,
-                                       cudaStream_t stream) {
+                                       void* out, int out_dt, int Hq, int Hkv, int D, int page, int num_pages,
+                                       int splits, cudaStream_t stream) {
   if (splits < 1) splits = 1;
   if (nv_attention_decode_scratch_floats(R, Hq, D, splits) > (long long)NV_NOALLOC_SCRATCH_FLOATS)
     return NV_ERR_NOALLOC_TOO_LARGE;
@@ -415,8 +735,8 @@ NV_API int nv_attention_decode_noalloc(const void* qkv, int q_dt, int q_stride, 
     g_noalloc_ptr[dev] = p;
   }
   return nv_attention_decode(qkv, q_dt, q_stride, kc, vc, cache_dt, block_table, max_blocks, row_entry, positions,
-                             rows, R, scale, window, out, out_dt, Hq, Hkv, D, page, splits, g_noalloc_ptr[dev],
-                             g_noalloc_err_ptr[dev], stream);
+                             rows, R, scale, window, out, out_dt, Hq, Hkv, D, page, num_pages, splits,
+                             g_noalloc_ptr[dev], g_noalloc_err_ptr[dev], stream);
 }
 
 NV_API int nv_attention_decode_noalloc_status(void) {

@@ -31,13 +31,14 @@
 extern "C" {
 #endif
 
-// Same arguments and result as nv_attention_decode without `scratch`; `splits` >= 1 as chosen by the caller
+// Same arguments and result as nv_attention_decode without `scratch` and the error flag (`num_pages`: pages in the
+// caches, i.e. their first dimension); `splits` >= 1 as chosen by the caller
 // (nv_attention_decode_splits gives the library's own choice).  Returns 0, a negative NV_ERR_* code or a
 // cudaError_t.
 int nv_attention_decode_noalloc(const void* qkv, int q_dt, int q_stride, const void* kc, const void* vc, int cache_dt,
                                 const int* block_table, int max_blocks, const int* row_entry, const int* positions,
                                 const int* rows, int R, float scale, int window, void* out, int out_dt, int Hq,
-                                int Hkv, int D, int page, int splits, cudaStream_t stream);
+                                int Hkv, int D, int page, int num_pages, int splits, cudaStream_t stream);
 
 // Largest number of rows one call can take for these sizes (0 if not even one fits).
 int nv_attention_decode_noalloc_max_rows(int Hq, int D, int splits);

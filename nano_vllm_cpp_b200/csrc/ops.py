@@ -214,8 +214,9 @@ def attention_decode(qkv, k_cache, v_cache, block_table, row_entry, positions, s
     _check(L.nv_attention_decode(_p(qkv), c_int(dt(qkv)), c_int(qkv.shape[1]), _p(k_cache), _p(v_cache),
                                  c_int(dt(k_cache)), _p(block_table), c_int(block_table.shape[1]), _p(row_entry),
                                  _p(positions), _p(rows), c_int(R), c_float(scale), c_int(window), _p(out),
-                                 c_int(dt(out)), c_int(Hq), c_int(Hkv), c_int(D), c_int(page), c_int(splits),
-                                 _p(scratch), _p(err.t if err is not None else _global_err().t), _stream()),
+                                 c_int(dt(out)), c_int(Hq), c_int(Hkv), c_int(D), c_int(page), c_int(k_cache.shape[0]),
+                                 c_int(splits), _p(scratch), _p(err.t if err is not None else _global_err().t),
+                                 _stream()),
            "attention_decode")
 
 

@@ -5,6 +5,8 @@
 
 #include "common.cuh"
 
+#include <cuda.h>
+
 constexpr long long NV_WAIT_CYCLES = 4000000000LL;   // ~2 s at 2 GHz
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -50,3 +52,15 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint
                ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
                : "memory");
 }
+
+// Tiled TMA load of one box into shared memory (128-byte swizzle as encoded in the map).
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* tm, uint64_t* bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"((uint64_t)tm), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+      : "memory");
+}
+
+// Host: tensor map of a row-major bf16 matrix [rows, cols] (row stride ld elements), boxes of box_rows x 64
+// elements, 128-byte swizzle, zero fill outside; cached.  Defined in tc_gemm.cu.
+int nv_tensor_map_bf16(const void* ptr, long long rows, long long cols, long long ld, int box_rows, CUtensorMap* out);

@@ -59,13 +59,6 @@ struct TcArgs {
 };
 
 // ------------------------------------------------------------------ PTX wrappers (mbarriers: pipeline.cuh)
-__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* tm, uint64_t* bar, int c0, int c1) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(smem_u32(smem_dst)), "l"((uint64_t)tm), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
-      : "memory");
-}
-
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
@@ -363,9 +356,11 @@ struct MapKeyHash {
   }
 };
 
+}  // namespace
+
 // A row-major bf16 matrix [rows, cols] with row stride ld elements; boxes of box_rows x 64, 128-byte swizzle,
-// zero fill outside.
-int get_map(const void* ptr, long long rows, long long cols, long long ld, int box_rows, CUtensorMap* out) {
+// zero fill outside.  Cached by (pointer, shape, box).  Declared in pipeline.cuh for the other kernels.
+int nv_tensor_map_bf16(const void* ptr, long long rows, long long cols, long long ld, int box_rows, CUtensorMap* out) {
   static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
   static std::mutex mu;
   MapKey key{ptr, rows, cols, ld, box_rows};
@@ -390,6 +385,12 @@ int get_map(const void* ptr, long long rows, long long cols, long long ld, int b
   cache[key] = m;
   *out = m;
   return NV_OK;
+}
+
+namespace {
+
+int get_map(const void* ptr, long long rows, long long cols, long long ld, int box_rows, CUtensorMap* out) {
+  return nv_tensor_map_bf16(ptr, rows, cols, ld, box_rows, out);
 }
 
 int pow2_at_least(int v) {

@@ -42,7 +42,7 @@ def _call(lib, name, qkv, kc, vc, bt, ent, pos, out, Hq, Hkv, D, page, splits, s
     args = [c_void_p(qkv.data_ptr()), c_int(1), c_int(qkv.shape[1]), c_void_p(kc.data_ptr()), c_void_p(vc.data_ptr()),
             c_int(1), c_void_p(bt.data_ptr()), c_int(bt.shape[1]), c_void_p(ent.data_ptr()), c_void_p(pos.data_ptr()),
             c_void_p(0), c_int(qkv.shape[0]), c_float(1.0 / math.sqrt(D)), c_int(0), c_void_p(out.data_ptr()), c_int(1),
-            c_int(Hq), c_int(Hkv), c_int(D), c_int(page), c_int(splits)]
+            c_int(Hq), c_int(Hkv), c_int(D), c_int(page), c_int(kc.shape[0]), c_int(splits)]
     if scratch is not None:
         args.append(c_void_p(scratch.data_ptr()))
         args.append(c_void_p(0))            # the ordinary entry point also takes an error flag; none here
