@@ -33,7 +33,7 @@ def small_linear(ctx, a32, w):
     out = torch.empty((a32.shape[0], w.shape[0]), dtype=torch.float32, device=a32.device)
     if a32.shape[0]:
         # float32 runs keep one kernel whatever the batch is; bfloat16 runs take the many-rows kernel for prompts
-        ops.rowdot(a32, w, out, wide=ctx.fast_kernels and ctx.act_dtype == torch.bfloat16 and a32.shape[0] >= 64)
+        ops.rowdot(a32, w, out, wide=ctx.fast_kernels and ctx.act_dtype == torch.bfloat16 and a32.shape[0] >= 256)
     return out
 
 
