@@ -83,19 +83,34 @@ __device__ __forceinline__ void align_block(const int* __restrict__ idx, int TK,
     atomicAdd(&cnt[e], 1);
   }
   __syncthreads();
-  if (tid == 0) {                           // E is small: a serial scan over shared memory
-    int off = 0, nt = 0, nt2 = 0;
-    for (int e = 0; e < E; ++e) {
-      cur[e] = off;
-      tbase[e] = nt;
-      tbase2[e] = nt2;
-      off += cnt[e];
-      nt += (cnt[e] + tile_m - 1) / tile_m;
-      if (tile_m2) nt2 += (cnt[e] + tile_m2 - 1) / tile_m2;
+  if (tid < 32) {                           // warp 0: exclusive prefix sums over the experts, 32 at a time
+    int carry_c = 0, carry_t = 0, carry_t2 = 0;
+    for (int base = 0; base < E; base += 32) {
+      const int e = base + tid;
+      const int c = e < E ? cnt[e] : 0;
+      const int tl = (c + tile_m - 1) / tile_m;
+      const int tl2 = tile_m2 ? (c + tile_m2 - 1) / tile_m2 : 0;
+      int sc = c, st = tl, st2 = tl2;       // inclusive scans
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int uc = __shfl_up_sync(0xffffffffu, sc, o), ut = __shfl_up_sync(0xffffffffu, st, o),
+                  ut2 = __shfl_up_sync(0xffffffffu, st2, o);
+        if (tid >= o) { sc += uc; st += ut; st2 += ut2; }
+      }
+      if (e < E) {
+        cur[e] = carry_c + sc - c;
+        tbase[e] = carry_t + st - tl;
+        tbase2[e] = carry_t2 + st2 - tl2;
+      }
+      carry_c += __shfl_sync(0xffffffffu, sc, 31);
+      carry_t += __shfl_sync(0xffffffffu, st, 31);
+      carry_t2 += __shfl_sync(0xffffffffu, st2, 31);
     }
-    offsets[E] = off;
-    *num_tiles = nt;
-    if (tile_m2) *num_tiles2 = nt2;
+    if (tid == 0) {
+      offsets[E] = carry_c;
+      *num_tiles = carry_t;
+      if (tile_m2) *num_tiles2 = carry_t2;
+    }
   }
   __syncthreads();
   for (int e = tid; e < E; e += nthr) {

@@ -141,10 +141,22 @@ __global__ void __launch_bounds__(1024) moe_route_small_kernel(
   if (!x_sorted) return;
   __threadfence_block();
   __syncthreads();
-  for (int p = warp; p < T * KT; p += 32) {
-    const uint4* src = (const uint4*)(x + (size_t)sorted_token[p] * H);
-    uint4* dst = (uint4*)(x_sorted + (size_t)p * H);
-    for (int i = lane; i < H / 8; i += 32) dst[i] = src[i];
+  // flat copy of T*KT rows of H/8 16-byte chunks; four loads in flight per thread before the stores
+  const int cpr = H / 8, total = T * KT * cpr;
+  for (int base = threadIdx.x; base < total; base += 4 * 1024) {
+    uint4 v[4];
+    int idx4[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      idx4[u] = base + u * 1024;
+      if (idx4[u] < total) {
+        const int p = idx4[u] / cpr, c = idx4[u] - p * cpr;
+        v[u] = *((const uint4*)(x + (size_t)sorted_token[p] * H) + c);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (idx4[u] < total) *((uint4*)x_sorted + idx4[u]) = v[u];
   }
 }
 

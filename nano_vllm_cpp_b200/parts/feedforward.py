@@ -149,7 +149,7 @@ class SparseMoeSwiGLU(FeedForward):
         x_sorted = None
         if fast and al.secondary is None and ops.moe_route_small_usable(T, self.E, self.K, C, self.hidden):
             x_sorted = ops.moe_route_small(logits, self.K, self.renorm, C, gate_logit, idx, score, al, ctx.err,
-                                           x=h if T * KT <= 128 else None)
+                                           x=None)   # one block copies rows slower than the copy kernel does
         else:
             ops.router_topk(logits, self.K, self.renorm, idx, score, C, gate_logit)
             ops.moe_align(idx, KT, al, ctx.err)
