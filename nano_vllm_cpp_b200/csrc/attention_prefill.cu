@@ -169,13 +169,16 @@ __global__ void __launch_bounds__(PF_THREADS, DP <= 128 ? 2 : 1) attention_prefi
         uint32_t qa[4];
         ldsm4(s_u32(Qs + (warp * 16 + (lane % 8) + 8 * ((lane / 8) % 2)) * LDS + kk * 16 + 8 * (lane / 16)), qa[0],
               qa[1], qa[2], qa[3]);
+        // the four fragment loads of a k-block go out together, then their eight products
+        uint32_t kf[BN / 16][4];
+#pragma unroll
+        for (int np = 0; np < BN / 16; ++np)
+          ldsm4(s_u32(kb + (np * 16 + (lane % 8) + 8 * (lane / 16)) * LDS + kk * 16 + 8 * ((lane / 8) % 2)), kf[np][0],
+                kf[np][1], kf[np][2], kf[np][3]);
 #pragma unroll
         for (int np = 0; np < BN / 16; ++np) {
-          uint32_t b0, b1, b2, b3;
-          ldsm4(s_u32(kb + (np * 16 + (lane % 8) + 8 * (lane / 16)) * LDS + kk * 16 + 8 * ((lane / 8) % 2)), b0, b1, b2,
-                b3);
-          mma16816(s[2 * np], qa, b0, b1);
-          mma16816(s[2 * np + 1], qa, b2, b3);
+          mma16816(s[2 * np], qa, kf[np][0], kf[np][1]);
+          mma16816(s[2 * np + 1], qa, kf[np][2], kf[np][3]);
         }
       }
     }
@@ -234,13 +237,36 @@ __global__ void __launch_bounds__(PF_THREADS, DP <= 128 ? 2 : 1) attention_prefi
       pa[2] = pack_bf16(s[2 * kb16 + 1][0], s[2 * kb16 + 1][1]);
       pa[3] = pack_bf16(s[2 * kb16 + 1][2], s[2 * kb16 + 1][3]);
 #pragma unroll
-      for (int dp = 0; dp < DP / 16; ++dp) {
-        if (dp * 16 < D) {
-          uint32_t b0, b1, b2, b3;
-          ldsm4_t(s_u32(vb + (kb16 * 16 + (lane % 8) + 8 * ((lane / 8) % 2)) * LDS + dp * 16 + 8 * (lane / 16)), b0, b1,
-                  b2, b3);
-          mma16816(o[2 * dp], pa, b0, b1);
-          mma16816(o[2 * dp + 1], pa, b2, b3);
+      for (int d4 = 0; d4 < DP / 64; ++d4) {
+        if (d4 * 64 < D) {
+          uint32_t vf[4][4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int dp = d4 * 4 + u;
+            if (dp * 16 < D)
+              ldsm4_t(s_u32(vb + (kb16 * 16 + (lane % 8) + 8 * ((lane / 8) % 2)) * LDS + dp * 16 + 8 * (lane / 16)),
+                      vf[u][0], vf[u][1], vf[u][2], vf[u][3]);
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int dp = d4 * 4 + u;
+            if (dp * 16 < D) {
+              mma16816(o[2 * dp], pa, vf[u][0], vf[u][1]);
+              mma16816(o[2 * dp + 1], pa, vf[u][2], vf[u][3]);
+            }
+          }
+        }
+      }
+      if (DP < 64) {                                 // head sizes below 64: at most two 16-wide blocks
+#pragma unroll
+        for (int dp = 0; dp < DP / 16; ++dp) {
+          if (dp * 16 < D) {
+            uint32_t b0, b1, b2, b3;
+            ldsm4_t(s_u32(vb + (kb16 * 16 + (lane % 8) + 8 * ((lane / 8) % 2)) * LDS + dp * 16 + 8 * (lane / 16)), b0, b1,
+                    b2, b3);
+            mma16816(o[2 * dp], pa, b0, b1);
+            mma16816(o[2 * dp + 1], pa, b2, b3);
+          }
         }
       }
     }

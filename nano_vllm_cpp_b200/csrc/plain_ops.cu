@@ -95,7 +95,25 @@ __global__ void __launch_bounds__(256) rope_store_kernel(void* __restrict__ qkv,
   // rotated heads (q, and k when the cache is written): the block's (head, pair) items flattened; a thread
   // owns whole pairs (f, f + half), so rotating q in place needs no barrier
   const int rot_end = min(h_end, write_kv ? Hq + Hkv : Hq);
-  if (half > 0)
+  const bool packed = dt == NV_DT_BF16 && cache_dt == NV_DT_BF16 && half % 2 == 0 && D % 8 == 0;
+  if (packed) {
+    // bfloat16 buffers: two pairs per thread, 4-byte loads and stores
+    const int hp = half / 2;
+    bf16* qb = (bf16*)qkv;
+    bf16* kb = (bf16*)kc;
+    for (int i = threadIdx.x; i < (rot_end - h_begin) * hp; i += blockDim.x) {
+      const int h = h_begin + i / hp, f = (i % hp) * 2;
+      const size_t base = row + (size_t)h * D;
+      const float2 x1 = __bfloat1622float2(*(const __nv_bfloat162*)(qb + base + f));
+      const float2 x2 = __bfloat1622float2(*(const __nv_bfloat162*)(qb + base + f + half));
+      const float c0 = cs[f], c1 = cs[f + 1], s0 = sn[f], s1 = sn[f + 1];
+      const __nv_bfloat162 o1 = __floats2bfloat162_rn(x1.x * c0 - x2.x * s0, x1.y * c1 - x2.y * s1);
+      const __nv_bfloat162 o2 = __floats2bfloat162_rn(x2.x * c0 + x1.x * s0, x2.y * c1 + x1.y * s1);
+      bf16* dst = h < Hq ? qb + base : kb + (((size_t)blk * Hkv + (h - Hq)) * page + slot) * D;
+      *(__nv_bfloat162*)(dst + f) = o1;
+      *(__nv_bfloat162*)(dst + f + half) = o2;
+    }
+  } else if (half > 0)
     for (int i = threadIdx.x; i < (rot_end - h_begin) * half; i += blockDim.x) {
       const int h = h_begin + i / half, f = i % half;
       const size_t base = row + (size_t)h * D;
@@ -120,6 +138,15 @@ __global__ void __launch_bounds__(256) rope_store_kernel(void* __restrict__ qkv,
     st_dt(kc, cache_dt, cbase + d, ld_dt(qkv, dt, row + (size_t)h * D + d));
   }
   const int v_lo = max(h_begin, Hq + Hkv);
+  if (packed) {                                    // 16-byte copies of v
+    const int cpd = D / 8;
+    for (int i = threadIdx.x; i < (h_end - v_lo) * cpd; i += blockDim.x) {
+      const int h = v_lo + i / cpd, c = i % cpd;
+      const size_t cbase = (((size_t)blk * Hkv + (h - Hq - Hkv)) * page + slot) * D;
+      *((uint4*)((bf16*)vc + cbase) + c) = *((const uint4*)((const bf16*)qkv + row + (size_t)h * D) + c);
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < (h_end - v_lo) * D; i += blockDim.x) {
     const int h = v_lo + i / D, d = i % D;
     const size_t cbase = (((size_t)blk * Hkv + (h - Hq - Hkv)) * page + slot) * D;

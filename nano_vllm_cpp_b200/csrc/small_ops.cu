@@ -63,29 +63,38 @@ __global__ void __launch_bounds__(256) rowdot_kernel(const float* __restrict__ a
   }
 }
 
-// The same product for many rows: one block per row keeps the row in shared memory and its 8 warps walk the
-// outputs four at a time, each warp summing all of k itself.  Fewer, fatter blocks and a fraction of the
-// loads; the order of the sum differs from rowdot_kernel's, so a run uses one of the two for a given op
-// and batch shape only where rounding-level differences between batch shapes are accepted (bfloat16 runs).
+// The same product for many rows: one block keeps WT rows in shared memory and its 8 warps walk the outputs
+// four at a time, each warp summing all of k itself for the WT rows at once, so a weight row is read once per
+// WT rows.  Fewer, fatter blocks and a fraction of the loads; the order of the sum differs from
+// rowdot_kernel's, so a run uses one of the two for a given op and batch shape only where rounding-level
+// differences between batch shapes are accepted (bfloat16 runs).
+constexpr int WT = 4;
 template <typename TW>
 __global__ void __launch_bounds__(256) rowdot_wide_kernel(const float* __restrict__ a, long long lda,
                                                           const TW* __restrict__ w, float* __restrict__ out,
-                                                          long long ldo, int N, int K) {
-  extern __shared__ float row_s[];
+                                                          long long ldo, int T, int N, int K) {
+  extern __shared__ float row_s[];                 // [WT][K]
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-  const int t = blockIdx.x;
-  const float* ar = a + (size_t)t * lda;
-  for (int k = threadIdx.x; k < K; k += 256) row_s[k] = ar[k];
+  const int t0 = blockIdx.x * WT;
+  const int nt = min(WT, T - t0);
+  for (int i = threadIdx.x; i < WT * K; i += 256) {
+    const int r = i / K, k = i - r * K;
+    row_s[i] = r < nt ? a[(size_t)(t0 + r) * lda + k] : 0.f;
+  }
   __syncthreads();
   const bool vec = K % 4 == 0 && ((uintptr_t)w & 15) == 0;
   for (int n0 = warp * 4; n0 < N; n0 += 32) {
-    float s[4] = {0.f, 0.f, 0.f, 0.f};
+    float s[WT][4];
+#pragma unroll
+    for (int r = 0; r < WT; ++r) s[r][0] = s[r][1] = s[r][2] = s[r][3] = 0.f;
     const TW* wr[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) wr[i] = w + (size_t)min(n0 + i, N - 1) * K;
     if (vec) {
       for (int k = lane * 4; k < K; k += 128) {
-        const float4 av = *(const float4*)(row_s + k);
+        float4 av[WT];
+#pragma unroll
+        for (int r = 0; r < WT; ++r) av[r] = *(const float4*)(row_s + r * K + k);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           float w0, w1, w2, w3;
@@ -98,22 +107,30 @@ __global__ void __launch_bounds__(256) rowdot_wide_kernel(const float* __restric
             const float2 hi = __bfloat1622float2(*(const __nv_bfloat162*)&raw.y);
             w0 = lo.x; w1 = lo.y; w2 = hi.x; w3 = hi.y;
           }
-          s[i] = fmaf(av.x, w0, s[i]); s[i] = fmaf(av.y, w1, s[i]);
-          s[i] = fmaf(av.z, w2, s[i]); s[i] = fmaf(av.w, w3, s[i]);
+#pragma unroll
+          for (int r = 0; r < WT; ++r) {
+            s[r][i] = fmaf(av[r].x, w0, s[r][i]); s[r][i] = fmaf(av[r].y, w1, s[r][i]);
+            s[r][i] = fmaf(av[r].z, w2, s[r][i]); s[r][i] = fmaf(av[r].w, w3, s[r][i]);
+          }
         }
       }
     } else {
       for (int k = lane; k < K; k += 32) {
-        const float av = row_s[k];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) s[i] = fmaf(av, to_f32(wr[i][k]), s[i]);
+        for (int i = 0; i < 4; ++i) {
+          const float wv = to_f32(wr[i][k]);
+#pragma unroll
+          for (int r = 0; r < WT; ++r) s[r][i] = fmaf(row_s[r * K + k], wv, s[r][i]);
+        }
       }
     }
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      s[i] = warp_sum(s[i]);
-      if (lane == 0 && n0 + i < N) out[(size_t)t * ldo + n0 + i] = s[i];
-    }
+    for (int r = 0; r < WT; ++r)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float v = warp_sum(s[r][i]);
+        if (lane == 0 && r < nt && n0 + i < N) out[(size_t)(t0 + r) * ldo + n0 + i] = v;
+      }
   }
 }
 
@@ -166,11 +183,12 @@ NV_API int nv_rowdot(const float* a, long long lda, const void* w, int w_dt, flo
                      int N, int K, int wide, cudaStream_t s) {
   if (!dt_ok(w_dt)) return NV_ERR_BAD_DTYPE;
   if (T == 0 || N == 0) return NV_OK;
-  if (wide && (size_t)K * 4 <= 48 * 1024) {
+  if (wide && (size_t)WT * K * 4 <= 48 * 1024) {
+    const unsigned blocks = (unsigned)((T + WT - 1) / WT);
     if (w_dt == NV_DT_F32)
-      rowdot_wide_kernel<float><<<T, 256, (size_t)K * 4, s>>>(a, lda, (const float*)w, out, ldo, N, K);
+      rowdot_wide_kernel<float><<<blocks, 256, (size_t)WT * K * 4, s>>>(a, lda, (const float*)w, out, ldo, T, N, K);
     else
-      rowdot_wide_kernel<bf16><<<T, 256, (size_t)K * 4, s>>>(a, lda, (const bf16*)w, out, ldo, N, K);
+      rowdot_wide_kernel<bf16><<<blocks, 256, (size_t)WT * K * 4, s>>>(a, lda, (const bf16*)w, out, ldo, T, N, K);
     NV_RETURN_LAST();
   }
   if ((N + 3) / 4 > 65535) return NV_ERR_BAD_SIZE;
