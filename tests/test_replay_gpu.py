@@ -133,3 +133,45 @@ def test_trace_run_program(folders, tmp_path):
     helpers.assert_close(s0, ref_a[[9]], dtype, "step 0")
     helpers.assert_close(s1, ref_b[[0, 8]], dtype, "step 1")
     helpers.assert_close(s2, ref_a[[38, 39]], dtype, "step 2")
+
+
+def test_bfloat16_run_of_a_model_stored_in_float32(tmp_path):
+    """Tensors stored in 32 bits stay float32 in a bfloat16 run (the products then take the plain kernel);
+    activations and the cache are bfloat16.  Portions and decode steps against the plain implementation."""
+    from nano_vllm_cpp_b200.weights import write_model_folder
+    cfg = dict(helpers.CASES["B"]["config"])
+    mdir = write_model_folder(cfg, str(tmp_path / "f32"), seed=4, std=0.05, norm_std=0.1, dtype="float32")
+    runner = make_runner(mdir, "bfloat16", 128)
+    assert runner.model.layers[1].feed_forward.w_gate_up.dtype == torch.float32
+    assert runner.cache.views[0].k.dtype == torch.bfloat16
+    rp = Replay(runner)
+    ids = prompt("B", 60, salt=6)
+    rp.step([("m", ids[:25], True)])
+    rp.step([("m", ids[25:27], True)])
+    for t in range(27, 60):
+        rp.step([("m", ids[t:t + 1], [0])])
+    rp.compare("m", ids, mdir, "bfloat16", "float32 weights, bfloat16 run")
+
+
+def test_trace_run_program_bfloat16(folders, tmp_path):
+    import json, os, subprocess, sys
+    import numpy as np
+    case, dtype = "B", "bfloat16"
+    ids = prompt(case, 50, salt=8)
+    steps = [{"step": 7, "entries": [{"id": 1, "tokens": ids[:18], "want": list(range(18))}], "end": []}]
+    steps += [{"step": 8 + i, "entries": [{"id": 1, "tokens": ids[18 + i:19 + i], "want": [0]}], "end": []} for i in range(32)]
+    steps[-1]["end"] = [1]
+    steps.append({"step": 99, "entries": [], "end": []})
+    out = tmp_path / "out"
+    exe = os.path.join(os.path.dirname(helpers.HERE), "bin", "trace_run")
+    r = subprocess.run([sys.executable, exe, "--model", folders[case], "--dtype", dtype, "--out", str(out),
+                        "--max-tokens", "64"], input="\n".join(json.dumps(s) for s in steps) + "\n",
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert r.stdout.split() == [w for s in steps for w in ("done", str(s["step"]))]
+    V = helpers.CASES[case]["config"]["vocab_size"]
+    ref = helpers.plain_logits(folders[case], ids)
+    helpers.assert_close(np.fromfile(out / "7.f32", dtype="<f4").reshape(-1, V), ref[:18], dtype, "portion")
+    got = np.stack([np.fromfile(out / f"{8 + i}.f32", dtype="<f4") for i in range(32)])
+    helpers.assert_close(got, ref[18:50], dtype, "decode steps")
+    assert not (out / "99.f32").exists()
