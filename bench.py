@@ -246,15 +246,12 @@ def main() -> int:
         B = args.batch
         rids = fill_context(B)
         sp = SamplingParams(temperature=0.0, max_tokens=args.steps + args.warmup + 8, ignore_eos=True)
-        from nano_vllm_cpp_b200.engine.sequence import Sequence, SequenceStatus
+        from nano_vllm_cpp_b200.engine.sequence import Sequence
         seqs = []
-        for rid in rids:     # requests that have "already prefilled" `context` tokens
+        for rid in rids:     # requests whose caches already hold `context` tokens join the running ones
             s = Sequence(torch.randint(0, V, (args.context + 1,), generator=g).tolist(), sp)
-            rc = runner.manager.requests.pop(rid)
-            rc.rid = s.seq_id
-            runner.manager.requests[s.seq_id] = rc
-            s.status = SequenceStatus.RUNNING
-            eng.scheduler.running.append(s)
+            runner.manager.rename(rid, s.seq_id)
+            eng.scheduler.add(s, running=True)
             seqs.append(s)
         for _ in range(args.warmup):
             eng.step()
@@ -268,10 +265,8 @@ def main() -> int:
         dt = time.perf_counter() - t0
         e2e = {"value": round(n / dt, 1), "unit": "tokens/s", "h2d_bytes_per_step": eng.runner.last_h2d_bytes + B * 12,
                "d2h_bytes_per_step": B * 4 + 4}
-        for s in seqs:
-            if runner.manager.has(s.seq_id):
-                runner.manager.close(s.seq_id)
-        eng.scheduler.running.clear()
+        while not eng.is_finished():      # let them run out (a few more steps)
+            eng.step()
 
     line = {
         "metric": "decode tok/s (batch 8, 2,048-token context); prefill tok/s at 2,048 tokens; % of roofline",

@@ -1,5 +1,6 @@
 """Host side of the cache: which pages and which state slot every live request holds.
 
+The class lives in native code (csrc/host_core.cpp, ``CacheManager``); this is its Python face.
 Layers with the same needs form a *group* with pages and block tables of its own: one group for
 layers that read every earlier key, one for each window size.  A group with a window gives a
 page back as soon as every position in it lies before the window of the next row to run.  A
@@ -13,23 +14,55 @@ their early pages back.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+import ctypes
 
-from .block_pool import BlockPool, NoFreePages, chain_hash
+import numpy as np
+
+from ..csrc import host
+from .block_pool import BlockPool, NoFreePages
 
 
 class NoFreeSlot(RuntimeError):
     pass
 
 
-@dataclass
 class RequestCache:
-    rid: object
-    slot: int
-    tables: list                      # per group: list of page ids, -1 where given back
-    num_tokens: int = 0               # tokens whose keys/values (or state) are in the cache
-    hashed_pages: int = 0             # leading full pages that carry a hash (prefix caching)
-    last_hash: int | None = None
+    """A view of one request's entry in the manager."""
+
+    def __init__(self, manager, rid, handle: int):
+        self._m, self.rid, self._id = manager, rid, handle
+
+    def _info(self, what: int) -> int:
+        v = host.lib().nvh_request_info(self._m._h, self._id, what)
+        if v < 0:
+            raise KeyError(self.rid)
+        return int(v)
+
+    @property
+    def slot(self) -> int:
+        return self._info(0)
+
+    @property
+    def num_tokens(self) -> int:
+        return self._info(1)
+
+    @property
+    def hashed_pages(self) -> int:
+        return self._info(2)
+
+    @property
+    def tables(self) -> list:
+        """Per group: list of page ids, -1 where given back."""
+        L = host.lib()
+        out = []
+        for g in range(self._m.num_groups):
+            n = L.nvh_table(self._m._h, self._id, g, None, 0)
+            if n < 0:
+                raise KeyError(self.rid)
+            buf = (ctypes.c_int * max(n, 1))()
+            L.nvh_table(self._m._h, self._id, g, buf, n)
+            out.append(list(buf[:n]))
+        return out
 
 
 class CacheManager:
@@ -41,147 +74,154 @@ class CacheManager:
             num_pages = [num_pages] * len(windows)
         self.windows = list(windows)
         self.page_size = page_size
-        self.pools = [BlockPool(n, page_size) for n in num_pages]
         self.max_requests = max_requests
-        self._free_slots = list(range(max_requests - 1, -1, -1))
-        self.requests: dict = {}
-        self.prefix_caching = bool(prefix_caching) and len(windows) == 1 and windows[0] == 0
+        self.num_groups = len(windows)
+        w, _ = host.ints(self.windows)
+        n, _ = host.ints(list(num_pages))
+        L = host.lib()
+        self._h = L.nvh_manager_create(w, n, self.num_groups, page_size, max_requests, 1 if prefix_caching else 0)
+        self.pools = [BlockPool(num_pages[g], page_size, _handle=L.nvh_manager_pool(self._h, g))
+                      for g in range(self.num_groups)]
+        self.prefix_caching = bool(L.nvh_manager_prefix_caching(self._h))
+        # Request ids: an integer is its own native id (so requests opened by the native scheduler are
+        # visible here under the same id); any other hashable gets a negative native id of its own.
+        self._ids: dict = {}
+        self._next_id = -1
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            host.lib().nvh_manager_destroy(self._h)
+            self._h = None
+
+    def _native(self, rid, create: bool = False) -> int:
+        if isinstance(rid, int) and not isinstance(rid, bool):
+            if rid < 0:
+                raise ValueError("integer request ids must not be negative")
+            return rid
+        if rid not in self._ids:
+            if not create:
+                raise KeyError(rid)
+            self._ids[rid] = self._next_id
+            self._next_id -= 1
+        return self._ids[rid]
+
+    def _id(self, rid) -> int:
+        h = self._native(rid)
+        if not host.lib().nvh_has(self._h, h):
+            raise KeyError(rid)
+        return h
+
+    @staticmethod
+    def _raise(code: int):
+        msg = host.last_error()
+        if code == host.ERR_NO_PAGES:
+            raise NoFreePages(msg)
+        if code == host.ERR_NO_SLOT:
+            raise NoFreeSlot(msg)
+        raise RuntimeError(msg)
 
     # ------------------------------------------------------------------ requests
     def has(self, rid) -> bool:
-        return rid in self.requests
+        try:
+            return bool(host.lib().nvh_has(self._h, self._native(rid)))
+        except KeyError:
+            return False
 
     def get(self, rid) -> RequestCache:
-        return self.requests[rid]
+        return RequestCache(self, rid, self._id(rid))
 
     def free_slots(self) -> int:
-        return len(self._free_slots)
+        return int(host.lib().nvh_manager_free_slots(self._h))
 
     def open(self, rid) -> RequestCache:
-        if rid in self.requests:
-            raise RuntimeError(f"request {rid!r} is already open")
-        if not self._free_slots:
-            raise NoFreeSlot("no free state slot")
-        rc = RequestCache(rid, self._free_slots.pop(), [[] for _ in self.pools])
-        self.requests[rid] = rc
-        return rc
+        h = self._native(rid, create=True)
+        rc = host.lib().nvh_open(self._h, h)
+        if rc < 0:
+            if rc == host.ERR_STATE:
+                raise RuntimeError(f"request {rid!r} is already open")
+            self._raise(rc)
+        return RequestCache(self, rid, h)
 
     def close(self, rid) -> None:
-        rc = self.requests.pop(rid)
-        for pool, table in zip(self.pools, rc.tables):
-            for page in reversed(table):          # reverse order, as src/block_manager.cpp:100-108
-                if page >= 0:
-                    pool.release(page)
-        self._free_slots.append(rc.slot)
+        rc = host.lib().nvh_close(self._h, self._id(rid))
+        if rc:
+            self._raise(rc)
+        self._ids.pop(rid, None)
+
+    def rename(self, rid, new_rid) -> None:
+        """The same cache under another request id (a request handed from one owner to another)."""
+        rc = host.lib().nvh_rename(self._h, self._id(rid), self._native(new_rid, create=True))
+        if rc:
+            self._raise(rc)
+        self._ids.pop(rid, None)
 
     # ------------------------------------------------------------------ pages
-    def _first_needed_page(self, g: int, start: int) -> int:
-        """Lowest page that rows from position ``start`` on still read in group g."""
-        w = self.windows[g]
-        if w <= 0:
-            return 0
-        return max(0, start + 1 - w) // self.page_size
-
     def pages_needed(self, rid, start: int, end: int) -> list:
         """Per group: pages to take minus pages that running rows [start, end) gives back first."""
-        rc = self.requests[rid]
-        need = []
-        for g, table in enumerate(rc.tables):
-            total = (end + self.page_size - 1) // self.page_size
-            fresh = max(0, total - len(table))
-            first = self._first_needed_page(g, start)
-            back = sum(1 for p in table[:first] if p >= 0 and self.pools[g].ref_count[p] == 1)
-            need.append(fresh - back)
-        return need
+        out = (ctypes.c_int * self.num_groups)()
+        if host.lib().nvh_pages_needed(self._h, self._id(rid), start, end, out):
+            raise RuntimeError(host.last_error())
+        return list(out)
 
     def can_extend(self, rid, start: int, end: int) -> bool:
-        return all(n <= pool.num_free() for n, pool in zip(self.pages_needed(rid, start, end), self.pools))
+        return bool(host.lib().nvh_can_extend(self._h, self._id(rid), start, end))
 
     def extend(self, rid, start: int, end: int) -> None:
         """Makes the cache ready for rows at positions [start, end): gives back pages that have left
         the window, then takes pages up to ``end``.  Raises ``NoFreePages`` (and changes nothing
         but the give-back) if a group runs out."""
-        rc = self.requests[rid]
-        if start != rc.num_tokens:
-            raise RuntimeError(f"request {rid!r}: rows start at {start} but {rc.num_tokens} tokens are cached")
-        for g, table in enumerate(rc.tables):
-            first = min(self._first_needed_page(g, start), len(table))
-            for i in range(first):
-                if table[i] >= 0:
-                    self.pools[g].release(table[i])
-                    table[i] = -1
-        if not all(n <= pool.num_free() for n, pool in zip(self.pages_needed(rid, start, end), self.pools)):
-            raise NoFreePages("no free blocks")
-        for g, table in enumerate(rc.tables):
-            total = (end + self.page_size - 1) // self.page_size
-            while len(table) < total:
-                table.append(self.pools[g].allocate())
+        rc = host.lib().nvh_extend(self._h, self._id(rid), start, end)
+        if rc:
+            if rc == host.ERR_STATE:
+                raise RuntimeError(f"request {rid!r}: {host.last_error()}")
+            self._raise(rc)
 
     def commit(self, rid, end: int, tokens=None) -> None:
         """Rows up to ``end`` have run.  With prefix caching, ``tokens`` (the request's ids so far)
         lets newly completed pages be hashed (src/block_manager.cpp:121-134)."""
-        rc = self.requests[rid]
-        rc.num_tokens = end
-        if self.prefix_caching and tokens is not None:
-            pool, table = self.pools[0], rc.tables[0]
-            full = end // self.page_size
-            for i in range(rc.hashed_pages, full):
-                toks = tokens[i * self.page_size:(i + 1) * self.page_size]
-                h = chain_hash(toks, rc.last_hash)
-                rc.last_hash = h
-                if pool.lookup(h, toks) is None:
-                    pool.set_hash(table[i], h, toks)
-            rc.hashed_pages = max(rc.hashed_pages, full)
+        arr, n = (None, 0)
+        if tokens is not None and self.prefix_caching:
+            arr, n = host.ints(list(tokens))
+        rc = host.lib().nvh_commit(self._h, self._id(rid), end, arr, n)
+        if rc:
+            self._raise(rc)
+
+    def fill_block_table(self, rid, group: int, dst: np.ndarray) -> int:
+        """Writes the request's block table of a group into ``dst`` (int32, -1 beyond it); returns its length."""
+        n = host.lib().nvh_table(self._h, self._id(rid), group, dst.ctypes.data_as(ctypes.c_void_p), dst.shape[0])
+        if n < 0:
+            raise KeyError(rid)
+        return int(n)
 
     # ------------------------------------------------------------------ prefix sharing
     def match_prefix(self, tokens) -> list:
-        """Pages holding the longest cached prefix of ``tokens``; never the page that holds the last
-        token, so that at least one row is left to run (src/block_manager.cpp:56-73)."""
+        """Pages holding the longest cached prefix of ``tokens`` as (page, hash) pairs; never the page that
+        holds the last token, so that at least one row is left to run (src/block_manager.cpp:56-73)."""
         if not self.prefix_caching:
             return []
-        pool = self.pools[0]
-        pages, h = [], None
-        n_pages = (len(tokens) + self.page_size - 1) // self.page_size
-        for i in range(n_pages - 1):
-            toks = tokens[i * self.page_size:(i + 1) * self.page_size]
-            h = chain_hash(toks, h)
-            page = pool.lookup(h, toks)
-            if page is None:
-                break
-            pages.append((page, h))
-        return pages
+        arr, n = host.ints(list(tokens))
+        cap = n // self.page_size + 1
+        pages = (ctypes.c_int * cap)()
+        hashes = (ctypes.c_uint64 * cap)()
+        k = host.lib().nvh_match_prefix(self._h, arr, n, pages, hashes, cap)
+        return [(int(pages[i]), int(hashes[i])) for i in range(k)]
 
     def adopt_prefix(self, rid, matched: list) -> int:
         """Gives a freshly opened request the matched pages; returns the number of cached tokens."""
-        rc = self.requests[rid]
-        if rc.num_tokens or rc.tables[0]:
-            raise RuntimeError("adopt_prefix on a request that already holds pages")
-        for page, h in matched:
-            self.pools[0].share(page)
-            rc.tables[0].append(page)
-            rc.last_hash = h
-        rc.hashed_pages = len(matched)
-        rc.num_tokens = len(matched) * self.page_size
-        return rc.num_tokens
+        pages, n = host.ints([p for p, _ in matched])
+        hashes = (ctypes.c_uint64 * max(n, 1))(*[h for _, h in matched])
+        rc = host.lib().nvh_adopt_prefix(self._h, self._id(rid), pages, hashes, n)
+        if rc < 0:
+            self._raise(rc)
+        return int(rc)
 
     def new_pages_for(self, tokens_len: int, matched: list) -> int:
         """Fresh pages a request of ``tokens_len`` tokens would take after adopting ``matched``
         (a matched page that is currently free must be revived, which costs a free page too)."""
-        total = (tokens_len + self.page_size - 1) // self.page_size
-        revived = sum(1 for page, _ in matched if self.pools[0].ref_count[page] == 0)
-        return total - len(matched) + revived
+        pages, n = host.ints([p for p, _ in matched])
+        return int(host.lib().nvh_new_pages_for(self._h, tokens_len, pages, n))
 
     # ------------------------------------------------------------------ invariants
     def check(self) -> None:
-        slots = [rc.slot for rc in self.requests.values()]
-        if len(set(slots)) != len(slots) or set(slots) & set(self._free_slots):
-            raise AssertionError("a state slot is held twice")
-        if len(slots) + len(self._free_slots) != self.max_requests:
-            raise AssertionError("a state slot is lost")
-        for g, pool in enumerate(self.pools):
-            held: dict = {}
-            for rc in self.requests.values():
-                for p in rc.tables[g]:
-                    if p >= 0:
-                        held[p] = held.get(p, 0) + 1
-            pool.check(held)
+        if host.lib().nvh_manager_check(self._h):
+            raise AssertionError(host.last_error())

@@ -30,7 +30,7 @@ class BuildError(RuntimeError):
 
 
 def _sources() -> list[str]:
-    return sorted(f for f in os.listdir(CSRC) if f.endswith(".cu"))
+    return sorted(f for f in os.listdir(CSRC) if f.endswith((".cu", ".cpp")))
 
 
 def _headers() -> list[str]:
@@ -98,11 +98,11 @@ def _compile(bdir: str, lib: str, verbose: bool) -> None:
     nvcc = _find_nvcc()
     srcs = _sources()
     t0 = time.time()
-    _say(verbose, f"compiling {len(srcs)} CUDA files for sm_100a with {nvcc}")
+    _say(verbose, f"compiling {len(srcs)} source files (CUDA for sm_100a, host C++) with {nvcc}")
     procs = []
     objs = []
     for s in srcs:
-        obj = os.path.join(bdir, s[:-3] + ".o")
+        obj = os.path.join(bdir, os.path.splitext(s)[0] + ".o")
         objs.append(obj)
         cmd = [nvcc, *NVCC_FLAGS, "-I", CSRC, "-c", os.path.join(CSRC, s), "-o", obj]
         procs.append((s, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))

@@ -105,15 +105,16 @@ def batch_layout(S: int, T: int, n_want: int, G: int, max_blocks: int):
     return seg, max(off, 4)
 
 
-def build_batch(entries: list, infos: list, tables: list, max_blocks: int, device, stager=None,
-                static_dev=None) -> StepBatch:
-    """``infos``: EntryInfo per entry; ``tables``: per group, per entry, the list of page ids.
+def build_batch(entries: list, infos: list, tables, max_blocks: int, device, stager=None,
+                static_dev=None, table_filler=None, num_groups=None) -> StepBatch:
+    """``infos``: EntryInfo per entry; ``tables``: per group, per entry, the list of page ids — or None with
+    ``table_filler(group, entry, dst)``, which writes an entry's block table into an int32 array view.
     With ``static_dev`` the arrays are written into that device buffer (whose layout must be the one
     of ``batch_layout`` for these sizes) instead of a fresh one."""
     S = len(entries)
     T = sum(len(e.tokens) for e in entries)
     n_want = sum(len(e.want) for e in entries)
-    G = len(tables)
+    G = len(tables) if tables is not None else num_groups
     seg, total = batch_layout(S, T, n_want, G, max_blocks)
     host = np.full(total, -1, dtype=np.int32)
 
@@ -136,6 +137,11 @@ def build_batch(entries: list, infos: list, tables: list, max_blocks: int, devic
     put("pos0", [i.pos0 for i in infos]), put("slot", [i.slot for i in infos]), put("want", want)
     for g in range(G):
         o, _ = seg[f"bt{g}"]
+        if tables is None:
+            for i in range(S):
+                if table_filler(g, i, host[o + i * max_blocks:o + (i + 1) * max_blocks]) > max_blocks:
+                    raise ValueError("a request holds more pages than the block table is wide")
+            continue
         for i, table in enumerate(tables[g]):
             if len(table) > max_blocks:
                 raise ValueError("a request holds more pages than the block table is wide")

@@ -102,8 +102,9 @@ class ModelRunner:
             self.manager.extend(e.rid, start, end)
             infos.append(EntryInfo(e.rid, rc.slot, start, len(e.tokens), row0))
             row0 += len(e.tokens)
-        tables = [[self.manager.get(e.rid).tables[g] for e in entries] for g in range(len(self.manager.pools))]
-        batch = build_batch(entries, infos, tables, self.max_blocks, self.device, self.stager, static_dev)
+        batch = build_batch(entries, infos, None, self.max_blocks, self.device, self.stager, static_dev,
+                            table_filler=lambda g, i, dst: self.manager.fill_block_table(entries[i].rid, g, dst),
+                            num_groups=len(self.manager.pools))
         self.last_h2d_bytes = batch.h2d_bytes
         return batch
 

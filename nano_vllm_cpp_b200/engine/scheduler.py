@@ -1,6 +1,9 @@
 """The scheduler: admits requests, cuts prompts into portions under a token budget, decodes,
 finishes and frees.
 
+The class lives in native code (csrc/host_core.cpp, ``Scheduler``); this is its Python face: it
+keeps the ``Sequence`` objects that users hold in step with the native records.
+
 Differences from the reference's scheduler (src/scheduler.cpp:23-89), which runs either prompt
 portions or decode tokens in a step: here every step takes one decode token of each running
 request first and fills the rest of the token budget with prompt portions, so prompts never
@@ -15,7 +18,7 @@ When pages run out
   the back of ``running`` (itself if it is the only one): the victim gives back its pages and
   state slot and goes to the front of ``waiting``; later its prompt *and* the tokens it has
   generated are prefilled again.  Its random stream is keyed by (seed, tokens drawn), so sampling
-  resumes where it stopped.
+  resumes where it stopped.  A step that had to preempt admits no new request.
 * A waiting request is admitted only while pages for its next portion are free; one that is part
   way through its prompt keeps its pages.  If nothing can run, requests holding pages are preempted
   from the back; if the request at the head still cannot get its pages with the whole pool free,
@@ -23,10 +26,11 @@ When pages run out
 """
 from __future__ import annotations
 
-from collections import deque
+import ctypes
 from dataclasses import dataclass
 
-from ..cache import CacheManager, NoFreePages
+from ..cache import CacheManager
+from ..csrc import host
 from .sequence import Sequence, SequenceStatus
 
 
@@ -42,6 +46,9 @@ class Scheduled:
     samples: bool       # the portion reaches the sequence's end: its last row is sampled
 
 
+_STATUS = {0: SequenceStatus.WAITING, 1: SequenceStatus.RUNNING, 2: SequenceStatus.FINISHED}
+
+
 class Scheduler:
     def __init__(self, manager: CacheManager, *, max_num_seqs: int, max_num_batched_tokens: int,
                  max_model_len: int, eos: int = -1, prefill_chunk: int = 0):
@@ -51,145 +58,85 @@ class Scheduler:
         self.max_model_len = max_model_len
         self.eos = eos
         self.prefill_chunk = prefill_chunk
-        self.waiting: deque = deque()
-        self.running: deque = deque()
-        self.num_preemptions = 0
+        self._h = host.lib().nvs_create(manager._h, max_num_seqs, max_num_batched_tokens, max_model_len, eos,
+                                        prefill_chunk)
+        self._seqs: dict = {}           # seq_id -> Sequence, for every sequence that is not finished
+        cap = max(max_num_seqs, 1)
+        self._ids = (ctypes.c_int64 * cap)()
+        self._starts = (ctypes.c_int * cap)()
+        self._counts = (ctypes.c_int * cap)()
+        self._samples = (ctypes.c_int * cap)()
+        self._done = (ctypes.c_int64 * cap)()
+        self._cap = cap
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            host.lib().nvs_destroy(self._h)
+            self._h = None
 
     # ------------------------------------------------------------------ queue
-    def add(self, seq: Sequence) -> None:
-        self.waiting.append(seq)
+    def add(self, seq: Sequence, running: bool = False) -> None:
+        """Queues a request.  ``running``: its cache already exists under ``seq.seq_id`` and holds all but
+        its last token, so it joins the running requests at once (a request taken over from elsewhere)."""
+        arr, n = host.ints(seq.token_ids)
+        rc = host.lib().nvs_add(self._h, seq.seq_id, arr, n, seq.num_prompt_tokens, seq.max_tokens,
+                                1 if seq.ignore_eos else 0, 1 if running else 0)
+        if rc:
+            raise SchedulerError(host.last_error())
+        if running:
+            seq.status = SequenceStatus.RUNNING
+        self._seqs[seq.seq_id] = seq
 
     def is_finished(self) -> bool:
-        return not self.waiting and not self.running
+        return bool(host.lib().nvs_is_finished(self._h))
 
-    def _cached(self, seq: Sequence) -> int:
-        return self.manager.get(seq.seq_id).num_tokens if self.manager.has(seq.seq_id) else 0
+    @property
+    def num_preemptions(self) -> int:
+        return int(host.lib().nvs_num_preemptions(self._h))
 
-    def preempt(self, seq: Sequence) -> None:
-        """Gives back what the sequence holds and queues it at the front (src/scheduler.cpp:16-21)."""
-        seq.status = SequenceStatus.WAITING
-        seq.num_preemptions += 1
-        self.num_preemptions += 1
-        if self.manager.has(seq.seq_id):
-            self.manager.close(seq.seq_id)
-        self.waiting.appendleft(seq)
+    def queue_sizes(self) -> tuple:
+        """(waiting, running)."""
+        w, r = ctypes.c_int(), ctypes.c_int()
+        host.lib().nvs_queue_sizes(self._h, ctypes.byref(w), ctypes.byref(r))
+        return w.value, r.value
+
+    def _sync(self, seq: Sequence) -> None:
+        L = host.lib()
+        seq.status = _STATUS[L.nvs_seq_info(self._h, seq.seq_id, 0)]
+        seq.num_preemptions = int(L.nvs_seq_info(self._h, seq.seq_id, 1))
 
     # ------------------------------------------------------------------ one step's decisions
     def schedule(self) -> list:
-        out: list = []
-        budget = self.max_num_batched_tokens
-
-        # 1. one token for every running sequence, oldest first
-        preempted_before = self.num_preemptions
-        kept: deque = deque()
-        while self.running and len(out) < self.max_num_seqs and budget > 0:
-            seq = self.running.popleft()
-            n = self._cached(seq)
-            ok = True
-            while True:
-                try:
-                    self.manager.extend(seq.seq_id, n, n + 1)   # takes the page now (src/scheduler.cpp:75)
-                    break
-                except NoFreePages:
-                    pass
-                if self.running:
-                    self.preempt(self.running.pop())
-                elif kept and kept[-1] is not seq:
-                    victim = kept.pop()
-                    out = [s for s in out if s.seq is not victim]
-                    budget += 1
-                    self.preempt(victim)
-                else:
-                    self.preempt(seq)
-                    ok = False
-                    break
-            if not ok:
-                break
-            out.append(Scheduled(seq, n, 1, True))
-            kept.append(seq)
-            budget -= 1
-        kept.extend(self.running)
-        self.running = kept
-
-        # 2. prompt portions from the waiting queue, in order
-        while (self.waiting and len(out) < self.max_num_seqs and budget > 0
-               and self.num_preemptions == preempted_before):   # no admission in a step that had to preempt
-            seq = self.waiting[0]
-            opened_here = False
-            if not self.manager.has(seq.seq_id):
-                if self.manager.free_slots() == 0:
-                    break
-                matched = self.manager.match_prefix(seq.token_ids)
-                first = min(seq.num_tokens - len(matched) * self.manager.page_size, budget,
-                            self.prefill_chunk or budget)
-                end = len(matched) * self.manager.page_size + first
-                if self.manager.new_pages_for(end, matched) > self.manager.pools[0].num_free() or any(
-                        (end + self.manager.page_size - 1) // self.manager.page_size > p.num_free()
-                        for p in self.manager.pools[1:]):
-                    break
-                self.manager.open(seq.seq_id)
-                self.manager.adopt_prefix(seq.seq_id, matched)
-                opened_here = True
-            start = self._cached(seq)
-            count = min(seq.num_tokens - start, budget, self.prefill_chunk or budget)
-            try:
-                self.manager.extend(seq.seq_id, start, start + count)
-            except NoFreePages:
-                if opened_here:
-                    self.manager.close(seq.seq_id)
-                break
-            completes = start + count == seq.num_tokens
-            out.append(Scheduled(seq, start, count, completes))
-            budget -= count
-            if completes:
-                self.waiting.popleft()
-                seq.status = SequenceStatus.RUNNING
-                self.running.append(seq)
-            else:
-                break   # the head of the queue is part way through its prompt; it goes on next step
-
-        if out:
-            for s in out:
-                s.seq.num_scheduled_tokens = s.count
-            return out
-        if self.is_finished():
-            return out
-        # 3. nothing can run: free pages held by waiting sequences, newest first, and try again
-        holders = [s for s in list(self.waiting)[1:] if self.manager.has(s.seq_id)]
-        if holders:
-            victim = holders[-1]
-            self.manager.close(victim.seq_id)
-            victim.num_preemptions += 1
-            self.num_preemptions += 1
-            return self.schedule()
-        head = self.waiting[0] if self.waiting else None
-        if head is not None and self.manager.has(head.seq_id) and self._cached(head) > 0:
-            # alone, part way through, and still short of pages: start over would not help
-            raise SchedulerError("scheduler could not make progress: the cache pool is smaller than one request")
-        raise SchedulerError("scheduler could not make progress")
+        n = host.lib().nvs_schedule(self._h, self._ids, self._starts, self._counts, self._samples, self._cap)
+        if n < 0:
+            raise SchedulerError(host.last_error())
+        out = []
+        for i in range(n):
+            seq = self._seqs[self._ids[i]]
+            seq.num_scheduled_tokens = self._counts[i]
+            out.append(Scheduled(seq, self._starts[i], self._counts[i], bool(self._samples[i])))
+        for seq in self._seqs.values():      # preemptions and admissions of this step
+            self._sync(seq)
+        return out
 
     # ------------------------------------------------------------------ after the step
     def postprocess(self, scheduled: list, sampled: dict) -> list:
         """``sampled``: seq_id -> token for every entry with ``samples``.  Returns finished sequences."""
-        finished = []
+        toks = (ctypes.c_int * max(len(scheduled), 1))(*[int(sampled.get(s.seq.seq_id, 0)) for s in scheduled])
+        n = host.lib().nvs_postprocess(self._h, toks, self._done, self._cap)
+        if n < 0:
+            raise SchedulerError(host.last_error())
+        L = host.lib()
         for s in scheduled:
             seq = s.seq
-            if not self.manager.has(seq.seq_id):
-                continue        # preempted after it was scheduled
-            self.manager.commit(seq.seq_id, s.start + s.count, seq.token_ids)
             seq.num_scheduled_tokens = 0
-            if not s.samples:
-                continue
-            token = int(sampled[seq.seq_id])
-            seq.token_ids.append(token)
-            done = ((not seq.ignore_eos and token == self.eos) or seq.num_completion_tokens >= seq.max_tokens
-                    or seq.num_tokens >= self.max_model_len)
-            if done:
-                seq.status = SequenceStatus.FINISHED
-                self.manager.close(seq.seq_id)
-                try:
-                    self.running.remove(seq)
-                except ValueError:
-                    pass
-                finished.append(seq)
+            # the native record grew by the sampled token unless the sequence was preempted meanwhile
+            if s.samples and L.nvs_seq_info(self._h, seq.seq_id, 2) == seq.num_tokens + 1:
+                seq.token_ids.append(int(sampled[seq.seq_id]))
+        finished = []
+        for i in range(n):
+            seq = self._seqs.pop(self._done[i])
+            seq.status = SequenceStatus.FINISHED
+            L.nvs_forget(self._h, seq.seq_id)
+            finished.append(seq)
         return finished

@@ -279,3 +279,88 @@ def test_prefix_hit_skips_cached_pages():
     s2 = Sequence(p + [60, 61], SamplingParams(max_tokens=2, ignore_eos=True))
     rec = drive(sched, [s2], random.Random(5))
     assert rec[0] == [(s2.seq_id, 48, 2, True)]           # the three cached pages are not run again
+
+
+# ------------------------------------------------------------------------------- native code against its plain restatement
+def test_native_host_code_decides_like_the_plain_restatement():
+    """The native pool, manager and scheduler against the plain Python classes of tests/plain_host.py: the same
+    random workloads, compared step by step (who runs, from where, how many tokens, which pages)."""
+    import plain_host as ph
+    rng = random.Random(11)
+    for trial in range(40):
+        windows = rng.choice([(0,), (0, 16), (0, 8, 32)])
+        pages = rng.choice([8, 10, 16, 40])
+        budget, max_seqs = rng.choice([16, 48, 200]), rng.choice([2, 4, 8])
+        prefix, chunk = rng.random() < 0.5, rng.choice([0, 0, 7])
+        native = make_sched(pages, windows=windows, budget=budget, max_seqs=max_seqs, prefix=prefix, chunk=chunk, eos=7)
+        pm = ph.CacheManager(list(windows), pages, 16, max_requests=max_seqs, prefix_caching=prefix)
+        plain = ph.Scheduler(pm, max_num_seqs=max_seqs, max_num_batched_tokens=budget, max_model_len=4096, eos=7,
+                             prefill_chunk=chunk)
+        pairs = []
+        for i in range(rng.randrange(1, 9)):
+            n, base = rng.choice([1, 3, 16, 17, 40, 64]), rng.choice([100, 200])
+            toks, mt, ig = [base + j for j in range(n)], rng.choice([1, 5, 30]), rng.random() < 0.7
+            a = Sequence(toks, SamplingParams(max_tokens=mt, ignore_eos=ig))
+            b = ph.PlainSeq(a.seq_id, toks, mt, ig)
+            native.add(a), plain.add(b)
+            pairs.append((a, b))
+        for step in range(5000):
+            assert native.is_finished() == plain.is_finished()
+            if native.is_finished():
+                break
+            try:
+                out_p = plain.schedule()
+            except ph.SchedulerError:
+                with pytest.raises(SchedulerError):
+                    native.schedule()
+                break
+            out_n = native.schedule()
+            assert [(s.seq.seq_id, s.start, s.count, s.samples) for s in out_n] == \
+                   [(s.seq.seq_id, s.start, s.count, s.samples) for s in out_p]
+            for s in out_n:            # the same pages in every group
+                assert native.manager.get(s.seq.seq_id).tables == pm.get(s.seq.seq_id).tables
+            assert [p.num_free() for p in native.manager.pools] == [p.num_free() for p in pm.pools]
+            sampled = {s.seq.seq_id: rng.choice([7, 9, 11, 13]) for s in out_n if s.samples}
+            fin_n = native.postprocess(out_n, sampled)
+            fin_p = plain.postprocess(out_p, sampled)
+            assert [q.seq_id for q in fin_n] == [q.seq_id for q in fin_p]
+            assert native.num_preemptions == plain.num_preemptions
+            native.manager.check()
+        for a, b in pairs:
+            assert a.token_ids == b.token_ids and a.num_preemptions == b.num_preemptions
+            assert a.is_finished == b.is_finished
+
+
+def test_native_pool_and_hash_against_the_plain_restatement():
+    import plain_host as ph
+    rng = random.Random(12)
+    for _ in range(20):
+        toks = [rng.randrange(0, 1 << 20) for _ in range(rng.choice([1, 4, 16]))]
+        prefix = rng.choice([None, rng.getrandbits(64)])
+        assert chain_hash(toks, prefix) == ph.chain_hash(toks, prefix)
+    a, b = BlockPool(6, 4), ph.BlockPool(6, 4)
+    held = []
+    for _ in range(400):
+        op = rng.random()
+        if op < 0.45 and a.num_free():
+            pa, pb = a.allocate(), b.allocate()
+            assert pa == pb
+            held.append(pa)
+            if rng.random() < 0.5:
+                t = [rng.randrange(5) for _ in range(4)]
+                h = chain_hash(t, None)
+                a.set_hash(pa, h, t), b.set_hash(pb, h, t)
+        elif op < 0.8 and held:
+            p = held.pop(rng.randrange(len(held)))
+            a.release(p), b.release(p)
+        else:
+            t = [rng.randrange(5) for _ in range(4)]
+            h = chain_hash(t, None)
+            la, lb = a.lookup(h, t), b.lookup(h, t)
+            assert la == lb
+            if la is not None and rng.random() < 0.5:
+                a.share(la), b.share(lb)
+                held.append(la)
+        assert a.num_free() == b.num_free()
+        assert [a.ref_count[p] for p in range(6)] == b.ref_count
+        a.check()
