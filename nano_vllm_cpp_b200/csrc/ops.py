@@ -133,8 +133,12 @@ def embedding(ids, table, out, err: ErrorFlag) -> None:
                               _p(err.t), _stream()), "embedding")
 
 
-def add_rmsnorm(x, branch, w, eps: float, out, out32=None) -> None:
-    """x (+= branch); out = rmsnorm(x) * w; optional float32 copy of out."""
+def add_rmsnorm(x, branch, w, eps: float, out, out32=None, *, mix=None) -> None:
+    """x (+= branch); out = rmsnorm(x) * w; optional float32 copy of out.
+
+    ``mix`` = (rows, index, weight, dense, gate_logit) gives the branch as a sum that has not been taken yet:
+    ``sigmoid(gate_logit[t]) * dense[t] + sum_r weight[t, r] * rows[index[t, r]]`` (dense and gate_logit may be
+    None); it is summed inside the kernel instead of by ``moe_combine`` first."""
     _cuda_contig(x, branch, w, out, out32)
     T, H = x.shape
     _need(x.dtype == torch.float32, "add_rmsnorm: the residual stream is float32")
@@ -142,8 +146,30 @@ def add_rmsnorm(x, branch, w, eps: float, out, out32=None) -> None:
           "add_rmsnorm: branch must be float32 and shaped like x")
     _need(w.numel() == H and out.shape == x.shape, "add_rmsnorm: shape mismatch")
     _need(out32 is None or (out32.dtype == torch.float32 and out32.shape == x.shape), "add_rmsnorm: out32")
+    rows = index = weight = dense = gate = None
+    R, gate_ld = 0, 1
+    if mix is not None:
+        _need(branch is None, "add_rmsnorm: a branch or a mix, not both")
+        rows, index, weight, dense, gate = mix
+        _cuda_contig(rows, index, weight, dense)
+        R = index.shape[1]
+        _need(R <= ADD_RMSNORM_MAX_MIX, f"add_rmsnorm: at most {ADD_RMSNORM_MAX_MIX} rows are mixed per token")
+        _need(rows.dtype == torch.float32 and rows.shape[1] == H and weight.dtype == torch.float32
+              and index.dtype == torch.int32 and index.shape == (T, R) and weight.shape == (T, R),
+              "add_rmsnorm: mix shapes")
+        _need(dense is None or (dense.dtype == torch.float32 and dense.shape == x.shape), "add_rmsnorm: mix dense term")
+        if gate is not None:
+            _need(gate.dtype == torch.float32, "add_rmsnorm: gate logits are float32")
+            gate_ld = gate.stride(0) if gate.dim() >= 1 else 1
+    if H % 4 == 0:
+        for t_ in (x, branch, out, out32, rows, dense):
+            _need(t_ is None or t_.data_ptr() % 16 == 0, "add_rmsnorm: rows must start on 16-byte boundaries")
     _check(lib().nv_add_rmsnorm(_p(x), _p(branch), _p(w), c_int(dt(w)), c_float(eps), _p(out), c_int(dt(out)),
-                                _p(out32), c_int(T), c_int(H), _stream()), "add_rmsnorm")
+                                _p(out32), c_int(T), c_int(H), _p(rows), _p(index), _p(weight), c_int(R), _p(dense),
+                                _p(gate), c_longlong(gate_ld), _stream()), "add_rmsnorm")
+
+
+ADD_RMSNORM_MAX_MIX = 64
 
 
 def gemm_plain(a, w, out, *, bias=None, a_rows=None, swiglu=False, M=None, tiles=None) -> None:

@@ -23,35 +23,154 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const void* __rest
 
 // ---------------------------------------------------------- residual add + RMSNorm
 // x += branch (if given); y = x * rsqrt(mean(x^2) + eps) * w     (src/hip_ops.hip:395-417)
-// One block per row.  The sum of squares is taken in a fixed order (a thread's strided
-// elements, then a tree), so a row's result does not depend on the batch.
-__global__ void __launch_bounds__(256) add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ branch,
-                                                          const void* __restrict__ w, int w_dt, float eps,
-                                                          void* __restrict__ out, int out_dt,
-                                                          float* __restrict__ out32, int H) {
-  __shared__ float red[256];
-  size_t base = (size_t)blockIdx.x * H;
-  float ss = 0.f;
-  for (int i = threadIdx.x; i < H; i += 256) {
-    float v = x[base + i];
-    if (branch) {
-      v += branch[base + i];
-      x[base + i] = v;
-    }
-    ss = fmaf(v, v, ss);
+// The branch is a float32 matrix, or a mix of rows that has not been summed yet:
+//   branch[t,:] = sigmoid(gate_logit[t]) * dense[t,:] + sum_r weight[t,r] * rows[index[t,r],:]
+// with the sum over r = 0..R-1 in that order and the dense term added to it afterwards, which is how
+// the experts' outputs are combined (src/hip_ops.hip:873-892, 926-934; src/model.cpp:803-811).
+// One block per row; a thread keeps its elements in registers between the two passes (rows wider
+// than 256 * VEC * NORM_CACHE elements re-read the rest from x).  The sum of squares is taken in
+// a fixed order (a thread's elements in order, a warp's shuffle tree, the warps in order), so a
+// row's result does not depend on the batch.
+constexpr int NORM_THREADS = 256, NORM_CACHE = 4, NORM_MAX_R = 64;
+
+struct NormArgs {
+  float* x;
+  const float* branch;
+  const void* w;
+  void* out;
+  float* out32;
+  const float* rows;
+  const int* index;
+  const float* weight;
+  const float* dense;
+  const float* gate_logit;
+  long long gate_ld;
+  float eps;
+  int w_dt, out_dt, H, R;
+};
+
+template <int VEC>
+struct Chunk { float v[VEC]; };
+
+template <int VEC>
+__device__ __forceinline__ Chunk<VEC> ld_chunk(const float* p) {
+  Chunk<VEC> c;
+  if (VEC == 4) {
+    float4 q = *reinterpret_cast<const float4*>(p);
+    c.v[0] = q.x; c.v[VEC > 1 ? 1 : 0] = q.y; c.v[VEC > 2 ? 2 : 0] = q.z; c.v[VEC > 3 ? 3 : 0] = q.w;
+  } else {
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) c.v[j] = p[j];
   }
-  red[threadIdx.x] = ss;
-  __syncthreads();
-  for (int s = 128; s > 0; s >>= 1) {
-    if (threadIdx.x < s) red[threadIdx.x] += red[threadIdx.x + s];
+  return c;
+}
+template <int VEC>
+__device__ __forceinline__ void st_chunk(float* p, const Chunk<VEC>& c) {
+  if (VEC == 4) *reinterpret_cast<float4*>(p) = make_float4(c.v[0], c.v[VEC > 1 ? 1 : 0], c.v[VEC > 2 ? 2 : 0], c.v[VEC > 3 ? 3 : 0]);
+  else {
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) p[j] = c.v[j];
+  }
+}
+
+template <int VEC>
+__global__ void __launch_bounds__(NORM_THREADS) add_rmsnorm_kernel(NormArgs a) {
+  __shared__ float red[NORM_THREADS / 32];
+  __shared__ int s_idx[NORM_MAX_R];
+  __shared__ float s_w[NORM_MAX_R];
+  const int t = blockIdx.x, tid = threadIdx.x;
+  const size_t base = (size_t)t * a.H;
+  const int chunks = a.H / VEC;
+  float gate = 1.f;
+  if (a.R > 0) {
+    if (tid < a.R) {
+      s_idx[tid] = a.index[(size_t)t * a.R + tid];
+      s_w[tid] = a.weight[(size_t)t * a.R + tid];
+    }
     __syncthreads();
   }
-  float inv = rsqrtf(red[0] / (float)H + eps);
-  for (int i = threadIdx.x; i < H; i += 256) {
-    float y = x[base + i] * inv * ld_dt(w, w_dt, i);
-    st_dt(out, out_dt, base + i, y);
-    if (out32) out32[base + i] = y;
+  if (a.dense && a.gate_logit) gate = 1.f / (1.f + expf(-a.gate_logit[(size_t)t * a.gate_ld]));
+  const bool adds = a.branch || a.R > 0 || a.dense;
+
+  // value of the updated residual stream at chunk c (and its write-back when something was added)
+  auto updated = [&](int c) {
+    Chunk<VEC> v = ld_chunk<VEC>(a.x + base + (size_t)c * VEC);
+    if (a.branch) {
+      Chunk<VEC> b = ld_chunk<VEC>(a.branch + base + (size_t)c * VEC);
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) v.v[j] += b.v[j];
+    } else if (a.R > 0 || a.dense) {
+      Chunk<VEC> r;
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) r.v[j] = 0.f;
+      for (int k = 0; k < a.R; ++k) {
+        Chunk<VEC> y = ld_chunk<VEC>(a.rows + (size_t)s_idx[k] * a.H + (size_t)c * VEC);
+        const float wk = s_w[k];
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) r.v[j] = fmaf(wk, y.v[j], r.v[j]);
+      }
+      if (a.dense) {
+        Chunk<VEC> d = ld_chunk<VEC>(a.dense + base + (size_t)c * VEC);
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) r.v[j] = d.v[j] * gate + r.v[j];
+      }
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) v.v[j] += r.v[j];
+    }
+    if (adds) st_chunk<VEC>(a.x + base + (size_t)c * VEC, v);
+    return v;
+  };
+
+  Chunk<VEC> keep[NORM_CACHE];
+  float ss = 0.f;
+#pragma unroll
+  for (int u = 0; u < NORM_CACHE; ++u) {
+    const int c = tid + u * NORM_THREADS;
+    if (c < chunks) {
+      keep[u] = updated(c);
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) ss = fmaf(keep[u].v[j], keep[u].v[j], ss);
+    }
   }
+  for (int c = tid + NORM_CACHE * NORM_THREADS; c < chunks; c += NORM_THREADS) {
+    Chunk<VEC> v = updated(c);
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) ss = fmaf(v.v[j], v.v[j], ss);
+  }
+  ss = warp_sum(ss);
+  if ((tid & 31) == 0) red[tid >> 5] = ss;
+  __syncthreads();
+  float total = 0.f;
+#pragma unroll
+  for (int i = 0; i < NORM_THREADS / 32; ++i) total += red[i];
+  const float inv = rsqrtf(total / (float)a.H + a.eps);
+
+  auto emit = [&](int c, const Chunk<VEC>& v) {
+    Chunk<VEC> y;
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) y.v[j] = v.v[j] * inv * ld_dt(a.w, a.w_dt, (size_t)c * VEC + j);
+    const size_t o = base + (size_t)c * VEC;
+    if (a.out_dt == NV_DT_F32) st_chunk<VEC>((float*)a.out + o, y);
+    else if (VEC == 4) {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(y.v[0], y.v[VEC > 1 ? 1 : 0]);
+      __nv_bfloat162 hi = __floats2bfloat162_rn(y.v[VEC > 2 ? 2 : 0], y.v[VEC > 3 ? 3 : 0]);
+      uint2 q;
+      q.x = *reinterpret_cast<uint32_t*>(&lo);
+      q.y = *reinterpret_cast<uint32_t*>(&hi);
+      *reinterpret_cast<uint2*>((bf16*)a.out + o) = q;
+    } else {
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) ((bf16*)a.out)[o + j] = __float2bfloat16_rn(y.v[j]);
+    }
+    if (a.out32) st_chunk<VEC>(a.out32 + o, y);
+  };
+#pragma unroll
+  for (int u = 0; u < NORM_CACHE; ++u) {
+    const int c = tid + u * NORM_THREADS;
+    if (c < chunks) emit(c, keep[u]);
+  }
+  for (int c = tid + NORM_CACHE * NORM_THREADS; c < chunks; c += NORM_THREADS)
+    emit(c, ld_chunk<VEC>(a.x + base + (size_t)c * VEC));
 }
 
 // ------------------------------------------------ rotary position encoding + cache write
@@ -376,10 +495,19 @@ NV_API int nv_embedding(const int* ids, const void* table, int table_dt, float* 
 }
 
 NV_API int nv_add_rmsnorm(float* x, const float* branch, const void* w, int w_dt, float eps, void* out,
-                          int out_dt, float* out32, int T, int H, cudaStream_t s) {
+                          int out_dt, float* out32, int T, int H, const float* rows, const int* index,
+                          const float* weight, int R, const float* dense, const float* gate_logit,
+                          long long gate_ld, cudaStream_t s) {
   if (!dt_ok(w_dt) || !dt_ok(out_dt)) return NV_ERR_BAD_DTYPE;
+  if (R < 0 || R > NORM_MAX_R || (R > 0 && (!rows || !index || !weight))) return NV_ERR_BAD_SIZE;
+  if (branch && (R > 0 || dense)) return NV_ERR_BAD_SIZE;   // one form of the branch at a time
   if (T == 0) return NV_OK;
-  add_rmsnorm_kernel<<<T, 256, 0, s>>>(x, branch, w, w_dt, eps, out, out_dt, out32, H);
+  NormArgs a;
+  a.x = x; a.branch = branch; a.w = w; a.out = out; a.out32 = out32; a.rows = rows; a.index = index;
+  a.weight = weight; a.dense = dense; a.gate_logit = gate_logit; a.gate_ld = gate_ld; a.eps = eps;
+  a.w_dt = w_dt; a.out_dt = out_dt; a.H = H; a.R = R;
+  if (H % 4 == 0) add_rmsnorm_kernel<4><<<T, NORM_THREADS, 0, s>>>(a);
+  else add_rmsnorm_kernel<1><<<T, NORM_THREADS, 0, s>>>(a);
   NV_RETURN_LAST();
 }
 

@@ -17,6 +17,10 @@ part                 what it must provide
 ``FeedForward``      ``wants_f32_input``; ``forward(h, h32, batch)`` -> float32 ``[T, hidden]``
 ===================  =======================================================================
 
+A branch output may also be a ``RowMix``: a weighted sum of rows that has not been taken yet.  A
+norm with ``accepts_mix`` sums it inside its own kernel; for every other consumer
+``resolve_branch`` takes the sum first, so a part never has to know about it.
+
 All parts also provide ``tensor_specs(available)`` (name -> shape and how to draw it at
 random) and ``load(fetch, ctx)``, which binds device tensors fetched by name.
 """
@@ -77,8 +81,40 @@ class Part:
 
 
 class Norm(Part):
+    accepts_mix: bool = False        # True: ``forward`` takes a ``RowMix`` as the branch
+
     def forward(self, x, branch, want_f32: bool = False):
         raise NotImplementedError
+
+
+@dataclass
+class RowMix:
+    """A branch output that is still a sum to be taken:
+    ``out[t] = sigmoid(gate_logit[t]) * dense[t] + sum_r weight[t, r] * rows[index[t, r]]``
+    (``dense`` and ``gate_logit`` may be None; without ``gate_logit`` the dense term is added as it is).
+    This is how experts' outputs are combined (src/hip_ops.hip:873-892, 926-934)."""
+    rows: torch.Tensor               # [R_total, hidden] float32
+    index: torch.Tensor              # [T, R] int32
+    weight: torch.Tensor             # [T, R] float32
+    dense: Optional[torch.Tensor] = None
+    gate_logit: Optional[torch.Tensor] = None
+
+    def sum(self) -> torch.Tensor:
+        from ..csrc import ops
+        T = self.index.shape[0]
+        out = torch.empty((T, self.rows.shape[1]), dtype=torch.float32, device=self.rows.device)
+        ops.moe_combine(self.rows, self.index, self.weight, self.dense, self.gate_logit, out)
+        return out
+
+    def as_tuple(self):
+        return (self.rows, self.index, self.weight, self.dense, self.gate_logit)
+
+
+def resolve_branch(norm: Norm, branch):
+    """What ``norm.forward`` may be given for ``branch``: the mix itself if the norm sums it, else its sum."""
+    if isinstance(branch, RowMix) and not norm.accepts_mix:
+        return branch.sum()
+    return branch
 
 
 class PositionEncoding(Part):

@@ -3,7 +3,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass, field
 
-from .base import PartSpec
+from .base import PartSpec, resolve_branch
 from .registry import register_part, build_part
 
 
@@ -41,9 +41,9 @@ class PreNormBlock:
                 (n["feed_forward"], self.feed_forward)]
 
     def forward(self, x, pending, batch, cache):
-        h, _ = self.norm1.forward(x, pending)
+        h, _ = self.norm1.forward(x, resolve_branch(self.norm1, pending))
         pending = self.mixer.forward(h, batch, cache)
-        h, h32 = self.norm2.forward(x, pending, want_f32=self.feed_forward.wants_f32_input)
+        h, h32 = self.norm2.forward(x, resolve_branch(self.norm2, pending), want_f32=self.feed_forward.wants_f32_input)
         pending = self.feed_forward.forward(h, h32, batch)
         return pending
 

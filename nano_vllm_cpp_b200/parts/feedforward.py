@@ -5,7 +5,7 @@ from __future__ import annotations
 import torch
 
 from ..csrc import ops
-from .base import FeedForward, TensorSpec
+from .base import FeedForward, RowMix, TensorSpec
 from .linear import linear, grouped_linear, small_linear
 from .registry import register_part
 
@@ -167,9 +167,8 @@ class SparseMoeSwiGLU(FeedForward):
             shared = linear(ctx, sact, self.sh_down, torch.float32)
             if gate_logit is None:
                 gate_logit = small_linear(ctx, h32, self.sh_gate)
-        out = torch.empty((T, self.hidden), dtype=torch.float32, device=dev)
-        ops.moe_combine(y, al.pair_pos, score, shared, gate_logit if shared is not None else None, out)
-        return out
+        # the combination (src/hip_ops.hip:873-892) is left to whoever takes the branch: the next norm sums it
+        return RowMix(y, al.pair_pos[:T * KT].view(T, KT), score, shared, gate_logit if shared is not None else None)
 
 
 def _cat(ts):

@@ -14,7 +14,7 @@ from typing import Optional
 import torch
 
 from ..csrc import ops
-from .base import PartSpec, RunContext, TensorSpec
+from .base import PartSpec, RunContext, TensorSpec, resolve_branch
 from .block import LayerSpec, build_layer
 from .linear import linear
 from .registry import build_part
@@ -124,7 +124,7 @@ class Model:
         pending = None
         for i, c in enumerate(self.calls):
             pending = self.layers[c.layer].forward(x, pending, batch, cache.view(i))
-        h, _ = self.final_norm.forward(x, pending)
+        h, _ = self.final_norm.forward(x, resolve_branch(self.final_norm, pending))
         n_want = batch.want_rows.numel()
         if n_want == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=ctx.device)

@@ -4,7 +4,7 @@ from __future__ import annotations
 import torch
 
 from ..csrc import ops
-from .base import Norm, TensorSpec
+from .base import Norm, RowMix, TensorSpec
 from .registry import register_part
 
 
@@ -12,7 +12,9 @@ class RMSNorm(Norm):
     """``x += branch; y = x * rsqrt(mean(x^2) + eps) * w`` (src/hip_ops.hip:395-417).
 
     The residual stream and the statistics are float32; ``y`` is written in the activation dtype.
+    A branch that is still a ``RowMix`` is summed by the same kernel.
     """
+    accepts_mix = True
 
     def __init__(self, size: int, eps: float):
         self.size, self.eps = size, float(eps)
@@ -29,7 +31,13 @@ class RMSNorm(Norm):
         out32 = None
         if want_f32:
             out32 = out if out.dtype == torch.float32 else torch.empty_like(x)
-        ops.add_rmsnorm(x, branch, self.weight, self.eps, out, None if out32 is out else out32)
+        mix = None
+        if isinstance(branch, RowMix):
+            if branch.index.shape[1] <= ops.ADD_RMSNORM_MAX_MIX:
+                mix, branch = branch.as_tuple(), None
+            else:
+                branch = branch.sum()
+        ops.add_rmsnorm(x, branch, self.weight, self.eps, out, None if out32 is out else out32, mix=mix)
         return out, out32
 
 

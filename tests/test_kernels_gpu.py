@@ -62,6 +62,20 @@ def test_add_rmsnorm(H, out_dtype):
     y = x.clone()
     o.add_rmsnorm(y, None, w, 1e-5, out)        # no branch: x unchanged
     assert torch.equal(y, x)
+    # the branch as a sum not yet taken: gate * dense + sum_r weight[t, r] * rows[index[t, r]]
+    for R, with_dense in ((3, True), (8, False), (1, True)):
+        rows, weight = rnd(50, H, seed=3), rnd(7, R, seed=4)
+        index = torch.randint(0, 50, (7, R), generator=torch.Generator().manual_seed(5), dtype=torch.int32).to(DEV)
+        dense, gate = (rnd(7, H, seed=6), rnd(7, 3, seed=7)) if with_dense else (None, None)
+        x1 = x0.clone()
+        o.add_rmsnorm(x1, None, w, 1e-5, out, out32, mix=(rows, index, weight, dense, None if gate is None else gate[:, 1:2]))
+        s = (weight.double()[:, :, None] * rows.double()[index.long()]).sum(1)
+        if with_dense:
+            s = s + torch.sigmoid(gate[:, 1].double())[:, None] * dense.double()
+        s = s + x0.double()
+        want = s * torch.rsqrt((s * s).mean(-1, keepdim=True) + 1e-5) * w.double()
+        close(x1, s, 2e-6, "residual after mix")
+        close(out32, want, 2e-6, "norm after mix")
 
 
 # ------------------------------------------------------------------------------- plain product

@@ -105,8 +105,9 @@ def test_sparse_moe_part(dtype, E, K, renorm, SI):
     part.load(DictFetch(W, dtype), ctx)
     h = (torch.randn(37, H, generator=torch.Generator().manual_seed(7))).to(torch.bfloat16)
     hd = h.to(dtype).to(DEV)
-    out = part.forward(hd, h.float().to(DEV), None)
+    mix = part.forward(hd, h.float().to(DEV), None)      # the experts' outputs, not yet summed
     ctx.err.check("moe")
+    out = mix.sum()
     cfg = dict(num_experts=E, num_experts_per_tok=K, norm_topk_prob=renorm, shared_expert_intermediate_size=SI,
                moe_intermediate_size=I)
     want = pm.sparse_mlp(h.double(), W, "", cfg)
@@ -119,7 +120,16 @@ def test_sparse_moe_part(dtype, E, K, renorm, SI):
         hidden_size=H, num_experts=E, top_k=K, intermediate_size=I, shared_intermediate_size=SI, renormalize=renorm)))
     assert set(part2.tensor_specs(lambda n: n in stacked)) == set(stacked)
     part2.load(DictFetch(stacked, dtype), ctx)
-    assert torch.equal(part2.forward(hd, h.float().to(DEV), None), out)
+    assert torch.equal(part2.forward(hd, h.float().to(DEV), None).sum(), out)
+    # the norm that takes the branch sums the mix itself: the same rows as the sum followed by the norm
+    norm = build_part("norm", PartSpec("rmsnorm", dict(size=H, eps=1e-6)))
+    norm.load(DictFetch({"weight": torch.linspace(0.5, 1.5, H)}, dtype), ctx)
+    x1 = torch.randn(37, H, generator=torch.Generator().manual_seed(8)).to(DEV)
+    x2 = x1.clone()
+    y1, _ = norm.forward(x1, mix)
+    y2, _ = norm.forward(x2, out)
+    close(x1, x2, 1e-6, "residual after mix")
+    close(y1.float(), y2.float(), 1e-6 if dtype == torch.float32 else 2 ** -7, "norm after mix")
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
