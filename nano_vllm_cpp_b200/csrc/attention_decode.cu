@@ -622,15 +622,25 @@ NV_API int nv_attention_decode_usable(int D, int page, int cache_dt) {
   return decode_stages(page, D, cache_dt == NV_DT_BF16 ? 2 : 4) > 0;
 }
 
-// Number of splits that fills `num_sms` multiprocessors a few times over for this many rows.
+// Number of splits for this many rows.  Blocks are short and all alike, so what counts is how full the last
+// wave of resident blocks is: the split count whose blocks fill whole waves best wins, with a small price per
+// split for its start-up and the merge.  Three blocks of the kernel live on a multiprocessor.
 NV_API int nv_attention_decode_splits(int rows, int Hq, int Hkv, int max_context, int num_sms) {
-  int G = Hq / Hkv;
-  int blocks = rows * Hkv * ((G + 15) / 16);
-  int want = (4 * num_sms + blocks - 1) / blocks;
+  if (const char* e = getenv("NV_DEC_SPLITS")) return atoi(e);      // experiments only
+  const int G = Hq / Hkv;
+  const long long slots = 3LL * num_sms;
+  const long long blocks = (long long)rows * Hkv * ((G + 15) / 16);
   int most = (max_context + 255) / 256;          // at least 256 keys per split
-  int s = want < most ? want : most;
-  if (s > 32) s = 32;
-  return s < 1 ? 1 : s;
+  if (most > 32) most = 32;
+  int best = 1;
+  double best_score = -1.0;
+  for (int s = 1; s <= most; ++s) {
+    const long long ctas = blocks * s;
+    const long long waves = (ctas + slots - 1) / slots;
+    const double score = (double)ctas / ((double)waves * (double)slots) - 0.01 * s;
+    if (score > best_score + 1e-9) { best_score = score; best = s; }
+  }
+  return best;
 }
 
 NV_API int nv_attention_decode(const void* qkv, int q_dt, int q_stride, const void* kc, const void* vc, int cache_dt,
