@@ -543,6 +543,7 @@ __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, 
   const int r = blockIdx.x, h = blockIdx.y;
   const int t = rows ? rows[r] : r;
   const size_t pi = ((size_t)r * Hq + h) * splits;
+  grid_dep_launch();
   float mm = -1e30f;
   for (int s = 0; s < splits; ++s) mm = fmaxf(mm, part_ml[(pi + s) * 2]);
   float ll = 0.f;

@@ -61,4 +61,13 @@ __device__ __forceinline__ float warp_max(float v) {
 // SiLU(g) * u exactly as the reference writes it: g / (1 + expf(-g)) * u  (src/hip_ops.hip:419-429).
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
 
+// Programmatic dependent launch.  A kernel launched with the programmatic-serialization attribute may start
+// while the kernel before it in the stream still runs; what it reads of that kernel's results, and whatever it
+// writes, must come after grid_dep_wait(), which returns once the earlier kernel has finished and its writes
+// are visible.  grid_dep_launch() in the earlier kernel says "my dependents may be scheduled now" (once every
+// CTA has said so or exited); without it they are scheduled as its CTAs exit.  Both are no-ops for kernels
+// launched the ordinary way.
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 static inline int dt_ok(int dt) { return dt == NV_DT_F32 || dt == NV_DT_BF16; }

@@ -8,6 +8,7 @@ build it) importing the ops fails with the reason.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_int, c_float, c_longlong, c_void_p
 
 import torch
@@ -513,13 +514,18 @@ def gemm_fast(a, w, out, *, bias=None, a_rows=None, swiglu=False, M=None, err=No
                         _p(bias), c_int(dt(bias) if bias is not None else 0), _p(out), c_int(dt(out)),
                         c_longlong(out.stride(0)), c_int(1 if swiglu else 0), c_int(n_tile), c_int(splits),
                         _p(scratch), _p(None), _p(None), _p(None), _p(None), c_int(0), c_int(0),
-                        _p(err.t if err is not None else _global_err().t), _stream()), "tc_gemm")
+                        _p(err.t if err is not None else _global_err().t), c_int(_early()), _stream()), "tc_gemm")
 
 
-def gemm_fast_grouped(a, w, out, align, *, a_rows=None, swiglu=False, err=None, tiles=None) -> None:
-    """Tensor-core form of the grouped ``gemm_plain``; ``tiles`` (a TileList of ``align``) picks the token tile."""
+def gemm_fast_grouped(a, w, out, align, *, a_rows=None, swiglu=False, err=None, tiles=None, tiles_ready=False) -> None:
+    """Tensor-core form of the grouped ``gemm_plain``; ``tiles`` (a TileList of ``align``) picks the token tile.
+
+    ``tiles_ready``: the tile lists were complete before the kernel that precedes this product on the stream
+    started, so the product may start beside that kernel and fetch its first weights (it reads the lists at
+    once).  With ``a_rows`` that holds by itself: the row copy comes between the routing and the product."""
     if a_rows is not None:
         a = permute_rows(a, a_rows, align.TK)
+        tiles_ready = True
     K = a.shape[1]
     E, rows_w = w.shape[0], w.shape[1]
     N = rows_w // 2 if swiglu else rows_w
@@ -530,8 +536,15 @@ def gemm_fast_grouped(a, w, out, align, *, a_rows=None, swiglu=False, err=None, 
                             c_int(K), _p(None), c_int(0), _p(out), c_int(dt(out)), c_longlong(out.stride(0)),
                             c_int(1 if swiglu else 0), c_int(tl.tile_m), c_int(1), _p(None), _p(tl.tile_expert),
                             _p(tl.tile_row0), _p(tl.tile_rows), _p(tl.num_tiles), c_int(tl.max_tiles),
-                            c_int(rows_w), _p(err.t if err is not None else _global_err().t), _stream()),
+                            c_int(rows_w), _p(err.t if err is not None else _global_err().t),
+                            c_int(_early() if tiles_ready else 0), _stream()),
            "tc_gemm_grouped")
+
+
+def _early() -> int:
+    """1: the tensor-core products are launched as programmatic dependents (NV_NO_EARLY=1 turns it off, for
+    comparisons)."""
+    return 0 if os.environ.get("NV_NO_EARLY") else 1
 
 
 _gerr = None

@@ -81,6 +81,7 @@ __global__ void __launch_bounds__(NORM_THREADS) add_rmsnorm_kernel(NormArgs a) {
   const int t = blockIdx.x, tid = threadIdx.x;
   const size_t base = (size_t)t * a.H;
   const int chunks = a.H / VEC;
+  grid_dep_launch();
   float gate = 1.f;
   if (a.R > 0) {
     if (tid < a.R) {

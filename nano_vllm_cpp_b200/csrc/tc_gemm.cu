@@ -19,7 +19,10 @@
 // The kernel is persistent (one or two CTAs per SM walk the tile list) with two accumulator sets in
 // TMEM, so a tile's epilogue overlaps the next tile's products.  Warp roles: warp 0 issues TMA
 // loads, warp 1 allocates TMEM and issues the MMAs, warps 2-5 read the accumulator back (tcgen05.ld)
-// and store.  Every wait on an mbarrier is bounded: after
+// and store.  Launched as a programmatic dependent (`early`), the kernel starts while its predecessor still runs
+// and fetches its first weights meanwhile; tokens are read, and anything is written, only after that kernel
+// has finished.  The caller may ask for it only if the tile lists of a grouped product were complete before
+// that predecessor started.  Every wait on an mbarrier is bounded: after
 // about two seconds a waiter records the fact in the error flag and goes on, so the kernel always
 // ends and frees its TMEM; its output is then garbage and the host raises.
 #include "pipeline.cuh"
@@ -56,6 +59,7 @@ struct TcArgs {
   int n_blocks;                       // blocks of w_per_cta features
   int acc_bufs;                       // accumulator sets in TMEM: 2 when two fit, else 1
   int tmem_cols;
+  int early;                          // launched as a programmatic dependent: weights are fetched before the wait
 };
 
 // ------------------------------------------------------------------ PTX wrappers (mbarriers: pipeline.cuh)
@@ -184,23 +188,41 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
+    // Launched early (a.early), the kernel may run beside the one before it: the weights of the first ring-full
+    // of k-steps are fetched at once, the tokens (that kernel's output) only after it has finished.
     if (lane == 0) {
-      int it = 0;                                  // k-steps issued so far, over all tiles
-      Tile t;
-      for (int tile = blockIdx.x; get_tile(a, tile, y_tiles, t); tile += gridDim.x) {
-        for (int k = 0; k < t.n_steps; ++k, ++it) {
-          const int s = it % a.stages;
-          mbar_wait(&empty_bar[s], ((it / a.stages) & 1) ^ 1, a.err, 0x7001);
-          uint8_t* st = smem + (size_t)s * stage_bytes;
-          mbar_expect_tx(&full_bar[s], stage_bytes);
-          const int kc = (t.k_begin + k) * BLOCK_K;
-          const int wr = t.w_row_base + t.nb * a.w_per_cta;
-          tma_load_2d(st, &tm_w, &full_bar[s], kc, wr);
-          if (two)     // swiglu: the up rows of the same features; dual: the next 128 features
-            tma_load_2d(st + a_bytes, &tm_w, &full_bar[s], kc, wr + (a.swiglu ? a.N : TILE_W));
-          tma_load_2d(st + a_bytes * (two ? 2 : 1), &tm_x, &full_bar[s], kc, t.row0);
+      const int pre = a.early ? a.stages : 0;
+      // issues the k-steps numbered [first, last) of this CTA's walk over its tiles
+      auto walk = [&](int first, int last, bool weights, bool tokens) {
+        int it = 0;
+        Tile t;
+        for (int tile = blockIdx.x; it < last && get_tile(a, tile, y_tiles, t); tile += gridDim.x) {
+          for (int k = 0; k < t.n_steps && it < last; ++k, ++it) {
+            if (it < first) continue;
+            const int s = it % a.stages;
+            uint8_t* st = smem + (size_t)s * stage_bytes;
+            if (weights) {
+              mbar_wait(&empty_bar[s], ((it / a.stages) & 1) ^ 1, a.err, 0x7001);
+              mbar_expect_tx(&full_bar[s], stage_bytes);
+            }
+            const int kc = (t.k_begin + k) * BLOCK_K;
+            const int wr = t.w_row_base + t.nb * a.w_per_cta;
+            if (weights) {
+              tma_load_2d(st, &tm_w, &full_bar[s], kc, wr);
+              if (two)     // swiglu: the up rows of the same features; dual: the next 128 features
+                tma_load_2d(st + a_bytes, &tm_w, &full_bar[s], kc, wr + (a.swiglu ? a.N : TILE_W));
+            }
+            if (tokens) tma_load_2d(st + a_bytes * (two ? 2 : 1), &tm_x, &full_bar[s], kc, t.row0);
+          }
         }
+      };
+      if (pre) {
+        walk(0, pre, true, false);
+        grid_dep_wait();
+        walk(0, pre, false, true);
       }
+      walk(pre, 0x7fffffff, true, true);
+      grid_dep_launch();          // all loads are on their way: the next kernel may take the SMs that fall idle
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
@@ -317,6 +339,7 @@ __global__ void permute_rows_bf16_kernel(const bf16* __restrict__ src, const int
   const int r = blockIdx.x;
   const uint4* s = (const uint4*)(src + (size_t)rows[r] * H);
   uint4* d = (uint4*)(dst + (size_t)r * H);
+  grid_dep_launch();
   for (int i = threadIdx.x; i < H / 8; i += blockDim.x) d[i] = s[i];
 }
 
@@ -431,7 +454,7 @@ NV_API int nv_tc_gemm(const void* X, long long ldx, int M_tok, const void* W, in
                       const void* bias, int bias_dt, void* out, int out_dt, long long ldo, int swiglu, int n_tile,
                       int splits, float* scratch, const int* tile_expert, const int* tile_row0,
                       const int* tile_rows, const int* num_tiles, int max_tiles, int rows_per_expert, int* err,
-                      cudaStream_t stream) {
+                      int early, cudaStream_t stream) {
   if (!dt_ok(out_dt) || (bias && !dt_ok(bias_dt))) return NV_ERR_BAD_DTYPE;
   if (K % 8 || ldx % 8 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return NV_ERR_UNSUPPORTED;  // TMA: 16-byte rules
   if (n_tile < 16 || n_tile > 256 || (n_tile & (n_tile - 1))) return NV_ERR_BAD_SIZE;
@@ -454,6 +477,7 @@ NV_API int nv_tc_gemm(const void* X, long long ldx, int M_tok, const void* W, in
   a.splits = splits < 1 ? 1 : splits;
   a.k_steps_per_split = (a.k_steps_total + a.splits - 1) / a.splits;
   a.n_tile = n_tile; a.swiglu = swiglu ? 1 : 0;
+  a.early = early ? 1 : 0;
   // Many tokens per tile and enough features: two weight tiles per CTA.  The operands then cost 2*16 KB + X
   // per k-step for twice the flops, which is what the shared-memory fill rate, the limit here, rewards.
   // ... provided the halved grid still covers the GPU (measured: a half-empty GPU loses more than the tile gains)
@@ -494,8 +518,25 @@ NV_API int nv_tc_gemm(const void* X, long long ldx, int M_tok, const void* W, in
   const long long total = (long long)a.n_blocks * y_tiles * a.splits;     // an upper bound when grouped
   const long long resident = (long long)num_sms * (pair ? 2 : 1);
   dim3 grid((unsigned)(total < resident ? total : resident));
-  tc_gemm_kernel<<<grid, NUM_THREADS, smem, stream>>>(tm_w, tm_x, a);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e;
+  if (a.early) {
+    // programmatic dependent of the kernel before it in the stream (an edge of that kind when captured)
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    e = cudaLaunchKernelEx(&cfg, tc_gemm_kernel, tm_w, tm_x, a);
+    if (e != cudaSuccess) return (int)e;
+  } else {
+    tc_gemm_kernel<<<grid, NUM_THREADS, smem, stream>>>(tm_w, tm_x, a);
+  }
+  e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
   if (a.splits > 1) {
     const long long outputs = (long long)M_tok * N;

@@ -160,7 +160,8 @@ class SparseMoeSwiGLU(FeedForward):
         else:
             act = grouped_linear(ctx, h, self.w_gate_up, ctx.act_dtype, al, a_rows=al.sorted_token, swiglu=True,
                                  tiles=wide)
-        y = grouped_linear(ctx, act, self.w_down, torch.float32, al)
+        # the tile lists were final before the first product started: the second may start beside it
+        y = grouped_linear(ctx, act, self.w_down, torch.float32, al, tiles_ready=True)
         shared = None
         if self.shared_inter > 0 and not C:
             sact = linear(ctx, h, self.sh_gate_up, ctx.act_dtype, swiglu=True)

@@ -37,7 +37,7 @@ def small_linear(ctx, a32, w):
     return out
 
 
-def grouped_linear(ctx, a, w, out_dtype, align, *, a_rows=None, swiglu=False, tiles=None):
+def grouped_linear(ctx, a, w, out_dtype, align, *, a_rows=None, swiglu=False, tiles=None, tiles_ready=False):
     """Per-expert product over an expert-sorted row list: row r of the output belongs to the expert
     whose segment of ``align`` holds r and is ``a[a_rows[r]] @ w[expert].T``."""
     rows_w = w.shape[1]
@@ -46,7 +46,8 @@ def grouped_linear(ctx, a, w, out_dtype, align, *, a_rows=None, swiglu=False, ti
     if align.TK == 0:
         return out
     if ctx.fast_kernels and ops.gemm_fast_usable(a, w, out, a_rows=a_rows, swiglu=swiglu, grouped=True):
-        ops.gemm_fast_grouped(a, w, out, align, a_rows=a_rows, swiglu=swiglu, err=ctx.err, tiles=tiles)
+        ops.gemm_fast_grouped(a, w, out, align, a_rows=a_rows, swiglu=swiglu, err=ctx.err, tiles=tiles,
+                              tiles_ready=tiles_ready)
     else:
         ops.gemm_plain(a, w, out, a_rows=a_rows, swiglu=swiglu, M=align.TK, tiles=align.tiles)
     return out
