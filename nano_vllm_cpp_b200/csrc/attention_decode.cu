@@ -104,6 +104,8 @@ __global__ void __launch_bounds__((WARPS + 1) * 32) attention_decode_kernel(DecA
     }
     mbar_fence_init();
   }
+  grid_dep_wait();              // the queries and the newest keys come from the kernel before
+  grid_dep_launch();
   for (int i = threadIdx.x; i < ng * D; i += (WARPS + 1) * 32) {
     int g = i / D, d = i % D;
     q_s[g][d] = ld_dt(a.qkv, a.q_dt, (size_t)t * a.q_stride + (size_t)(kvh * G + g0 + g) * D + d) * a.scale;
@@ -352,6 +354,8 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
     }
     mbar_fence_init();
   }
+  grid_dep_wait();              // the queries and the newest keys come from the kernel before
+  grid_dep_launch();
   for (int i = threadIdx.x; i < TC_ROWS * D; i += (WARPS + 1) * 32) {
     const int g = i / D, d = i % D;
     float v = 0.f;
@@ -543,6 +547,7 @@ __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, 
   const int r = blockIdx.x, h = blockIdx.y;
   const int t = rows ? rows[r] : r;
   const size_t pi = ((size_t)r * Hq + h) * splits;
+  grid_dep_wait();
   grid_dep_launch();
   float mm = -1e30f;
   for (int s = 0; s < splits; ++s) mm = fmaxf(mm, part_ml[(pi + s) * 2]);
@@ -566,7 +571,7 @@ int launch_decode_g(const DecArgs& a, int R, int G, size_t smem, cudaStream_t s)
     attr_done = true;
   }
   dim3 grid(R, a.Hkv * ((G + GB - 1) / GB), a.splits);
-  attention_decode_kernel<TC, CPL, GB><<<grid, (WARPS + 1) * 32, smem, s>>>(a);
+  NV_RETURN_IF(launch_dep(attention_decode_kernel<TC, CPL, GB>, grid, dim3((WARPS + 1) * 32), smem, s, a));
   NV_RETURN_LAST();
 }
 
@@ -596,7 +601,7 @@ int launch_decode_tc(DecArgs a, int R, const void* kc, const void* vc, int num_p
     attr_done = true;
   }
   dim3 grid(R, a.Hkv * ((G + TC_ROWS - 1) / TC_ROWS), a.splits);
-  attention_decode_tc_kernel<D><<<grid, (WARPS + 1) * 32, smem, s>>>(tm_k, tm_v, a);
+  NV_RETURN_IF(launch_dep(attention_decode_tc_kernel<D>, grid, dim3((WARPS + 1) * 32), smem, s, tm_k, tm_v, a));
   NV_RETURN_LAST();
 }
 
@@ -693,7 +698,8 @@ NV_API int nv_attention_decode(const void* qkv, int q_dt, int q_stride, const vo
   if (rc) return rc;
   if (splits > 1) {
     dim3 grid(R, Hq);
-    attention_decode_merge_kernel<<<grid, 128, 0, stream>>>(a.part_o, a.part_ml, rows, out, out_dt, Hq, D, splits);
+    NV_RETURN_IF(launch_dep(attention_decode_merge_kernel, grid, dim3(128), 0, stream, (const float*)a.part_o,
+                            (const float*)a.part_ml, rows, out, out_dt, Hq, D, splits));
   }
   NV_RETURN_LAST();
 }

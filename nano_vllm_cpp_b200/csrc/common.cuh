@@ -9,6 +9,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <utility>
+
 #define NV_DT_F32 0
 #define NV_DT_BF16 1
 
@@ -69,5 +71,36 @@ __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f +
 // launched the ordinary way.
 __device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Launches `kernel` as a programmatic dependent of the kernel before it on the stream (an ordinary launch
+// when nv_set_dependent_launch(0) was called).  Such a kernel must call grid_dep_wait() before it reads anything
+// an earlier kernel of the step wrote and before it writes anything, and calls grid_dep_launch() right after,
+// so that at most one kernel is ever set up ahead of the one that runs: everything older has finished by then.
+// Grids of more than NV_DEP_MAX_BLOCKS blocks are launched the ordinary way: their waiting blocks would crowd
+// the multiprocessors on which the kernel before them is still finishing (measured: a prompt of 2,048 tokens
+// ran 7 % slower with every kernel a dependent), and a launch latency is nothing beside such a kernel's time.
+constexpr unsigned NV_DEP_MAX_BLOCKS = 2048;
+extern int g_nv_dependent_launch;
+template <typename... Exp, typename... Act>
+static inline cudaError_t launch_dep(void (*kernel)(Exp...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                     Act&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  const unsigned long long blocks = (unsigned long long)grid.x * grid.y * grid.z;
+  attr[0].val.programmaticStreamSerializationAllowed = (g_nv_dependent_launch && blocks <= NV_DEP_MAX_BLOCKS) ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<Exp>(args)...);
+}
+#define NV_RETURN_IF(e)                            \
+  do {                                             \
+    cudaError_t e2__ = (e);                        \
+    if (e2__ != cudaSuccess) return (int)e2__;     \
+  } while (0)
 
 static inline int dt_ok(int dt) { return dt == NV_DT_F32 || dt == NV_DT_BF16; }

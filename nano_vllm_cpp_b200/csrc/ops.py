@@ -36,6 +36,7 @@ def lib() -> ctypes.CDLL:
             _lib = ctypes.CDLL(path)
         except OSError as e:
             raise KernelError(f"cannot load the CUDA library {path}: {e}") from None
+        _lib.nv_set_dependent_launch(c_int(_early()))
     return _lib
 
 

@@ -6,6 +6,8 @@
 #include "common.cuh"
 #include "moe_route.cuh"
 
+int g_nv_dependent_launch = 1;
+
 namespace {
 
 // ------------------------------------------------------------------ embedding
@@ -81,6 +83,7 @@ __global__ void __launch_bounds__(NORM_THREADS) add_rmsnorm_kernel(NormArgs a) {
   const int t = blockIdx.x, tid = threadIdx.x;
   const size_t base = (size_t)t * a.H;
   const int chunks = a.H / VEC;
+  grid_dep_wait();
   grid_dep_launch();
   float gate = 1.f;
   if (a.R > 0) {
@@ -188,6 +191,8 @@ __global__ void __launch_bounds__(256) rope_store_kernel(void* __restrict__ qkv,
                                   const int* __restrict__ row_entry, int Hq, int Hkv, int D, int page,
                                   int write_kv, int hpb, int* __restrict__ err) {
   __shared__ float cs[128], sn[128];
+  grid_dep_wait();
+  grid_dep_launch();
   const int t = blockIdx.x;
   const int h_begin = blockIdx.y * hpb;
   const int h_end = min(Hq + 2 * Hkv, h_begin + hpb);
@@ -507,8 +512,8 @@ NV_API int nv_add_rmsnorm(float* x, const float* branch, const void* w, int w_dt
   a.x = x; a.branch = branch; a.w = w; a.out = out; a.out32 = out32; a.rows = rows; a.index = index;
   a.weight = weight; a.dense = dense; a.gate_logit = gate_logit; a.gate_ld = gate_ld; a.eps = eps;
   a.w_dt = w_dt; a.out_dt = out_dt; a.H = H; a.R = R;
-  if (H % 4 == 0) add_rmsnorm_kernel<4><<<T, NORM_THREADS, 0, s>>>(a);
-  else add_rmsnorm_kernel<1><<<T, NORM_THREADS, 0, s>>>(a);
+  if (H % 4 == 0) NV_RETURN_IF(launch_dep(add_rmsnorm_kernel<4>, dim3(T), dim3(NORM_THREADS), 0, s, a));
+  else NV_RETURN_IF(launch_dep(add_rmsnorm_kernel<1>, dim3(T), dim3(NORM_THREADS), 0, s, a));
   NV_RETURN_LAST();
 }
 
@@ -524,8 +529,9 @@ NV_API int nv_rope_store(void* qkv, int dt, const int* positions, const float* i
   const int heads = Hq + 2 * Hkv;
   const int hpb = T >= 256 ? heads : 4;
   dim3 grid(T, (heads + hpb - 1) / hpb);
-  rope_store_kernel<<<grid, T >= 256 ? 256 : 128, 0, s>>>(qkv, dt, positions, inv_freq, rotary_dim, kc, vc, cache_dt,
-                                             block_table, max_blocks, row_entry, Hq, Hkv, D, page, write_kv, hpb, err);
+  NV_RETURN_IF(launch_dep(rope_store_kernel, grid, dim3(T >= 256 ? 256 : 128), 0, s, qkv, dt, positions, inv_freq,
+                          rotary_dim, kc, vc, cache_dt, block_table, max_blocks, row_entry, Hq, Hkv, D, page, write_kv,
+                          hpb, err));
   NV_RETURN_LAST();
 }
 
@@ -597,3 +603,7 @@ NV_API int nv_sample(const float* logits, int R, int V, const float* temperature
   sample_kernel<<<R, SAMPLE_THREADS, 0, s>>>(logits, V, temperature, u, out);
   NV_RETURN_LAST();
 }
+
+// 0: every kernel is launched the ordinary way (each starts when the one before it has ended); 1 (the default):
+// the kernels of a step are launched as programmatic dependents, see launch_dep.
+NV_API void nv_set_dependent_launch(int on) { g_nv_dependent_launch = on ? 1 : 0; }

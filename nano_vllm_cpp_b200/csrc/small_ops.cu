@@ -15,6 +15,8 @@ __global__ void __launch_bounds__(256) rowdot_kernel(const float* __restrict__ a
                                                      const TW* __restrict__ w, float* __restrict__ out,
                                                      long long ldo, int N, int K) {
   __shared__ float part[8][4];
+  grid_dep_wait();
+  grid_dep_launch();
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const int t = blockIdx.x, n0 = blockIdx.y * 4;
   const float* ar = a + (size_t)t * lda;
@@ -145,6 +147,8 @@ __global__ void __launch_bounds__(1024) moe_route_small_kernel(
     int* __restrict__ tile_rows, int* __restrict__ num_tiles, int* __restrict__ err,
     const bf16* __restrict__ x, bf16* __restrict__ x_sorted, int H) {
   extern __shared__ double rs_smem[];
+  grid_dep_wait();
+  grid_dep_launch();
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const int KT = K + C;
   for (int t = warp; t < T; t += 32)
@@ -193,8 +197,8 @@ NV_API int nv_rowdot(const float* a, long long lda, const void* w, int w_dt, flo
   }
   if ((N + 3) / 4 > 65535) return NV_ERR_BAD_SIZE;
   dim3 grid(T, (N + 3) / 4);
-  if (w_dt == NV_DT_F32) rowdot_kernel<float><<<grid, 256, 0, s>>>(a, lda, (const float*)w, out, ldo, N, K);
-  else rowdot_kernel<bf16><<<grid, 256, 0, s>>>(a, lda, (const bf16*)w, out, ldo, N, K);
+  if (w_dt == NV_DT_F32) NV_RETURN_IF(launch_dep(rowdot_kernel<float>, grid, dim3(256), 0, s, a, lda, (const float*)w, out, ldo, N, K));
+  else NV_RETURN_IF(launch_dep(rowdot_kernel<bf16>, grid, dim3(256), 0, s, a, lda, (const bf16*)w, out, ldo, N, K));
   NV_RETURN_LAST();
 }
 
@@ -212,8 +216,8 @@ NV_API int nv_moe_route_small(const float* logits, long long ld, int T, int E, i
   if (!nv_moe_route_small_usable(T, E, K, C, H) || K < 1 || K > E || (C > 0 && !gate_logit)) return NV_ERR_UNSUPPORTED;
   if (T == 0) return NV_OK;
   const size_t smem = (size_t)32 * E * sizeof(double) + (size_t)4 * (E + C) * sizeof(int);
-  moe_route_small_kernel<<<1, 1024, smem, s>>>(logits, ld, T, E, K, renorm, C, gate_logit, gate_ld, idx, score, tile_m,
-                                               counts, offsets, sorted_token, pair_pos, tile_expert, tile_row0,
-                                               tile_rows, num_tiles, err, (const bf16*)x, (bf16*)x_sorted, H);
+  NV_RETURN_IF(launch_dep(moe_route_small_kernel, dim3(1), dim3(1024), smem, s, logits, ld, T, E, K, renorm, C,
+                          gate_logit, gate_ld, idx, score, tile_m, counts, offsets, sorted_token, pair_pos, tile_expert,
+                          tile_row0, tile_rows, num_tiles, err, (const bf16*)x, (bf16*)x_sorted, H));
   NV_RETURN_LAST();
 }

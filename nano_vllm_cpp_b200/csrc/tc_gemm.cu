@@ -317,6 +317,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
 __global__ void tc_gemm_finish_kernel(const float* __restrict__ partial, int splits, int M_tok, int N, int swiglu,
                                       const void* __restrict__ bias, int bias_dt, void* __restrict__ out, int out_dt,
                                       long long ldo) {
+  grid_dep_wait();
+  grid_dep_launch();
   const int width = swiglu ? 2 * N : N;
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= (long long)M_tok * N) return;
@@ -336,10 +338,11 @@ __global__ void tc_gemm_finish_kernel(const float* __restrict__ partial, int spl
 // out[r, :] = src[rows[r], :] for bf16 rows (the expert-sorted copy of the activations)
 __global__ void permute_rows_bf16_kernel(const bf16* __restrict__ src, const int* __restrict__ rows,
                                          bf16* __restrict__ dst, int H) {
+  grid_dep_wait();
+  grid_dep_launch();
   const int r = blockIdx.x;
   const uint4* s = (const uint4*)(src + (size_t)rows[r] * H);
   uint4* d = (uint4*)(dst + (size_t)r * H);
-  grid_dep_launch();
   for (int i = threadIdx.x; i < H / 8; i += blockDim.x) d[i] = s[i];
 }
 
@@ -528,7 +531,7 @@ NV_API int nv_tc_gemm(const void* X, long long ldx, int M_tok, const void* W, in
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[0].val.programmaticStreamSerializationAllowed = g_nv_dependent_launch ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     e = cudaLaunchKernelEx(&cfg, tc_gemm_kernel, tm_w, tm_x, a);
@@ -540,8 +543,8 @@ NV_API int nv_tc_gemm(const void* X, long long ldx, int M_tok, const void* W, in
   if (e != cudaSuccess) return (int)e;
   if (a.splits > 1) {
     const long long outputs = (long long)M_tok * N;
-    tc_gemm_finish_kernel<<<(unsigned)((outputs + 255) / 256), 256, 0, stream>>>(scratch, a.splits, M_tok, N, a.swiglu,
-                                                                              bias, bias_dt, out, out_dt, ldo);
+    NV_RETURN_IF(launch_dep(tc_gemm_finish_kernel, dim3((unsigned)((outputs + 255) / 256)), dim3(256), 0, stream,
+                            (const float*)scratch, a.splits, M_tok, N, a.swiglu, bias, bias_dt, out, out_dt, ldo));
   }
   NV_RETURN_LAST();
 }
@@ -549,6 +552,6 @@ NV_API int nv_tc_gemm(const void* X, long long ldx, int M_tok, const void* W, in
 NV_API int nv_permute_rows_bf16(const void* src, const int* rows, void* dst, int R, int H, cudaStream_t stream) {
   if (H % 8 || ((uintptr_t)src & 15) || ((uintptr_t)dst & 15)) return NV_ERR_UNSUPPORTED;
   if (R == 0) return NV_OK;
-  permute_rows_bf16_kernel<<<R, 128, 0, stream>>>((const bf16*)src, rows, (bf16*)dst, H);
+  NV_RETURN_IF(launch_dep(permute_rows_bf16_kernel, dim3(R), dim3(128), 0, stream, (const bf16*)src, rows, (bf16*)dst, H));
   NV_RETURN_LAST();
 }
