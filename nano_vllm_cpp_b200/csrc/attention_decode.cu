@@ -354,17 +354,24 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
     }
     mbar_fence_init();
   }
-  grid_dep_wait();              // the queries and the newest keys come from the kernel before
-  grid_dep_launch();
-  for (int i = threadIdx.x; i < TC_ROWS * D; i += (WARPS + 1) * 32) {
-    const int g = i / D, d = i % D;
-    float v = 0.f;
-    if (g < ng) v = ld_dt(a.qkv, a.q_dt, (size_t)t * a.q_stride + (size_t)(kvh * G + g0 + g) * D + d);
-    q_s[g * QLD + d] = __float2bfloat16_rn(v);
-  }
+  // Launched as a programmatic dependent, the kernel may run beside the one that rotates the queries and writes
+  // the newest key and value.  The block table and the positions are inputs of the whole step; every page but
+  // the one that holds position n - 1 is final.  So the producer starts on the older pages at once, and the
+  // queries, the newest page and all writes come after the wait.
   const int* bt = a.block_table + (size_t)a.row_entry[t] * a.max_blocks;
   for (int i = threadIdx.x; i < min(n_pages, BT_CACHE); i += (WARPS + 1) * 32) bt_s[i] = bt[pb + i];
   __syncthreads();
+  if (warp < WARPS) {
+    grid_dep_wait();
+    grid_dep_launch();
+    for (int i = threadIdx.x; i < TC_ROWS * D; i += WARPS * 32) {
+      const int g = i / D, d = i % D;
+      float v = 0.f;
+      if (g < ng) v = ld_dt(a.qkv, a.q_dt, (size_t)t * a.q_stride + (size_t)(kvh * G + g0 + g) * D + d);
+      q_s[g * QLD + d] = __float2bfloat16_rn(v);
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(WARPS * 32) : "memory");      // the consumer warps only
+  }
 
   const int g = lane / 4, tq = lane % 4;
   float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
@@ -373,12 +380,22 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
   if (warp == WARPS) {
     // ---------------------------------------------------------------- producer
     if (lane == 0) {
+      const int newest = (n - 1) / a.page - pb;          // this split's page that is still being written
+      bool waited = false;
       for (int i = 0; i < n_pages; ++i) {
         const int s = i % a.stages;
+        if (!waited && (i >= a.stages || i == newest)) {
+          grid_dep_wait();
+          waited = true;
+        }
         mbar_wait(&empty_bar[s], ((i / a.stages) & 1) ^ 1, a.err, 0x7111);
         const int blk = i < BT_CACHE ? bt_s[i] : bt[pb + i];
         uint8_t* st = dec_smem + (size_t)s * stage_bytes;
         if (blk < 0) {
+          if (!waited) {
+            grid_dep_wait();
+            waited = true;
+          }
           if (a.err) atomicExch(a.err, 1 + t);
           mbar_arrive(&full_bar[s]);
           continue;
