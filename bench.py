@@ -234,12 +234,6 @@ def main() -> int:
                 "frac": round(achieved / P["hbm_gbs"], 4), "of": peak_src,
                 "bytes_per_step": rbytes, "distinct_experts_per_layer": round(sum(distinct) / max(1, len(distinct)), 1)}
 
-    points = {}
-    if not args.no_points:
-        for B in (1, 64):
-            pms, _, _, _ = decode_device(B, max(8, args.steps // 2), args.warmup)
-            points[f"decode_b{B}"] = round(B / pms * 1e3, 1)
-
     # ------------------------------------------------------------------ end to end through LLMEngine.step
     e2e = None
     if not args.no_e2e:
@@ -263,10 +257,16 @@ def main() -> int:
             n += len(out.new_tokens)
         torch.cuda.synchronize()
         dt = time.perf_counter() - t0
-        e2e = {"value": round(n / dt, 1), "unit": "tokens/s", "h2d_bytes_per_step": eng.runner.last_h2d_bytes + B * 12,
+        e2e = {"value": round(n / dt, 1), "unit": "tokens/s", "h2d_bytes_per_step": eng.runner.last_h2d_bytes,
                "d2h_bytes_per_step": B * 4 + 4}
         while not eng.is_finished():      # let them run out (a few more steps)
             eng.step()
+
+    points = {}
+    if not args.no_points:
+        for B in (1, 64):
+            pms, _, _, _ = decode_device(B, max(8, args.steps // 2), args.warmup)
+            points[f"decode_b{B}"] = round(B / pms * 1e3, 1)
 
     line = {
         "metric": "decode tok/s (batch 8, 2,048-token context); prefill tok/s at 2,048 tokens; % of roofline",

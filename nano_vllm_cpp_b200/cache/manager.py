@@ -193,6 +193,37 @@ class CacheManager:
             raise KeyError(rid)
         return int(n)
 
+    def prepare_step(self, entries: list, max_blocks: int, max_model_len: int, sampling: bool, buf: np.ndarray):
+        """Takes the pages that the entries' next rows need and writes the step's index arrays into ``buf`` (int32)
+        in the layout of ``engine.batch.batch_layout``.  ``entries``: objects with ``rid``, ``tokens``, ``want`` of
+        open requests.  Returns (ints used, [(slot, first position)] per entry, native ids)."""
+        S = len(entries)
+        rids = (ctypes.c_int64 * max(S, 1))(*[self._native(e.rid) for e in entries])
+        lens = (ctypes.c_int * max(S, 1))(*[len(e.tokens) for e in entries])
+        flat = [t for e in entries for t in e.tokens]
+        tokens = (ctypes.c_int * max(len(flat), 1))(*flat)
+        cu, wants = [0], []
+        for e in entries:
+            wants.extend(e.want)
+            cu.append(len(wants))
+        wants_cu = (ctypes.c_int * (S + 1))(*cu)
+        wants_a = (ctypes.c_int * max(len(wants), 1))(*wants)
+        info = (ctypes.c_int * max(2 * S, 1))()
+        n = host.lib().nvh_prepare_step(self._h, S, rids, lens, tokens, wants_cu, wants_a, max_blocks, max_model_len,
+                                        1 if sampling else 0, buf.ctypes.data_as(ctypes.c_void_p), buf.shape[0], info)
+        if n < 0:
+            if n == host.ERR_STATE:
+                raise ValueError(host.last_error())
+            self._raise(n)
+        return int(n), [(info[2 * i], info[2 * i + 1]) for i in range(S)], rids
+
+    def commit_many(self, native_ids, ends: list) -> None:
+        """``commit`` for many requests at once (``native_ids`` as returned by ``prepare_step``); no page hashing."""
+        S = len(ends)
+        rc = host.lib().nvh_commit_many(self._h, S, native_ids, (ctypes.c_int * max(S, 1))(*ends))
+        if rc:
+            self._raise(rc)
+
     # ------------------------------------------------------------------ prefix sharing
     def match_prefix(self, tokens) -> list:
         """Pages holding the longest cached prefix of ``tokens`` as (page, hash) pairs; never the page that

@@ -617,6 +617,111 @@ NVH_API int nvh_rename(void* m, int64_t from, int64_t to) {      // the same cac
 }
 NVH_API int nvh_manager_check(void* m) { return ((CacheManager*)m)->check(); }
 
+// Rows up to ends[i] of request rids[i] have run (no hashing of pages: the caller that wants it commits one by one).
+NVH_API int nvh_commit_many(void* m, int S, const int64_t* rids, const int* ends) {
+  CacheManager* cm = (CacheManager*)m;
+  for (int i = 0; i < S; ++i) {
+    const int r = cm->commit(rids[i], ends[i], nullptr, 0);
+    if (r) return r;
+  }
+  return OK;
+}
+
+// ---- the index arrays of one step
+// Layout of the one int32 buffer that carries a step's index arrays to the device, every segment starting on a
+// multiple of four ints: ids[T] pos[T] row_entry[T] cu[S+1] pos0[S] slot[S] want[W], one block table
+// [S][max_blocks] per group, and with `sampling` temp[W] (float bits) and u[2W] (doubles).  offsets[] receives
+// the 7 + groups (+ 2) segment starts; the return value is the buffer's length in ints.
+static inline int align4(int n) { return (n + 3) & ~3; }
+NVH_API int nvh_step_layout(int S, int T, int W, int groups, int max_blocks, int sampling, int* offsets) {
+  int off = 0, k = 0;
+  const int lens[7] = {T, T, T, S + 1, S, S, W};
+  for (int i = 0; i < 7; ++i) {
+    if (offsets) offsets[k] = off;
+    ++k;
+    off = align4(off + lens[i]);
+  }
+  for (int g = 0; g < groups; ++g) {
+    if (offsets) offsets[k] = off;
+    ++k;
+    off = align4(off + S * max_blocks);
+  }
+  if (sampling) {
+    if (offsets) offsets[k] = off;
+    ++k;
+    off = align4(off + W);
+    if (offsets) offsets[k] = off;
+    ++k;
+    off = align4(off + 2 * W);
+  }
+  return off < 4 ? 4 : off;
+}
+
+// Takes the pages that the entries' next rows need and writes the step's arrays into `buf` (cap ints, filled
+// with -1 first).  Entry i is request rids[i] with lens[i] next tokens (tokens[] holds them back to back) whose
+// wanted places are wants[wants_cu[i] .. wants_cu[i+1]).  info[2i], info[2i+1] receive the entry's state slot and
+// first position.  Requests must be open.  Returns the length used, or an error (the entries before the failing
+// one keep the pages they took: taking them again is harmless).
+NVH_API int nvh_prepare_step(void* m, int S, const int64_t* rids, const int* lens, const int* tokens,
+                             const int* wants_cu, const int* wants, int max_blocks, int max_model_len, int sampling,
+                             int* buf, int cap, int* info) {
+  CacheManager* cm = (CacheManager*)m;
+  const int G = (int)cm->pools.size();
+  int T = 0;
+  for (int i = 0; i < S; ++i) {
+    if (lens[i] < 1) return fail(ERR_STATE, "an entry needs at least one token");
+    T += lens[i];
+  }
+  const int W = wants_cu[S];
+  int off[7 + 64 + 2];
+  if (G > 64) return fail(ERR_STATE, "too many cache groups");
+  const int total = nvh_step_layout(S, T, W, G, max_blocks, sampling, off);
+  if (total > cap) return fail(ERR_STATE, "the step's arrays do not fit the staging buffer");
+  std::fill(buf, buf + total, -1);
+  int* ids = buf + off[0];
+  int* pos = buf + off[1];
+  int* row_entry = buf + off[2];
+  int* cu = buf + off[3];
+  int* pos0 = buf + off[4];
+  int* slot = buf + off[5];
+  int* want = buf + off[6];
+  int row = 0;
+  cu[0] = 0;
+  for (int i = 0; i < S; ++i) {
+    RequestCache* rc = cm->find(rids[i]);
+    if (!rc) return fail(ERR_STATE, "request is not open");
+    const int start = rc->num_tokens, n = lens[i], end = start + n;
+    if (end > max_model_len)
+      return fail(ERR_STATE, "request " + std::to_string(rids[i]) + ": " + std::to_string(end) +
+                                 " tokens exceed the longest sequence " + std::to_string(max_model_len));
+    const int r = cm->extend(rids[i], start, end);
+    if (r) return r;
+    for (int j = 0; j < n; ++j) {
+      ids[row + j] = tokens[row + j];
+      pos[row + j] = start + j;
+      row_entry[row + j] = i;
+    }
+    for (int w = wants_cu[i]; w < wants_cu[i + 1]; ++w) {
+      if (wants[w] < 0 || wants[w] >= n)
+        return fail(ERR_STATE, "wanted place " + std::to_string(wants[w]) + " is not among the entry's " +
+                                   std::to_string(n) + " tokens");
+      want[w] = row + wants[w];
+    }
+    pos0[i] = start;
+    slot[i] = rc->slot;
+    info[2 * i] = rc->slot;
+    info[2 * i + 1] = start;
+    for (int g = 0; g < G; ++g) {
+      const auto& t = rc->tables[g];
+      if ((int)t.size() > max_blocks) return fail(ERR_STATE, "a request holds more pages than the block table is wide");
+      std::memcpy(buf + off[7 + g] + (size_t)i * max_blocks, t.data(), sizeof(int) * t.size());
+    }
+    row += n;
+    cu[i + 1] = row;
+  }
+  return total;
+}
+
 // ---- the scheduler
 NVH_API void* nvs_create(void* manager, int max_num_seqs, int max_batched_tokens, int max_model_len, int eos,
                          int prefill_chunk) {

@@ -46,6 +46,9 @@ class StepBatch:
     max_context: int                # largest pos0 + length
     decode_only: bool               # every entry has one row
     h2d_bytes: int = 0              # bytes of index arrays copied to the device for this step
+    temperatures: torch.Tensor = None   # [n_want] float32, when the step also samples
+    uniforms: torch.Tensor = None       # [n_want] float64
+    native_ids: object = None           # the entries' request ids as the native cache manager knows them
 
 
 def _align4(n: int) -> int:
@@ -63,36 +66,49 @@ class BatchStager:
         self.events = [None] * depth
         self.at = 0
 
+    def acquire(self, n: int):
+        """The next buffer of the ring as (ticket, int32 numpy array of at least ``n``), free to be written."""
+        i = self.at
+        self.at = (self.at + 1) % self.depth
+        cuda = self.device.type == "cuda"
+        if cuda and self.events[i] is not None:
+            self.events[i].synchronize()
+        if self.bufs[i] is None or self.bufs[i].numel() < n:
+            t = torch.empty(max(n, 1024), dtype=torch.int32)
+            self.bufs[i] = t.pin_memory() if cuda else t
+        return i, self.bufs[i].numpy()
+
+    def submit(self, ticket: int, n: int, static_dev=None) -> torch.Tensor:
+        """Copies the first ``n`` ints of an acquired buffer to the device: into ``static_dev`` if given, else
+        into a new tensor."""
+        src = self.bufs[ticket][:n]
+        if self.device.type != "cuda":
+            if static_dev is not None:
+                static_dev[:n].copy_(src)
+                return static_dev
+            return src.clone()
+        if static_dev is not None:
+            static_dev[:n].copy_(src, non_blocking=True)
+            dev = static_dev
+        else:
+            dev = src.to(self.device, non_blocking=True)
+        if self.events[ticket] is None:
+            self.events[ticket] = torch.cuda.Event()
+        self.events[ticket].record()
+        return dev
+
     def stage(self, host: np.ndarray, static_dev=None) -> torch.Tensor:
         """Copies ``host`` (int32) to the device: into ``static_dev`` if given, else into a new tensor."""
         n = host.shape[0]
-        if self.device.type != "cuda":
-            t = torch.from_numpy(host.copy())
-            if static_dev is not None:
-                static_dev[:n].copy_(t)
-                return static_dev
-            return t
-        i = self.at
-        self.at = (self.at + 1) % self.depth
-        if self.events[i] is not None:
-            self.events[i].synchronize()
-        if self.bufs[i] is None or self.bufs[i].numel() < n:
-            self.bufs[i] = torch.empty(max(n, 1024), dtype=torch.int32).pin_memory()
-        pinned = self.bufs[i]
-        pinned.numpy()[:n] = host
-        if static_dev is not None:
-            static_dev[:n].copy_(pinned[:n], non_blocking=True)
-            dev = static_dev
-        else:
-            dev = pinned[:n].to(self.device, non_blocking=True)
-        if self.events[i] is None:
-            self.events[i] = torch.cuda.Event()
-        self.events[i].record()
-        return dev
+        ticket, buf = self.acquire(n)
+        buf[:n] = host
+        return self.submit(ticket, n, static_dev)
 
 
-def batch_layout(S: int, T: int, n_want: int, G: int, max_blocks: int):
-    """Offsets of the index arrays inside the one int32 buffer of a step: name -> (offset, length)."""
+def batch_layout(S: int, T: int, n_want: int, G: int, max_blocks: int, sampling: bool = False):
+    """Offsets of the index arrays inside the one int32 buffer of a step: name -> (offset, length).  With
+    ``sampling`` the buffer also carries a temperature (float32) and a uniform number (float64) per wanted row.
+    The native ``nvh_step_layout`` computes the same layout."""
     seg = {}
     off = 0
     for name, n in (("ids", T), ("pos", T), ("row_entry", T), ("cu", S + 1), ("pos0", S), ("slot", S),
@@ -102,7 +118,32 @@ def batch_layout(S: int, T: int, n_want: int, G: int, max_blocks: int):
     for g in range(G):
         seg[f"bt{g}"] = (off, S * max_blocks)
         off = _align4(off + S * max_blocks)
+    if sampling:
+        seg["temp"] = (off, n_want)
+        off = _align4(off + n_want)
+        seg["u"] = (off, 2 * n_want)
+        off = _align4(off + 2 * n_want)
     return seg, max(off, 4)
+
+
+def batch_from_buffer(dev: torch.Tensor, seg: dict, infos: list, S: int, T: int, G: int, max_blocks: int,
+                      h2d_bytes: int) -> StepBatch:
+    """The views of a step's arrays inside the device copy ``dev`` of its buffer."""
+    def view(name):
+        o, n = seg[name]
+        return dev[o:o + n]
+
+    temps = us = None
+    if "temp" in seg:
+        temps = view("temp").view(torch.float32)
+        us = view("u").view(torch.float64)
+    return StepBatch(
+        T=T, S=S, input_ids=view("ids"), positions=view("pos"), row_entry=view("row_entry"), cu_rows=view("cu"),
+        entry_pos0=view("pos0"), entry_slot=view("slot"), want_rows=view("want"),
+        block_tables=[view(f"bt{g}").view(S, max_blocks) for g in range(G)], entries=list(infos),
+        max_rows=max((i.length for i in infos), default=0),
+        max_context=max((i.pos0 + i.length for i in infos), default=0),
+        decode_only=all(i.length == 1 for i in infos), h2d_bytes=h2d_bytes, temperatures=temps, uniforms=us)
 
 
 def build_batch(entries: list, infos: list, tables, max_blocks: int, device, stager=None,
@@ -150,14 +191,4 @@ def build_batch(entries: list, infos: list, tables, max_blocks: int, device, sta
         stager = BatchStager(device, depth=1)
     dev = stager.stage(host, static_dev)
 
-    def view(name):
-        o, n = seg[name]
-        return dev[o:o + n]
-
-    return StepBatch(
-        T=T, S=S, input_ids=view("ids"), positions=view("pos"), row_entry=view("row_entry"), cu_rows=view("cu"),
-        entry_pos0=view("pos0"), entry_slot=view("slot"), want_rows=view("want"),
-        block_tables=[view(f"bt{g}").view(S, max_blocks) for g in range(G)], entries=list(infos),
-        max_rows=max((i.length for i in infos), default=0),
-        max_context=max((i.pos0 + i.length for i in infos), default=0),
-        decode_only=all(i.length == 1 for i in infos), h2d_bytes=int(host.nbytes))
+    return batch_from_buffer(dev, seg, infos, S, T, G, max_blocks, int(host.nbytes))

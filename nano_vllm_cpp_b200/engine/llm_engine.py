@@ -122,8 +122,7 @@ class LLMEngine:
                 n_decode += 1
             else:
                 n_prefill += s.count
-        logits = self.runner.step(entries)
-        tokens = self.sampler.sample(logits, temps, us)
+        tokens = self.runner.step_tokens(entries, temps, us)
         sampled = {seq.seq_id: tok for seq, tok in zip(sampled_seqs, tokens)}
         finished = self.scheduler.postprocess(scheduled, sampled)
         return StepOutput([(q.seq_id, q.completion_token_ids) for q in finished], n_prefill, n_decode,

@@ -10,13 +10,14 @@ inside.
 """
 from __future__ import annotations
 
+import numpy as np
 import torch
 
 from ..cache import CacheManager, DeviceCache
 from ..csrc import ops
 from ..parts.base import RunContext, KVCacheSpec
 from ..weights.loader import load_model
-from .batch import StepEntry, EntryInfo, build_batch, batch_layout, BatchStager
+from .batch import StepEntry, EntryInfo, batch_from_buffer, batch_layout, BatchStager
 
 _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32, "bf16": torch.bfloat16, "fp32": torch.float32}
 
@@ -59,7 +60,8 @@ class ModelRunner:
         self.last_h2d_bytes = 0
         self.stager = BatchStager(self.device)
         self.cuda_graphs = cuda_graphs and self.model.graph_safe
-        self._graphs: dict = {}        # decode batch size -> captured step
+        self._graphs: dict = {}        # (decode batch size, with sampling) -> captured step
+        self._pinned_out: dict = {}
         self._seen: dict = {}
 
     def _pages_from_free_memory(self, utilization: float) -> int:
@@ -83,9 +85,9 @@ class ModelRunner:
         return self.manager.get(rid).num_tokens
 
     # ------------------------------------------------------------------ the step
-    def prepare(self, entries: list, static_dev=None):
-        """Takes pages for the entries' positions and builds the batch arrays."""
-        infos, row0 = [], 0
+    def prepare(self, entries: list, static_dev=None, sampling=None):
+        """Takes pages for the entries' positions and builds the batch arrays (natively, straight into a pinned
+        buffer).  ``sampling`` = (temperatures, uniforms), one pair per wanted row, rides along in the same copy."""
         seen = set()
         for e in entries:
             if e.rid in seen:
@@ -95,18 +97,38 @@ class ModelRunner:
                 raise StepError(f"request {e.rid!r}: an entry needs at least one token")
             if not self.manager.has(e.rid):
                 self.open(e.rid)
-            rc = self.manager.get(e.rid)
-            start, end = rc.num_tokens, rc.num_tokens + len(e.tokens)
-            if end > self.max_model_len:
-                raise StepError(f"request {e.rid!r}: {end} tokens exceed the longest sequence {self.max_model_len}")
-            self.manager.extend(e.rid, start, end)
-            infos.append(EntryInfo(e.rid, rc.slot, start, len(e.tokens), row0))
+        S = len(entries)
+        T = sum(len(e.tokens) for e in entries)
+        W = sum(len(e.want) for e in entries)
+        G = len(self.manager.pools)
+        seg, total = batch_layout(S, T, W, G, self.max_blocks, sampling is not None)
+        ticket, buf = self.stager.acquire(total)
+        try:
+            used, slots, native_ids = self.manager.prepare_step(entries, self.max_blocks, self.max_model_len,
+                                                               sampling is not None, buf)
+        except ValueError as e:
+            raise StepError(str(e)) from None
+        assert used == total
+        if sampling is not None:
+            temps, us = sampling
+            if len(temps) != W or len(us) != W:
+                raise StepError("one temperature and one uniform number per wanted row")
+            o, n = seg["temp"]
+            buf[o:o + n].view(np.float32)[:] = temps
+            o, n = seg["u"]
+            buf[o:o + n].view(np.float64)[:] = us
+        dev = self.stager.submit(ticket, total, static_dev)
+        infos, row0 = [], 0
+        for e, (slot, pos0) in zip(entries, slots):
+            infos.append(EntryInfo(e.rid, slot, pos0, len(e.tokens), row0))
             row0 += len(e.tokens)
-        batch = build_batch(entries, infos, None, self.max_blocks, self.device, self.stager, static_dev,
-                            table_filler=lambda g, i, dst: self.manager.fill_block_table(entries[i].rid, g, dst),
-                            num_groups=len(self.manager.pools))
+        batch = batch_from_buffer(dev, seg, infos, S, T, G, self.max_blocks, total * 4)
+        batch.native_ids = native_ids
         self.last_h2d_bytes = batch.h2d_bytes
         return batch
+
+    def _commit(self, batch) -> None:
+        self.manager.commit_many(batch.native_ids, [i.pos0 + i.length for i in batch.entries])
 
     @torch.no_grad()
     def step(self, entries: list, check: bool = True) -> torch.Tensor:
@@ -116,42 +138,84 @@ class ModelRunner:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
         logits = batch = None
         if self.cuda_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
-            logits, batch = self._graph_step(entries)
+            logits, batch, _ = self._graph_step(entries, None)
         if batch is None:
             batch = self.prepare(entries)
             logits = self.model.forward(batch, self.cache)
         if check:
             self.ctx.err.check("step")
-        for info in batch.entries:
-            self.manager.commit(info.rid, info.pos0 + info.length)
+        self._commit(batch)
         return logits
 
+    @torch.no_grad()
+    def step_tokens(self, entries: list, temperatures: list, uniforms: list) -> list:
+        """``step`` followed by the choice of one token per wanted row (greedy where the temperature is <= 0, else
+        by the row's uniform number; see ``sampling``), all on the device: the sampling inputs travel with the
+        step's index arrays, the tokens and the kernels' error flag come back in one copy, and the host waits
+        once.  Returns the tokens in the order of the wanted rows."""
+        if not entries:
+            return []
+        sampling = (temperatures, uniforms)
+        out = batch = None
+        if self.cuda_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
+            _, batch, out = self._graph_step(entries, sampling)
+        if batch is None:
+            batch = self.prepare(entries, sampling=sampling)
+            logits = self.model.forward(batch, self.cache)
+            out = self._sample_into_host(logits, batch)
+        torch.cuda.current_stream(self.device).synchronize()
+        W = len(temperatures)
+        host = out.numpy()
+        flag = int(host[W])
+        if flag:
+            self.ctx.err.check("step")
+        self._commit(batch)
+        return host[:W].tolist()
+
+    def _sample_into_host(self, logits, batch):
+        """Queues the sampling kernel and the copy of [tokens..., error flag] into pinned memory."""
+        W = logits.shape[0]
+        dev = torch.empty(W + 1, dtype=torch.int32, device=self.device)
+        if W:
+            ops.sample(logits, batch.temperatures, batch.uniforms, dev[:W])
+        dev[W:].copy_(self.ctx.err.t)
+        key = ("out", W)
+        host = self._pinned_out.get(key)
+        if host is None:
+            host = self._pinned_out[key] = torch.empty(W + 1, dtype=torch.int32).pin_memory()
+        host.copy_(dev, non_blocking=True)
+        return host
+
     # ------------------------------------------------------------------ decode steps as CUDA graphs
-    def _graph_step(self, entries: list):
+    def _graph_step(self, entries: list, sampling):
         """A batch of single rows that all want their logits always launches the same kernels with the
-        same sizes; only the index arrays differ.  Such a step is captured once per batch size and
-        replayed afterwards: the arrays are copied into the buffer the graph reads, and the graph's
-        logits tensor is returned (valid until the next step of the same size)."""
+        same sizes; only the index arrays differ.  Such a step is captured once per batch size (and once more
+        with the sampling kernel and the copy of the tokens to the host behind it) and replayed afterwards: the
+        arrays are copied into the buffer the graph reads, and the graph's logits tensor (or pinned token
+        buffer) is returned, valid until the next step of the same size."""
         S = len(entries)
-        g = self._graphs.get(S)
+        key = (S, sampling is not None)
+        g = self._graphs.get(key)
         if g is None:
-            self._seen[S] = self._seen.get(S, 0) + 1
-            if self._seen[S] < 2 or len(self._graphs) >= 24:
-                return None, None          # a size seen once is not worth a capture
-            seg, total = batch_layout(S, S, S, len(self.manager.pools), self.max_blocks)
+            self._seen[key] = self._seen.get(key, 0) + 1
+            if self._seen[key] < 2 or len(self._graphs) >= 24:
+                return None, None, None          # a size seen once is not worth a capture
+            seg, total = batch_layout(S, S, S, len(self.manager.pools), self.max_blocks, sampling is not None)
             static_dev = torch.full((total,), -1, dtype=torch.int32, device=self.device)
-            batch = self.prepare(entries, static_dev)
+            batch = self.prepare(entries, static_dev, sampling)
             batch.max_context = self.max_model_len        # the split of the keys must not depend on the step
             logits = self.model.forward(batch, self.cache)       # warms up; also this step's result
+            out = self._sample_into_host(logits, batch) if sampling is not None else None
             torch.cuda.synchronize(self.device)
             before = ops.launch_count()
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
                 static_logits = self.model.forward(batch, self.cache)
-            self._graphs[S] = (graph, static_dev, static_logits, ops.launch_count() - before)
-            return logits, batch
-        graph, static_dev, static_logits, launches = g
-        batch = self.prepare(entries, static_dev)
+                static_out = self._sample_into_host(static_logits, batch) if sampling is not None else None
+            self._graphs[key] = (graph, static_dev, static_logits, static_out, ops.launch_count() - before)
+            return logits, batch, out
+        graph, static_dev, static_logits, static_out, launches = g
+        batch = self.prepare(entries, static_dev, sampling)
         graph.replay()
         ops.add_launches(launches)
-        return static_logits, batch
+        return static_logits, batch, static_out

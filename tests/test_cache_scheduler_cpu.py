@@ -364,3 +364,66 @@ def test_native_pool_and_hash_against_the_plain_restatement():
         assert a.num_free() == b.num_free()
         assert [a.ref_count[p] for p in range(6)] == b.ref_count
         a.check()
+
+
+def test_native_step_arrays_match_the_python_builder():
+    """The native fill of a step's index arrays against ``build_batch`` on the same requests."""
+    import numpy as np
+    from nano_vllm_cpp_b200.engine.batch import StepEntry, EntryInfo, build_batch, batch_layout
+    rng = random.Random(5)
+    for trial in range(30):
+        windows = rng.choice([(0,), (0, 16)])
+        m = CacheManager(list(windows), 64, 16, max_requests=6)
+        max_blocks = 12
+        live = {}
+        for step in range(6):
+            entries = []
+            for rid in rng.sample(["a", "b", 3, 4, "e"], rng.randrange(1, 5)):
+                if not m.has(rid):
+                    m.open(rid)
+                    live[rid] = 0
+                n = rng.choice([1, 1, 2, 5, 17])
+                if live[rid] + n > 150:
+                    continue
+                toks = [rng.randrange(1000) for _ in range(n)]
+                want = sorted(rng.sample(range(n), rng.randrange(0, min(n, 3) + 1)))
+                entries.append(StepEntry(rid, toks, want))
+            if not entries:
+                continue
+            sampling = rng.random() < 0.5
+            S, T = len(entries), sum(len(e.tokens) for e in entries)
+            W = sum(len(e.want) for e in entries)
+            seg, total = batch_layout(S, T, W, len(windows), max_blocks, sampling)
+            buf = np.full(total + 7, 12345, dtype=np.int32)
+            used, slots, ids = m.prepare_step(entries, max_blocks, 160, sampling, buf)
+            assert used == total and (buf[total:] == 12345).all()
+            infos, row0 = [], 0
+            for e, (slot, pos0) in zip(entries, slots):
+                assert (slot, pos0) == (m.get(e.rid).slot, live[e.rid])
+                infos.append(EntryInfo(e.rid, slot, pos0, len(e.tokens), row0))
+                row0 += len(e.tokens)
+            tables = [[m.get(e.rid).tables[g] for e in entries] for g in range(len(windows))]
+            ref = build_batch(entries, infos, tables, max_blocks, "cpu")
+            for name, t in (("ids", ref.input_ids), ("pos", ref.positions), ("row_entry", ref.row_entry),
+                            ("cu", ref.cu_rows), ("pos0", ref.entry_pos0), ("slot", ref.entry_slot),
+                            ("want", ref.want_rows)):
+                o, n = seg[name]
+                assert buf[o:o + n].tolist() == t.tolist(), name
+            for g in range(len(windows)):
+                o, n = seg[f"bt{g}"]
+                assert buf[o:o + n].tolist() == ref.block_tables[g].flatten().tolist()
+            m.commit_many(ids, [i.pos0 + i.length for i in infos])
+            for e in entries:
+                live[e.rid] += len(e.tokens)
+                assert m.get(e.rid).num_tokens == live[e.rid]
+        m.check()
+    # errors: a place that is not among the tokens, an entry without tokens, too long a sequence
+    m = CacheManager([0], 8, 16, max_requests=2)
+    m.open("x")
+    buf = np.zeros(256, dtype=np.int32)
+    with pytest.raises(ValueError, match="wanted place"):
+        m.prepare_step([StepEntry("x", [1, 2], [2])], 4, 100, False, buf)
+    with pytest.raises(ValueError, match="exceed"):
+        m.prepare_step([StepEntry("x", list(range(40)), [])], 4, 30, False, buf)
+    with pytest.raises(NoFreePages):
+        m.prepare_step([StepEntry("x", list(range(16 * 9)), [])], 16, 1000, False, np.zeros(1024, dtype=np.int32))
