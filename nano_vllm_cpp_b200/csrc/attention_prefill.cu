@@ -13,9 +13,11 @@
 // Reference twin: nv_paged_attention_plain.  (The reference's kernel: src/hip_ops.hip:473-551.)
 #include "common.cuh"
 
+#include <stdlib.h>
+
 namespace {
 
-constexpr int BM = 128, BN = 64, PF_THREADS = 256;   // 8 warps of 16 rows share every tile of keys
+constexpr int BN = 64;   // keys per shared-memory tile; a CTA is BM / 16 warps of 16 rows that share it (BM: 64 or 128)
 
 struct PfArgs {
   const bf16* qkv;
@@ -58,8 +60,9 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 // DP: head dimension rounded up to 32, 64, 128 or 256 (sizes the shared memory and the accumulators).
-template <int DP>
-__global__ void __launch_bounds__(PF_THREADS, DP <= 128 ? 2 : 1) attention_prefill_kernel(PfArgs a) {
+template <int DP, int BM>
+__global__ void __launch_bounds__(BM * 2, DP <= 128 ? 2 : 1) attention_prefill_kernel(PfArgs a) {
+  constexpr int PF_THREADS = BM * 2;
   constexpr int LDS = DP + 8;                      // row stride (elements): 16 bytes of padding against bank conflicts
   extern __shared__ __align__(16) uint8_t pf_smem[];
   bf16* Qs = (bf16*)pf_smem;
@@ -292,26 +295,37 @@ __global__ void __launch_bounds__(PF_THREADS, DP <= 128 ? 2 : 1) attention_prefi
   }
 }
 
-template <int DP>
-int launch_prefill(const PfArgs& a, int max_tiles, cudaStream_t s) {
+template <int DP, int BM>
+int launch_prefill_bm(const PfArgs& a, int max_tiles, cudaStream_t s) {
   const size_t smem = (size_t)(BM + 4 * BN) * (DP + 8) * sizeof(bf16);
   static bool attr_done = false;
   if (!attr_done) {
-    cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<DP, BM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)smem);
     if (e != cudaSuccess) return (int)e;
     attr_done = true;
   }
   dim3 grid(max_tiles, a.Hq);
-  attention_prefill_kernel<DP><<<grid, PF_THREADS, smem, s>>>(a);
+  attention_prefill_kernel<DP, BM><<<grid, BM * 2, smem, s>>>(a);
   NV_RETURN_LAST();
+}
+
+// Tiles of 128 rows read every key once per 128 rows; tiles of 64 rows make twice as many, shorter blocks, which
+// evens out a causal prompt (its last tile sees all keys, its first almost none) but leaves a multiprocessor
+// with half the warps: measured slower (a 2,048-token prompt: 21.7 against 20.5 ms), so 128 it is.
+template <int DP>
+int launch_prefill(const PfArgs& a, int max_tiles64, int num_sms, cudaStream_t s) {
+  const char* force = getenv("NV_PREFILL_TILE");        // experiments only
+  (void)num_sms;
+  if (force && atoi(force) == 64) return launch_prefill_bm<DP, 64>(a, max_tiles64, s);
+  return launch_prefill_bm<DP, 128>(a, max_tiles64, s);
 }
 
 }  // namespace
 
 // bfloat16 only; head_dim a multiple of 16 up to 256.  `max_tiles` >= sum over entries of
-// ceil(rows / nv_attention_prefill_tile_rows()); surplus CTAs leave at once.
-NV_API int nv_attention_prefill_tile_rows() { return BM; }
+// ceil(rows / nv_attention_prefill_tile_rows()), the smallest tile the launcher may choose; surplus CTAs leave at once.
+NV_API int nv_attention_prefill_tile_rows() { return 64; }
 
 NV_API int nv_attention_prefill(const void* qkv, int q_stride, const void* kc, const void* vc,
                                 const int* block_table, int max_blocks, const int* cu_rows, const int* entry_pos0,
@@ -326,8 +340,15 @@ NV_API int nv_attention_prefill(const void* qkv, int q_stride, const void* kc, c
   a.scale_log2 = scale * 1.4426950408889634f;
   a.S = S; a.q_stride = q_stride; a.max_blocks = max_blocks; a.window = window; a.Hq = Hq; a.Hkv = Hkv; a.D = D;
   a.page = page;
-  if (D <= 32) return launch_prefill<32>(a, max_tiles, stream);
-  if (D <= 64) return launch_prefill<64>(a, max_tiles, stream);
-  if (D <= 128) return launch_prefill<128>(a, max_tiles, stream);
-  return launch_prefill<256>(a, max_tiles, stream);
+  static int num_sms = 0;
+  if (!num_sms) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+      num_sms = 148;
+  }
+  if (D <= 32) return launch_prefill<32>(a, max_tiles, num_sms, stream);
+  if (D <= 64) return launch_prefill<64>(a, max_tiles, num_sms, stream);
+  if (D <= 128) return launch_prefill<128>(a, max_tiles, num_sms, stream);
+  return launch_prefill<256>(a, max_tiles, num_sms, stream);
 }

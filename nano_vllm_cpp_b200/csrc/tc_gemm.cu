@@ -28,6 +28,7 @@
 #include "pipeline.cuh"
 
 #include <cuda.h>
+#include <stdlib.h>
 #include <mutex>
 #include <unordered_map>
 
@@ -60,6 +61,7 @@ struct TcArgs {
   int acc_bufs;                       // accumulator sets in TMEM: 2 when two fit, else 1
   int tmem_cols;
   int early;                          // launched as a programmatic dependent: weights are fetched before the wait
+  int x_box;                          // token rows per TMA box of X: min(n_tile, 64)
 };
 
 // ------------------------------------------------------------------ PTX wrappers (mbarriers: pipeline.cuh)
@@ -201,9 +203,12 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
             if (it < first) continue;
             const int s = it % a.stages;
             uint8_t* st = smem + (size_t)s * stage_bytes;
+            // tokens come in boxes of x_box rows, as many as the tile's rows (rounded up to the 16 of the MMA) need
+            const int n_act = min(a.n_tile, (t.rows_here + 15) & ~15);
+            const int boxes = (n_act + a.x_box - 1) / a.x_box;
             if (weights) {
               mbar_wait(&empty_bar[s], ((it / a.stages) & 1) ^ 1, a.err, 0x7001);
-              mbar_expect_tx(&full_bar[s], stage_bytes);
+              mbar_expect_tx(&full_bar[s], a_bytes * (two ? 2 : 1) + (uint32_t)boxes * a.x_box * 128);
             }
             const int kc = (t.k_begin + k) * BLOCK_K;
             const int wr = t.w_row_base + t.nb * a.w_per_cta;
@@ -212,7 +217,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
               if (two)     // swiglu: the up rows of the same features; dual: the next 128 features
                 tma_load_2d(st + a_bytes, &tm_w, &full_bar[s], kc, wr + (a.swiglu ? a.N : TILE_W));
             }
-            if (tokens) tma_load_2d(st + a_bytes * (two ? 2 : 1), &tm_x, &full_bar[s], kc, t.row0);
+            if (tokens)
+              for (int b = 0; b < boxes; ++b)
+                tma_load_2d(st + a_bytes * (two ? 2 : 1) + (size_t)b * a.x_box * 128, &tm_x, &full_bar[s], kc,
+                            t.row0 + b * a.x_box);
           }
         }
       };
@@ -227,7 +235,6 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0) {
-      const uint32_t idesc = instr_desc(a.n_tile);
       int it = 0, n = 0;                           // k-steps consumed, tiles done
       Tile t;
       for (int tile = blockIdx.x; get_tile(a, tile, y_tiles, t); tile += gridDim.x, ++n) {
@@ -236,6 +243,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         mbar_wait(&acc_empty[b], (use & 1) ^ 1, a.err, 0x7004);  // the epilogue has drained it
         tc_fence_after();
         const uint32_t acc_addr = tmem_base + b * acc_cols;
+        // the N of the instruction is what the tile's rows need, not the widest tile: a short last tile of an
+        // expert costs a short product
+        const uint32_t idesc = instr_desc(min(a.n_tile, (t.rows_here + 15) & ~15));
         for (int k = 0; k < t.n_steps; ++k, ++it) {
           const int s = it % a.stages;
           mbar_wait(&full_bar[s], (it / a.stages) & 1, a.err, 0x7002);
@@ -469,7 +479,8 @@ NV_API int nv_tc_gemm(const void* X, long long ldx, int M_tok, const void* W, in
   CUtensorMap tm_w, tm_x;
   int rc = get_map(W, w_rows_total, K, K, TILE_W, &tm_w);
   if (rc) return rc;
-  rc = get_map(X, M_tok, K, ldx, n_tile, &tm_x);
+  const int x_box = n_tile < 64 ? n_tile : 64;
+  rc = get_map(X, M_tok, K, ldx, x_box, &tm_x);
   if (rc) return rc;
 
   TcArgs a;
@@ -481,6 +492,7 @@ NV_API int nv_tc_gemm(const void* X, long long ldx, int M_tok, const void* W, in
   a.k_steps_per_split = (a.k_steps_total + a.splits - 1) / a.splits;
   a.n_tile = n_tile; a.swiglu = swiglu ? 1 : 0;
   a.early = early ? 1 : 0;
+  a.x_box = x_box;
   // Many tokens per tile and enough features: two weight tiles per CTA.  The operands then cost 2*16 KB + X
   // per k-step for twice the flops, which is what the shared-memory fill rate, the limit here, rewards.
   // ... provided the halved grid still covers the GPU (measured: a half-empty GPU loses more than the tile gains)

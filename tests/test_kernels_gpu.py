@@ -152,7 +152,7 @@ def test_tc_gemm_split_k(splits):
     tc_case(3, 200, 1160, True, False, torch.bfloat16, splits=splits)
 
 
-@pytest.mark.parametrize("T,E,K", [(5, 6, 3), (64, 8, 2), (300, 60, 4), (1, 60, 4)])
+@pytest.mark.parametrize("T,E,K", [(5, 6, 3), (64, 8, 2), (300, 60, 4), (1, 60, 4), (700, 6, 3), (130, 3, 2)])
 def test_tc_gemm_grouped(T, E, K):
     """Both grouped products of an expert layer against the plain grouped kernel and float64."""
     o = ops()
