@@ -253,18 +253,29 @@ def attention_prefill_tile_rows() -> int:
 
 
 def attention_prefill(qkv, k_cache, v_cache, block_table, cu_rows, entry_pos0, max_tiles: int, scale: float,
-                      window: int, out, Hq: int, Hkv: int, D: int) -> None:
-    """bfloat16 rows of any mix of portions against their paged keys (tensor cores)."""
+                      window: int, out, Hq: int, Hkv: int, D: int, err=None) -> None:
+    """bfloat16 rows of any mix of portions against their paged keys: the tcgen05 kernel for head sizes 64 and
+    128 and pages of 16, 32 or 64 keys, else the mma.sync kernel."""
     _cuda_contig(qkv, k_cache, v_cache, block_table, cu_rows, entry_pos0, out)
     _i32(block_table, cu_rows, entry_pos0)
     _need(qkv.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16,
           "attention_prefill: bfloat16 only")
     _need(out.shape == (qkv.shape[0], Hq * D), "attention_prefill: out shape")
     S = entry_pos0.numel()
-    _check(lib().nv_attention_prefill(_p(qkv), c_int(qkv.shape[1]), _p(k_cache), _p(v_cache), _p(block_table),
-                                      c_int(block_table.shape[1]), _p(cu_rows), _p(entry_pos0), c_int(S),
-                                      c_int(max_tiles), c_float(scale), c_int(window), _p(out), c_int(Hq), c_int(Hkv),
-                                      c_int(D), c_int(k_cache.shape[2]), _stream()), "attention_prefill")
+    L = lib()
+    page = k_cache.shape[2]
+    if L.nv_attention_prefill_tc_usable(c_int(D), c_int(page)):
+        _check(L.nv_attention_prefill_tc(_p(qkv), c_int(qkv.shape[1]), c_int(qkv.shape[0]), _p(k_cache), _p(v_cache),
+                                         c_int(k_cache.shape[0]), _p(block_table), c_int(block_table.shape[1]),
+                                         _p(cu_rows), _p(entry_pos0), c_int(S), c_int(max_tiles), c_float(scale),
+                                         c_int(window), _p(out), c_int(Hq), c_int(Hkv), c_int(D), c_int(page),
+                                         _p(err.t if err is not None else _global_err().t), _stream()),
+               "attention_prefill_tc")
+        return
+    _check(L.nv_attention_prefill(_p(qkv), c_int(qkv.shape[1]), _p(k_cache), _p(v_cache), _p(block_table),
+                                  c_int(block_table.shape[1]), _p(cu_rows), _p(entry_pos0), c_int(S),
+                                  c_int(max_tiles), c_float(scale), c_int(window), _p(out), c_int(Hq), c_int(Hkv),
+                                  c_int(D), c_int(page), _stream()), "attention_prefill")
 
 
 def gemm_plain_tile_m() -> int:

@@ -25,7 +25,7 @@
 // that predecessor started.  Every wait on an mbarrier is bounded: after
 // about two seconds a waiter records the fact in the error flag and goes on, so the kernel always
 // ends and frees its TMEM; its output is then garbage and the host raises.
-#include "pipeline.cuh"
+#include "tcgen05.cuh"
 
 #include <cuda.h>
 #include <stdlib.h>
@@ -63,64 +63,6 @@ struct TcArgs {
   int early;                          // launched as a programmatic dependent: weights are fetched before the wait
   int x_box;                          // token rows per TMA box of X: min(n_tile, 64)
 };
-
-// ------------------------------------------------------------------ PTX wrappers (mbarriers: pipeline.cuh)
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t cols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)), "r"(cols)
-               : "memory");
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
-}
-
-// D[tmem] (+)= A[smem desc] * B[smem desc]; issued by one thread
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                          uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// the mbarrier gets one arrival when every MMA issued so far by this thread has finished
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-               : "memory");
-}
-
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
-  uint32_t r[16];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
-
-// Shared-memory operand descriptor: K-major tile of rows x 64 bf16 (128 bytes per row), written by TMA with
-// the 128-byte swizzle; 8-row groups are 1024 bytes apart.
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((saddr >> 4) & 0x3FFF);        // start address
-  d |= (uint64_t)1 << 16;                        // leading byte offset (unused with swizzle): 16 B
-  d |= (uint64_t)(1024 >> 4) << 32;              // stride byte offset between 8-row groups
-  d |= (uint64_t)1 << 46;                        // descriptor version of this architecture
-  d |= (uint64_t)2 << 61;                        // 128-byte swizzle
-  return d;
-}
-
-// Instruction descriptor: bf16 x bf16 -> f32, both operands K-major, M = 128, N = n.
-__device__ __forceinline__ uint32_t instr_desc(int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TILE_W >> 4) << 24);
-}
 
 // ------------------------------------------------------------------ the kernel
 // Persistent: the grid is as many CTAs as fit the GPU at once and every CTA walks the tile list

@@ -80,7 +80,7 @@ class PagedAttention(Mixer):
                 tm = ops.attention_prefill_tile_rows()
                 tiles = sum((e.length + tm - 1) // tm for e in batch.entries)
                 ops.attention_prefill(qkv, cache.k, cache.v, bt, batch.cu_rows, batch.entry_pos0, tiles, self.scale,
-                                      self.window, att, self.Hq, self.Hkv, self.D)
+                                      self.window, att, self.Hq, self.Hkv, self.D, err=self.ctx.err)
             return
         ops.paged_attention_plain(qkv, cache.k, cache.v, bt, batch.row_entry, batch.positions, self.scale,
                                   self.window, att, self.Hq, self.Hkv, self.D)

@@ -402,7 +402,8 @@ def test_rope_store(Hq, Hkv, D, rot, dtype):
 
 
 @pytest.mark.parametrize("Hq,Hkv,D,page", [(3, 1, 32, 16), (4, 4, 16, 16), (6, 2, 48, 32), (4, 2, 128, 16), (2, 1, 256, 16),
-                                           (5, 5, 80, 16)])
+                                           (5, 5, 80, 16), (3, 3, 64, 16), (6, 2, 64, 32), (2, 1, 128, 64), (7, 1, 64, 64),
+                                           (2, 2, 128, 32)])
 @pytest.mark.parametrize("window", [0, 20, 100])
 def test_attention_prefill_against_plain(Hq, Hkv, D, page, window):
     """Portions of several requests in one batch: a whole prompt, a portion that continues a cached
