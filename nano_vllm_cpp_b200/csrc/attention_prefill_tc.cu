@@ -14,8 +14,9 @@
 //              maximum of some row of its warp moved (exactly: by exp2 of the difference), writes P(i) as
 //              bfloat16 into shared memory in the swizzled K-major layout, and at the end reads O, divides by
 //              the row sum and stores.
-// S(i+1) is issued right behind O += P(i) V(i), so the tensor core works on it while the softmax warps finish
-// block i; two CTAs share a multiprocessor and fill each other's gaps.  Every wait is bounded.
+// S has two buffers in tensor memory and K two in shared memory: S(i+1) and S(i+2) are issued ahead, so the softmax
+// warps go from block to block without waiting for the tensor core, and the tensor core computes S while they
+// work.  Two CTAs share a multiprocessor and fill each other's gaps.  Every wait is bounded.
 //
 // Takes bfloat16, head_dim 64 or 128, pages of 16, 32 or 64 keys; everything else goes to the mma.sync kernel
 // (attention_prefill.cu), which is also this kernel's twin in the tests.  (The reference's kernel:
@@ -29,6 +30,7 @@ namespace {
 constexpr int TQ = 128;          // rows per CTA: the M of the instruction, one tensor-memory lane per row
 constexpr int TKB = 64;          // keys per block: one 128-byte swizzle row of P
 constexpr int PT_THREADS = 192;
+constexpr int BT_CAP = 1024;     // block-table entries kept in shared memory (16,384 keys with pages of 16)
 
 struct PtArgs {
   const int* block_table;
@@ -40,6 +42,13 @@ struct PtArgs {
   int S, max_blocks, window, Hq, Hkv, page;
 };
 
+// 2^x by the special-function unit; exp2(-inf) = 0.
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 template <int D>
 __global__ void __launch_bounds__(PT_THREADS, 2)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -47,14 +56,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
   constexpr int SL = D / 64;                       // 64-element slabs of the head dimension
   constexpr uint32_t Q_SLAB = TQ * 128, KV_SLAB = TKB * 128;
   extern __shared__ __align__(1024) uint8_t pt_smem_raw[];
-  __shared__ uint64_t q_full, k_full, k_empty, v_full, v_empty, s_full, p_full, o_full;
+  __shared__ uint64_t q_full, k_full[2], k_empty[2], v_full, v_empty, s_full[2], p_full, pv_done;
   __shared__ uint32_t tmem_base_s;
   __shared__ int tile_info[3];                     // entry, first row (batch), rows
+  __shared__ int bt_s[BT_CAP];                     // the tile's block-table entries, fetched once up front
 
   uint8_t* smem = (uint8_t*)(((uintptr_t)pt_smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* Qs = smem;
-  uint8_t* Ks = Qs + SL * Q_SLAB;
-  uint8_t* Vs = Ks + SL * KV_SLAB;
+  uint8_t* Ks = Qs + SL * Q_SLAB;                  // two buffers
+  uint8_t* Vs = Ks + 2 * SL * KV_SLAB;
   uint8_t* Ps = Vs + SL * KV_SLAB;                 // [128 rows][64 keys] bf16
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
@@ -65,20 +75,22 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
     asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&tm_k) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&tm_v) : "memory");
     mbar_init(&q_full, 1);
-    mbar_init(&k_full, 1);
-    mbar_init(&k_empty, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&k_full[b], 1);
+      mbar_init(&k_empty[b], 1);
+      mbar_init(&s_full[b], 1);
+    }
     mbar_init(&v_full, 1);
     mbar_init(&v_empty, 1);
-    mbar_init(&s_full, 1);
     mbar_init(&p_full, 4);                         // one arrival per softmax warp
-    mbar_init(&o_full, 1);
+    mbar_init(&pv_done, 1);
     mbar_fence_init();
   }
   // keys that a block never loads (beyond the last key, pages a window gave back) must still be finite numbers:
   // their probabilities are zero, and zero times whatever the shared memory held before must be zero
-  for (int i = tid; i < (int)(2 * SL * KV_SLAB / 16); i += PT_THREADS) ((uint4*)Ks)[i] = make_uint4(0, 0, 0, 0);
+  for (int i = tid; i < (int)(3 * SL * KV_SLAB / 16); i += PT_THREADS) ((uint4*)Ks)[i] = make_uint4(0, 0, 0, 0);
   fence_async_smem();
-  if (warp == 1) tmem_alloc(&tmem_base_s, D == 128 ? 256 : 128);
+  if (warp == 1) tmem_alloc(&tmem_base_s, 256);
   grid_dep_wait();              // queries, and this step's keys and values, come from the kernel before
   grid_dep_launch();
   if (tid == 0) {               // which (entry, tile of 128 rows) is this CTA's?  later tiles (more keys) first
@@ -107,44 +119,50 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
     const int lo = a.window > 0 ? max(0, pos0 + 1 - a.window) : 0; // first key any row of the tile sees
     const int kv0 = lo / TKB * TKB;
     const int n_blocks = (hi - kv0 + TKB - 1) / TKB;
-    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + TKB;
+    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 2 * TKB;     // S(even), S(odd), O
+    const int* bt = a.block_table + (size_t)e * a.max_blocks;
+    const int page_shift = 31 - __clz(a.page);                     // pages are 16, 32 or 64 keys
+    const int pg0 = kv0 >> page_shift, n_pg = min(((hi - 1) >> page_shift) + 1 - pg0, BT_CAP);
+    for (int i = tid; i < n_pg; i += PT_THREADS) bt_s[i] = bt[pg0 + i];
+    __syncthreads();
 
     if (warp == 0) {
       // ---------------------------------------------------------------- TMA producer
+      // The whole warp works: a tile of keys (or values) is pages x slabs boxes, and lane (page, slab) issues its
+      // own box, so a tile costs one instruction's time and not a thread's walk over sixteen of them.
       if (lane == 0) {
-        const int* bt = a.block_table + (size_t)e * a.max_blocks;
         mbar_expect_tx(&q_full, SL * Q_SLAB);
 #pragma unroll
         for (int s = 0; s < SL; ++s) tma_load_2d(Qs + s * Q_SLAB, &tm_q, &q_full, h * D + s * 64, row0);
-        const int pages = TKB / a.page;
-        const uint32_t box = (uint32_t)a.page * 128;
-        for (int i = 0; i < n_blocks; ++i) {
-          const int j0 = kv0 + i * TKB;
-          // the pages of this block that hold keys some row can see
-          int blk[8];
-          uint32_t bytes = 0;
-          for (int p = 0; p < pages; ++p) {
-            const int j = j0 + p * a.page;
-            blk[p] = -1;
-            if (j < hi && j + a.page > lo) {
-              blk[p] = bt[j / a.page];
-              if (blk[p] < 0) atomicExch(a.err, 1 + row0);        // a page that should be there is not
-              else bytes += box * SL;
-            }
-          }
-          for (int kv = 0; kv < 2; ++kv) {
-            uint64_t* full = kv ? &v_full : &k_full;
-            mbar_wait(kv ? &v_empty : &k_empty, (i & 1) ^ 1, a.err, 0x7201 + kv);
-            mbar_expect_tx(full, bytes);
-            for (int p = 0; p < pages; ++p) {
-              if (blk[p] < 0) continue;
-              const int row = (blk[p] * a.Hkv + kvh) * a.page;
-#pragma unroll
-              for (int s = 0; s < SL; ++s)
-                tma_load_2d((kv ? Vs : Ks) + s * KV_SLAB + p * box, kv ? &tm_v : &tm_k, full, s * 64, row);
-            }
-          }
+      }
+      const int pages = TKB >> page_shift;
+      const uint32_t box = (uint32_t)a.page * 128;
+      const int my_p = lane / SL, my_s = lane % SL;
+      auto load = [&](int i, bool values) {
+        const int j = kv0 + i * TKB + (my_p << page_shift);          // first key of this lane's page
+        int blk = -1;
+        if (my_p < pages && j < hi && j + a.page > lo) {               // a page some row can see
+          const int pi = (j >> page_shift) - pg0;
+          blk = pi < BT_CAP ? bt_s[pi] : bt[pg0 + pi];
+          if (blk < 0) atomicExch(a.err, 1 + row0);                    // it should be there and is not
         }
+        const uint32_t boxes = __popc(__ballot_sync(0xffffffffu, blk >= 0));
+        uint64_t* full = values ? &v_full : &k_full[i & 1];
+        if (lane == 0) {
+          if (values) mbar_wait(&v_empty, (i & 1) ^ 1, a.err, 0x7202);
+          else mbar_wait(&k_empty[i & 1], ((i >> 1) & 1) ^ 1, a.err, 0x7201);
+          mbar_expect_tx(full, boxes * box);
+        }
+        __syncwarp();
+        if (blk >= 0) {
+          uint8_t* dst = (values ? Vs : Ks + (i & 1) * SL * KV_SLAB) + my_s * KV_SLAB + my_p * box;
+          tma_load_2d(dst, values ? &tm_v : &tm_k, full, my_s * 64, (blk * a.Hkv + kvh) * a.page);
+        }
+      };
+      load(0, false);
+      for (int i = 0; i < n_blocks; ++i) {         // the next keys go out before these values: they are free earlier
+        if (i + 1 < n_blocks) load(i + 1, false);
+        load(i, true);
       }
     } else if (warp == 1) {
       // ---------------------------------------------------------------- MMA issuer
@@ -152,21 +170,24 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
         const uint32_t idesc_s = instr_desc(TKB), idesc_o = instr_desc_b_mn(D);
         const uint32_t q_addr = smem_u32(Qs), k_addr = smem_u32(Ks), v_addr = smem_u32(Vs), p_addr = smem_u32(Ps);
         auto issue_s = [&](int i) {
-          mbar_wait(&k_full, i & 1, a.err, 0x7203);
+          const int b = i & 1;
+          mbar_wait(&k_full[b], (i >> 1) & 1, a.err, 0x7203);
           tc_fence_after();
 #pragma unroll
           for (int s = 0; s < SL; ++s)
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk)
-              umma_bf16(tmem_s, smem_desc_sw128(q_addr + s * Q_SLAB) + (uint64_t)(kk * 2),
-                        smem_desc_sw128(k_addr + s * KV_SLAB) + (uint64_t)(kk * 2), idesc_s, (s | kk) ? 1u : 0u);
-          umma_commit(&k_empty);
-          umma_commit(&s_full);
+              umma_bf16(tmem_s + b * TKB, smem_desc_sw128(q_addr + s * Q_SLAB) + (uint64_t)(kk * 2),
+                        smem_desc_sw128(k_addr + (b * SL + s) * KV_SLAB) + (uint64_t)(kk * 2), idesc_s,
+                        (s | kk) ? 1u : 0u);
+          umma_commit(&k_empty[b]);
+          umma_commit(&s_full[b]);
         };
         mbar_wait(&q_full, 0, a.err, 0x7204);
         issue_s(0);
+        if (n_blocks > 1) issue_s(1);
         for (int i = 0; i < n_blocks; ++i) {
-          mbar_wait(&p_full, i & 1, a.err, 0x7205);
+          mbar_wait(&p_full, i & 1, a.err, 0x7205);  // P(i) is written, S(i) is read, O is rescaled
           mbar_wait(&v_full, i & 1, a.err, 0x7206);
           tc_fence_after();
 #pragma unroll
@@ -174,9 +195,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
             umma_bf16(tmem_o, smem_desc_sw128(p_addr) + (uint64_t)(kk * 2),
                       smem_desc_sw128_mn(v_addr + kk * 2048, KV_SLAB, 1024), idesc_o, (i | kk) ? 1u : 0u);
           umma_commit(&v_empty);
-          if (i + 1 < n_blocks) issue_s(i + 1);
+          umma_commit(&pv_done);
+          if (i + 2 < n_blocks) issue_s(i + 2);      // into the buffer that S(i) has left
         }
-        umma_commit(&o_full);
       }
     } else {
       // ---------------------------------------------------------------- softmax: thread r owns row r
@@ -189,24 +210,39 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
       float m = -INFINITY, l = 0.f;
       for (int i = 0; i < n_blocks; ++i) {
         const int j0 = kv0 + i * TKB;
-        mbar_wait(&s_full, i & 1, a.err, 0x7207);
+        mbar_wait(&s_full[i & 1], (i >> 1) & 1, a.err, 0x7207);
         tc_fence_after();
         float s[TKB];
-        tmem_ld32(tmem_s + lane_off, s);
-        tmem_ld32(tmem_s + lane_off + 32, s + 32);
+        tmem_ld32_nowait(tmem_s + (i & 1) * TKB + lane_off, s);
+        tmem_ld32_nowait(tmem_s + (i & 1) * TKB + lane_off + 32, s + 32);
+        tmem_ld_wait();
         if (!live || j0 + TKB - 1 > p_row || j0 < w_lo) {
 #pragma unroll
           for (int c = 0; c < TKB; ++c)
             if (!(live && j0 + c <= p_row && j0 + c >= w_lo)) s[c] = -INFINITY;
         }
-        float mx = -INFINITY;
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};       // four chains instead of one of 64
 #pragma unroll
-        for (int c = 0; c < TKB; ++c) mx = fmaxf(mx, s[c]);
-        const float m_new = fmaxf(m, mx);
-        const float ms = m_new == -INFINITY ? 0.f : m_new * a.scale_log2;
-        const float alpha = m_new == m ? 1.f : exp2f(m * a.scale_log2 - ms);
-        m = m_new;
-        // O of the earlier blocks is complete here: S(i) was issued behind O += P(i-1) V(i-1)
+        for (int c = 0; c < TKB; c += 4) {
+          mx4[0] = fmaxf(mx4[0], s[c]); mx4[1] = fmaxf(mx4[1], s[c + 1]);
+          mx4[2] = fmaxf(mx4[2], s[c + 2]); mx4[3] = fmaxf(mx4[3], s[c + 3]);
+        }
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+        // The exponent's reference m follows the running maximum only when that has moved by more than 2^8 in
+        // the scaled (log2) units: P = exp2(s - m) may then be as large as 256, which costs bfloat16 and the
+        // float32 sums nothing, O / l is the same quotient, and O in tensor memory is rescaled once in a long
+        // while instead of at almost every block of a short prompt.
+        float alpha = 1.f;
+        if (mx > m && (m == -INFINITY || (mx - m) * a.scale_log2 > 8.f)) {
+          alpha = m == -INFINITY ? 0.f : ex2_approx((m - mx) * a.scale_log2);
+          m = mx;
+        }
+        const float ms = m == -INFINITY ? 0.f : m * a.scale_log2;
+        // O += P(i-1) V(i-1) must have ended before O is rescaled and before P is overwritten
+        if (i > 0) {
+          mbar_wait(&pv_done, (i - 1) & 1, a.err, 0x7209);
+          tc_fence_after();
+        }
         if (i > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
 #pragma unroll
           for (int c = 0; c < D / 32; ++c) {
@@ -217,13 +253,16 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
             tmem_st32(tmem_o + lane_off + c * 32, o);
           }
         }
-        float sum = 0.f;
+        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int c = 0; c < TKB; ++c) {
-          s[c] = exp2f(s[c] * a.scale_log2 - ms);
-          sum += s[c];
+        for (int c = 0; c < TKB; c += 4) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            s[c + u] = ex2_approx(fmaf(s[c + u], a.scale_log2, -ms));
+            sum4[u] += s[c + u];
+          }
         }
-        l = l * alpha + sum;
+        l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
         // P row r: 8 chunks of 8 bfloat16, chunk c at physical chunk c ^ (r % 8) (the 128-byte swizzle)
         uint8_t* prow = Ps + (size_t)r * 128;
 #pragma unroll
@@ -242,7 +281,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
         if (lane == 0) mbar_arrive(&p_full);
       }
       // ---- the result: O / l
-      mbar_wait(&o_full, 0, a.err, 0x7208);
+      mbar_wait(&pv_done, (n_blocks - 1) & 1, a.err, 0x7208);
       tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
@@ -267,7 +306,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, D == 128 ? 256 : 128);
+  if (warp == 1) tmem_dealloc(tmem_base, 256);
 }
 
 template <int D>
@@ -282,7 +321,7 @@ int launch_prefill_tc(const PtArgs& a, const void* qkv, int q_stride, int T, con
   rc = nv_tensor_map_bf16(vc, rows, D, D, a.page, &tm_v);
   if (rc) return rc;
   constexpr int SL = D / 64;
-  const size_t smem = (size_t)SL * TQ * 128 + 2 * (size_t)SL * TKB * 128 + (size_t)TQ * 128 + 1024;
+  const size_t smem = (size_t)SL * TQ * 128 + 3 * (size_t)SL * TKB * 128 + (size_t)TQ * 128 + 1024;
   static bool attr_done = false;
   if (!attr_done) {
     cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
