@@ -169,6 +169,18 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
       if (lane == 0) {
         const uint32_t idesc_s = instr_desc(TKB), idesc_o = instr_desc_b_mn(D);
         const uint32_t q_addr = smem_u32(Qs), k_addr = smem_u32(Ks), v_addr = smem_u32(Vs), p_addr = smem_u32(Ps);
+        // one thread issues everything, so its instruction count is on the critical path: the descriptors are
+        // built once, a product costs an add and the instruction
+        uint64_t dq[SL], dk[2][SL], dv[TKB / 16];
+#pragma unroll
+        for (int s = 0; s < SL; ++s) {
+          dq[s] = smem_desc_sw128(q_addr + s * Q_SLAB);
+          dk[0][s] = smem_desc_sw128(k_addr + s * KV_SLAB);
+          dk[1][s] = smem_desc_sw128(k_addr + (SL + s) * KV_SLAB);
+        }
+#pragma unroll
+        for (int kk = 0; kk < TKB / 16; ++kk) dv[kk] = smem_desc_sw128_mn(v_addr + kk * 2048, KV_SLAB, 1024);
+        const uint64_t dp = smem_desc_sw128(p_addr);
         auto issue_s = [&](int i) {
           const int b = i & 1;
           mbar_wait(&k_full[b], (i >> 1) & 1, a.err, 0x7203);
@@ -177,9 +189,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
           for (int s = 0; s < SL; ++s)
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk)
-              umma_bf16(tmem_s + b * TKB, smem_desc_sw128(q_addr + s * Q_SLAB) + (uint64_t)(kk * 2),
-                        smem_desc_sw128(k_addr + (b * SL + s) * KV_SLAB) + (uint64_t)(kk * 2), idesc_s,
-                        (s | kk) ? 1u : 0u);
+              umma_bf16(tmem_s + b * TKB, dq[s] + (uint64_t)(kk * 2), (b ? dk[1][s] : dk[0][s]) + (uint64_t)(kk * 2),
+                        idesc_s, (s | kk) ? 1u : 0u);
           umma_commit(&k_empty[b]);
           umma_commit(&s_full[b]);
         };
@@ -192,8 +203,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
           tc_fence_after();
 #pragma unroll
           for (int kk = 0; kk < TKB / 16; ++kk)      // 16 keys per MMA: 32 bytes along P's rows, two 8-key groups of V
-            umma_bf16(tmem_o, smem_desc_sw128(p_addr) + (uint64_t)(kk * 2),
-                      smem_desc_sw128_mn(v_addr + kk * 2048, KV_SLAB, 1024), idesc_o, (i | kk) ? 1u : 0u);
+            umma_bf16(tmem_o, dp + (uint64_t)(kk * 2), dv[kk], idesc_o, (i | kk) ? 1u : 0u);
           umma_commit(&v_empty);
           umma_commit(&pv_done);
           if (i + 2 < n_blocks) issue_s(i + 2);      // into the buffer that S(i) has left
