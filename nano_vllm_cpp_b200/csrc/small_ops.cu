@@ -70,8 +70,7 @@ __global__ void __launch_bounds__(256) rowdot_kernel(const float* __restrict__ a
 // WT rows.  Fewer, fatter blocks and a fraction of the loads; the order of the sum differs from
 // rowdot_kernel's, so a run uses one of the two for a given op and batch shape only where rounding-level
 // differences between batch shapes are accepted (bfloat16 runs).
-constexpr int WT = 4;
-template <typename TW>
+template <typename TW, int WT>
 __global__ void __launch_bounds__(256) rowdot_wide_kernel(const float* __restrict__ a, long long lda,
                                                           const TW* __restrict__ w, float* __restrict__ out,
                                                           long long ldo, int T, int N, int K) {
@@ -187,12 +186,30 @@ NV_API int nv_rowdot(const float* a, long long lda, const void* w, int w_dt, flo
                      int N, int K, int wide, cudaStream_t s) {
   if (!dt_ok(w_dt)) return NV_ERR_BAD_DTYPE;
   if (T == 0 || N == 0) return NV_OK;
-  if (wide && (size_t)WT * K * 4 <= 48 * 1024) {
-    const unsigned blocks = (unsigned)((T + WT - 1) / WT);
+  // many rows: eight per block where they fit the shared memory (every block reads the whole matrix, so
+  // fewer, fatter blocks halve what comes out of L2), else four
+  if (wide && T >= 1024 && (size_t)8 * K * 4 <= 96 * 1024) {
+    static bool attr_done = false;
+    if (!attr_done) {
+      cudaError_t e = cudaFuncSetAttribute(rowdot_wide_kernel<float, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+      if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(rowdot_wide_kernel<bf16, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+      if (e != cudaSuccess) return (int)e;
+      attr_done = true;
+    }
+    const unsigned blocks = (unsigned)((T + 7) / 8);
     if (w_dt == NV_DT_F32)
-      rowdot_wide_kernel<float><<<blocks, 256, (size_t)WT * K * 4, s>>>(a, lda, (const float*)w, out, ldo, T, N, K);
+      rowdot_wide_kernel<float, 8><<<blocks, 256, (size_t)8 * K * 4, s>>>(a, lda, (const float*)w, out, ldo, T, N, K);
     else
-      rowdot_wide_kernel<bf16><<<blocks, 256, (size_t)WT * K * 4, s>>>(a, lda, (const bf16*)w, out, ldo, T, N, K);
+      rowdot_wide_kernel<bf16, 8><<<blocks, 256, (size_t)8 * K * 4, s>>>(a, lda, (const bf16*)w, out, ldo, T, N, K);
+    NV_RETURN_LAST();
+  }
+  if (wide && (size_t)4 * K * 4 <= 48 * 1024) {
+    const unsigned blocks = (unsigned)((T + 3) / 4);
+    if (w_dt == NV_DT_F32)
+      rowdot_wide_kernel<float, 4><<<blocks, 256, (size_t)4 * K * 4, s>>>(a, lda, (const float*)w, out, ldo, T, N, K);
+    else
+      rowdot_wide_kernel<bf16, 4><<<blocks, 256, (size_t)4 * K * 4, s>>>(a, lda, (const bf16*)w, out, ldo, T, N, K);
     NV_RETURN_LAST();
   }
   if ((N + 3) / 4 > 65535) return NV_ERR_BAD_SIZE;

@@ -191,7 +191,7 @@ def test_tc_gemm_grouped(T, E, K):
 
 
 # ------------------------------------------------------------------------------- small products, router
-@pytest.mark.parametrize("T,N,K", [(1, 1, 64), (8, 60, 2048), (33, 7, 100), (5, 64, 3000)])
+@pytest.mark.parametrize("T,N,K", [(1, 1, 64), (8, 60, 2048), (33, 7, 100), (5, 64, 3000), (1030, 61, 520), (1025, 9, 2050)])
 @pytest.mark.parametrize("tw", [torch.float32, torch.bfloat16])
 def test_rowdot(T, N, K, tw):
     o = ops()
