@@ -141,19 +141,21 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         int it = 0;
         Tile t;
         for (int tile = blockIdx.x; it < last && get_tile(a, tile, y_tiles, t); tile += gridDim.x) {
-          for (int k = 0; k < t.n_steps && it < last; ++k, ++it) {
+          // tokens come in boxes of x_box rows, as many as the tile's rows (rounded up to the 16 of the MMA) need.
+          // (What a tile fixes is worked out here, once: this one thread's instructions are the pace of the ring.)
+          const int n_act = min(a.n_tile, (t.rows_here + 15) & ~15);
+          const int boxes = (n_act + a.x_box - 1) / a.x_box;
+          const uint32_t bytes = a_bytes * (two ? 2 : 1) + (uint32_t)boxes * a.x_box * 128;
+          const int wr = t.w_row_base + t.nb * a.w_per_cta;
+          int s = it % a.stages, ph = (it / a.stages) & 1;          // stage and phase of k-step `it`, kept by counting
+          for (int k = 0; k < t.n_steps && it < last; ++k, ++it, s = (s + 1 == a.stages ? 0 : s + 1), ph ^= (s == 0)) {
             if (it < first) continue;
-            const int s = it % a.stages;
             uint8_t* st = smem + (size_t)s * stage_bytes;
-            // tokens come in boxes of x_box rows, as many as the tile's rows (rounded up to the 16 of the MMA) need
-            const int n_act = min(a.n_tile, (t.rows_here + 15) & ~15);
-            const int boxes = (n_act + a.x_box - 1) / a.x_box;
             if (weights) {
-              mbar_wait(&empty_bar[s], ((it / a.stages) & 1) ^ 1, a.err, 0x7001);
-              mbar_expect_tx(&full_bar[s], a_bytes * (two ? 2 : 1) + (uint32_t)boxes * a.x_box * 128);
+              mbar_wait(&empty_bar[s], ph ^ 1, a.err, 0x7001);
+              mbar_expect_tx(&full_bar[s], bytes);
             }
             const int kc = (t.k_begin + k) * BLOCK_K;
-            const int wr = t.w_row_base + t.nb * a.w_per_cta;
             if (weights) {
               tma_load_2d(st, &tm_w, &full_bar[s], kc, wr);
               if (two)     // swiglu: the up rows of the same features; dual: the next 128 features
@@ -178,6 +180,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       int it = 0, n = 0;                           // k-steps consumed, tiles done
+      int s = 0;                                   // stage of k-step `it` and the parity of its use, kept by counting:
+      uint32_t ph = 0;                             // this one thread's instructions pace the tensor core
+      const uint64_t desc0 = smem_desc_sw128(0);
+      const uint32_t smem0 = smem_u32(smem);
       Tile t;
       for (int tile = blockIdx.x; get_tile(a, tile, y_tiles, t); tile += gridDim.x, ++n) {
         const int b = a.acc_bufs == 2 ? (n & 1) : 0;
@@ -189,13 +195,12 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         // expert costs a short product
         const uint32_t idesc = instr_desc(min(a.n_tile, (t.rows_here + 15) & ~15));
         for (int k = 0; k < t.n_steps; ++k, ++it) {
-          const int s = it % a.stages;
-          mbar_wait(&full_bar[s], (it / a.stages) & 1, a.err, 0x7002);
+          mbar_wait(&full_bar[s], ph, a.err, 0x7002);
           tc_fence_after();
-          const uint32_t sa = smem_u32(smem + (size_t)s * stage_bytes);
-          const uint64_t da = smem_desc_sw128(sa);
-          const uint64_t du = smem_desc_sw128(sa + a_bytes);
-          const uint64_t dx = smem_desc_sw128(sa + a_bytes * (two ? 2 : 1));
+          // a descriptor is fixed bits plus the tile's address / 16 (shared memory addresses fit its 14 bits)
+          const uint64_t da = desc0 + (uint64_t)((smem0 + (uint32_t)s * stage_bytes) >> 4);
+          const uint64_t du = da + (uint64_t)(a_bytes >> 4);
+          const uint64_t dx = da + (uint64_t)((a_bytes * (two ? 2 : 1)) >> 4);
 #pragma unroll
           for (int kk = 0; kk < BLOCK_K / UMMA_K; ++kk) {
             const uint64_t adv = (uint64_t)(kk * UMMA_K * 2 >> 4);   // 32 bytes per k-slice inside the swizzle row
@@ -204,6 +209,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
             if (two) umma_bf16(acc_addr + a.n_tile, du + adv, dx + adv, idesc, acc);
           }
           umma_commit(&empty_bar[s]);     // the stage may be refilled once these MMAs have read it
+          if (++s == a.stages) { s = 0; ph ^= 1; }
         }
         umma_commit(&acc_full[b]);        // the accumulator is complete (at once if the tile had no k-steps)
       }
