@@ -201,13 +201,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
           const uint64_t da = desc0 + (uint64_t)((smem0 + (uint32_t)s * stage_bytes) >> 4);
           const uint64_t du = da + (uint64_t)(a_bytes >> 4);
           const uint64_t dx = da + (uint64_t)((a_bytes * (two ? 2 : 1)) >> 4);
-#pragma unroll
-          for (int kk = 0; kk < BLOCK_K / UMMA_K; ++kk) {
-            const uint64_t adv = (uint64_t)(kk * UMMA_K * 2 >> 4);   // 32 bytes per k-slice inside the swizzle row
-            const uint32_t acc = (k > 0 || kk > 0) ? 1u : 0u;
-            umma_bf16(acc_addr, da + adv, dx + adv, idesc, acc);
-            if (two) umma_bf16(acc_addr + a.n_tile, du + adv, dx + adv, idesc, acc);
-          }
+          // (the order differs from slice-by-slice over both accumulators only in which accumulator goes first)
+          umma_bf16_x4(acc_addr, da, dx, idesc, k > 0 ? 1u : 0u);
+          if (two) umma_bf16_x4(acc_addr + a.n_tile, du, dx, idesc, k > 0 ? 1u : 0u);
           umma_commit(&empty_bar[s]);     // the stage may be refilled once these MMAs have read it
           if (++s == a.stages) { s = 0; ph ^= 1; }
         }
