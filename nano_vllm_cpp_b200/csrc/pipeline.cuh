@@ -61,6 +61,18 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* t
       : "memory");
 }
 
+// The same with shared-memory addresses already in their 32-bit form, for a thread whose instruction count is on
+// the critical path.
+__device__ __forceinline__ void tma_load_2d_a(uint32_t smem_dst, const CUtensorMap* tm, uint32_t bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_dst), "l"((uint64_t)tm), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx_a(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
 // Host: tensor map of a row-major bf16 matrix [rows, cols] (row stride ld elements), boxes of box_rows x 64
 // elements, 128-byte swizzle, zero fill outside; cached.  Defined in tc_gemm.cu.
 int nv_tensor_map_bf16(const void* ptr, long long rows, long long cols, long long ld, int box_rows, CUtensorMap* out);

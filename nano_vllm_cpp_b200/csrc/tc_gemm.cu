@@ -136,6 +136,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     // of k-steps are fetched at once, the tokens (that kernel's output) only after it has finished.
     if (lane == 0) {
       const int pre = a.early ? a.stages : 0;
+      const uint32_t smem0 = smem_u32(smem), full0 = smem_u32(&full_bar[0]);
       // issues the k-steps numbered [first, last) of this CTA's walk over its tiles
       auto walk = [&](int first, int last, bool weights, bool tokens) {
         int it = 0;
@@ -150,21 +151,21 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
           int s = it % a.stages, ph = (it / a.stages) & 1;          // stage and phase of k-step `it`, kept by counting
           for (int k = 0; k < t.n_steps && it < last; ++k, ++it, s = (s + 1 == a.stages ? 0 : s + 1), ph ^= (s == 0)) {
             if (it < first) continue;
-            uint8_t* st = smem + (size_t)s * stage_bytes;
+            const uint32_t st = smem0 + (uint32_t)s * stage_bytes, bar = full0 + (uint32_t)s * 8;
             if (weights) {
               mbar_wait(&empty_bar[s], ph ^ 1, a.err, 0x7001);
-              mbar_expect_tx(&full_bar[s], bytes);
+              mbar_expect_tx_a(bar, bytes);
             }
             const int kc = (t.k_begin + k) * BLOCK_K;
             if (weights) {
-              tma_load_2d(st, &tm_w, &full_bar[s], kc, wr);
+              tma_load_2d_a(st, &tm_w, bar, kc, wr);
               if (two)     // swiglu: the up rows of the same features; dual: the next 128 features
-                tma_load_2d(st + a_bytes, &tm_w, &full_bar[s], kc, wr + (a.swiglu ? a.N : TILE_W));
+                tma_load_2d_a(st + a_bytes, &tm_w, bar, kc, wr + (a.swiglu ? a.N : TILE_W));
             }
             if (tokens)
               for (int b = 0; b < boxes; ++b)
-                tma_load_2d(st + a_bytes * (two ? 2 : 1) + (size_t)b * a.x_box * 128, &tm_x, &full_bar[s], kc,
-                            t.row0 + b * a.x_box);
+                tma_load_2d_a(st + a_bytes * (two ? 2 : 1) + (uint32_t)b * a.x_box * 128, &tm_x, bar, kc,
+                              t.row0 + b * a.x_box);
           }
         }
       };
