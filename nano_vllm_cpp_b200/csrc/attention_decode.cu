@@ -382,13 +382,14 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
     if (lane == 0) {
       const int newest = (n - 1) / a.page - pb;          // this split's page that is still being written
       bool waited = false;
-      for (int i = 0; i < n_pages; ++i) {
-        const int s = i % a.stages;
+      int s = 0;                                   // stage of page i and the parity of its use, kept by counting
+      uint32_t ph = 0;                             // (this one thread's instructions pace the ring)
+      for (int i = 0; i < n_pages; ++i, s = (s + 1 == a.stages ? 0 : s + 1), ph ^= (s == 0)) {
         if (!waited && (i >= a.stages || i == newest)) {
           grid_dep_wait();
           waited = true;
         }
-        mbar_wait(&empty_bar[s], ((i / a.stages) & 1) ^ 1, a.err, 0x7111);
+        mbar_wait(&empty_bar[s], ph ^ 1, a.err, 0x7111);
         const int blk = i < BT_CACHE ? bt_s[i] : bt[pb + i];
         uint8_t* st = dec_smem + (size_t)s * stage_bytes;
         if (blk < 0) {
@@ -418,10 +419,12 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
     for (int kk = 0; kk < D / 16; ++kk)
       ldsm4(smem_u32(q_s + ((lane % 8) + 8 * ((lane / 8) % 2)) * QLD + kk * 16 + 8 * (lane / 16)), qa[kk][0], qa[kk][1],
             qa[kk][2], qa[kk][3]);
+    int s = warp % a.stages;                       // stage of page i (the ring is a multiple of WARPS stages deep)
+    uint32_t ph = (warp / a.stages) & 1;
+    const uint32_t smem0 = smem_u32(dec_smem);
     for (int i = warp; i < n_pages; i += WARPS) {
-      const int s = i % a.stages;
-      mbar_wait(&full_bar[s], (i / a.stages) & 1, a.err, 0x7112);
-      const uint32_t kbase = smem_u32(dec_smem + (size_t)s * stage_bytes);
+      mbar_wait(&full_bar[s], ph, a.err, 0x7112);
+      const uint32_t kbase = smem0 + (uint32_t)s * stage_bytes;
       const uint32_t vbase = kbase + half_stage;
       const int j_page = (pb + i) * a.page;
       for (int kb = 0; kb < a.page / 16; ++kb) {
@@ -505,6 +508,8 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __gri
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty_bar[s]);
+      s += WARPS;
+      if (s >= a.stages) { s -= a.stages; ph ^= 1; }
     }
     l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
     l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
