@@ -186,11 +186,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
           mbar_wait(&k_full[b], (i >> 1) & 1, a.err, 0x7203);
           tc_fence_after();
 #pragma unroll
-          for (int s = 0; s < SL; ++s)
-#pragma unroll
-            for (int kk = 0; kk < 4; ++kk)
-              umma_bf16(tmem_s + b * TKB, dq[s] + (uint64_t)(kk * 2), (b ? dk[1][s] : dk[0][s]) + (uint64_t)(kk * 2),
-                        idesc_s, (s | kk) ? 1u : 0u);
+          for (int s = 0; s < SL; ++s)           // the four 16-wide slices of a 64-element slab in one block
+            umma_bf16_x4(tmem_s + b * TKB, dq[s], b ? dk[1][s] : dk[0][s], idesc_s, s ? 1u : 0u);
           umma_commit(&k_empty[b]);
           umma_commit(&s_full[b]);
         };
@@ -201,9 +198,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
           mbar_wait(&p_full, i & 1, a.err, 0x7205);  // P(i) is written, S(i) is read, O is rescaled
           mbar_wait(&v_full, i & 1, a.err, 0x7206);
           tc_fence_after();
-#pragma unroll
-          for (int kk = 0; kk < TKB / 16; ++kk)      // 16 keys per MMA: 32 bytes along P's rows, two 8-key groups of V
-            umma_bf16(tmem_o, dp + (uint64_t)(kk * 2), dv[kk], idesc_o, (i | kk) ? 1u : 0u);
+          // 16 keys per product: 32 bytes (2 units) along P's rows, two 8-key groups (2,048 bytes = 128 units) of V
+          umma_bf16_x4s(tmem_o, dp, dv[0], idesc_o, i ? 1u : 0u, 2, 128);
           umma_commit(&v_empty);
           umma_commit(&pv_done);
           if (i + 2 < n_blocks) issue_s(i + 2);      // into the buffer that S(i) has left
