@@ -78,9 +78,31 @@ __global__ void __launch_bounds__(256) rowdot_wide_kernel(const float* __restric
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const int t0 = blockIdx.x * WT;
   const int nt = min(WT, T - t0);
-  for (int i = threadIdx.x; i < WT * K; i += 256) {
-    const int r = i / K, k = i - r * K;
-    row_s[i] = r < nt ? a[(size_t)(t0 + r) * lda + k] : 0.f;
+  if (K % 4 == 0 && lda % 4 == 0 && ((uintptr_t)a & 15) == 0) {
+    // 16-byte loads, four in flight per thread: one scalar load at a time made this copy the kernel's time
+    const int k4 = K / 4;
+    for (int r = 0; r < WT; ++r) {
+      const float4* src = (const float4*)(a + (size_t)(t0 + r) * lda);
+      float4* dst = (float4*)(row_s + (size_t)r * K);
+      for (int i0 = threadIdx.x; i0 < k4; i0 += 4 * 256) {
+        float4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int i = i0 + u * 256;
+          v[u] = (r < nt && i < k4) ? src[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int i = i0 + u * 256;
+          if (i < k4) dst[i] = v[u];
+        }
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < WT * K; i += 256) {
+      const int r = i / K, k = i - r * K;
+      row_s[i] = r < nt ? a[(size_t)(t0 + r) * lda + k] : 0.f;
+    }
   }
   __syncthreads();
   const bool vec = K % 4 == 0 && ((uintptr_t)w & 15) == 0;
