@@ -77,10 +77,18 @@ __device__ __forceinline__ void align_block(const int* __restrict__ idx, int TK,
   const int tid = threadIdx.x, nthr = blockDim.x;
   for (int e = tid; e < E; e += nthr) cnt[e] = 0;
   __syncthreads();
-  for (int i = tid; i < TK; i += nthr) {
-    int e = idx[i];
-    if (e < 0 || e >= E) { atomicExch(err, 1 + i); continue; }
-    atomicAdd(&cnt[e], 1);
+  // eight loads in flight per thread: one load per atomic made the two passes over idx the kernel's time
+  for (int i0 = tid; i0 < TK; i0 += 8 * nthr) {
+    int ev[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) ev[u] = i0 + u * nthr < TK ? idx[i0 + u * nthr] : 0;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int i = i0 + u * nthr;
+      if (i >= TK) break;
+      if (ev[u] < 0 || ev[u] >= E) { atomicExch(err, 1 + i); continue; }
+      atomicAdd(&cnt[ev[u]], 1);
+    }
   }
   __syncthreads();
   if (tid < 32) {                           // warp 0: exclusive prefix sums over the experts, 32 at a time
@@ -130,11 +138,18 @@ __device__ __forceinline__ void align_block(const int* __restrict__ idx, int TK,
       }
   }
   __syncthreads();
-  for (int i = tid; i < TK; i += nthr) {
-    int e = idx[i];
-    if (e < 0 || e >= E) continue;
-    int p = atomicAdd(&cur[e], 1);
-    sorted_token[p] = i / K;
-    pair_pos[i] = p;
+  for (int i0 = tid; i0 < TK; i0 += 8 * nthr) {
+    int ev[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) ev[u] = i0 + u * nthr < TK ? idx[i0 + u * nthr] : -1;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int i = i0 + u * nthr;
+      if (i >= TK) break;
+      if (ev[u] < 0 || ev[u] >= E) continue;
+      const int p = atomicAdd(&cur[ev[u]], 1);
+      sorted_token[p] = i / K;
+      pair_pos[i] = p;
+    }
   }
 }
