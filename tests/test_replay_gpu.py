@@ -9,12 +9,12 @@ from helpers import Replay, prompt
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"A": [5, 17, 33, 70], "B": [1, 9, 24, 40, 70]}
+LENGTHS = {"A": [5, 17, 33, 70], "B": [1, 9, 24, 40, 70], "C": [2, 33, 64, 129, 200]}
 
 
 @pytest.fixture(scope="module")
 def folders(tmp_path_factory):
-    return {c: helpers.model_folder(c, tmp_path_factory) for c in ("A", "B")}
+    return {c: helpers.model_folder(c, tmp_path_factory) for c in ("A", "B", "C")}
 
 
 def make_runner(mdir, dtype, max_tokens, max_requests=4):
@@ -23,9 +23,9 @@ def make_runner(mdir, dtype, max_tokens, max_requests=4):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("case", ["A", "B"])
+@pytest.mark.parametrize("case", ["A", "B", "C"])
 def test_whole(case, dtype, folders):
-    runner = make_runner(folders[case], dtype, 128)
+    runner = make_runner(folders[case], dtype, 256 if case == "C" else 128)
     rp = Replay(runner)
     for n in LENGTHS[case]:
         ids = prompt(case, n)
@@ -34,7 +34,7 @@ def test_whole(case, dtype, folders):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("case", ["A", "B"])
+@pytest.mark.parametrize("case", ["A", "B", "C"])
 def test_last_32_one_by_one(case, dtype, folders):
     runner = make_runner(folders[case], dtype, 128)
     rp = Replay(runner)
@@ -49,7 +49,7 @@ def test_last_32_one_by_one(case, dtype, folders):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("case", ["A", "B"])
+@pytest.mark.parametrize("case", ["A", "B", "C"])
 def test_portions_of_changing_size(case, dtype, folders):
     runner = make_runner(folders[case], dtype, 128)
     rp = Replay(runner)
@@ -64,7 +64,7 @@ def test_portions_of_changing_size(case, dtype, folders):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("case", ["A", "B"])
+@pytest.mark.parametrize("case", ["A", "B", "C"])
 def test_mixed_with_page_reuse(case, dtype, folders):
     """Up to four live requests; portions of some beside decode tokens of others; the pool holds 192
     tokens while the requests need 5 x 64 in turn, so finished requests' pages are used again."""
