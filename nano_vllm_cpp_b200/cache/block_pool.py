@@ -46,7 +46,10 @@ class BlockPool:
 
     def __del__(self):
         if getattr(self, "_owned", False) and self._h:
-            host.lib().nvh_pool_destroy(self._h)
+            try:
+                host.lib().nvh_pool_destroy(self._h)
+            except TypeError:          # the interpreter is shutting down and the module is already gone
+                pass
             self._h = None
 
     def _page(self, page: int) -> int:

@@ -90,7 +90,10 @@ class CacheManager:
 
     def __del__(self):
         if getattr(self, "_h", None):
-            host.lib().nvh_manager_destroy(self._h)
+            try:
+                host.lib().nvh_manager_destroy(self._h)
+            except TypeError:          # the interpreter is shutting down and the module is already gone
+                pass
             self._h = None
 
     def _native(self, rid, create: bool = False) -> int:

@@ -71,7 +71,10 @@ class Scheduler:
 
     def __del__(self):
         if getattr(self, "_h", None):
-            host.lib().nvs_destroy(self._h)
+            try:
+                host.lib().nvs_destroy(self._h)
+            except TypeError:          # the interpreter is shutting down and the module is already gone
+                pass
             self._h = None
 
     # ------------------------------------------------------------------ queue
