@@ -401,6 +401,33 @@ def test_rope_store(Hq, Hkv, D, rot, dtype):
         err.check("rope")
 
 
+@pytest.mark.parametrize("D,window,ctx,new", [(128, 0, 0, 1100), (64, 300, 500, 700), (128, 0, 16000, 900), (128, 5000, 0, 17000)])
+def test_attention_prefill_tc_long(D, window, ctx, new, monkeypatch):
+    """Long portions on the tcgen05 kernel against the mma.sync kernel on the same cache: many row tiles, a
+    window that gives early blocks of keys to nobody, and more pages than the kernel keeps in shared memory."""
+    o = ops()
+    Hq, Hkv, page = 2, 1, 16
+    n = ctx + new
+    kc, vc, bt, ks, vs = paged_setup([n], Hkv, D, page, torch.bfloat16, seed=3)
+    qkv = rnd(new, (Hq + 2 * Hkv) * D, dtype=torch.bfloat16, seed=4)
+    cu = torch.tensor([0, new], dtype=torch.int32, device=DEV)
+    p0 = torch.tensor([ctx], dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(D)
+    outs = []
+    for legacy in (False, True):
+        if legacy:
+            monkeypatch.setenv("NV_PREFILL_LEGACY", "1")
+        out = torch.full((new, Hq * D), float("nan"), dtype=torch.bfloat16, device=DEV)
+        err = o.ErrorFlag(DEV)
+        o.attention_prefill(qkv, kc, vc, bt, cu, p0, (new + 63) // 64, scale, window, out, Hq, Hkv, D, err=err)
+        err.check("prefill attention")
+        outs.append(out)
+    close(outs[0], outs[1], 1.5e-2, "tcgen05 vs mma.sync")
+    for r in (0, new // 2, new - 1):                     # and a few rows against float64
+        want = attention_reference(qkv[r, :Hq * D].reshape(Hq, D).cpu(), ks[0], vs[0], ctx + r, scale, window)
+        close(outs[0][r], want.reshape(-1), 1.5e-2, f"row {r}")
+
+
 @pytest.mark.parametrize("Hq,Hkv,D,page", [(3, 1, 32, 16), (4, 4, 16, 16), (6, 2, 48, 32), (4, 2, 128, 16), (2, 1, 256, 16),
                                            (5, 5, 80, 16), (3, 3, 64, 16), (6, 2, 64, 32), (2, 1, 128, 64), (7, 1, 64, 64),
                                            (2, 2, 128, 32)])
