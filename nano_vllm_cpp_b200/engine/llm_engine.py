@@ -116,7 +116,8 @@ class LLMEngine:
             entries.append(StepEntry(s.seq.seq_id, toks, [s.count - 1] if s.samples else []))
             if s.samples:
                 temps.append(s.seq.temperature)
-                us.append(uniform(s.seq.seed, s.seq.num_completion_tokens))
+                # greedy rows draw nothing: their number is never looked at
+                us.append(uniform(s.seq.seed, s.seq.num_completion_tokens) if s.seq.temperature > 0 else 0.0)
                 sampled_seqs.append(s.seq)
             if s.count == 1 and s.start >= s.seq.num_prompt_tokens:
                 n_decode += 1

@@ -26,6 +26,14 @@ class StepError(RuntimeError):
     pass
 
 
+class _Prepared:
+    """What is left of a step's preparation when nobody needs its arrays on the host side."""
+    __slots__ = ("native_ids", "ends")
+
+    def __init__(self, native_ids, ends):
+        self.native_ids, self.ends = native_ids, ends
+
+
 class ModelRunner:
     def __init__(self, model_dir: str, *, dtype: str = "bfloat16", page_size: int = 16, num_pages: int | None = None,
                  max_tokens: int | None = None, max_requests: int = 4, max_model_len: int | None = None,
@@ -85,7 +93,7 @@ class ModelRunner:
         return self.manager.get(rid).num_tokens
 
     # ------------------------------------------------------------------ the step
-    def prepare(self, entries: list, static_dev=None, sampling=None):
+    def prepare(self, entries: list, static_dev=None, sampling=None, views: bool = True):
         """Takes pages for the entries' positions and builds the batch arrays (natively, straight into a pinned
         buffer).  ``sampling`` = (temperatures, uniforms), one pair per wanted row, rides along in the same copy."""
         seen = set()
@@ -118,6 +126,9 @@ class ModelRunner:
             o, n = seg["u"]
             buf[o:o + n].view(np.float64)[:] = us
         dev = self.stager.submit(ticket, total, static_dev)
+        self.last_h2d_bytes = total * 4
+        if views is False:          # a replayed graph has its views already: only what the commit needs
+            return _Prepared(native_ids, [pos0 + len(e.tokens) for e, (_, pos0) in zip(entries, slots)])
         infos, row0 = [], 0
         for e, (slot, pos0) in zip(entries, slots):
             infos.append(EntryInfo(e.rid, slot, pos0, len(e.tokens), row0))
@@ -128,7 +139,8 @@ class ModelRunner:
         return batch
 
     def _commit(self, batch) -> None:
-        self.manager.commit_many(batch.native_ids, [i.pos0 + i.length for i in batch.entries])
+        ends = batch.ends if isinstance(batch, _Prepared) else [i.pos0 + i.length for i in batch.entries]
+        self.manager.commit_many(batch.native_ids, ends)
 
     @torch.no_grad()
     def step(self, entries: list, check: bool = True) -> torch.Tensor:
@@ -215,7 +227,7 @@ class ModelRunner:
             self._graphs[key] = (graph, static_dev, static_logits, static_out, ops.launch_count() - before)
             return logits, batch, out
         graph, static_dev, static_logits, static_out, launches = g
-        batch = self.prepare(entries, static_dev, sampling)
+        batch = self.prepare(entries, static_dev, sampling, views=False)
         graph.replay()
         ops.add_launches(launches)
         return static_logits, batch, static_out
