@@ -62,6 +62,9 @@ struct TcArgs {
   int tmem_cols;
   int early;                          // launched as a programmatic dependent: weights are fetched before the wait
   int x_box;                          // token rows per TMA box of X: min(n_tile, 64)
+  // Dense products whose tiles do not fill a last wave of CTAs: the tiles from rest_first on are cut into
+  // rest_parts token parts each (numbered part by part after rest_first), so that the last wave is short.
+  int rest_first, rest_parts;
 };
 
 // ------------------------------------------------------------------ the kernel
@@ -76,6 +79,12 @@ struct Tile {
 
 __device__ __forceinline__ bool get_tile(const TcArgs& a, int tile_id, int y_tiles, Tile& t) {
   const int total = a.n_blocks * y_tiles * a.splits;
+  int part = 0;
+  if (a.rest_parts > 1 && tile_id >= a.rest_first) {
+    const int h = tile_id - a.rest_first;
+    tile_id = a.rest_first + h / a.rest_parts;
+    part = h % a.rest_parts;
+  }
   if (tile_id >= total) return false;
   t.nb = tile_id % a.n_blocks;
   const int rest = tile_id / a.n_blocks;
@@ -89,6 +98,10 @@ __device__ __forceinline__ bool get_tile(const TcArgs& a, int tile_id, int y_til
     t.row0 = y * a.n_tile;
     t.rows_here = min(a.n_tile, a.M_tok - t.row0);
     t.w_row_base = 0;
+    if (a.rest_parts > 1 && tile_id >= a.rest_first) {     // (only when every tile is whole: see the launcher)
+      t.rows_here = a.n_tile / a.rest_parts;
+      t.row0 += part * t.rows_here;
+    }
   }
   t.k_begin = t.z * a.k_steps_per_split;
   t.n_steps = max(0, min(a.k_steps_total, t.k_begin + a.k_steps_per_split) - t.k_begin);
@@ -478,6 +491,16 @@ NV_API int nv_tc_gemm(const void* X, long long ldx, int M_tok, const void* W, in
   const long long total = (long long)a.n_blocks * y_tiles * a.splits;     // an upper bound when grouped
   const long long resident = (long long)num_sms * (pair ? 2 : 1);
   dim3 grid((unsigned)(total < resident ? total : resident));
+  // a last wave with tiles for less than half of the CTAs: cut those tiles into two or four token parts
+  a.rest_first = 0;
+  a.rest_parts = 1;
+  if (!grouped && a.splits == 1 && total > resident && M_tok % n_tile == 0 && n_tile >= 128) {
+    const long long rest = total % resident;
+    if (rest > 0 && rest * 2 <= resident) {
+      a.rest_parts = (rest * 4 <= resident && n_tile >= 256) ? 4 : 2;
+      a.rest_first = (int)(total - rest);
+    }
+  }
   cudaError_t e;
   if (a.early) {
     // programmatic dependent of the kernel before it in the stream (an edge of that kind when captured)

@@ -146,6 +146,12 @@ def test_tc_gemm_shapes(M, N, K, swiglu):
     tc_case(M, N, K, swiglu, False, torch.bfloat16, seed=5)
 
 
+def test_tc_gemm_short_last_wave():
+    """More tiles than CTAs and a last wave for less than half of them: its tiles are cut into token parts."""
+    tc_case(2048, 6144, 264, False, True, torch.bfloat16)        # 192 tiles of 256 x 256 on 148 CTAs
+    tc_case(1024, 5120, 136, False, False, torch.float32)        # 160 tiles: twelve left over, four parts each
+
+
 @pytest.mark.parametrize("splits", [2, 3, 7])
 def test_tc_gemm_split_k(splits):
     tc_case(8, 256, 2048, False, True, torch.float32, splits=splits)
