@@ -415,7 +415,7 @@ NV_API int nv_tc_gemm_splits(int M_tok, int N, int K, int n_tile, int num_sms) {
   int ctas = ((N + TILE_W - 1) / TILE_W) * ((M_tok + n_tile - 1) / n_tile);
   int k_steps = (K + BLOCK_K - 1) / BLOCK_K;
   if (ctas >= num_sms || k_steps < 8) return 1;
-  int s = num_sms / ctas;
+  int s = 2 * num_sms / ctas;                      // two CTAs of these small stages live on a multiprocessor
   if (s > k_steps / 4) s = k_steps / 4;
   if (s > 16) s = 16;
   return s < 1 ? 1 : s;
