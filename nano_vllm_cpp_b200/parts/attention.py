@@ -42,6 +42,7 @@ class PagedAttention(Mixer):
         if self.bias:
             s.update({"q_proj.bias": TensorSpec((q,), kind="vector"), "k_proj.bias": TensorSpec((kv,), kind="vector"),
                       "v_proj.bias": TensorSpec((kv,), kind="vector")})
+        s.update(self.position.tensor_specs(available))      # a position encoding may have tensors of its own
         return s
 
     def load(self, fetch, ctx):

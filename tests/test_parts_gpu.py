@@ -3,6 +3,7 @@ order list (a layer run twice, a call that reads another call's cache); and a to
 per-request state that is defined here, registered, built from a config.json and stepped through the
 engine without any change to the package."""
 import json
+import math
 import os
 from dataclasses import dataclass
 
@@ -353,3 +354,144 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
     for r in ids:
         got = torch.stack([rp.logits[(r, p)] for p in range(len(ids[r]))])
         helpers.assert_close(got, toy_plain(cfg, W, ids[r]), "float32", f"toy request {r}")
+
+
+# ------------------------------------------------------------------------------- two more toy parts: a position encoding and a routing feed-forward
+@dataclass
+class Toy2Config:
+    vocab_size: int
+    hidden_size: int
+    num_hidden_layers: int
+    num_heads: int
+    head_dim: int
+    intermediate_size: int
+    rms_norm_eps: float
+
+    @classmethod
+    def from_dict(cls, d):
+        return cls(*(d[k] for k in ("vocab_size", "hidden_size", "num_hidden_layers", "num_heads", "head_dim",
+                                   "intermediate_size", "rms_norm_eps")))
+
+
+def define_toy2():
+    """A position encoding whose frequencies are a tensor of the model (and that turns only half of a head), and a
+    feed-forward that sends a row to one of two SwiGLU experts by the sign of a learned projection."""
+    from nano_vllm_cpp_b200.parts import (FeedForward, PositionEncoding, TensorSpec, PartSpec, LayerSpec, ModelSpec,
+                                          register_part)
+    from nano_vllm_cpp_b200.parts.linear import linear
+    from nano_vllm_cpp_b200.config import register_architecture
+
+    class LearnedFrequencies(PositionEncoding):
+        def __init__(self, rotary_dim):
+            self.rotary_dim = rotary_dim
+
+        def tensor_specs(self, available=None):
+            return {"freq": TensorSpec((self.rotary_dim // 2,), kind="vector")}
+
+        def load(self, fetch, ctx):
+            self.ctx = ctx
+            self._inv = fetch("freq").float().contiguous()
+
+        def inv_freq(self):
+            return self._inv
+
+    class SignSwitch(FeedForward):
+        graph_safe = False                      # gathers rows by a mask on the host side of the stream
+
+        def __init__(self, hidden_size, intermediate_size):
+            self.hidden, self.inter = hidden_size, intermediate_size
+
+        def tensor_specs(self, available=None):
+            s = {"switch.weight": TensorSpec((1, self.hidden))}
+            for e in (0, 1):
+                s[f"e{e}.gate_up.weight"] = TensorSpec((2 * self.inter, self.hidden))
+                s[f"e{e}.down.weight"] = TensorSpec((self.hidden, self.inter))
+            return s
+
+        def load(self, fetch, ctx):
+            self.ctx = ctx
+            self.sw = fetch("switch.weight").float()
+            self.w = [(fetch(f"e{e}.gate_up.weight"), fetch(f"e{e}.down.weight")) for e in (0, 1)]
+
+        def forward(self, h, h32, batch):
+            side = (h.float() @ self.sw.T).flatten() < 0
+            out = torch.zeros((h.shape[0], self.hidden), dtype=torch.float32, device=h.device)
+            for e in (0, 1):
+                rows = torch.nonzero(side == bool(e)).flatten()
+                if rows.numel():
+                    x = h.index_select(0, rows).contiguous()
+                    act = linear(self.ctx, x, self.w[e][0], self.ctx.act_dtype, swiglu=True)
+                    out.index_copy_(0, rows, linear(self.ctx, act, self.w[e][1], torch.float32))
+            return out
+
+    register_part("position", "toy_learned_frequencies", LearnedFrequencies)
+    register_part("feed_forward", "toy_sign_switch", SignSwitch)
+
+    def build(cfg):
+        norm = PartSpec("rmsnorm", dict(size=cfg.hidden_size, eps=cfg.rms_norm_eps))
+        att = PartSpec("paged_attention", dict(
+            hidden_size=cfg.hidden_size, num_heads=cfg.num_heads, num_kv_heads=cfg.num_heads, head_dim=cfg.head_dim,
+            bias=False, position=PartSpec("toy_learned_frequencies", dict(rotary_dim=cfg.head_dim // 2))))
+        ff = PartSpec("toy_sign_switch", dict(hidden_size=cfg.hidden_size, intermediate_size=cfg.intermediate_size))
+        layers = [LayerSpec(norm1=norm, mixer=att, norm2=norm, feed_forward=ff) for _ in range(cfg.num_hidden_layers)]
+        return ModelSpec(vocab_size=cfg.vocab_size, hidden_size=cfg.hidden_size, layers=layers, final_norm=norm,
+                         tie_word_embeddings=True, init_std=0.1)
+
+    register_architecture("ToySwitchForCausalLM", Toy2Config.from_dict, build)
+
+
+def toy2_plain(cfg, W, ids):
+    T, Hh, D, R = len(ids), cfg["num_heads"], cfg["head_dim"], cfg["head_dim"] // 2
+    x = pm.embedding(W["model.embed_tokens.weight"], ids)
+    pos = torch.arange(T, dtype=torch.float64)
+    for l in range(cfg["num_hidden_layers"]):
+        p = f"model.layers.{l}."
+        h = pm.rms_norm(x, W[p + "input_layernorm.weight"], cfg["rms_norm_eps"])
+        q, k, v = (h @ W[p + f"self_attn.{n}_proj.weight"].double().T for n in "qkv")
+        ang = pos[:, None] * W[p + "self_attn.freq"].double()[None, :]          # [T, R/2]
+        c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+
+        def turn(t):
+            t = t.reshape(T, Hh, D).clone()
+            a, b = t[..., :R // 2].clone(), t[..., R // 2:R].clone()
+            t[..., :R // 2], t[..., R // 2:R] = a * c - b * s, b * c + a * s
+            return t
+
+        q, k, v = turn(q), turn(k), v.reshape(T, Hh, D)
+        sc = torch.einsum("thd,uhd->htu", q, k) / math.sqrt(D)
+        sc = sc.masked_fill(torch.triu(torch.ones(T, T, dtype=torch.bool), 1), float("-inf"))
+        att = torch.einsum("htu,uhd->thd", torch.softmax(sc, -1), v).reshape(T, Hh * D)
+        x = x + att @ W[p + "self_attn.o_proj.weight"].double().T
+        h = pm.rms_norm(x, W[p + "post_attention_layernorm.weight"], cfg["rms_norm_eps"])
+        side = (h @ W[p + "mlp.switch.weight"].double().T).flatten() < 0
+        out = torch.zeros_like(x)
+        for e in (0, 1):
+            gu = h @ W[p + f"mlp.e{e}.gate_up.weight"].double().T
+            I = gu.shape[1] // 2
+            y = (gu[:, :I] / (1 + torch.exp(-gu[:, :I])) * gu[:, I:]) @ W[p + f"mlp.e{e}.down.weight"].double().T
+            out[side == bool(e)] = y[side == bool(e)]
+        x = x + out
+    return pm.rms_norm(x, W["model.norm.weight"], cfg["rms_norm_eps"]) @ W["model.embed_tokens.weight"].double().T
+
+
+def test_toy_position_encoding_and_routing_feed_forward(tmp_path):
+    """Another position encoding and a feed-forward with routing of its own, registered from outside the package,
+    in a model that is built, loaded and stepped (whole, and cut into a portion and single tokens)."""
+    from nano_vllm_cpp_b200.weights import write_model_folder
+    from nano_vllm_cpp_b200.engine.runner import ModelRunner
+    define_toy2()
+    cfg = dict(architectures=["ToySwitchForCausalLM"], vocab_size=70, hidden_size=48, num_hidden_layers=2, num_heads=3,
+               head_dim=16, intermediate_size=40, rms_norm_eps=1e-5)
+    mdir = write_model_folder(cfg, str(tmp_path / "toy2"), seed=5, norm_std=0.1, dtype="float32")
+    _, W = pm.read_folder(mdir)
+    runner = ModelRunner(mdir, dtype="float32", max_tokens=64, max_requests=2)
+    ids = [int(t) for t in np.random.RandomState(1).randint(0, 70, size=21)]
+    want = toy2_plain(cfg, W, ids)
+    rp = helpers.Replay(runner)
+    rp.step([("w", ids, True)], end=["w"])
+    rp.step([("c", ids[:13], True)])
+    for t in range(13, 21):
+        rp.step([("c", ids[t:t + 1], True)])
+    for r in ("w", "c"):
+        got = torch.stack([rp.logits[(r, p)] for p in range(len(ids))])
+        helpers.assert_close(got, want, "float32", f"toy switch request {r}")
