@@ -340,6 +340,28 @@ def test_attention_plain_and_decode(Hq, Hkv, D, page, dtype, window):
     assert float(out3[[1, 2, 4]].abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("D,window", [(128, 0), (64, 6000), (128, 70)])
+def test_attention_decode_long_context(D, window):
+    """Contexts of tens of thousands of keys (more splits, more pages than the kernel caches per block) beside
+    a short one, grouped queries, against float64."""
+    o = ops()
+    Hq, Hkv, page = 8, 2, 16
+    lens = [20000, 5, 33000]
+    kc, vc, bt, ks, vs = paged_setup(lens, Hkv, D, page, torch.bfloat16, seed=D + window)
+    T = len(lens)
+    qkv = rnd(T, (Hq + 2 * Hkv) * D, dtype=torch.bfloat16, seed=9)
+    pos = torch.tensor([n - 1 for n in lens], dtype=torch.int32, device=DEV)
+    row_entry = torch.arange(T, dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(D)
+    want = torch.stack([attention_reference(qkv[i, :Hq * D].reshape(Hq, D).cpu(), ks[i], vs[i], lens[i] - 1, scale, window)
+                        for i in range(T)]).reshape(T, Hq * D)
+    out = torch.full((T, Hq * D), float("nan"), dtype=torch.bfloat16, device=DEV)
+    err = o.ErrorFlag(DEV)
+    o.attention_decode(qkv, kc, vc, bt, row_entry, pos, scale, window, out, Hq, Hkv, D, max(lens), err=err)
+    err.check("decode attention")
+    close(out, want, 1.5e-2, "decode attention, long context")
+
+
 @pytest.mark.parametrize("kernel", ["plain", "decode"])
 def test_attention_finds_one_far_key(kernel):
     """Among 700 keys one far key matches the query; its value must dominate the output.  With a window
