@@ -415,7 +415,9 @@ NV_API int nv_tc_gemm_splits(int M_tok, int N, int K, int n_tile, int num_sms) {
   int ctas = ((N + TILE_W - 1) / TILE_W) * ((M_tok + n_tile - 1) / n_tile);
   int k_steps = (K + BLOCK_K - 1) / BLOCK_K;
   if (ctas >= num_sms || k_steps < 8) return 1;
-  int s = 2 * num_sms / ctas;                      // two CTAs of these small stages live on a multiprocessor
+  // a few rows: two CTAs of these small stages live on a multiprocessor; many rows: the partial sums are big, so
+  // split only what would leave more than half of the GPU idle
+  int s = (M_tok <= 64 ? 2 * num_sms : num_sms) / ctas;
   if (s > k_steps / 4) s = k_steps / 4;
   if (s > 16) s = 16;
   return s < 1 ? 1 : s;
@@ -467,7 +469,10 @@ NV_API int nv_tc_gemm(const void* X, long long ldx, int M_tok, const void* W, in
   // Small stages (few tokens): keep a CTA under half of the shared memory so that two CTAs share an SM and
   // one's start-up and epilogue overlap the other's streaming.  Large stages, or more than half of the
   // TMEM columns: one CTA per SM, deep ring.
-  const bool pair = stage_bytes * 4 <= 104 * 1024 && a.tmem_cols <= 256;
+  // (with many rows, hence most experts in use and many tiles, two CTAs with three stages each stream the
+  // SwiGLU product's two weight tiles a little faster than one CTA with five: measured at batch 64, not at 8 or 1)
+  const int min_stages = (grouped && swiglu && M_tok >= 256) ? 3 : 4;
+  const bool pair = stage_bytes * min_stages <= 104 * 1024 && a.tmem_cols <= 256;
   const int budget = pair ? 104 * 1024 : 200 * 1024;
   int stages = budget / stage_bytes;
   if (stages > MAX_STAGES) stages = MAX_STAGES;
