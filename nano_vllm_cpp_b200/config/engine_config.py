@@ -21,6 +21,7 @@ class EngineConfig:
     prefill_chunk: int = 0                # 0 = portions limited by the token budget only
     enable_prefix_caching: bool = True
     cuda_graphs: bool = True
+    run_ahead: bool = True                # launch a step before the host has read the tokens of the one before
     device: str = "cuda:0"
 
     def validate(self) -> None:

@@ -63,6 +63,8 @@ _PROTOS = {
     "nvs_forget": (c_int, [c_void_p, c_int64]),
     "nvs_schedule": (c_int, [c_void_p, _LP, _IP, _IP, _IP, c_int]),
     "nvs_postprocess": (c_int, [c_void_p, _IP, _LP, c_int]),
+    "nvs_patch_token": (c_int, [c_void_p, c_int64, c_int, c_int]),
+    "nvs_finish_late": (c_int, [c_void_p, c_int64]),
 }
 
 

@@ -503,7 +503,7 @@ class Scheduler {
       const int token = sampled[i];
       s->tokens.push_back(token);
       const int completion = (int)s->tokens.size() - s->num_prompt;
-      if ((!s->ignore_eos && token == eos) || completion >= s->max_tokens || (int)s->tokens.size() >= max_model_len) {
+      if ((!s->ignore_eos && eos >= 0 && token == eos) || completion >= s->max_tokens || (int)s->tokens.size() >= max_model_len) {
         s->status = 2;
         m->close(s->id);
         auto it = std::find(running.begin(), running.end(), s);
@@ -796,4 +796,32 @@ NVH_API int nvs_postprocess(void* s, const int* sampled, int64_t* finished, int 
   const int n = (int)h->done.size();
   for (int i = 0; i < n && i < cap; ++i) finished[i] = h->done[i];
   return n;
+}
+
+// A token that was recorded as a stand-in (a negative number, while the step that draws it was still running) gets
+// its value.
+NVH_API int nvs_patch_token(void* s, int64_t seq_id, int index, int token) {
+  Scheduler& sc = ((SchedHandle*)s)->s;
+  auto it = sc.seqs.find(seq_id);
+  if (it == sc.seqs.end()) return fail(ERR_STATE, "unknown sequence");
+  std::vector<int>& t = it->second->tokens;
+  if (index < 0 || index >= (int)t.size()) return fail(ERR_STATE, "token index out of range");
+  t[index] = token;
+  return OK;
+}
+// A sequence turns out to have ended (its stop token was drawn in a step whose tokens were read late): it gives
+// back what it holds and leaves its queue, wherever the decisions made meanwhile have put it.
+NVH_API int nvs_finish_late(void* s, int64_t seq_id) {
+  Scheduler& sc = ((SchedHandle*)s)->s;
+  auto it = sc.seqs.find(seq_id);
+  if (it == sc.seqs.end()) return fail(ERR_STATE, "unknown sequence");
+  Seq* q = it->second.get();
+  if (q->status == 2) return OK;
+  q->status = 2;
+  if (sc.m->find(q->id)) sc.m->close(q->id);
+  auto r = std::find(sc.running.begin(), sc.running.end(), q);
+  if (r != sc.running.end()) sc.running.erase(r);
+  auto w = std::find(sc.waiting.begin(), sc.waiting.end(), q);
+  if (w != sc.waiting.end()) sc.waiting.erase(w);
+  return OK;
 }

@@ -126,12 +126,13 @@ class ErrorFlag:
 
 
 # ----------------------------------------------------------------------------- plain ops
-def embedding(ids, table, out, err: ErrorFlag) -> None:
-    _cuda_contig(ids, table, out)
-    _i32(ids)
+def embedding(ids, table, out, err: ErrorFlag, feed=None) -> None:
+    """``feed``: int32 tokens that negative ids point into (id ``-(r + 1)`` reads ``feed[r]``)."""
+    _cuda_contig(ids, table, out, feed)
+    _i32(ids, feed)
     T, (V, H) = ids.numel(), table.shape
     _need(out.dtype == torch.float32 and out.shape == (T, H), "embedding: out must be float32 [T, H]")
-    _check(lib().nv_embedding(_p(ids), _p(table), c_int(dt(table)), _p(out), c_int(T), c_int(H), c_int(V),
+    _check(lib().nv_embedding(_p(ids), _p(feed), _p(table), c_int(dt(table)), _p(out), c_int(T), c_int(H), c_int(V),
                               _p(err.t), _stream()), "embedding")
 
 

@@ -12,10 +12,17 @@ namespace {
 
 // ------------------------------------------------------------------ embedding
 // out[t,:] = float(table[ids[t],:])                       (src/hip_ops.hip:553-563)
+// A negative id -(r + 1) stands for "the token that the step before this one drew for its row r": it is read
+// from `feed`, where that step's sampling kernel left it, so that a step can be launched before the host has
+// seen the tokens of the step before.
 __global__ void embedding_kernel(const int* __restrict__ ids, const void* __restrict__ table, int dt,
-                                 float* __restrict__ out, int H, int V, int* __restrict__ err) {
+                                 float* __restrict__ out, int H, int V, int* __restrict__ err,
+                                 const int* __restrict__ feed) {
+  grid_dep_wait();
+  grid_dep_launch();
   int t = blockIdx.x;
   int id = ids[t];
+  if (id < 0 && feed) id = feed[-id - 1];
   if (id < 0 || id >= V) {
     if (threadIdx.x == 0) atomicExch(err, 1 + t);
     id = 0;
@@ -492,11 +499,11 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const float* __r
 
 NV_API const char* nv_error_string(int code) { return cudaGetErrorString((cudaError_t)code); }
 
-NV_API int nv_embedding(const int* ids, const void* table, int table_dt, float* out, int T, int H, int V,
+NV_API int nv_embedding(const int* ids, const int* feed, const void* table, int table_dt, float* out, int T, int H, int V,
                         int* err, cudaStream_t s) {
   if (!dt_ok(table_dt)) return NV_ERR_BAD_DTYPE;
   if (T == 0) return NV_OK;
-  embedding_kernel<<<T, 256, 0, s>>>(ids, table, table_dt, out, H, V, err);
+  NV_RETURN_IF(launch_dep(embedding_kernel, dim3(T), dim3(256), 0, s, ids, table, table_dt, out, H, V, err, feed));
   NV_RETURN_LAST();
 }
 

@@ -28,6 +28,16 @@ class StepOutput:
     new_tokens: list = field(default_factory=list)  # [(seq_id, token)] for every token drawn this step
 
 
+class _Pending:
+    """A step that has been queued on the GPU and not read yet."""
+
+    def __init__(self, scheduled, sampled_seqs, handle, n_prefill, n_decode):
+        self.scheduled, self.sampled_seqs, self.handle = scheduled, sampled_seqs, handle
+        self.n_prefill, self.n_decode = n_prefill, n_decode
+        self.finished = []          # sequences that the stand-in bookkeeping ended (by length)
+        self.places = None          # per sampled row: index of its stand-in in the sequence's tokens, or None
+
+
 class LLMEngine:
     def __init__(self, model: str, max_model_len: int = 4096, num_kv_blocks: int = 0, **kwargs):
         cfg = EngineConfig(model=model, max_model_len=max_model_len,
@@ -59,6 +69,7 @@ class LLMEngine:
                                    max_num_batched_tokens=cfg.max_num_batched_tokens,
                                    max_model_len=cfg.max_model_len, eos=cfg.eos, prefill_chunk=cfg.prefill_chunk)
         self.sampler = Sampler(self.runner.device)
+        self._pending = None
 
     @staticmethod
     def _eos_from_files(model_dir: str, from_config: int) -> int:
@@ -101,14 +112,32 @@ class LLMEngine:
         self.scheduler.add(seq)
         return seq.seq_id
 
-    def is_finished(self) -> bool:
-        return self.scheduler.is_finished()
-
     # ------------------------------------------------------------------ one step
+    def is_finished(self) -> bool:
+        return self._pending is None and self.scheduler.is_finished()
+
     def step(self) -> StepOutput:
+        """Runs one step and returns what it produced.  With ``run_ahead`` the step after it is decided and queued
+        on the GPU first, before this step's tokens have been read: the sequences get stand-ins (negative
+        numbers that name the row of this step that draws the token, which the next step reads on the device),
+        and the values are filled in when they arrive.  A sequence whose stop token arrives that way ends then;
+        what the step in flight computes for it is dropped."""
+        if self._pending is None:
+            self._pending = self._launch()
+            if self._pending is None:
+                return StepOutput([])
+        cur, nxt = self._pending, None
+        if self.config.run_ahead:
+            self._stand_ins(cur)
+            nxt = self._launch()
+        tokens = self.runner.collect(cur.handle)
+        self._pending = nxt
+        return self._resolve(cur, tokens)
+
+    def _launch(self):
         scheduled = self.scheduler.schedule()
         if not scheduled:
-            return StepOutput([])
+            return None
         entries, temps, us, sampled_seqs = [], [], [], []
         n_prefill = n_decode = 0
         for s in scheduled:
@@ -123,11 +152,32 @@ class LLMEngine:
                 n_decode += 1
             else:
                 n_prefill += s.count
-        tokens = self.runner.step_tokens(entries, temps, us)
-        sampled = {seq.seq_id: tok for seq, tok in zip(sampled_seqs, tokens)}
-        finished = self.scheduler.postprocess(scheduled, sampled)
-        return StepOutput([(q.seq_id, q.completion_token_ids) for q in finished], n_prefill, n_decode,
-                          list(sampled.items()))
+        handle = self.runner.launch_tokens(entries, temps, us)
+        return _Pending(scheduled, sampled_seqs, handle, n_prefill, n_decode)
+
+    def _stand_ins(self, cur) -> None:
+        """The bookkeeping of a step whose tokens are not known yet: every sampled row r appends -(r + 1)."""
+        before = [seq.num_tokens for seq in cur.sampled_seqs]
+        sampled = {seq.seq_id: -(r + 1) for r, seq in enumerate(cur.sampled_seqs)}
+        cur.finished = self.scheduler.postprocess(cur.scheduled, sampled)
+        cur.places = [n if seq.num_tokens == n + 1 else None for seq, n in zip(cur.sampled_seqs, before)]
+
+    def _resolve(self, cur, tokens: list) -> StepOutput:
+        if cur.places is None:                                   # nothing was decided ahead: the plain order
+            sampled = {seq.seq_id: tok for seq, tok in zip(cur.sampled_seqs, tokens)}
+            finished = self.scheduler.postprocess(cur.scheduled, sampled)
+            return StepOutput([(q.seq_id, q.completion_token_ids) for q in finished], cur.n_prefill, cur.n_decode,
+                              list(sampled.items()))
+        finished, new = list(cur.finished), []
+        for seq, place, tok in zip(cur.sampled_seqs, cur.places, tokens):
+            if place is None:                                    # preempted meanwhile, or ended a step earlier
+                continue
+            self.scheduler.patch(seq, place, tok)
+            new.append((seq.seq_id, tok))
+            if tok == self.config.eos and not seq.ignore_eos and not seq.is_finished:
+                self.scheduler.finish_late(seq)
+                finished.append(seq)
+        return StepOutput([(q.seq_id, q.completion_token_ids) for q in finished], cur.n_prefill, cur.n_decode, new)
 
     # ------------------------------------------------------------------ generate
     def generate(self, prompts, sampling_params=None) -> list:

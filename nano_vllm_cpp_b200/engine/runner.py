@@ -65,11 +65,15 @@ class ModelRunner:
         self.manager = CacheManager(self.cache.windows or [0], num_pages, page_size, max_requests,
                                     prefix_caching=prefix_caching)
         self.num_pages = num_pages
+        # tokens of the last launch's wanted rows (then the kernels' error flag): the next launch may read them there
+        self.feed = torch.zeros(max(max_requests, 1) + 1, dtype=torch.int32, device=self.device)
+        self.ctx.feed = self.feed
         self.last_h2d_bytes = 0
         self.stager = BatchStager(self.device)
         self.cuda_graphs = cuda_graphs and self.model.graph_safe
         self._graphs: dict = {}        # (decode batch size, with sampling) -> captured step
-        self._pinned_out: dict = {}
+        self._out_ring: list = [None, None, None]     # pinned [tokens..., error flag] of the launches in flight
+        self._out_at = 0
         self._seen: dict = {}
 
     def _pages_from_free_memory(self, utilization: float) -> int:
@@ -150,7 +154,7 @@ class ModelRunner:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
         logits = batch = None
         if self.cuda_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
-            logits, batch, _ = self._graph_step(entries, None)
+            logits, batch = self._graph_step(entries, None)
         if batch is None:
             batch = self.prepare(entries)
             logits = self.model.forward(batch, self.cache)
@@ -167,67 +171,82 @@ class ModelRunner:
         once.  Returns the tokens in the order of the wanted rows."""
         if not entries:
             return []
+        return self.collect(self.launch_tokens(entries, temperatures, uniforms))
+
+    @torch.no_grad()
+    def launch_tokens(self, entries: list, temperatures: list, uniforms: list):
+        """Queues ``step_tokens`` and returns a handle for ``collect`` without waiting.  The tokens also stay on the
+        device (``self.feed``): an entry of the *next* launch may name the token drawn for wanted row r of this
+        one as ``-(r + 1)`` instead of its value, so the next step can be queued before this one has been read."""
         sampling = (temperatures, uniforms)
-        out = batch = None
+        batch = None
         if self.cuda_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
-            _, batch, out = self._graph_step(entries, sampling)
+            _, batch = self._graph_step(entries, sampling)
         if batch is None:
             batch = self.prepare(entries, sampling=sampling)
             logits = self.model.forward(batch, self.cache)
-            out = self._sample_into_host(logits, batch)
-        torch.cuda.current_stream(self.device).synchronize()
+            self._sample_into_feed(logits, batch)
         W = len(temperatures)
-        host = out.numpy()
-        flag = int(host[W])
-        if flag:
-            self.ctx.err.check("step")
+        k = self._out_at
+        self._out_at = (k + 1) % len(self._out_ring)
+        if self._out_ring[k] is None or self._out_ring[k].numel() < W + 1:
+            self._out_ring[k] = torch.empty(max(W + 1, self.feed.numel()), dtype=torch.int32).pin_memory()
+        host = self._out_ring[k]
+        host[:W + 1].copy_(self.feed[:W + 1], non_blocking=True)
+        done = torch.cuda.Event()
+        done.record()
         self._commit(batch)
-        return host[:W].tolist()
+        return (host, done, W)
 
-    def _sample_into_host(self, logits, batch):
-        """Queues the sampling kernel and the copy of [tokens..., error flag] into pinned memory."""
+    def collect(self, handle) -> list:
+        """Waits for a launch and returns its tokens; raises if a kernel of the step flagged an error."""
+        host, done, W = handle
+        done.synchronize()
+        view = host.numpy()
+        if int(view[W]):
+            self.ctx.err.check("step")
+        return view[:W].tolist()
+
+    def _sample_into_feed(self, logits, batch) -> None:
+        """Queues the sampling kernel; tokens go to ``feed[:W]``, the kernels' error flag to ``feed[W]``."""
         W = logits.shape[0]
-        dev = torch.empty(W + 1, dtype=torch.int32, device=self.device)
+        if W + 1 > self.feed.numel():
+            raise StepError(f"a step may sample at most {self.feed.numel() - 1} rows, found {W}")
         if W:
-            ops.sample(logits, batch.temperatures, batch.uniforms, dev[:W])
-        dev[W:].copy_(self.ctx.err.t)
-        key = ("out", W)
-        host = self._pinned_out.get(key)
-        if host is None:
-            host = self._pinned_out[key] = torch.empty(W + 1, dtype=torch.int32).pin_memory()
-        host.copy_(dev, non_blocking=True)
-        return host
+            ops.sample(logits, batch.temperatures, batch.uniforms, self.feed[:W])
+        self.feed[W:W + 1].copy_(self.ctx.err.t)
 
     # ------------------------------------------------------------------ decode steps as CUDA graphs
     def _graph_step(self, entries: list, sampling):
         """A batch of single rows that all want their logits always launches the same kernels with the
         same sizes; only the index arrays differ.  Such a step is captured once per batch size (and once more
-        with the sampling kernel and the copy of the tokens to the host behind it) and replayed afterwards: the
-        arrays are copied into the buffer the graph reads, and the graph's logits tensor (or pinned token
-        buffer) is returned, valid until the next step of the same size."""
+        with the sampling kernel behind it) and replayed afterwards: the arrays are copied into the buffer the
+        graph reads, and the graph's logits tensor is returned, valid until the next step of the same size."""
         S = len(entries)
         key = (S, sampling is not None)
         g = self._graphs.get(key)
         if g is None:
             self._seen[key] = self._seen.get(key, 0) + 1
             if self._seen[key] < 2 or len(self._graphs) >= 24:
-                return None, None, None          # a size seen once is not worth a capture
+                return None, None          # a size seen once is not worth a capture
             seg, total = batch_layout(S, S, S, len(self.manager.pools), self.max_blocks, sampling is not None)
             static_dev = torch.full((total,), -1, dtype=torch.int32, device=self.device)
             batch = self.prepare(entries, static_dev, sampling)
             batch.max_context = self.max_model_len        # the split of the keys must not depend on the step
             logits = self.model.forward(batch, self.cache)       # warms up; also this step's result
-            out = self._sample_into_host(logits, batch) if sampling is not None else None
+            if sampling is not None:
+                self._sample_into_feed(logits, batch)
             torch.cuda.synchronize(self.device)
             before = ops.launch_count()
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
                 static_logits = self.model.forward(batch, self.cache)
-                static_out = self._sample_into_host(static_logits, batch) if sampling is not None else None
-            self._graphs[key] = (graph, static_dev, static_logits, static_out, ops.launch_count() - before)
-            return logits, batch, out
-        graph, static_dev, static_logits, static_out, launches = g
+                if sampling is not None:
+                    self._sample_into_feed(static_logits, batch)
+            self._graphs[key] = (graph, static_dev, static_logits, ops.launch_count() - before)
+            return logits, batch
+        graph, static_dev, static_logits, launches = g
         batch = self.prepare(entries, static_dev, sampling, views=False)
         graph.replay()
         ops.add_launches(launches)
-        return static_logits, batch, static_out
+        return static_logits, batch

@@ -61,6 +61,7 @@ class Scheduler:
         self._h = host.lib().nvs_create(manager._h, max_num_seqs, max_num_batched_tokens, max_model_len, eos,
                                         prefill_chunk)
         self._seqs: dict = {}           # seq_id -> Sequence, for every sequence that is not finished
+        self._forget_later: list = []
         cap = max(max_num_seqs, 1)
         self._ids = (ctypes.c_int64 * cap)()
         self._starts = (ctypes.c_int * cap)()
@@ -142,4 +143,29 @@ class Scheduler:
             seq.status = SequenceStatus.FINISHED
             L.nvs_forget(self._h, seq.seq_id)
             finished.append(seq)
+        for sid in self._forget_later:
+            L.nvs_forget(self._h, sid)
+        self._forget_later.clear()
         return finished
+
+    # ------------------------------------------------------------------ tokens that arrive a step late
+    def patch(self, seq: Sequence, index: int, token: int) -> None:
+        """``postprocess`` was given a stand-in (a negative number) for a token that was still being drawn; here is
+        its value."""
+        seq.token_ids[index] = int(token)
+        if seq.seq_id in self._seqs:                   # a finished sequence has no native record any more
+            if host.lib().nvs_patch_token(self._h, seq.seq_id, index, int(token)):
+                raise SchedulerError(host.last_error())
+
+    def finish_late(self, seq: Sequence) -> None:
+        """The token that was patched in was the stop token: the sequence ends now, whatever was decided for it
+        in the meantime (what a step still in flight computes for it is dropped by the caller)."""
+        if seq.seq_id not in self._seqs:
+            return
+        if host.lib().nvs_finish_late(self._h, seq.seq_id):
+            raise SchedulerError(host.last_error())
+        self._seqs.pop(seq.seq_id)
+        seq.status = SequenceStatus.FINISHED
+        seq.num_scheduled_tokens = 0
+        # the decisions of the step in flight still name the native record: it is dropped after their postprocess
+        self._forget_later.append(seq.seq_id)

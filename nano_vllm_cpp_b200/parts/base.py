@@ -62,6 +62,7 @@ class RunContext:
     err: object = None               # csrc.ops.ErrorFlag
     page_size: int = 16
     fast_kernels: bool = True        # False: plain kernels everywhere (the twin path of the tests)
+    feed: object = None              # int32 device tokens that negative input ids point into (see ops.embedding)
 
 
 Fetch = Callable[[str], torch.Tensor]

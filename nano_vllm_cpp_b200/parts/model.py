@@ -120,7 +120,7 @@ class Model:
         """Runs the rows of ``batch`` through every call; returns float32 logits ``[wanted, vocab]``."""
         ctx = self.ctx
         x = torch.empty((batch.T, self.spec.hidden_size), dtype=torch.float32, device=ctx.device)
-        ops.embedding(batch.input_ids, self.embed, x, ctx.err)
+        ops.embedding(batch.input_ids, self.embed, x, ctx.err, feed=ctx.feed)
         pending = None
         for i, c in enumerate(self.calls):
             pending = self.layers[c.layer].forward(x, pending, batch, cache.view(i))

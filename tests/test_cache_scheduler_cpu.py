@@ -262,6 +262,70 @@ def test_random_workloads_with_tight_pools():
         assert sched.manager.free_slots() == sched.max_num_seqs
 
 
+def drive_late(sched, seqs, rng, stop, max_steps=10000):
+    """The order of an engine that queues step k+1 before it has read step k's tokens: the bookkeeping of step k
+    runs with stand-ins (negative numbers), step k+1 is decided, then the tokens of step k arrive and are patched
+    in; a stop token that arrives so ends its sequence late.  Returns the decisions per step."""
+    for s in seqs:
+        sched.add(s)
+    records = []
+    pending = sched.schedule()
+    for _ in range(max_steps):
+        if pending is None:
+            assert sched.is_finished()
+            return records
+        cur = pending
+        records.append([(s.seq.seq_id, s.start, s.count, s.samples) for s in cur])
+        rows = [s.seq for s in cur if s.samples]
+        before = [q.num_tokens for q in rows]
+        finished = sched.postprocess(cur, {q.seq_id: -(r + 1) for r, q in enumerate(rows)})
+        places = [n if q.num_tokens == n + 1 else None for q, n in zip(rows, before)]
+        sched.manager.check()
+        pending = sched.schedule() if not sched.is_finished() else None
+        if pending is not None:
+            assert pending, "an unfinished scheduler must schedule something"
+            for s in pending:                        # the pages are there although the newest token is a stand-in
+                rc = sched.manager.get(s.seq.seq_id)
+                assert all(len(t) * sched.manager.page_size >= s.start + s.count for t in rc.tables)
+        for q, place in zip(rows, places):           # the tokens of `cur` arrive
+            if place is None:
+                continue
+            tok = rng.randrange(2, 50)
+            sched.patch(q, place, tok)
+            if tok == stop and not q.ignore_eos and not q.is_finished:
+                sched.finish_late(q)
+                finished.append(q)
+        sched.manager.check()
+        if pending is not None and not pending and sched.is_finished():
+            pending = None
+    raise AssertionError("the scheduler did not finish")
+
+
+def test_tokens_that_arrive_a_step_late():
+    rng = random.Random(11)
+    for trial in range(25):
+        windows = rng.choice([(0,), (0, 16)])
+        sched = make_sched(rng.choice([8, 10, 16]), windows=windows, budget=rng.choice([16, 48, 200]),
+                           max_seqs=rng.choice([2, 4, 8]), prefix=rng.random() < 0.5, chunk=rng.choice([0, 0, 7]),
+                           eos=7)
+        seqs = []
+        for _ in range(rng.randrange(1, 9)):
+            n = rng.choice([1, 3, 16, 17, 40, 64])
+            base = rng.choice([100, 200])
+            seqs.append(Sequence([base + i for i in range(n)],
+                                 SamplingParams(max_tokens=rng.choice([1, 5, 30]), ignore_eos=rng.random() < 0.3)))
+        drive_late(sched, seqs, rng, stop=7)
+        for q in seqs:
+            assert q.is_finished and all(t >= 0 for t in q.token_ids)       # no stand-in is left
+            done = q.completion_token_ids
+            if not q.ignore_eos and 7 in done:
+                assert done.index(7) == len(done) - 1                       # nothing follows the stop token
+            else:
+                assert len(done) == q.max_tokens
+        assert all(p.num_free() == p.num_pages for p in sched.manager.pools)
+        assert sched.manager.free_slots() == sched.max_num_seqs
+
+
 def test_pool_smaller_than_one_request_is_an_error():
     sched = make_sched(2, budget=64)
     sched.add(Sequence(list(range(2, 42)), SamplingParams(max_tokens=4)))

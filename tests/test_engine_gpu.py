@@ -73,6 +73,35 @@ def test_preempted_request_resumes_with_the_same_tokens(folders):
     assert got == want
 
 
+def test_steps_queued_ahead_give_the_same_tokens(folders):
+    """The engine queues a step before it has read the tokens of the one before (they are fed back on the
+    device) and learns of a stop token a step late: every request's tokens equal those of the plain order, with
+    prompts beside decoded tokens, stop tokens in mid-run and so few pages that requests are preempted."""
+    from nano_vllm_cpp_b200 import SamplingParams
+    case = "A"
+    prompts = [prompt(case, n, salt=40 + i) for i, n in enumerate((20, 3, 33, 20, 9, 26))]
+    sp = [SamplingParams(temperature=0.9, max_tokens=30, ignore_eos=True, seed=50 + i) for i in range(6)]
+    free = [o["token_ids"] for o in engine(folders[case], run_ahead=False).generate(prompts, sp)]
+    # a stop token that some requests draw in mid-run: the most frequent token among the free runs' middles
+    counts = {}
+    for toks in free:
+        for t in set(toks[5:25]):
+            counts[t] = counts.get(t, 0) + 1
+    stop = max(counts, key=counts.get)
+    sp = [SamplingParams(temperature=0.9, max_tokens=30, seed=50 + i) for i in range(6)]
+    want = [t[:t.index(stop) + 1] if stop in t else t for t in free]
+    assert any(len(w) < 30 for w in want)
+    for kw in (dict(), dict(num_kv_blocks=8, max_num_seqs=4), dict(max_num_batched_tokens=16)):
+        plain = engine(folders[case], run_ahead=False, eos=stop, **kw)
+        ahead = engine(folders[case], run_ahead=True, eos=stop, **kw)
+        a = [o["token_ids"] for o in plain.generate(prompts, sp)]
+        b = [o["token_ids"] for o in ahead.generate(prompts, sp)]
+        assert a == want and b == want
+        if "num_kv_blocks" in kw:
+            assert ahead.scheduler.num_preemptions > 0
+        assert all(p.num_free() == p.num_pages for p in ahead.runner.manager.pools)
+
+
 def test_sample_kernel_against_plain_sampler():
     from nano_vllm_cpp_b200.csrc import ops
     g = torch.Generator().manual_seed(0)
