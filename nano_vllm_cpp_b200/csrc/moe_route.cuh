@@ -62,6 +62,9 @@ __device__ __forceinline__ void route_row(const float* __restrict__ r, int E, in
 // (t2 == nullptr: none).  One block of 1024 threads; `al_s` is 4 * E ints of shared memory.  The
 // order of pairs inside an expert's segment comes from atomics and may differ from run to run; it
 // decides only where a pair's row sits, never a sum's order.
+// The last `n_static` experts are ones that every row visits (a shared expert's chunks): their pairs sit in row
+// order, so their part of the permutation is known before any routing is (segment of expert E - n_static + c
+// starts at TK - (n_static - c) * rows), and they get no tiles here: whoever runs them has a fixed list.
 __device__ __forceinline__ void align_block(const int* __restrict__ idx, int TK, int K, int E, int tile_m,
                                             int* __restrict__ counts, int* __restrict__ offsets,
                                             int* __restrict__ sorted_token, int* __restrict__ pair_pos,
@@ -69,7 +72,9 @@ __device__ __forceinline__ void align_block(const int* __restrict__ idx, int TK,
                                             int* __restrict__ tile_rows, int* __restrict__ num_tiles,
                                             int* __restrict__ err, int* al_s, int tile_m2 = 0,
                                             int* __restrict__ t2_expert = nullptr, int* __restrict__ t2_row0 = nullptr,
-                                            int* __restrict__ t2_rows = nullptr, int* __restrict__ num_tiles2 = nullptr) {
+                                            int* __restrict__ t2_rows = nullptr, int* __restrict__ num_tiles2 = nullptr,
+                                            int n_static = 0) {
+  const int E_dyn = E - n_static;
   int* cnt = al_s;
   int* cur = al_s + E;
   int* tbase = al_s + 2 * E;
@@ -96,8 +101,8 @@ __device__ __forceinline__ void align_block(const int* __restrict__ idx, int TK,
     for (int base = 0; base < E; base += 32) {
       const int e = base + tid;
       const int c = e < E ? cnt[e] : 0;
-      const int tl = (c + tile_m - 1) / tile_m;
-      const int tl2 = tile_m2 ? (c + tile_m2 - 1) / tile_m2 : 0;
+      const int tl = e < E_dyn ? (c + tile_m - 1) / tile_m : 0;
+      const int tl2 = (tile_m2 && e < E_dyn) ? (c + tile_m2 - 1) / tile_m2 : 0;
       int sc = c, st = tl, st2 = tl2;       // inclusive scans
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
@@ -125,6 +130,7 @@ __device__ __forceinline__ void align_block(const int* __restrict__ idx, int TK,
     const int c = cnt[e], off = cur[e];
     counts[e] = c;
     offsets[e] = off;
+    if (e >= E_dyn) continue;
     for (int r = 0, t = tbase[e]; r < c; r += tile_m, ++t) {
       tile_expert[t] = e;
       tile_row0[t] = off + r;
@@ -147,7 +153,7 @@ __device__ __forceinline__ void align_block(const int* __restrict__ idx, int TK,
       const int i = i0 + u * nthr;
       if (i >= TK) break;
       if (ev[u] < 0 || ev[u] >= E) continue;
-      const int p = atomicAdd(&cur[ev[u]], 1);
+      const int p = ev[u] < E_dyn ? atomicAdd(&cur[ev[u]], 1) : cur[ev[u]] + i / K;
       sorted_token[p] = i / K;
       pair_pos[i] = p;
     }

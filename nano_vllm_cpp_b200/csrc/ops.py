@@ -397,9 +397,11 @@ def moe_route_small_usable(T: int, E: int, K: int, C: int, H: int) -> bool:
     return bool(lib().nv_moe_route_small_usable(c_int(T), c_int(E), c_int(K), c_int(C), c_int(H)))
 
 
-def moe_route_small(logits, K: int, renorm: bool, C: int, gate_logit, idx, score, al: "MoeAlignment", err, x=None):
+def moe_route_small(logits, K: int, renorm: bool, C: int, gate_logit, idx, score, al: "MoeAlignment", err, x=None,
+                    static: bool = False):
     """Top-k, expert permutation and (with ``x``, bfloat16 rows) the expert-sorted copy of x, in one launch.
-    Returns the sorted copy or None."""
+    Returns the sorted copy or None.  ``static``: the C always-on experts' pairs sit in row order at the end of
+    the permutation and get no tiles (``static_tiles`` lists them; they can then run before the routing)."""
     T, E = logits.shape
     KT = K + C
     _need(idx.shape == (T, KT) and score.shape == (T, KT) and al.TK == T * KT and al.E == E + C, "route: sizes")
@@ -415,8 +417,30 @@ def moe_route_small(logits, K: int, renorm: bool, C: int, gate_logit, idx, score
                                     c_longlong(gate_logit.stride(0) if gate_logit is not None else 0), _p(idx),
                                     _p(score), c_int(al.tile_m), _p(al.counts), _p(al.offsets), _p(al.sorted_token),
                                     _p(al.pair_pos), _p(al.tile_expert), _p(al.tile_row0), _p(al.tile_rows),
-                                    _p(al.num_tiles), _p(err.t), _p(x), _p(xs), c_int(H), _stream()), "moe_route_small")
+                                    _p(al.num_tiles), _p(err.t), _p(x), _p(xs), c_int(H), c_int(C if static else 0),
+                                    _stream()), "moe_route_small")
     return xs
+
+
+class StaticTiles:
+    """The tiles of C experts E .. E + C - 1 that each take all T rows, in row order, their segments behind the
+    T * K routed pairs: what ``moe_route_small(static=True)`` leaves out of its list."""
+
+    def __init__(self, T: int, K: int, E: int, C: int, device):
+        self.tile_m = 16 if T <= 16 else (32 if T <= 32 else 64)
+        experts, row0, rows = [], [], []
+        for c in range(C):
+            for r in range(0, T, self.tile_m):
+                experts.append(E + c)
+                row0.append(T * K + c * T + r)
+                rows.append(min(self.tile_m, T - r))
+        i32 = dict(dtype=torch.int32, device=device)
+        self.max_tiles = len(experts)
+        self.tile_expert = torch.tensor(experts, **i32)
+        self.tile_row0 = torch.tensor(row0, **i32)
+        self.tile_rows = torch.tensor(rows, **i32)
+        self.num_tiles = torch.tensor([len(experts)], **i32)
+        self.x_rows = (T * K, T)
 
 
 def moe_combine(y, pair_pos, score, shared, gate_logit, out) -> None:
@@ -530,11 +554,16 @@ def gemm_fast(a, w, out, *, bias=None, a_rows=None, swiglu=False, M=None, err=No
                         _p(bias), c_int(dt(bias) if bias is not None else 0), _p(out), c_int(dt(out)),
                         c_longlong(out.stride(0)), c_int(1 if swiglu else 0), c_int(n_tile), c_int(splits),
                         _p(scratch), _p(None), _p(None), _p(None), _p(None), c_int(0), c_int(0),
-                        _p(err.t if err is not None else _global_err().t), c_int(_early()), _stream()), "tc_gemm")
+                        _p(err.t if err is not None else _global_err().t), c_int(_early()), c_int(0), c_int(0),
+                        _stream()), "tc_gemm")
 
 
-def gemm_fast_grouped(a, w, out, align, *, a_rows=None, swiglu=False, err=None, tiles=None, tiles_ready=False) -> None:
+def gemm_fast_grouped(a, w, out, align, *, a_rows=None, swiglu=False, err=None, tiles=None, tiles_ready=False,
+                      x_rows=None) -> None:
     """Tensor-core form of the grouped ``gemm_plain``; ``tiles`` (a TileList of ``align``) picks the token tile.
+
+    ``x_rows`` = (sub, mod): a tile whose outputs are rows r.. takes rows ``(r - sub) % mod``.. of ``a`` (several
+    experts that all take the same few rows, their outputs one segment after the other).
 
     ``tiles_ready``: the tile lists were complete before the kernel that precedes this product on the stream
     started, so the product may start beside that kernel and fetch its first weights (it reads the lists at
@@ -547,12 +576,14 @@ def gemm_fast_grouped(a, w, out, align, *, a_rows=None, swiglu=False, err=None, 
     N = rows_w // 2 if swiglu else rows_w
     tl = tiles if tiles is not None else align.primary
     _need(tl.tile_m in (16, 32, 64, 128, 256), "grouped product: token tile must be 16, 32, 64, 128 or 256")
-    _check(lib().nv_tc_gemm(_p(a), c_longlong(a.stride(0)), c_int(align.TK), _p(w), c_int(E * rows_w), c_int(N),
+    x_sub, x_mod = x_rows if x_rows is not None else (0, 0)
+    _need(out.shape[0] >= align.TK and (x_mod or a.shape[0] <= align.TK), "grouped product: row counts")
+    _check(lib().nv_tc_gemm(_p(a), c_longlong(a.stride(0)), c_int(a.shape[0]), _p(w), c_int(E * rows_w), c_int(N),
                             c_int(K), _p(None), c_int(0), _p(out), c_int(dt(out)), c_longlong(out.stride(0)),
                             c_int(1 if swiglu else 0), c_int(tl.tile_m), c_int(1), _p(None), _p(tl.tile_expert),
                             _p(tl.tile_row0), _p(tl.tile_rows), _p(tl.num_tiles), c_int(tl.max_tiles),
                             c_int(rows_w), _p(err.t if err is not None else _global_err().t),
-                            c_int(_early() if tiles_ready else 0), _stream()),
+                            c_int(_early() if tiles_ready else 0), c_int(x_sub), c_int(x_mod), _stream()),
            "tc_gemm_grouped")
 
 

@@ -166,7 +166,7 @@ __global__ void __launch_bounds__(1024) moe_route_small_kernel(
     int tile_m, int* __restrict__ counts, int* __restrict__ offsets, int* __restrict__ sorted_token,
     int* __restrict__ pair_pos, int* __restrict__ tile_expert, int* __restrict__ tile_row0,
     int* __restrict__ tile_rows, int* __restrict__ num_tiles, int* __restrict__ err,
-    const bf16* __restrict__ x, bf16* __restrict__ x_sorted, int H) {
+    const bf16* __restrict__ x, bf16* __restrict__ x_sorted, int H, int n_static) {
   extern __shared__ double rs_smem[];
   grid_dep_wait();
   grid_dep_launch();
@@ -179,7 +179,7 @@ __global__ void __launch_bounds__(1024) moe_route_small_kernel(
   __syncthreads();
   int* al_s = (int*)(rs_smem + (size_t)32 * E);
   align_block(idx, T * KT, KT, E + C, tile_m, counts, offsets, sorted_token, pair_pos, tile_expert, tile_row0,
-              tile_rows, num_tiles, err, al_s);
+              tile_rows, num_tiles, err, al_s, 0, nullptr, nullptr, nullptr, nullptr, n_static);
   if (!x_sorted) return;
   __threadfence_block();
   __syncthreads();
@@ -251,12 +251,13 @@ NV_API int nv_moe_route_small(const float* logits, long long ld, int T, int E, i
                               const float* gate_logit, long long gate_ld, int* idx, float* score, int tile_m,
                               int* counts, int* offsets, int* sorted_token, int* pair_pos, int* tile_expert,
                               int* tile_row0, int* tile_rows, int* num_tiles, int* err, const void* x,
-                              void* x_sorted, int H, cudaStream_t s) {
+                              void* x_sorted, int H, int n_static, cudaStream_t s) {
   if (!nv_moe_route_small_usable(T, E, K, C, H) || K < 1 || K > E || (C > 0 && !gate_logit)) return NV_ERR_UNSUPPORTED;
+  if (n_static != 0 && n_static != C) return NV_ERR_UNSUPPORTED;
   if (T == 0) return NV_OK;
   const size_t smem = (size_t)32 * E * sizeof(double) + (size_t)4 * (E + C) * sizeof(int);
   NV_RETURN_IF(launch_dep(moe_route_small_kernel, dim3(1), dim3(1024), smem, s, logits, ld, T, E, K, renorm, C,
                           gate_logit, gate_ld, idx, score, tile_m, counts, offsets, sorted_token, pair_pos, tile_expert,
-                          tile_row0, tile_rows, num_tiles, err, (const bf16*)x, (bf16*)x_sorted, H));
+                          tile_row0, tile_rows, num_tiles, err, (const bf16*)x, (bf16*)x_sorted, H, n_static));
   NV_RETURN_LAST();
 }

@@ -65,6 +65,9 @@ struct TcArgs {
   // Dense products whose tiles do not fill a last wave of CTAs: the tiles from rest_first on are cut into
   // rest_parts token parts each (numbered part by part after rest_first), so that the last wave is short.
   int rest_first, rest_parts;
+  // Grouped products whose tiles' tokens are not rows row0.. of X but rows (row0 - x_sub) mod x_mod.. of it
+  // (x_mod > 0): several experts that all take the same rows of a short X, outputs one segment after the other.
+  int x_sub, x_mod;
 };
 
 // ------------------------------------------------------------------ the kernel
@@ -74,7 +77,7 @@ struct TcArgs {
 // ring and the barriers' phases run on across tiles, and the accumulator is double-buffered in
 // TMEM (when two fit), so the epilogue of one tile overlaps the products of the next.
 struct Tile {
-  int nb, row0, rows_here, w_row_base, z, n_steps, k_begin;
+  int nb, row0, x_row0, rows_here, w_row_base, z, n_steps, k_begin;
 };
 
 __device__ __forceinline__ bool get_tile(const TcArgs& a, int tile_id, int y_tiles, Tile& t) {
@@ -94,6 +97,7 @@ __device__ __forceinline__ bool get_tile(const TcArgs& a, int tile_id, int y_til
     t.row0 = a.tile_row0[y];
     t.rows_here = a.tile_rows[y];
     t.w_row_base = a.tile_expert[y] * a.rows_per_expert;
+    t.x_row0 = a.x_mod ? (t.row0 - a.x_sub) % a.x_mod : t.row0;
   } else {
     t.row0 = y * a.n_tile;
     t.rows_here = min(a.n_tile, a.M_tok - t.row0);
@@ -102,6 +106,7 @@ __device__ __forceinline__ bool get_tile(const TcArgs& a, int tile_id, int y_til
       t.rows_here = a.n_tile / a.rest_parts;
       t.row0 += part * t.rows_here;
     }
+    t.x_row0 = t.row0;
   }
   t.k_begin = t.z * a.k_steps_per_split;
   t.n_steps = max(0, min(a.k_steps_total, t.k_begin + a.k_steps_per_split) - t.k_begin);
@@ -178,7 +183,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
             if (tokens)
               for (int b = 0; b < boxes; ++b)
                 tma_load_2d_a(st + a_bytes * (two ? 2 : 1) + (uint32_t)b * a.x_box * 128, &tm_x, bar, kc,
-                              t.row0 + b * a.x_box);
+                              t.x_row0 + b * a.x_box);
           }
         }
       };
@@ -427,13 +432,14 @@ NV_API int nv_tc_gemm(const void* X, long long ldx, int M_tok, const void* W, in
                       const void* bias, int bias_dt, void* out, int out_dt, long long ldo, int swiglu, int n_tile,
                       int splits, float* scratch, const int* tile_expert, const int* tile_row0,
                       const int* tile_rows, const int* num_tiles, int max_tiles, int rows_per_expert, int* err,
-                      int early, cudaStream_t stream) {
+                      int early, int x_sub, int x_mod, cudaStream_t stream) {
   if (!dt_ok(out_dt) || (bias && !dt_ok(bias_dt))) return NV_ERR_BAD_DTYPE;
   if (K % 8 || ldx % 8 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return NV_ERR_UNSUPPORTED;  // TMA: 16-byte rules
   if (n_tile < 16 || n_tile > 256 || (n_tile & (n_tile - 1))) return NV_ERR_BAD_SIZE;
   if (M_tok <= 0 || N <= 0) return NV_OK;
   const bool grouped = tile_expert != nullptr;
   if (grouped && splits != 1) return NV_ERR_UNSUPPORTED;
+  if (x_mod < 0 || x_sub < 0 || (x_mod && !grouped)) return NV_ERR_BAD_SIZE;
   if (splits > 1 && !scratch) return NV_ERR_BAD_SIZE;
 
   CUtensorMap tm_w, tm_x;
@@ -453,6 +459,7 @@ NV_API int nv_tc_gemm(const void* X, long long ldx, int M_tok, const void* W, in
   a.n_tile = n_tile; a.swiglu = swiglu ? 1 : 0;
   a.early = early ? 1 : 0;
   a.x_box = x_box;
+  a.x_sub = x_sub; a.x_mod = x_mod;
   // Many tokens per tile and enough features: two weight tiles per CTA.  The operands then cost 2*16 KB + X
   // per k-step for twice the flops, which is what the shared-memory fill rate, the limit here, rewards.
   // ... provided the halved grid still covers the GPU (measured: a half-empty GPU loses more than the tile gains)

@@ -2,12 +2,17 @@
 softmax router, top-k routing and an optional sigmoid-gated shared expert."""
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..csrc import ops
 from .base import FeedForward, RowMix, TensorSpec
 from .linear import linear, grouped_linear, small_linear
 from .registry import register_part
+
+# Batches of up to this many rows run the shared expert's chunks on a second stream beside the routing.
+SIDE_MAX_ROWS = int(os.environ.get("NV_SIDE_MAX_ROWS", "64"))
 
 
 class DenseSwiGLU(FeedForward):
@@ -52,6 +57,7 @@ class SparseMoeSwiGLU(FeedForward):
         self.hidden, self.E, self.K = hidden_size, num_experts, top_k
         self.inter, self.shared_inter, self.renorm = intermediate_size, shared_intermediate_size, renormalize
         self._align = {}
+        self._static = {}
         self.router_and_gate = None
         self.last_alignment = None      # the permutation buffers of the latest forward (for statistics)
 
@@ -147,6 +153,9 @@ class SparseMoeSwiGLU(FeedForward):
                 and self.w_down.dtype == torch.bfloat16 and self.hidden % 8 == 0 and self.inter % 8 == 0)
         al = self._alignment(T * KT, self.E + C, dev, fast)
         x_sorted = None
+        if (fast and C and T <= SIDE_MAX_ROWS and al.secondary is None
+                and ops.moe_route_small_usable(T, self.E, self.K, C, self.hidden)):
+            return self._forward_beside(h, logits, gate_logit, idx, score, al)
         if fast and al.secondary is None and ops.moe_route_small_usable(T, self.E, self.K, C, self.hidden):
             x_sorted = ops.moe_route_small(logits, self.K, self.renorm, C, gate_logit, idx, score, al, ctx.err,
                                            x=None)   # one block copies rows slower than the copy kernel does
@@ -170,6 +179,47 @@ class SparseMoeSwiGLU(FeedForward):
                 gate_logit = small_linear(ctx, h32, self.sh_gate)
         # the combination (src/hip_ops.hip:873-892) is left to whoever takes the branch: the next norm sums it
         return RowMix(y, al.pair_pos[:T * KT].view(T, KT), score, shared, gate_logit if shared is not None else None)
+
+
+    def _forward_beside(self, h, logits, gate_logit, idx, score, al):
+        """Few rows: the shared expert's chunks need no routing, so their two products run on a second stream
+        beside the routing and the row copy, which keep few multiprocessors busy; the routed experts' products
+        follow on the first stream and write the other rows of the same two buffers."""
+        ctx, T, K, C, dev = self.ctx, h.shape[0], self.K, self.virtual, h.device
+        KT = K + C
+        key = (T, dev)
+        st = self._static.get(key)
+        if st is None:
+            st = self._static[key] = ops.StaticTiles(T, K, self.E, C, dev)
+        act = torch.empty((T * KT, self.inter), dtype=ctx.act_dtype, device=dev)
+        y = torch.empty((T * KT, self.hidden), dtype=torch.float32, device=dev)
+        main, side = torch.cuda.current_stream(dev), _side_stream(dev)
+        fork, join = torch.cuda.Event(), torch.cuda.Event()
+        fork.record(main)
+        side.wait_event(fork)
+        with torch.cuda.stream(side):
+            ops.gemm_fast_grouped(h, self.w_gate_up, act, al, swiglu=True, err=ctx.err, tiles=st, tiles_ready=True,
+                                  x_rows=st.x_rows)
+            ops.gemm_fast_grouped(act, self.w_down, y, al, err=ctx.err, tiles=st, tiles_ready=True)
+            join.record(side)
+        ops.moe_route_small(logits, K, self.renorm, C, gate_logit, idx, score, al, ctx.err, x=None, static=True)
+        self.last_alignment = al
+        x_sorted = ops.permute_rows(h, al.sorted_token, T * K)
+        ops.gemm_fast_grouped(x_sorted, self.w_gate_up, act, al, swiglu=True, err=ctx.err, tiles_ready=True)
+        ops.gemm_fast_grouped(act, self.w_down, y, al, err=ctx.err, tiles_ready=True)
+        main.wait_event(join)
+        return RowMix(y, al.pair_pos[:T * KT].view(T, KT), score, None, None)
+
+
+_side = {}
+
+
+def _side_stream(dev):
+    """One second stream per device for work that runs beside a step's main stream."""
+    key = torch.device(dev)
+    if key not in _side:
+        _side[key] = torch.cuda.Stream(device=key)
+    return _side[key]
 
 
 def _cat(ts):

@@ -37,12 +37,13 @@ def small_linear(ctx, a32, w):
     return out
 
 
-def grouped_linear(ctx, a, w, out_dtype, align, *, a_rows=None, swiglu=False, tiles=None, tiles_ready=False):
+def grouped_linear(ctx, a, w, out_dtype, align, *, a_rows=None, swiglu=False, tiles=None, tiles_ready=False, out=None):
     """Per-expert product over an expert-sorted row list: row r of the output belongs to the expert
     whose segment of ``align`` holds r and is ``a[a_rows[r]] @ w[expert].T``."""
     rows_w = w.shape[1]
     N = rows_w // 2 if swiglu else rows_w
-    out = torch.empty((align.TK, N), dtype=out_dtype, device=a.device)
+    if out is None:
+        out = torch.empty((align.TK, N), dtype=out_dtype, device=a.device)
     if align.TK == 0:
         return out
     if ctx.fast_kernels and ops.gemm_fast_usable(a, w, out, a_rows=a_rows, swiglu=swiglu, grouped=True):

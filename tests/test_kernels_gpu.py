@@ -196,6 +196,57 @@ def test_tc_gemm_grouped(T, E, K):
     close(res[True], res[False], 2e-2, "tc vs plain grouped")
 
 
+@pytest.mark.parametrize("T,E,K,C", [(5, 6, 3, 2), (1, 60, 4, 4), (40, 7, 2, 3), (64, 9, 1, 1)])
+def test_always_on_experts_run_before_the_routing(T, E, K, C):
+    """C experts that every row visits sit in row order behind the routed pairs and get no tiles from the routing;
+    a fixed tile list runs them straight from the unsorted rows (here on a second stream, before the routing is
+    launched), the routed experts follow, and both fill the same buffers.  Against float64."""
+    o = ops()
+    H, I, KT = 136, 72, K + C
+    x = rnd(T, H, dtype=torch.bfloat16)
+    w1 = rnd(E + C, 2 * I, H, dtype=torch.bfloat16, scale=0.3, seed=1)
+    w2 = rnd(E + C, H, I, dtype=torch.bfloat16, scale=0.3, seed=2)
+    logits, gate = rnd(T, E, scale=2.0, seed=3), rnd(T, seed=4)
+    err = o.ErrorFlag(DEV)
+    al = o.MoeAlignment(T * KT, E + C, o.grouped_token_tile(T * KT, E + C), DEV)
+    st = o.StaticTiles(T, K, E, C, DEV)
+    idx = torch.empty(T, KT, dtype=torch.int32, device=DEV)
+    score = torch.empty(T, KT, device=DEV)
+    act = torch.full((T * KT, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    y = torch.full((T * KT, H), float("nan"), dtype=torch.float32, device=DEV)
+    main, side = torch.cuda.current_stream(), torch.cuda.Stream()
+    fork, join = torch.cuda.Event(), torch.cuda.Event()
+    fork.record(main)
+    side.wait_event(fork)
+    with torch.cuda.stream(side):
+        o.gemm_fast_grouped(x, w1, act, al, swiglu=True, err=err, tiles=st, tiles_ready=True, x_rows=st.x_rows)
+        o.gemm_fast_grouped(act, w2, y, al, err=err, tiles=st, tiles_ready=True)
+        join.record(side)
+    o.moe_route_small(logits, K, False, C, gate, idx, score, al, err, static=True)
+    xs = o.permute_rows(x, al.sorted_token, T * K)
+    o.gemm_fast_grouped(xs, w1, act, al, swiglu=True, err=err, tiles_ready=True)
+    o.gemm_fast_grouped(act, w2, y, al, err=err, tiles_ready=True)
+    main.wait_event(join)
+    err.check("grouped")
+    pos = al.pair_pos.cpu().view(T, KT)
+    for t in range(T):
+        assert idx[t, K:].tolist() == list(range(E, E + C))
+        assert pos[t, K:].tolist() == [T * K + c * T + t for c in range(C)]
+        assert all(0 <= int(q) < T * K for q in pos[t, :K])
+    nt = int(al.num_tiles)
+    assert all(int(e) < E for e in al.tile_expert[:nt])
+    assert sum(int(r) for r in al.tile_rows[:nt]) == T * K
+    got = y[al.pair_pos.long()].reshape(T, KT, H)
+    want = torch.zeros(T, KT, H, dtype=torch.float64)
+    xd, w1d, w2d = x.double().cpu(), w1.double().cpu(), w2.double().cpu()
+    for t in range(T):
+        for k in range(KT):
+            e = int(idx[t, k])
+            gg, uu = xd[t] @ w1d[e, :I].T, xd[t] @ w1d[e, I:].T
+            want[t, k] = (gg / (1 + torch.exp(-gg)) * uu).to(torch.bfloat16).double() @ w2d[e].T
+    close(got, want, 2e-2, "always-on and routed experts")
+
+
 # ------------------------------------------------------------------------------- small products, router
 @pytest.mark.parametrize("T,N,K", [(1, 1, 64), (8, 60, 2048), (33, 7, 100), (5, 64, 3000), (1030, 61, 520), (1025, 9, 2050)])
 @pytest.mark.parametrize("tw", [torch.float32, torch.bfloat16])
