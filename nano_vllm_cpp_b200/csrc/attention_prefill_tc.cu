@@ -222,6 +222,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
         tmem_ld32_nowait(tmem_s + (i & 1) * TKB + lane_off, s);
         tmem_ld32_nowait(tmem_s + (i & 1) * TKB + lane_off + 32, s + 32);
         tmem_ld_wait();
+        tmem_ld_fence<64>(s);
         if (!live || j0 + TKB - 1 > p_row || j0 < w_lo) {
 #pragma unroll
           for (int c = 0; c < TKB; ++c)

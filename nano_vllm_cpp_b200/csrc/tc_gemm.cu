@@ -113,6 +113,93 @@ __device__ __forceinline__ bool get_tile(const TcArgs& a, int tile_id, int y_til
   return true;
 }
 
+
+// The epilogue's work on W (16 or 32) token columns of one tile for this thread's output feature n (and, with two
+// accumulator sets, the second set's: the up rows of a SwiGLU, or feature n2 of a dual tile): both sets' loads from
+// tensor memory are in flight together, all values are worked out before the first store, and a whole chunk is
+// stored without a test per element, so that the one warp a scheduler has for this overlaps its own latencies.
+template <int W>
+__device__ __forceinline__ void epilogue_chunk(const TcArgs& a, const Tile& t, int two, uint32_t taddr, int c0, int n,
+                                               int n2, bool n_ok, bool n2_ok, float bias, float bias2) {
+  float g[W], u[W];
+  if (t.n_steps > 0) {
+    if (W == 32) {
+      tmem_ld32_nowait(taddr, g);
+      if (two) tmem_ld32_nowait(taddr + a.n_tile, u);
+    } else {
+      tmem_ld16_nowait(taddr, g);
+      if (two) tmem_ld16_nowait(taddr + a.n_tile, u);
+    }
+    tmem_ld_wait();
+    tmem_ld_fence<W>(g);
+    if (two) tmem_ld_fence<W>(u);
+  } else {
+#pragma unroll
+    for (int j = 0; j < W; ++j) g[j] = u[j] = 0.f;
+  }
+  if (!two) {
+#pragma unroll
+    for (int j = 0; j < W; ++j) u[j] = 0.f;
+  }
+  if (!n_ok) return;
+  const size_t row = (size_t)t.row0 + c0;
+  const int valid = min(W, t.rows_here - c0);
+  if (a.splits > 1) {
+    const int width = a.swiglu ? 2 * a.N : a.N;
+    float* p = a.partial + ((size_t)t.z * a.M_tok + row) * width;
+#pragma unroll
+    for (int j = 0; j < W; ++j) {
+      if (j < valid) {
+        p[(size_t)j * width + n] = g[j];
+        if (a.swiglu) p[(size_t)j * width + a.N + n] = u[j];
+        if (n2_ok) p[(size_t)j * width + n2] = u[j];
+      }
+    }
+    return;
+  }
+  if (valid < W) {
+    // a ragged chunk (the few rows of an expert's tile while decoding): only the rows that exist are worked out
+#pragma unroll
+    for (int j = 0; j < W; ++j) {
+      if (j < valid) {
+        const float v = (a.swiglu ? silu_mul(g[j], u[j]) : g[j]) + bias;
+        st_dt(a.out, a.out_dt, (row + j) * a.ldo + n, v);
+        if (n2_ok) st_dt(a.out, a.out_dt, (row + j) * a.ldo + n2, u[j] + bias2);
+      }
+    }
+    return;
+  }
+  if (a.swiglu) {
+#pragma unroll
+    for (int j = 0; j < W; ++j) g[j] = silu_mul(g[j], u[j]);
+  }
+#pragma unroll
+  for (int j = 0; j < W; ++j) {
+    g[j] += bias;
+    u[j] += bias2;
+  }
+  if (a.out_dt == NV_DT_BF16) {
+    bf16* o = (bf16*)a.out + row * a.ldo;
+#pragma unroll
+    for (int j = 0; j < W; ++j) o[(size_t)j * a.ldo + n] = __float2bfloat16_rn(g[j]);
+    if (n2_ok) {
+#pragma unroll
+      for (int j = 0; j < W; ++j) o[(size_t)j * a.ldo + n2] = __float2bfloat16_rn(u[j]);
+    }
+  } else {
+    float* o = (float*)a.out + row * a.ldo;
+#pragma unroll
+    for (int j = 0; j < W; ++j) o[(size_t)j * a.ldo + n] = g[j];
+    if (n2_ok) {
+#pragma unroll
+      for (int j = 0; j < W; ++j) o[(size_t)j * a.ldo + n2] = u[j];
+    }
+  }
+}
+
+// WIDE: token tiles of 32 columns or more (the epilogue works on 32 at a time and needs the registers for it); the
+// other form, for the small tiles of decoding, stays lean so that the kernels launched beside it find room.
+template <bool WIDE>
 __global__ void __launch_bounds__(NUM_THREADS, 2)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, TcArgs a) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -248,31 +335,36 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         if (n2_ok) bias2 = ld_dt(a.bias, a.bias_dt, n2);
       }
       const uint32_t lane_addr = tmem_base + b * acc_cols + ((uint32_t)(q * 32) << 16);
-      for (int c0 = 0; c0 < a.n_tile; c0 += 16) {
-        if (c0 >= t.rows_here) break;                // uniform over the warp
-        float g[16], u[16];
-        if (t.n_steps > 0) {
-          tmem_ld16(lane_addr + c0, g);
-          if (two) tmem_ld16(lane_addr + a.n_tile + c0, u);
-        } else {
-#pragma unroll
-          for (int j = 0; j < 16; ++j) g[j] = u[j] = 0.f;
-        }
-        if (!n_ok) continue;
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          if (c0 + j >= t.rows_here) break;
-          const size_t row = (size_t)(t.row0 + c0 + j);
-          if (a.splits > 1) {
-            const int width = a.swiglu ? 2 * a.N : a.N;
-            float* p = a.partial + ((size_t)t.z * a.M_tok + row) * width;
-            p[n] = g[j];
-            if (a.swiglu) p[a.N + n] = u[j];
-            if (n2_ok) p[n2] = u[j];
+      if (WIDE) {
+        for (int c0 = 0; c0 < t.rows_here; c0 += 32)             // uniform over the warp
+          epilogue_chunk<32>(a, t, two, lane_addr + c0, c0, n, n2, n_ok, n2_ok, bias, bias2);
+      } else {
+        for (int c0 = 0; c0 < a.n_tile; c0 += 16) {
+          if (c0 >= t.rows_here) break;                // uniform over the warp
+          float g[16], u[16];
+          if (t.n_steps > 0) {
+            tmem_ld16(lane_addr + c0, g);
+            if (two) tmem_ld16(lane_addr + a.n_tile + c0, u);
           } else {
-            float v = a.swiglu ? silu_mul(g[j], u[j]) : g[j];
-            st_dt(a.out, a.out_dt, row * a.ldo + n, v + bias);
-            if (n2_ok) st_dt(a.out, a.out_dt, row * a.ldo + n2, u[j] + bias2);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) g[j] = u[j] = 0.f;
+          }
+          if (!n_ok) continue;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            if (c0 + j >= t.rows_here) break;
+            const size_t row = (size_t)(t.row0 + c0 + j);
+            if (a.splits > 1) {
+              const int width = a.swiglu ? 2 * a.N : a.N;
+              float* p = a.partial + ((size_t)t.z * a.M_tok + row) * width;
+              p[n] = g[j];
+              if (a.swiglu) p[a.N + n] = u[j];
+              if (n2_ok) p[n2] = u[j];
+            } else {
+              float v = a.swiglu ? silu_mul(g[j], u[j]) : g[j];
+              st_dt(a.out, a.out_dt, row * a.ldo + n, v + bias);
+              if (n2_ok) st_dt(a.out, a.out_dt, row * a.ldo + n2, u[j] + bias2);
+            }
           }
         }
       }
@@ -467,6 +559,19 @@ NV_API int nv_tc_gemm(const void* X, long long ldx, int M_tok, const void* W, in
                                        : (M_tok >= 256 && (long long)((N + 255) / 256) * ((M_tok + n_tile - 1) / n_tile) >= 120);
   a.dual = (!swiglu && many_tokens && N >= 2 * TILE_W && a.splits == 1) ? 1 : 0;
   a.w_per_cta = a.dual ? 2 * TILE_W : TILE_W;
+  static std::once_flag once;
+  static cudaError_t attr_rc = cudaSuccess;
+  static int num_sms = 0;
+  std::call_once(once, [] {
+    attr_rc = cudaFuncSetAttribute(tc_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+    if (attr_rc == cudaSuccess)
+      attr_rc = cudaFuncSetAttribute(tc_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+    int dev = 0;
+    if (attr_rc == cudaSuccess) attr_rc = cudaGetDevice(&dev);
+    if (attr_rc == cudaSuccess) attr_rc = cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
+  });
+  if (attr_rc != cudaSuccess) return (int)attr_rc;
+
   const int two = (swiglu || a.dual) ? 1 : 0;
   const int stage_bytes = TILE_W * 128 * (two ? 2 : 1) + n_tile * 128;
   a.n_blocks = (N + a.w_per_cta - 1) / a.w_per_cta;
@@ -487,17 +592,6 @@ NV_API int nv_tc_gemm(const void* X, long long ldx, int M_tok, const void* W, in
   a.stages = stages;
   size_t smem = (size_t)stages * stage_bytes + 1024;
   if (!pair && smem < 120 * 1024) smem = 120 * 1024;   // more than half an SM's shared memory: no second CTA
-
-  static std::once_flag once;
-  static cudaError_t attr_rc = cudaSuccess;
-  static int num_sms = 0;
-  std::call_once(once, [] {
-    attr_rc = cudaFuncSetAttribute(tc_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
-    int dev = 0;
-    if (attr_rc == cudaSuccess) attr_rc = cudaGetDevice(&dev);
-    if (attr_rc == cudaSuccess) attr_rc = cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
-  });
-  if (attr_rc != cudaSuccess) return (int)attr_rc;
 
   const long long y_tiles = grouped ? max_tiles : (M_tok + n_tile - 1) / n_tile;
   const long long total = (long long)a.n_blocks * y_tiles * a.splits;     // an upper bound when grouped
@@ -526,10 +620,12 @@ NV_API int nv_tc_gemm(const void* X, long long ldx, int M_tok, const void* W, in
     attr[0].val.programmaticStreamSerializationAllowed = g_nv_dependent_launch ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    e = cudaLaunchKernelEx(&cfg, tc_gemm_kernel, tm_w, tm_x, a);
+    e = cudaLaunchKernelEx(&cfg, n_tile >= 32 ? tc_gemm_kernel<true> : tc_gemm_kernel<false>, tm_w, tm_x, a);
     if (e != cudaSuccess) return (int)e;
+  } else if (n_tile >= 32) {
+    tc_gemm_kernel<true><<<grid, NUM_THREADS, smem, stream>>>(tm_w, tm_x, a);
   } else {
-    tc_gemm_kernel<<<grid, NUM_THREADS, smem, stream>>>(tm_w, tm_x, a);
+    tc_gemm_kernel<false><<<grid, NUM_THREADS, smem, stream>>>(tm_w, tm_x, a);
   }
   e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
@@ -547,3 +643,4 @@ NV_API int nv_permute_rows_bf16(const void* src, const int* rows, void* dst, int
   NV_RETURN_IF(launch_dep(permute_rows_bf16_kernel, dim3(R), dim3(128), 0, stream, (const bf16*)src, rows, (bf16*)dst, H));
   NV_RETURN_LAST();
 }
+

@@ -151,7 +151,22 @@ __device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, float* v) {
         "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr));
 }
+__device__ __forceinline__ void tmem_ld16_nowait(uint32_t taddr, float* v) {
+  uint32_t* r = reinterpret_cast<uint32_t*>(v);
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// After tmem_ld_wait(): ties the loaded registers to the wait, so that nothing computed from them is moved above it
+// (the loads' asm defines the registers, but only this makes their use depend on the wait).
+template <int W>
+__device__ __forceinline__ void tmem_ld_fence(float* v) {
+#pragma unroll
+  for (int i = 0; i < W; ++i) asm volatile("" : "+f"(v[i]));
+}
 // 32 packed 32-bit words (here: pairs of bfloat16) of this thread's lane to 32 consecutive columns.
 __device__ __forceinline__ void tmem_st32_u32(uint32_t taddr, const uint32_t* v) {
   asm volatile(
@@ -183,3 +198,4 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
 }
 // Writes of ordinary threads to shared memory become visible to the tensor core and TMA (the async proxy).
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
