@@ -197,10 +197,14 @@ __device__ __forceinline__ void epilogue_chunk(const TcArgs& a, const Tile& t, i
   }
 }
 
-// WIDE: token tiles of 32 columns or more (the epilogue works on 32 at a time and needs the registers for it); the
-// other form, for the small tiles of decoding, stays lean so that the kernels launched beside it find room.
-template <bool WIDE>
-__global__ void __launch_bounds__(NUM_THREADS, 2)
+// MODE 0: the small token tiles of decoding; the epilogue takes 16 columns at a time and the kernel stays lean, so that
+// the kernels launched beside it find room.  MODE 1: tiles of 32 columns or more; the epilogue works on 32 at a time
+// and needs the registers for it.  MODE 2: the same with eight epilogue warps instead of four (two per quarter of the
+// tensor memory's lanes, taking turns at the chunks of columns), for the big tiles of a prompt, whose CTAs have a
+// multiprocessor to themselves.
+constexpr int WIDE_THREADS = 320;
+template <int MODE>
+__global__ void __launch_bounds__(MODE == 2 ? WIDE_THREADS : NUM_THREADS, MODE == 2 ? 1 : 2)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, TcArgs a) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   __shared__ uint64_t full_bar[MAX_STAGES], empty_bar[MAX_STAGES], acc_full[2], acc_empty[2];
@@ -225,7 +229,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&acc_full[b], 1);
-      mbar_init(&acc_empty[b], 4);                 // one arrival per epilogue warp
+      mbar_init(&acc_empty[b], MODE == 2 ? 8 : 4);  // one arrival per epilogue warp
     }
     mbar_fence_init();
   }
@@ -335,7 +339,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         if (n2_ok) bias2 = ld_dt(a.bias, a.bias_dt, n2);
       }
       const uint32_t lane_addr = tmem_base + b * acc_cols + ((uint32_t)(q * 32) << 16);
-      if (WIDE) {
+      if (MODE == 2) {
+        for (int c0 = warp >= 6 ? 32 : 0; c0 < t.rows_here; c0 += 64)
+          epilogue_chunk<32>(a, t, two, lane_addr + c0, c0, n, n2, n_ok, n2_ok, bias, bias2);
+      } else if (MODE == 1) {
         for (int c0 = 0; c0 < t.rows_here; c0 += 32)             // uniform over the warp
           epilogue_chunk<32>(a, t, two, lane_addr + c0, c0, n, n2, n_ok, n2_ok, bias, bias2);
       } else {
@@ -563,9 +570,11 @@ NV_API int nv_tc_gemm(const void* X, long long ldx, int M_tok, const void* W, in
   static cudaError_t attr_rc = cudaSuccess;
   static int num_sms = 0;
   std::call_once(once, [] {
-    attr_rc = cudaFuncSetAttribute(tc_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+    attr_rc = cudaFuncSetAttribute(tc_gemm_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
     if (attr_rc == cudaSuccess)
-      attr_rc = cudaFuncSetAttribute(tc_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+      attr_rc = cudaFuncSetAttribute(tc_gemm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+    if (attr_rc == cudaSuccess)
+      attr_rc = cudaFuncSetAttribute(tc_gemm_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
     int dev = 0;
     if (attr_rc == cudaSuccess) attr_rc = cudaGetDevice(&dev);
     if (attr_rc == cudaSuccess) attr_rc = cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
@@ -607,12 +616,15 @@ NV_API int nv_tc_gemm(const void* X, long long ldx, int M_tok, const void* W, in
       a.rest_first = (int)(total - rest);
     }
   }
+  const int mode = n_tile < 32 ? 0 : ((!pair && n_tile >= 128) ? 2 : 1);
+  const auto kernel = mode == 0 ? tc_gemm_kernel<0> : (mode == 1 ? tc_gemm_kernel<1> : tc_gemm_kernel<2>);
+  const unsigned threads = mode == 2 ? WIDE_THREADS : NUM_THREADS;
   cudaError_t e;
   if (a.early) {
     // programmatic dependent of the kernel before it in the stream (an edge of that kind when captured)
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
-    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.blockDim = dim3(threads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
@@ -620,12 +632,10 @@ NV_API int nv_tc_gemm(const void* X, long long ldx, int M_tok, const void* W, in
     attr[0].val.programmaticStreamSerializationAllowed = g_nv_dependent_launch ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    e = cudaLaunchKernelEx(&cfg, n_tile >= 32 ? tc_gemm_kernel<true> : tc_gemm_kernel<false>, tm_w, tm_x, a);
+    e = cudaLaunchKernelEx(&cfg, kernel, tm_w, tm_x, a);
     if (e != cudaSuccess) return (int)e;
-  } else if (n_tile >= 32) {
-    tc_gemm_kernel<true><<<grid, NUM_THREADS, smem, stream>>>(tm_w, tm_x, a);
   } else {
-    tc_gemm_kernel<false><<<grid, NUM_THREADS, smem, stream>>>(tm_w, tm_x, a);
+    kernel<<<grid, threads, smem, stream>>>(tm_w, tm_x, a);
   }
   e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
