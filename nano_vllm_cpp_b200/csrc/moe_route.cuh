@@ -55,6 +55,42 @@ __device__ __forceinline__ void route_row(const float* __restrict__ r, int E, in
   }
 }
 
+// Re-orders a tile list of `total` entries whose last `tail` entries belong to experts that every row visits (a few
+// experts with very many rows: their weights stay in L2 and their tiles are bound by arithmetic) so that those are
+// spread evenly among the others (many experts with few rows each: their tiles are bound by the stream of
+// weights from memory).  CTAs that walk the list together then work on both kinds at once, and the two limits
+// overlap instead of following one another.  One block; every entry is read before any is written.
+__device__ __forceinline__ void spread_tail_tiles(int* __restrict__ tile_expert, int* __restrict__ tile_row0,
+                                                  int* __restrict__ tile_rows, int total, int tail) {
+  constexpr int PER = 4;                          // entries per thread: lists longer than PER * threads stay as they are
+  const int tid = threadIdx.x, nthr = blockDim.x;
+  const int head = total - tail;
+  if (tail <= 0 || head <= 0 || total > PER * nthr) return;
+  int e[PER], r0[PER], rw[PER];
+#pragma unroll
+  for (int u = 0; u < PER; ++u) {
+    const int j = tid + u * nthr;
+    if (j < total) {
+      // of the slots before j, floor(j * tail / total) hold tail entries; slot j is one if that count steps at j + 1
+      const int before = (int)((long long)j * tail / total), upto = (int)((long long)(j + 1) * tail / total);
+      const int src = upto > before ? head + before : j - before;
+      e[u] = tile_expert[src];
+      r0[u] = tile_row0[src];
+      rw[u] = tile_rows[src];
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int u = 0; u < PER; ++u) {
+    const int j = tid + u * nthr;
+    if (j < total) {
+      tile_expert[j] = e[u];
+      tile_row0[j] = r0[u];
+      tile_rows[j] = rw[u];
+    }
+  }
+}
+
 // From idx[TK] (expert of every (row, k) pair; K pairs per row) build, for the grouped products:
 // counts and offsets per expert, the pairs sorted by expert (sorted_token = source row of each sorted
 // position, pair_pos = sorted position of each pair) and the list of tiles (expert, first row, rows)
@@ -65,6 +101,7 @@ __device__ __forceinline__ void route_row(const float* __restrict__ r, int E, in
 // The last `n_static` experts are ones that every row visits (a shared expert's chunks): their pairs sit in row
 // order, so their part of the permutation is known before any routing is (segment of expert E - n_static + c
 // starts at TK - (n_static - c) * rows), and they get no tiles here: whoever runs them has a fixed list.
+// With `n_spread` instead, the tiles of the last n_spread experts are spread through the list (spread_tail_tiles).
 __device__ __forceinline__ void align_block(const int* __restrict__ idx, int TK, int K, int E, int tile_m,
                                             int* __restrict__ counts, int* __restrict__ offsets,
                                             int* __restrict__ sorted_token, int* __restrict__ pair_pos,
@@ -73,7 +110,7 @@ __device__ __forceinline__ void align_block(const int* __restrict__ idx, int TK,
                                             int* __restrict__ err, int* al_s, int tile_m2 = 0,
                                             int* __restrict__ t2_expert = nullptr, int* __restrict__ t2_row0 = nullptr,
                                             int* __restrict__ t2_rows = nullptr, int* __restrict__ num_tiles2 = nullptr,
-                                            int n_static = 0) {
+                                            int n_static = 0, int n_spread = 0) {
   const int E_dyn = E - n_static;
   int* cnt = al_s;
   int* cur = al_s + E;
@@ -157,5 +194,18 @@ __device__ __forceinline__ void align_block(const int* __restrict__ idx, int TK,
       sorted_token[p] = i / K;
       pair_pos[i] = p;
     }
+  }
+  if (n_spread > 0 && n_spread < E) {
+    __threadfence_block();
+    __syncthreads();                       // the lists are complete, and this block wrote them
+    const int first = E - n_spread;        // tbase of the first spread expert = entries before the tail
+    int total = 0, total2 = 0;
+    {
+      const int cl = cnt[E - 1];
+      total = tbase[E - 1] + (cl + tile_m - 1) / tile_m;
+      if (tile_m2) total2 = tbase2[E - 1] + (cl + tile_m2 - 1) / tile_m2;
+    }
+    spread_tail_tiles(tile_expert, tile_row0, tile_rows, total, total - tbase[first]);
+    if (tile_m2) spread_tail_tiles(t2_expert, t2_row0, t2_rows, total2, total2 - tbase2[first]);
   }
 }

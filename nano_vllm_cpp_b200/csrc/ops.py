@@ -379,7 +379,9 @@ class MoeAlignment:
         return self.primary
 
 
-def moe_align(idx, K: int, al: MoeAlignment, err: ErrorFlag) -> None:
+def moe_align(idx, K: int, al: MoeAlignment, err: ErrorFlag, spread_last: int = 0) -> None:
+    """``spread_last``: the tiles of the last so many experts (ones that every row visits) are spread evenly through
+    the tile lists instead of standing at their end."""
     _cuda_contig(idx)
     _i32(idx)
     T = idx.numel() // K
@@ -389,7 +391,8 @@ def moe_align(idx, K: int, al: MoeAlignment, err: ErrorFlag) -> None:
                               _p(al.offsets), _p(al.sorted_token), _p(al.pair_pos),
                               _p(al.tile_expert), _p(al.tile_row0), _p(al.tile_rows), _p(al.num_tiles), _p(err.t),
                               c_int(s2.tile_m if s2 else 0), _p(s2.tile_expert if s2 else None), _p(s2.tile_row0 if s2 else None),
-                              _p(s2.tile_rows if s2 else None), _p(s2.num_tiles if s2 else None), _stream()),
+                              _p(s2.tile_rows if s2 else None), _p(s2.num_tiles if s2 else None), c_int(spread_last),
+                              _stream()),
            "moe_align")
 
 

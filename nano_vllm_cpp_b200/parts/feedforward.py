@@ -161,7 +161,7 @@ class SparseMoeSwiGLU(FeedForward):
                                            x=None)   # one block copies rows slower than the copy kernel does
         else:
             ops.router_topk(logits, self.K, self.renorm, idx, score, C, gate_logit)
-            ops.moe_align(idx, KT, al, ctx.err)
+            ops.moe_align(idx, KT, al, ctx.err, spread_last=C if fast else 0)
         self.last_alignment = al
         wide = al.secondary                      # the tile list of the SwiGLU product, if it has one of its own
         if x_sorted is not None:

@@ -319,6 +319,19 @@ def test_moe_align_and_combine():
     close(out, want, 2e-6, "combine")
     o.moe_combine(y, al.pair_pos, score, None, None, out)
     close(out, (score.double()[:, :, None] * yy).sum(1), 2e-6, "combine without shared expert")
+    # the last experts' tiles spread through the list: the same tiles in another order
+    def tiles(a):
+        m = int(a.num_tiles)
+        return [(int(a.tile_expert[i]), int(a.tile_row0[i]), int(a.tile_rows[i])) for i in range(m)]
+    plain_order = tiles(al)
+    o.moe_align(idx, K, al, err, spread_last=3)
+    err.check("align")
+    spread = tiles(al)
+    assert sorted(spread) == sorted(plain_order) and spread != plain_order
+    tail = [i for i, t3 in enumerate(spread) if t3[0] >= E - 3]
+    others = [t3 for t3 in spread if t3[0] < E - 3]
+    assert others == [t3 for t3 in plain_order if t3[0] < E - 3]          # each kind keeps its own order
+    assert tail[0] < len(spread) // 2 and all(b - a >= 2 for a, b in zip(tail, tail[1:])) or len(tail) * 2 > len(spread)
     bad = idx.clone()
     bad[5, 1] = E
     o.moe_align(bad, K, al, err)
