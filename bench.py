@@ -33,6 +33,14 @@ MODEL = dict(  # Qwen1.5-MoE-A2.7B layer sizes
     qkv_bias=True)
 FULL_LAYERS = 24
 SEED = 2
+# A second shape for measurements beyond the default run (--shape 57b): the layer sizes of Qwen2-57B-A14B.
+SHAPES = {
+    "a2.7b": ("Qwen1.5-MoE-A2.7B shape", MODEL, FULL_LAYERS, SEED),
+    "57b": ("Qwen2-57B-A14B shape", dict(
+        MODEL, num_hidden_layers=28, hidden_size=3584, num_attention_heads=28, num_key_value_heads=4, head_dim=128,
+        num_experts=64, num_experts_per_tok=8, moe_intermediate_size=2560, shared_expert_intermediate_size=20480,
+        intermediate_size=18944, max_position_embeddings=32768), 28, 4),
+}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
 
@@ -117,7 +125,8 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=2048)
-    ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the model has (named in config)")
+    ap.add_argument("--shape", default="a2.7b", choices=sorted(SHAPES), help="layer sizes (default: the headline shape)")
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (named in config)")
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--no-e2e", action="store_true")
@@ -141,7 +150,10 @@ def main() -> int:
     from nano_vllm_cpp_b200.engine.llm_engine import LLMEngine
     from nano_vllm_cpp_b200.config import SamplingParams
 
-    cfg = dict(MODEL, num_hidden_layers=args.layers)
+    shape_name, model, full_layers, seed = SHAPES[args.shape]
+    if args.layers is None:
+        args.layers = full_layers
+    cfg = dict(model, num_hidden_layers=args.layers)
     P, peak_src = peaks()
     work = tempfile.mkdtemp(prefix="bench_model_")
     with open(os.path.join(work, "config.json"), "w") as f:
@@ -151,13 +163,13 @@ def main() -> int:
     margin = args.steps + args.warmup + 80
     need_tokens = biggest * (args.context + margin) + args.prefill_tokens + 64
     page = 16
-    eng = LLMEngine(work, max_model_len=args.context + margin + 16, num_kv_blocks=(need_tokens + page - 1) // page,
-                    dtype="bfloat16", random_weights=True, seed=SEED, max_num_seqs=biggest + 1,
+    eng = LLMEngine(work, max_model_len=max(args.context + margin, args.prefill_tokens) + 16, num_kv_blocks=(need_tokens + page - 1) // page,
+                    dtype="bfloat16", random_weights=True, seed=seed, max_num_seqs=biggest + 1,
                     max_num_batched_tokens=max(args.prefill_tokens, biggest), enable_prefix_caching=False)
     runner = eng.runner
     dev = runner.device
     V = cfg["vocab_size"]
-    g = torch.Generator().manual_seed(SEED)
+    g = torch.Generator().manual_seed(seed)
 
     def ev():
         return torch.cuda.Event(enable_timing=True)
@@ -269,13 +281,14 @@ def main() -> int:
             points[f"decode_b{B}"] = round(B / pms * 1e3, 1)
 
     line = {
-        "metric": "decode tok/s (batch 8, 2,048-token context); prefill tok/s at 2,048 tokens; % of roofline",
+        "metric": f"decode tok/s (batch {args.batch}, {args.context:,}-token context); "
+                  f"prefill tok/s at {args.prefill_tokens:,} tokens; % of roofline",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic: random weights N(0,0.02) seed 2, uniform-random token ids, "
+        "dtype": "bf16", "data": f"synthetic: random weights N(0,0.02) seed {seed}, uniform-random token ids, "
                                  "synthetic cache contents for the decode context",
-        "config": {"model": "Qwen1.5-MoE-A2.7B shape", "global_batch": args.batch, "seq_len": args.context,
-                   "parallelism": "single GPU", "num_hidden_layers": args.layers, "full_num_hidden_layers": FULL_LAYERS,
+        "config": {"model": shape_name, "global_batch": args.batch, "seq_len": args.context,
+                   "parallelism": "single GPU", "num_hidden_layers": args.layers, "full_num_hidden_layers": full_layers,
                    "hidden_size": cfg["hidden_size"], "num_attention_heads": cfg["num_attention_heads"],
                    "num_key_value_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
                    "num_experts": cfg["num_experts"], "num_experts_per_tok": cfg["num_experts_per_tok"],
