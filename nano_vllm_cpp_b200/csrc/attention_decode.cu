@@ -620,6 +620,10 @@ int launch_decode_tc(DecArgs a, int R, const void* kc, const void* vc, int num_p
     cudaError_t e = cudaFuncSetAttribute(attention_decode_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          160 * 1024);
     if (e != cudaSuccess) return (int)e;
+    // three CTAs with a 64 KB ring each need nearly all of a multiprocessor's shared memory
+    e = cudaFuncSetAttribute(attention_decode_tc_kernel<D>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                             cudaSharedmemCarveoutMaxShared);
+    if (e != cudaSuccess) return (int)e;
     attr_done = true;
   }
   dim3 grid(R, a.Hkv * ((G + TC_ROWS - 1) / TC_ROWS), a.splits);
@@ -698,8 +702,10 @@ NV_API int nv_attention_decode(const void* qkv, int q_dt, int q_stride, const vo
   int rc;
   // The tensor-core form gives every stage of the ring to one warp (stage s to warp s % 4), so that the waits
   // of a warp on a barrier are for consecutive uses of it; that needs a ring of a multiple of four stages.
+  // A ring of up to 64 KB: with pages of 16 keys of 128 elements that is eight stages, two per warp, so that a warp's
+  // next page is on its way while it works on one (with one stage per warp a warp sat out the whole memory latency
+  // between two pages), and three CTAs of 76 KB still share a multiprocessor.  Deeper rings lose CTAs and time.
   int tc_stages = stages / WARPS * WARPS;
-  if (tc_stages > WARPS && (long long)WARPS * 2 * page * D * esize >= 32 * 1024) tc_stages = WARPS;   // more CTAs per SM beat a deeper ring
   if (cache_dt == NV_DT_BF16 && D % 64 == 0 && page <= 256 && num_pages > 0 && tc_stages >= WARPS &&
       !getenv("NV_DECODE_ATTENTION_SIMT")) {
     a.stages = tc_stages;
