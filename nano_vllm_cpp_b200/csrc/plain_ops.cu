@@ -114,7 +114,20 @@ __global__ void __launch_bounds__(NORM_THREADS) add_rmsnorm_kernel(NormArgs a) {
       Chunk<VEC> r;
 #pragma unroll
       for (int j = 0; j < VEC; ++j) r.v[j] = 0.f;
-      for (int k = 0; k < a.R; ++k) {
+      // four rows' loads are in flight before the first is used; the sum keeps the order of k
+      int k = 0;
+      for (; k + 4 <= a.R; k += 4) {
+        Chunk<VEC> y[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) y[u] = ld_chunk<VEC>(a.rows + (size_t)s_idx[k + u] * a.H + (size_t)c * VEC);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const float wk = s_w[k + u];
+#pragma unroll
+          for (int j = 0; j < VEC; ++j) r.v[j] = fmaf(wk, y[u].v[j], r.v[j]);
+        }
+      }
+      for (; k < a.R; ++k) {
         Chunk<VEC> y = ld_chunk<VEC>(a.rows + (size_t)s_idx[k] * a.H + (size_t)c * VEC);
         const float wk = s_w[k];
 #pragma unroll

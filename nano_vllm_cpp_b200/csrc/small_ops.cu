@@ -80,22 +80,21 @@ __global__ void __launch_bounds__(256) rowdot_wide_kernel(const float* __restric
   const int nt = min(WT, T - t0);
   if (K % 4 == 0 && lda % 4 == 0 && ((uintptr_t)a & 15) == 0) {
     // 16-byte loads, four in flight per thread: one scalar load at a time made this copy the kernel's time
-    const int k4 = K / 4;
-    for (int r = 0; r < WT; ++r) {
-      const float4* src = (const float4*)(a + (size_t)(t0 + r) * lda);
-      float4* dst = (float4*)(row_s + (size_t)r * K);
-      for (int i0 = threadIdx.x; i0 < k4; i0 += 4 * 256) {
-        float4 v[4];
+    // (the rows of the tile are walked as one run of WT * K / 4 loads, eight in flight per thread: row by row a
+    // thread had only K / 1024 loads under way at a time)
+    const int k4 = K / 4, total = WT * k4;
+    for (int i0 = threadIdx.x; i0 < total; i0 += 8 * 256) {
+      float4 v[8];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int i = i0 + u * 256;
-          v[u] = (r < nt && i < k4) ? src[i] : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
+      for (int u = 0; u < 8; ++u) {
+        const int i = i0 + u * 256;
+        const int r = i / k4, c = i - r * k4;
+        v[u] = (i < total && r < nt) ? ((const float4*)(a + (size_t)(t0 + r) * lda))[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int i = i0 + u * 256;
-          if (i < k4) dst[i] = v[u];
-        }
+      for (int u = 0; u < 8; ++u) {
+        const int i = i0 + u * 256;
+        if (i < total) ((float4*)row_s)[i] = v[u];
       }
     }
   } else {
