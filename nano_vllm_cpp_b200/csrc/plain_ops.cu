@@ -241,7 +241,32 @@ __global__ void __launch_bounds__(256) rope_store_kernel(void* __restrict__ qkv,
   // owns whole pairs (f, f + half), so rotating q in place needs no barrier
   const int rot_end = min(h_end, write_kv ? Hq + Hkv : Hq);
   const bool packed = dt == NV_DT_BF16 && cache_dt == NV_DT_BF16 && half % 2 == 0 && D % 8 == 0;
-  if (packed) {
+  if (packed && half % 8 == 0) {
+    // bfloat16 buffers, eight pairs per thread: 16-byte loads and stores
+    const int hp = half / 8;
+    bf16* qb = (bf16*)qkv;
+    bf16* kb = (bf16*)kc;
+    for (int i = threadIdx.x; i < (rot_end - h_begin) * hp; i += blockDim.x) {
+      const int h = h_begin + i / hp, f = (i % hp) * 8;
+      const size_t base = row + (size_t)h * D;
+      const uint4 r1 = *(const uint4*)(qb + base + f), r2 = *(const uint4*)(qb + base + f + half);
+      const __nv_bfloat162* p1 = (const __nv_bfloat162*)&r1;
+      const __nv_bfloat162* p2 = (const __nv_bfloat162*)&r2;
+      uint4 w1, w2;
+      __nv_bfloat162* o1 = (__nv_bfloat162*)&w1;
+      __nv_bfloat162* o2 = (__nv_bfloat162*)&w2;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 x1 = __bfloat1622float2(p1[j]), x2 = __bfloat1622float2(p2[j]);
+        const float c0 = cs[f + 2 * j], c1 = cs[f + 2 * j + 1], s0 = sn[f + 2 * j], s1 = sn[f + 2 * j + 1];
+        o1[j] = __floats2bfloat162_rn(x1.x * c0 - x2.x * s0, x1.y * c1 - x2.y * s1);
+        o2[j] = __floats2bfloat162_rn(x2.x * c0 + x1.x * s0, x2.y * c1 + x1.y * s1);
+      }
+      bf16* dst = h < Hq ? qb + base : kb + (((size_t)blk * Hkv + (h - Hq)) * page + slot) * D;
+      *(uint4*)(dst + f) = w1;
+      *(uint4*)(dst + f + half) = w2;
+    }
+  } else if (packed) {
     // bfloat16 buffers: two pairs per thread, 4-byte loads and stores
     const int hp = half / 2;
     bf16* qb = (bf16*)qkv;
