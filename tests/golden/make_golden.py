@@ -113,7 +113,9 @@ def prompt_ids(case_name, n, vocab):
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        sys.exit("usage: make_golden.py /path/to/reference  (a checkout of Maxritz/Nano_vLLM_cpp)")
+    ref = sys.argv[1]
     work = tempfile.mkdtemp()
     exe = os.path.join(work, "ref_top5")
     subprocess.check_call(["g++", "-std=c++20", "-O2", f"-I{ref}/include", f"{ref}/tools/ref_top5.cpp",
