@@ -8,6 +8,9 @@
 The prompt is given as token ids (``--tokens``); this engine has no tokenizer, so a text prompt
 is refused.  ``--chat`` and ``--server`` belong to parts of the reference that are not built
 here.  ``--expert-budget`` is accepted and ignored: every expert stays resident in device memory.
+``--top-p``, ``--rep-penalty`` and ``--rep-window`` are those of the reference's second command line
+(src/main_vulkan.cpp:260-298): nucleus sampling, and the scores of ids among the last W completion tokens
+divided by THETA (1.0 = off, W = 0: the whole completion).
 Exit codes as the reference's: 1 usage, 2 error (src/main.cpp:432-438).
 """
 from __future__ import annotations
@@ -20,6 +23,7 @@ USAGE = """Usage: nanovllm <model_dir> --tokens 1,2,3 [--max-tokens N] [--temper
   further options: --num-kv-blocks N  --dtype bfloat16|float32  --random-weights  --seed S
                    --page-size N  --prefill-chunk N  --max-num-batched-tokens N  --max-num-seqs N
                    --eos ID  --ignore-eos  --expert-budget GB (ignored)
+                   --top-p P  --rep-penalty THETA  --rep-window W   (nucleus sampling and repetition penalty)
 """
 
 
@@ -36,14 +40,15 @@ def main(argv=None) -> int:
     opt = dict(model_dir="", prompt="", prompt_ids=[], max_tokens=64, temperature=0.6, max_model_len=4096,
                bench=False, num_seqs=4, num_kv_blocks=0, dtype="bfloat16", random_weights=False, seed=0,
                page_size=16, prefill_chunk=0, max_num_batched_tokens=16384, max_num_seqs=512, eos=-1,
-               ignore_eos=False)
+               ignore_eos=False, top_p=1.0, rep_penalty=1.0, rep_window=64)
     with_value = {"--tokens": ("prompt_ids", parse_ids), "--max-tokens": ("max_tokens", int),
                   "--temperature": ("temperature", float), "--max-model-len": ("max_model_len", int),
                   "--num-kv-blocks": ("num_kv_blocks", int), "--expert-budget": (None, float),
                   "--num-seqs": ("num_seqs", int), "--dtype": ("dtype", str), "--seed": ("seed", int),
                   "--page-size": ("page_size", int), "--prefill-chunk": ("prefill_chunk", int),
                   "--max-num-batched-tokens": ("max_num_batched_tokens", int),
-                  "--max-num-seqs": ("max_num_seqs", int), "--eos": ("eos", int)}
+                  "--max-num-seqs": ("max_num_seqs", int), "--eos": ("eos", int), "--top-p": ("top_p", float),
+                  "--rep-penalty": ("rep_penalty", float), "--rep-window": ("rep_window", int)}
     i = 0
     try:
         while i < len(args):
@@ -96,7 +101,8 @@ def _run(opt) -> int:
                        prefill_chunk=opt["prefill_chunk"], max_num_batched_tokens=opt["max_num_batched_tokens"],
                        max_num_seqs=opt["max_num_seqs"], eos=opt["eos"])
     sp = SamplingParams(temperature=opt["temperature"], max_tokens=opt["max_tokens"],
-                        ignore_eos=opt["ignore_eos"] or opt["bench"])
+                        ignore_eos=opt["ignore_eos"] or opt["bench"], top_p=opt["top_p"],
+                        repetition_penalty=opt["rep_penalty"], repetition_window=opt["rep_window"])
     if opt["bench"]:
         # synthetic prompts of 64 ids, 1 + ((i*37 + t) % (V-2))  (src/main.cpp:388-412)
         import torch

@@ -48,9 +48,22 @@ class SamplingParams:
     max_tokens: int = 64
     ignore_eos: bool = False
     seed: int | None = None
+    # The reference's second sampler (include/nanovllm/sampler.hpp:46-88; its command line's --top-p,
+    # --rep-penalty, --rep-window, src/main_vulkan.cpp:260-298).  A request with top_p < 1 or a penalty other
+    # than 1 is sampled by that rule (nucleus in descending order of probability); the defaults leave the
+    # engine's first rule (sampler.hpp:10-34) in place.
+    top_p: float = 1.0
+    repetition_penalty: float = 1.0       # scores of ids among the recent completion tokens are divided by it
+    repetition_window: int = 64           # how many of the latest completion tokens count; 0 = all of them
 
     def validate(self) -> None:
         if self.temperature < 0:
             raise ValueError("temperature cannot be negative")
         if self.max_tokens < 1:
             raise ValueError("max_tokens must be positive")
+        if self.top_p < 0:
+            raise ValueError("top_p cannot be negative")
+        if not (self.repetition_penalty >= 1e-3):
+            raise ValueError("repetition_penalty must be at least 0.001 (1 = off)")
+        if self.repetition_window < 0:
+            raise ValueError("repetition_window cannot be negative (0 = the whole completion)")

@@ -485,6 +485,21 @@ def sample(logits, temperature, u, out) -> None:
     _check(lib().nv_sample(_p(logits), c_int(R), c_int(V), _p(temperature), _p(u), _p(out), _stream()), "sample")
 
 
+def sample_nucleus(logits, params, recent, recent_off, out) -> None:
+    """One token per row by nucleus (top-p) sampling with a repetition penalty (include/nanovllm/sampler.hpp:46-88).
+    ``params``: float64 [R, 4] = (temperature, top_p, penalty, u) per row; ``recent``: int32 ids whose scores are
+    divided by the row's penalty, row r's being ``recent[recent_off[r]:recent_off[r + 1]]``."""
+    _cuda_contig(logits, params, recent, recent_off, out)
+    R, V = logits.shape
+    _need(logits.dtype == torch.float32 and params.dtype == torch.float64 and params.shape == (R, 4),
+          "sample_nucleus: logits float32 [R, V], params float64 [R, 4]")
+    _i32(recent, recent_off, out)
+    _need(recent_off.numel() == R + 1 and out.numel() == R, "sample_nucleus: one entry per row")
+    work = torch.empty_like(logits)
+    _check(lib().nv_sample_nucleus(_p(logits), _p(work), c_int(R), c_int(V), _p(params), _p(recent), _p(recent_off),
+                                   _p(out), _stream()), "sample_nucleus")
+
+
 # ----------------------------------------------------------------------------- fast products
 _num_sms = None
 

@@ -70,6 +70,7 @@ class LLMEngine:
                                    max_model_len=cfg.max_model_len, eos=cfg.eos, prefill_chunk=cfg.prefill_chunk)
         self.sampler = Sampler(self.runner.device)
         self._pending = None
+        self._nucleus_live = set()      # ids of live requests that are sampled by the nucleus rule
 
     @staticmethod
     def _eos_from_files(model_dir: str, from_config: int) -> int:
@@ -110,6 +111,8 @@ class LLMEngine:
             raise ValueError(f"token id {bad[0]} is outside the vocabulary [0, {self.vocab_size})")
         seq = Sequence(ids, sp, base_seed=self.config.seed)
         self.scheduler.add(seq)
+        if seq.nucleus_sampling:
+            self._nucleus_live.add(seq.seq_id)
         return seq.seq_id
 
     # ------------------------------------------------------------------ one step
@@ -127,7 +130,9 @@ class LLMEngine:
             if self._pending is None:
                 return StepOutput([])
         cur, nxt = self._pending, None
-        if self.config.run_ahead:
+        # (a request under the nucleus rule needs its latest tokens on the host for the repetition penalty:
+        # while one is live, steps run in the plain order)
+        if self.config.run_ahead and not self._nucleus_live:
             self._stand_ins(cur)
             nxt = self._launch()
         tokens = self.runner.collect(cur.handle)
@@ -138,7 +143,7 @@ class LLMEngine:
         scheduled = self.scheduler.schedule()
         if not scheduled:
             return None
-        entries, temps, us, sampled_seqs = [], [], [], []
+        entries, temps, us, sampled_seqs, nucleus = [], [], [], [], []
         n_prefill = n_decode = 0
         for s in scheduled:
             toks = s.seq.token_ids[s.start:s.start + s.count]
@@ -148,11 +153,13 @@ class LLMEngine:
                 # greedy rows draw nothing: their number is never looked at
                 us.append(uniform(s.seq.seed, s.seq.num_completion_tokens) if s.seq.temperature > 0 else 0.0)
                 sampled_seqs.append(s.seq)
+                nucleus.append((s.seq.top_p, s.seq.repetition_penalty, s.seq.recent_token_ids)
+                               if s.seq.nucleus_sampling else None)
             if s.count == 1 and s.start >= s.seq.num_prompt_tokens:
                 n_decode += 1
             else:
                 n_prefill += s.count
-        handle = self.runner.launch_tokens(entries, temps, us)
+        handle = self.runner.launch_tokens(entries, temps, us, nucleus if any(x is not None for x in nucleus) else None)
         return _Pending(scheduled, sampled_seqs, handle, n_prefill, n_decode)
 
     def _stand_ins(self, cur) -> None:
@@ -166,6 +173,7 @@ class LLMEngine:
         if cur.places is None:                                   # nothing was decided ahead: the plain order
             sampled = {seq.seq_id: tok for seq, tok in zip(cur.sampled_seqs, tokens)}
             finished = self.scheduler.postprocess(cur.scheduled, sampled)
+            self._nucleus_live.difference_update(q.seq_id for q in finished)
             return StepOutput([(q.seq_id, q.completion_token_ids) for q in finished], cur.n_prefill, cur.n_decode,
                               list(sampled.items()))
         finished, new = list(cur.finished), []
@@ -177,6 +185,7 @@ class LLMEngine:
             if tok == self.config.eos and not seq.ignore_eos and not seq.is_finished:
                 self.scheduler.finish_late(seq)
                 finished.append(seq)
+        self._nucleus_live.difference_update(q.seq_id for q in finished)
         return StepOutput([(q.seq_id, q.completion_token_ids) for q in finished], cur.n_prefill, cur.n_decode, new)
 
     # ------------------------------------------------------------------ generate

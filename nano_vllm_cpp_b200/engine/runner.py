@@ -164,28 +164,35 @@ class ModelRunner:
         return logits
 
     @torch.no_grad()
-    def step_tokens(self, entries: list, temperatures: list, uniforms: list) -> list:
+    def step_tokens(self, entries: list, temperatures: list, uniforms: list, nucleus: list | None = None) -> list:
         """``step`` followed by the choice of one token per wanted row (greedy where the temperature is <= 0, else
         by the row's uniform number; see ``sampling``), all on the device: the sampling inputs travel with the
         step's index arrays, the tokens and the kernels' error flag come back in one copy, and the host waits
         once.  Returns the tokens in the order of the wanted rows."""
         if not entries:
             return []
-        return self.collect(self.launch_tokens(entries, temperatures, uniforms))
+        return self.collect(self.launch_tokens(entries, temperatures, uniforms, nucleus))
 
     @torch.no_grad()
-    def launch_tokens(self, entries: list, temperatures: list, uniforms: list):
+    def launch_tokens(self, entries: list, temperatures: list, uniforms: list, nucleus: list | None = None):
         """Queues ``step_tokens`` and returns a handle for ``collect`` without waiting.  The tokens also stay on the
         device (``self.feed``): an entry of the *next* launch may name the token drawn for wanted row r of this
-        one as ``-(r + 1)`` instead of its value, so the next step can be queued before this one has been read."""
+        one as ``-(r + 1)`` instead of its value, so the next step can be queued before this one has been read.
+
+        ``nucleus``: per wanted row ``None`` or ``(top_p, penalty, recent ids)``: such a row's token is drawn by the
+        nucleus rule with repetition penalty (``ops.sample_nucleus``) from the same logits, temperature and
+        uniform number; the other rows are untouched by it."""
         sampling = (temperatures, uniforms)
         batch = None
-        if self.cuda_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
+        picked = [r for r, x in enumerate(nucleus or []) if x is not None]
+        if not picked and self.cuda_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
             _, batch = self._graph_step(entries, sampling)
         if batch is None:
             batch = self.prepare(entries, sampling=sampling)
             logits = self.model.forward(batch, self.cache)
             self._sample_into_feed(logits, batch)
+            if picked:
+                self._nucleus_into_feed(logits, picked, temperatures, uniforms, nucleus)
         W = len(temperatures)
         k = self._out_at
         self._out_at = (k + 1) % len(self._out_ring)
@@ -215,6 +222,22 @@ class ModelRunner:
         if W:
             ops.sample(logits, batch.temperatures, batch.uniforms, self.feed[:W])
         self.feed[W:W + 1].copy_(self.ctx.err.t)
+
+    def _nucleus_into_feed(self, logits, picked, temperatures, uniforms, nucleus) -> None:
+        """Draws the rows ``picked`` again by the nucleus rule and puts their tokens in their places of ``feed``."""
+        params, flat, off = [], [], [0]
+        for r in picked:
+            top_p, penalty, recent = nucleus[r]
+            params.append([float(temperatures[r]), float(top_p), float(penalty), float(uniforms[r])])
+            flat += [int(t) for t in recent]
+            off.append(len(flat))
+        dev = self.device
+        rows = torch.tensor(picked, dtype=torch.int64).to(dev, non_blocking=True)
+        out = torch.empty(len(picked), dtype=torch.int32, device=dev)
+        ops.sample_nucleus(logits.index_select(0, rows), torch.tensor(params, dtype=torch.float64).to(dev),
+                           torch.tensor(flat or [0], dtype=torch.int32).to(dev),
+                           torch.tensor(off, dtype=torch.int32).to(dev), out)
+        self.feed.index_copy_(0, rows, out)
 
     # ------------------------------------------------------------------ decode steps as CUDA graphs
     def _graph_step(self, entries: list, sampling):

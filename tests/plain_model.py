@@ -246,6 +246,46 @@ def sample(logits, temperature: float, u: float) -> int:
     return int(hit[0]) if len(hit) else len(l) - 1
 
 
+def sample_row(logits, temperature: float, top_p: float, u: float, recent=(), rep_penalty: float = 1.0,
+               rep_window: int = 64) -> int:
+    """The reference's second sampler (include/nanovllm/sampler.hpp:46-88): greedy at temperature <= 0, else
+    s_i = float(exp((l_i - max) / T)); the ids seen among the last ``rep_window`` of ``recent`` (0: all of it; each
+    id once) have s divided by float(rep_penalty); tokens in descending order of s (the reference's sort leaves
+    the order of equal scores open: here the lower id first); the nucleus ends at the first place i > 0 whose
+    running share reaches top_p; r = u * (share of the nucleus), answer = first token whose running share
+    reaches r, else the nucleus's last."""
+    l = np.asarray(logits, dtype=np.float32)
+    V = len(l)
+    if temperature <= 0:
+        return int(np.argmax(l))
+    mx = l.max()
+    sc = np.exp((l - mx).astype(np.float64) / temperature).astype(np.float32)
+    recent = list(recent)
+    if rep_penalty != 1.0 and rep_penalty > 0.0 and recent:
+        w = min(rep_window, len(recent)) if rep_window > 0 else len(recent)
+        seen = []
+        for tok in recent[len(recent) - w:]:
+            if tok < 0 or tok >= V or tok in seen:
+                continue
+            seen.append(tok)
+            sc[tok] = np.float32(sc[tok] / np.float32(rep_penalty))
+    total = float(np.sum(sc.astype(np.float64)))
+    order = np.argsort(-sc.astype(np.float64), kind="stable")
+    share = sc[order].astype(np.float64) / total
+    acc, keep = 0.0, V
+    for i in range(V):
+        acc += share[i]
+        if acc >= top_p and i > 0:
+            keep = i + 1
+            break
+    r, run = u * acc, 0.0
+    for i in range(keep):
+        run += share[i]
+        if r <= run:
+            return int(order[i])
+    return int(order[keep - 1])
+
+
 def greedy_generate(cfg, W, prompt, n_new: int):
     ids = list(prompt)
     for _ in range(n_new):

@@ -187,3 +187,12 @@ def test_random_source_is_order_independent():
     a = {n: s1.stored(n) for n in names}
     b = {n: s2.stored(n) for n in reversed(names)}
     assert all(torch.equal(a[n], b[n]) for n in names)
+
+
+def test_sampling_params_are_checked():
+    from nano_vllm_cpp_b200 import SamplingParams
+    SamplingParams(temperature=0.0, top_p=0.0, repetition_penalty=1.3, repetition_window=0).validate()
+    for bad in (dict(temperature=-1.0), dict(max_tokens=0), dict(top_p=-0.1), dict(repetition_penalty=0.0),
+                dict(repetition_penalty=float("nan")), dict(repetition_window=-1)):
+        with pytest.raises(ValueError):
+            SamplingParams(**bad).validate()

@@ -121,6 +121,72 @@ def test_sample_kernel_against_plain_sampler():
     assert out.tolist() == [7, 0]                            # the first largest logit
 
 
+def nucleus(logits, rows):
+    """rows: (temperature, top_p, penalty, u, recent ids) per row -> the kernel's tokens."""
+    from nano_vllm_cpp_b200.csrc import ops
+    params = torch.tensor([[t, p, pen, u] for t, p, pen, u, _ in rows], dtype=torch.float64).cuda()
+    flat, off = [], [0]
+    for *_, recent in rows:
+        flat += list(recent)
+        off.append(len(flat))
+    recent = torch.tensor(flat or [0], dtype=torch.int32).cuda()
+    out = torch.empty(len(rows), dtype=torch.int32, device="cuda")
+    ops.sample_nucleus(logits, params, recent, torch.tensor(off, dtype=torch.int32).cuda(), out)
+    return out.tolist()
+
+
+def test_nucleus_kernel_against_plain_sampler():
+    g = torch.Generator().manual_seed(3)
+    for V in (2, 5, 384, 1000, 151936):
+        rows = [(0.0, 0.9, 1.0, 0.3, []), (0.5, 0.9, 1.0, 0.0, []), (1.0, 0.95, 1.0, 0.999999, []),
+                (2.0, 0.5, 1.0, 0.5, []), (0.7, 0.1, 1.0, 0.97, []), (1.3, 1.0, 1.0, 0.9999, []),
+                (1.0, 0.9, 1.3, 0.4, [1, 0, 1, V - 1, V + 5, -2]), (0.8, 0.8, 0.5, 0.6, [V // 2] * 3 + [0]),
+                (1.0, 0.0, 1.0, 0.75, []), (0.9, 0.3, 1e20, 0.2, list(range(min(V - 1, 40))))]
+        logits = (torch.randn(len(rows), V, generator=g) * 3).cuda()
+        want = [helpers.plain_model.sample_row(logits[r].cpu().numpy(), t, p, u, recent, pen, 0)
+                for r, (t, p, pen, u, recent) in enumerate(rows)]
+        assert nucleus(logits, rows) == want, f"V = {V}"
+    # equal scores are taken in index order; one dominant token still leaves a nucleus of two
+    tie = torch.zeros(4, 100)
+    tie[:, 7] = tie[:, 50] = tie[:, 51] = 3.0
+    tie[3, 7] = 6.0
+    rows = [(1.0, 0.9, 1.0, 0.0, []), (1.0, 0.9, 1.0, 0.5, []), (1.0, 0.9, 1.0, 0.95, []), (1.0, 0.5, 1.0, 0.9999999, [])]
+    got = nucleus(tie.cuda(), rows)
+    want = [helpers.plain_model.sample_row(tie[r].numpy(), t, p, u, recent, pen, 0) for r, (t, p, pen, u, recent) in enumerate(rows)]
+    assert got == want and got[0] == 7 and got[3] == 50
+
+
+def test_nucleus_sampling_through_the_entry_point(folders):
+    """Requests with top_p and a repetition penalty beside a greedy one and a plainly sampled one: every token is the
+    plain sampler's choice on the plain logits of its prefix, with the request's own uniform numbers; the other
+    requests' tokens are what they are without such neighbours; another batching changes nothing."""
+    from nano_vllm_cpp_b200 import SamplingParams
+    from nano_vllm_cpp_b200.sampling import uniform
+    case = "A"
+    prompts = [prompt(case, n, salt=60 + i) for i, n in enumerate((9, 17, 5, 12))]
+    sps = [SamplingParams(temperature=0.9, top_p=0.6, max_tokens=14, ignore_eos=True, seed=200),
+           SamplingParams(temperature=1.2, top_p=0.9, repetition_penalty=1.5, repetition_window=4, max_tokens=14,
+                          ignore_eos=True, seed=201),
+           SamplingParams(temperature=0.0, top_p=0.5, repetition_penalty=2.0, max_tokens=14, ignore_eos=True),
+           SamplingParams(temperature=0.8, max_tokens=14, ignore_eos=True, seed=203)]
+    a = [o["token_ids"] for o in engine(folders[case]).generate(prompts, sps)]
+    b = [o["token_ids"] for o in engine(folders[case], max_num_batched_tokens=16, max_num_seqs=2).generate(prompts, sps)]
+    assert a == b
+    alone = engine(folders[case]).generate(prompts[2:], sps[2:])
+    assert [o["token_ids"] for o in alone] == a[2:]
+    cfg, W = helpers.plain_model.read_folder(folders[case])
+    for i in (0, 1):
+        ids, done = list(prompts[i]), []
+        for k, tok in enumerate(a[i]):
+            logits = helpers.plain_model.forward(cfg, W, ids)[-1].float().numpy()
+            want = helpers.plain_model.sample_row(logits, sps[i].temperature, sps[i].top_p, uniform(sps[i].seed, k), done,
+                                                  sps[i].repetition_penalty, sps[i].repetition_window)
+            assert tok == want, f"request {i}, token {k}"
+            ids.append(tok)
+            done.append(tok)
+    assert a[2] == plain_greedy(folders[case], prompts[2], 14)      # greedy is never penalised
+
+
 def test_command_line(folders):
     exe = os.path.join(os.path.dirname(helpers.HERE), "bin", "nanovllm")
     ids = prompt("A", 5, salt=9)
