@@ -11,6 +11,8 @@ here.  ``--expert-budget`` is accepted and ignored: every expert stays resident 
 ``--top-p``, ``--rep-penalty`` and ``--rep-window`` are those of the reference's second command line
 (src/main_vulkan.cpp:260-298): nucleus sampling, and the scores of ids among the last W completion tokens
 divided by THETA (1.0 = off, W = 0: the whole completion).
+``temperature``, ``top_p`` and ``max_new_tokens`` of the model folder's ``generation_config.json`` are the
+defaults of the options that are not given (src/main_vulkan.cpp:360-363).
 Exit codes as the reference's: 1 usage, 2 error (src/main.cpp:432-438).
 """
 from __future__ import annotations
@@ -25,6 +27,29 @@ USAGE = """Usage: nanovllm <model_dir> --tokens 1,2,3 [--max-tokens N] [--temper
                    --eos ID  --ignore-eos  --expert-budget GB (ignored)
                    --top-p P  --rep-penalty THETA  --rep-window W   (nucleus sampling and repetition penalty)
 """
+
+
+def generation_defaults(model_dir: str) -> dict:
+    """``temperature``, ``top_p`` and ``max_tokens`` (from ``max_new_tokens`` >= 1) of
+    ``<model_dir>/generation_config.json``, read best-effort: a missing or unreadable file or key gives no
+    default (include/nanovllm/config.hpp:213-250).  They stand in for options that the command line does not
+    give (src/main_vulkan.cpp:360-363)."""
+    import json
+    import os
+    out = {}
+    try:
+        with open(os.path.join(model_dir, "generation_config.json")) as f:
+            g = json.load(f)
+        if isinstance(g.get("temperature"), (int, float)) and not isinstance(g.get("temperature"), bool):
+            out["temperature"] = float(g["temperature"])
+        if isinstance(g.get("top_p"), (int, float)) and not isinstance(g.get("top_p"), bool):
+            out["top_p"] = float(g["top_p"])
+        if isinstance(g.get("max_new_tokens"), int) and not isinstance(g.get("max_new_tokens"), bool) \
+                and g["max_new_tokens"] >= 1:
+            out["max_tokens"] = int(g["max_new_tokens"])
+    except (OSError, ValueError, AttributeError):
+        return {}
+    return out
 
 
 def parse_ids(s: str) -> list:
@@ -50,6 +75,7 @@ def main(argv=None) -> int:
                   "--max-num-seqs": ("max_num_seqs", int), "--eos": ("eos", int), "--top-p": ("top_p", float),
                   "--rep-penalty": ("rep_penalty", float), "--rep-window": ("rep_window", int)}
     i = 0
+    given = set()
     try:
         while i < len(args):
             a = args[i]
@@ -58,6 +84,7 @@ def main(argv=None) -> int:
                 i += 1
                 if key is not None:
                     opt[key] = conv(args[i])
+                    given.add(key)
             elif a == "--bench":
                 opt["bench"] = True
             elif a == "--random-weights":
@@ -84,6 +111,9 @@ def main(argv=None) -> int:
     if not opt["model_dir"]:
         sys.stderr.write(USAGE)
         return 1
+    for key, value in generation_defaults(opt["model_dir"]).items():
+        if key not in given:                  # explicit options win
+            opt[key] = value
     try:
         return _run(opt)
     except Exception as e:  # src/main.cpp:432-438

@@ -36,3 +36,20 @@ def test_a_text_prompt_is_refused_before_anything_is_loaded(capsys):
 
 def test_token_list():
     assert cli.parse_ids("1,2, 3,") == [1, 2, 3]
+
+
+def test_generation_config_gives_defaults_that_options_override(tmp_path, monkeypatch):
+    import json
+    (tmp_path / "generation_config.json").write_text(json.dumps(
+        {"temperature": 0.25, "top_p": 0.8, "max_new_tokens": 7, "eos_token_id": [5, 6]}))
+    assert cli.generation_defaults(str(tmp_path)) == {"temperature": 0.25, "top_p": 0.8, "max_tokens": 7}
+    seen = {}
+    monkeypatch.setattr(cli, "_run", lambda opt: seen.update(opt) or 0)
+    assert cli.main([str(tmp_path), "--tokens", "1,2", "--top-p", "0.5"]) == 0
+    assert (seen["temperature"], seen["top_p"], seen["max_tokens"]) == (0.25, 0.5, 7)
+    # a broken or absent file gives nothing and never fails
+    (tmp_path / "generation_config.json").write_text("{ not json")
+    assert cli.generation_defaults(str(tmp_path)) == {}
+    assert cli.generation_defaults(str(tmp_path / "nowhere")) == {}
+    (tmp_path / "generation_config.json").write_text(json.dumps({"temperature": "hot", "max_new_tokens": 0}))
+    assert cli.generation_defaults(str(tmp_path)) == {}
