@@ -1,5 +1,6 @@
-"""Makes tests/golden/ref_sample_row.json: what the reference's own nucleus sampler (``sample_row``,
-include/nanovllm/sampler.hpp:46-88, compiled unchanged with g++) picks for small random rows of logits.
+"""Makes tests/golden/ref_sample_row.json: what the reference's own samplers (``Sampler::sample``,
+include/nanovllm/sampler.hpp:10-34, and the nucleus sampler ``sample_row``, sampler.hpp:46-88, compiled
+unchanged with g++) pick for small random rows of logits.
 
     python tests/golden/make_golden_sampler.py /path/to/reference
 
@@ -19,12 +20,27 @@ import tempfile
 import numpy as np
 
 DRIVER = r"""
+#define private public            // the first sampler keeps its generator private: the driver seeds it
 #include "nanovllm/sampler.hpp"
+#undef private
 #include <cstdio>
 #include <vector>
 int main() {
-  int cases;
-  if (std::scanf("%d", &cases) != 1) return 1;
+  int cases, first;
+  if (std::scanf("%d %d", &cases, &first) != 2) return 1;
+  for (int c = 0; c < first; ++c) {     // Sampler::sample (sampler.hpp:10-34): V, temperature, seed, logits
+    int V;
+    unsigned seed;
+    double temp;
+    if (std::scanf("%d %lf %u", &V, &temp, &seed) != 3) return 1;
+    std::vector<float> logits(V);
+    for (float& l : logits) if (std::scanf("%f", &l) != 1) return 1;
+    Sampler s;
+    s.rng_.seed(seed);
+    std::mt19937 peek(seed);
+    const double u = std::uniform_real_distribution<double>(0.0, 1.0)(peek);
+    std::printf("%.17g %d\n", u, s.sample(logits.data(), V, temp));
+  }
   for (int c = 0; c < cases; ++c) {
     int V, window, n_recent;
     unsigned seed;
@@ -63,6 +79,16 @@ def rows():
     return out
 
 
+def first_rows():
+    """Rows for the engine's first sampler (``Sampler::sample``): (logits, temperature, seed)."""
+    rs = np.random.RandomState(78)
+    out = []
+    for k, temp in enumerate((0.0, 0.3, 0.8, 1.0, 1.7, 0.01, 5.0, 0.6)):
+        V = (33, 200)[k % 2]
+        out.append(((rs.standard_normal(V) * 2.0).astype(np.float32), temp, 500 + k))
+    return out
+
+
 def main():
     if len(sys.argv) != 2:
         sys.exit("usage: make_golden_sampler.py /path/to/reference  (a checkout of Maxritz/Nano_vLLM_cpp)")
@@ -72,17 +98,21 @@ def main():
         f.write(DRIVER)
     exe = os.path.join(work, "driver")
     subprocess.check_call(["g++", "-std=c++20", "-O2", f"-I{ref}/include", os.path.join(work, "driver.cpp"), "-o", exe])
-    cases = rows()
-    text = [str(len(cases))]
+    cases, first = rows(), first_rows()
+    text = [f"{len(cases)} {len(first)}"]
+    for logits, temp, seed in first:
+        text.append(f"{len(logits)} {temp!r} {seed}")
+        text.append(" ".join(f"{float(x)!r}" for x in logits))
     for logits, temp, top_p, pen, window, recent, seed in cases:
         text.append(f"{len(logits)} {temp!r} {top_p!r} {pen!r} {window} {seed} {len(recent)} " + " ".join(map(str, recent)))
         text.append(" ".join(f"{float(x)!r}" for x in logits))
     out = subprocess.run([exe], input="\n".join(text) + "\n", capture_output=True, text=True, check=True).stdout.split()
-    assert len(out) == 2 * len(cases)
-    result = [dict(u=float(out[2 * i]), token=int(out[2 * i + 1])) for i in range(len(cases))]
+    assert len(out) == 2 * (len(cases) + len(first))
+    pairs = [dict(u=float(out[2 * i]), token=int(out[2 * i + 1])) for i in range(len(cases) + len(first))]
+    result = dict(sample=pairs[:len(first)], sample_row=pairs[len(first):])
     with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "ref_sample_row.json"), "w") as f:
         json.dump(result, f)
-    print(len(result), "cases written")
+    print(len(first), "+", len(cases), "cases written")
 
 
 if __name__ == "__main__":

@@ -48,15 +48,18 @@ def test_plain_matches_reference_cpu(key, tmp_path):
             x = x + plain_model.dense_mlp(h, W, p + "mlp.")
 
 
-def test_plain_nucleus_sampler_matches_the_reference_cpu():
-    """plain_model.sample_row against the recorded choices of the reference's own ``sample_row``
-    (include/nanovllm/sampler.hpp:46-88, see tests/golden/make_golden_sampler.py) for the same rows, parameters
-    and uniform numbers."""
+def test_plain_samplers_match_the_reference_cpu():
+    """plain_model.sample and plain_model.sample_row against the recorded choices of the reference's own
+    ``Sampler::sample`` and ``sample_row`` (include/nanovllm/sampler.hpp, see tests/golden/make_golden_sampler.py)
+    for the same rows, parameters and uniform numbers."""
     import make_golden_sampler
     with open(os.path.join(HERE, "golden", "ref_sample_row.json")) as f:
         gold = json.load(f)
     rows = make_golden_sampler.rows()
-    assert len(rows) == len(gold)
-    for i, ((logits, temp, top_p, pen, window, recent, _), g) in enumerate(zip(rows, gold)):
+    first = make_golden_sampler.first_rows()
+    assert len(rows) == len(gold["sample_row"]) and len(first) == len(gold["sample"])
+    for i, ((logits, temp, _), g) in enumerate(zip(first, gold["sample"])):      # Sampler::sample, sampler.hpp:10-34
+        assert plain_model.sample(logits, temp, g["u"]) == g["token"], f"first sampler, case {i}"
+    for i, ((logits, temp, top_p, pen, window, recent, _), g) in enumerate(zip(rows, gold["sample_row"])):
         got = plain_model.sample_row(logits, temp, top_p, g["u"], recent, pen, window)
         assert got == g["token"], f"case {i}: temperature {temp}, top_p {top_p}, penalty {pen}, window {window}"
