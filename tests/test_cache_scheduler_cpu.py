@@ -491,3 +491,44 @@ def test_native_step_arrays_match_the_python_builder():
         m.prepare_step([StepEntry("x", list(range(40)), [])], 4, 30, False, buf)
     with pytest.raises(NoFreePages):
         m.prepare_step([StepEntry("x", list(range(16 * 9)), [])], 16, 1000, False, np.zeros(1024, dtype=np.int32))
+
+
+# ------------------------------------------------------------------------------- the reference's block manager
+@pytest.mark.parametrize("which", ["native", "plain"])
+def test_pages_handed_out_as_the_reference_block_manager_does(which):
+    """The scripted life of a few requests of tests/golden/make_golden_blocks.py on this engine's cache manager
+    (and on its plain restatement): cached pages on admission, every block table and the number of free pages
+    after every line equal what the reference's own BlockManager (src/block_manager.cpp) recorded."""
+    import json
+    import os
+    import sys
+    here = os.path.dirname(os.path.abspath(__file__))
+    sys.path.insert(0, os.path.join(here, "golden"))
+    import make_golden_blocks as G
+    import plain_host
+    with open(os.path.join(here, "golden", "ref_block_manager.json")) as f:
+        gold = json.load(f)
+    cls = CacheManager if which == "native" else plain_host.CacheManager
+    m = cls([0], G.PAGES, G.PAGE, max_requests=8, prefix_caching=True)
+    tokens = {}
+    for line, want in zip(G.SCRIPT, gold):
+        op, name = line[0], line[1]
+        if op == "admit":
+            tokens[name] = list(line[2])
+            matched = m.match_prefix(tokens[name])
+            assert len(matched) == want["cached_pages"], line
+            m.open(name)
+            cached = m.adopt_prefix(name, matched)
+            m.extend(name, cached, len(tokens[name]))
+            m.commit(name, len(tokens[name]), tokens[name])
+        elif op == "decode":
+            tokens[name].append(line[2])
+            n = len(tokens[name])
+            m.extend(name, n - 1, n)
+            m.commit(name, n, tokens[name])
+        else:
+            m.close(name)
+        m.check()
+        assert m.pools[0].num_free() == want["free"], line
+        if op != "end":
+            assert m.get(name).tables[0] == want["table"], line
