@@ -163,6 +163,18 @@ def main() -> int:
     margin = args.steps + args.warmup + 80
     need_tokens = biggest * (args.context + margin) + args.prefill_tokens + 64
     page = 16
+    # A run that would not fit comfortably is refused before anything is allocated (the full 57B shape holds
+    # 115 GB of weights: give it fewer --layers, which the line then names beside the full number).
+    H, D = cfg["hidden_size"], cfg["head_dim"]
+    per_layer = ((cfg["num_attention_heads"] + 2 * cfg["num_key_value_heads"]) * D * H + H * cfg["num_attention_heads"] * D
+                 + cfg["num_experts"] * (H + 3 * cfg["moe_intermediate_size"] * H)
+                 + 3 * cfg["shared_expert_intermediate_size"] * H + 3 * H)
+    need_bytes = 2 * (args.layers * per_layer + 2 * cfg["vocab_size"] * H) + kv_bytes(cfg, args.layers, [need_tokens])
+    free_bytes, _ = torch.cuda.mem_get_info()
+    if need_bytes > 0.7 * free_bytes:
+        print(f"bench.py: this run needs about {need_bytes / 1e9:.0f} GB of device memory and {free_bytes / 1e9:.0f} GB "
+              f"are free; run it with fewer --layers (now {args.layers})")
+        return 2
     eng = LLMEngine(work, max_model_len=max(args.context + margin, args.prefill_tokens) + 16, num_kv_blocks=(need_tokens + page - 1) // page,
                     dtype="bfloat16", random_weights=True, seed=seed, max_num_seqs=biggest + 1,
                     max_num_batched_tokens=max(args.prefill_tokens, biggest), enable_prefix_caching=False)
