@@ -126,6 +126,14 @@ class ErrorFlag:
 
 
 # ----------------------------------------------------------------------------- plain ops
+def random_fill(out, key: int, mean: float, std: float) -> None:
+    """``out[i] = mean + z_i * std`` with z_i a function of (key, i) alone (see weights/random_values.py, whose
+    host function gives the same bits)."""
+    _cuda_contig(out)
+    _check(lib().nv_random_fill(_p(out), c_int(dt(out)), c_longlong(out.numel()), ctypes.c_ulonglong(key & (2**64 - 1)),
+                                c_float(mean), c_float(std), _stream()), "random_fill")
+
+
 def embedding(ids, table, out, err: ErrorFlag, feed=None) -> None:
     """``feed``: int32 tokens that negative ids point into (id ``-(r + 1)`` reads ``feed[r]``)."""
     _cuda_contig(ids, table, out, feed)

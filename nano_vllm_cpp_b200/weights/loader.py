@@ -14,12 +14,12 @@ both runs, which is exact for either storage type.
 """
 from __future__ import annotations
 
-import hashlib
 import json
 import os
 
 import torch
 
+from .random_values import host_values, tensor_key
 from .safetensors_io import SafetensorsFolder, save_safetensors
 
 
@@ -78,15 +78,11 @@ class FolderSource:
         return t.to(device=self.device, dtype=_device_dtype(t.dtype, kind, self.run_dtype))
 
 
-def _name_seed(seed: int, name: str) -> int:
-    h = hashlib.sha256(f"{seed}:{name}".encode()).digest()
-    return int.from_bytes(h[:8], "little") & 0x7FFFFFFFFFFFFFFF
-
-
 class RandomSource:
-    """Random tensors drawn per name from (seed, name), so that the order of requests and the
-    presence of other tensors do not matter.  Matrices and biases are N(0, std); norm weights are
-    1 + N(0, norm_std).  Values are drawn in float32 and rounded once to ``store_dtype``."""
+    """Random tensors whose every value is a function of (seed, tensor name, element index): the order of
+    requests, the presence of other tensors and the device that draws them do not matter, and a tensor drawn on
+    the GPU has the bits of the one drawn on the CPU (see ``random_values``).  Matrices and biases are N(0, std);
+    norm weights are 1 + N(0, norm_std).  Values are made in float32 and rounded once to ``store_dtype``."""
 
     def __init__(self, specs: dict, seed: int, std: float, norm_std: float, device, store_dtype: torch.dtype,
                  run_dtype: torch.dtype | None = None):
@@ -97,19 +93,28 @@ class RandomSource:
     def has(self, name: str) -> bool:
         return name in self.specs
 
+    def _draw(self, name: str, shape, mean: float, std: float) -> torch.Tensor:
+        n = 1
+        for d in shape:
+            n *= int(d)
+        key = tensor_key(self.seed, name)
+        if self.device.type == "cuda":
+            from ..csrc import ops
+            t = torch.empty(tuple(shape), dtype=self.store_dtype, device=self.device)
+            ops.random_fill(t, key, mean, std)
+            return t
+        t = torch.from_numpy(host_values(key, n, mean, std)).reshape(tuple(shape))
+        return t.to(self.store_dtype)
+
     def stored(self, name: str) -> torch.Tensor:
         spec = self.specs[name]
-        g = torch.Generator(device=self.device)
-        g.manual_seed(_name_seed(self.seed, name))
         if spec.init == "zeros":
-            t = torch.zeros(spec.shape, dtype=torch.float32, device=self.device)
-        elif spec.init == "ones":
-            t = torch.ones(spec.shape, dtype=torch.float32, device=self.device)
+            return torch.zeros(spec.shape, dtype=self.store_dtype, device=self.device)
+        if spec.init == "ones":
             if self.norm_std > 0:
-                t += torch.randn(spec.shape, generator=g, dtype=torch.float32, device=self.device) * self.norm_std
-        else:
-            t = torch.randn(spec.shape, generator=g, dtype=torch.float32, device=self.device) * self.std
-        return t.to(self.store_dtype)
+                return self._draw(name, spec.shape, 1.0, self.norm_std)
+            return torch.ones(spec.shape, dtype=self.store_dtype, device=self.device)
+        return self._draw(name, spec.shape, 0.0, self.std)
 
     def get(self, name: str) -> torch.Tensor:
         t = self.stored(name)

@@ -189,6 +189,42 @@ def test_random_source_is_order_independent():
     assert all(torch.equal(a[n], b[n]) for n in names)
 
 
+def _value_by_hand(seed, name, i, mean, std):
+    """One value of the random-weights rule, restated with Python integers (64-bit wrap by masking)."""
+    import hashlib
+    import numpy as np
+    M = (1 << 64) - 1
+
+    def mix(z):
+        z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & M
+        z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & M
+        return z ^ (z >> 31)
+
+    key = int.from_bytes(hashlib.sha256(f"{seed}:{name}".encode()).digest()[:8], "little")
+    c = (key + i * 0x9E3779B97F4A7C15) & M
+    total = 0
+    for h in (mix(c), mix(c ^ 0xD6E8FEB86659FD93), mix(c ^ 0xA0761D6478BD642F)):
+        total += (h & 0xFFFF) + ((h >> 16) & 0xFFFF) + ((h >> 32) & 0xFFFF) + (h >> 48)
+    z = np.float32(total - 393210) * np.float32(2.0 ** -16)
+    return np.float32(mean) + z * np.float32(std)
+
+
+def test_random_values_follow_the_stated_rule():
+    """Every value is a function of (seed, name, element index); mean 0 and variance 1 before scaling."""
+    import numpy as np
+    from nano_vllm_cpp_b200.weights.random_values import host_values, tensor_key
+    key = tensor_key(5, "model.layers.1.mlp.gate.weight")
+    v = host_values(key, 5_000_003, 0.0, 1.0)             # more than one chunk of the host loop
+    for i in (0, 1, 17, 4_194_303, 4_194_304, 5_000_002):
+        assert v[i] == _value_by_hand(5, "model.layers.1.mlp.gate.weight", i, 0.0, 1.0)
+    assert abs(float(v.mean())) < 2e-3 and abs(float(v.std()) - 1.0) < 2e-3
+    assert abs(float(np.mean(v ** 4)) - 2.9) < 0.05        # twelve uniforms: kurtosis 3 - 0.1
+    w = host_values(key, 1000, 1.0, 0.1)
+    assert w[5] == _value_by_hand(5, "model.layers.1.mlp.gate.weight", 5, 1.0, 0.1)
+    assert not np.array_equal(host_values(tensor_key(6, "model.layers.1.mlp.gate.weight"), 1000, 0.0, 1.0), v[:1000])
+    assert not np.array_equal(host_values(tensor_key(5, "model.layers.0.mlp.gate.weight"), 1000, 0.0, 1.0), v[:1000])
+
+
 def test_sampling_params_are_checked():
     from nano_vllm_cpp_b200 import SamplingParams
     SamplingParams(temperature=0.0, top_p=0.0, repetition_penalty=1.3, repetition_window=0).validate()

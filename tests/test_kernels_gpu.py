@@ -28,6 +28,32 @@ def close(got, want, rel, what=""):
     assert err <= bound, f"{what}: max error {err:.3g} > {bound:.3g}"
 
 
+# ------------------------------------------------------------------------------- random weights
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n,mean,std", [(1, 0.0, 0.02), (4099, 0.0, 0.05), (5_000_003, 0.0, 0.02), (3584, 1.0, 0.1)])
+def test_random_fill_has_the_bits_of_the_host_rule(dtype, n, mean, std):
+    """A tensor drawn on the device equals the one numpy draws on the host, bit for bit."""
+    from nano_vllm_cpp_b200.weights.random_values import host_values, tensor_key
+    key = tensor_key(9, f"some.tensor.{n}")
+    out = torch.empty(n, dtype=dtype, device=DEV)
+    ops().random_fill(out, key, mean, std)
+    want = torch.from_numpy(host_values(key, n, mean, std)).to(dtype)
+    assert torch.equal(out.cpu(), want)
+
+
+def test_random_source_draws_the_same_model_on_both_devices():
+    from nano_vllm_cpp_b200.config.registry import get_architecture
+    from nano_vllm_cpp_b200.parts import Model
+    from nano_vllm_cpp_b200.weights import RandomSource
+    import helpers
+    arch = get_architecture("Qwen2MoeForCausalLM")
+    specs = Model(arch.build_model(arch.config_from_dict(helpers.CASES["B"]["config"]))).tensor_specs()
+    host = RandomSource(specs, 3, 0.05, 0.1, "cpu", torch.bfloat16)
+    dev = RandomSource(specs, 3, 0.05, 0.1, DEV, torch.bfloat16)
+    for name in specs:
+        assert torch.equal(dev.stored(name).cpu(), host.stored(name)), name
+
+
 # ------------------------------------------------------------------------------- embedding, norm
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_embedding(dtype):
