@@ -7,8 +7,14 @@ Default run: the layer sizes of the Qwen1.5-MoE-A2.7B shape with random bfloat16
 of 8 sequences each at a 2,048-token context; a step is one decode step of that batch.  ``value``
 is decoded tokens per second timed on the device; ``e2e`` is the same through
 ``LLMEngine.step`` with host token ids in and out; ``prefill`` times one 2,048-token prompt;
-``points`` holds decode at batch 1 and 64; ``roofline`` compares the bytes a decode step has to
-read (every weight it uses once, the cache of the live requests) with the measured copy bandwidth.
+``points`` holds decode at batch 1 and 64 and a mixed step (64 single rows beside a 512-token portion of a
+prompt); ``roofline`` compares the bytes a decode step has to read (every weight it uses once, the cache of
+the live requests) with the measured copy bandwidth.  A decode step here is the whole step: the model, the
+sampling kernel behind it, and the next step reading the drawn tokens on the device.
+
+``--kernel-times`` adds ``kernels``: per kernel class of one decode step and of the prompt, CUDA-event time,
+calls and the fraction of the measured peak its bytes (decode) or flops (prompt) come to.  Those steps run
+outside CUDA graphs, one kernel after the other, so their sum is more than the step's own time.
 """
 from __future__ import annotations
 
@@ -42,6 +48,7 @@ SHAPES = {
         intermediate_size=18944, max_position_embeddings=32768), 28, 4),
 }
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+MIXED_ROWS, MIXED_PORTION = 64, 512      # the mixed point: this many single rows beside a portion of this many tokens
 
 
 def peaks():
@@ -117,6 +124,78 @@ def prefill_flops(cfg, layers, T):
     return layers * (per_tok * T + attn) + 2 * cfg["vocab_size"] * H
 
 
+def kernel_times(runner, cfg, args, P, fill_context, StepEntry, ops, torch, g, V):
+    """Per kernel class: CUDA-event time of one decode step at the default batch and of the prompt, run outside
+    CUDA graphs.  What each class must move or compute comes from the launcher where it knows it (dense products) and
+    from the configuration otherwise (attention, expert products)."""
+    L, H, D = args.layers, cfg["hidden_size"], cfg["head_dim"]
+    I, E, K = cfg["moe_intermediate_size"], cfg["num_experts"], cfg["num_experts_per_tok"]
+    C = cfg["shared_expert_intermediate_size"] // I
+    graphs, runner.cuda_graphs = runner.cuda_graphs, False
+    out = []
+
+    def rows_of(kt, steps, what, flops_of, bytes_of):
+        for r in kt.summary()[:7]:
+            ms = r["ms"] / steps
+            nb = bytes_of(r) / steps
+            fl = flops_of(r) / steps
+            row = {"step": what, "name": r["name"], "calls": r["calls"] // steps, "ms": round(ms, 4)}
+            if what == "decode" and nb:
+                row["frac_hbm"] = round(nb / (ms * 1e-3) / (P["hbm_gbs"] * 1e9), 3)
+            if what == "prefill" and fl:
+                row["frac_bf16"] = round(fl / (ms * 1e-3) / (P["bf16_tflops"] * 1e12), 3)
+            out.append(row)
+
+    try:
+        B = args.batch
+        rids = fill_context(B)
+        toks = torch.randint(0, V, (B,), generator=g).tolist()
+        entries = [StepEntry(r, [t], [0]) for r, t in zip(rids, toks)]
+        for _ in range(3):
+            runner.step(entries, check=False)
+        steps = 4
+        with ops.KernelTimes() as kt:
+            for _ in range(steps):
+                runner.step(entries, check=False)
+        ctx_tokens = sum(runner.num_cached(r) for r in rids)
+        distinct = [int((p.last_alignment.counts[:E] > 0).sum()) for p in
+                    (l.feed_forward for l in runner.model.layers) if getattr(p, "last_alignment", None) is not None]
+        per_layer_experts = (sum(distinct) / max(1, len(distinct)) + C) * steps * L
+
+        def dec_bytes(r):
+            if r["name"] == "attention_decode":
+                return steps * L * ctx_tokens * 2 * cfg["num_key_value_heads"] * D * 2
+            if r["name"].startswith("tc_gemm_grouped"):
+                n = int(r["name"].split("N=")[1].split()[0])
+                return per_layer_experts * n * (H if n == 2 * I else I) * 2
+            return r["bytes"]
+
+        rows_of(kt, steps, "decode", lambda r: 0.0, dec_bytes)
+        for r in rids:
+            runner.close(r)
+        T = args.prefill_tokens
+        ids = torch.randint(0, V, (T,), generator=g).tolist()
+        for _ in range(2):
+            runner.step([StepEntry("kt", ids, [T - 1])], check=False)
+            runner.close("kt")
+        with ops.KernelTimes() as kt:
+            runner.step([StepEntry("kt", ids, [T - 1])], check=False)
+        runner.close("kt")
+
+        def pf_flops(r):
+            if r["name"].startswith("attention_prefill"):
+                return L * 4 * cfg["num_attention_heads"] * D * (T * (T + 1) // 2)
+            if r["name"].startswith("tc_gemm_grouped"):
+                n = int(r["name"].split("N=")[1].split()[0])
+                return L * 2.0 * T * (K + C) * n * (H if n == 2 * I else I)
+            return r["flops"]
+
+        rows_of(kt, 1, "prefill", pf_flops, lambda r: 0.0)
+    finally:
+        runner.cuda_graphs = graphs
+    return out
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -131,6 +210,7 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-prefill", action="store_true")
+    ap.add_argument("--kernel-times", action="store_true", help="add per-kernel-class CUDA-event times to the line")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -161,7 +241,7 @@ def main() -> int:
 
     biggest = max(args.batch, 1 if args.no_points else 64)
     margin = args.steps + args.warmup + 80
-    need_tokens = biggest * (args.context + margin) + args.prefill_tokens + 64
+    need_tokens = biggest * (args.context + margin) + args.prefill_tokens + MIXED_PORTION + 128
     page = 16
     # A run that would not fit comfortably is refused before anything is allocated (the full 57B shape holds
     # 115 GB of weights: give it fewer --layers, which the line then names beside the full number).
@@ -171,7 +251,7 @@ def main() -> int:
                  + 3 * cfg["shared_expert_intermediate_size"] * H + 3 * H)
     need_bytes = 2 * (args.layers * per_layer + 2 * cfg["vocab_size"] * H) + kv_bytes(cfg, args.layers, [need_tokens])
     free_bytes, _ = torch.cuda.mem_get_info()
-    if need_bytes > 0.7 * free_bytes:
+    if need_bytes > 0.85 * free_bytes:
         print(f"bench.py: this run needs about {need_bytes / 1e9:.0f} GB of device memory and {free_bytes / 1e9:.0f} GB "
               f"are free; run it with fewer --layers (now {args.layers})")
         return 2
@@ -225,19 +305,24 @@ def main() -> int:
         return [l.feed_forward for l in runner.model.layers if hasattr(l.feed_forward, "last_alignment")]
 
     def decode_device(B, steps, warmup):
+        """Whole decode steps: model, sampling kernel, and the next step's ids read from the tokens just drawn."""
         rids = fill_context(B)
         toks = torch.randint(0, V, (B,), generator=g).tolist()
+        temps, us = [0.0] * B, [0.0] * B
         launches0 = 0
         a, b = ev(), ev()
+        handle = None
         for it in range(warmup + steps):
             if it == warmup:
                 torch.cuda.synchronize()
                 launches0 = ops.launch_count()
                 a.record()
-            runner.step([StepEntry(r, [t], [0]) for r, t in zip(rids, toks)], check=False)
+            ids = toks if it == 0 else [-(r + 1) for r in range(B)]      # row r reads the token drawn for row r
+            handle = runner.launch_tokens([StepEntry(r, [t], [0]) for r, t in zip(rids, ids)], temps, us)
         b.record()
         torch.cuda.synchronize()
         launches = ops.launch_count() - launches0
+        runner.collect(handle)
         runner.ctx.err.check("decode")
         ms = a.elapsed_time(b) / steps
         distinct = [int((p.last_alignment.counts[:cfg["num_experts"]] > 0).sum()) for p in moe_parts()
@@ -246,6 +331,41 @@ def main() -> int:
         for r in rids:
             runner.close(r)
         return ms, launches, distinct, ctxs
+
+    def mixed_device(steps, warmup):
+        """MIXED_ROWS single rows at the decode context beside the first MIXED_PORTION tokens of a new prompt."""
+        rids = fill_context(MIXED_ROWS)
+        toks = torch.randint(0, V, (MIXED_ROWS,), generator=g).tolist()
+        portion = torch.randint(0, V, (MIXED_PORTION,), generator=g).tolist()
+        a, b = ev(), ev()
+        for it in range(warmup + steps):
+            if it == warmup:
+                torch.cuda.synchronize()
+                a.record()
+            entries = [StepEntry(r, [t], [0]) for r, t in zip(rids, toks)]
+            entries.append(StepEntry(f"mx{it}", portion, [MIXED_PORTION - 1]))
+            runner.step(entries, check=False)
+            runner.close(f"mx{it}")
+        b.record()
+        torch.cuda.synchronize()
+        runner.ctx.err.check("mixed step")
+        ms = a.elapsed_time(b) / steps
+        distinct = [int((p.last_alignment.counts[:cfg["num_experts"]] > 0).sum()) for p in moe_parts()
+                    if p.last_alignment is not None]
+        ctxs = [runner.num_cached(r) for r in rids]
+        for r in rids:
+            runner.close(r)
+        # the portion alone, for comparison
+        c, d = ev(), ev()
+        for it in range(warmup + steps):
+            if it == warmup:
+                torch.cuda.synchronize()
+                c.record()
+            runner.step([StepEntry("mxa", portion, [MIXED_PORTION - 1])], check=False)
+            runner.close("mxa")
+        d.record()
+        torch.cuda.synchronize()
+        return ms, c.elapsed_time(d) / steps, distinct, ctxs
 
     clocks = ClockSampler()
     clocks.start()
@@ -286,11 +406,26 @@ def main() -> int:
         while not eng.is_finished():      # let them run out (a few more steps)
             eng.step()
 
-    points = {}
+    points, mixed = {}, None
     if not args.no_points:
+        ms_b64 = None
         for B in (1, 64):
             pms, _, _, _ = decode_device(B, max(8, args.steps // 2), args.warmup)
             points[f"decode_b{B}"] = round(B / pms * 1e3, 1)
+            ms_b64 = pms
+        mms, portion_ms, mdistinct, mctxs = mixed_device(max(6, args.steps // 4), args.warmup)
+        mbytes = weight_bytes(cfg, args.layers, mdistinct) + kv_bytes(cfg, args.layers, mctxs)
+        mflops = prefill_flops(cfg, args.layers, MIXED_PORTION)
+        # the step can be no faster than its reads and no faster than its products: the larger of the two times
+        floor_ms = max(mbytes / (P["hbm_gbs"] * 1e9), mflops / (P["bf16_tflops"] * 1e12)) * 1e3
+        points["mixed_b64_p512"] = round((MIXED_ROWS + MIXED_PORTION) / mms * 1e3, 1)
+        mixed = {"rows": MIXED_ROWS, "portion": MIXED_PORTION, "ms": round(mms, 3), "decode_b64_ms": round(ms_b64, 3),
+                 "portion_alone_ms": round(portion_ms, 3), "frac": round(floor_ms / mms, 4),
+                 "bound": "max(hbm bytes, bf16 flops)"}
+
+    kernels = None
+    if args.kernel_times:
+        kernels = kernel_times(runner, cfg, args, P, fill_context, StepEntry, ops, torch, g, V)
 
     line = {
         "metric": f"decode tok/s (batch {args.batch}, {args.context:,}-token context); "
@@ -307,13 +442,18 @@ def main() -> int:
                    "moe_intermediate_size": cfg["moe_intermediate_size"],
                    "shared_expert_intermediate_size": cfg["shared_expert_intermediate_size"],
                    "vocab_size": cfg["vocab_size"], "page_size": page, "prefill_tokens": args.prefill_tokens,
-                   "l2": "inputs larger than L2 (weights and cache read per step exceed 126 MB)"},
+                   "l2": "inputs larger than L2 (weights and cache read per step exceed 126 MB)",
+                   "step": "model + sampling kernel; ids fed back on the device"},
         "clocks": clk, "gpu_launches": launches, "roofline": roofline,
     }
     if prefill is not None:
         line["prefill"] = prefill
     if points:
         line["points"] = points
+    if mixed is not None:
+        line["mixed"] = mixed
+    if kernels is not None:
+        line["kernels"] = kernels
     if e2e is not None:
         line["e2e"] = e2e
     print(json.dumps(line))

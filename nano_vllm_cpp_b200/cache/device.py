@@ -78,8 +78,16 @@ class DeviceCache:
     def view(self, call_index: int) -> CacheView:
         return self.views[call_index]
 
-    def reset_slot(self, slot: int) -> None:
-        """A request has just been given this slot: its states start from zero."""
+    @property
+    def has_state(self) -> bool:
+        return any(isinstance(s, StateCacheSpec) for s in self.specs)
+
+    def reset_fresh(self, batch) -> None:
+        """Before a step runs: the state of every entry that starts its request (first position 0) is zeroed, on
+        the device, from the step's own index arrays.  A request therefore begins from zero whoever held its slot
+        before, also after a preemption (it runs again from its first token), and a captured step does the same
+        when it is replayed."""
+        from ..csrc import ops
         for v in self.views:
-            if v.kind == "state" and v.write:
-                v.state[slot].zero_()
+            if v is not None and v.kind == "state" and v.write:
+                ops.reset_fresh_state(v.state, batch.entry_slot, batch.entry_pos0)

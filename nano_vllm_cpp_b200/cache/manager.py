@@ -67,9 +67,11 @@ class RequestCache:
 
 class CacheManager:
     def __init__(self, windows: list, num_pages, page_size: int, max_requests: int,
-                 prefix_caching: bool = False):
-        """``windows``: one entry per group (0 = reads every key).  ``num_pages``: an int for all
-        groups or a list."""
+                 prefix_caching: bool = False, has_state: bool = False):
+        """``windows``: one entry per group (0 = reads every key); it may be empty for a model without paged
+        layers, whose requests hold a state slot and nothing else.  ``num_pages``: an int for all groups or a
+        list.  ``has_state``: some layer keeps a fixed-size state per request; prefix sharing is then refused
+        (a request that adopted another's pages would skip tokens its state never saw)."""
         if isinstance(num_pages, int):
             num_pages = [num_pages] * len(windows)
         self.windows = list(windows)
@@ -79,7 +81,8 @@ class CacheManager:
         w, _ = host.ints(self.windows)
         n, _ = host.ints(list(num_pages))
         L = host.lib()
-        self._h = L.nvh_manager_create(w, n, self.num_groups, page_size, max_requests, 1 if prefix_caching else 0)
+        self._h = L.nvh_manager_create(w, n, self.num_groups, page_size, max_requests, 1 if prefix_caching else 0,
+                                       1 if has_state else 0)
         self.pools = [BlockPool(num_pages[g], page_size, _handle=L.nvh_manager_pool(self._h, g))
                       for g in range(self.num_groups)]
         self.prefix_caching = bool(L.nvh_manager_prefix_caching(self._h))

@@ -4,6 +4,7 @@
     nanovllm <model_dir> --tokens 1,2,3 [--max-tokens N] [--temperature T] [--max-model-len N]
                          [--num-kv-blocks N]
     nanovllm --bench <model_dir> [--num-seqs N] [--max-tokens N] [--max-model-len N]
+    nanovllm --config config.json [--seed S] --tokens 1,2,3 ...      (random weights, no model folder)
 
 The prompt is given as token ids (``--tokens``); this engine has no tokenizer, so a text prompt
 is refused.  ``--chat`` and ``--server`` belong to parts of the reference that are not built
@@ -22,7 +23,8 @@ import time
 
 USAGE = """Usage: nanovllm <model_dir> --tokens 1,2,3 [--max-tokens N] [--temperature T] [--max-model-len N]
        nanovllm --bench <model_dir> [--num-seqs N] [--max-tokens N] [--max-model-len N]
-  further options: --num-kv-blocks N  --dtype bfloat16|float32  --random-weights  --seed S
+       nanovllm --config <config.json> [--seed S] --tokens 1,2,3 ...   (random weights, no model folder)
+  further options: --num-kv-blocks N  --dtype bfloat16|float32 (or bf16|fp32)  --random-weights  --seed S
                    --page-size N  --prefill-chunk N  --max-num-batched-tokens N  --max-num-seqs N
                    --eos ID  --ignore-eos  --expert-budget GB (ignored)
                    --top-p P  --rep-penalty THETA  --rep-window W   (nucleus sampling and repetition penalty)
@@ -65,7 +67,7 @@ def main(argv=None) -> int:
     opt = dict(model_dir="", prompt="", prompt_ids=[], max_tokens=64, temperature=0.6, max_model_len=4096,
                bench=False, num_seqs=4, num_kv_blocks=0, dtype="bfloat16", random_weights=False, seed=0,
                page_size=16, prefill_chunk=0, max_num_batched_tokens=16384, max_num_seqs=512, eos=-1,
-               ignore_eos=False, top_p=1.0, rep_penalty=1.0, rep_window=64)
+               ignore_eos=False, top_p=1.0, rep_penalty=1.0, rep_window=64, config="")
     with_value = {"--tokens": ("prompt_ids", parse_ids), "--max-tokens": ("max_tokens", int),
                   "--temperature": ("temperature", float), "--max-model-len": ("max_model_len", int),
                   "--num-kv-blocks": ("num_kv_blocks", int), "--expert-budget": (None, float),
@@ -73,7 +75,8 @@ def main(argv=None) -> int:
                   "--page-size": ("page_size", int), "--prefill-chunk": ("prefill_chunk", int),
                   "--max-num-batched-tokens": ("max_num_batched_tokens", int),
                   "--max-num-seqs": ("max_num_seqs", int), "--eos": ("eos", int), "--top-p": ("top_p", float),
-                  "--rep-penalty": ("rep_penalty", float), "--rep-window": ("rep_window", int)}
+                  "--rep-penalty": ("rep_penalty", float), "--rep-window": ("rep_window", int),
+                  "--config": ("config", str)}
     i = 0
     given = set()
     try:
@@ -108,17 +111,33 @@ def main(argv=None) -> int:
     except ValueError as e:
         sys.stderr.write(f"Error: bad option value: {e}\n")
         return 1
-    if not opt["model_dir"]:
+    if opt["config"] and opt["model_dir"] and not opt["prompt"]:
+        # with --config there is no model folder: a positional argument is the (text) prompt
+        opt["prompt"], opt["model_dir"] = opt["model_dir"], ""
+    if not opt["model_dir"] and not opt["config"]:
         sys.stderr.write(USAGE)
         return 1
     for key, value in generation_defaults(opt["model_dir"]).items():
         if key not in given:                  # explicit options win
             opt[key] = value
     try:
+        if opt["config"]:
+            return _run_from_config(opt)
         return _run(opt)
     except Exception as e:  # src/main.cpp:432-438
         sys.stderr.write(f"Error: {e}\n")
         return 2
+
+
+def _run_from_config(opt) -> int:
+    """``--config <json>``: a run with random weights (drawn from ``--seed``) of the model that the file describes,
+    without a model folder: the file becomes the ``config.json`` of a temporary one."""
+    import os
+    import shutil
+    import tempfile
+    with tempfile.TemporaryDirectory(prefix="nanovllm_config_") as d:
+        shutil.copyfile(opt["config"], os.path.join(d, "config.json"))
+        return _run(dict(opt, model_dir=d, random_weights=True))
 
 
 def _run(opt) -> int:

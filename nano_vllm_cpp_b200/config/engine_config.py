@@ -23,8 +23,10 @@ class EngineConfig:
     cuda_graphs: bool = True
     run_ahead: bool = True                # launch a step before the host has read the tokens of the one before
     device: str = "cuda:0"
+    log_stats: bool = True                # at start-up, on stderr: device memory after loading, size of the page pool
 
     def validate(self) -> None:
+        self.dtype = {"bf16": "bfloat16", "fp32": "float32"}.get(self.dtype, self.dtype)
         if self.kvcache_block_size <= 0 or self.kvcache_block_size % 16:
             raise ValueError("kvcache_block_size must be a positive multiple of 16")
         if self.max_num_batched_tokens < 1:
@@ -34,7 +36,7 @@ class EngineConfig:
         if self.max_model_len < 1:
             raise ValueError("max_model_len must be positive")
         if self.dtype not in ("bfloat16", "float32"):
-            raise ValueError("dtype must be 'bfloat16' or 'float32'")
+            raise ValueError("dtype must be 'bfloat16' (or 'bf16') or 'float32' (or 'fp32')")
         if not (0.0 < self.gpu_memory_utilization <= 1.0):
             raise ValueError("gpu_memory_utilization must lie in (0, 1]")
 

@@ -635,7 +635,6 @@ int launch_decode_tc(DecArgs a, int R, const void* kc, const void* vc, int num_p
 // 64 KB (two CTAs per SM and more), at least 2 within 160 KB, else 0 (refused).
 int decode_stages(int page, int D, int esize) {
   const long long stage = 2LL * page * D * esize;
-  if (const char* e = getenv("NV_DEC_STAGES")) return atoi(e);      // experiments only
   long long s = (64 * 1024) / stage;
   if (s >= 2) return (int)(s > MAX_STAGES ? MAX_STAGES : s);
   return 2 * stage <= 160 * 1024 ? 2 : 0;
@@ -658,7 +657,6 @@ NV_API int nv_attention_decode_usable(int D, int page, int cache_dt) {
 // wave of resident blocks is: the split count whose blocks fill whole waves best wins, with a small price per
 // split for its start-up and the merge.  Three blocks of the kernel live on a multiprocessor.
 NV_API int nv_attention_decode_splits(int rows, int Hq, int Hkv, int max_context, int num_sms) {
-  if (const char* e = getenv("NV_DEC_SPLITS")) return atoi(e);      // experiments only
   const int G = Hq / Hkv;
   const long long slots = 3LL * num_sms;
   const long long blocks = (long long)rows * Hkv * ((G + 15) / 16);
@@ -706,8 +704,7 @@ NV_API int nv_attention_decode(const void* qkv, int q_dt, int q_stride, const vo
   // next page is on its way while it works on one (with one stage per warp a warp sat out the whole memory latency
   // between two pages), and three CTAs of 76 KB still share a multiprocessor.  Deeper rings lose CTAs and time.
   int tc_stages = stages / WARPS * WARPS;
-  if (cache_dt == NV_DT_BF16 && D % 64 == 0 && page <= 256 && num_pages > 0 && tc_stages >= WARPS &&
-      !getenv("NV_DECODE_ATTENTION_SIMT")) {
+  if (cache_dt == NV_DT_BF16 && D % 64 == 0 && page <= 256 && num_pages > 0 && tc_stages >= WARPS) {
     a.stages = tc_stages;
     // tensor-core form (a page of keys per warp); its blocks take up to 16 query heads of a kv head
     rc = D == 64 ? launch_decode_tc<64>(a, R, kc, vc, num_pages, scale, stream)

@@ -29,6 +29,7 @@ struct PfArgs {
   bf16* out;
   float scale_log2;         // scale * log2(e)
   int S, q_stride, max_blocks, window, Hq, Hkv, D, page;
+  int min_rows;             // entries with fewer rows are left to another kernel
 };
 
 __device__ __forceinline__ uint32_t s_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -79,7 +80,7 @@ __global__ void __launch_bounds__(BM * 2, DP <= 128 ? 2 : 1) attention_prefill_k
     int left = (int)(gridDim.x - 1 - blockIdx.x), e = 0, found = -1;
     for (; e < a.S; ++e) {
       int n = a.cu_rows[e + 1] - a.cu_rows[e];
-      int tiles = (n + BM - 1) / BM;
+      int tiles = n >= a.min_rows ? (n + BM - 1) / BM : 0;
       if (left < tiles) { found = e; break; }
       left -= tiles;
     }
@@ -315,9 +316,7 @@ int launch_prefill_bm(const PfArgs& a, int max_tiles, cudaStream_t s) {
 // with half the warps: measured slower (a 2,048-token prompt: 21.7 against 20.5 ms), so 128 it is.
 template <int DP>
 int launch_prefill(const PfArgs& a, int max_tiles64, int num_sms, cudaStream_t s) {
-  const char* force = getenv("NV_PREFILL_TILE");        // experiments only
   (void)num_sms;
-  if (force && atoi(force) == 64) return launch_prefill_bm<DP, 64>(a, max_tiles64, s);
   return launch_prefill_bm<DP, 128>(a, max_tiles64, s);
 }
 
@@ -325,12 +324,14 @@ int launch_prefill(const PfArgs& a, int max_tiles64, int num_sms, cudaStream_t s
 
 // bfloat16 only; head_dim a multiple of 16 up to 256.  `max_tiles` >= sum over entries of
 // ceil(rows / nv_attention_prefill_tile_rows()), the smallest tile the launcher may choose; surplus CTAs leave at once.
+// Entries with fewer than `min_rows` rows are skipped (their rows of `out` stay untouched): in a mixed step the
+// single rows go to the decode kernel.
 NV_API int nv_attention_prefill_tile_rows() { return 64; }
 
 NV_API int nv_attention_prefill(const void* qkv, int q_stride, const void* kc, const void* vc,
                                 const int* block_table, int max_blocks, const int* cu_rows, const int* entry_pos0,
                                 int S, int max_tiles, float scale, int window, void* out, int Hq, int Hkv, int D,
-                                int page, cudaStream_t stream) {
+                                int page, int min_rows, cudaStream_t stream) {
   if (D <= 0 || D > 256 || D % 16 || Hkv <= 0 || Hq % Hkv) return NV_ERR_UNSUPPORTED;
   if (q_stride % 8 || ((uintptr_t)qkv & 15) || ((uintptr_t)kc & 15) || ((uintptr_t)vc & 15)) return NV_ERR_UNSUPPORTED;
   if (S == 0 || max_tiles == 0) return NV_OK;
@@ -340,6 +341,7 @@ NV_API int nv_attention_prefill(const void* qkv, int q_stride, const void* kc, c
   a.scale_log2 = scale * 1.4426950408889634f;
   a.S = S; a.q_stride = q_stride; a.max_blocks = max_blocks; a.window = window; a.Hq = Hq; a.Hkv = Hkv; a.D = D;
   a.page = page;
+  a.min_rows = min_rows;
   static int num_sms = 0;
   if (!num_sms) {
     int dev = 0;

@@ -40,6 +40,7 @@ struct PtArgs {
   int* err;
   float scale_log2;         // scale * log2(e)
   int S, max_blocks, window, Hq, Hkv, page;
+  int min_rows;             // entries with fewer rows are left to another kernel
 };
 
 // 2^x by the special-function unit; exp2(-inf) = 0.
@@ -97,7 +98,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
     int left = (int)(gridDim.x - 1 - blockIdx.x), e = 0, found = -1;
     for (; e < a.S; ++e) {
       const int n = a.cu_rows[e + 1] - a.cu_rows[e];
-      const int tiles = (n + TQ - 1) / TQ;
+      const int tiles = n >= a.min_rows ? (n + TQ - 1) / TQ : 0;
       if (left < tiles) { found = e; break; }
       left -= tiles;
     }
@@ -344,7 +345,6 @@ int launch_prefill_tc(const PtArgs& a, const void* qkv, int q_stride, int T, con
 }  // namespace
 
 NV_API int nv_attention_prefill_tc_usable(int D, int page) {
-  if (getenv("NV_PREFILL_LEGACY")) return 0;           // experiments only
   return (D == 64 || D == 128) && (page == 16 || page == 32 || page == 64);
 }
 
@@ -355,7 +355,7 @@ NV_API int nv_attention_prefill_tc_usable(int D, int page) {
 NV_API int nv_attention_prefill_tc(const void* qkv, int q_stride, int T, const void* kc, const void* vc, int num_pages,
                                    const int* block_table, int max_blocks, const int* cu_rows, const int* entry_pos0,
                                    int S, int max_tiles, float scale, int window, void* out, int Hq, int Hkv, int D,
-                                   int page, int* err, cudaStream_t stream) {
+                                   int page, int min_rows, int* err, cudaStream_t stream) {
   if (!nv_attention_prefill_tc_usable(D, page) || Hkv <= 0 || Hq % Hkv) return NV_ERR_UNSUPPORTED;
   if (q_stride % 8 || ((uintptr_t)qkv & 15) || ((uintptr_t)kc & 15) || ((uintptr_t)vc & 15)) return NV_ERR_UNSUPPORTED;
   if (S == 0 || max_tiles == 0 || T == 0) return NV_OK;
@@ -363,6 +363,7 @@ NV_API int nv_attention_prefill_tc(const void* qkv, int q_stride, int T, const v
   a.block_table = block_table; a.cu_rows = cu_rows; a.entry_pos0 = entry_pos0; a.out = (bf16*)out; a.err = err;
   a.scale_log2 = scale * 1.4426950408889634f;
   a.S = S; a.max_blocks = max_blocks; a.window = window; a.Hq = Hq; a.Hkv = Hkv; a.page = page;
+  a.min_rows = min_rows;
   const int tiles = (max_tiles + S + 1) / 2;
   if (D == 64) return launch_prefill_tc<64>(a, qkv, q_stride, T, kc, vc, num_pages, tiles, stream);
   return launch_prefill_tc<128>(a, qkv, q_stride, T, kc, vc, num_pages, tiles, stream);

@@ -29,7 +29,7 @@ _PROTOS = {
     "nvh_pool_lookup": (c_int, [c_void_p, c_uint64, _IP, c_int]),
     "nvh_pool_set_hash": (None, [c_void_p, c_int, c_uint64, _IP, c_int]),
     "nvh_pool_check": (c_int, [c_void_p, _IP]),
-    "nvh_manager_create": (c_void_p, [_IP, _IP, c_int, c_int, c_int, c_int]),
+    "nvh_manager_create": (c_void_p, [_IP, _IP, c_int, c_int, c_int, c_int, c_int]),
     "nvh_manager_destroy": (None, [c_void_p]),
     "nvh_manager_pool": (c_void_p, [c_void_p, c_int]),
     "nvh_manager_groups": (c_int, [c_void_p]),

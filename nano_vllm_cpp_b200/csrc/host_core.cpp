@@ -171,11 +171,15 @@ class CacheManager {
   std::unordered_map<int64_t, RequestCache> requests;
   bool prefix_caching;
 
-  CacheManager(const int* w, const int* n_pages, int groups, int ps, int max_req, bool prefix)
+  // `has_state`: some layer keeps a fixed-size state per request instead of (or beside) pages.  Such a state has
+  // seen every token of its request, so a request must never skip tokens that another request's pages hold:
+  // prefix sharing is refused then, as it is for more than one group or a window.  `groups` may be 0 (a model
+  // without paged layers): requests then hold a state slot and nothing else.
+  CacheManager(const int* w, const int* n_pages, int groups, int ps, int max_req, bool prefix, bool has_state)
       : windows(w, w + groups), page_size(ps), max_requests(max_req) {
     for (int g = 0; g < groups; ++g) pools.emplace_back(n_pages[g], ps);
     for (int s = max_req - 1; s >= 0; --s) free_slots.push_back(s);
-    prefix_caching = prefix && groups == 1 && windows[0] == 0;
+    prefix_caching = prefix && !has_state && groups == 1 && windows[0] == 0;
   }
   RequestCache* find(int64_t rid) {
     auto it = requests.find(rid);
@@ -302,6 +306,8 @@ class CacheManager {
   int adopt_prefix(int64_t rid, const int* pages, const uint64_t* hashes, int n) {
     RequestCache* rc = find(rid);
     if (!rc) return fail(ERR_STATE, "request is not open");
+    if (n == 0) return rc->num_tokens;
+    if (!prefix_caching) return fail(ERR_STATE, "adopt_prefix: this manager shares no pages");
     if (rc->num_tokens || !rc->tables[0].empty()) return fail(ERR_STATE, "adopt_prefix on a request that already holds pages");
     for (int i = 0; i < n; ++i) {
       int r = pools[0].share(pages[i]);
@@ -448,7 +454,7 @@ class Scheduler {
         const int cap = prefill_chunk ? prefill_chunk : budget;
         const int first = std::min(std::min(n_tok - matched * m->page_size, budget), cap);
         const int end = matched * m->page_size + first;
-        bool fits = m->new_pages_for(end, pages.data(), matched) <= m->pools[0].n_free;
+        bool fits = m->pools.empty() || m->new_pages_for(end, pages.data(), matched) <= m->pools[0].n_free;
         for (size_t g = 1; g < m->pools.size() && fits; ++g)
           if ((end + m->page_size - 1) / m->page_size > m->pools[g].n_free) fits = false;
         if (!fits) break;
@@ -555,8 +561,8 @@ NVH_API int nvh_pool_check(void* p, const int* held) {
 
 // ---- the cache manager
 NVH_API void* nvh_manager_create(const int* windows, const int* num_pages, int groups, int page_size, int max_requests,
-                                 int prefix_caching) {
-  return new CacheManager(windows, num_pages, groups, page_size, max_requests, prefix_caching != 0);
+                                 int prefix_caching, int has_state) {
+  return new CacheManager(windows, num_pages, groups, page_size, max_requests, prefix_caching != 0, has_state != 0);
 }
 NVH_API void nvh_manager_destroy(void* m) { delete (CacheManager*)m; }
 NVH_API void* nvh_manager_pool(void* m, int g) { return &((CacheManager*)m)->pools[g]; }
@@ -629,14 +635,15 @@ NVH_API int nvh_commit_many(void* m, int S, const int64_t* rids, const int* ends
 
 // ---- the index arrays of one step
 // Layout of the one int32 buffer that carries a step's index arrays to the device, every segment starting on a
-// multiple of four ints: ids[T] pos[T] row_entry[T] cu[S+1] pos0[S] slot[S] want[W], one block table
-// [S][max_blocks] per group, and with `sampling` temp[W] (float bits) and u[2W] (doubles).  offsets[] receives
-// the 7 + groups (+ 2) segment starts; the return value is the buffer's length in ints.
+// multiple of four ints: ids[T] pos[T] row_entry[T] cu[S+1] pos0[S] slot[S] want[W] single[S] (the batch rows of
+// the entries that have one row, in entry order, then -1), one block table [S][max_blocks] per group, and with
+// `sampling` temp[W] (float bits) and u[2W] (doubles).  offsets[] receives the 8 + groups (+ 2) segment starts; the
+// return value is the buffer's length in ints.
 static inline int align4(int n) { return (n + 3) & ~3; }
 NVH_API int nvh_step_layout(int S, int T, int W, int groups, int max_blocks, int sampling, int* offsets) {
   int off = 0, k = 0;
-  const int lens[7] = {T, T, T, S + 1, S, S, W};
-  for (int i = 0; i < 7; ++i) {
+  const int lens[8] = {T, T, T, S + 1, S, S, W, S};
+  for (int i = 0; i < 8; ++i) {
     if (offsets) offsets[k] = off;
     ++k;
     off = align4(off + lens[i]);
@@ -673,7 +680,7 @@ NVH_API int nvh_prepare_step(void* m, int S, const int64_t* rids, const int* len
     T += lens[i];
   }
   const int W = wants_cu[S];
-  int off[7 + 64 + 2];
+  int off[8 + 64 + 2];
   if (G > 64) return fail(ERR_STATE, "too many cache groups");
   const int total = nvh_step_layout(S, T, W, G, max_blocks, sampling, off);
   if (total > cap) return fail(ERR_STATE, "the step's arrays do not fit the staging buffer");
@@ -685,7 +692,8 @@ NVH_API int nvh_prepare_step(void* m, int S, const int64_t* rids, const int* len
   int* pos0 = buf + off[4];
   int* slot = buf + off[5];
   int* want = buf + off[6];
-  int row = 0;
+  int* single = buf + off[7];
+  int row = 0, n_single = 0;
   cu[0] = 0;
   for (int i = 0; i < S; ++i) {
     RequestCache* rc = cm->find(rids[i]);
@@ -707,6 +715,7 @@ NVH_API int nvh_prepare_step(void* m, int S, const int64_t* rids, const int* len
                                    std::to_string(n) + " tokens");
       want[w] = row + wants[w];
     }
+    if (n == 1) single[n_single++] = row;
     pos0[i] = start;
     slot[i] = rc->slot;
     info[2 * i] = rc->slot;
@@ -714,7 +723,7 @@ NVH_API int nvh_prepare_step(void* m, int S, const int64_t* rids, const int* len
     for (int g = 0; g < G; ++g) {
       const auto& t = rc->tables[g];
       if ((int)t.size() > max_blocks) return fail(ERR_STATE, "a request holds more pages than the block table is wide");
-      std::memcpy(buf + off[7 + g] + (size_t)i * max_blocks, t.data(), sizeof(int) * t.size());
+      std::memcpy(buf + off[8 + g] + (size_t)i * max_blocks, t.data(), sizeof(int) * t.size());
     }
     row += n;
     cu[i + 1] = row;

@@ -8,7 +8,6 @@ build it) importing the ops fails with the reason.
 from __future__ import annotations
 
 import ctypes
-import os
 from ctypes import c_int, c_float, c_longlong, c_void_p
 
 import torch
@@ -54,9 +53,63 @@ def add_launches(n: int) -> None:
     _launches += n
 
 
-def _check(code: int, what: str) -> None:
+class KernelTimes:
+    """CUDA-event timers per kernel class, off unless asked for:
+
+        with ops.KernelTimes() as kt:
+            runner.step(...)
+        rows = kt.summary()        # [{"name", "calls", "ms", "flops", "bytes"}], largest first
+
+    While it is active every launcher call records an event behind its launch; the time between two consecutive
+    events of a stream is booked to the later launch (so a gap before a kernel counts as its own).  Steps must run
+    outside CUDA graphs to be seen.  ``flops`` and ``bytes`` are what the launcher knows from its arguments (matrix
+    sizes); 0 where it knows nothing."""
+
+    def __init__(self):
+        self.records = []           # (name, start event, end event, flops, bytes)
+        self.last = {}
+
+    def __enter__(self):
+        global _timer
+        torch.cuda.synchronize()
+        self.start = torch.cuda.Event(enable_timing=True)
+        self.start.record()
+        self.last = {}
+        _timer = self
+        return self
+
+    def __exit__(self, *exc):
+        global _timer
+        _timer = None
+        torch.cuda.synchronize()
+
+    def note(self, name: str, flops: float, nbytes: float) -> None:
+        stream = torch.cuda.current_stream()
+        e = torch.cuda.Event(enable_timing=True)
+        e.record(stream)
+        self.records.append((name, self.last.get(stream.cuda_stream, self.start), e, flops, nbytes))
+        self.last[stream.cuda_stream] = e
+
+    def summary(self) -> list:
+        torch.cuda.synchronize()
+        rows = {}
+        for name, a, b, flops, nbytes in self.records:
+            r = rows.setdefault(name, {"name": name, "calls": 0, "ms": 0.0, "flops": 0.0, "bytes": 0.0})
+            r["calls"] += 1
+            r["ms"] += a.elapsed_time(b)
+            r["flops"] += flops
+            r["bytes"] += nbytes
+        return sorted(rows.values(), key=lambda r: -r["ms"])
+
+
+_timer = None
+
+
+def _check(code: int, what: str, flops: float = 0.0, nbytes: float = 0.0) -> None:
     global _launches
     _launches += 1
+    if _timer is not None and code == 0:
+        _timer.note(what, flops, nbytes)
     if code == 0:
         return
     if code < 0:
@@ -262,9 +315,11 @@ def attention_prefill_tile_rows() -> int:
 
 
 def attention_prefill(qkv, k_cache, v_cache, block_table, cu_rows, entry_pos0, max_tiles: int, scale: float,
-                      window: int, out, Hq: int, Hkv: int, D: int, err=None) -> None:
+                      window: int, out, Hq: int, Hkv: int, D: int, err=None, min_rows: int = 1,
+                      kernel: str = "auto") -> None:
     """bfloat16 rows of any mix of portions against their paged keys: the tcgen05 kernel for head sizes 64 and
-    128 and pages of 16, 32 or 64 keys, else the mma.sync kernel."""
+    128 and pages of 16, 32 or 64 keys, else the mma.sync kernel (``kernel="mma"`` asks for that one).  Entries
+    with fewer than ``min_rows`` rows are skipped and their rows of ``out`` left as they are."""
     _cuda_contig(qkv, k_cache, v_cache, block_table, cu_rows, entry_pos0, out)
     _i32(block_table, cu_rows, entry_pos0)
     _need(qkv.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16,
@@ -273,18 +328,20 @@ def attention_prefill(qkv, k_cache, v_cache, block_table, cu_rows, entry_pos0, m
     S = entry_pos0.numel()
     L = lib()
     page = k_cache.shape[2]
-    if L.nv_attention_prefill_tc_usable(c_int(D), c_int(page)):
+    _need(kernel in ("auto", "mma"), "attention_prefill: kernel is 'auto' or 'mma'")
+    if kernel == "auto" and L.nv_attention_prefill_tc_usable(c_int(D), c_int(page)):
         _check(L.nv_attention_prefill_tc(_p(qkv), c_int(qkv.shape[1]), c_int(qkv.shape[0]), _p(k_cache), _p(v_cache),
                                          c_int(k_cache.shape[0]), _p(block_table), c_int(block_table.shape[1]),
                                          _p(cu_rows), _p(entry_pos0), c_int(S), c_int(max_tiles), c_float(scale),
                                          c_int(window), _p(out), c_int(Hq), c_int(Hkv), c_int(D), c_int(page),
-                                         _p(err.t if err is not None else _global_err().t), _stream()),
+                                         c_int(min_rows), _p(err.t if err is not None else _global_err().t),
+                                         _stream()),
                "attention_prefill_tc")
         return
     _check(L.nv_attention_prefill(_p(qkv), c_int(qkv.shape[1]), _p(k_cache), _p(v_cache), _p(block_table),
                                   c_int(block_table.shape[1]), _p(cu_rows), _p(entry_pos0), c_int(S),
                                   c_int(max_tiles), c_float(scale), c_int(window), _p(out), c_int(Hq), c_int(Hkv),
-                                  c_int(D), c_int(page), _stream()), "attention_prefill")
+                                  c_int(D), c_int(page), c_int(min_rows), _stream()), "attention_prefill")
 
 
 def gemm_plain_tile_m() -> int:
@@ -482,6 +539,17 @@ def gather_rows(src, rows, dst) -> None:
                                 c_int(src.shape[1]), _stream()), "gather_rows")
 
 
+def reset_fresh_state(state, entry_slot, entry_pos0) -> None:
+    """Zeroes ``state[slot]`` (``state``: [slots, ...]) for every entry whose first position is 0."""
+    _cuda_contig(state, entry_slot, entry_pos0)
+    _i32(entry_slot, entry_pos0)
+    slots = state.shape[0]
+    slot_bytes = (state.numel() // max(slots, 1)) * state.element_size()
+    _need(slot_bytes % 4 == 0, "reset_fresh_state: a slot's bytes must be a multiple of four")
+    _check(lib().nv_reset_fresh_state(_p(state), c_longlong(slot_bytes), c_int(slots), _p(entry_slot), _p(entry_pos0),
+                                      c_int(entry_slot.numel()), _stream()), "reset_fresh_state")
+
+
 def sample(logits, temperature, u, out) -> None:
     """One token per row: greedy where temperature <= 0, else inverse-CDF with the given u in [0,1)."""
     _cuda_contig(logits, temperature, u, out)
@@ -542,8 +610,6 @@ def grouped_token_tile(TK: int, E: int, swiglu: bool = False) -> int:
     of 16) and so are its token loads (in boxes of 64 rows), so a short last tile of an expert is cheap.  Tiles
     of 256 rows are accepted but lose (one accumulator set instead of two: 23.9 against 20.5 ms for a prompt of
     2,048 tokens).  ``swiglu`` lets the two products of an expert layer choose differently; they agree."""
-    if os.environ.get("NV_GROUPED_TILE"):              # experiments only: "down,gate_up"
-        return int(os.environ["NV_GROUPED_TILE"].split(",")[1 if swiglu else 0])
     avg = (TK + E - 1) // E
     if avg <= 12:
         return 16
@@ -581,7 +647,8 @@ def gemm_fast(a, w, out, *, bias=None, a_rows=None, swiglu=False, M=None, err=No
                         c_longlong(out.stride(0)), c_int(1 if swiglu else 0), c_int(n_tile), c_int(splits),
                         _p(scratch), _p(None), _p(None), _p(None), _p(None), c_int(0), c_int(0),
                         _p(err.t if err is not None else _global_err().t), c_int(_early()), c_int(0), c_int(0),
-                        _stream()), "tc_gemm")
+                        _stream()), f"tc_gemm N={rows_w} K={K}", 2.0 * M * rows_w * K,
+           w.element_size() * rows_w * K + a.element_size() * M * K + out.element_size() * M * N)
 
 
 def gemm_fast_grouped(a, w, out, align, *, a_rows=None, swiglu=False, err=None, tiles=None, tiles_ready=False,
@@ -610,13 +677,22 @@ def gemm_fast_grouped(a, w, out, align, *, a_rows=None, swiglu=False, err=None, 
                             _p(tl.tile_row0), _p(tl.tile_rows), _p(tl.num_tiles), c_int(tl.max_tiles),
                             c_int(rows_w), _p(err.t if err is not None else _global_err().t),
                             c_int(_early() if tiles_ready else 0), c_int(x_sub), c_int(x_mod), _stream()),
-           "tc_gemm_grouped")
+           f"tc_gemm_grouped N={rows_w} K={K}")
+
+
+_dependent_launch = 1
+
+
+def set_dependent_launch(on: bool) -> None:
+    """Whether a step's kernels are launched as programmatic dependents of one another (the default) or the
+    ordinary way; for comparisons."""
+    global _dependent_launch
+    _dependent_launch = 1 if on else 0
+    lib().nv_set_dependent_launch(c_int(_dependent_launch))
 
 
 def _early() -> int:
-    """1: the tensor-core products are launched as programmatic dependents (NV_NO_EARLY=1 turns it off, for
-    comparisons)."""
-    return 0 if os.environ.get("NV_NO_EARLY") else 1
+    return _dependent_launch
 
 
 _gerr = None

@@ -643,6 +643,28 @@ NV_API int nv_gather_rows(const void* src, int dt, const int* rows, void* dst, i
   NV_RETURN_LAST();
 }
 
+// Zeroes the per-request state of every entry that starts its request (first position 0): a request's state must
+// not begin with what the slot's previous holder, or the request itself before a preemption, left there.
+// state: [slots][slot_bytes] bytes, slot_bytes a multiple of 4.  One block per entry.
+__global__ void reset_fresh_state_kernel(uint32_t* __restrict__ state, long long slot_words,
+                                         const int* __restrict__ entry_slot, const int* __restrict__ entry_pos0,
+                                         int num_slots) {
+  const int e = blockIdx.x;
+  if (entry_pos0[e] != 0) return;
+  const int slot = entry_slot[e];
+  if (slot < 0 || slot >= num_slots) return;
+  uint32_t* p = state + (size_t)slot * slot_words;
+  for (long long i = threadIdx.x; i < slot_words; i += blockDim.x) p[i] = 0u;
+}
+
+NV_API int nv_reset_fresh_state(void* state, long long slot_bytes, int num_slots, const int* entry_slot,
+                                const int* entry_pos0, int S, cudaStream_t s) {
+  if (slot_bytes % 4 || ((uintptr_t)state & 3)) return NV_ERR_BAD_SIZE;
+  if (S == 0 || slot_bytes == 0) return NV_OK;
+  reset_fresh_state_kernel<<<S, 256, 0, s>>>((uint32_t*)state, slot_bytes / 4, entry_slot, entry_pos0, num_slots);
+  NV_RETURN_LAST();
+}
+
 NV_API int nv_sample(const float* logits, int R, int V, const float* temperature, const double* u, int* out,
                      cudaStream_t s) {
   if (R == 0) return NV_OK;

@@ -1,3 +1,3 @@
-from .batch import StepEntry, StepBatch, EntryInfo, build_batch
+from .batch import StepEntry, StepBatch, EntryInfo
 
-__all__ = ["StepEntry", "StepBatch", "EntryInfo", "build_batch"]
+__all__ = ["StepEntry", "StepBatch", "EntryInfo"]

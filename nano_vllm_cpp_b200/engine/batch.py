@@ -45,6 +45,9 @@ class StepBatch:
     max_rows: int                   # longest entry
     max_context: int                # largest pos0 + length
     decode_only: bool               # every entry has one row
+    single_rows: torch.Tensor = None    # [n_single] int32: the batch rows of the entries that have one row
+    n_single: int = 0
+    max_single_context: int = 0         # largest pos0 + 1 among the entries that have one row
     h2d_bytes: int = 0              # bytes of index arrays copied to the device for this step
     temperatures: torch.Tensor = None   # [n_want] float32, when the step also samples
     uniforms: torch.Tensor = None       # [n_want] float64
@@ -112,7 +115,7 @@ def batch_layout(S: int, T: int, n_want: int, G: int, max_blocks: int, sampling:
     seg = {}
     off = 0
     for name, n in (("ids", T), ("pos", T), ("row_entry", T), ("cu", S + 1), ("pos0", S), ("slot", S),
-                    ("want", n_want)):
+                    ("want", n_want), ("single", S)):
         seg[name] = (off, n)
         off = _align4(off + n)
     for g in range(G):
@@ -137,58 +140,13 @@ def batch_from_buffer(dev: torch.Tensor, seg: dict, infos: list, S: int, T: int,
     if "temp" in seg:
         temps = view("temp").view(torch.float32)
         us = view("u").view(torch.float64)
+    n_single = sum(1 for i in infos if i.length == 1)
     return StepBatch(
         T=T, S=S, input_ids=view("ids"), positions=view("pos"), row_entry=view("row_entry"), cu_rows=view("cu"),
         entry_pos0=view("pos0"), entry_slot=view("slot"), want_rows=view("want"),
         block_tables=[view(f"bt{g}").view(S, max_blocks) for g in range(G)], entries=list(infos),
         max_rows=max((i.length for i in infos), default=0),
         max_context=max((i.pos0 + i.length for i in infos), default=0),
-        decode_only=all(i.length == 1 for i in infos), h2d_bytes=h2d_bytes, temperatures=temps, uniforms=us)
-
-
-def build_batch(entries: list, infos: list, tables, max_blocks: int, device, stager=None,
-                static_dev=None, table_filler=None, num_groups=None) -> StepBatch:
-    """``infos``: EntryInfo per entry; ``tables``: per group, per entry, the list of page ids — or None with
-    ``table_filler(group, entry, dst)``, which writes an entry's block table into an int32 array view.
-    With ``static_dev`` the arrays are written into that device buffer (whose layout must be the one
-    of ``batch_layout`` for these sizes) instead of a fresh one."""
-    S = len(entries)
-    T = sum(len(e.tokens) for e in entries)
-    n_want = sum(len(e.want) for e in entries)
-    G = len(tables) if tables is not None else num_groups
-    seg, total = batch_layout(S, T, n_want, G, max_blocks)
-    host = np.full(total, -1, dtype=np.int32)
-
-    def put(name, values):
-        o, n = seg[name]
-        host[o:o + n] = values
-
-    ids, pos, row_entry, cu, want = [], [], [], [0], []
-    for i, (e, info) in enumerate(zip(entries, infos)):
-        n = len(e.tokens)
-        ids.extend(e.tokens)
-        pos.extend(range(info.pos0, info.pos0 + n))
-        row_entry.extend([i] * n)
-        for w in e.want:
-            if not (0 <= w < n):
-                raise ValueError(f"request {e.rid!r}: wanted place {w} is not among its {n} tokens")
-            want.append(info.row0 + w)
-        cu.append(cu[-1] + n)
-    put("ids", ids), put("pos", pos), put("row_entry", row_entry), put("cu", cu)
-    put("pos0", [i.pos0 for i in infos]), put("slot", [i.slot for i in infos]), put("want", want)
-    for g in range(G):
-        o, _ = seg[f"bt{g}"]
-        if tables is None:
-            for i in range(S):
-                if table_filler(g, i, host[o + i * max_blocks:o + (i + 1) * max_blocks]) > max_blocks:
-                    raise ValueError("a request holds more pages than the block table is wide")
-            continue
-        for i, table in enumerate(tables[g]):
-            if len(table) > max_blocks:
-                raise ValueError("a request holds more pages than the block table is wide")
-            host[o + i * max_blocks:o + i * max_blocks + len(table)] = table
-    if stager is None:
-        stager = BatchStager(device, depth=1)
-    dev = stager.stage(host, static_dev)
-
-    return batch_from_buffer(dev, seg, infos, S, T, G, max_blocks, int(host.nbytes))
+        decode_only=n_single == len(infos), single_rows=view("single")[:n_single], n_single=n_single,
+        max_single_context=max((i.pos0 + 1 for i in infos if i.length == 1), default=0),
+        h2d_bytes=h2d_bytes, temperatures=temps, uniforms=us)

@@ -57,7 +57,7 @@ class LLMEngine:
             max_requests=cfg.max_num_seqs, max_model_len=cfg.max_model_len, device=cfg.device,
             random_seed=cfg.seed if random_weights else None, norm_std=norm_std, std=std,
             gpu_memory_utilization=cfg.gpu_memory_utilization, prefix_caching=cfg.enable_prefix_caching,
-            cuda_graphs=cfg.cuda_graphs)
+            cuda_graphs=cfg.cuda_graphs, log_stats=cfg.log_stats)
         mc = self.runner.config
         max_pos = getattr(mc, "max_position_embeddings", None)
         if max_pos:                                              # include/nanovllm/config.hpp:269

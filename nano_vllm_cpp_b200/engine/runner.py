@@ -10,6 +10,8 @@ inside.
 """
 from __future__ import annotations
 
+import sys
+
 import numpy as np
 import torch
 
@@ -39,7 +41,7 @@ class ModelRunner:
                  max_tokens: int | None = None, max_requests: int = 4, max_model_len: int | None = None,
                  device: str = "cuda:0", random_seed: int | None = None, norm_std: float = 0.0,
                  std: float | None = None, gpu_memory_utilization: float = 0.9, prefix_caching: bool = False,
-                 fast_kernels: bool = True, cuda_graphs: bool = True):
+                 fast_kernels: bool = True, cuda_graphs: bool = True, log_stats: bool = False):
         if not torch.cuda.is_available():
             raise StepError("no CUDA device: this engine runs on the GPU only (there is no CPU fallback)")
         if dtype not in _DTYPES:
@@ -50,6 +52,10 @@ class ModelRunner:
         self.ctx = RunContext(device=self.device, act_dtype=_DTYPES[dtype], err=ops.ErrorFlag(self.device),
                               page_size=page_size, fast_kernels=fast_kernels)
         self.config, self.model = load_model(model_dir, self.ctx, random_seed=random_seed, norm_std=norm_std, std=std)
+        if log_stats:               # the reference reports the same two facts (src/main.cpp:373-375, src/model.cpp:647-648)
+            free, total = torch.cuda.mem_get_info(self.device)
+            print(f"[nanovllm] weights loaded: {(total - free) / 2**30:.2f} GiB of {total / 2**30:.2f} GiB device "
+                  f"memory in use ({dtype})", file=sys.stderr, flush=True)
         self.page_size = page_size
         self.vocab_size = self.model.spec.vocab_size
         self.cache = DeviceCache(self.model.cache_specs(), page_size, max_requests, self.device, self.ctx.act_dtype)
@@ -57,14 +63,21 @@ class ModelRunner:
             num_pages = (max_tokens + page_size - 1) // page_size
         if num_pages is None:
             num_pages = self._pages_from_free_memory(gpu_memory_utilization)
-        if max_model_len is None:
-            max_model_len = num_pages * page_size
+        paged = bool(self.cache.windows)
+        if max_model_len is None:       # a model without paged layers is bounded by what the caller says, if anything
+            max_model_len = num_pages * page_size if paged else (max_tokens or 1 << 30)
         self.max_model_len = max_model_len
-        self.max_blocks = max(1, (max_model_len + page_size - 1) // page_size)
+        self.max_blocks = max(1, (max_model_len + page_size - 1) // page_size) if paged else 1
         self.cache.allocate(num_pages)
-        self.manager = CacheManager(self.cache.windows or [0], num_pages, page_size, max_requests,
-                                    prefix_caching=prefix_caching)
+        # prefix sharing only where every layer's cache is pages without a window (the manager refuses it otherwise)
+        self.manager = CacheManager(self.cache.windows, num_pages, page_size, max_requests,
+                                    prefix_caching=prefix_caching, has_state=self.cache.has_state)
         self.num_pages = num_pages
+        if log_stats:
+            per_page = sum(self.cache.bytes_per_page())
+            print(f"[nanovllm] cache pool: {num_pages} pages of {page_size} tokens in {len(self.cache.windows)} group(s) "
+                  f"= {num_pages * page_size} tokens, {num_pages * per_page / 2**30:.2f} GiB; {max_requests} state "
+                  f"slots; longest sequence {self.max_model_len}", file=sys.stderr, flush=True)
         # tokens of the last launch's wanted rows (then the kernels' error flag): the next launch may read them there
         self.feed = torch.zeros(max(max_requests, 1) + 1, dtype=torch.int32, device=self.device)
         self.ctx.feed = self.feed
@@ -77,9 +90,11 @@ class ModelRunner:
         self._seen: dict = {}
 
     def _pages_from_free_memory(self, utilization: float) -> int:
+        per_page = sum(self.cache.bytes_per_page())
+        if per_page == 0:               # no layer keeps pages: there is no pool
+            return 0
         free, total = torch.cuda.mem_get_info(self.device)
         budget = free - (1.0 - utilization) * total
-        per_page = sum(self.cache.bytes_per_page()) or 1
         n = int(budget // per_page)
         if n < 1:
             raise StepError("no memory left for the cache after loading the weights")
@@ -87,8 +102,7 @@ class ModelRunner:
 
     # ------------------------------------------------------------------ requests
     def open(self, rid) -> None:
-        rc = self.manager.open(rid)
-        self.cache.reset_slot(rc.slot)
+        self.manager.open(rid)
 
     def close(self, rid) -> None:
         self.manager.close(rid)
@@ -142,6 +156,10 @@ class ModelRunner:
         self.last_h2d_bytes = batch.h2d_bytes
         return batch
 
+    def _forward(self, batch):
+        self.cache.reset_fresh(batch)
+        return self.model.forward(batch, self.cache)
+
     def _commit(self, batch) -> None:
         ends = batch.ends if isinstance(batch, _Prepared) else [i.pos0 + i.length for i in batch.entries]
         self.manager.commit_many(batch.native_ids, ends)
@@ -157,7 +175,7 @@ class ModelRunner:
             logits, batch = self._graph_step(entries, None)
         if batch is None:
             batch = self.prepare(entries)
-            logits = self.model.forward(batch, self.cache)
+            logits = self._forward(batch)
         if check:
             self.ctx.err.check("step")
         self._commit(batch)
@@ -189,7 +207,7 @@ class ModelRunner:
             _, batch = self._graph_step(entries, sampling)
         if batch is None:
             batch = self.prepare(entries, sampling=sampling)
-            logits = self.model.forward(batch, self.cache)
+            logits = self._forward(batch)
             self._sample_into_feed(logits, batch)
             if picked:
                 self._nucleus_into_feed(logits, picked, temperatures, uniforms, nucleus)
@@ -256,14 +274,14 @@ class ModelRunner:
             static_dev = torch.full((total,), -1, dtype=torch.int32, device=self.device)
             batch = self.prepare(entries, static_dev, sampling)
             batch.max_context = self.max_model_len        # the split of the keys must not depend on the step
-            logits = self.model.forward(batch, self.cache)       # warms up; also this step's result
+            logits = self._forward(batch)       # warms up; also this step's result
             if sampling is not None:
                 self._sample_into_feed(logits, batch)
             torch.cuda.synchronize(self.device)
             before = ops.launch_count()
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
-                static_logits = self.model.forward(batch, self.cache)
+                static_logits = self._forward(batch)
                 if sampling is not None:
                     self._sample_into_feed(static_logits, batch)
             self._graphs[key] = (graph, static_dev, static_logits, ops.launch_count() - before)

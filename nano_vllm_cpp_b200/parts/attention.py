@@ -71,20 +71,26 @@ class PagedAttention(Mixer):
         return linear(ctx, att, self.o_weight, torch.float32)
 
     def _attend(self, qkv, cache, bt, batch, att):
-        # bfloat16 runs take the split-key kernel for batches of single rows; float32 runs keep the
-        # plain kernel everywhere, so that their sums have one order however the work is cut
-        if self.ctx.fast_kernels and self.ctx.act_dtype == torch.bfloat16 and cache.k.dtype == torch.bfloat16:
-            if batch.decode_only and ops.attention_decode_usable(cache.k, self.D):
-                ops.attention_decode(qkv, cache.k, cache.v, bt, batch.row_entry, batch.positions, self.scale,
-                                     self.window, att, self.Hq, self.Hkv, self.D, batch.max_context, err=self.ctx.err)
-            else:
-                tm = ops.attention_prefill_tile_rows()
-                tiles = sum((e.length + tm - 1) // tm for e in batch.entries)
-                ops.attention_prefill(qkv, cache.k, cache.v, bt, batch.cu_rows, batch.entry_pos0, tiles, self.scale,
-                                      self.window, att, self.Hq, self.Hkv, self.D, err=self.ctx.err)
+        """Which kernel runs which rows.  float32 runs keep the plain kernel for every row, so that their sums have
+        one order however the work is cut.  bfloat16 runs send entries of one row to the split-key decode kernel and
+        the other entries to the prefill kernel, in the same step if it holds both kinds."""
+        ctx = self.ctx
+        if not (ctx.fast_kernels and ctx.act_dtype == torch.bfloat16 and cache.k.dtype == torch.bfloat16):
+            ops.paged_attention_plain(qkv, cache.k, cache.v, bt, batch.row_entry, batch.positions, self.scale,
+                                      self.window, att, self.Hq, self.Hkv, self.D)
             return
-        ops.paged_attention_plain(qkv, cache.k, cache.v, bt, batch.row_entry, batch.positions, self.scale,
-                                  self.window, att, self.Hq, self.Hkv, self.D)
+        single = batch.n_single if ops.attention_decode_usable(cache.k, self.D) else 0
+        if single:
+            ops.attention_decode(qkv, cache.k, cache.v, bt, batch.row_entry, batch.positions, self.scale, self.window,
+                                 att, self.Hq, self.Hkv, self.D,
+                                 batch.max_context if batch.decode_only else batch.max_single_context,
+                                 rows=None if batch.decode_only else batch.single_rows, err=ctx.err)
+        if single < batch.S:
+            tm = ops.attention_prefill_tile_rows()
+            min_rows = 2 if single else 1
+            tiles = sum((e.length + tm - 1) // tm for e in batch.entries if e.length >= min_rows)
+            ops.attention_prefill(qkv, cache.k, cache.v, bt, batch.cu_rows, batch.entry_pos0, tiles, self.scale,
+                                  self.window, att, self.Hq, self.Hkv, self.D, err=ctx.err, min_rows=min_rows)
 
 
 def _cat(ts):

@@ -49,7 +49,8 @@ class KVCacheSpec:
 
 @dataclass(frozen=True)
 class StateCacheSpec:
-    """A fixed-size state per request, zeroed when a request gets its slot."""
+    """A fixed-size state per request (``shape`` elements of ``dtype``, a multiple of four bytes), zeroed before
+    the step that runs the request's first token."""
     shape: tuple
     dtype: torch.dtype = torch.float32
 

@@ -2,8 +2,6 @@
 softmax router, top-k routing and an optional sigmoid-gated shared expert."""
 from __future__ import annotations
 
-import os
-
 import torch
 
 from ..csrc import ops
@@ -12,7 +10,9 @@ from .linear import linear, grouped_linear, small_linear
 from .registry import register_part
 
 # Batches of up to this many rows run the shared expert's chunks on a second stream beside the routing.
-SIDE_MAX_ROWS = int(os.environ.get("NV_SIDE_MAX_ROWS", "64"))
+SIDE_MAX_ROWS = 64
+# Permutation buffers are kept per batch size; beyond this many sizes the oldest set is dropped.
+MAX_ALIGNMENTS = 16
 
 
 class DenseSwiGLU(FeedForward):
@@ -57,6 +57,7 @@ class SparseMoeSwiGLU(FeedForward):
         self.hidden, self.E, self.K = hidden_size, num_experts, top_k
         self.inter, self.shared_inter, self.renorm = intermediate_size, shared_intermediate_size, renormalize
         self._align = {}
+        self._captured = {}
         self._static = {}
         self.router_and_gate = None
         self.last_alignment = None      # the permutation buffers of the latest forward (for statistics)
@@ -131,9 +132,18 @@ class SparseMoeSwiGLU(FeedForward):
         else:
             tile_m, tile_m2 = ops.gemm_plain_tile_m(), 0
         key = (TK, n_experts, tile_m, tile_m2)
-        if key not in self._align:
-            self._align[key] = ops.MoeAlignment(TK, n_experts, tile_m, device, tile_m2)
-        return self._align[key]
+        if key in self._captured:
+            return self._captured[key]
+        al = self._align.pop(key, None)
+        if al is None:
+            if len(self._align) >= MAX_ALIGNMENTS:
+                self._align.pop(next(iter(self._align)))
+            al = ops.MoeAlignment(TK, n_experts, tile_m, device, tile_m2)
+        if torch.cuda.is_current_stream_capturing():     # a captured step names these buffers by address: kept for good
+            self._captured[key] = al
+        else:
+            self._align[key] = al                        # most recently used last
+        return al
 
     def forward(self, h, h32, batch):
         ctx = self.ctx

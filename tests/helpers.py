@@ -28,6 +28,14 @@ CASES["C"] = dict(
                 qkv_bias=True, hidden_act="silu"),
     seed=4, std=0.03, norm_std=0.1, prompts={})
 
+# C without its window: one group of layers, so that requests can share pages of a common prefix, with the head size
+# that the tensor-core attention kernels take.
+CASES["D"] = dict(config=dict(CASES["C"]["config"], use_sliding_window=False), seed=6, std=0.03, norm_std=0.1, prompts={})
+# A with weights four times as large: in A itself (weights N(0, 0.02), width 64) the branches of a layer are tiny
+# beside the path from the embedding to the head, so a fault inside a layer could hide under the bfloat16 tolerance;
+# here every layer's branch weighs as much as what it is added to.
+CASES["A8"] = dict(config=dict(CASES["A"]["config"]), seed=8, std=0.08, norm_std=0.1, prompts={})
+
 # Tolerances, fixed before the first GPU run.  float32: sums of at most a few hundred float32
 # products against float64 -> 1e-5 absolute on logits of order one.  bfloat16: activations are
 # rounded to 8 bits of mantissa (2^-9 relative) a few times per layer; over the layers of the
@@ -113,3 +121,24 @@ class Replay:
         assert pos, f"{what}: no logits were collected for {rid}"
         got = torch.stack([self.logits[(rid, p)] for p in pos])
         assert_close(got, want[pos], dtype, f"{what} request {rid}")
+
+
+def assert_greedy_follows_plain(mdir, prompt_ids, tokens, dtype, what=""):
+    """``tokens`` were generated greedily by the engine from ``prompt_ids``.  Every token must be the plain
+    implementation's choice for its prefix, up to the first position where the plain logits leave the choice open
+    within the dtype's tolerance (their two largest values closer than twice the bound, since both may move): from
+    there on the two runs may rightly follow different sequences.  Returns the number of tokens that were held."""
+    cfg, W = _plain_cache.setdefault(mdir, plain_model.read_folder(mdir))
+    tol = TOL[dtype]
+    ids = list(prompt_ids)
+    for k, tok in enumerate(tokens):
+        logits = plain_model.forward(cfg, W, ids)[-1]
+        top = torch.topk(logits, 2)
+        bound = tol["abs"] + tol["rel"] * float(logits.abs().max())
+        if int(top.indices[0]) != int(tok):
+            gap = float(top.values[0] - logits[int(tok)])
+            assert gap <= 2 * bound, (f"{what}: token {k} is {tok}, the plain implementation takes {int(top.indices[0])} "
+                                      f"with a lead of {gap:.3g} over it (tolerance {2 * bound:.3g})")
+            return k
+        ids.append(int(tok))
+    return len(tokens)

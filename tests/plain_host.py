@@ -123,9 +123,10 @@ class RequestCache:
 
 class CacheManager:
     def __init__(self, windows: list, num_pages, page_size: int, max_requests: int,
-                 prefix_caching: bool = False):
-        """``windows``: one entry per group (0 = reads every key).  ``num_pages``: an int for all
-        groups or a list."""
+                 prefix_caching: bool = False, has_state: bool = False):
+        """``windows``: one entry per group (0 = reads every key; none for a model without paged layers).
+        ``num_pages``: an int for all groups or a list.  ``has_state``: some layer keeps a per-request state, which
+        rules prefix sharing out."""
         if isinstance(num_pages, int):
             num_pages = [num_pages] * len(windows)
         self.windows = list(windows)
@@ -134,7 +135,7 @@ class CacheManager:
         self.max_requests = max_requests
         self._free_slots = list(range(max_requests - 1, -1, -1))
         self.requests: dict = {}
-        self.prefix_caching = bool(prefix_caching) and len(windows) == 1 and windows[0] == 0
+        self.prefix_caching = (bool(prefix_caching) and not has_state and len(windows) == 1 and windows[0] == 0)
 
     # ------------------------------------------------------------------ requests
     def has(self, rid) -> bool:
@@ -243,6 +244,8 @@ class CacheManager:
     def adopt_prefix(self, rid, matched: list) -> int:
         """Gives a freshly opened request the matched pages; returns the number of cached tokens."""
         rc = self.requests[rid]
+        if not matched:
+            return rc.num_tokens
         if rc.num_tokens or rc.tables[0]:
             raise RuntimeError("adopt_prefix on a request that already holds pages")
         for page, h in matched:
@@ -369,7 +372,8 @@ class Scheduler:
                 first = min(seq.num_tokens - len(matched) * self.manager.page_size, budget,
                             self.prefill_chunk or budget)
                 end = len(matched) * self.manager.page_size + first
-                if self.manager.new_pages_for(end, matched) > self.manager.pools[0].num_free() or any(
+                if self.manager.pools and (
+                        self.manager.new_pages_for(end, matched) > self.manager.pools[0].num_free()) or any(
                         (end + self.manager.page_size - 1) // self.manager.page_size > p.num_free()
                         for p in self.manager.pools[1:]):
                     break

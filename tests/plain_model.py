@@ -1,5 +1,6 @@
-"""Plain, slow implementation of Qwen2-MoE on the CPU: whole sequences, no cache, one function
-per part, float64 arithmetic on the float32 (or bfloat16) weight values.
+"""Plain, slow implementation of Qwen2-MoE: whole sequences, no cache, one function per part, float64
+arithmetic on the float32 (or bfloat16) weight values.  It runs where its tensors are: on the CPU for the tiny
+models, and with float64 tensors on the GPU where a test holds the engine to it at real layer sizes.
 
 It shares no code with the package: it reads ``config.json`` as a dict and the safetensors file
 with a reader of its own.  Every function is written from the reference's formulas and cites
@@ -82,7 +83,7 @@ def layer_window(cfg, l: int) -> int:
 # ------------------------------------------------------------------------------ parts
 def embedding(table, ids):
     """h[t] = table[id_t]  (src/hip_ops.hip:553-563)."""
-    return table[torch.as_tensor(ids, dtype=torch.long)].clone()
+    return table[torch.as_tensor(ids, dtype=torch.long, device=table.device)].clone()
 
 
 def rms_norm(x, w, eps: float):
@@ -99,8 +100,8 @@ def rope_neox(x, positions, theta: float):
     inv = np.array([1.0 / (theta ** ((2.0 * i) / D)) for i in range(half)], dtype=np.float64).astype(np.float32)
     pos = np.asarray(positions, dtype=np.float32)[:, None]
     ang = (pos * inv[None, :]).astype(np.float32)            # float32 product, as the reference
-    c = torch.from_numpy(np.cos(ang.astype(np.float64)))[:, None, :]
-    s = torch.from_numpy(np.sin(ang.astype(np.float64)))[:, None, :]
+    c = torch.from_numpy(np.cos(ang.astype(np.float64)))[:, None, :].to(x.device)
+    s = torch.from_numpy(np.sin(ang.astype(np.float64)))[:, None, :].to(x.device)
     x1, x2 = x[..., :half], x[..., half:]
     return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], dim=-1)
 
@@ -112,12 +113,12 @@ def causal_attention(q, k, v, scale: float, window: int = 0):
     T, Hq, D = q.shape
     Hkv = k.shape[1]
     rep = Hq // Hkv
-    out = torch.zeros(T, Hq, D, dtype=F64)
+    out = torch.zeros(T, Hq, D, dtype=F64, device=q.device)
     for h in range(Hq):
         kh = h // rep
         s = (q[:, h, :] @ k[:, kh, :].T) * scale                       # [T, T]
-        i = torch.arange(T)[:, None]
-        j = torch.arange(T)[None, :]
+        i = torch.arange(T, device=q.device)[:, None]
+        j = torch.arange(T, device=q.device)[None, :]
         keep = j <= i
         if window > 0:
             keep &= j >= i + 1 - window
@@ -159,60 +160,67 @@ def dense_mlp(x_norm, W, prefix: str):
     return silu_mul(g, u) @ W[prefix + "down_proj.weight"].T
 
 
-def route(x_norm, Wg, top_k: int, renorm: bool):
+def route(x_norm, Wg, top_k: int, renorm: bool, margins: list | None = None):
     """p = softmax(x Wg^T) over all experts; the top_k largest in descending order, a tie going to the
     lower index (selection with strict >); weights p or p / sum(p_topk)
-    (tools/ref_top5.cpp:484-515; src/hip_ops.hip:813-841).  Returns (idx [T,K], w [T,K])."""
+    (tools/ref_top5.cpp:484-515; src/hip_ops.hip:813-841).  Returns (idx [T,K], w [T,K]).
+    ``margins``, if a list, receives per row the gap between the top_k-th and the next router logit."""
     logits = (x_norm @ Wg.T).to(torch.float32).to(F64)                 # router logits are stored as float32
     p = torch.softmax(logits, dim=-1)
     T, E = p.shape
-    idx = torch.zeros(T, top_k, dtype=torch.long)
-    w = torch.zeros(T, top_k, dtype=F64)
-    for t in range(T):
-        rem = p[t].clone()
-        for k in range(top_k):
-            best = 0
-            for e in range(1, E):
-                if rem[e] > rem[best]:
-                    best = e
-            idx[t, k], w[t, k] = best, rem[best]
-            rem[best] = -1.0
+    idx = torch.zeros(T, top_k, dtype=torch.long, device=p.device)
+    w = torch.zeros(T, top_k, dtype=F64, device=p.device)
+    rem = p.clone()
+    rows = torch.arange(T, device=p.device)
+    for k in range(top_k):                  # one selection pass per rank; argmax returns the first largest
+        best = torch.argmax(rem, dim=-1)
+        idx[:, k], w[:, k] = best, rem[rows, best]
+        rem[rows, best] = -1.0
+    if margins is not None and top_k < E:
+        top = torch.sort(logits, dim=-1, descending=True).values
+        margins.append((top[:, top_k - 1] - top[:, top_k]).cpu())
     if renorm:
         w = w / w.sum(dim=-1, keepdim=True)
     return idx, w.to(torch.float32).to(F64)                            # weights are stored as float32
 
 
-def sparse_mlp(x_norm, W, prefix: str, cfg):
-    """shared expert times its sigmoid gate, plus the routed experts in rank order
-    (tools/ref_top5.cpp:467-552; src/model.cpp:789-827)."""
+def sparse_mlp(x_norm, W, prefix: str, cfg, margins: list | None = None):
+    """shared expert times its sigmoid gate, plus the routed experts
+    (tools/ref_top5.cpp:467-552; src/model.cpp:789-827).  The reference walks a row's experts in rank order;
+    here the rows of one expert are taken together (float64 sums: the order moves nothing that is compared)."""
     T, H = x_norm.shape
     E, K = cfg["num_experts"], cfg["num_experts_per_tok"]
-    idx, w = route(x_norm, W[prefix + "gate.weight"], K, bool(cfg.get("norm_topk_prob", False)))
-    y = torch.zeros(T, H, dtype=F64)
+    idx, w = route(x_norm, W[prefix + "gate.weight"], K, bool(cfg.get("norm_topk_prob", False)), margins)
+    y = torch.zeros(T, H, dtype=F64, device=x_norm.device)
     if cfg.get("shared_expert_intermediate_size", 0) > 0:
         sh = dense_mlp(x_norm, W, prefix + "shared_expert.")
         gate = 1.0 / (1.0 + torch.exp(-(x_norm @ W[prefix + "shared_expert_gate.weight"].reshape(-1))))
         y = y + gate[:, None] * sh
     stacked = prefix + "experts.gate_up_proj" in W
     I = cfg["moe_intermediate_size"]
-    for t in range(T):
-        r = torch.zeros(H, dtype=F64)
-        for k in range(K):
-            e = int(idx[t, k])
-            if stacked:      # [E, 2I, H] gate rows then up rows; [E, H, I]  (src/model.cpp:274-281, 356-365)
-                gu, dn = W[prefix + "experts.gate_up_proj"][e], W[prefix + "experts.down_proj"][e]
-                g, u = x_norm[t] @ gu[:I].T, x_norm[t] @ gu[I:].T
-            else:
-                pe = f"{prefix}experts.{e}."
-                g, u, dn = x_norm[t] @ W[pe + "gate_proj.weight"].T, x_norm[t] @ W[pe + "up_proj.weight"].T, W[pe + "down_proj.weight"]
-            r = r + w[t, k] * (silu_mul(g, u) @ dn.T)
-        y[t] = y[t] + r
+    for e in range(E):
+        hit = (idx == e)
+        rows = torch.nonzero(hit.any(dim=-1)).reshape(-1)
+        if rows.numel() == 0:
+            continue
+        if stacked:      # [E, 2I, H] gate rows then up rows; [E, H, I]  (src/model.cpp:274-281, 356-365)
+            gu, dn = W[prefix + "experts.gate_up_proj"][e], W[prefix + "experts.down_proj"][e]
+            wg, wu = gu[:I], gu[I:]
+        else:
+            pe = f"{prefix}experts.{e}."
+            wg, wu, dn = W[pe + "gate_proj.weight"], W[pe + "up_proj.weight"], W[pe + "down_proj.weight"]
+        xe = x_norm[rows]
+        out = silu_mul(xe @ wg.T, xe @ wu.T) @ dn.T
+        we = (w[rows] * hit[rows]).sum(dim=-1)                          # an expert appears once in a row's top k
+        y[rows] = y[rows] + we[:, None] * out
     return y
 
 
-def forward(cfg, W, ids, positions=None):
+def forward(cfg, W, ids, positions=None, margins: list | None = None):
     """Logits [T, V] (float64) of one whole sequence  (tools/ref_top5.cpp:314-592;
-    src/model.cpp:698-848).  x <- x + attention(norm(x)); x <- x + mlp(norm(x)); final norm; head."""
+    src/model.cpp:698-848).  x <- x + attention(norm(x)); x <- x + mlp(norm(x)); final norm; head.
+    ``W`` is any mapping from tensor names to float64 tensors (all on one device); ``margins`` collects the
+    router's margins of every sparse layer (see ``route``)."""
     T = len(ids)
     if positions is None:
         positions = list(range(T))
@@ -224,7 +232,7 @@ def forward(cfg, W, ids, positions=None):
         x = x + attention_layer(h, W, p + "self_attn.", cfg, l, positions)
         h = rms_norm(x, W[p + "post_attention_layernorm.weight"], eps)
         if layer_is_sparse(cfg, l):
-            x = x + sparse_mlp(h, W, p + "mlp.", cfg)
+            x = x + sparse_mlp(h, W, p + "mlp.", cfg, margins)
         else:
             x = x + dense_mlp(h, W, p + "mlp.")
     h = rms_norm(x, W["model.norm.weight"], eps)

@@ -345,6 +345,51 @@ def test_prefix_hit_skips_cached_pages():
     assert rec[0] == [(s2.seq_id, 48, 2, True)]           # the three cached pages are not run again
 
 
+def test_a_state_rules_prefix_sharing_out():
+    """A layer with a per-request state has seen every token of its request: pages of another request must not
+    let a request skip tokens.  So must a window, or a second group."""
+    import plain_host
+    for cls in (CacheManager, plain_host.CacheManager):
+        assert cls([0], 8, 16, 4, prefix_caching=True).prefix_caching
+        assert not cls([0], 8, 16, 4, prefix_caching=True, has_state=True).prefix_caching
+        assert not cls([16], 8, 16, 4, prefix_caching=True).prefix_caching
+        assert not cls([0, 16], 8, 16, 4, prefix_caching=True).prefix_caching
+        assert not cls([], 8, 16, 4, prefix_caching=True, has_state=True).prefix_caching
+    m = CacheManager([0], 16, 16, 4, prefix_caching=True, has_state=True)
+    sched = Scheduler(m, max_num_seqs=4, max_num_batched_tokens=256, max_model_len=4096)
+    p = list(range(2, 50))
+    drive(sched, [Sequence(p, SamplingParams(max_tokens=2, ignore_eos=True))], random.Random(5))
+    s2 = Sequence(p + [60, 61], SamplingParams(max_tokens=2, ignore_eos=True))
+    rec = drive(sched, [s2], random.Random(5))
+    assert rec[0] == [(s2.seq_id, 0, 50, True)]           # every token runs again
+
+
+def test_a_model_without_pages_is_admitted_by_state_slots_alone():
+    """No paged layer: the manager has no pool; requests hold a slot each, and the scheduler admits while slots
+    are free, whatever their lengths."""
+    import plain_host
+    m = CacheManager([], 0, 16, max_requests=3, has_state=True)
+    assert m.pools == [] and m.free_slots() == 3
+    sched = Scheduler(m, max_num_seqs=8, max_num_batched_tokens=64, max_model_len=4096)
+    seqs = [Sequence(list(range(2, 2 + n)), SamplingParams(max_tokens=5, ignore_eos=True)) for n in (70, 5, 40, 9, 200)]
+    rec = drive(sched, seqs, random.Random(3), check=lambda out: None)
+    assert all(len(step) <= 3 for step in rec)             # never more live requests than slots
+    assert all(len(q.completion_token_ids) == 5 for q in seqs)
+    assert m.free_slots() == 3
+    # the plain restatement decides the same
+    pm = plain_host.CacheManager([], 0, 16, max_requests=3, has_state=True)
+    ps = plain_host.Scheduler(pm, max_num_seqs=8, max_num_batched_tokens=64, max_model_len=4096)
+    qs = [plain_host.PlainSeq(100 + i, list(range(2, 2 + n)), 5) for i, n in enumerate((70, 5, 40, 9, 200))]
+    for q in qs:
+        ps.add(q)
+    rng, prec = random.Random(3), []
+    while not ps.is_finished():
+        out = ps.schedule()
+        prec.append([(s.start, s.count, s.samples) for s in out])
+        ps.postprocess(out, {s.seq.seq_id: rng.randrange(2, 50) for s in out if s.samples})
+    assert prec == [[(b, c, d) for _, b, c, d in step] for step in rec]
+
+
 # ------------------------------------------------------------------------------- native code against its plain restatement
 def test_native_host_code_decides_like_the_plain_restatement():
     """The native pool, manager and scheduler against the plain Python classes of tests/plain_host.py: the same
@@ -433,7 +478,8 @@ def test_native_pool_and_hash_against_the_plain_restatement():
 def test_native_step_arrays_match_the_python_builder():
     """The native fill of a step's index arrays against ``build_batch`` on the same requests."""
     import numpy as np
-    from nano_vllm_cpp_b200.engine.batch import StepEntry, EntryInfo, build_batch, batch_layout
+    from nano_vllm_cpp_b200.engine.batch import StepEntry, EntryInfo, batch_layout
+    from batch_builder import build_batch
     rng = random.Random(5)
     for trial in range(30):
         windows = rng.choice([(0,), (0, 16)])
@@ -473,6 +519,10 @@ def test_native_step_arrays_match_the_python_builder():
                             ("want", ref.want_rows)):
                 o, n = seg[name]
                 assert buf[o:o + n].tolist() == t.tolist(), name
+            o, n = seg["single"]
+            singles = [i.row0 for i in infos if i.length == 1]
+            assert buf[o:o + n].tolist() == singles + [-1] * (S - len(singles))
+            assert ref.single_rows.tolist() == singles and ref.n_single == len(singles)
             for g in range(len(windows)):
                 o, n = seg[f"bt{g}"]
                 assert buf[o:o + n].tolist() == ref.block_tables[g].flatten().tolist()

@@ -53,3 +53,37 @@ def test_generation_config_gives_defaults_that_options_override(tmp_path, monkey
     assert cli.generation_defaults(str(tmp_path / "nowhere")) == {}
     (tmp_path / "generation_config.json").write_text(json.dumps({"temperature": "hot", "max_new_tokens": 0}))
     assert cli.generation_defaults(str(tmp_path)) == {}
+
+
+def test_config_option_runs_random_weights_without_a_folder(tmp_path, monkeypatch):
+    """``--config <json>`` stands for a model folder: the run gets a temporary folder whose config.json is the file
+    and draws its weights from ``--seed``."""
+    import json
+    import os
+    cfg = tmp_path / "tiny.json"
+    cfg.write_text(json.dumps({"architectures": ["Qwen2MoeForCausalLM"], "hidden_size": 64}))
+    seen = {}
+
+    def fake_run(opt):
+        seen.update(opt)
+        with open(os.path.join(opt["model_dir"], "config.json")) as f:
+            seen["config_json"] = json.load(f)
+        return 0
+
+    monkeypatch.setattr(cli, "_run", fake_run)
+    assert cli.main(["--config", str(cfg), "--seed", "7", "--tokens", "1,2", "--dtype", "fp32"]) == 0
+    assert seen["random_weights"] is True and seen["seed"] == 7 and seen["dtype"] == "fp32"
+    assert seen["config_json"]["hidden_size"] == 64
+    assert not os.path.exists(seen["model_dir"])            # the temporary folder is gone afterwards
+    assert cli.main(["--config", str(tmp_path / "absent.json"), "--tokens", "1"]) == 2
+
+
+def test_dtype_spellings():
+    from nano_vllm_cpp_b200.config import EngineConfig
+    import pytest
+    for given, want in (("bf16", "bfloat16"), ("fp32", "float32"), ("bfloat16", "bfloat16"), ("float32", "float32")):
+        c = EngineConfig(dtype=given)
+        c.validate()
+        assert c.dtype == want
+    with pytest.raises(ValueError, match="dtype"):
+        EngineConfig(dtype="half").validate()

@@ -16,7 +16,7 @@ pytestmark = pytest.mark.gpu
 
 @pytest.fixture(scope="module")
 def folders(tmp_path_factory):
-    return {c: helpers.model_folder(c, tmp_path_factory) for c in ("A", "B")}
+    return {c: helpers.model_folder(c, tmp_path_factory) for c in ("A", "B", "C", "D")}
 
 
 def engine(mdir, **kw):
@@ -40,6 +40,114 @@ def test_greedy_generation_equals_plain(case, folders):
     outs = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True))
     for p, o in zip(prompts, outs):
         assert o["token_ids"] == plain_greedy(folders[case], p, 12)
+
+
+@pytest.mark.parametrize("case", ["A", "B", "C"])
+def test_greedy_generation_in_bfloat16_follows_plain(case, folders):
+    """bfloat16 through the scheduler: every greedy token is the plain implementation's choice up to the first
+    position where the plain logits leave the choice open within the bfloat16 tolerance; and at least the
+    first tokens of every request are held."""
+    from nano_vllm_cpp_b200 import SamplingParams
+    lengths = {"A": [5, 17, 33], "B": [1, 9, 24], "C": [2, 40, 70]}[case]
+    prompts = [prompt(case, n, salt=9) for n in lengths]
+    eng = engine(folders[case], dtype="bfloat16")
+    outs = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True))
+    held = [helpers.assert_greedy_follows_plain(folders[case], p, o["token_ids"], "bfloat16", f"{case} prompt {len(p)}")
+            for p, o in zip(prompts, outs)]
+    assert sum(held) >= 12, f"only {held} tokens could be held to the plain implementation"
+
+
+# ------------------------------------------------------------------------------- prefix sharing
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("case", ["A", "D"])
+def test_logits_of_a_request_that_adopts_another_requests_pages(case, dtype, folders):
+    """Request 2 shares its first 40 tokens with request 1 and takes over request 1's two full pages instead of
+    running those tokens: once while request 1 is live (the pages are held twice), once after request 1 has ended
+    (the pages are revived from the free list), once after a stranger has been through the pool in between.  The
+    logits of every position that request 2 runs equal the plain implementation's."""
+    from nano_vllm_cpp_b200.engine.runner import ModelRunner
+    from nano_vllm_cpp_b200.engine.batch import StepEntry
+    mdir = folders[case]
+    runner = ModelRunner(mdir, dtype=dtype, max_tokens=192, max_requests=4, prefix_caching=True)
+    m = runner.manager
+    assert m.prefix_caching
+    shared = prompt(case, 40, salt=70)
+    one = shared + prompt(case, 9, salt=71)
+    two = shared + prompt(case, 21, salt=72)
+    three = shared[:32] + prompt(case, 30, salt=73)
+    stranger = prompt(case, 100, salt=74)
+
+    def run_whole(rid, ids):
+        runner.step([StepEntry(rid, ids, [len(ids) - 1])])
+        m.commit(rid, len(ids), ids)                      # hashes the full pages, as the scheduler's bookkeeping does
+
+    def run_adopting(rid, ids, expect_cached):
+        runner.open(rid)
+        matched = m.match_prefix(ids)
+        cached = m.adopt_prefix(rid, matched)
+        assert cached == expect_cached
+        rest = ids[cached:]
+        logits = runner.step([StepEntry(rid, rest, list(range(len(rest))))]).float().cpu()
+        m.commit(rid, len(ids), ids)
+        want = helpers.plain_logits(mdir, ids)[cached:]
+        helpers.assert_close(logits, want, dtype, f"{case} {dtype} request {rid} after {cached} adopted tokens")
+        m.check()
+
+    run_whole("one", one)
+    run_adopting("two", two, 32)                          # pages 0 and 1 of "one", which is still live
+    assert m.pools[0].ref_count[m.get("one").tables[0][0]] == 2
+    runner.close("one")
+    runner.close("two")
+    assert m.pools[0].num_free() == m.pools[0].num_pages
+    run_adopting("three", three, 32)                      # both owners are gone: the pages come back from the free list
+    runner.close("three")
+    run_whole("stranger", stranger)                       # 7 of the 12 pages: the hashed pages are at the back, untouched
+    runner.close("stranger")
+    run_adopting("again", two, 48)                        # the third page that "two" wrote is still there, too
+    runner.close("again")
+    run_whole("big", prompt(case, 190, salt=75))          # all 12 pages taken: the hashes are forgotten
+    runner.close("big")
+    run_adopting("fresh", two, 0)
+    runner.close("fresh")
+    assert m.pools[0].num_free() == m.pools[0].num_pages
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_prefix_sharing_through_the_entry_point(dtype, folders):
+    """Two waves of requests with common prefixes through the engine with prefix sharing on (its default): the
+    second wave adopts pages the first wave wrote.  Greedy tokens follow the plain implementation, and in float32
+    they equal those of an engine without prefix sharing."""
+    from nano_vllm_cpp_b200 import SamplingParams
+    case = "D"
+    base = prompt(case, 48, salt=80)
+    wave1 = [base + prompt(case, 5, salt=81), prompt(case, 20, salt=82)]
+    wave2 = [base + prompt(case, 11, salt=83), base[:40] + prompt(case, 3, salt=84), prompt(case, 33, salt=85)]
+    sp = SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True)
+    eng = engine(folders[case], dtype=dtype, max_model_len=256, num_kv_blocks=32)
+    assert eng.runner.manager.prefix_caching
+    got1 = [o["token_ids"] for o in eng.generate(wave1, sp)]
+    free_before = eng.runner.manager.pools[0].num_free()
+    started = []
+    inner = eng.runner.launch_tokens
+
+    def spy(entries, *a, **k):
+        started.extend((e.rid, len(e.tokens)) for e in entries)
+        return inner(entries, *a, **k)
+
+    eng.runner.launch_tokens = spy
+    got2 = [o["token_ids"] for o in eng.generate(wave2, sp)]
+    assert free_before == eng.runner.manager.pools[0].num_pages
+    first_portion = {}
+    for rid, n in started:
+        first_portion.setdefault(rid, n)
+    # 48 and 32 of the shared tokens were adopted, not run again
+    assert sorted(first_portion.values()) == [len(wave2[1]) - 32, len(wave2[0]) - 48, 33]
+    for p, toks in zip(wave1 + wave2, got1 + got2):
+        held = helpers.assert_greedy_follows_plain(folders[case], p, toks, dtype, f"prefix sharing {dtype}")
+        assert held >= (10 if dtype == "float32" else 3)
+    if dtype == "float32":
+        plain = engine(folders[case], dtype=dtype, max_model_len=256, num_kv_blocks=32, enable_prefix_caching=False)
+        assert [o["token_ids"] for o in plain.generate(wave1 + wave2, sp)] == got1 + got2
 
 
 def test_temperature_sampling_is_reproducible_and_follows_the_plain_sampler(folders):
@@ -73,6 +181,24 @@ def test_preempted_request_resumes_with_the_same_tokens(folders):
     assert got == want
 
 
+@pytest.mark.parametrize("case", ["A", "C"])
+def test_preemption_in_bfloat16(case, folders):
+    """A preempted request runs its prompt and its own tokens again as one portion, where the uninterrupted run
+    decoded them one by one: other kernels, so in bfloat16 the logits differ by rounding and a sampled token may
+    differ where two candidates are close.  What must hold: everything finishes, every page comes back, and
+    the greedy tokens of the tight run follow the plain implementation like those of the roomy run."""
+    from nano_vllm_cpp_b200 import SamplingParams
+    prompts = [prompt(case, 20, salt=20 + i) for i in range(3)]
+    sp = SamplingParams(temperature=0.0, max_tokens=30, ignore_eos=True)
+    tight = engine(folders[case], dtype="bfloat16", num_kv_blocks=8)
+    got = [o["token_ids"] for o in tight.generate(prompts, sp)]
+    assert tight.scheduler.num_preemptions > 0
+    assert all(len(t) == 30 for t in got)
+    assert all(p.num_free() == p.num_pages for p in tight.runner.manager.pools)
+    held = [helpers.assert_greedy_follows_plain(folders[case], p, t, "bfloat16", f"preempted {case}") for p, t in zip(prompts, got)]
+    assert sum(held) >= 10
+
+
 def test_steps_queued_ahead_give_the_same_tokens(folders):
     """The engine queues a step before it has read the tokens of the one before (they are fed back on the
     device) and learns of a stop token a step late: every request's tokens equal those of the plain order, with
@@ -99,6 +225,13 @@ def test_steps_queued_ahead_give_the_same_tokens(folders):
         assert a == want and b == want
         if "num_kv_blocks" in kw:
             assert ahead.scheduler.num_preemptions > 0
+        assert all(p.num_free() == p.num_pages for p in ahead.runner.manager.pools)
+    # bfloat16: the two orders run the same kernels on the same batches, so their tokens are equal exactly
+    # (without preemption: a preempted request's second prompt is cut by when its victim was picked)
+    for kw in (dict(), dict(max_num_batched_tokens=16)):
+        a = [o["token_ids"] for o in engine(folders[case], dtype="bfloat16", run_ahead=False, eos=stop, **kw).generate(prompts, sp)]
+        ahead = engine(folders[case], dtype="bfloat16", run_ahead=True, eos=stop, **kw)
+        assert [o["token_ids"] for o in ahead.generate(prompts, sp)] == a
         assert all(p.num_free() == p.num_pages for p in ahead.runner.manager.pools)
 
 

@@ -520,7 +520,7 @@ def test_rope_store(Hq, Hkv, D, rot, dtype):
 
 
 @pytest.mark.parametrize("D,window,ctx,new", [(128, 0, 0, 1100), (64, 300, 500, 700), (128, 0, 16000, 900), (128, 5000, 0, 17000)])
-def test_attention_prefill_tc_long(D, window, ctx, new, monkeypatch):
+def test_attention_prefill_tc_long(D, window, ctx, new):
     """Long portions on the tcgen05 kernel against the mma.sync kernel on the same cache: many row tiles, a
     window that gives early blocks of keys to nobody, and more pages than the kernel keeps in shared memory."""
     o = ops()
@@ -532,18 +532,100 @@ def test_attention_prefill_tc_long(D, window, ctx, new, monkeypatch):
     p0 = torch.tensor([ctx], dtype=torch.int32, device=DEV)
     scale = 1.0 / math.sqrt(D)
     outs = []
-    for legacy in (False, True):
-        if legacy:
-            monkeypatch.setenv("NV_PREFILL_LEGACY", "1")
+    for kernel in ("auto", "mma"):
         out = torch.full((new, Hq * D), float("nan"), dtype=torch.bfloat16, device=DEV)
         err = o.ErrorFlag(DEV)
-        o.attention_prefill(qkv, kc, vc, bt, cu, p0, (new + 63) // 64, scale, window, out, Hq, Hkv, D, err=err)
+        o.attention_prefill(qkv, kc, vc, bt, cu, p0, (new + 63) // 64, scale, window, out, Hq, Hkv, D, err=err,
+                            kernel=kernel)
         err.check("prefill attention")
         outs.append(out)
     close(outs[0], outs[1], 1.5e-2, "tcgen05 vs mma.sync")
+    # row by row, each with its own largest value as the scale: a row that averages thousands of keys is small
+    # beside row 0, which sees one, and must not pass on the strength of that
+    a, b = outs[0].double(), outs[1].double()
+    scale_of_row = b.abs().max(dim=-1, keepdim=True).values.clamp_min(1e-6)
+    worst = float(((a - b).abs() / scale_of_row).max())
+    assert worst <= 4e-2, f"a row differs from the mma.sync kernel by {worst:.3g} of its own largest value"
     for r in (0, new // 2, new - 1):                     # and a few rows against float64
         want = attention_reference(qkv[r, :Hq * D].reshape(Hq, D).cpu(), ks[0], vs[0], ctx + r, scale, window)
         close(outs[0][r], want.reshape(-1), 1.5e-2, f"row {r}")
+
+
+@pytest.mark.parametrize("kernel", ["auto", "mma"])
+@pytest.mark.parametrize("where", ["window edge", "beyond the shared-memory table", "first page of a continued portion"])
+def test_attention_prefill_finds_one_far_key(kernel, where):
+    """One query row in the middle of a row tile matches one key among thousands; that key's value must dominate
+    the row's output, on the tcgen05 kernel and on the mma.sync kernel: at the two sides of a window's edge, in a
+    page beyond the first 1,024 entries of the block table (the part the kernel keeps in shared memory), and in the
+    first page of a portion that continues a cached prefix."""
+    o = ops()
+    Hq = Hkv = 2
+    D, page = 64, 16
+    if where == "window edge":
+        ctx, new, row, window = 600, 300, 170, 400           # the row sits at position 770 and sees keys 371..770
+        fars = [(371, True), (370, False)]
+    elif where == "beyond the shared-memory table":
+        ctx, new, row, window = 16900, 200, 77, 0            # pages 1,024 and later hold keys from 16,384 on
+        fars = [(16500, True), (16385, True)]
+    else:
+        ctx, new, row, window = 130, 200, 90, 0              # the portion starts in the middle of page 8
+        fars = [(130, True), (128, True)]
+    n = ctx + new
+    kc, vc, bt, ks, vs = paged_setup([n], Hkv, D, page, torch.bfloat16, seed=5)
+    cu = torch.tensor([0, new], dtype=torch.int32, device=DEV)
+    p0 = torch.tensor([ctx], dtype=torch.int32, device=DEV)
+    for far, hit in fars:
+        qkv = rnd(new, (Hq + 2 * Hkv) * D, dtype=torch.bfloat16, seed=6)
+        key = ks[0][far, 1].float()
+        qkv[row, D:2 * D] = (key / key.norm() * 40).to(torch.bfloat16).to(DEV)      # head 1 of that row looks for the key
+        out = torch.full((new, Hq * D), float("nan"), dtype=torch.bfloat16, device=DEV)
+        err = o.ErrorFlag(DEV)
+        o.attention_prefill(qkv, kc, vc, bt, cu, p0, (new + 63) // 64, 1.0, window, out, Hq, Hkv, D, err=err, kernel=kernel)
+        err.check("prefill attention")
+        want = attention_reference(qkv[row, :Hq * D].reshape(Hq, D).cpu(), ks[0], vs[0], ctx + row, 1.0, window)
+        close(out[row], want.reshape(-1), 1.5e-2, f"{where}: key {far}")
+        near = float((out[row, D:].float().cpu() - vs[0][far, 1].float()).abs().max())
+        assert (near < 0.1) == hit, f"{where}: key {far} should {'dominate' if hit else 'be out of sight'} ({near:.3g})"
+        other = attention_reference(qkv[row - 1, :Hq * D].reshape(Hq, D).cpu(), ks[0], vs[0], ctx + row - 1, 1.0, window)
+        close(out[row - 1], other.reshape(-1), 1.5e-2, f"{where}: the row before")
+
+
+@pytest.mark.parametrize("D,page", [(64, 16), (128, 16), (48, 32)])
+@pytest.mark.parametrize("window", [0, 50])
+def test_mixed_step_sends_single_rows_and_portions_to_their_kernels(D, page, window):
+    """A step that holds single rows beside portions: the prefill kernel skips entries of one row (min_rows = 2),
+    the decode kernel takes exactly those rows; together they fill every row of the output and equal the plain
+    kernel.  The single rows come first, last and in between."""
+    o = ops()
+    Hq, Hkv = 4, 2
+    ctx_len = [300, 0, 75, 1000, 31, 5]
+    new = [1, 70, 1, 150, 2, 1]
+    lens = [c + n for c, n in zip(ctx_len, new)]
+    kc, vc, bt, ks, vs = paged_setup(lens, Hkv, D, page, torch.bfloat16, seed=D + window)
+    T = sum(new)
+    qkv = rnd(T, (Hq + 2 * Hkv) * D, dtype=torch.bfloat16, seed=12)
+    cu = [0]
+    for n in new:
+        cu.append(cu[-1] + n)
+    pos = torch.tensor([c + i for c, n in zip(ctx_len, new) for i in range(n)], dtype=torch.int32, device=DEV)
+    row_entry = torch.tensor([e for e, n in enumerate(new) for _ in range(n)], dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(D)
+    ref = torch.empty(T, Hq * D, dtype=torch.bfloat16, device=DEV)
+    o.paged_attention_plain(qkv, kc, vc, bt, row_entry, pos, scale, window, ref, Hq, Hkv, D)
+    out = torch.full_like(ref, float("nan"))
+    singles = torch.tensor([cu[e] for e, n in enumerate(new) if n == 1], dtype=torch.int32, device=DEV)
+    err = o.ErrorFlag(DEV)
+    o.attention_decode(qkv, kc, vc, bt, row_entry, pos, scale, window, out, Hq, Hkv, D, 1001, rows=singles, err=err)
+    assert int(torch.isnan(out.float()).any(dim=-1).sum()) == T - 3          # only the three single rows are written
+    tiles = sum((n + 63) // 64 for n in new if n >= 2)
+    o.attention_prefill(qkv, kc, vc, bt, torch.tensor(cu, dtype=torch.int32, device=DEV),
+                        torch.tensor(ctx_len, dtype=torch.int32, device=DEV), tiles, scale, window, out, Hq, Hkv, D,
+                        err=err, min_rows=2)
+    err.check("mixed step")
+    close(out, ref, 1.5e-2, "decode rows + portions vs plain")
+    a, b = out.double(), ref.double()
+    worst = float(((a - b).abs() / b.abs().max(dim=-1, keepdim=True).values.clamp_min(1e-6)).max())
+    assert worst <= 4e-2
 
 
 @pytest.mark.parametrize("Hq,Hkv,D,page", [(3, 1, 32, 16), (4, 4, 16, 16), (6, 2, 48, 32), (4, 2, 128, 16), (2, 1, 256, 16),

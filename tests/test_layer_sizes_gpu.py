@@ -1,17 +1,21 @@
-"""The engine at the layer sizes of the benchmark shapes (two layers, a small vocabulary, random weights made on
-the device): the float32 run must not depend on how a request is cut into steps, and the bfloat16 run on the
-tensor-core kernels must agree with it within the bfloat16 tolerance of the other tests.
+"""The engine at the layer sizes of the benchmark shapes against the plain implementation.
 
-The tiny configurations of the other tests reach none of these sizes (sixty or sixty-four experts, a shared
-expert of four or eight expert widths, widths of 2,048 and 3,584, seven query heads per kv head), and the plain
-CPU implementation is too slow for them, so here the float32 run, which the tiny configurations hold to the
-plain implementation, is the reference.
+Two layers of the Qwen1.5-MoE-A2.7B and of the Qwen2-57B-A14B sizes (sixty or sixty-four experts, a shared expert
+of four or eight expert widths, widths of 2,048 and 3,584, seven query heads per kv head, head size 128), a small
+vocabulary, random weights.  The weights are a function of (seed, tensor name, element index), so the plain
+implementation gets exactly the model that the engine draws for itself: it takes each tensor, drawn by the same
+rule, as float64 when it needs it and runs its formulas on the GPU in float64 (the tiny models' tests run the same
+functions on the CPU).
 
-A bfloat16 run may rightly send a token to another expert than the float32 run does when the token sits on the
+Requests of 1 to 1,024 tokens are run whole, with the last 32 tokens one by one, in portions of changing size
+down to two tokens, and mixed (up to four live requests, portions beside single rows, on a pool so small that
+pages are used again).  Every position's logits are compared: float32 within 1e-5, and bit for bit between the
+schedules; bfloat16 within the tolerance of the other tests.
+
+A bfloat16 run may rightly send a token to another expert than the float64 run does when the token sits on the
 edge between two experts (its K-th and (K+1)-th router logits nearly equal): such a row then differs by more than
-rounding.  With 64 experts that happens to a row in a hundred or so.  The test therefore reads the router's margins
-from the float32 run and lets a row exceed the tolerance only if its margin is small in some layer, and only a
-few rows in all.
+rounding.  With 64 experts that happens to a row in a hundred or so.  A row may therefore exceed the tolerance
+only if the plain implementation's router margin of that row is small in some layer.
 """
 import json
 import os
@@ -19,10 +23,10 @@ import os
 import pytest
 import torch
 
-from helpers import TOL, Replay, assert_close
+import plain_model
+from helpers import TOL, Replay
 
 EDGE_MARGIN = 0.03     # router logits (of order one) closer than this: the bfloat16 run may pick either expert
-MAX_EDGE_ROWS = 3
 
 pytestmark = pytest.mark.gpu
 
@@ -39,83 +43,154 @@ SHAPES = {
                 num_experts_per_tok=8, moe_intermediate_size=2560, shared_expert_intermediate_size=20480,
                 intermediate_size=18944),
 }
-N = 200            # tokens of the request
-WANT = [0, 1, 15, 16, 17, 63, 64, 127, 128, 150] + list(range(N - 33, N))
+SEED, STD, NORM_STD = 5, 0.02, 0.1
+LENGTHS = {"a": 1024, "b": 1, "c": 200, "d": 77, "e": 333, "f": 16, "g": 64}
+POOL_TOKENS = 1536      # a + c + d + e's start are live together; all seven need 1,715: pages are used again
+
+# the mixed schedule: per step [(request, tokens)], then the requests that end after it
+MIXED = [
+    ([("a", 500), ("b", 1)], ["b"]),
+    ([("a", 500), ("c", 100), ("d", 2)], []),
+    ([("a", 23), ("c", 99), ("d", 68)], []),
+    ([("a", 1), ("c", 1), ("d", 7), ("e", 50)], ["a", "c", "d"]),
+    ([("e", 1), ("f", 16)], ["f"]),
+    ([("e", 281), ("g", 62)], []),
+    ([("e", 1), ("g", 2)], ["e", "g"]),
+]
 
 
-def run(folder, dtype, cuts, seed):
-    """Logits at the wanted positions of one request fed in portions of the given sizes."""
-    from nano_vllm_cpp_b200.engine.runner import ModelRunner
-    runner = ModelRunner(folder, dtype=dtype, max_tokens=1024, max_requests=4, random_seed=seed)
-    ids = torch.randint(0, BASE["vocab_size"], (N,), generator=torch.Generator().manual_seed(11)).tolist()
-    other = torch.randint(0, BASE["vocab_size"], (40,), generator=torch.Generator().manual_seed(12)).tolist()
+class DrawnWeights:
+    """name -> float64 tensor on the GPU, drawn when asked for by the random-weights rule."""
+
+    def __init__(self, cfg):
+        from nano_vllm_cpp_b200.config.registry import get_architecture
+        from nano_vllm_cpp_b200.parts import Model
+        from nano_vllm_cpp_b200.weights import RandomSource
+        arch = get_architecture(cfg["architectures"][0])
+        self.specs = Model(arch.build_model(arch.config_from_dict(cfg))).tensor_specs()
+        self.source = RandomSource(self.specs, SEED, STD, NORM_STD, "cuda", torch.bfloat16)
+
+    def __contains__(self, name):
+        return name in self.specs
+
+    def __getitem__(self, name):
+        return self.source.stored(name).double()
+
+
+def request_ids(rid):
+    g = torch.Generator().manual_seed(100 + ord(rid))
+    return torch.randint(0, BASE["vocab_size"], (LENGTHS[rid],), generator=g).tolist()
+
+
+def schedules():
+    """name -> list of (parts [(request, tokens)], ends)."""
+    whole = [([(r, n)], [r]) for r, n in LENGTHS.items()]
+    tail = []
+    for r, n in LENGTHS.items():
+        head = max(n - 32, 1)
+        tail.append(([(r, head)], []))
+        tail += [([(r, 1)], []) for _ in range(n - head)]
+        tail[-1] = (tail[-1][0], [r])
+    portions = []
+    sizes = [7, 64, 2, 33, 16, 1, 45, 128, 3, 2, 300, 2, 5]
+    for r, n in LENGTHS.items():
+        at, k = 0, 0
+        while at < n:
+            s = min(sizes[k % len(sizes)], n - at)
+            if n - at - s == 1:          # never leave a single last token behind: the last portion has two
+                s = n - at if s == 1 else s - 1
+            portions.append(([(r, s)], []))
+            at, k = at + s, k + 1
+        portions[-1] = (portions[-1][0], [r])
+    return {"whole": whole, "last 32 one by one": tail, "portions": portions, "mixed": MIXED}
+
+
+def run_schedule(runner, steps):
+    """All positions' logits of all requests: {request: float32 [n, V]}."""
+    ids = {r: request_ids(r) for r in LENGTHS}
+    at = {r: 0 for r in LENGTHS}
     rp = Replay(runner)
-    at = 0
-    for k, n in enumerate(cuts):
-        places = [w - at for w in WANT if at <= w < at + n]
-        parts = [("a", ids[at:at + n], places)]
-        if k % 2 == 1 and k // 2 < len(other):       # another request's tokens ride along in every second step
-            parts.append(("b", other[k // 2:k // 2 + 1], []))
-        rp.step(parts)
-        at += n
-    assert at == N
-    rows = torch.stack([rp.logits[("a", w)] for w in WANT])
-    runner.close("a")
-    del rp, runner
-    torch.cuda.empty_cache()
-    return rows
+    out = {}
+    for parts, ends in steps:
+        entries = []
+        for r, n in parts:
+            entries.append((r, ids[r][at[r]:at[r] + n], True))
+            at[r] += n
+        rp.step(entries)
+        for r in ends:
+            assert at[r] == LENGTHS[r]
+            out[r] = torch.stack([rp.logits[(r, p)] for p in range(LENGTHS[r])])
+        rp.step([], end=ends)
+    assert sorted(out) == sorted(LENGTHS)
+    for pool in runner.manager.pools:
+        assert pool.num_free() == pool.num_pages
+    return out
 
 
-def router_margins(folder, cuts, seed, monkeypatch):
-    """The float32 run of the whole request with, per position, the smallest gap between the K-th and the
-    (K+1)-th router logit over the layers."""
-    from nano_vllm_cpp_b200.parts import feedforward
-    seen = []
-    inner = feedforward.small_linear
-
-    def spy(ctx, h32, w):
-        out = inner(ctx, h32, w)
-        seen.append(out.detach().float().cpu())
-        return out
-
-    monkeypatch.setattr(feedforward, "small_linear", spy)
-    rows = run(folder, "float32", cuts, seed)
-    monkeypatch.undo()
-    return rows, seen
-
-
-def assert_close_but_for_edges(got, ref, margin_of_row, what):
-    tol = TOL["bfloat16"]
-    bound = tol["abs"] + tol["rel"] * float(ref.abs().max())
-    err = (got.double() - ref.double()).abs().max(-1).values
-    off = [i for i in range(len(err)) if float(err[i]) > bound]
-    not_edge = [(i, float(err[i]), margin_of_row[i]) for i in off if margin_of_row[i] >= EDGE_MARGIN]
-    assert not not_edge, f"{what}: rows (index, error, router margin) beyond {bound:.3g} that sit on no edge: {not_edge}"
-    assert len(off) <= MAX_EDGE_ROWS, f"{what}: {len(off)} rows beyond {bound:.3g}"
-
-
-@pytest.mark.parametrize("shape", sorted(SHAPES))
-def test_benchmark_layer_sizes(shape, tmp_path, monkeypatch):
-    cfg = SHAPES[shape]
-    folder = str(tmp_path / shape)
-    os.makedirs(folder)
+@pytest.fixture(scope="module", params=sorted(SHAPES))
+def shape(request, tmp_path_factory):
+    """(name, config, folder, plain logits and router margins per request)."""
+    cfg = SHAPES[request.param]
+    folder = str(tmp_path_factory.mktemp(request.param))
     with open(os.path.join(folder, "config.json"), "w") as f:
         json.dump(cfg, f)
-    whole = [N]
-    tail = [N - 32] + [1] * 32                                     # the last 32 tokens one by one
-    pieces = [7, 64, 2, 33, 16, 1, 45]
-    pieces += [N - sum(pieces) - 2, 2]                              # portions of changing size, down to two tokens
-    ref, logits = router_margins(folder, whole, 5, monkeypatch)
-    assert torch.isfinite(ref).all() and float(ref.abs().max()) > 0.05
-    E, K = cfg["num_experts"], cfg["num_experts_per_tok"]
-    logits = [x for x in logits if x.shape[1] >= E]                 # (the shared expert's gate may be a call of its own)
-    assert len(logits) == cfg["num_hidden_layers"] and all(x.shape[0] == N for x in logits)
-    margin = torch.full((N,), float("inf"))
-    for x in logits:
-        top = torch.sort(x[:, :E], dim=-1, descending=True).values
-        margin = torch.minimum(margin, top[:, K - 1] - top[:, K])
-    margin_of_row = [float(margin[w]) for w in WANT]
-    for name, cuts in (("last 32 one by one", tail), ("portions", pieces)):
-        assert_close(run(folder, "float32", cuts, seed=5), ref, "float32", f"{shape} float32 {name}")
-    for name, cuts in (("whole", whole), ("last 32 one by one", tail), ("portions", pieces)):
-        assert_close_but_for_edges(run(folder, "bfloat16", cuts, seed=5), ref, margin_of_row, f"{shape} bfloat16 {name}")
+    W = DrawnWeights(cfg)
+    plain, margin = {}, {}
+    for r in LENGTHS:
+        ms = []
+        plain[r] = plain_model.forward(cfg, W, request_ids(r), margins=ms).cpu()
+        assert len(ms) == cfg["num_hidden_layers"]
+        margin[r] = torch.stack(ms).min(dim=0).values
+    del W
+    torch.cuda.empty_cache()
+    return request.param, cfg, folder, plain, margin
+
+
+def make_runner(folder, dtype):
+    from nano_vllm_cpp_b200.engine.runner import ModelRunner
+    return ModelRunner(folder, dtype=dtype, max_tokens=POOL_TOKENS, max_requests=4, max_model_len=1024,
+                       random_seed=SEED, std=STD, norm_std=NORM_STD)
+
+
+def test_float32_against_plain_and_bit_equal_between_schedules(shape):
+    name, cfg, folder, plain, _ = shape
+    runner = make_runner(folder, "float32")
+    tol = TOL["float32"]
+    first = None
+    for sname, steps in schedules().items():
+        got = run_schedule(runner, steps)
+        for r in LENGTHS:
+            want = plain[r]
+            assert float(want.abs().max()) > 0.5
+            bound = tol["abs"] + tol["rel"] * float(want.abs().max())
+            err = float((got[r].double() - want).abs().max())
+            assert err <= bound, f"{name} float32 {sname} request {r}: max error {err:.3g} > {bound:.3g}"
+        if first is None:
+            first = got
+        else:
+            for r in LENGTHS:
+                assert torch.equal(got[r], first[r]), f"{name} float32: {sname} differs from whole in request {r}"
+    del runner
+    torch.cuda.empty_cache()
+
+
+def test_bfloat16_against_plain(shape):
+    name, cfg, folder, plain, margin = shape
+    runner = make_runner(folder, "bfloat16")
+    tol = TOL["bfloat16"]
+    for sname, steps in schedules().items():
+        got = run_schedule(runner, steps)
+        edge_rows = rows = 0
+        for r in LENGTHS:
+            want = plain[r]
+            bound = tol["abs"] + tol["rel"] * float(want.abs().max())
+            err = (got[r].double() - want).abs().max(dim=-1).values
+            off = torch.nonzero(err > bound).reshape(-1).tolist()
+            not_edge = [(p, float(err[p]), float(margin[r][p])) for p in off if float(margin[r][p]) >= EDGE_MARGIN]
+            assert not not_edge, (f"{name} bfloat16 {sname} request {r}: rows (position, error, router margin) beyond "
+                                  f"{bound:.3g} that sit on no edge: {not_edge[:8]}")
+            edge_rows += len(off)
+            rows += LENGTHS[r]
+        assert edge_rows <= 0.03 * rows, f"{name} bfloat16 {sname}: {edge_rows} of {rows} rows beyond the tolerance"
+    del runner
+    torch.cuda.empty_cache()

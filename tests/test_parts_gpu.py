@@ -156,7 +156,8 @@ def test_attention_part_in_portions(dtype, Hq, Hkv, D, window, bias):
     want_a = pm.attention_layer(xa.double(), W, "", cfg, 0, list(range(40)))
     want_b = pm.attention_layer(xb.double(), W, "", cfg, 0, list(range(50)))
     # step 1: a whole minus one row (39 rows), b's first 20 rows.  Pages: a -> 0..2, b -> 3..6
-    from nano_vllm_cpp_b200.engine.batch import StepEntry, EntryInfo, build_batch
+    from nano_vllm_cpp_b200.engine.batch import StepEntry, EntryInfo
+    from batch_builder import build_batch
     ta, tb = [0, 1, 2], [3, 4, 5, 6]
 
     def run(parts):
@@ -354,6 +355,111 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
     for r in ids:
         got = torch.stack([rp.logits[(r, p)] for p in range(len(ids[r]))])
         helpers.assert_close(got, toy_plain(cfg, W, ids[r]), "float32", f"toy request {r}")
+
+
+def define_toy_hybrid():
+    """The state mixer in layer 0 and paged attention in layer 1: a model whose requests hold a state slot *and*
+    pages, so that the engine's scheduler can run out of pages and preempt it."""
+    from nano_vllm_cpp_b200.parts import PartSpec, LayerSpec, ModelSpec
+    from nano_vllm_cpp_b200.config import register_architecture
+    define_toy()
+
+    def build(cfg):
+        H = cfg["hidden_size"]
+        norm = PartSpec("rmsnorm", dict(size=H, eps=cfg["rms_norm_eps"]))
+        mlp = PartSpec("dense_swiglu", dict(hidden_size=H, intermediate_size=cfg["intermediate_size"]))
+        attn = PartSpec("paged_attention", dict(
+            hidden_size=H, num_heads=cfg["num_attention_heads"], num_kv_heads=cfg["num_key_value_heads"],
+            head_dim=cfg["head_dim"], bias=False,
+            position=PartSpec("rotary_neox", dict(rotary_dim=cfg["head_dim"], theta=cfg["rope_theta"]))))
+        names = {"norm1": "ln1.", "norm2": "ln2.", "feed_forward": "mlp."}
+        layers = [LayerSpec(norm1=norm, mixer=PartSpec("toy_decaying_sum", dict(hidden_size=H, decay=cfg["decay"])),
+                            norm2=norm, feed_forward=mlp, names=dict(names, mixer="toy.")),
+                  LayerSpec(norm1=norm, mixer=attn, norm2=norm, feed_forward=mlp, names=dict(names, mixer="self_attn."))]
+        return ModelSpec(vocab_size=cfg["vocab_size"], hidden_size=H, layers=layers, final_norm=norm,
+                         tie_word_embeddings=True, init_std=0.1)
+
+    register_architecture("ToyHybridForCausalLM", dict, build)
+
+
+def toy_hybrid_plain(cfg, W, ids):
+    x = pm.embedding(W["model.embed_tokens.weight"], ids)
+    eps = cfg["rms_norm_eps"]
+    p = "model.layers.0."
+    h = pm.rms_norm(x, W[p + "ln1.weight"], eps)
+    s = torch.zeros(cfg["hidden_size"], dtype=torch.float64)
+    out = []
+    for t in range(len(ids)):
+        s = cfg["decay"] * s + h[t]
+        out.append(W[p + "toy.mix.weight"] @ s)
+    x = x + torch.stack(out)
+    x = x + pm.dense_mlp(pm.rms_norm(x, W[p + "ln2.weight"], eps), W, p + "mlp.")
+    p = "model.layers.1."
+    h = pm.rms_norm(x, W[p + "ln1.weight"], eps)
+    x = x + pm.attention_layer(h, W, p + "self_attn.", cfg, 1, list(range(len(ids))))
+    x = x + pm.dense_mlp(pm.rms_norm(x, W[p + "ln2.weight"], eps), W, p + "mlp.")
+    return pm.rms_norm(x, W["model.norm.weight"], eps) @ W["model.embed_tokens.weight"].T
+
+
+def test_toy_state_through_the_engine(tmp_path):
+    """The state of a request starts from zero whoever held its slot before, also after a preemption, and a model
+    with a state never shares prefix pages: two requests one after the other on the only slot, two prompts with 32
+    common tokens under an engine that was asked for prefix sharing, and a pool so small that requests are
+    preempted.  Greedy tokens equal the plain restatement's."""
+    from nano_vllm_cpp_b200 import LLMEngine, SamplingParams
+    from nano_vllm_cpp_b200.weights import write_model_folder
+    define_toy_hybrid()
+    cfg = dict(architectures=["ToyHybridForCausalLM"], vocab_size=90, hidden_size=40, num_hidden_layers=2,
+               intermediate_size=56, rms_norm_eps=1e-5, decay=0.9, num_attention_heads=2, num_key_value_heads=1,
+               head_dim=16, rope_theta=10000.0)
+    mdir = write_model_folder(cfg, str(tmp_path / "hybrid"), seed=5, norm_std=0.1, dtype="float32")
+    _, W = pm.read_folder(mdir)
+
+    def plain_greedy(ids, n):
+        ids = list(ids)
+        for _ in range(n):
+            ids.append(int(torch.argmax(toy_hybrid_plain(cfg, W, ids)[-1])))
+        return ids[-n:]
+
+    g = np.random.RandomState(1)
+    common = [int(t) for t in g.randint(0, 90, size=32)]
+    prompts = [common + [int(t) for t in g.randint(0, 90, size=n)] for n in (3, 9)] + [[int(t) for t in g.randint(0, 90, size=20)]]
+    want = [plain_greedy(p, 12) for p in prompts]
+    sp = SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)
+    # one slot: every request takes over the slot of the one before it
+    eng = LLMEngine(mdir, max_model_len=128, num_kv_blocks=16, dtype="float32", max_num_seqs=1, enable_prefix_caching=True)
+    assert not eng.runner.manager.prefix_caching and eng.runner.cache.has_state
+    assert [o["token_ids"] for o in eng.generate(prompts, sp)] == want
+    # all live together; the second prompt must not adopt the first's pages
+    eng = LLMEngine(mdir, max_model_len=128, num_kv_blocks=16, dtype="float32", max_num_seqs=4, enable_prefix_caching=True)
+    assert [o["token_ids"] for o in eng.generate(prompts, sp)] == want
+    # 8 pages = 128 tokens for 44 + 53 + 32 at the end: somebody is preempted and starts again from zero
+    eng = LLMEngine(mdir, max_model_len=128, num_kv_blocks=8, dtype="float32", max_num_seqs=4)
+    assert [o["token_ids"] for o in eng.generate(prompts, sp)] == want
+    assert eng.scheduler.num_preemptions > 0
+    assert eng.runner.manager.free_slots() == 4
+
+
+def test_a_model_without_pages_has_no_pool(tmp_path):
+    """The toy model whose mixers keep only a state: no page pool is made, however much memory is free, and the
+    engine admits requests by state slots."""
+    from nano_vllm_cpp_b200 import LLMEngine, SamplingParams
+    from nano_vllm_cpp_b200.weights import write_model_folder
+    define_toy()
+    cfg = dict(architectures=["ToyStateForCausalLM"], vocab_size=90, hidden_size=40, num_hidden_layers=2,
+               intermediate_size=56, rms_norm_eps=1e-5, decay=0.9)
+    mdir = write_model_folder(cfg, str(tmp_path / "toy"), seed=3, norm_std=0.1, dtype="float32")
+    _, W = pm.read_folder(mdir)
+    eng = LLMEngine(mdir, max_model_len=64, num_kv_blocks=0, dtype="float32", max_num_seqs=2)
+    assert eng.runner.manager.pools == [] and eng.runner.num_pages == 0
+    g = np.random.RandomState(2)
+    prompts = [[int(t) for t in g.randint(0, 90, size=n)] for n in (5, 11, 8)]
+    outs = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True))
+    for p, o in zip(prompts, outs):
+        ids = list(p)
+        for _ in range(6):
+            ids.append(int(torch.argmax(toy_plain(cfg, W, ids)[-1])))
+        assert o["token_ids"] == ids[len(p):]
 
 
 # ------------------------------------------------------------------------------- two more toy parts: a position encoding and a routing feed-forward

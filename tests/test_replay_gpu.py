@@ -9,12 +9,12 @@ from helpers import Replay, prompt
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"A": [5, 17, 33, 70], "B": [1, 9, 24, 40, 70], "C": [2, 33, 64, 129, 200]}
+LENGTHS = {"A": [5, 17, 33, 70], "A8": [5, 17, 33, 70], "B": [1, 9, 24, 40, 70], "C": [2, 33, 64, 129, 200]}
 
 
 @pytest.fixture(scope="module")
 def folders(tmp_path_factory):
-    return {c: helpers.model_folder(c, tmp_path_factory) for c in ("A", "B", "C")}
+    return {c: helpers.model_folder(c, tmp_path_factory) for c in ("A", "A8", "B", "C")}
 
 
 def make_runner(mdir, dtype, max_tokens, max_requests=4):
@@ -23,7 +23,7 @@ def make_runner(mdir, dtype, max_tokens, max_requests=4):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("case", ["A", "B", "C"])
+@pytest.mark.parametrize("case", ["A", "A8", "B", "C"])
 def test_whole(case, dtype, folders):
     runner = make_runner(folders[case], dtype, 256 if case == "C" else 128)
     rp = Replay(runner)
@@ -34,7 +34,7 @@ def test_whole(case, dtype, folders):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("case", ["A", "B", "C"])
+@pytest.mark.parametrize("case", ["A", "A8", "B", "C"])
 def test_last_32_one_by_one(case, dtype, folders):
     runner = make_runner(folders[case], dtype, 128)
     rp = Replay(runner)
@@ -49,7 +49,7 @@ def test_last_32_one_by_one(case, dtype, folders):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("case", ["A", "B", "C"])
+@pytest.mark.parametrize("case", ["A", "A8", "B", "C"])
 def test_portions_of_changing_size(case, dtype, folders):
     runner = make_runner(folders[case], dtype, 128)
     rp = Replay(runner)
@@ -64,7 +64,7 @@ def test_portions_of_changing_size(case, dtype, folders):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("case", ["A", "B", "C"])
+@pytest.mark.parametrize("case", ["A", "A8", "B", "C"])
 def test_mixed_with_page_reuse(case, dtype, folders):
     """Up to four live requests; portions of some beside decode tokens of others; the pool holds 192
     tokens while the requests need 5 x 64 in turn, so finished requests' pages are used again."""
@@ -92,6 +92,39 @@ def test_mixed_with_page_reuse(case, dtype, folders):
         rp.compare(r, ids[r], folders[case], dtype, f"mixed {case}")
     for pool in runner.manager.pools:
         assert pool.num_free() == pool.num_pages
+
+
+@pytest.mark.parametrize("case", ["A", "A8", "B", "C"])
+def test_float32_logits_are_bit_equal_however_the_work_is_cut(case, folders):
+    """The float32 run uses one kernel per operation whatever the batch is, each output a sum in one fixed order:
+    a position's logits are the same bits whole, one by one, in portions, beside other requests and on other pages."""
+    runner = make_runner(folders[case], "float32", 256)
+    ids = prompt(case, 101, salt=11)
+    other = prompt(case, 60, salt=12)
+
+    def collect(rp, rid="x"):
+        return torch.stack([rp.logits[(rid, p)] for p in range(101)])
+
+    rp = Replay(runner)
+    rp.step([("x", ids, True)], end=["x"])
+    whole = collect(rp)
+    rp = Replay(runner)
+    rp.step([("o", other[:20], [])])                          # another request first: x lies on other pages
+    rp.step([("x", ids[:69], True), ("o", other[20:21], [])])
+    for t in range(69, 101):
+        rp.step([("x", ids[t:t + 1], [0])] + ([("o", other[t - 48:t - 47], [])] if t % 2 else []))
+    assert torch.equal(collect(rp), whole), "last 32 one by one"
+    rp.step([], end=["x", "o"])
+    rp = Replay(runner)
+    at = 0
+    for k, n in enumerate([7, 2, 16, 1, 3, 31, 2, 17, 2, 5, 15]):
+        parts = [("x", ids[at:at + n], True)]
+        if k % 3 == 0:
+            parts.insert(0, ("o", other[k:k + 3], []))
+        rp.step(parts)
+        at += n
+    assert at == 101 and torch.equal(collect(rp), whole), "portions beside another request"
+    rp.step([], end=["x", "o"])
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
