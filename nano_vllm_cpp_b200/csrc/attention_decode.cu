@@ -673,6 +673,10 @@ NV_API int nv_attention_decode_splits(int rows, int Hq, int Hkv, int max_context
   return best;
 }
 
+// The kernel is launched as a programmatic dependent of the kernel before it on the stream and reads the index
+// arrays, the block table and every page but each row's newest one before that kernel has ended: the kernel
+// directly before it may write only the query rows and the newest page of each row (the engine's rotary kernel
+// over single rows does exactly that).
 NV_API int nv_attention_decode(const void* qkv, int q_dt, int q_stride, const void* kc, const void* vc, int cache_dt,
                                const int* block_table, int max_blocks, const int* row_entry, const int* positions,
                                const int* rows, int R, float scale, int window, void* out, int out_dt, int Hq,
@@ -749,7 +753,7 @@ int* g_noalloc_err_ptr[MAX_DEVICES] = {};
 }  // namespace
 
 NV_API int nv_attention_decode_noalloc_max_rows(int Hq, int D, int splits) {
-  if (Hq <= 0 || D <= 0) return 0;
+  if (Hq <= 0 || D <= 0 || D > 256 || D % 8) return 0;
   if (splits <= 1) return 0x7fffffff;      // one split writes its result directly and needs no scratch
   return (int)((long long)NV_NOALLOC_SCRATCH_FLOATS / ((long long)Hq * splits * (D + 2)));
 }
@@ -760,6 +764,10 @@ NV_API int nv_attention_decode_noalloc(const void* qkv, int q_dt, int q_stride, 
                                        void* out, int out_dt, int Hq, int Hkv, int D, int page, int num_pages,
                                        int splits, cudaStream_t stream) {
   if (splits < 1) splits = 1;
+  // sizes that nv_attention_decode refuses are refused here first, so that the size test below sees sane numbers
+  if (!dt_ok(q_dt) || !dt_ok(cache_dt) || !dt_ok(out_dt)) return NV_ERR_BAD_DTYPE;
+  if (R < 0 || splits > 1024) return NV_ERR_BAD_SIZE;
+  if (D <= 0 || D > 256 || D % 8 || Hkv <= 0 || Hq <= 0 || Hq % Hkv || page <= 0 || page % 16) return NV_ERR_UNSUPPORTED;
   if (nv_attention_decode_scratch_floats(R, Hq, D, splits) > (long long)NV_NOALLOC_SCRATCH_FLOATS)
     return NV_ERR_NOALLOC_TOO_LARGE;
   int dev = -1;

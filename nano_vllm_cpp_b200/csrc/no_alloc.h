@@ -20,6 +20,18 @@
 //   * All calls share the one array, and it keeps the last call's contents.  Nothing in it has to
 //     start at zero: every slot a call reads was written by that call first.  Two calls that overlap
 //     on the GPU (different streams, no ordering between them) race on the array; order them.
+//   * The first call on a device must not run at the same time as another call on that device from
+//     a second host thread (the address look-up is not guarded); once it has returned, calls may
+//     come from any thread.
+//   * What runs before it on the stream: like nv_attention_decode, the kernel is launched as a
+//     programmatic dependent of the kernel before it and reads `positions`, `rows`, `row_entry`, the
+//     block table and every page but each row's newest one before that kernel has finished.  So the
+//     kernel directly before it on the stream may write nothing of these but the query rows and the
+//     newest page of each row (this library's nv_rope_store over single rows is such a kernel).  If
+//     the kernel before it writes older pages or the index arrays (nv_rope_store over a portion of
+//     several tokens does), put any other kernel or an event between the two, or switch dependent
+//     launches off with nv_set_dependent_launch(0).
+//   * The status (below) stays set once a kernel has reported trouble, until the process ends.
 #pragma once
 
 #include <cuda_runtime.h>
@@ -40,7 +52,8 @@ int nv_attention_decode_noalloc(const void* qkv, int q_dt, int q_stride, const v
                                 const int* rows, int R, float scale, int window, void* out, int out_dt, int Hq,
                                 int Hkv, int D, int page, int num_pages, int splits, cudaStream_t stream);
 
-// Largest number of rows one call can take for these sizes (0 if not even one fits).
+// Largest number of rows one call can take for these sizes (0 if not even one fits, or if the kernel does not
+// take the sizes at all: Hq or D not positive, D above 256 or no multiple of 8).
 int nv_attention_decode_noalloc_max_rows(int Hq, int D, int splits);
 
 // 0 while no kernel launched through this entry point has reported trouble on the current device (a block

@@ -444,9 +444,10 @@ class MoeAlignment:
         return self.primary
 
 
-def moe_align(idx, K: int, al: MoeAlignment, err: ErrorFlag, spread_last: int = 0) -> None:
+def moe_align(idx, K: int, al: MoeAlignment, err: ErrorFlag, spread_last: int = 0, static_last: int = 0) -> None:
     """``spread_last``: the tiles of the last so many experts (ones that every row visits) are spread evenly through
-    the tile lists instead of standing at their end."""
+    the tile lists instead of standing at their end.  ``static_last`` instead: those experts' pairs sit in row order
+    at the end of the permutation and get no tiles (``StaticTiles`` lists them; they can run before the routing)."""
     _cuda_contig(idx)
     _i32(idx)
     T = idx.numel() // K
@@ -457,7 +458,7 @@ def moe_align(idx, K: int, al: MoeAlignment, err: ErrorFlag, spread_last: int = 
                               _p(al.tile_expert), _p(al.tile_row0), _p(al.tile_rows), _p(al.num_tiles), _p(err.t),
                               c_int(s2.tile_m if s2 else 0), _p(s2.tile_expert if s2 else None), _p(s2.tile_row0 if s2 else None),
                               _p(s2.tile_rows if s2 else None), _p(s2.num_tiles if s2 else None), c_int(spread_last),
-                              _stream()),
+                              c_int(static_last), _stream()),
            "moe_align")
 
 
@@ -495,7 +496,7 @@ class StaticTiles:
     T * K routed pairs: what ``moe_route_small(static=True)`` leaves out of its list."""
 
     def __init__(self, T: int, K: int, E: int, C: int, device):
-        self.tile_m = 16 if T <= 16 else (32 if T <= 32 else 64)
+        self.tile_m = 16 if T <= 16 else (32 if T <= 32 else (64 if T <= 64 else 128))
         experts, row0, rows = [], [], []
         for c in range(C):
             for r in range(0, T, self.tile_m):
@@ -647,16 +648,18 @@ def gemm_fast(a, w, out, *, bias=None, a_rows=None, swiglu=False, M=None, err=No
                         c_longlong(out.stride(0)), c_int(1 if swiglu else 0), c_int(n_tile), c_int(splits),
                         _p(scratch), _p(None), _p(None), _p(None), _p(None), c_int(0), c_int(0),
                         _p(err.t if err is not None else _global_err().t), c_int(_early()), c_int(0), c_int(0),
-                        _stream()), f"tc_gemm N={rows_w} K={K}", 2.0 * M * rows_w * K,
+                        c_int(0), _stream()), f"tc_gemm N={rows_w} K={K}", 2.0 * M * rows_w * K,
            w.element_size() * rows_w * K + a.element_size() * M * K + out.element_size() * M * N)
 
 
 def gemm_fast_grouped(a, w, out, align, *, a_rows=None, swiglu=False, err=None, tiles=None, tiles_ready=False,
-                      x_rows=None) -> None:
+                      x_rows=None, max_ctas: int = 0) -> None:
     """Tensor-core form of the grouped ``gemm_plain``; ``tiles`` (a TileList of ``align``) picks the token tile.
 
     ``x_rows`` = (sub, mod): a tile whose outputs are rows r.. takes rows ``(r - sub) % mod``.. of ``a`` (several
     experts that all take the same few rows, their outputs one segment after the other).
+
+    ``max_ctas`` > 0 caps the grid, for a product that runs beside other kernels and must leave them room.
 
     ``tiles_ready``: the tile lists were complete before the kernel that precedes this product on the stream
     started, so the product may start beside that kernel and fetch its first weights (it reads the lists at
@@ -676,7 +679,8 @@ def gemm_fast_grouped(a, w, out, align, *, a_rows=None, swiglu=False, err=None, 
                             c_int(1 if swiglu else 0), c_int(tl.tile_m), c_int(1), _p(None), _p(tl.tile_expert),
                             _p(tl.tile_row0), _p(tl.tile_rows), _p(tl.num_tiles), c_int(tl.max_tiles),
                             c_int(rows_w), _p(err.t if err is not None else _global_err().t),
-                            c_int(_early() if tiles_ready else 0), c_int(x_sub), c_int(x_mod), _stream()),
+                            c_int(_early() if tiles_ready else 0), c_int(x_sub), c_int(x_mod), c_int(max_ctas),
+                            _stream()),
            f"tc_gemm_grouped N={rows_w} K={K}")
 
 

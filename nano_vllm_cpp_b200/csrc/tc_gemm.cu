@@ -531,7 +531,7 @@ NV_API int nv_tc_gemm(const void* X, long long ldx, int M_tok, const void* W, in
                       const void* bias, int bias_dt, void* out, int out_dt, long long ldo, int swiglu, int n_tile,
                       int splits, float* scratch, const int* tile_expert, const int* tile_row0,
                       const int* tile_rows, const int* num_tiles, int max_tiles, int rows_per_expert, int* err,
-                      int early, int x_sub, int x_mod, cudaStream_t stream) {
+                      int early, int x_sub, int x_mod, int max_ctas, cudaStream_t stream) {
   if (!dt_ok(out_dt) || (bias && !dt_ok(bias_dt))) return NV_ERR_BAD_DTYPE;
   if (K % 8 || ldx % 8 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return NV_ERR_UNSUPPORTED;  // TMA: 16-byte rules
   if (n_tile < 16 || n_tile > 256 || (n_tile & (n_tile - 1))) return NV_ERR_BAD_SIZE;
@@ -604,7 +604,10 @@ NV_API int nv_tc_gemm(const void* X, long long ldx, int M_tok, const void* W, in
 
   const long long y_tiles = grouped ? max_tiles : (M_tok + n_tile - 1) / n_tile;
   const long long total = (long long)a.n_blocks * y_tiles * a.splits;     // an upper bound when grouped
-  const long long resident = (long long)num_sms * (pair ? 2 : 1);
+  // `max_ctas` > 0 caps the grid: a product that runs beside other kernels on a second stream leaves them
+  // multiprocessors (its CTAs each hold one for the whole tile list)
+  long long resident = (long long)num_sms * (pair ? 2 : 1);
+  if (max_ctas > 0 && max_ctas < resident) resident = max_ctas;
   dim3 grid((unsigned)(total < resident ? total : resident));
   // a last wave with tiles for less than half of the CTAs: cut those tiles into two or four token parts
   a.rest_first = 0;

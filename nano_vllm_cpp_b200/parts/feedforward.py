@@ -11,6 +11,10 @@ from .registry import register_part
 
 # Batches of up to this many rows run the shared expert's chunks on a second stream beside the routing.
 SIDE_MAX_ROWS = 64
+# Prompts: the shared expert's two products run beside the routing chain (router product, top-k, permutation, row
+# copy) on a second stream with their grid capped to this share of the multiprocessors, which leaves the chain's
+# kernels room; the routed experts' products follow on the first stream.
+SIDE_GRID_SHARE = 0.88
 # Permutation buffers are kept per batch size; beyond this many sizes the oldest set is dropped.
 MAX_ALIGNMENTS = 16
 
@@ -166,6 +170,8 @@ class SparseMoeSwiGLU(FeedForward):
         if (fast and C and T <= SIDE_MAX_ROWS and al.secondary is None
                 and ops.moe_route_small_usable(T, self.E, self.K, C, self.hidden)):
             return self._forward_beside(h, logits, gate_logit, idx, score, al)
+        if fast and C and T >= 256 and al.secondary is None:
+            return self._forward_beside(h, logits, gate_logit, idx, score, al, many=True)
         if fast and al.secondary is None and ops.moe_route_small_usable(T, self.E, self.K, C, self.hidden):
             x_sorted = ops.moe_route_small(logits, self.K, self.renorm, C, gate_logit, idx, score, al, ctx.err,
                                            x=None)   # one block copies rows slower than the copy kernel does
@@ -191,15 +197,20 @@ class SparseMoeSwiGLU(FeedForward):
         return RowMix(y, al.pair_pos[:T * KT].view(T, KT), score, shared, gate_logit if shared is not None else None)
 
 
-    def _forward_beside(self, h, logits, gate_logit, idx, score, al):
-        """Few rows: the shared expert's chunks need no routing, so their two products run on a second stream
-        beside the routing and the row copy, which keep few multiprocessors busy; the routed experts' products
-        follow on the first stream and write the other rows of the same two buffers."""
+    def _forward_beside(self, h, logits, gate_logit, idx, score, al, many=False):
+        """The shared expert's chunks need no routing, so their two products run on a second stream beside the
+        routing and the row copy, which keep few multiprocessors busy; the routed experts' products follow on the
+        first stream and write the other rows of the same two buffers.  Few rows (decoding): one launch routes.
+        ``many`` rows (a prompt): the routing is three kernels that take a tenth of the layer's time, and the side
+        products leave them some multiprocessors."""
         ctx, T, K, C, dev = self.ctx, h.shape[0], self.K, self.virtual, h.device
         KT = K + C
         key = (T, dev)
         st = self._static.get(key)
         if st is None:
+            big = [k for k in self._static if k[0] > SIDE_MAX_ROWS]      # (small ones may belong to captured steps)
+            if len(big) >= MAX_ALIGNMENTS:
+                self._static.pop(big[0])
             st = self._static[key] = ops.StaticTiles(T, K, self.E, C, dev)
         act = torch.empty((T * KT, self.inter), dtype=ctx.act_dtype, device=dev)
         y = torch.empty((T * KT, self.hidden), dtype=torch.float32, device=dev)
@@ -207,12 +218,17 @@ class SparseMoeSwiGLU(FeedForward):
         fork, join = torch.cuda.Event(), torch.cuda.Event()
         fork.record(main)
         side.wait_event(fork)
+        cap = int(ops.num_sms() * SIDE_GRID_SHARE) if many else 0
         with torch.cuda.stream(side):
             ops.gemm_fast_grouped(h, self.w_gate_up, act, al, swiglu=True, err=ctx.err, tiles=st, tiles_ready=True,
-                                  x_rows=st.x_rows)
-            ops.gemm_fast_grouped(act, self.w_down, y, al, err=ctx.err, tiles=st, tiles_ready=True)
+                                  x_rows=st.x_rows, max_ctas=cap)
+            ops.gemm_fast_grouped(act, self.w_down, y, al, err=ctx.err, tiles=st, tiles_ready=True, max_ctas=cap)
             join.record(side)
-        ops.moe_route_small(logits, K, self.renorm, C, gate_logit, idx, score, al, ctx.err, x=None, static=True)
+        if many:
+            ops.router_topk(logits, K, self.renorm, idx, score, C, gate_logit)
+            ops.moe_align(idx, KT, al, ctx.err, static_last=C)
+        else:
+            ops.moe_route_small(logits, K, self.renorm, C, gate_logit, idx, score, al, ctx.err, x=None, static=True)
         self.last_alignment = al
         x_sorted = ops.permute_rows(h, al.sorted_token, T * K)
         ops.gemm_fast_grouped(x_sorted, self.w_gate_up, act, al, swiglu=True, err=ctx.err, tiles_ready=True)

@@ -15,9 +15,6 @@ CASES = dict(make_golden.CASES)
 # A third configuration, for the kernels that only head sizes 64 and 128 reach (tensor-core attention for prompts
 # and for decoding) inside the whole engine: grouped queries, a window on the second layer, a shared expert that
 # is a whole number of expert widths (so that it runs as extra experts on the fast path), sizes no power of two.
-# (The seed is one for which no token of the test prompts sits on the edge between two experts: there a bfloat16
-# run may rightly pick the other expert, and that row then differs by more than rounding.  Most seeds have one
-# or two such tokens among the two thousand that the replay tests route.)
 CASES["C"] = dict(
     config=dict(architectures=["Qwen2MoeForCausalLM"], model_type="qwen2_moe", num_hidden_layers=2,
                 hidden_size=136, num_attention_heads=4, num_key_value_heads=2, head_dim=64, num_experts=5,
@@ -55,18 +52,56 @@ def prompt(case_name, n, salt=0):
     return [int(x) for x in rs.randint(0, CASES[case_name]["config"]["vocab_size"], size=n)]
 
 
+# A bfloat16 run may rightly send a token to another expert than the float64 run does when the token sits on the
+# edge between two experts: its K-th and (K+1)-th router logits closer than this fraction of the spread of its
+# router logits (bfloat16 activations carry errors of about one percent).  Such a row then differs by more than
+# rounding; the comparisons below let a bfloat16 row exceed the tolerance only if it is such a row, and only a few.
+EDGE_MARGIN = 0.01
+MAX_EDGE_SHARE = 0.03
+
 _plain_cache = {}
 
 
-def plain_logits(mdir, ids):
-    """float64 logits [T, V] of the plain implementation for one whole sequence (cached)."""
+def _plain(mdir, ids):
     key = (mdir, tuple(ids))
     if key not in _plain_cache:
         if mdir not in _plain_cache:
             _plain_cache[mdir] = plain_model.read_folder(mdir)
         cfg, W = _plain_cache[mdir]
-        _plain_cache[key] = plain_model.forward(cfg, W, list(ids))
+        ms = []
+        logits = plain_model.forward(cfg, W, list(ids), margins=ms)
+        margin = torch.stack(ms).min(dim=0).values if ms else torch.full((len(ids),), float("inf"), dtype=torch.float64)
+        _plain_cache[key] = (logits, margin)
     return _plain_cache[key]
+
+
+def plain_logits(mdir, ids):
+    """float64 logits [T, V] of the plain implementation for one whole sequence (cached)."""
+    return _plain(mdir, ids)[0]
+
+
+def plain_margins(mdir, ids):
+    """Per position, the smallest router margin over the sparse layers (see ``plain_model.route``)."""
+    return _plain(mdir, ids)[1]
+
+
+def assert_rows_close(got, want, margin, dtype, what=""):
+    """``assert_close`` row by row; in bfloat16 a row may exceed the bound if it sits on a router edge
+    (``margin`` below EDGE_MARGIN), and only a few rows may."""
+    got = torch.as_tensor(got, dtype=torch.float64).cpu()
+    want = torch.as_tensor(want, dtype=torch.float64).cpu()
+    assert got.shape == want.shape, f"{what}: shape {tuple(got.shape)} vs {tuple(want.shape)}"
+    tol = TOL[dtype]
+    bound = tol["abs"] + tol["rel"] * float(want.abs().max())
+    err = (got - want).abs().max(dim=-1).values
+    off = torch.nonzero(err > bound).reshape(-1).tolist()
+    if dtype != "bfloat16":
+        assert not off, f"{what}: rows {off[:8]} differ by more than {bound:.3g}; max {float(err.max()):.3g}"
+        return
+    plain_rows = [(r, float(err[r]), float(margin[r])) for r in off if float(margin[r]) >= EDGE_MARGIN]
+    assert not plain_rows, (f"{what}: rows (row, error, router margin) beyond {bound:.3g} that sit on no router edge: "
+                            f"{plain_rows[:8]}")
+    assert len(off) <= max(1, MAX_EDGE_SHARE * len(err)), f"{what}: {len(off)} of {len(err)} rows beyond {bound:.3g}"
 
 
 def assert_close(got, want, dtype, what=""):
@@ -120,7 +155,7 @@ class Replay:
         pos = sorted(p for (r, p) in self.logits if r == rid)
         assert pos, f"{what}: no logits were collected for {rid}"
         got = torch.stack([self.logits[(rid, p)] for p in pos])
-        assert_close(got, want[pos], dtype, f"{what} request {rid}")
+        assert_rows_close(got, want[pos], plain_margins(mdir, ids)[pos], dtype, f"{what} request {rid}")
 
 
 def assert_greedy_follows_plain(mdir, prompt_ids, tokens, dtype, what=""):

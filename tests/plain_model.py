@@ -164,7 +164,8 @@ def route(x_norm, Wg, top_k: int, renorm: bool, margins: list | None = None):
     """p = softmax(x Wg^T) over all experts; the top_k largest in descending order, a tie going to the
     lower index (selection with strict >); weights p or p / sum(p_topk)
     (tools/ref_top5.cpp:484-515; src/hip_ops.hip:813-841).  Returns (idx [T,K], w [T,K]).
-    ``margins``, if a list, receives per row the gap between the top_k-th and the next router logit."""
+    ``margins``, if a list, receives per row the gap between the top_k-th and the next router logit as a fraction
+    of the spread of the row's logits (largest minus smallest): how far the row is from choosing another expert."""
     logits = (x_norm @ Wg.T).to(torch.float32).to(F64)                 # router logits are stored as float32
     p = torch.softmax(logits, dim=-1)
     T, E = p.shape
@@ -178,7 +179,7 @@ def route(x_norm, Wg, top_k: int, renorm: bool, margins: list | None = None):
         rem[rows, best] = -1.0
     if margins is not None and top_k < E:
         top = torch.sort(logits, dim=-1, descending=True).values
-        margins.append((top[:, top_k - 1] - top[:, top_k]).cpu())
+        margins.append(((top[:, top_k - 1] - top[:, top_k]) / (top[:, 0] - top[:, -1]).clamp_min(1e-30)).cpu())
     if renorm:
         w = w / w.sum(dim=-1, keepdim=True)
     return idx, w.to(torch.float32).to(F64)                            # weights are stored as float32

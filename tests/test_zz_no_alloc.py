@@ -82,3 +82,10 @@ def test_no_alloc_decode_attention_matches_the_ordinary_entry_point():
     torch.cuda.synchronize()
     lib.nv_attention_decode_noalloc_status.restype = c_int
     assert lib.nv_attention_decode_noalloc_status() == 0
+    # sizes the kernel does not take are refused before the size test, and fit no row
+    assert lib.nv_attention_decode_noalloc_max_rows(c_int(Hq), c_int(20), c_int(splits)) == 0
+    assert lib.nv_attention_decode_noalloc_max_rows(c_int(Hq), c_int(264), c_int(splits)) == 0
+    assert lib.nv_attention_decode_noalloc_max_rows(c_int(0), c_int(D), c_int(splits)) == 0
+    assert _call(lib, "nv_attention_decode_noalloc", qkv[:2], kc, vc, bt, ent, pos, out[:2], Hq, Hkv, 20, page, splits) == -4
+    assert _call(lib, "nv_attention_decode_noalloc", qkv[:2], kc, vc, bt, ent, pos, out[:2], Hq, 0, D, page, splits) == -4
+    assert _call(lib, "nv_attention_decode_noalloc", qkv[:2], kc, vc, bt, ent, pos, out[:2], -Hq, -Hkv, D, page, splits) == -4
