@@ -14,7 +14,9 @@ sampling kernel behind it, and the next step reading the drawn tokens on the dev
 
 ``--kernel-times`` adds ``kernels``: per kernel class of one decode step and of the prompt, CUDA-event time,
 calls and the fraction of the measured peak its bytes (decode) or flops (prompt) come to.  Those steps run
-outside CUDA graphs, one kernel after the other, so their sum is more than the step's own time.
+outside CUDA graphs with an event between any two kernels, one kernel after the other on one stream (the decode
+step behind a delay kernel, so that the host has queued it all before the GPU starts): nothing overlaps, and
+their sum is more than the step's own time.
 """
 from __future__ import annotations
 
@@ -156,6 +158,7 @@ def kernel_times(runner, cfg, args, P, fill_context, StepEntry, ops, torch, g, V
         steps = 4
         with ops.KernelTimes() as kt:
             for _ in range(steps):
+                ops.delay(30000)       # the host queues the whole step meanwhile: no waits for it between the kernels
                 runner.step(entries, check=False)
         ctx_tokens = sum(runner.num_cached(r) for r in rids)
         distinct = [int((p.last_alignment.counts[:E] > 0).sum()) for p in
@@ -381,16 +384,18 @@ def main() -> int:
     # ------------------------------------------------------------------ end to end through LLMEngine.step
     e2e = None
     if not args.no_e2e:
+        # B requests with prompts of `context` tokens go through the public entry point: the engine runs their
+        # prompts first (untimed), then every step decodes one token of each; host token ids in and out.
         B = args.batch
-        rids = fill_context(B)
-        sp = SamplingParams(temperature=0.0, max_tokens=args.steps + args.warmup + 8, ignore_eos=True)
-        from nano_vllm_cpp_b200.engine.sequence import Sequence
-        seqs = []
-        for rid in rids:     # requests whose caches already hold `context` tokens join the running ones
-            s = Sequence(torch.randint(0, V, (args.context + 1,), generator=g).tolist(), sp)
-            runner.manager.rename(rid, s.seq_id)
-            eng.scheduler.add(s, running=True)
-            seqs.append(s)
+        sp = SamplingParams(temperature=0.0, max_tokens=args.steps + args.warmup + 24, ignore_eos=True)
+        for _ in range(B):
+            eng.add_request(torch.randint(0, V, (args.context,), generator=g).tolist(), sp)
+        for _ in range(200):                  # until every request decodes
+            out = eng.step()
+            if out.num_decode_tokens == B and out.num_prefill_tokens == 0:
+                break
+        else:
+            raise RuntimeError("bench.py: the requests of the end-to-end run never all reached decoding")
         for _ in range(args.warmup):
             eng.step()
         torch.cuda.synchronize()

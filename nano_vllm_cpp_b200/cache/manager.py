@@ -154,13 +154,6 @@ class CacheManager:
             self._raise(rc)
         self._ids.pop(rid, None)
 
-    def rename(self, rid, new_rid) -> None:
-        """The same cache under another request id (a request handed from one owner to another)."""
-        rc = host.lib().nvh_rename(self._h, self._id(rid), self._native(new_rid, create=True))
-        if rc:
-            self._raise(rc)
-        self._ids.pop(rid, None)
-
     # ------------------------------------------------------------------ pages
     def pages_needed(self, rid, start: int, end: int) -> list:
         """Per group: pages to take minus pages that running rows [start, end) gives back first."""

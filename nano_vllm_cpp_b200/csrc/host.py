@@ -48,14 +48,13 @@ _PROTOS = {
     "nvh_match_prefix": (c_int, [c_void_p, _IP, c_int, _IP, _UP, c_int]),
     "nvh_adopt_prefix": (c_int, [c_void_p, c_int64, _IP, _UP, c_int]),
     "nvh_new_pages_for": (c_int, [c_void_p, c_int, _IP, c_int]),
-    "nvh_rename": (c_int, [c_void_p, c_int64, c_int64]),
     "nvh_manager_check": (c_int, [c_void_p]),
     "nvh_commit_many": (c_int, [c_void_p, c_int, _LP, _IP]),
     "nvh_step_layout": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, _IP]),
     "nvh_prepare_step": (c_int, [c_void_p, c_int, _LP, _IP, _IP, _IP, _IP, c_int, c_int, c_int, c_void_p, c_int, _IP]),
     "nvs_create": (c_void_p, [c_void_p, c_int, c_int, c_int, c_int, c_int]),
     "nvs_destroy": (None, [c_void_p]),
-    "nvs_add": (c_int, [c_void_p, c_int64, _IP, c_int, c_int, c_int, c_int, c_int]),
+    "nvs_add": (c_int, [c_void_p, c_int64, _IP, c_int, c_int, c_int, c_int]),
     "nvs_is_finished": (c_int, [c_void_p]),
     "nvs_num_preemptions": (c_int, [c_void_p]),
     "nvs_queue_sizes": (c_int, [c_void_p, _IP, _IP]),

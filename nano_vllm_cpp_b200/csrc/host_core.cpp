@@ -611,16 +611,6 @@ NVH_API int nvh_adopt_prefix(void* m, int64_t rid, const int* pages, const uint6
 NVH_API int nvh_new_pages_for(void* m, int tokens_len, const int* pages, int n) {
   return ((CacheManager*)m)->new_pages_for(tokens_len, pages, n);
 }
-NVH_API int nvh_rename(void* m, int64_t from, int64_t to) {      // the same cache under another request id
-  CacheManager* cm = (CacheManager*)m;
-  auto it = cm->requests.find(from);
-  if (it == cm->requests.end() || cm->requests.count(to)) return fail(ERR_STATE, "rename: bad ids");
-  RequestCache rc = std::move(it->second);
-  cm->requests.erase(it);
-  rc.rid = to;
-  cm->requests.emplace(to, std::move(rc));
-  return OK;
-}
 NVH_API int nvh_manager_check(void* m) { return ((CacheManager*)m)->check(); }
 
 // Rows up to ends[i] of request rids[i] have run (no hashing of pages: the caller that wants it commits one by one).
@@ -737,9 +727,7 @@ NVH_API void* nvs_create(void* manager, int max_num_seqs, int max_batched_tokens
   return new SchedHandle((CacheManager*)manager, max_num_seqs, max_batched_tokens, max_model_len, eos, prefill_chunk);
 }
 NVH_API void nvs_destroy(void* s) { delete (SchedHandle*)s; }
-// running != 0: the sequence already holds its cache (under seq_id) and goes straight to `running`.
-NVH_API int nvs_add(void* s, int64_t seq_id, const int* tokens, int n, int num_prompt, int max_tokens, int ignore_eos,
-                    int running) {
+NVH_API int nvs_add(void* s, int64_t seq_id, const int* tokens, int n, int num_prompt, int max_tokens, int ignore_eos) {
   Scheduler& sc = ((SchedHandle*)s)->s;
   if (sc.seqs.count(seq_id)) return fail(ERR_STATE, "sequence id is already known");
   auto q = std::make_unique<Seq>();
@@ -750,12 +738,7 @@ NVH_API int nvs_add(void* s, int64_t seq_id, const int* tokens, int n, int num_p
   q->ignore_eos = ignore_eos != 0;
   Seq* raw = q.get();
   sc.seqs.emplace(seq_id, std::move(q));
-  if (running) {
-    raw->status = 1;
-    sc.running.push_back(raw);
-  } else {
-    sc.waiting.push_back(raw);
-  }
+  sc.waiting.push_back(raw);
   return OK;
 }
 NVH_API int nvs_is_finished(void* s) { return ((SchedHandle*)s)->s.finished() ? 1 : 0; }

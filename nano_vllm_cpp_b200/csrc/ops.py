@@ -83,6 +83,14 @@ class KernelTimes:
         _timer = None
         torch.cuda.synchronize()
 
+    def mark(self) -> None:
+        """The next launch's time starts here (the model calls this when a step's kernels begin, so that the host's
+        preparation of the step is not booked to its first kernel)."""
+        stream = torch.cuda.current_stream()
+        e = torch.cuda.Event(enable_timing=True)
+        e.record(stream)
+        self.last[stream.cuda_stream] = e
+
     def note(self, name: str, flops: float, nbytes: float) -> None:
         stream = torch.cuda.current_stream()
         e = torch.cuda.Event(enable_timing=True)
@@ -103,6 +111,17 @@ class KernelTimes:
 
 
 _timer = None
+
+
+def timing() -> bool:
+    """True while a ``KernelTimes`` is active: work that would run on a second stream stays on the first then, so
+    that every kernel's time is its own."""
+    return _timer is not None
+
+
+def mark_step() -> None:
+    if _timer is not None:
+        _timer.mark()
 
 
 def _check(code: int, what: str, flops: float = 0.0, nbytes: float = 0.0) -> None:
@@ -496,7 +515,7 @@ class StaticTiles:
     T * K routed pairs: what ``moe_route_small(static=True)`` leaves out of its list."""
 
     def __init__(self, T: int, K: int, E: int, C: int, device):
-        self.tile_m = 16 if T <= 16 else (32 if T <= 32 else (64 if T <= 64 else 128))
+        self.tile_m = 8 if T <= 8 else 16 if T <= 16 else (32 if T <= 32 else (64 if T <= 64 else 128))
         experts, row0, rows = [], [], []
         for c in range(C):
             for r in range(0, T, self.tile_m):
@@ -551,6 +570,15 @@ def reset_fresh_state(state, entry_slot, entry_pos0) -> None:
                                       c_int(entry_slot.numel()), _stream()), "reset_fresh_state")
 
 
+def delay(micros: int) -> None:
+    """Keeps the current stream busy for about ``micros`` microseconds (at most 200,000); for measurements that
+    want a step's launches queued before the GPU starts on them."""
+    global _launches
+    code = lib().nv_delay(c_int(int(micros)), _stream())
+    if code:
+        raise KernelError(f"delay: {_ERR.get(code, code)}")
+
+
 def sample(logits, temperature, u, out) -> None:
     """One token per row: greedy where temperature <= 0, else inverse-CDF with the given u in [0,1)."""
     _cuda_contig(logits, temperature, u, out)
@@ -603,6 +631,47 @@ def gemm_fast_usable(a, w, out, *, bias=None, a_rows=None, swiglu=False, grouped
     if a.shape[-1] % 8 or out.dtype not in _DT or out.stride(-1) != 1:
         return False
     return True
+
+
+SKINNY_MAX_ROWS = 8
+
+
+def skinny_usable(a, w, rows: int) -> bool:
+    """Whether the weight-streaming product for a handful of rows (skinny_gemm.cu) takes these operands."""
+    return (1 <= rows <= SKINNY_MAX_ROWS and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+            and a.stride(-1) == 1 and w.is_contiguous() and a.shape[-1] % 8 == 0 and a.stride(0) % 8 == 0
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def skinny_gemm(a, w, out, *, bias=None, swiglu=False, rows=None, tiles=None, a_rows=None, x_rows=None,
+                max_tile_rows: int = 0, err=None) -> None:
+    """``out = a @ w.T`` for at most eight rows (``rows``: how many rows of ``a``, default all), by streaming ``w``
+    once; ``swiglu`` as in ``gemm_plain``.  Grouped form with ``tiles`` (a ``TileList`` whose tiles have at most
+    ``max_tile_rows`` <= 8 rows; ``w`` is [E, rows, K]): output row r of a tile of expert e is
+    ``a[a_rows[r]] @ w[e].T``, or ``a[(r - sub) % mod]`` with ``x_rows = (sub, mod)``, or ``a[r]``."""
+    _cuda_contig(w, bias, a_rows)
+    _i32(a_rows)
+    K = a.shape[-1]
+    rows_w = w.shape[-2]
+    N = rows_w // 2 if swiglu else rows_w
+    grouped = tiles is not None
+    R = (a.shape[0] if rows is None else rows) if not grouped else 0
+    _need(skinny_usable(a, w, max_tile_rows if grouped else R), "skinny product: operands or row count not supported")
+    _need(w.shape[-1] == K and out.shape[1] == N and out.stride(1) == 1, "skinny product: shapes")
+    x_sub, x_mod = x_rows if x_rows is not None else (0, 0)
+    te = tr0 = tr = nt = None
+    max_tiles = 0
+    if grouped:
+        te, tr0, tr, nt, max_tiles = tiles.tile_expert, tiles.tile_row0, tiles.tile_rows, tiles.num_tiles, tiles.max_tiles
+    else:
+        _need(out.shape[0] >= R, "skinny product: out rows")
+    _check(lib().nv_skinny_gemm(_p(a), c_longlong(a.stride(0)), c_int(a.shape[0]), c_int(R), _p(w), c_int(N), c_int(K),
+                                _p(bias), c_int(dt(bias) if bias is not None else 0), _p(out), c_int(dt(out)),
+                                c_longlong(out.stride(0)), c_int(1 if swiglu else 0), _p(a_rows), _p(te), _p(tr0), _p(tr),
+                                _p(nt), c_int(max_tiles), c_int(max_tile_rows), c_int(x_sub), c_int(x_mod),
+                                _p(err.t if err is not None else _global_err().t), _stream()),
+           f"skinny_gemm{'_grouped' if grouped else ''} N={rows_w} K={K}", 0.0,
+           0.0 if grouped else float(w.element_size() * rows_w * K))
 
 
 def grouped_token_tile(TK: int, E: int, swiglu: bool = False) -> int:

@@ -667,6 +667,25 @@ NV_API int nv_reset_fresh_state(void* state, long long slot_bytes, int num_slots
   NV_RETURN_LAST();
 }
 
+// Keeps the stream busy for about `micros` microseconds (at most 200,000) and does nothing else: a measurement queues
+// it before a step, so that the host has launched the whole step by the time the GPU starts on it and the times
+// between the step's kernels hold no waits for the host.
+__global__ void delay_kernel(unsigned long long nanos) {
+  unsigned long long t0, t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  do {
+    __nanosleep(1000);
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  } while (t - t0 < nanos);
+}
+
+NV_API int nv_delay(int micros, cudaStream_t s) {
+  if (micros < 0 || micros > 200000) return NV_ERR_BAD_SIZE;
+  if (micros == 0) return NV_OK;
+  delay_kernel<<<1, 1, 0, s>>>((unsigned long long)micros * 1000ull);
+  NV_RETURN_LAST();
+}
+
 NV_API int nv_sample(const float* logits, int R, int V, const float* temperature, const double* u, int* out,
                      cudaStream_t s) {
   if (R == 0) return NV_OK;

@@ -79,16 +79,13 @@ class Scheduler:
             self._h = None
 
     # ------------------------------------------------------------------ queue
-    def add(self, seq: Sequence, running: bool = False) -> None:
-        """Queues a request.  ``running``: its cache already exists under ``seq.seq_id`` and holds all but
-        its last token, so it joins the running requests at once (a request taken over from elsewhere)."""
+    def add(self, seq: Sequence) -> None:
+        """Queues a request."""
         arr, n = host.ints(seq.token_ids)
         rc = host.lib().nvs_add(self._h, seq.seq_id, arr, n, seq.num_prompt_tokens, seq.max_tokens,
-                                1 if seq.ignore_eos else 0, 1 if running else 0)
+                                1 if seq.ignore_eos else 0)
         if rc:
             raise SchedulerError(host.last_error())
-        if running:
-            seq.status = SequenceStatus.RUNNING
         self._seqs[seq.seq_id] = seq
 
     def is_finished(self) -> bool:

@@ -6,6 +6,7 @@ import torch
 
 from ..csrc import ops
 from .base import FeedForward, RowMix, TensorSpec
+from . import linear as linear_mod
 from .linear import linear, grouped_linear, small_linear
 from .registry import register_part
 
@@ -130,8 +131,10 @@ class SparseMoeSwiGLU(FeedForward):
         else:
             self.virtual = 0
 
-    def _alignment(self, TK, n_experts, device, fast):
-        if fast:    # the down product's tile is the primary list, the SwiGLU product may want a wider one
+    def _alignment(self, TK, n_experts, device, fast, rows=0):
+        if fast and 0 < rows <= linear_mod.SKINNY_ROWS:      # the weight-streaming products: tiles of at most 8 rows
+            tile_m, tile_m2 = ops.SKINNY_MAX_ROWS, 0
+        elif fast:  # the down product's tile is the primary list, the SwiGLU product may want a wider one
             tile_m, tile_m2 = ops.grouped_token_tile(TK, n_experts), ops.grouped_token_tile(TK, n_experts, swiglu=True)
         else:
             tile_m, tile_m2 = ops.gemm_plain_tile_m(), 0
@@ -165,7 +168,7 @@ class SparseMoeSwiGLU(FeedForward):
         score = torch.empty((T, KT), dtype=torch.float32, device=dev)
         fast = (ctx.fast_kernels and h.dtype == torch.bfloat16 and self.w_gate_up.dtype == torch.bfloat16
                 and self.w_down.dtype == torch.bfloat16 and self.hidden % 8 == 0 and self.inter % 8 == 0)
-        al = self._alignment(T * KT, self.E + C, dev, fast)
+        al = self._alignment(T * KT, self.E + C, dev, fast, rows=T)
         x_sorted = None
         if (fast and C and T <= SIDE_MAX_ROWS and al.secondary is None
                 and ops.moe_route_small_usable(T, self.E, self.K, C, self.hidden)):
@@ -219,10 +222,16 @@ class SparseMoeSwiGLU(FeedForward):
         fork.record(main)
         side.wait_event(fork)
         cap = int(ops.num_sms() * SIDE_GRID_SHARE) if many else 0
+        skinny = al.tile_m <= ops.SKINNY_MAX_ROWS and st.tile_m <= ops.SKINNY_MAX_ROWS
         with torch.cuda.stream(side):
-            ops.gemm_fast_grouped(h, self.w_gate_up, act, al, swiglu=True, err=ctx.err, tiles=st, tiles_ready=True,
-                                  x_rows=st.x_rows, max_ctas=cap)
-            ops.gemm_fast_grouped(act, self.w_down, y, al, err=ctx.err, tiles=st, tiles_ready=True, max_ctas=cap)
+            if skinny:
+                ops.skinny_gemm(h, self.w_gate_up, act, swiglu=True, tiles=st, x_rows=st.x_rows, max_tile_rows=st.tile_m,
+                                err=ctx.err)
+                ops.skinny_gemm(act, self.w_down, y, tiles=st, max_tile_rows=st.tile_m, err=ctx.err)
+            else:
+                ops.gemm_fast_grouped(h, self.w_gate_up, act, al, swiglu=True, err=ctx.err, tiles=st, tiles_ready=True,
+                                      x_rows=st.x_rows, max_ctas=cap)
+                ops.gemm_fast_grouped(act, self.w_down, y, al, err=ctx.err, tiles=st, tiles_ready=True, max_ctas=cap)
             join.record(side)
         if many:
             ops.router_topk(logits, K, self.renorm, idx, score, C, gate_logit)
@@ -230,9 +239,14 @@ class SparseMoeSwiGLU(FeedForward):
         else:
             ops.moe_route_small(logits, K, self.renorm, C, gate_logit, idx, score, al, ctx.err, x=None, static=True)
         self.last_alignment = al
-        x_sorted = ops.permute_rows(h, al.sorted_token, T * K)
-        ops.gemm_fast_grouped(x_sorted, self.w_gate_up, act, al, swiglu=True, err=ctx.err, tiles_ready=True)
-        ops.gemm_fast_grouped(act, self.w_down, y, al, err=ctx.err, tiles_ready=True)
+        if skinny:      # the rows are read where they are: no sorted copy
+            ops.skinny_gemm(h, self.w_gate_up, act, swiglu=True, tiles=al.primary, a_rows=al.sorted_token,
+                            max_tile_rows=al.tile_m, err=ctx.err)
+            ops.skinny_gemm(act, self.w_down, y, tiles=al.primary, max_tile_rows=al.tile_m, err=ctx.err)
+        else:
+            x_sorted = ops.permute_rows(h, al.sorted_token, T * K)
+            ops.gemm_fast_grouped(x_sorted, self.w_gate_up, act, al, swiglu=True, err=ctx.err, tiles_ready=True)
+            ops.gemm_fast_grouped(act, self.w_down, y, al, err=ctx.err, tiles_ready=True)
         main.wait_event(join)
         return RowMix(y, al.pair_pos[:T * KT].view(T, KT), score, None, None)
 
@@ -242,6 +256,8 @@ _side = {}
 
 def _side_stream(dev):
     """One second stream per device for work that runs beside a step's main stream."""
+    if ops.timing():                 # per-kernel timers are running: one stream, one kernel after the other
+        return torch.cuda.current_stream(dev)
     key = torch.device(dev)
     if key not in _side:
         _side[key] = torch.cuda.Stream(device=key)

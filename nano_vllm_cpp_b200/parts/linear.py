@@ -9,6 +9,9 @@ import torch
 
 from ..csrc import ops
 
+# Products with at most this many rows take the weight-streaming kernel (0: never; at most ops.SKINNY_MAX_ROWS).
+SKINNY_ROWS = ops.SKINNY_MAX_ROWS
+
 
 def linear(ctx, a, w, out_dtype, *, bias=None, a_rows=None, swiglu=False, M=None, out=None):
     """``out = a[a_rows] @ w.T (+ bias)``; with ``swiglu`` w is [2N, K] (gate rows, then up rows)
@@ -20,6 +23,12 @@ def linear(ctx, a, w, out_dtype, *, bias=None, a_rows=None, swiglu=False, M=None
     if out is None:
         out = torch.empty((M, N), dtype=out_dtype, device=a.device)
     if M == 0:
+        return out
+    if ctx.fast_kernels and M <= SKINNY_ROWS and ops.skinny_usable(a, w, M):
+        # a handful of rows: the product is a stream of w, and the kernel without tiles starts it soonest
+        if a_rows is not None:
+            a = ops.permute_rows(a, a_rows, M)
+        ops.skinny_gemm(a, w, out, bias=bias, swiglu=swiglu, rows=M, err=ctx.err)
         return out
     if ctx.fast_kernels and ops.gemm_fast_usable(a, w, out, bias=bias, a_rows=a_rows, swiglu=swiglu):
         ops.gemm_fast(a, w, out, bias=bias, a_rows=a_rows, swiglu=swiglu, M=M, err=ctx.err)
@@ -45,6 +54,10 @@ def grouped_linear(ctx, a, w, out_dtype, align, *, a_rows=None, swiglu=False, ti
     if out is None:
         out = torch.empty((align.TK, N), dtype=out_dtype, device=a.device)
     if align.TK == 0:
+        return out
+    tl = tiles if tiles is not None else align.primary
+    if ctx.fast_kernels and tl.tile_m <= ops.SKINNY_MAX_ROWS and ops.skinny_usable(a, w, tl.tile_m):
+        ops.skinny_gemm(a, w, out, swiglu=swiglu, tiles=tl, a_rows=a_rows, max_tile_rows=tl.tile_m, err=ctx.err)
         return out
     if ctx.fast_kernels and ops.gemm_fast_usable(a, w, out, a_rows=a_rows, swiglu=swiglu, grouped=True):
         ops.gemm_fast_grouped(a, w, out, align, a_rows=a_rows, swiglu=swiglu, err=ctx.err, tiles=tiles,

@@ -103,7 +103,7 @@ class Model:
             if c.cache_of is not None:
                 out.append(("shared", c.cache_of))
             else:
-                out.append(self.layers[c.layer].mixer.cache_spec())
+                out.append(self.layers[c.layer].cache_spec())
         return out
 
     def load(self, source, ctx: RunContext) -> None:
@@ -119,6 +119,7 @@ class Model:
     def forward(self, batch, cache) -> torch.Tensor:
         """Runs the rows of ``batch`` through every call; returns float32 logits ``[wanted, vocab]``."""
         ctx = self.ctx
+        ops.mark_step()
         x = torch.empty((batch.T, self.spec.hidden_size), dtype=torch.float32, device=ctx.device)
         ops.embedding(batch.input_ids, self.embed, x, ctx.err, feed=ctx.feed)
         pending = None

@@ -601,3 +601,93 @@ def test_toy_position_encoding_and_routing_feed_forward(tmp_path):
     for r in ("w", "c"):
         got = torch.stack([rp.logits[(r, p)] for p in range(len(ids))])
         helpers.assert_close(got, want, "float32", f"toy switch request {r}")
+
+
+# ------------------------------------------------------------------------------- toy arrangements
+def define_toy_arrangements():
+    """Two arrangements that the package does not have: a parallel block (one norm feeds the mixer and the
+    feed-forward, both outputs are added) and a layer that is a mixer and nothing else."""
+    from nano_vllm_cpp_b200.parts import Arrangement, PartSpec, LayerSpec, ModelSpec, register_part
+    from nano_vllm_cpp_b200.parts.base import resolve_branch
+    from nano_vllm_cpp_b200.config import register_architecture
+
+    class ParallelBlock(Arrangement):
+        slots = {"norm": "norm", "mixer": "mixer", "feed_forward": "feed_forward"}
+
+        def forward(self, x, pending, batch, cache):
+            h, h32 = self.norm.forward(x, resolve_branch(self.norm, pending), want_f32=self.feed_forward.wants_f32_input)
+            a = self.mixer.forward(h, batch, cache)
+            f = self.feed_forward.forward(h, h32, batch)
+            return a + f                     # one float32 branch; the next norm adds it to the stream
+
+    class MixerOnly(Arrangement):
+        slots = {"norm": "norm", "mixer": "mixer"}
+
+        def forward(self, x, pending, batch, cache):
+            h, _ = self.norm.forward(x, resolve_branch(self.norm, pending))
+            return self.mixer.forward(h, batch, cache)
+
+    register_part("arrangement", "toy_parallel", ParallelBlock)
+    register_part("arrangement", "toy_mixer_only", MixerOnly)
+
+    def build(cfg):
+        H = cfg["hidden_size"]
+        norm = PartSpec("rmsnorm", dict(size=H, eps=cfg["rms_norm_eps"]))
+        mlp = PartSpec("dense_swiglu", dict(hidden_size=H, intermediate_size=cfg["intermediate_size"]))
+
+        def attn(window):
+            return PartSpec("paged_attention", dict(
+                hidden_size=H, num_heads=cfg["num_attention_heads"], num_kv_heads=cfg["num_key_value_heads"],
+                head_dim=cfg["head_dim"], bias=False, window=window,
+                position=PartSpec("rotary_neox", dict(rotary_dim=cfg["head_dim"], theta=cfg["rope_theta"]))))
+
+        layers = [LayerSpec("toy_parallel", dict(norm=norm, mixer=attn(0), feed_forward=mlp),
+                            names={"norm": "ln.", "mixer": "self_attn.", "feed_forward": "mlp."}),
+                  LayerSpec("toy_mixer_only", dict(norm=norm, mixer=attn(cfg["sliding_window"])),
+                            names={"norm": "ln.", "mixer": "self_attn."})]
+        return ModelSpec(vocab_size=cfg["vocab_size"], hidden_size=H, layers=layers, final_norm=norm,
+                         tie_word_embeddings=True, init_std=0.1)
+
+    register_architecture("ToyArrangementsForCausalLM", dict, build)
+
+
+def toy_arrangements_plain(cfg, W, ids):
+    eps, pos = cfg["rms_norm_eps"], list(range(len(ids)))
+    x = pm.embedding(W["model.embed_tokens.weight"], ids)
+    p = "model.layers.0."
+    h = pm.rms_norm(x, W[p + "ln.weight"], eps)
+    x = x + pm.attention_layer(h, W, p + "self_attn.", dict(cfg, use_sliding_window=False), 0, pos) + pm.dense_mlp(h, W, p + "mlp.")
+    p = "model.layers.1."
+    h = pm.rms_norm(x, W[p + "ln.weight"], eps)
+    x = x + pm.attention_layer(h, W, p + "self_attn.", dict(cfg, use_sliding_window=True, max_window_layers=0), 1, pos)
+    return pm.rms_norm(x, W["model.norm.weight"], eps) @ W["model.embed_tokens.weight"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_arrangements_are_registered_built_and_stepped(dtype, tmp_path):
+    """A layer is an arrangement kind plus whatever parts that arrangement names: a parallel block and a layer without
+    a feed-forward, defined here, make a model that is loaded, checked against its tensor names and stepped (whole,
+    in portions, one by one, two requests at once) without a change to the package."""
+    from nano_vllm_cpp_b200.weights import write_model_folder
+    from nano_vllm_cpp_b200.engine.runner import ModelRunner
+    define_toy_arrangements()
+    cfg = dict(architectures=["ToyArrangementsForCausalLM"], vocab_size=90, hidden_size=48, intermediate_size=56,
+               rms_norm_eps=1e-5, num_attention_heads=3, num_key_value_heads=1, head_dim=16, rope_theta=10000.0,
+               sliding_window=20)
+    mdir = write_model_folder(cfg, str(tmp_path / "arr"), seed=7, norm_std=0.1, dtype="bfloat16")
+    _, W = pm.read_folder(mdir)
+    assert sorted(n for n in W if ".layers.1." in n) == sorted(
+        "model.layers.1." + n for n in ("ln.weight", "self_attn.q_proj.weight", "self_attn.k_proj.weight",
+                                        "self_attn.v_proj.weight", "self_attn.o_proj.weight"))
+    runner = ModelRunner(mdir, dtype=dtype, max_tokens=128, max_requests=2)
+    assert len(runner.manager.pools) == 2                 # a group for the full layer, one for the windowed one
+    g = np.random.RandomState(4)
+    ids = {r: [int(t) for t in g.randint(0, 90, size=n)] for r, n in (("a", 50), ("b", 33))}
+    rp = helpers.Replay(runner)
+    rp.step([("a", ids["a"][:30], True), ("b", ids["b"][:2], True)])
+    rp.step([("a", ids["a"][30:31], True), ("b", ids["b"][2:], True)], end=["b"])
+    for t in range(31, 50):
+        rp.step([("a", ids["a"][t:t + 1], True)])
+    for r in ids:
+        got = torch.stack([rp.logits[(r, p)] for p in range(len(ids[r]))])
+        helpers.assert_close(got, toy_arrangements_plain(cfg, W, ids[r]), dtype, f"toy arrangements, request {r}")
