@@ -514,8 +514,9 @@ class StaticTiles:
     """The tiles of C experts E .. E + C - 1 that each take all T rows, in row order, their segments behind the
     T * K routed pairs: what ``moe_route_small(static=True)`` leaves out of its list."""
 
-    def __init__(self, T: int, K: int, E: int, C: int, device):
-        self.tile_m = 8 if T <= 8 else 16 if T <= 16 else (32 if T <= 32 else (64 if T <= 64 else 128))
+    def __init__(self, T: int, K: int, E: int, C: int, device, tile_m: int = 0):
+        """``tile_m``: rows per tile (0: the tensor-core product's tile for T rows)."""
+        self.tile_m = tile_m or (16 if T <= 16 else (32 if T <= 32 else (64 if T <= 64 else 128)))
         experts, row0, rows = [], [], []
         for c in range(C):
             for r in range(0, T, self.tile_m):
@@ -639,16 +640,18 @@ SKINNY_MAX_ROWS = 8
 def skinny_usable(a, w, rows: int) -> bool:
     """Whether the weight-streaming product for a handful of rows (skinny_gemm.cu) takes these operands."""
     return (1 <= rows <= SKINNY_MAX_ROWS and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
-            and a.stride(-1) == 1 and w.is_contiguous() and a.shape[-1] % 8 == 0 and a.stride(0) % 8 == 0
+            and a.stride(-1) == 1 and w.is_contiguous() and a.shape[-1] % 32 == 0 and a.stride(0) % 8 == 0
             and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
 def skinny_gemm(a, w, out, *, bias=None, swiglu=False, rows=None, tiles=None, a_rows=None, x_rows=None,
-                max_tile_rows: int = 0, err=None) -> None:
+                max_tile_rows: int = 0, tiles_ready: bool = False, err=None) -> None:
     """``out = a @ w.T`` for at most eight rows (``rows``: how many rows of ``a``, default all), by streaming ``w``
     once; ``swiglu`` as in ``gemm_plain``.  Grouped form with ``tiles`` (a ``TileList`` whose tiles have at most
     ``max_tile_rows`` <= 8 rows; ``w`` is [E, rows, K]): output row r of a tile of expert e is
-    ``a[a_rows[r]] @ w[e].T``, or ``a[(r - sub) % mod]`` with ``x_rows = (sub, mod)``, or ``a[r]``."""
+    ``a[a_rows[r]] @ w[e].T``, or ``a[(r - sub) % mod]`` with ``x_rows = (sub, mod)``, or ``a[r]``.
+    ``tiles_ready``: the tile list was complete before the kernel that precedes this product on the stream started,
+    so the product may ask for its weights while that kernel still runs."""
     _cuda_contig(w, bias, a_rows)
     _i32(a_rows)
     K = a.shape[-1]
@@ -669,7 +672,8 @@ def skinny_gemm(a, w, out, *, bias=None, swiglu=False, rows=None, tiles=None, a_
                                 _p(bias), c_int(dt(bias) if bias is not None else 0), _p(out), c_int(dt(out)),
                                 c_longlong(out.stride(0)), c_int(1 if swiglu else 0), _p(a_rows), _p(te), _p(tr0), _p(tr),
                                 _p(nt), c_int(max_tiles), c_int(max_tile_rows), c_int(x_sub), c_int(x_mod),
-                                _p(err.t if err is not None else _global_err().t), _stream()),
+                                c_int(1 if tiles_ready else 0), _p(err.t if err is not None else _global_err().t),
+                                _stream()),
            f"skinny_gemm{'_grouped' if grouped else ''} N={rows_w} K={K}", 0.0,
            0.0 if grouped else float(w.element_size() * rows_w * K))
 

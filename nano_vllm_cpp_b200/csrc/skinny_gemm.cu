@@ -1,13 +1,18 @@
-// Products of a handful of rows with bfloat16 weights: out[r, n] = sum_k x[r, k] * W[n, k].
+// Products of a handful of rows with bfloat16 weights: out[r, n] = sum_k x[r, k] * W[n, k], r < 8.
 //
 // With one to eight rows a product is nothing but a stream of W from memory, and what decides its time is how soon
-// every multiprocessor has loads in flight and how many.  The tensor-core kernel (tc_gemm.cu) pays for its set-up
-// here: a weight tile of 128 rows per CTA leaves a 2,048 x 2,048 matrix with 16 tiles for 148 multiprocessors, so
-// it splits K and needs a second kernel to add the parts, and an expert's matrix for one row is 11 tiles that each
-// pull 1 MB through one CTA's ring.  This kernel has no tiles: a warp takes four output features at a time
-// (consecutive rows of W, 16-byte loads, a lane's eight elements of every row in registers), multiplies them with
-// the rows of x (read through L1, where they stay) and adds the lanes up with shuffles; the grid covers the GPU
-// with sixteen warps per multiprocessor whatever the matrix is.  Sums are float32.  Forms:
+// the whole matrix is on its way.  The tcgen05 kernel (tc_gemm.cu) pays for its set-up here: a weight tile of 128
+// rows per CTA leaves a 2,048 x 2,048 matrix with 16 tiles for 148 multiprocessors, so it splits K and needs a
+// second kernel to add the parts, and an expert's matrix for one row is 11 tiles that each pull 1 MB through one
+// CTA's ring.  This kernel has no ring and no set-up: a block of sixteen warps owns sixteen output features (sixteen
+// rows of W; with swiglu sixteen gate rows and their sixteen up rows), its warps share out K in steps of 32
+// elements, and every lane asks for all of its pieces of W at once, 16 bytes each, before it waits for the kernel
+// before it, whose output (x) it reads last.  The sums run on the tensor cores all the same: one
+// mma.sync.m16n8k16 takes sixteen weight rows as A and up to eight rows of x as B.  A lane's 16 bytes are eight
+// consecutive k of one weight row; they are used as the lane's slots of two instructions' A fragments, and the
+// lane's 16 bytes of the x row at the same k as its B slots, so each instruction sums 16 values of k that are not
+// the 16 the fragment layout names, but the same 16 in A and in B, and all of them exactly once.  Warps' partial
+// sums are added in warp order in shared memory.  A row's result depends on no other row.  Forms:
 //
 //   dense      W [N, K]; rows 0 .. R-1 of x; optional bias; out bfloat16 or float32
 //   grouped    W [E, rows, K]; a tile list (expert, first row, rows <= 8) over an expert-sorted row list as built by
@@ -15,14 +20,14 @@
 //              experts that all take the same few rows, or x[row0 + j]
 //   swiglu     W holds gate rows [0, N) and up rows [N, 2N) (per expert); out = silu(gate) * up
 //
-// The reference computes these products row by row on the vector units too (src/hip_ops.hip:43-64, 861-893).
+// The reference computes these products row by row on the vector units (src/hip_ops.hip:43-64, 861-893).
 #include "common.cuh"
 
 namespace {
 
-constexpr int SK_WARPS = 16;          // warps per block
-constexpr int SK_NF = 4;              // output features a warp works on at once
+constexpr int SK_WARPS = 16;          // warps per block: the block's share of K is cut into this many
 constexpr int SK_MAX_ROWS = 8;
+constexpr int SK_LOADS = 8;           // 16-byte weight loads a lane has in flight together
 
 struct SkArgs {
   const bf16* x;
@@ -37,163 +42,155 @@ struct SkArgs {
   int* err;
   long long ldx, ldo, w_expert_stride;   // elements
   int R;                    // dense: rows
-  int N, K, swiglu, out_dt, bias_dt, x_sub, x_mod, x_rows_total;
+  int N, K, groups_n, out_dt, bias_dt, x_sub, x_mod, x_rows_total;
+  int tiles_ready;          // grouped: the tile list was complete before the kernel before this one started
 };
 
-__device__ __forceinline__ void fma8(float (&acc), const uint4& wv, const uint4& xv) {
-  const __nv_bfloat162* wp = (const __nv_bfloat162*)&wv;
-  const __nv_bfloat162* xp = (const __nv_bfloat162*)&xv;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float2 a = __bfloat1622float2(wp[i]), b = __bfloat1622float2(xp[i]);
-    acc = fmaf(a.x, b.x, acc);
-    acc = fmaf(a.y, b.y, acc);
-  }
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+               "{%0, %1, %2, %3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// One warp, one tile (up to RMAX rows), SK_NF features from feature n0 on (swiglu: gate and up rows of SK_NF / 2
-// features).  wrow[f] points at the f-th weight row; a row that does not exist points at row 0 and is not stored.
-template <int RMAX>
-__device__ __forceinline__ void warp_unit(const SkArgs& a, const bf16* const (&wrow)[SK_NF], const bf16* const (&xrow)[RMAX],
-                                          int rows, int lane, float (&sum)[SK_NF][RMAX]) {
-#pragma unroll
-  for (int f = 0; f < SK_NF; ++f)
-#pragma unroll
-    for (int r = 0; r < RMAX; ++r) sum[f][r] = 0.f;
-  const int chunks = a.K / 8;                     // 16-byte pieces of a row
-  // two pieces per lane and step: eight weight loads in flight per lane
-  for (int c0 = lane; c0 < chunks; c0 += 64) {
-    const int c1 = c0 + 32;
-    const bool two = c1 < chunks;
-    uint4 wv0[SK_NF], wv1[SK_NF];
-#pragma unroll
-    for (int f = 0; f < SK_NF; ++f) {
-      wv0[f] = __ldcs((const uint4*)wrow[f] + c0);          // streamed once: no reason to keep it in L1 or early in L2
-      wv1[f] = two ? __ldcs((const uint4*)wrow[f] + c1) : make_uint4(0, 0, 0, 0);
+template <bool SWIGLU>
+__global__ void __launch_bounds__(SK_WARPS * 32, 2) skinny_kernel(SkArgs a) {
+  constexpr int NA = SWIGLU ? 2 : 1;                  // accumulators: gate and up
+  constexpr int SK_BATCH = SK_LOADS / (2 * NA);       // steps of 32 elements of K per round of loads
+  __shared__ float part[SK_WARPS][NA][32][4];
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int g = lane / 4, c = lane % 4;               // fragment row / column group of this lane
+  const int grouped = a.tile_expert != nullptr;
+  const int y = grouped ? (int)(blockIdx.x / a.groups_n) : 0;
+  const int n0 = (int)(blockIdx.x % a.groups_n) * 16;
+  // A grouped product must know its tile before it can ask for weights; it may look before the wait only if the
+  // list is older than the kernel before it.
+  bool waited = false;
+  if (grouped && !a.tiles_ready) {
+    grid_dep_wait();
+    waited = true;
+  }
+  int row0 = 0, rows = a.R;
+  const bf16* wbase = a.w;
+  if (grouped) {
+    if (y >= *a.num_tiles) return;
+    row0 = a.tile_row0[y];
+    rows = a.tile_rows[y];
+    if (rows > SK_MAX_ROWS) {                         // the list was cut for another kernel: flag it, do what fits
+      if (a.err && threadIdx.x == 0) atomicExch(a.err, 1 + row0);
+      rows = SK_MAX_ROWS;
     }
+    if (rows <= 0) return;
+    wbase += (size_t)a.tile_expert[y] * a.w_expert_stride;
+  }
+  // this lane's two weight rows (features n0 + g and n0 + g + 8), clamped to rows that exist
+  const int f_lo = min(n0 + g, a.N - 1), f_hi = min(n0 + g + 8, a.N - 1);
+  const uint4* w_lo[NA];
+  const uint4* w_hi[NA];
 #pragma unroll
-    for (int r = 0; r < RMAX; ++r) {
-      if (r < rows) {
-        const uint4 xv0 = __ldg((const uint4*)xrow[r] + c0);
-        const uint4 xv1 = two ? __ldg((const uint4*)xrow[r] + c1) : make_uint4(0, 0, 0, 0);
+  for (int s = 0; s < NA; ++s) {
+    w_lo[s] = (const uint4*)(wbase + ((size_t)s * a.N + f_lo) * a.K) + c;
+    w_hi[s] = (const uint4*)(wbase + ((size_t)s * a.N + f_hi) * a.K) + c;
+  }
+  float acc[NA][4];
 #pragma unroll
-        for (int f = 0; f < SK_NF; ++f) {
-          fma8(sum[f][r], wv0[f], xv0);
-          fma8(sum[f][r], wv1[f], xv1);
+  for (int s = 0; s < NA; ++s) acc[s][0] = acc[s][1] = acc[s][2] = acc[s][3] = 0.f;
+  const int steps = a.K / 32;                         // this warp takes steps warp, warp + 16, ...
+  const uint4* xp = nullptr;
+  for (int s0 = warp; s0 < steps; s0 += SK_WARPS * SK_BATCH) {
+    uint4 wl[SK_BATCH][NA], wh[SK_BATCH][NA], xv[SK_BATCH];
+#pragma unroll
+    for (int b = 0; b < SK_BATCH; ++b) {
+      const int st = s0 + b * SK_WARPS;
+      if (st < steps) {
+#pragma unroll
+        for (int s = 0; s < NA; ++s) {
+          wl[b][s] = __ldcs(w_lo[s] + st * 4);        // streamed once
+          wh[b][s] = __ldcs(w_hi[s] + st * 4);
         }
       }
     }
-  }
-#pragma unroll
-  for (int f = 0; f < SK_NF; ++f)
-#pragma unroll
-    for (int r = 0; r < RMAX; ++r)
-      if (r < rows) sum[f][r] = warp_sum(sum[f][r]);
-}
-
-template <int RMAX, bool SWIGLU>
-__global__ void __launch_bounds__(SK_WARPS * 32) skinny_kernel(SkArgs a) {
-  grid_dep_wait();            // x is the output of the kernel before
-  grid_dep_launch();
-  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-  const int gwarp = blockIdx.x * SK_WARPS + warp, nwarps = gridDim.x * SK_WARPS;
-  constexpr int fpu = SWIGLU ? SK_NF / 2 : SK_NF;                 // output features per unit
-  const int units_n = (a.N + fpu - 1) / fpu;
-  const int tiles = a.tile_expert ? *a.num_tiles : 1;
-  const long long total = (long long)tiles * units_n;
-  for (long long u = gwarp; u < total; u += nwarps) {
-    const int y = (int)(u / units_n), n0 = (int)(u % units_n) * fpu;
-    int row0 = 0, rows = a.R;
-    const bf16* wbase = a.w;
-    if (a.tile_expert) {
-      row0 = a.tile_row0[y];
-      rows = a.tile_rows[y];
-      if (rows > RMAX) {                              // the list was cut for another kernel: flag it, do what fits
-        if (a.err && lane == 0) atomicExch(a.err, 1 + row0);
-        rows = RMAX;
-      }
-      if (rows <= 0) continue;
-      wbase += (size_t)a.tile_expert[y] * a.w_expert_stride;
+    if (!waited) {                                    // the weights are on their way: now wait for x
+      grid_dep_wait();
+      waited = true;
     }
-    const bf16* xrow[RMAX];
-#pragma unroll
-    for (int r = 0; r < RMAX; ++r) {
-      int src = row0 + min(r, rows - 1);
-      if (a.tile_expert) {
+    if (xp == nullptr) {
+      // this lane's row of x (column g of the B operand); lanes beyond the tile's rows multiply zeros
+      int src = row0 + g;
+      if (grouped && g < rows) {
         if (a.a_rows) src = a.a_rows[src];
         else if (a.x_mod) src = (src - a.x_sub) % a.x_mod;
       }
-      if (src < 0 || src >= a.x_rows_total) {          // a bad permutation: flag it and read row 0
-        if (a.err && lane == 0) atomicExch(a.err, 1 + row0 + r);
+      if (g < rows && (src < 0 || src >= a.x_rows_total)) {      // a bad permutation: flag it and read row 0
+        if (a.err && c == 0) atomicExch(a.err, 1 + row0 + g);
         src = 0;
       }
-      xrow[r] = a.x + (size_t)src * a.ldx;
+      xp = (const uint4*)(a.x + (size_t)(g < rows ? src : 0) * a.ldx) + c;
     }
-    const bf16* wrow[SK_NF];
-    bool ok[SK_NF];
 #pragma unroll
-    for (int f = 0; f < SK_NF; ++f) {
-      // swiglu: features n0, n0 + 1 as (gate, gate, up, up); else features n0 .. n0 + 3
-      const int n = SWIGLU ? n0 + (f % fpu) : n0 + f;
-      ok[f] = n < a.N;
-      const int wr = ok[f] ? (SWIGLU && f >= fpu ? a.N + n : n) : 0;
-      wrow[f] = wbase + (size_t)wr * a.K;
+    for (int b = 0; b < SK_BATCH; ++b) {
+      const int st = s0 + b * SK_WARPS;
+      xv[b] = (st < steps && g < rows) ? __ldg(xp + st * 4) : make_uint4(0, 0, 0, 0);
     }
-    float sum[SK_NF][RMAX];
-    warp_unit<RMAX>(a, wrow, xrow, rows, lane, sum);
-    // lane r stores row r (every lane holds every sum)
 #pragma unroll
-    for (int r = 0; r < RMAX; ++r) {
-      if (r < rows && lane == r) {
-        const size_t o = (size_t)(row0 + r) * a.ldo;
-        if (SWIGLU) {
+    for (int b = 0; b < SK_BATCH; ++b) {
+      const int st = s0 + b * SK_WARPS;
+      if (st < steps) {
 #pragma unroll
-          for (int f = 0; f < SK_NF / 2; ++f)
-            if (ok[f]) st_dt(a.out, a.out_dt, o + n0 + f, silu_mul(sum[f][r], sum[f + SK_NF / 2][r]));
-        } else {
-#pragma unroll
-          for (int f = 0; f < SK_NF; ++f)
-            if (ok[f]) {
-              float v = sum[f][r];
-              if (a.bias) v += ld_dt(a.bias, a.bias_dt, n0 + f);
-              st_dt(a.out, a.out_dt, o + n0 + f, v);
-            }
+        for (int s = 0; s < NA; ++s) {
+          mma_bf16_16816(acc[s], wl[b][s].x, wh[b][s].x, wl[b][s].y, wh[b][s].y, xv[b].x, xv[b].y);
+          mma_bf16_16816(acc[s], wl[b][s].z, wh[b][s].z, wl[b][s].w, wh[b][s].w, xv[b].z, xv[b].w);
         }
       }
     }
   }
-}
-
-int sk_blocks() {
-  static int blocks = 0;
-  if (!blocks) {
-    int dev = 0, sms = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess ||
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
-      sms = 148;
-    blocks = sms * 2;           // two blocks of sixteen warps per multiprocessor
+  if (!waited) grid_dep_wait();                       // (a warp without a step of K) nothing is written before this
+  grid_dep_launch();
+#pragma unroll
+  for (int s = 0; s < NA; ++s)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) part[warp][s][lane][j] = acc[s][j];
+  __syncthreads();
+  if (threadIdx.x < 128) {
+    const int l = threadIdx.x / 4, j = threadIdx.x % 4;
+    float v[NA];
+#pragma unroll
+    for (int s = 0; s < NA; ++s) {
+      v[s] = 0.f;
+#pragma unroll
+      for (int wi = 0; wi < SK_WARPS; ++wi) v[s] += part[wi][s][l][j];
+    }
+    // accumulator element j of lane l: feature (l / 4) + 8 * (j / 2), row 2 * (l % 4) + (j % 2)
+    const int feat = n0 + l / 4 + 8 * (j / 2), row = 2 * (l % 4) + (j % 2);
+    if (feat < a.N && row < rows) {
+      float r = SWIGLU ? silu_mul(v[0], v[NA - 1]) : v[0];
+      if (!SWIGLU && a.bias) r += ld_dt(a.bias, a.bias_dt, feat);
+      st_dt(a.out, a.out_dt, (size_t)(row0 + row) * a.ldo + feat, r);
+    }
   }
-  return blocks;
 }
 
 }  // namespace
 
 NV_API int nv_skinny_gemm_max_rows() { return SK_MAX_ROWS; }
 
-// Whether the kernel takes these sizes: K a multiple of 8 (16-byte loads), rows of x and W 16-byte aligned.
+// Whether the kernel takes these sizes: K a multiple of 32 (a warp's step), rows of x and W 16-byte aligned.
 NV_API int nv_skinny_gemm_usable(int rows, int K, long long ldx, const void* x, const void* w) {
-  return rows >= 1 && rows <= SK_MAX_ROWS && K > 0 && K % 8 == 0 && ldx % 8 == 0 && !((uintptr_t)x & 15) &&
+  return rows >= 1 && rows <= SK_MAX_ROWS && K > 0 && K % 32 == 0 && ldx % 8 == 0 && !((uintptr_t)x & 15) &&
          !((uintptr_t)w & 15);
 }
 
 // Dense (tile_expert == nullptr: rows 0 .. R-1 of x, R <= 8) or grouped (tiles of at most `max_tile_rows` <= 8 rows;
 // rows of W per expert = N, or 2N with swiglu; max_tiles bounds the list, whose length is read on the device).
-// x has x_rows_total rows.  out row = sorted row (grouped) or row (dense).
+// x has x_rows_total rows.  out row = sorted row (grouped) or row (dense).  `tiles_ready`: the tile list was complete
+// before the kernel before this one on the stream started (a fixed list): the product may then ask for its weights
+// while that kernel still runs.
 NV_API int nv_skinny_gemm(const void* x, long long ldx, int x_rows_total, int R, const void* w, int N, int K,
                           const void* bias, int bias_dt, void* out, int out_dt, long long ldo, int swiglu,
                           const int* a_rows, const int* tile_expert, const int* tile_row0, const int* tile_rows,
-                          const int* num_tiles, int max_tiles, int max_tile_rows, int x_sub, int x_mod, int* err,
-                          cudaStream_t stream) {
+                          const int* num_tiles, int max_tiles, int max_tile_rows, int x_sub, int x_mod, int tiles_ready,
+                          int* err, cudaStream_t stream) {
   if (!dt_ok(out_dt) || (bias && !dt_ok(bias_dt))) return NV_ERR_BAD_DTYPE;
   const bool grouped = tile_expert != nullptr;
   const int rmax = grouped ? max_tile_rows : R;
@@ -204,25 +201,25 @@ NV_API int nv_skinny_gemm(const void* x, long long ldx, int x_rows_total, int R,
   a.x = (const bf16*)x; a.w = (const bf16*)w; a.bias = bias; a.out = out; a.a_rows = a_rows;
   a.tile_expert = tile_expert; a.tile_row0 = tile_row0; a.tile_rows = tile_rows; a.num_tiles = num_tiles; a.err = err;
   a.ldx = ldx; a.ldo = ldo; a.w_expert_stride = (long long)(swiglu ? 2 * N : N) * K;
-  a.R = R; a.N = N; a.K = K; a.swiglu = swiglu ? 1 : 0; a.out_dt = out_dt; a.bias_dt = bias_dt;
-  a.x_sub = x_sub; a.x_mod = x_mod; a.x_rows_total = x_rows_total;
-  const int fpu = swiglu ? SK_NF / 2 : SK_NF;
-  const long long units = (long long)(grouped ? max_tiles : 1) * ((N + fpu - 1) / fpu);
-  long long blocks = (units + SK_WARPS - 1) / SK_WARPS;
-  if (blocks > sk_blocks()) blocks = sk_blocks();
+  a.R = R; a.N = N; a.K = K; a.out_dt = out_dt; a.bias_dt = bias_dt;
+  a.x_sub = x_sub; a.x_mod = x_mod; a.x_rows_total = x_rows_total; a.tiles_ready = tiles_ready ? 1 : 0;
+  a.groups_n = (N + 15) / 16;
+  const long long blocks = (long long)(grouped ? max_tiles : 1) * a.groups_n;
+  if (blocks > 0x7fffffffLL) return NV_ERR_BAD_SIZE;
   const dim3 grid((unsigned)blocks), block(SK_WARPS * 32);
-  cudaError_t e;
-  if (swiglu) {
-    if (rmax <= 1) e = launch_dep(skinny_kernel<1, true>, grid, block, 0, stream, a);
-    else if (rmax <= 2) e = launch_dep(skinny_kernel<2, true>, grid, block, 0, stream, a);
-    else if (rmax <= 4) e = launch_dep(skinny_kernel<4, true>, grid, block, 0, stream, a);
-    else e = launch_dep(skinny_kernel<8, true>, grid, block, 0, stream, a);
-  } else {
-    if (rmax <= 1) e = launch_dep(skinny_kernel<1, false>, grid, block, 0, stream, a);
-    else if (rmax <= 2) e = launch_dep(skinny_kernel<2, false>, grid, block, 0, stream, a);
-    else if (rmax <= 4) e = launch_dep(skinny_kernel<4, false>, grid, block, 0, stream, a);
-    else e = launch_dep(skinny_kernel<8, false>, grid, block, 0, stream, a);
-  }
+  // (the dependent-launch limit on the grid size does not apply: these blocks hold no shared-memory ring and leave
+  // as soon as their few loads are done)
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = g_nv_dependent_launch ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = swiglu ? cudaLaunchKernelEx(&cfg, skinny_kernel<true>, a) : cudaLaunchKernelEx(&cfg, skinny_kernel<false>, a);
   NV_RETURN_IF(e);
   NV_RETURN_LAST();
 }

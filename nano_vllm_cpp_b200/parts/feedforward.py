@@ -132,7 +132,8 @@ class SparseMoeSwiGLU(FeedForward):
             self.virtual = 0
 
     def _alignment(self, TK, n_experts, device, fast, rows=0):
-        if fast and 0 < rows <= linear_mod.SKINNY_ROWS:      # the weight-streaming products: tiles of at most 8 rows
+        if (fast and 0 < rows <= linear_mod.SKINNY_ROWS and self.hidden % 32 == 0
+                and self.inter % 32 == 0):                   # the weight-streaming products: tiles of at most 8 rows
             tile_m, tile_m2 = ops.SKINNY_MAX_ROWS, 0
         elif fast:  # the down product's tile is the primary list, the SwiGLU product may want a wider one
             tile_m, tile_m2 = ops.grouped_token_tile(TK, n_experts), ops.grouped_token_tile(TK, n_experts, swiglu=True)
@@ -208,13 +209,14 @@ class SparseMoeSwiGLU(FeedForward):
         products leave them some multiprocessors."""
         ctx, T, K, C, dev = self.ctx, h.shape[0], self.K, self.virtual, h.device
         KT = K + C
-        key = (T, dev)
+        small = al.tile_m if al.tile_m <= ops.SKINNY_MAX_ROWS else 0     # tiles for the weight-streaming products
+        key = (T, dev, small)
         st = self._static.get(key)
         if st is None:
             big = [k for k in self._static if k[0] > SIDE_MAX_ROWS]      # (small ones may belong to captured steps)
             if len(big) >= MAX_ALIGNMENTS:
                 self._static.pop(big[0])
-            st = self._static[key] = ops.StaticTiles(T, K, self.E, C, dev)
+            st = self._static[key] = ops.StaticTiles(T, K, self.E, C, dev, tile_m=small)
         act = torch.empty((T * KT, self.inter), dtype=ctx.act_dtype, device=dev)
         y = torch.empty((T * KT, self.hidden), dtype=torch.float32, device=dev)
         main, side = torch.cuda.current_stream(dev), _side_stream(dev)
@@ -222,12 +224,13 @@ class SparseMoeSwiGLU(FeedForward):
         fork.record(main)
         side.wait_event(fork)
         cap = int(ops.num_sms() * SIDE_GRID_SHARE) if many else 0
-        skinny = al.tile_m <= ops.SKINNY_MAX_ROWS and st.tile_m <= ops.SKINNY_MAX_ROWS
+        skinny = (al.tile_m <= ops.SKINNY_MAX_ROWS and st.tile_m <= ops.SKINNY_MAX_ROWS
+                  and ops.skinny_usable(h, self.w_gate_up, st.tile_m) and self.inter % 32 == 0)
         with torch.cuda.stream(side):
             if skinny:
                 ops.skinny_gemm(h, self.w_gate_up, act, swiglu=True, tiles=st, x_rows=st.x_rows, max_tile_rows=st.tile_m,
-                                err=ctx.err)
-                ops.skinny_gemm(act, self.w_down, y, tiles=st, max_tile_rows=st.tile_m, err=ctx.err)
+                                tiles_ready=True, err=ctx.err)
+                ops.skinny_gemm(act, self.w_down, y, tiles=st, max_tile_rows=st.tile_m, tiles_ready=True, err=ctx.err)
             else:
                 ops.gemm_fast_grouped(h, self.w_gate_up, act, al, swiglu=True, err=ctx.err, tiles=st, tiles_ready=True,
                                       x_rows=st.x_rows, max_ctas=cap)
@@ -242,7 +245,8 @@ class SparseMoeSwiGLU(FeedForward):
         if skinny:      # the rows are read where they are: no sorted copy
             ops.skinny_gemm(h, self.w_gate_up, act, swiglu=True, tiles=al.primary, a_rows=al.sorted_token,
                             max_tile_rows=al.tile_m, err=ctx.err)
-            ops.skinny_gemm(act, self.w_down, y, tiles=al.primary, max_tile_rows=al.tile_m, err=ctx.err)
+            ops.skinny_gemm(act, self.w_down, y, tiles=al.primary, max_tile_rows=al.tile_m, tiles_ready=True,
+                            err=ctx.err)
         else:
             x_sorted = ops.permute_rows(h, al.sorted_token, T * K)
             ops.gemm_fast_grouped(x_sorted, self.w_gate_up, act, al, swiglu=True, err=ctx.err, tiles_ready=True)

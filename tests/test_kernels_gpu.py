@@ -275,8 +275,8 @@ def test_always_on_experts_run_before_the_routing(T, E, K, C):
 
 # ------------------------------------------------------------------------------- small products, router
 # ------------------------------------------------------------------------------- products of a handful of rows
-@pytest.mark.parametrize("R,N,K", [(1, 5, 8), (1, 6144, 2048), (2, 130, 264), (3, 2048, 1408), (5, 61, 520), (8, 200, 3584),
-                                   (8, 4, 40), (7, 1000, 72)])
+@pytest.mark.parametrize("R,N,K", [(1, 5, 32), (1, 6144, 2048), (2, 130, 288), (3, 2048, 1408), (5, 61, 544), (8, 200, 3584),
+                                   (8, 4, 64), (7, 1000, 96), (4, 33, 20480)])
 @pytest.mark.parametrize("swiglu", [False, True])
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 def test_skinny_gemm_dense(R, N, K, swiglu, out_dtype):
@@ -297,6 +297,10 @@ def test_skinny_gemm_dense(R, N, K, swiglu, out_dtype):
         one = torch.empty((1, N), dtype=out_dtype, device=DEV)
         o.skinny_gemm(a[R - 1:R], w, one, bias=bias, swiglu=swiglu, rows=1)
         assert torch.equal(one[0], out[R - 1])
+    # sizes it does not take are refused, not guessed at
+    assert not o.skinny_usable(a[:, :K - 8], w[:, :K - 8].contiguous(), R) and not o.skinny_usable(a, w, 9)
+    with pytest.raises(o.KernelError):
+        o.skinny_gemm(a[:, :K - 8].contiguous(), w[:, :K - 8].contiguous(), out, swiglu=swiglu, rows=R)
 
 
 @pytest.mark.parametrize("T,E,K,I,H", [(1, 60, 4, 1408, 2048), (8, 6, 3, 40, 136), (5, 9, 2, 48, 96), (3, 3, 3, 24, 64)])
@@ -319,7 +323,7 @@ def test_skinny_gemm_grouped_through_the_routing(T, E, K, I, H):
     if not o.moe_route_small_usable(T, E, K, C, H):
         pytest.skip("the one-launch routing does not take these sizes")
     o.moe_route_small(logits, K, False, C, gate, idx, score, al, err, x=None, static=True)
-    st = o.StaticTiles(T, K, E, C, DEV)
+    st = o.StaticTiles(T, K, E, C, DEV, tile_m=o.SKINNY_MAX_ROWS)
     act = torch.full((T * KT, I), float("nan"), dtype=torch.bfloat16, device=DEV)
     y = torch.full((T * KT, H), float("nan"), device=DEV)
     o.skinny_gemm(x, w_gu, act, swiglu=True, tiles=st, x_rows=st.x_rows, max_tile_rows=st.tile_m, err=err)
