@@ -4,10 +4,10 @@
 // the whole matrix is on its way.  The tcgen05 kernel (tc_gemm.cu) pays for its set-up here: a weight tile of 128
 // rows per CTA leaves a 2,048 x 2,048 matrix with 16 tiles for 148 multiprocessors, so it splits K and needs a
 // second kernel to add the parts, and an expert's matrix for one row is 11 tiles that each pull 1 MB through one
-// CTA's ring.  This kernel has no ring and no set-up: a block of sixteen warps owns sixteen output features (sixteen
-// rows of W; with swiglu sixteen gate rows and their sixteen up rows), its warps share out K in steps of 32
-// elements, and every lane asks for all of its pieces of W at once, 16 bytes each, before it waits for the kernel
-// before it, whose output (x) it reads last.  The sums run on the tensor cores all the same: one
+// CTA's ring.  This kernel has no ring and no set-up: a block of sixteen warps takes sixteen output features at a
+// time (sixteen rows of W; with swiglu sixteen gate rows and their sixteen up rows), its warps share out K in steps
+// of 32 elements, and every lane asks for its pieces of W, 16 bytes each, a round ahead of the one it works on,
+// the first of them before it waits for the kernel before it, whose output (x) it reads last.  The sums run on the tensor cores all the same: one
 // mma.sync.m16n8k16 takes sixteen weight rows as A and up to eight rows of x as B.  A lane's 16 bytes are eight
 // consecutive k of one weight row; they are used as the lane's slots of two instructions' A fragments, and the
 // lane's 16 bytes of the x row at the same k as its B slots, so each instruction sums 16 values of k that are not
@@ -44,6 +44,7 @@ struct SkArgs {
   int R;                    // dense: rows
   int N, K, groups_n, out_dt, bias_dt, x_sub, x_mod, x_rows_total;
   int tiles_ready;          // grouped: the tile list was complete before the kernel before this one started
+  int max_tiles;
 };
 
 __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -54,89 +55,93 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint3
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// What a block works on at a time: sixteen output features of one tile (dense: the one tile of rows 0 .. R-1).
+struct SkGroup {
+  int row0, rows, n0;
+  const bf16* wbase;
+};
+
 template <bool SWIGLU>
-__global__ void __launch_bounds__(SK_WARPS * 32, 2) skinny_kernel(SkArgs a) {
+__global__ void __launch_bounds__(SK_WARPS * 32, 1) skinny_kernel(SkArgs a) {
   constexpr int NA = SWIGLU ? 2 : 1;                  // accumulators: gate and up
   constexpr int SK_BATCH = SK_LOADS / (2 * NA);       // steps of 32 elements of K per round of loads
-  __shared__ float part[SK_WARPS][NA][32][4];
+  __shared__ float part[2][SK_WARPS][NA][32][4];
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const int g = lane / 4, c = lane % 4;               // fragment row / column group of this lane
   const int grouped = a.tile_expert != nullptr;
-  const int y = grouped ? (int)(blockIdx.x / a.groups_n) : 0;
-  const int n0 = (int)(blockIdx.x % a.groups_n) * 16;
-  // A grouped product must know its tile before it can ask for weights; it may look before the wait only if the
+  // A grouped product must know its tiles before it can ask for weights; it may look before the wait only if the
   // list is older than the kernel before it.
   bool waited = false;
   if (grouped && !a.tiles_ready) {
     grid_dep_wait();
     waited = true;
   }
-  int row0 = 0, rows = a.R;
-  const bf16* wbase = a.w;
-  if (grouped) {
-    if (y >= *a.num_tiles) return;
-    row0 = a.tile_row0[y];
-    rows = a.tile_rows[y];
-    if (rows > SK_MAX_ROWS) {                         // the list was cut for another kernel: flag it, do what fits
-      if (a.err && threadIdx.x == 0) atomicExch(a.err, 1 + row0);
-      rows = SK_MAX_ROWS;
+  const int tiles = grouped ? min(*a.num_tiles, a.max_tiles) : 1;
+  const long long total = (long long)tiles * a.groups_n;            // groups of sixteen features, over all tiles
+  const int steps = a.K / 32;                                       // this warp takes steps warp, warp + 16, ...
+  const int my_steps = steps > warp ? (steps - warp + SK_WARPS - 1) / SK_WARPS : 0;
+  const int rounds = max(1, ((steps + SK_WARPS - 1) / SK_WARPS + SK_BATCH - 1) / SK_BATCH);   // the same for every warp
+
+  auto group_of = [&](long long q, SkGroup& gr) {
+    const int y = (int)(q / a.groups_n);
+    gr.n0 = (int)(q % a.groups_n) * 16;
+    gr.row0 = 0;
+    gr.rows = a.R;
+    gr.wbase = a.w;
+    if (grouped) {
+      gr.row0 = a.tile_row0[y];
+      gr.rows = a.tile_rows[y];
+      if (gr.rows > SK_MAX_ROWS) {                    // the list was cut for another kernel: flag it, do what fits
+        if (a.err && threadIdx.x == 0) atomicExch(a.err, 1 + gr.row0);
+        gr.rows = SK_MAX_ROWS;
+      }
+      gr.wbase += (size_t)a.tile_expert[y] * a.w_expert_stride;
     }
-    if (rows <= 0) return;
-    wbase += (size_t)a.tile_expert[y] * a.w_expert_stride;
-  }
-  // this lane's two weight rows (features n0 + g and n0 + g + 8), clamped to rows that exist
-  const int f_lo = min(n0 + g, a.N - 1), f_hi = min(n0 + g + 8, a.N - 1);
-  const uint4* w_lo[NA];
-  const uint4* w_hi[NA];
-#pragma unroll
-  for (int s = 0; s < NA; ++s) {
-    w_lo[s] = (const uint4*)(wbase + ((size_t)s * a.N + f_lo) * a.K) + c;
-    w_hi[s] = (const uint4*)(wbase + ((size_t)s * a.N + f_hi) * a.K) + c;
-  }
-  float acc[NA][4];
-#pragma unroll
-  for (int s = 0; s < NA; ++s) acc[s][0] = acc[s][1] = acc[s][2] = acc[s][3] = 0.f;
-  const int steps = a.K / 32;                         // this warp takes steps warp, warp + 16, ...
-  const uint4* xp = nullptr;
-  for (int s0 = warp; s0 < steps; s0 += SK_WARPS * SK_BATCH) {
-    uint4 wl[SK_BATCH][NA], wh[SK_BATCH][NA], xv[SK_BATCH];
+  };
+  // asks for this lane's pieces of W of round r of a group: its two weight rows (features n0 + g and n0 + g + 8,
+  // clamped to rows that exist), steps warp + 16 * (r * SK_BATCH + b)
+  auto issue = [&](const SkGroup& gr, int r, uint4 (&wl)[SK_BATCH][NA], uint4 (&wh)[SK_BATCH][NA]) {
+    const int f_lo = min(gr.n0 + g, a.N - 1), f_hi = min(gr.n0 + g + 8, a.N - 1);
 #pragma unroll
     for (int b = 0; b < SK_BATCH; ++b) {
-      const int st = s0 + b * SK_WARPS;
-      if (st < steps) {
+      const int i = r * SK_BATCH + b;
+      if (i < my_steps) {
+        const int st = warp + i * SK_WARPS;
 #pragma unroll
         for (int s = 0; s < NA; ++s) {
-          wl[b][s] = __ldcs(w_lo[s] + st * 4);        // streamed once
-          wh[b][s] = __ldcs(w_hi[s] + st * 4);
+          wl[b][s] = __ldcs((const uint4*)(gr.wbase + ((size_t)s * a.N + f_lo) * a.K) + c + st * 4);   // streamed once
+          wh[b][s] = __ldcs((const uint4*)(gr.wbase + ((size_t)s * a.N + f_hi) * a.K) + c + st * 4);
         }
       }
     }
-    if (!waited) {                                    // the weights are on their way: now wait for x
-      grid_dep_wait();
-      waited = true;
+  };
+  float acc[NA][4];
+  auto clear = [&]() {
+#pragma unroll
+    for (int s = 0; s < NA; ++s) acc[s][0] = acc[s][1] = acc[s][2] = acc[s][3] = 0.f;
+  };
+  int done = 0;                                       // groups this block has finished: which half of `part` is next
+  auto compute = [&](const SkGroup& gr, int r, const uint4 (&wl)[SK_BATCH][NA], const uint4 (&wh)[SK_BATCH][NA]) {
+    // this lane's row of x (column g of the B operand); lanes beyond the tile's rows multiply zeros
+    int src = gr.row0 + g;
+    if (grouped && g < gr.rows) {
+      if (a.a_rows) src = a.a_rows[src];
+      else if (a.x_mod) src = (src - a.x_sub) % a.x_mod;
     }
-    if (xp == nullptr) {
-      // this lane's row of x (column g of the B operand); lanes beyond the tile's rows multiply zeros
-      int src = row0 + g;
-      if (grouped && g < rows) {
-        if (a.a_rows) src = a.a_rows[src];
-        else if (a.x_mod) src = (src - a.x_sub) % a.x_mod;
-      }
-      if (g < rows && (src < 0 || src >= a.x_rows_total)) {      // a bad permutation: flag it and read row 0
-        if (a.err && c == 0) atomicExch(a.err, 1 + row0 + g);
-        src = 0;
-      }
-      xp = (const uint4*)(a.x + (size_t)(g < rows ? src : 0) * a.ldx) + c;
+    if (g < gr.rows && (src < 0 || src >= a.x_rows_total)) {      // a bad permutation: flag it and read row 0
+      if (a.err && c == 0) atomicExch(a.err, 1 + gr.row0 + g);
+      src = 0;
+    }
+    const uint4* xp = (const uint4*)(a.x + (size_t)(g < gr.rows ? src : 0) * a.ldx) + c;
+    uint4 xv[SK_BATCH];
+#pragma unroll
+    for (int b = 0; b < SK_BATCH; ++b) {
+      const int i = r * SK_BATCH + b;
+      xv[b] = (i < my_steps && g < gr.rows) ? __ldg(xp + (warp + i * SK_WARPS) * 4) : make_uint4(0, 0, 0, 0);
     }
 #pragma unroll
     for (int b = 0; b < SK_BATCH; ++b) {
-      const int st = s0 + b * SK_WARPS;
-      xv[b] = (st < steps && g < rows) ? __ldg(xp + st * 4) : make_uint4(0, 0, 0, 0);
-    }
-#pragma unroll
-    for (int b = 0; b < SK_BATCH; ++b) {
-      const int st = s0 + b * SK_WARPS;
-      if (st < steps) {
+      if (r * SK_BATCH + b < my_steps) {
 #pragma unroll
         for (int s = 0; s < NA; ++s) {
           mma_bf16_16816(acc[s], wl[b][s].x, wh[b][s].x, wl[b][s].y, wh[b][s].y, xv[b].x, xv[b].y);
@@ -144,30 +149,71 @@ __global__ void __launch_bounds__(SK_WARPS * 32, 2) skinny_kernel(SkArgs a) {
         }
       }
     }
+    if (r + 1 < rounds) return;
+    // the group is complete: the warps' sums are added in warp order.  The halves of `part` take turns, so one
+    // barrier per group is enough: a half is written again only after the barrier of the group in between.
+    float (*p)[NA][32][4] = part[done & 1];
+    ++done;
+#pragma unroll
+    for (int s = 0; s < NA; ++s)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) p[warp][s][lane][j] = acc[s][j];
+    clear();
+    __syncthreads();
+    if (threadIdx.x < 128) {
+      const int l = threadIdx.x / 4, j = threadIdx.x % 4;
+      float v[NA];
+#pragma unroll
+      for (int s = 0; s < NA; ++s) {
+        v[s] = 0.f;
+#pragma unroll
+        for (int wi = 0; wi < SK_WARPS; ++wi) v[s] += p[wi][s][l][j];
+      }
+      // accumulator element j of lane l: feature (l / 4) + 8 * (j / 2), row 2 * (l % 4) + (j % 2)
+      const int feat = gr.n0 + l / 4 + 8 * (j / 2), row = 2 * (l % 4) + (j % 2);
+      if (feat < a.N && row < gr.rows) {
+        float o = SWIGLU ? silu_mul(v[0], v[NA - 1]) : v[0];
+        if (!SWIGLU && a.bias) o += ld_dt(a.bias, a.bias_dt, feat);
+        st_dt(a.out, a.out_dt, (size_t)(gr.row0 + row) * a.ldo + feat, o);
+      }
+    }
+  };
+
+  // The block's work is the rounds of its groups (blockIdx.x, + gridDim.x, ...), one after the other; the loads of
+  // the round after next are asked for before a round is worked on (two sets of registers taking turns), so a lane
+  // always has loads in flight, also across the sum of a group.
+  uint4 wl0[SK_BATCH][NA], wh0[SK_BATCH][NA], wl1[SK_BATCH][NA], wh1[SK_BATCH][NA];
+  SkGroup g0, g1;
+  long long q0 = blockIdx.x, q1;
+  int r0 = 0, r1;
+  clear();
+  auto advance = [&](long long q, int r, long long& qn, int& rn) {
+    if (r + 1 < rounds) { qn = q; rn = r + 1; }
+    else { qn = q + gridDim.x; rn = 0; }
+  };
+  if (q0 < total) {
+    group_of(q0, g0);
+    issue(g0, r0, wl0, wh0);
   }
-  if (!waited) grid_dep_wait();                       // (a warp without a step of K) nothing is written before this
+  if (!waited) {                                      // the first weights are on their way: now wait for x
+    grid_dep_wait();
+    waited = true;
+  }
   grid_dep_launch();
-#pragma unroll
-  for (int s = 0; s < NA; ++s)
-#pragma unroll
-    for (int j = 0; j < 4; ++j) part[warp][s][lane][j] = acc[s][j];
-  __syncthreads();
-  if (threadIdx.x < 128) {
-    const int l = threadIdx.x / 4, j = threadIdx.x % 4;
-    float v[NA];
-#pragma unroll
-    for (int s = 0; s < NA; ++s) {
-      v[s] = 0.f;
-#pragma unroll
-      for (int wi = 0; wi < SK_WARPS; ++wi) v[s] += part[wi][s][l][j];
+  while (q0 < total) {
+    advance(q0, r0, q1, r1);
+    if (q1 < total) {
+      if (r1 == 0) group_of(q1, g1); else g1 = g0;
+      issue(g1, r1, wl1, wh1);
     }
-    // accumulator element j of lane l: feature (l / 4) + 8 * (j / 2), row 2 * (l % 4) + (j % 2)
-    const int feat = n0 + l / 4 + 8 * (j / 2), row = 2 * (l % 4) + (j % 2);
-    if (feat < a.N && row < rows) {
-      float r = SWIGLU ? silu_mul(v[0], v[NA - 1]) : v[0];
-      if (!SWIGLU && a.bias) r += ld_dt(a.bias, a.bias_dt, feat);
-      st_dt(a.out, a.out_dt, (size_t)(row0 + row) * a.ldo + feat, r);
+    compute(g0, r0, wl0, wh0);
+    if (q1 >= total) break;
+    advance(q1, r1, q0, r0);
+    if (q0 < total) {
+      if (r0 == 0) group_of(q0, g0); else g0 = g1;
+      issue(g0, r0, wl0, wh0);
     }
+    compute(g1, r1, wl1, wh1);
   }
 }
 
@@ -204,11 +250,17 @@ NV_API int nv_skinny_gemm(const void* x, long long ldx, int x_rows_total, int R,
   a.R = R; a.N = N; a.K = K; a.out_dt = out_dt; a.bias_dt = bias_dt;
   a.x_sub = x_sub; a.x_mod = x_mod; a.x_rows_total = x_rows_total; a.tiles_ready = tiles_ready ? 1 : 0;
   a.groups_n = (N + 15) / 16;
-  const long long blocks = (long long)(grouped ? max_tiles : 1) * a.groups_n;
-  if (blocks > 0x7fffffffLL) return NV_ERR_BAD_SIZE;
+  a.max_tiles = grouped ? max_tiles : 1;
+  long long blocks = (long long)a.max_tiles * a.groups_n;           // an upper bound when grouped
+  static int num_sms = 0;
+  if (!num_sms) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || num_sms <= 0)
+      num_sms = 148;
+  }
+  if (blocks > num_sms) blocks = num_sms;                           // one block per multiprocessor walks the groups
   const dim3 grid((unsigned)blocks), block(SK_WARPS * 32);
-  // (the dependent-launch limit on the grid size does not apply: these blocks hold no shared-memory ring and leave
-  // as soon as their few loads are done)
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;

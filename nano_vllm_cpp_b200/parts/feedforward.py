@@ -132,8 +132,9 @@ class SparseMoeSwiGLU(FeedForward):
             self.virtual = 0
 
     def _alignment(self, TK, n_experts, device, fast, rows=0):
-        if (fast and 0 < rows <= linear_mod.SKINNY_ROWS and self.hidden % 32 == 0
-                and self.inter % 32 == 0):                   # the weight-streaming products: tiles of at most 8 rows
+        if (fast and 0 < rows <= linear_mod.SKINNY_ROWS and rows * self.K <= linear_mod.SKINNY_MAX_PAIRS
+                and self.hidden % 32 == 0 and self.inter % 32 == 0):
+            # a few pairs: the weight-streaming products, over tiles of at most 8 rows
             tile_m, tile_m2 = ops.SKINNY_MAX_ROWS, 0
         elif fast:  # the down product's tile is the primary list, the SwiGLU product may want a wider one
             tile_m, tile_m2 = ops.grouped_token_tile(TK, n_experts), ops.grouped_token_tile(TK, n_experts, swiglu=True)

@@ -303,7 +303,7 @@ def test_skinny_gemm_dense(R, N, K, swiglu, out_dtype):
         o.skinny_gemm(a[:, :K - 8].contiguous(), w[:, :K - 8].contiguous(), out, swiglu=swiglu, rows=R)
 
 
-@pytest.mark.parametrize("T,E,K,I,H", [(1, 60, 4, 1408, 2048), (8, 6, 3, 40, 136), (5, 9, 2, 48, 96), (3, 3, 3, 24, 64)])
+@pytest.mark.parametrize("T,E,K,I,H", [(1, 60, 4, 1408, 2048), (8, 6, 3, 64, 160), (5, 9, 2, 96, 96), (3, 3, 3, 32, 64), (8, 60, 4, 1408, 2048)])
 def test_skinny_gemm_grouped_through_the_routing(T, E, K, I, H):
     """The two expert products over the one-launch routing's tile list (tiles of at most eight rows), rows read in
     place through the permutation, and the always-on experts' rows by (row - sub) mod T, against float64."""
