@@ -721,18 +721,20 @@ def gemm_fast(a, w, out, *, bias=None, a_rows=None, swiglu=False, M=None, err=No
                         c_longlong(out.stride(0)), c_int(1 if swiglu else 0), c_int(n_tile), c_int(splits),
                         _p(scratch), _p(None), _p(None), _p(None), _p(None), c_int(0), c_int(0),
                         _p(err.t if err is not None else _global_err().t), c_int(_early()), c_int(0), c_int(0),
-                        c_int(0), _stream()), f"tc_gemm N={rows_w} K={K}", 2.0 * M * rows_w * K,
+                        c_int(0), _p(None), _stream()), f"tc_gemm N={rows_w} K={K}", 2.0 * M * rows_w * K,
            w.element_size() * rows_w * K + a.element_size() * M * K + out.element_size() * M * N)
 
 
 def gemm_fast_grouped(a, w, out, align, *, a_rows=None, swiglu=False, err=None, tiles=None, tiles_ready=False,
-                      x_rows=None, max_ctas: int = 0) -> None:
+                      x_rows=None, max_ctas: int = 0, counter=None) -> None:
     """Tensor-core form of the grouped ``gemm_plain``; ``tiles`` (a TileList of ``align``) picks the token tile.
 
     ``x_rows`` = (sub, mod): a tile whose outputs are rows r.. takes rows ``(r - sub) % mod``.. of ``a`` (several
     experts that all take the same few rows, their outputs one segment after the other).
 
     ``max_ctas`` > 0 caps the grid, for a product that runs beside other kernels and must leave them room.
+    ``counter`` (one int32 on the device, 0 between launches, used by one product at a time): the CTAs take their
+    tiles from it instead of by position, so a CTA that starts late takes fewer.
 
     ``tiles_ready``: the tile lists were complete before the kernel that precedes this product on the stream
     started, so the product may start beside that kernel and fetch its first weights (it reads the lists at
@@ -753,7 +755,7 @@ def gemm_fast_grouped(a, w, out, align, *, a_rows=None, swiglu=False, err=None, 
                             _p(tl.tile_row0), _p(tl.tile_rows), _p(tl.num_tiles), c_int(tl.max_tiles),
                             c_int(rows_w), _p(err.t if err is not None else _global_err().t),
                             c_int(_early() if tiles_ready else 0), c_int(x_sub), c_int(x_mod), c_int(max_ctas),
-                            _stream()),
+                            _p(counter), _stream()),
            f"tc_gemm_grouped N={rows_w} K={K}")
 
 

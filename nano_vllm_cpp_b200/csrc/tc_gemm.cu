@@ -39,6 +39,7 @@ constexpr int BLOCK_K = 64;     // elements of K per stage: 128 bytes = one swiz
 constexpr int UMMA_K = 16;
 constexpr int MAX_STAGES = 8;
 constexpr int NUM_THREADS = 192;
+constexpr int TQ_DEPTH = 4;     // tile numbers in flight between the producer and the other warps (counter mode)
 
 struct TcArgs {
   void* out;
@@ -68,6 +69,10 @@ struct TcArgs {
   // Grouped products whose tiles' tokens are not rows row0.. of X but rows (row0 - x_sub) mod x_mod.. of it
   // (x_mod > 0): several experts that all take the same rows of a short X, outputs one segment after the other.
   int x_sub, x_mod;
+  // Tiles handed out by a counter instead of by position (nullptr: CTA b takes tiles b, b + grid, ...): a CTA that
+  // starts late, because another kernel still holds its multiprocessor, then takes fewer tiles, and CTAs whose tiles
+  // are short take more.  The counter must be 0 at launch; the CTA that draws the last number sets it back to 0.
+  int* tile_counter;
 };
 
 // ------------------------------------------------------------------ the kernel
@@ -208,6 +213,8 @@ __global__ void __launch_bounds__(MODE == 2 ? WIDE_THREADS : NUM_THREADS, MODE =
 tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, TcArgs a) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   __shared__ uint64_t full_bar[MAX_STAGES], empty_bar[MAX_STAGES], acc_full[2], acc_empty[2];
+  __shared__ uint64_t tq_full[TQ_DEPTH], tq_empty[TQ_DEPTH];       // the producer hands the tile numbers it drew on
+  __shared__ int tq_tile[TQ_DEPTH];
   __shared__ uint32_t tmem_base_s;
 
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
@@ -231,6 +238,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       mbar_init(&acc_full[b], 1);
       mbar_init(&acc_empty[b], MODE == 2 ? 8 : 4);  // one arrival per epilogue warp
     }
+    for (int q = 0; q < TQ_DEPTH; ++q) {
+      mbar_init(&tq_full[q], 1);
+      mbar_init(&tq_empty[q], 1 + (MODE == 2 ? 8 : 4));   // the MMA thread and every epilogue warp have read it
+    }
     mbar_fence_init();
   }
   if (warp == 1) tmem_alloc(&tmem_base_s, a.tmem_cols);
@@ -238,6 +249,18 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_s;
+  const bool by_counter = a.tile_counter != nullptr;
+  // The n-th tile of this CTA as the MMA thread and the epilogue warps learn it: by position, or from the producer.
+  // (`whole_warp`: all 32 lanes call it together, as the epilogue warps do; the MMA thread calls it alone.)
+  auto nth_tile = [&](int n, bool whole_warp) -> int {
+    if (!by_counter) return (int)blockIdx.x + n * (int)gridDim.x;
+    const int q = n % TQ_DEPTH;
+    mbar_wait(&tq_full[q], (n / TQ_DEPTH) & 1, a.err, 0x7005);
+    const int tile = tq_tile[q];
+    if (whole_warp) __syncwarp();                  // every lane has read the number before the slot is given back
+    if (lane == 0) mbar_arrive(&tq_empty[q]);
+    return tile;
+  };
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
@@ -246,44 +269,104 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     if (lane == 0) {
       const int pre = a.early ? a.stages : 0;
       const uint32_t smem0 = smem_u32(smem), full0 = smem_u32(&full_bar[0]);
-      // issues the k-steps numbered [first, last) of this CTA's walk over its tiles
-      auto walk = [&](int first, int last, bool weights, bool tokens) {
-        int it = 0;
-        Tile t;
-        for (int tile = blockIdx.x; it < last && get_tile(a, tile, y_tiles, t); tile += gridDim.x) {
-          // tokens come in boxes of x_box rows, as many as the tile's rows (rounded up to the 16 of the MMA) need.
-          // (What a tile fixes is worked out here, once: this one thread's instructions are the pace of the ring.)
-          const int n_act = min(a.n_tile, (t.rows_here + 15) & ~15);
-          const int boxes = (n_act + a.x_box - 1) / a.x_box;
-          const uint32_t bytes = a_bytes * (two ? 2 : 1) + (uint32_t)boxes * a.x_box * 128;
-          const int wr = t.w_row_base + t.nb * a.w_per_cta;
-          int s = it % a.stages, ph = (it / a.stages) & 1;          // stage and phase of k-step `it`, kept by counting
-          for (int k = 0; k < t.n_steps && it < last; ++k, ++it, s = (s + 1 == a.stages ? 0 : s + 1), ph ^= (s == 0)) {
-            if (it < first) continue;
-            const uint32_t st = smem0 + (uint32_t)s * stage_bytes, bar = full0 + (uint32_t)s * 8;
-            if (weights) {
-              mbar_wait(&empty_bar[s], ph ^ 1, a.err, 0x7001);
-              mbar_expect_tx_a(bar, bytes);
-            }
-            const int kc = (t.k_begin + k) * BLOCK_K;
-            if (weights) {
-              tma_load_2d_a(st, &tm_w, bar, kc, wr);
-              if (two)     // swiglu: the up rows of the same features; dual: the next 128 features
-                tma_load_2d_a(st + a_bytes, &tm_w, bar, kc, wr + (a.swiglu ? a.N : TILE_W));
-            }
-            if (tokens)
-              for (int b = 0; b < boxes; ++b)
-                tma_load_2d_a(st + a_bytes * (two ? 2 : 1) + (uint32_t)b * a.x_box * 128, &tm_x, bar, kc,
-                              t.x_row0 + b * a.x_box);
+      // The n-th tile of this CTA as the producer learns it: by position, or by drawing the next number from the
+      // counter, which it also hands on to the other warps.  Numbers past the last tile end the walk; the CTA that
+      // draws the very last one (every CTA draws exactly one such number) sets the counter back for the next launch.
+      const int total_tiles = a.n_blocks * y_tiles * a.splits;
+      auto draw = [&](int n) -> int {
+        if (!by_counter) return (int)blockIdx.x + n * (int)gridDim.x;
+        const int tile = atomicAdd(a.tile_counter, 1);
+        if (tile == total_tiles + (int)gridDim.x - 1) *a.tile_counter = 0;
+        const int q = n % TQ_DEPTH;
+        mbar_wait(&tq_empty[q], ((n / TQ_DEPTH) & 1) ^ 1, a.err, 0x7006);
+        tq_tile[q] = tile;
+        mbar_arrive(&tq_full[q]);
+        return tile;
+      };
+      int it = 0;                                              // k-steps issued so far
+      int s = 0, ph = 0;                                       // stage and phase of k-step `it`, kept by counting
+      // issues k-steps [k0, k1) of a tile: weights and / or tokens
+      auto issue = [&](const Tile& t, int k0, int k1, bool weights, bool tokens, int s_, int ph_) {
+        // tokens come in boxes of x_box rows, as many as the tile's rows (rounded up to the 16 of the MMA) need.
+        // (What a tile fixes is worked out here, once: this one thread's instructions are the pace of the ring.)
+        const int n_act = min(a.n_tile, (t.rows_here + 15) & ~15);
+        const int boxes = (n_act + a.x_box - 1) / a.x_box;
+        const uint32_t bytes = a_bytes * (two ? 2 : 1) + (uint32_t)boxes * a.x_box * 128;
+        const int wr = t.w_row_base + t.nb * a.w_per_cta;
+        for (int k = k0; k < k1; ++k, s_ = (s_ + 1 == a.stages ? 0 : s_ + 1), ph_ ^= (s_ == 0)) {
+          const uint32_t st = smem0 + (uint32_t)s_ * stage_bytes, bar = full0 + (uint32_t)s_ * 8;
+          if (weights) {
+            mbar_wait(&empty_bar[s_], ph_ ^ 1, a.err, 0x7001);
+            mbar_expect_tx_a(bar, bytes);
           }
+          const int kc = (t.k_begin + k) * BLOCK_K;
+          if (weights) {
+            tma_load_2d_a(st, &tm_w, bar, kc, wr);
+            if (two)     // swiglu: the up rows of the same features; dual: the next 128 features
+              tma_load_2d_a(st + a_bytes, &tm_w, bar, kc, wr + (a.swiglu ? a.N : TILE_W));
+          }
+          if (tokens)
+            for (int b = 0; b < boxes; ++b)
+              tma_load_2d_a(st + a_bytes * (two ? 2 : 1) + (uint32_t)b * a.x_box * 128, &tm_x, bar, kc,
+                            t.x_row0 + b * a.x_box);
         }
       };
+      auto advance = [&](int steps) {
+        for (int k = 0; k < steps; ++k) {
+          if (++s == a.stages) { s = 0; ph ^= 1; }
+        }
+        it += steps;
+      };
+      Tile t;
+      int n = 0;
+      bool have = get_tile(a, draw(n), y_tiles, t);
       if (pre) {
-        walk(0, pre, true, false);
-        grid_dep_wait();
-        walk(0, pre, false, true);
+        // the weights of the first ring-full of k-steps before the wait, their tokens after it.  (By position the
+        // ring-full may span several tiles; by counter it ends with the first tile, the second is drawn later.)
+        if (!by_counter) {
+          // walk the first `pre` k-steps twice
+          Tile u = t;
+          int n2 = 0, left = pre, s2 = 0, ph2 = 0;
+          bool h2 = have;
+          while (h2 && left > 0) {
+            const int k1 = min(u.n_steps, left);
+            issue(u, 0, k1, true, false, s2, ph2);
+            for (int k = 0; k < k1; ++k) if (++s2 == a.stages) { s2 = 0; ph2 ^= 1; }
+            left -= k1;
+            if (k1 < u.n_steps) break;
+            h2 = get_tile(a, draw(++n2), y_tiles, u);
+          }
+          grid_dep_wait();
+          left = pre;
+          while (have && left > 0) {
+            const int k1 = min(t.n_steps, left);
+            issue(t, 0, k1, false, true, s, ph);
+            advance(k1);
+            left -= k1;
+            if (k1 < t.n_steps) {          // the rest of this tile follows below
+              issue(t, k1, t.n_steps, true, true, s, ph);
+              advance(t.n_steps - k1);
+            }
+            have = get_tile(a, draw(++n), y_tiles, t);
+          }
+        } else {
+          const int k1 = have ? min(t.n_steps, pre) : 0;
+          if (have) issue(t, 0, k1, true, false, s, ph);
+          grid_dep_wait();
+          if (have) {
+            issue(t, 0, k1, false, true, s, ph);
+            advance(k1);
+            issue(t, k1, t.n_steps, true, true, s, ph);
+            advance(t.n_steps - k1);
+            have = get_tile(a, draw(++n), y_tiles, t);
+          }
+        }
       }
-      walk(pre, 0x7fffffff, true, true);
+      while (have) {
+        issue(t, 0, t.n_steps, true, true, s, ph);
+        advance(t.n_steps);
+        have = get_tile(a, draw(++n), y_tiles, t);
+      }
       grid_dep_launch();          // all loads are on their way: the next kernel may take the SMs that fall idle
     }
   } else if (warp == 1) {
@@ -295,7 +378,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       const uint64_t desc0 = smem_desc_sw128(0);
       const uint32_t smem0 = smem_u32(smem);
       Tile t;
-      for (int tile = blockIdx.x; get_tile(a, tile, y_tiles, t); tile += gridDim.x, ++n) {
+      for (; get_tile(a, nth_tile(n, false), y_tiles, t); ++n) {
         const int b = a.acc_bufs == 2 ? (n & 1) : 0;
         const int use = a.acc_bufs == 2 ? (n >> 1) : n;          // how often this buffer was used before
         mbar_wait(&acc_empty[b], (use & 1) ^ 1, a.err, 0x7004);  // the epilogue has drained it
@@ -325,7 +408,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     const int q = warp % 4;                        // a warp may read TMEM lanes [32q, 32q + 32) only
     int n_done = 0;
     Tile t;
-    for (int tile = blockIdx.x; get_tile(a, tile, y_tiles, t); tile += gridDim.x, ++n_done) {
+    for (; get_tile(a, nth_tile(n_done, true), y_tiles, t); ++n_done) {
       const int b = a.acc_bufs == 2 ? (n_done & 1) : 0;
       const int use = a.acc_bufs == 2 ? (n_done >> 1) : n_done;
       const int n = t.nb * a.w_per_cta + q * 32 + lane;   // this thread's output feature (dual: and n + 128)
@@ -531,7 +614,7 @@ NV_API int nv_tc_gemm(const void* X, long long ldx, int M_tok, const void* W, in
                       const void* bias, int bias_dt, void* out, int out_dt, long long ldo, int swiglu, int n_tile,
                       int splits, float* scratch, const int* tile_expert, const int* tile_row0,
                       const int* tile_rows, const int* num_tiles, int max_tiles, int rows_per_expert, int* err,
-                      int early, int x_sub, int x_mod, int max_ctas, cudaStream_t stream) {
+                      int early, int x_sub, int x_mod, int max_ctas, int* tile_counter, cudaStream_t stream) {
   if (!dt_ok(out_dt) || (bias && !dt_ok(bias_dt))) return NV_ERR_BAD_DTYPE;
   if (K % 8 || ldx % 8 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return NV_ERR_UNSUPPORTED;  // TMA: 16-byte rules
   if (n_tile < 16 || n_tile > 256 || (n_tile & (n_tile - 1))) return NV_ERR_BAD_SIZE;
@@ -559,6 +642,7 @@ NV_API int nv_tc_gemm(const void* X, long long ldx, int M_tok, const void* W, in
   a.early = early ? 1 : 0;
   a.x_box = x_box;
   a.x_sub = x_sub; a.x_mod = x_mod;
+  a.tile_counter = tile_counter;
   // Many tokens per tile and enough features: two weight tiles per CTA.  The operands then cost 2*16 KB + X
   // per k-step for twice the flops, which is what the shared-memory fill rate, the limit here, rewards.
   // ... provided the halved grid still covers the GPU (measured: a half-empty GPU loses more than the tile gains)
@@ -612,7 +696,7 @@ NV_API int nv_tc_gemm(const void* X, long long ldx, int M_tok, const void* W, in
   // a last wave with tiles for less than half of the CTAs: cut those tiles into two or four token parts
   a.rest_first = 0;
   a.rest_parts = 1;
-  if (!grouped && a.splits == 1 && total > resident && M_tok % n_tile == 0 && n_tile >= 128) {
+  if (!grouped && !tile_counter && a.splits == 1 && total > resident && M_tok % n_tile == 0 && n_tile >= 128) {
     const long long rest = total % resident;
     if (rest > 0 && rest * 2 <= resident) {
       a.rest_parts = (rest * 4 <= resident && n_tile >= 256) ? 4 : 2;

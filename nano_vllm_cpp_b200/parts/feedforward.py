@@ -62,6 +62,7 @@ class SparseMoeSwiGLU(FeedForward):
         self.hidden, self.E, self.K = hidden_size, num_experts, top_k
         self.inter, self.shared_inter, self.renorm = intermediate_size, shared_intermediate_size, renormalize
         self._align = {}
+        self._counters = None
         self._captured = {}
         self._static = {}
         self.router_and_gate = None
@@ -249,9 +250,16 @@ class SparseMoeSwiGLU(FeedForward):
             ops.skinny_gemm(act, self.w_down, y, tiles=al.primary, max_tile_rows=al.tile_m, tiles_ready=True,
                             err=ctx.err)
         else:
+            # (a prompt's routed products start while the side products still hold most multiprocessors: their CTAs
+            # take tiles from a counter, so the ones that start early do more of the work)
+            c0 = c1 = None
+            if many:
+                if self._counters is None:
+                    self._counters = torch.zeros(2, dtype=torch.int32, device=dev)
+                c0, c1 = self._counters[0:1], self._counters[1:2]
             x_sorted = ops.permute_rows(h, al.sorted_token, T * K)
-            ops.gemm_fast_grouped(x_sorted, self.w_gate_up, act, al, swiglu=True, err=ctx.err, tiles_ready=True)
-            ops.gemm_fast_grouped(act, self.w_down, y, al, err=ctx.err, tiles_ready=True)
+            ops.gemm_fast_grouped(x_sorted, self.w_gate_up, act, al, swiglu=True, err=ctx.err, tiles_ready=True, counter=c0)
+            ops.gemm_fast_grouped(act, self.w_down, y, al, err=ctx.err, tiles_ready=True, counter=c1)
         main.wait_event(join)
         return RowMix(y, al.pair_pos[:T * KT].view(T, KT), score, None, None)
 

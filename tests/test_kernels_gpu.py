@@ -205,6 +205,16 @@ def test_tc_gemm_grouped(T, E, K):
         if fast:
             o.gemm_fast_grouped(x, w1, act, al, a_rows=al.sorted_token, swiglu=True, err=err)
             o.gemm_fast_grouped(act, w2, y, al, err=err)
+            # the same with tiles taken from a counter (twice: the counter sets itself back), also on a capped grid
+            counter = torch.zeros(2, dtype=torch.int32, device=DEV)
+            for cap in (0, 3):
+                act2, y2 = torch.full_like(act, float("nan")), torch.full_like(y, float("nan"))
+                o.gemm_fast_grouped(x, w1, act2, al, a_rows=al.sorted_token, swiglu=True, err=err, counter=counter[0:1],
+                                    max_ctas=cap)
+                o.gemm_fast_grouped(act2, w2, y2, al, err=err, tiles_ready=True, counter=counter[1:2], max_ctas=cap)
+                err.check("grouped, by counter")
+                assert counter.tolist() == [0, 0]
+                assert torch.equal(act2, act) and torch.equal(y2, y)
         else:
             o.gemm_plain(x, w1, act, a_rows=al.sorted_token, swiglu=True, M=T * K, tiles=al.tiles)
             o.gemm_plain(act, w2, y, M=T * K, tiles=al.tiles)
