@@ -468,8 +468,10 @@ __global__ void gather_rows_kernel(const void* __restrict__ src, int dt, const i
 // ------------------------------------------------------------------------ sampling
 // temperature <= 0: the first largest logit.  Otherwise p_i = exp((l_i - max) / T) in double,
 // target = u * sum p, answer = first i whose running sum exceeds target, V-1 if none
-// (include/nanovllm/sampler.hpp:10-34).  One block per row; a thread owns a contiguous run of
-// the vocabulary, so the running sum is taken in index order.
+// (include/nanovllm/sampler.hpp:10-34).  One block per row.  The largest logit is found with the threads striding
+// through the row together (a thread meets its own candidates in ascending order and ties go to the lower index
+// when threads are compared, so the first largest wins); for the running sum a thread owns a contiguous run of
+// the vocabulary, so that it is taken in index order.
 constexpr int SAMPLE_THREADS = 1024;
 __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const float* __restrict__ logits, int V,
                                                                 const float* __restrict__ temperature,
@@ -485,8 +487,14 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const float* __r
   const int b = min(V, tid * per), e = min(V, b + per);
   float mx = -INFINITY;
   int mi = 0x7fffffff;
-  for (int i = b; i < e; ++i)
-    if (l[i] > mx) { mx = l[i]; mi = i; }
+  for (int i0 = tid; i0 < V; i0 += 4 * SAMPLE_THREADS) {      // four loads in flight
+    float v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = i0 + j * SAMPLE_THREADS < V ? l[i0 + j * SAMPLE_THREADS] : -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (v[j] > mx) { mx = v[j]; mi = i0 + j * SAMPLE_THREADS; }
+  }
   fmx[tid] = mx;
   fidx[tid] = mi;
   __syncthreads();
