@@ -514,9 +514,8 @@ class StaticTiles:
     """The tiles of C experts E .. E + C - 1 that each take all T rows, in row order, their segments behind the
     T * K routed pairs: what ``moe_route_small(static=True)`` leaves out of its list."""
 
-    def __init__(self, T: int, K: int, E: int, C: int, device, tile_m: int = 0):
-        """``tile_m``: rows per tile (0: the tensor-core product's tile for T rows)."""
-        self.tile_m = tile_m or (16 if T <= 16 else (32 if T <= 32 else (64 if T <= 64 else 128)))
+    def __init__(self, T: int, K: int, E: int, C: int, device):
+        self.tile_m = 16 if T <= 16 else (32 if T <= 32 else (64 if T <= 64 else 128))
         experts, row0, rows = [], [], []
         for c in range(C):
             for r in range(0, T, self.tile_m):
@@ -644,38 +643,22 @@ def skinny_usable(a, w, rows: int) -> bool:
             and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def skinny_gemm(a, w, out, *, bias=None, swiglu=False, rows=None, tiles=None, a_rows=None, x_rows=None,
-                max_tile_rows: int = 0, tiles_ready: bool = False, err=None) -> None:
-    """``out = a @ w.T`` for at most eight rows (``rows``: how many rows of ``a``, default all), by streaming ``w``
-    once; ``swiglu`` as in ``gemm_plain``.  Grouped form with ``tiles`` (a ``TileList`` whose tiles have at most
-    ``max_tile_rows`` <= 8 rows; ``w`` is [E, rows, K]): output row r of a tile of expert e is
-    ``a[a_rows[r]] @ w[e].T``, or ``a[(r - sub) % mod]`` with ``x_rows = (sub, mod)``, or ``a[r]``.
-    ``tiles_ready``: the tile list was complete before the kernel that precedes this product on the stream started,
-    so the product may ask for its weights while that kernel still runs."""
-    _cuda_contig(w, bias, a_rows)
-    _i32(a_rows)
+def skinny_gemm(a, w, out, *, bias=None, swiglu=False, rows=None, err=None) -> None:
+    """``out[:rows] = a[:rows] @ w.T (+ bias)`` for at most eight rows (default: all rows of ``a``), by streaming
+    ``w`` once; ``swiglu`` as in ``gemm_plain``."""
+    _cuda_contig(w, bias)
     K = a.shape[-1]
-    rows_w = w.shape[-2]
+    rows_w = w.shape[0]
     N = rows_w // 2 if swiglu else rows_w
-    grouped = tiles is not None
-    R = (a.shape[0] if rows is None else rows) if not grouped else 0
-    _need(skinny_usable(a, w, max_tile_rows if grouped else R), "skinny product: operands or row count not supported")
-    _need(w.shape[-1] == K and out.shape[1] == N and out.stride(1) == 1, "skinny product: shapes")
-    x_sub, x_mod = x_rows if x_rows is not None else (0, 0)
-    te = tr0 = tr = nt = None
-    max_tiles = 0
-    if grouped:
-        te, tr0, tr, nt, max_tiles = tiles.tile_expert, tiles.tile_row0, tiles.tile_rows, tiles.num_tiles, tiles.max_tiles
-    else:
-        _need(out.shape[0] >= R, "skinny product: out rows")
-    _check(lib().nv_skinny_gemm(_p(a), c_longlong(a.stride(0)), c_int(a.shape[0]), c_int(R), _p(w), c_int(N), c_int(K),
+    R = a.shape[0] if rows is None else rows
+    _need(skinny_usable(a, w, R), "skinny product: operands or row count not supported")
+    _need(w.dim() == 2 and w.shape[1] == K and out.shape[1] == N and out.stride(1) == 1 and out.shape[0] >= R,
+          "skinny product: shapes")
+    _need(bias is None or (not swiglu and bias.numel() == N), "skinny product: bias")
+    _check(lib().nv_skinny_gemm(_p(a), c_longlong(a.stride(0)), c_int(R), _p(w), c_int(N), c_int(K),
                                 _p(bias), c_int(dt(bias) if bias is not None else 0), _p(out), c_int(dt(out)),
-                                c_longlong(out.stride(0)), c_int(1 if swiglu else 0), _p(a_rows), _p(te), _p(tr0), _p(tr),
-                                _p(nt), c_int(max_tiles), c_int(max_tile_rows), c_int(x_sub), c_int(x_mod),
-                                c_int(1 if tiles_ready else 0), _p(err.t if err is not None else _global_err().t),
-                                _stream()),
-           f"skinny_gemm{'_grouped' if grouped else ''} N={rows_w} K={K}", 0.0,
-           0.0 if grouped else float(w.element_size() * rows_w * K))
+                                c_longlong(out.stride(0)), c_int(1 if swiglu else 0), _stream()),
+           f"skinny_gemm N={rows_w} K={K}", 0.0, float(w.element_size() * rows_w * K))
 
 
 def grouped_token_tile(TK: int, E: int, swiglu: bool = False) -> int:
@@ -721,7 +704,7 @@ def gemm_fast(a, w, out, *, bias=None, a_rows=None, swiglu=False, M=None, err=No
                         c_longlong(out.stride(0)), c_int(1 if swiglu else 0), c_int(n_tile), c_int(splits),
                         _p(scratch), _p(None), _p(None), _p(None), _p(None), c_int(0), c_int(0),
                         _p(err.t if err is not None else _global_err().t), c_int(_early()), c_int(0), c_int(0),
-                        c_int(0), _p(None), _stream()), f"tc_gemm N={rows_w} K={K}", 2.0 * M * rows_w * K,
+                        c_int(0), _p(None), c_int(0), _stream()), f"tc_gemm N={rows_w} K={K}", 2.0 * M * rows_w * K,
            w.element_size() * rows_w * K + a.element_size() * M * K + out.element_size() * M * N)
 
 
@@ -749,13 +732,23 @@ def gemm_fast_grouped(a, w, out, align, *, a_rows=None, swiglu=False, err=None, 
     _need(tl.tile_m in (16, 32, 64, 128, 256), "grouped product: token tile must be 16, 32, 64, 128 or 256")
     x_sub, x_mod = x_rows if x_rows is not None else (0, 0)
     _need(out.shape[0] >= align.TK and (x_mod or a.shape[0] <= align.TK), "grouped product: row counts")
+    # A handful of rows: the list has few tiles (an expert's matrix is a dozen tiles of 128 features), which would
+    # leave most multiprocessors idle and each CTA with a long stream of its own; K is then split as in a small
+    # dense product and a finishing kernel adds the parts.
+    splits, scratch = 1, None
+    k_steps = (K + 63) // 64
+    ctas = tl.max_tiles * ((N + 127) // 128)
+    if counter is None and ctas < num_sms() and k_steps >= 8:
+        splits = max(1, min(2 * num_sms() // ctas, k_steps // 4, 16))
+        if splits > 1:
+            scratch = torch.empty((splits, align.TK, 2 * N if swiglu else N), dtype=torch.float32, device=a.device)
     _check(lib().nv_tc_gemm(_p(a), c_longlong(a.stride(0)), c_int(a.shape[0]), _p(w), c_int(E * rows_w), c_int(N),
                             c_int(K), _p(None), c_int(0), _p(out), c_int(dt(out)), c_longlong(out.stride(0)),
-                            c_int(1 if swiglu else 0), c_int(tl.tile_m), c_int(1), _p(None), _p(tl.tile_expert),
+                            c_int(1 if swiglu else 0), c_int(tl.tile_m), c_int(splits), _p(scratch), _p(tl.tile_expert),
                             _p(tl.tile_row0), _p(tl.tile_rows), _p(tl.num_tiles), c_int(tl.max_tiles),
                             c_int(rows_w), _p(err.t if err is not None else _global_err().t),
                             c_int(_early() if tiles_ready else 0), c_int(x_sub), c_int(x_mod), c_int(max_ctas),
-                            _p(counter), _stream()),
+                            _p(counter), c_int(align.TK), _stream()),
            f"tc_gemm_grouped N={rows_w} K={K}")
 
 

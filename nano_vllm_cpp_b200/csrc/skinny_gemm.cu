@@ -1,50 +1,40 @@
-// Products of a handful of rows with bfloat16 weights: out[r, n] = sum_k x[r, k] * W[n, k], r < 8.
+// Dense products of a handful of rows with bfloat16 weights: out[r, n] = sum_k x[r, k] * W[n, k], r < 8.
 //
 // With one to eight rows a product is nothing but a stream of W from memory, and what decides its time is how soon
 // the whole matrix is on its way.  The tcgen05 kernel (tc_gemm.cu) pays for its set-up here: a weight tile of 128
 // rows per CTA leaves a 2,048 x 2,048 matrix with 16 tiles for 148 multiprocessors, so it splits K and needs a
-// second kernel to add the parts, and an expert's matrix for one row is 11 tiles that each pull 1 MB through one
-// CTA's ring.  This kernel has no ring and no set-up: a block of sixteen warps takes sixteen output features at a
-// time (sixteen rows of W; with swiglu sixteen gate rows and their sixteen up rows), its warps share out K in steps
-// of 32 elements, and every lane asks for its pieces of W, 16 bytes each, a round ahead of the one it works on,
-// the first of them before it waits for the kernel before it, whose output (x) it reads last.  The sums run on the tensor cores all the same: one
-// mma.sync.m16n8k16 takes sixteen weight rows as A and up to eight rows of x as B.  A lane's 16 bytes are eight
-// consecutive k of one weight row; they are used as the lane's slots of two instructions' A fragments, and the
-// lane's 16 bytes of the x row at the same k as its B slots, so each instruction sums 16 values of k that are not
-// the 16 the fragment layout names, but the same 16 in A and in B, and all of them exactly once.  Warps' partial
-// sums are added in warp order in shared memory.  A row's result depends on no other row.  Forms:
+// second kernel to add the parts.  This kernel has no ring and no set-up: a block of sixteen warps takes sixteen
+// output features at a time (sixteen rows of W; with swiglu sixteen gate rows and their sixteen up rows), its warps
+// share out K in steps of 32 elements, and every lane asks for its pieces of W, 16 bytes each, a round ahead of the
+// one it works on, the first of them before it waits for the kernel before it, whose output (x) it reads last.
+// The sums run on the tensor cores all the same: one mma.sync.m16n8k16 takes sixteen weight rows as A and up to
+// eight rows of x as B.  A lane's 16 bytes are eight consecutive k of one weight row; they are used as the lane's
+// slots of two instructions' A fragments, and the lane's 16 bytes of the x row at the same k as its B slots, so each
+// instruction sums 16 values of k that are not the 16 the fragment layout names, but the same 16 in A and in B, and
+// all of them exactly once.  Warps' partial sums are added in warp order in shared memory.  A row's result depends
+// on no other row.  Options: bias; swiglu (W holds gate rows [0, N) and up rows [N, 2N); out = silu(gate) * up).
 //
-//   dense      W [N, K]; rows 0 .. R-1 of x; optional bias; out bfloat16 or float32
-//   grouped    W [E, rows, K]; a tile list (expert, first row, rows <= 8) over an expert-sorted row list as built by
-//              the routing kernels; a tile's row j is x[a_rows[row0 + j]], or x[(row0 + j - x_sub) % x_mod] for
-//              experts that all take the same few rows, or x[row0 + j]
-//   swiglu     W holds gate rows [0, N) and up rows [N, 2N) (per expert); out = silu(gate) * up
+// It is for small streams: one block per multiprocessor with a round of loads ahead tops out near 4.5 TB/s, so
+// matrices beyond about a hundred MB stay with the tcgen05 kernel, whose ring is deeper; and inside a decode step
+// it pays for the dense projections only (measured: the experts' grouped products were no faster on it than on
+// the tcgen05 kernel, which fetches its first weights while the kernel before it still runs).
 //
-// The reference computes these products row by row on the vector units (src/hip_ops.hip:43-64, 861-893).
+// The reference computes these products row by row on the vector units (src/hip_ops.hip:43-64).
 #include "common.cuh"
 
 namespace {
 
 constexpr int SK_WARPS = 16;          // warps per block: the block's share of K is cut into this many
 constexpr int SK_MAX_ROWS = 8;
-constexpr int SK_LOADS = 8;           // 16-byte weight loads a lane has in flight together
+constexpr int SK_LOADS = 8;           // 16-byte weight loads of a lane per round; two rounds are in flight
 
 struct SkArgs {
   const bf16* x;
   const bf16* w;
   const void* bias;
   void* out;
-  const int* a_rows;        // grouped: source row of every sorted row (nullptr: see x_mod)
-  const int* tile_expert;   // grouped: tile list; nullptr = dense
-  const int* tile_row0;
-  const int* tile_rows;
-  const int* num_tiles;
-  int* err;
-  long long ldx, ldo, w_expert_stride;   // elements
-  int R;                    // dense: rows
-  int N, K, groups_n, out_dt, bias_dt, x_sub, x_mod, x_rows_total;
-  int tiles_ready;          // grouped: the tile list was complete before the kernel before this one started
-  int max_tiles;
+  long long ldx, ldo;       // elements
+  int R, N, K, groups_n, out_dt, bias_dt;
 };
 
 __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -55,12 +45,6 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint3
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// What a block works on at a time: sixteen output features of one tile (dense: the one tile of rows 0 .. R-1).
-struct SkGroup {
-  int row0, rows, n0;
-  const bf16* wbase;
-};
-
 template <bool SWIGLU>
 __global__ void __launch_bounds__(SK_WARPS * 32, 1) skinny_kernel(SkArgs a) {
   constexpr int NA = SWIGLU ? 2 : 1;                  // accumulators: gate and up
@@ -68,40 +52,15 @@ __global__ void __launch_bounds__(SK_WARPS * 32, 1) skinny_kernel(SkArgs a) {
   __shared__ float part[2][SK_WARPS][NA][32][4];
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const int g = lane / 4, c = lane % 4;               // fragment row / column group of this lane
-  const int grouped = a.tile_expert != nullptr;
-  // A grouped product must know its tiles before it can ask for weights; it may look before the wait only if the
-  // list is older than the kernel before it.
-  bool waited = false;
-  if (grouped && !a.tiles_ready) {
-    grid_dep_wait();
-    waited = true;
-  }
-  const int tiles = grouped ? min(*a.num_tiles, a.max_tiles) : 1;
-  const long long total = (long long)tiles * a.groups_n;            // groups of sixteen features, over all tiles
-  const int steps = a.K / 32;                                       // this warp takes steps warp, warp + 16, ...
+  const int total = a.groups_n;                       // groups of sixteen features
+  const int steps = a.K / 32;                         // this warp takes steps warp, warp + 16, ...
   const int my_steps = steps > warp ? (steps - warp + SK_WARPS - 1) / SK_WARPS : 0;
   const int rounds = max(1, ((steps + SK_WARPS - 1) / SK_WARPS + SK_BATCH - 1) / SK_BATCH);   // the same for every warp
 
-  auto group_of = [&](long long q, SkGroup& gr) {
-    const int y = (int)(q / a.groups_n);
-    gr.n0 = (int)(q % a.groups_n) * 16;
-    gr.row0 = 0;
-    gr.rows = a.R;
-    gr.wbase = a.w;
-    if (grouped) {
-      gr.row0 = a.tile_row0[y];
-      gr.rows = a.tile_rows[y];
-      if (gr.rows > SK_MAX_ROWS) {                    // the list was cut for another kernel: flag it, do what fits
-        if (a.err && threadIdx.x == 0) atomicExch(a.err, 1 + gr.row0);
-        gr.rows = SK_MAX_ROWS;
-      }
-      gr.wbase += (size_t)a.tile_expert[y] * a.w_expert_stride;
-    }
-  };
-  // asks for this lane's pieces of W of round r of a group: its two weight rows (features n0 + g and n0 + g + 8,
-  // clamped to rows that exist), steps warp + 16 * (r * SK_BATCH + b)
-  auto issue = [&](const SkGroup& gr, int r, uint4 (&wl)[SK_BATCH][NA], uint4 (&wh)[SK_BATCH][NA]) {
-    const int f_lo = min(gr.n0 + g, a.N - 1), f_hi = min(gr.n0 + g + 8, a.N - 1);
+  // asks for this lane's pieces of W of round r of the group of features from n0 on: its two weight rows (features
+  // n0 + g and n0 + g + 8, clamped to rows that exist), steps warp + 16 * (r * SK_BATCH + b)
+  auto issue = [&](int n0, int r, uint4 (&wl)[SK_BATCH][NA], uint4 (&wh)[SK_BATCH][NA]) {
+    const int f_lo = min(n0 + g, a.N - 1), f_hi = min(n0 + g + 8, a.N - 1);
 #pragma unroll
     for (int b = 0; b < SK_BATCH; ++b) {
       const int i = r * SK_BATCH + b;
@@ -109,8 +68,8 @@ __global__ void __launch_bounds__(SK_WARPS * 32, 1) skinny_kernel(SkArgs a) {
         const int st = warp + i * SK_WARPS;
 #pragma unroll
         for (int s = 0; s < NA; ++s) {
-          wl[b][s] = __ldcs((const uint4*)(gr.wbase + ((size_t)s * a.N + f_lo) * a.K) + c + st * 4);   // streamed once
-          wh[b][s] = __ldcs((const uint4*)(gr.wbase + ((size_t)s * a.N + f_hi) * a.K) + c + st * 4);
+          wl[b][s] = __ldcs((const uint4*)(a.w + ((size_t)s * a.N + f_lo) * a.K) + c + st * 4);   // streamed once
+          wh[b][s] = __ldcs((const uint4*)(a.w + ((size_t)s * a.N + f_hi) * a.K) + c + st * 4);
         }
       }
     }
@@ -120,24 +79,15 @@ __global__ void __launch_bounds__(SK_WARPS * 32, 1) skinny_kernel(SkArgs a) {
 #pragma unroll
     for (int s = 0; s < NA; ++s) acc[s][0] = acc[s][1] = acc[s][2] = acc[s][3] = 0.f;
   };
+  // this lane's row of x (column g of the B operand); lanes beyond the rows multiply zeros
+  const uint4* xp = (const uint4*)(a.x + (size_t)(g < a.R ? g : 0) * a.ldx) + c;
   int done = 0;                                       // groups this block has finished: which half of `part` is next
-  auto compute = [&](const SkGroup& gr, int r, const uint4 (&wl)[SK_BATCH][NA], const uint4 (&wh)[SK_BATCH][NA]) {
-    // this lane's row of x (column g of the B operand); lanes beyond the tile's rows multiply zeros
-    int src = gr.row0 + g;
-    if (grouped && g < gr.rows) {
-      if (a.a_rows) src = a.a_rows[src];
-      else if (a.x_mod) src = (src - a.x_sub) % a.x_mod;
-    }
-    if (g < gr.rows && (src < 0 || src >= a.x_rows_total)) {      // a bad permutation: flag it and read row 0
-      if (a.err && c == 0) atomicExch(a.err, 1 + gr.row0 + g);
-      src = 0;
-    }
-    const uint4* xp = (const uint4*)(a.x + (size_t)(g < gr.rows ? src : 0) * a.ldx) + c;
+  auto compute = [&](int n0, int r, const uint4 (&wl)[SK_BATCH][NA], const uint4 (&wh)[SK_BATCH][NA]) {
     uint4 xv[SK_BATCH];
 #pragma unroll
     for (int b = 0; b < SK_BATCH; ++b) {
       const int i = r * SK_BATCH + b;
-      xv[b] = (i < my_steps && g < gr.rows) ? __ldg(xp + (warp + i * SK_WARPS) * 4) : make_uint4(0, 0, 0, 0);
+      xv[b] = (i < my_steps && g < a.R) ? __ldg(xp + (warp + i * SK_WARPS) * 4) : make_uint4(0, 0, 0, 0);
     }
 #pragma unroll
     for (int b = 0; b < SK_BATCH; ++b) {
@@ -170,50 +120,36 @@ __global__ void __launch_bounds__(SK_WARPS * 32, 1) skinny_kernel(SkArgs a) {
         for (int wi = 0; wi < SK_WARPS; ++wi) v[s] += p[wi][s][l][j];
       }
       // accumulator element j of lane l: feature (l / 4) + 8 * (j / 2), row 2 * (l % 4) + (j % 2)
-      const int feat = gr.n0 + l / 4 + 8 * (j / 2), row = 2 * (l % 4) + (j % 2);
-      if (feat < a.N && row < gr.rows) {
+      const int feat = n0 + l / 4 + 8 * (j / 2), row = 2 * (l % 4) + (j % 2);
+      if (feat < a.N && row < a.R) {
         float o = SWIGLU ? silu_mul(v[0], v[NA - 1]) : v[0];
         if (!SWIGLU && a.bias) o += ld_dt(a.bias, a.bias_dt, feat);
-        st_dt(a.out, a.out_dt, (size_t)(gr.row0 + row) * a.ldo + feat, o);
+        st_dt(a.out, a.out_dt, (size_t)row * a.ldo + feat, o);
       }
     }
   };
 
   // The block's work is the rounds of its groups (blockIdx.x, + gridDim.x, ...), one after the other; the loads of
-  // the round after next are asked for before a round is worked on (two sets of registers taking turns), so a lane
+  // the round after are asked for before a round is worked on (two sets of registers taking turns), so a lane
   // always has loads in flight, also across the sum of a group.
   uint4 wl0[SK_BATCH][NA], wh0[SK_BATCH][NA], wl1[SK_BATCH][NA], wh1[SK_BATCH][NA];
-  SkGroup g0, g1;
-  long long q0 = blockIdx.x, q1;
-  int r0 = 0, r1;
+  int q0 = blockIdx.x, q1, r0 = 0, r1;
   clear();
-  auto advance = [&](long long q, int r, long long& qn, int& rn) {
+  auto advance = [&](int q, int r, int& qn, int& rn) {
     if (r + 1 < rounds) { qn = q; rn = r + 1; }
     else { qn = q + gridDim.x; rn = 0; }
   };
-  if (q0 < total) {
-    group_of(q0, g0);
-    issue(g0, r0, wl0, wh0);
-  }
-  if (!waited) {                                      // the first weights are on their way: now wait for x
-    grid_dep_wait();
-    waited = true;
-  }
+  if (q0 < total) issue(q0 * 16, r0, wl0, wh0);
+  grid_dep_wait();                                    // the first weights are on their way: now wait for x
   grid_dep_launch();
   while (q0 < total) {
     advance(q0, r0, q1, r1);
-    if (q1 < total) {
-      if (r1 == 0) group_of(q1, g1); else g1 = g0;
-      issue(g1, r1, wl1, wh1);
-    }
-    compute(g0, r0, wl0, wh0);
+    if (q1 < total) issue(q1 * 16, r1, wl1, wh1);
+    compute(q0 * 16, r0, wl0, wh0);
     if (q1 >= total) break;
     advance(q1, r1, q0, r0);
-    if (q0 < total) {
-      if (r0 == 0) group_of(q0, g0); else g0 = g1;
-      issue(g0, r0, wl0, wh0);
-    }
-    compute(g1, r1, wl1, wh1);
+    if (q0 < total) issue(q0 * 16, r0, wl0, wh0);
+    compute(q1 * 16, r1, wl1, wh1);
   }
 }
 
@@ -227,31 +163,16 @@ NV_API int nv_skinny_gemm_usable(int rows, int K, long long ldx, const void* x, 
          !((uintptr_t)w & 15);
 }
 
-// Dense (tile_expert == nullptr: rows 0 .. R-1 of x, R <= 8) or grouped (tiles of at most `max_tile_rows` <= 8 rows;
-// rows of W per expert = N, or 2N with swiglu; max_tiles bounds the list, whose length is read on the device).
-// x has x_rows_total rows.  out row = sorted row (grouped) or row (dense).  `tiles_ready`: the tile list was complete
-// before the kernel before this one on the stream started (a fixed list): the product may then ask for its weights
-// while that kernel still runs.
-NV_API int nv_skinny_gemm(const void* x, long long ldx, int x_rows_total, int R, const void* w, int N, int K,
-                          const void* bias, int bias_dt, void* out, int out_dt, long long ldo, int swiglu,
-                          const int* a_rows, const int* tile_expert, const int* tile_row0, const int* tile_rows,
-                          const int* num_tiles, int max_tiles, int max_tile_rows, int x_sub, int x_mod, int tiles_ready,
-                          int* err, cudaStream_t stream) {
+// out[r, :] for rows r < R <= 8 of x; W is [N, K], or [2N, K] with swiglu.
+NV_API int nv_skinny_gemm(const void* x, long long ldx, int R, const void* w, int N, int K, const void* bias, int bias_dt,
+                          void* out, int out_dt, long long ldo, int swiglu, cudaStream_t stream) {
   if (!dt_ok(out_dt) || (bias && !dt_ok(bias_dt))) return NV_ERR_BAD_DTYPE;
-  const bool grouped = tile_expert != nullptr;
-  const int rmax = grouped ? max_tile_rows : R;
-  if (!nv_skinny_gemm_usable(rmax, K, ldx, x, w) || N <= 0 || x_rows_total <= 0) return NV_ERR_UNSUPPORTED;
-  if (x_mod < 0 || x_sub < 0 || (bias && (swiglu || grouped))) return NV_ERR_BAD_SIZE;
-  if (grouped && max_tiles <= 0) return NV_OK;
+  if (!nv_skinny_gemm_usable(R, K, ldx, x, w) || N <= 0) return NV_ERR_UNSUPPORTED;
+  if (bias && swiglu) return NV_ERR_BAD_SIZE;
   SkArgs a;
-  a.x = (const bf16*)x; a.w = (const bf16*)w; a.bias = bias; a.out = out; a.a_rows = a_rows;
-  a.tile_expert = tile_expert; a.tile_row0 = tile_row0; a.tile_rows = tile_rows; a.num_tiles = num_tiles; a.err = err;
-  a.ldx = ldx; a.ldo = ldo; a.w_expert_stride = (long long)(swiglu ? 2 * N : N) * K;
-  a.R = R; a.N = N; a.K = K; a.out_dt = out_dt; a.bias_dt = bias_dt;
-  a.x_sub = x_sub; a.x_mod = x_mod; a.x_rows_total = x_rows_total; a.tiles_ready = tiles_ready ? 1 : 0;
+  a.x = (const bf16*)x; a.w = (const bf16*)w; a.bias = bias; a.out = out;
+  a.ldx = ldx; a.ldo = ldo; a.R = R; a.N = N; a.K = K; a.out_dt = out_dt; a.bias_dt = bias_dt;
   a.groups_n = (N + 15) / 16;
-  a.max_tiles = grouped ? max_tiles : 1;
-  long long blocks = (long long)a.max_tiles * a.groups_n;           // an upper bound when grouped
   static int num_sms = 0;
   if (!num_sms) {
     int dev = 0;
@@ -259,19 +180,9 @@ NV_API int nv_skinny_gemm(const void* x, long long ldx, int x_rows_total, int R,
         cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || num_sms <= 0)
       num_sms = 148;
   }
-  if (blocks > num_sms) blocks = num_sms;                           // one block per multiprocessor walks the groups
-  const dim3 grid((unsigned)blocks), block(SK_WARPS * 32);
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = grid;
-  cfg.blockDim = block;
-  cfg.dynamicSmemBytes = 0;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = g_nv_dependent_launch ? 1 : 0;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  cudaError_t e = swiglu ? cudaLaunchKernelEx(&cfg, skinny_kernel<true>, a) : cudaLaunchKernelEx(&cfg, skinny_kernel<false>, a);
+  const int blocks = a.groups_n < num_sms ? a.groups_n : num_sms;   // one block per multiprocessor walks the groups
+  const cudaError_t e = swiglu ? launch_dep(skinny_kernel<true>, dim3(blocks), dim3(SK_WARPS * 32), 0, stream, a)
+                               : launch_dep(skinny_kernel<false>, dim3(blocks), dim3(SK_WARPS * 32), 0, stream, a);
   NV_RETURN_IF(e);
   NV_RETURN_LAST();
 }

@@ -13,8 +13,9 @@
 //             expert-sorted row list, as built by nv_moe_align with tile_m = the token tile
 //   dual      (chosen by the launcher for many tokens) a CTA takes 256 weight rows as two tiles with two
 //             accumulators over one token tile: a third fewer operand bytes per flop than one tile
-//   split-K   grid.z CTAs each sum a range of k; raw float32 partial sums go to a scratch
-//             buffer and nv_tc_gemm_finish adds them in split order, then bias / swiglu / cast
+//   split-K   the tile list is walked once per range of k; raw float32 partial sums go to a scratch
+//             buffer and a finishing kernel adds them in split order, then bias / swiglu / cast (dense products with
+//             few tiles, and grouped ones over a handful of rows, whose few tiles would leave most of the GPU idle)
 //
 // The kernel is persistent (one or two CTAs per SM walk the tile list) with two accumulator sets in
 // TMEM, so a tile's epilogue overlaps the next tile's products.  Warp roles: warp 0 issues TMA
@@ -52,7 +53,8 @@ struct TcArgs {
   int* err;
   long long ldo;
   int out_dt, bias_dt;
-  int M_tok;            // rows of X that exist (dense); grouped: total sorted rows
+  int M_tok;            // rows of X that exist
+  int M_out;            // rows of the output (and of every split's partial sums): M_tok, or the sorted rows of a grouped product
   int N;                // output features (rows of W per matrix; W has 2N rows with swiglu)
   int rows_per_expert;  // rows of W per expert (grouped), N or 2N
   int k_steps_total, k_steps_per_split, splits;
@@ -151,7 +153,7 @@ __device__ __forceinline__ void epilogue_chunk(const TcArgs& a, const Tile& t, i
   const int valid = min(W, t.rows_here - c0);
   if (a.splits > 1) {
     const int width = a.swiglu ? 2 * a.N : a.N;
-    float* p = a.partial + ((size_t)t.z * a.M_tok + row) * width;
+    float* p = a.partial + ((size_t)t.z * a.M_out + row) * width;
 #pragma unroll
     for (int j = 0; j < W; ++j) {
       if (j < valid) {
@@ -446,7 +448,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
             const size_t row = (size_t)(t.row0 + c0 + j);
             if (a.splits > 1) {
               const int width = a.swiglu ? 2 * a.N : a.N;
-              float* p = a.partial + ((size_t)t.z * a.M_tok + row) * width;
+              float* p = a.partial + ((size_t)t.z * a.M_out + row) * width;
               p[n] = g[j];
               if (a.swiglu) p[a.N + n] = u[j];
               if (n2_ok) p[n2] = u[j];
@@ -488,6 +490,31 @@ __global__ void tc_gemm_finish_kernel(const float* __restrict__ partial, int spl
   float v = swiglu ? silu_mul(g, u) : g;
   if (bias) v += ld_dt(bias, bias_dt, n);
   st_dt(out, out_dt, t * ldo + n, v);
+}
+
+// The same for a grouped product: only the rows that the tile list covers are finished (other rows of `out` belong
+// to other products).  One block per (tile, 256 features).
+__global__ void tc_gemm_finish_grouped_kernel(const float* __restrict__ partial, int splits, int M_out, int N, int swiglu,
+                                              const int* __restrict__ tile_row0, const int* __restrict__ tile_rows,
+                                              const int* __restrict__ num_tiles, void* __restrict__ out, int out_dt,
+                                              long long ldo) {
+  grid_dep_wait();
+  grid_dep_launch();
+  const int y = blockIdx.x;
+  if (y >= *num_tiles) return;
+  const int n = blockIdx.y * blockDim.x + threadIdx.x;
+  if (n >= N) return;
+  const int width = swiglu ? 2 * N : N;
+  const int row0 = tile_row0[y], rows = tile_rows[y];
+  for (int r = row0; r < row0 + rows; ++r) {
+    float g = 0.f, u = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const float* p = partial + ((size_t)s * M_out + r) * width;
+      g += p[n];
+      if (swiglu) u += p[N + n];
+    }
+    st_dt(out, out_dt, (long long)r * ldo + n, swiglu ? silu_mul(g, u) : g);
+  }
 }
 
 // out[r, :] = src[rows[r], :] for bf16 rows (the expert-sorted copy of the activations)
@@ -614,13 +641,14 @@ NV_API int nv_tc_gemm(const void* X, long long ldx, int M_tok, const void* W, in
                       const void* bias, int bias_dt, void* out, int out_dt, long long ldo, int swiglu, int n_tile,
                       int splits, float* scratch, const int* tile_expert, const int* tile_row0,
                       const int* tile_rows, const int* num_tiles, int max_tiles, int rows_per_expert, int* err,
-                      int early, int x_sub, int x_mod, int max_ctas, int* tile_counter, cudaStream_t stream) {
+                      int early, int x_sub, int x_mod, int max_ctas, int* tile_counter, int m_out,
+                      cudaStream_t stream) {
   if (!dt_ok(out_dt) || (bias && !dt_ok(bias_dt))) return NV_ERR_BAD_DTYPE;
   if (K % 8 || ldx % 8 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return NV_ERR_UNSUPPORTED;  // TMA: 16-byte rules
   if (n_tile < 16 || n_tile > 256 || (n_tile & (n_tile - 1))) return NV_ERR_BAD_SIZE;
   if (M_tok <= 0 || N <= 0) return NV_OK;
   const bool grouped = tile_expert != nullptr;
-  if (grouped && splits != 1) return NV_ERR_UNSUPPORTED;
+  if (grouped && splits > 1 && m_out <= 0) return NV_ERR_BAD_SIZE;     // the partial sums are [splits, m_out, width]
   if (x_mod < 0 || x_sub < 0 || (x_mod && !grouped)) return NV_ERR_BAD_SIZE;
   if (splits > 1 && !scratch) return NV_ERR_BAD_SIZE;
 
@@ -635,6 +663,7 @@ NV_API int nv_tc_gemm(const void* X, long long ldx, int M_tok, const void* W, in
   a.out = out; a.partial = scratch; a.bias = bias; a.tile_expert = tile_expert; a.tile_row0 = tile_row0;
   a.tile_rows = tile_rows; a.num_tiles = num_tiles; a.err = err; a.ldo = ldo; a.out_dt = out_dt; a.bias_dt = bias_dt;
   a.M_tok = M_tok; a.N = N; a.rows_per_expert = rows_per_expert;
+  a.M_out = grouped && m_out > 0 ? m_out : M_tok;
   a.k_steps_total = (K + BLOCK_K - 1) / BLOCK_K;
   a.splits = splits < 1 ? 1 : splits;
   a.k_steps_per_split = (a.k_steps_total + a.splits - 1) / a.splits;
@@ -727,9 +756,15 @@ NV_API int nv_tc_gemm(const void* X, long long ldx, int M_tok, const void* W, in
   e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
   if (a.splits > 1) {
-    const long long outputs = (long long)M_tok * N;
-    NV_RETURN_IF(launch_dep(tc_gemm_finish_kernel, dim3((unsigned)((outputs + 255) / 256)), dim3(256), 0, stream,
-                            (const float*)scratch, a.splits, M_tok, N, a.swiglu, bias, bias_dt, out, out_dt, ldo));
+    if (grouped) {
+      NV_RETURN_IF(launch_dep(tc_gemm_finish_grouped_kernel, dim3((unsigned)max_tiles, (unsigned)((N + 255) / 256)),
+                              dim3(256), 0, stream, (const float*)scratch, a.splits, a.M_out, N, a.swiglu, tile_row0,
+                              tile_rows, num_tiles, out, out_dt, ldo));
+    } else {
+      const long long outputs = (long long)a.M_out * N;
+      NV_RETURN_IF(launch_dep(tc_gemm_finish_kernel, dim3((unsigned)((outputs + 255) / 256)), dim3(256), 0, stream,
+                              (const float*)scratch, a.splits, a.M_out, N, a.swiglu, bias, bias_dt, out, out_dt, ldo));
+    }
   }
   NV_RETURN_LAST();
 }

@@ -6,7 +6,6 @@ import torch
 
 from ..csrc import ops
 from .base import FeedForward, RowMix, TensorSpec
-from . import linear as linear_mod
 from .linear import linear, grouped_linear, small_linear
 from .registry import register_part
 
@@ -132,12 +131,8 @@ class SparseMoeSwiGLU(FeedForward):
         else:
             self.virtual = 0
 
-    def _alignment(self, TK, n_experts, device, fast, rows=0):
-        if (fast and 0 < rows <= linear_mod.SKINNY_ROWS and rows * self.K <= linear_mod.SKINNY_MAX_PAIRS
-                and self.hidden % 32 == 0 and self.inter % 32 == 0):
-            # a few pairs: the weight-streaming products, over tiles of at most 8 rows
-            tile_m, tile_m2 = ops.SKINNY_MAX_ROWS, 0
-        elif fast:  # the down product's tile is the primary list, the SwiGLU product may want a wider one
+    def _alignment(self, TK, n_experts, device, fast):
+        if fast:    # the down product's tile is the primary list, the SwiGLU product may want a wider one
             tile_m, tile_m2 = ops.grouped_token_tile(TK, n_experts), ops.grouped_token_tile(TK, n_experts, swiglu=True)
         else:
             tile_m, tile_m2 = ops.gemm_plain_tile_m(), 0
@@ -171,7 +166,7 @@ class SparseMoeSwiGLU(FeedForward):
         score = torch.empty((T, KT), dtype=torch.float32, device=dev)
         fast = (ctx.fast_kernels and h.dtype == torch.bfloat16 and self.w_gate_up.dtype == torch.bfloat16
                 and self.w_down.dtype == torch.bfloat16 and self.hidden % 8 == 0 and self.inter % 8 == 0)
-        al = self._alignment(T * KT, self.E + C, dev, fast, rows=T)
+        al = self._alignment(T * KT, self.E + C, dev, fast)
         x_sorted = None
         if (fast and C and T <= SIDE_MAX_ROWS and al.secondary is None
                 and ops.moe_route_small_usable(T, self.E, self.K, C, self.hidden)):
@@ -211,14 +206,13 @@ class SparseMoeSwiGLU(FeedForward):
         products leave them some multiprocessors."""
         ctx, T, K, C, dev = self.ctx, h.shape[0], self.K, self.virtual, h.device
         KT = K + C
-        small = al.tile_m if al.tile_m <= ops.SKINNY_MAX_ROWS else 0     # tiles for the weight-streaming products
-        key = (T, dev, small)
+        key = (T, dev)
         st = self._static.get(key)
         if st is None:
             big = [k for k in self._static if k[0] > SIDE_MAX_ROWS]      # (small ones may belong to captured steps)
             if len(big) >= MAX_ALIGNMENTS:
                 self._static.pop(big[0])
-            st = self._static[key] = ops.StaticTiles(T, K, self.E, C, dev, tile_m=small)
+            st = self._static[key] = ops.StaticTiles(T, K, self.E, C, dev)
         act = torch.empty((T * KT, self.inter), dtype=ctx.act_dtype, device=dev)
         y = torch.empty((T * KT, self.hidden), dtype=torch.float32, device=dev)
         main, side = torch.cuda.current_stream(dev), _side_stream(dev)
@@ -226,17 +220,10 @@ class SparseMoeSwiGLU(FeedForward):
         fork.record(main)
         side.wait_event(fork)
         cap = int(ops.num_sms() * SIDE_GRID_SHARE) if many else 0
-        skinny = (al.tile_m <= ops.SKINNY_MAX_ROWS and st.tile_m <= ops.SKINNY_MAX_ROWS
-                  and ops.skinny_usable(h, self.w_gate_up, st.tile_m) and self.inter % 32 == 0)
         with torch.cuda.stream(side):
-            if skinny:
-                ops.skinny_gemm(h, self.w_gate_up, act, swiglu=True, tiles=st, x_rows=st.x_rows, max_tile_rows=st.tile_m,
-                                tiles_ready=True, err=ctx.err)
-                ops.skinny_gemm(act, self.w_down, y, tiles=st, max_tile_rows=st.tile_m, tiles_ready=True, err=ctx.err)
-            else:
-                ops.gemm_fast_grouped(h, self.w_gate_up, act, al, swiglu=True, err=ctx.err, tiles=st, tiles_ready=True,
-                                      x_rows=st.x_rows, max_ctas=cap)
-                ops.gemm_fast_grouped(act, self.w_down, y, al, err=ctx.err, tiles=st, tiles_ready=True, max_ctas=cap)
+            ops.gemm_fast_grouped(h, self.w_gate_up, act, al, swiglu=True, err=ctx.err, tiles=st, tiles_ready=True,
+                                  x_rows=st.x_rows, max_ctas=cap)
+            ops.gemm_fast_grouped(act, self.w_down, y, al, err=ctx.err, tiles=st, tiles_ready=True, max_ctas=cap)
             join.record(side)
         if many:
             ops.router_topk(logits, K, self.renorm, idx, score, C, gate_logit)
@@ -244,22 +231,16 @@ class SparseMoeSwiGLU(FeedForward):
         else:
             ops.moe_route_small(logits, K, self.renorm, C, gate_logit, idx, score, al, ctx.err, x=None, static=True)
         self.last_alignment = al
-        if skinny:      # the rows are read where they are: no sorted copy
-            ops.skinny_gemm(h, self.w_gate_up, act, swiglu=True, tiles=al.primary, a_rows=al.sorted_token,
-                            max_tile_rows=al.tile_m, err=ctx.err)
-            ops.skinny_gemm(act, self.w_down, y, tiles=al.primary, max_tile_rows=al.tile_m, tiles_ready=True,
-                            err=ctx.err)
-        else:
-            # (a prompt's routed products start while the side products still hold most multiprocessors: their CTAs
-            # take tiles from a counter, so the ones that start early do more of the work)
-            c0 = c1 = None
-            if many:
-                if self._counters is None:
-                    self._counters = torch.zeros(2, dtype=torch.int32, device=dev)
-                c0, c1 = self._counters[0:1], self._counters[1:2]
-            x_sorted = ops.permute_rows(h, al.sorted_token, T * K)
-            ops.gemm_fast_grouped(x_sorted, self.w_gate_up, act, al, swiglu=True, err=ctx.err, tiles_ready=True, counter=c0)
-            ops.gemm_fast_grouped(act, self.w_down, y, al, err=ctx.err, tiles_ready=True, counter=c1)
+        # (a prompt's routed products start while the side products still hold most multiprocessors: their CTAs take
+        # tiles from a counter, so the ones that start early do more of the work)
+        c0 = c1 = None
+        if many:
+            if self._counters is None:
+                self._counters = torch.zeros(2, dtype=torch.int32, device=dev)
+            c0, c1 = self._counters[0:1], self._counters[1:2]
+        x_sorted = ops.permute_rows(h, al.sorted_token, T * K)
+        ops.gemm_fast_grouped(x_sorted, self.w_gate_up, act, al, swiglu=True, err=ctx.err, tiles_ready=True, counter=c0)
+        ops.gemm_fast_grouped(act, self.w_down, y, al, err=ctx.err, tiles_ready=True, counter=c1)
         main.wait_event(join)
         return RowMix(y, al.pair_pos[:T * KT].view(T, KT), score, None, None)
 

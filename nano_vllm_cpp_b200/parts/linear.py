@@ -14,8 +14,6 @@ from ..csrc import ops
 # 4.3 TB/s on a 622 MB output head, 2.5 against 3.5 TB/s on a 25 MB projection).
 SKINNY_ROWS = ops.SKINNY_MAX_ROWS
 SKINNY_MAX_BYTES = 128 << 20
-# Expert products take it while a step has at most this many routed (row, expert) pairs: few experts, a few dozen MB.
-SKINNY_MAX_PAIRS = 8
 
 
 def linear(ctx, a, w, out_dtype, *, bias=None, a_rows=None, swiglu=False, M=None, out=None):
@@ -60,10 +58,6 @@ def grouped_linear(ctx, a, w, out_dtype, align, *, a_rows=None, swiglu=False, ti
     if out is None:
         out = torch.empty((align.TK, N), dtype=out_dtype, device=a.device)
     if align.TK == 0:
-        return out
-    tl = tiles if tiles is not None else align.primary
-    if ctx.fast_kernels and tl.tile_m <= ops.SKINNY_MAX_ROWS and ops.skinny_usable(a, w, tl.tile_m):
-        ops.skinny_gemm(a, w, out, swiglu=swiglu, tiles=tl, a_rows=a_rows, max_tile_rows=tl.tile_m, err=ctx.err)
         return out
     if ctx.fast_kernels and ops.gemm_fast_usable(a, w, out, a_rows=a_rows, swiglu=swiglu, grouped=True):
         ops.gemm_fast_grouped(a, w, out, align, a_rows=a_rows, swiglu=swiglu, err=ctx.err, tiles=tiles,

@@ -313,45 +313,6 @@ def test_skinny_gemm_dense(R, N, K, swiglu, out_dtype):
         o.skinny_gemm(a[:, :K - 8].contiguous(), w[:, :K - 8].contiguous(), out, swiglu=swiglu, rows=R)
 
 
-@pytest.mark.parametrize("T,E,K,I,H", [(1, 60, 4, 1408, 2048), (8, 6, 3, 64, 160), (5, 9, 2, 96, 96), (3, 3, 3, 32, 64), (8, 60, 4, 1408, 2048)])
-def test_skinny_gemm_grouped_through_the_routing(T, E, K, I, H):
-    """The two expert products over the one-launch routing's tile list (tiles of at most eight rows), rows read in
-    place through the permutation, and the always-on experts' rows by (row - sub) mod T, against float64."""
-    o = ops()
-    C = 2
-    g = torch.Generator().manual_seed(T * 7 + E)
-    x = (torch.randn(T, H, generator=g)).to(torch.bfloat16).to(DEV)
-    w_gu = (torch.randn(E + C, 2 * I, H, generator=g) * 0.1).to(torch.bfloat16).to(DEV)
-    w_dn = (torch.randn(E + C, H, I, generator=g) * 0.1).to(torch.bfloat16).to(DEV)
-    logits = torch.randn(T, E, generator=g).to(DEV)
-    gate = torch.randn(T, 1, generator=g).to(DEV)
-    KT = K + C
-    idx = torch.empty(T, KT, dtype=torch.int32, device=DEV)
-    score = torch.empty(T, KT, device=DEV)
-    al = o.MoeAlignment(T * KT, E + C, o.SKINNY_MAX_ROWS, DEV)
-    err = o.ErrorFlag(DEV)
-    if not o.moe_route_small_usable(T, E, K, C, H):
-        pytest.skip("the one-launch routing does not take these sizes")
-    o.moe_route_small(logits, K, False, C, gate, idx, score, al, err, x=None, static=True)
-    st = o.StaticTiles(T, K, E, C, DEV, tile_m=o.SKINNY_MAX_ROWS)
-    act = torch.full((T * KT, I), float("nan"), dtype=torch.bfloat16, device=DEV)
-    y = torch.full((T * KT, H), float("nan"), device=DEV)
-    o.skinny_gemm(x, w_gu, act, swiglu=True, tiles=st, x_rows=st.x_rows, max_tile_rows=st.tile_m, err=err)
-    o.skinny_gemm(x, w_gu, act, swiglu=True, tiles=al.primary, a_rows=al.sorted_token, max_tile_rows=al.tile_m, err=err)
-    o.skinny_gemm(act, w_dn, y, tiles=st, max_tile_rows=st.tile_m, err=err)
-    o.skinny_gemm(act, w_dn, y, tiles=al.primary, max_tile_rows=al.tile_m, err=err)
-    err.check("skinny grouped")
-    pos = al.pair_pos[:T * KT].view(T, KT).cpu()
-    for t in range(T):
-        for k in range(KT):
-            e = int(idx[t, k])
-            gu = x[t].double() @ w_gu[e].double().T
-            a_ref = gu[:I] / (1 + torch.exp(-gu[:I])) * gu[I:]
-            close(act[int(pos[t, k])], a_ref, 1.2e-2, f"act of pair ({t}, {k})")
-            y_ref = act[int(pos[t, k])].double() @ w_dn[e].double().T
-            close(y[int(pos[t, k])], y_ref, 2e-5, f"y of pair ({t}, {k})")
-
-
 @pytest.mark.parametrize("T,N,K", [(1, 1, 64), (8, 60, 2048), (33, 7, 100), (5, 64, 3000), (1030, 61, 520), (1025, 9, 2050)])
 @pytest.mark.parametrize("tw", [torch.float32, torch.bfloat16])
 def test_rowdot(T, N, K, tw):
