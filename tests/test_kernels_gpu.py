@@ -184,11 +184,12 @@ def test_tc_gemm_split_k(splits):
     tc_case(3, 200, 1160, True, False, torch.bfloat16, splits=splits)
 
 
-@pytest.mark.parametrize("T,E,K", [(5, 6, 3), (64, 8, 2), (300, 60, 4), (1, 60, 4), (700, 6, 3), (130, 3, 2)])
-def test_tc_gemm_grouped(T, E, K):
+@pytest.mark.parametrize("T,E,K,H,I", [(5, 6, 3, 136, 72), (64, 8, 2, 136, 72), (300, 60, 4, 136, 72), (1, 60, 4, 136, 72),
+                                       (700, 6, 3, 136, 72), (130, 3, 2, 136, 72),
+                                       (1, 9, 4, 1032, 520), (4, 5, 3, 2048, 1408)])     # few pairs, long K: K is split
+def test_tc_gemm_grouped(T, E, K, H, I):
     """Both grouped products of an expert layer against the plain grouped kernel and float64."""
     o = ops()
-    H, I = 136, 72
     g = torch.Generator().manual_seed(T)
     x = rnd(T, H, dtype=torch.bfloat16)
     w1 = rnd(E, 2 * I, H, dtype=torch.bfloat16, scale=0.3, seed=1)
