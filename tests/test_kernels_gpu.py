@@ -215,7 +215,11 @@ def test_tc_gemm_grouped(T, E, K, H, I):
                 o.gemm_fast_grouped(act2, w2, y2, al, err=err, tiles_ready=True, counter=counter[1:2], max_ctas=cap)
                 err.check("grouped, by counter")
                 assert counter.tolist() == [0, 0]
-                assert torch.equal(act2, act) and torch.equal(y2, y)
+                if T * K <= o.GROUPED_SPLIT_MAX_PAIRS and H >= 512:     # the product by position split K: other sums
+                    close(act2, act, 1e-2, "by counter vs split K")
+                    close(y2, y, 1e-2, "by counter vs split K")
+                else:
+                    assert torch.equal(act2, act) and torch.equal(y2, y)
         else:
             o.gemm_plain(x, w1, act, a_rows=al.sorted_token, swiglu=True, M=T * K, tiles=al.tiles)
             o.gemm_plain(act, w2, y, M=T * K, tiles=al.tiles)
