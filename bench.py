@@ -12,7 +12,7 @@ prompt); ``roofline`` compares the bytes a decode step has to read (every weight
 the live requests) with the measured copy bandwidth.  A decode step here is the whole step: the model, the
 sampling kernel behind it, and the next step reading the drawn tokens on the device.
 
-``--kernel-times`` adds ``kernels``: per kernel class of one decode step and of the prompt, CUDA-event time,
+``kernels`` (``--no-kernel-times`` leaves it out): per kernel class of one decode step and of the prompt, CUDA-event time,
 calls and the fraction of the measured peak its bytes (decode) or flops (prompt) come to.  Those steps run
 outside CUDA graphs with an event between any two kernels, one kernel after the other on one stream (the decode
 step behind a delay kernel, so that the host has queued it all before the GPU starts): nothing overlaps, and
@@ -213,7 +213,7 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-prefill", action="store_true")
-    ap.add_argument("--kernel-times", action="store_true", help="add per-kernel-class CUDA-event times to the line")
+    ap.add_argument("--no-kernel-times", action="store_true", help="skip the per-kernel-class CUDA-event times")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -415,8 +415,10 @@ def main() -> int:
     if not args.no_points:
         ms_b64 = None
         for B in (1, 64):
-            pms, _, _, _ = decode_device(B, max(8, args.steps // 2), args.warmup)
+            pms, _, pdistinct, pctxs = decode_device(B, max(8, args.steps // 2), args.warmup)
             points[f"decode_b{B}"] = round(B / pms * 1e3, 1)
+            pbytes = weight_bytes(cfg, args.layers, pdistinct) + kv_bytes(cfg, args.layers, pctxs)
+            points[f"decode_b{B}_frac"] = round(pbytes / (pms * 1e-3) / 1e9 / P["hbm_gbs"], 4)
             ms_b64 = pms
         mms, portion_ms, mdistinct, mctxs = mixed_device(max(6, args.steps // 4), args.warmup)
         mbytes = weight_bytes(cfg, args.layers, mdistinct) + kv_bytes(cfg, args.layers, mctxs)
@@ -429,7 +431,7 @@ def main() -> int:
                  "bound": "max(hbm bytes, bf16 flops)"}
 
     kernels = None
-    if args.kernel_times:
+    if not args.no_kernel_times:
         kernels = kernel_times(runner, cfg, args, P, fill_context, StepEntry, ops, torch, g, V)
 
     line = {
