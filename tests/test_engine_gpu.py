@@ -338,6 +338,41 @@ def test_command_line(folders):
     assert r.returncode == 2 and "token ids" in r.stderr
 
 
+def test_command_line_with_a_config_file_and_the_start_up_lines(tmp_path):
+    """``--config`` runs random weights of the model a JSON file describes, without a model folder; ``--dtype fp32``
+    is the reference's spelling; at start-up the engine says what the weights took and how large the cache pool is."""
+    import json
+    exe = os.path.join(os.path.dirname(helpers.HERE), "bin", "nanovllm")
+    cfg = tmp_path / "tiny.json"
+    cfg.write_text(json.dumps(helpers.CASES["B"]["config"]))
+    runs = []
+    for _ in range(2):
+        r = subprocess.run([sys.executable, exe, "--config", str(cfg), "--seed", "3", "--tokens", "5,17,3", "--max-tokens", "5",
+                            "--temperature", "0", "--dtype", "fp32", "--max-model-len", "64", "--num-kv-blocks", "8",
+                            "--ignore-eos"], capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stderr[-2000:]
+        runs.append([l for l in r.stdout.splitlines() if l.startswith("token_ids:")][0])
+        assert "[nanovllm] weights loaded:" in r.stderr and "[nanovllm] cache pool: 8 pages of 16 tokens" in r.stderr
+    assert runs[0] == runs[1] and len(runs[0].split()) == 6          # the seed fixes the weights
+
+
+def test_kernel_times():
+    """``ops.KernelTimes`` books every launch of a step to its kernel class."""
+    from nano_vllm_cpp_b200.csrc import ops
+    a = torch.randn(4, 256, device="cuda").to(torch.bfloat16)
+    w = torch.randn(64, 256, device="cuda").to(torch.bfloat16)
+    out = torch.empty(4, 64, device="cuda")
+    with ops.KernelTimes() as kt:
+        for _ in range(3):
+            ops.skinny_gemm(a, w, out)
+        ops.gemm_plain(a, w, out)
+    rows = {r["name"]: r for r in kt.summary()}
+    assert rows["skinny_gemm N=64 K=256"]["calls"] == 3 and rows["gemm_plain"]["calls"] == 1
+    assert all(r["ms"] > 0 for r in rows.values())
+    assert rows["skinny_gemm N=64 K=256"]["bytes"] == 3 * 64 * 256 * 2
+    assert not ops.timing()
+
+
 def test_smoke_entry():
     sys.path.insert(0, os.path.dirname(helpers.HERE))
     import __graft_entry__
