@@ -10,6 +10,7 @@ inside.
 """
 from __future__ import annotations
 
+import gc
 import sys
 
 import numpy as np
@@ -280,10 +281,18 @@ class ModelRunner:
             torch.cuda.synchronize(self.device)
             before = ops.launch_count()
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                static_logits = self._forward(batch)
-                if sampling is not None:
-                    self._sample_into_feed(static_logits, batch)
+            # The collector stays off while the stream is capturing: an old engine's graphs or buffers that it
+            # happened to free in the middle would be CUDA calls that a capture does not permit.
+            collecting = gc.isenabled()
+            gc.disable()
+            try:
+                with torch.cuda.graph(graph):
+                    static_logits = self._forward(batch)
+                    if sampling is not None:
+                        self._sample_into_feed(static_logits, batch)
+            finally:
+                if collecting:
+                    gc.enable()
             self._graphs[key] = (graph, static_dev, static_logits, ops.launch_count() - before)
             return logits, batch
         graph, static_dev, static_logits, launches = g

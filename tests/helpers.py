@@ -57,7 +57,7 @@ def prompt(case_name, n, salt=0):
 # router logits (bfloat16 activations carry errors of about one percent).  Such a row then differs by more than
 # rounding; the comparisons below let a bfloat16 row exceed the tolerance only if it is such a row, and only a few.
 EDGE_MARGIN = 0.01
-MAX_EDGE_SHARE = 0.03
+MAX_EDGE_SHARE = 0.1        # (with a dozen experts and two sparse layers about one row in fifteen has such a margin)
 
 _plain_cache = {}
 
@@ -101,7 +101,7 @@ def assert_rows_close(got, want, margin, dtype, what=""):
     plain_rows = [(r, float(err[r]), float(margin[r])) for r in off if float(margin[r]) >= EDGE_MARGIN]
     assert not plain_rows, (f"{what}: rows (row, error, router margin) beyond {bound:.3g} that sit on no router edge: "
                             f"{plain_rows[:8]}")
-    assert len(off) <= max(1, MAX_EDGE_SHARE * len(err)), f"{what}: {len(off)} of {len(err)} rows beyond {bound:.3g}"
+    assert len(off) <= max(2, MAX_EDGE_SHARE * len(err)), f"{what}: {len(off)} of {len(err)} rows beyond {bound:.3g}"
 
 
 def assert_close(got, want, dtype, what=""):
