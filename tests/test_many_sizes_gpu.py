@@ -193,3 +193,77 @@ def test_sizes_that_no_kernel_takes_are_refused(tmp_path):
         mdir = write_model(c, str(tmp_path / f"d{D}"), seed=1)
         with pytest.raises(Exception, match="head_dim"):
             ModelRunner(mdir, dtype="bfloat16", max_tokens=64, max_requests=2)
+
+
+def random_schedule(rng, lengths, page, pool_tokens, max_live=4):
+    """Steps [(parts [(request, tokens)], ends)] that feed every request whole, in portions of random sizes (single
+    tokens and pairs among them), with up to ``max_live`` requests live and never more tokens held (each request's
+    count rounded up to whole pages) than the pool has."""
+    left = dict(lengths)
+    fed = {r: 0 for r in lengths}
+    waiting, live, steps = list(lengths), [], []
+    pages = lambda n: (n + page - 1) // page
+
+    def reserved():                      # what the live requests will hold when they are whole
+        return sum(pages(lengths[r]) for r in live) * page
+
+    while waiting or live:
+        while waiting and len(live) < max_live and rng.random() < 0.7:
+            r = waiting[0]
+            if reserved() + pages(lengths[r]) * page > pool_tokens:  # room for the whole request, so nobody gets stuck
+                break
+            live.append(waiting.pop(0))
+        if not live:
+            live.append(waiting.pop(0))
+        parts, ends = [], []
+        for r in list(live):
+            if rng.random() < 0.25 and len(live) > 1:
+                continue                                   # the request sits this step out
+            n = min(left[r], rng.choice([1, 1, 2, 2, 3, 5, 7, 16, 17, 31, 64]))
+            if left[r] - n == 1 and rng.random() < 0.5:
+                n += 1
+            parts.append((r, n))
+        if not parts:
+            continue
+        for r, n in parts:
+            fed[r] += n
+            left[r] -= n
+            if left[r] == 0:
+                ends.append(r)
+                live.remove(r)
+        steps.append((parts, ends))
+    return steps
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["d16_one_kv_head", "d64_seven_per_kv_head_pages32", "d96_window33_second_layer",
+                                  "d128_benchmark_like"])
+def test_random_schedules(name, dtype, folders):
+    """Five random ways of cutting and mixing six requests, on a pool that holds less than half of their tokens."""
+    import random
+    from nano_vllm_cpp_b200.engine.runner import ModelRunner
+    c, page = CONFIGS[name]
+    mdir = folders[name]
+    lengths = {"a": 90, "b": 1, "c": 47, "d": 2, "e": 64, "f": 33}
+    ids = {r: ids_of(name, r, n) for r, n in lengths.items()}
+    pool = 224
+    runner = ModelRunner(mdir, dtype=dtype, page_size=page, max_tokens=pool, max_requests=4)
+    for seed in range(5):
+        rng = random.Random(1000 * seed + len(name))
+        order = list(lengths)
+        rng.shuffle(order)
+        steps = random_schedule(rng, {r: lengths[r] for r in order}, page, pool)
+        rp = Replay(runner)
+        at = {r: 0 for r in lengths}
+        done = {}
+        for parts, ends in steps:
+            rp.step([(r, ids[r][at[r]:at[r] + n], True) for r, n in parts])
+            for r, n in parts:
+                at[r] += n
+            for r in ends:
+                rp.compare(r, ids[r], mdir, dtype, f"{name} {dtype} random schedule {seed}")
+                done[r] = True
+            rp.step([], end=ends)
+        assert sorted(done) == sorted(lengths)
+        for p in runner.manager.pools:
+            assert p.num_free() == p.num_pages
