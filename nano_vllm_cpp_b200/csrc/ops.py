@@ -573,7 +573,6 @@ def reset_fresh_state(state, entry_slot, entry_pos0) -> None:
 def delay(micros: int) -> None:
     """Keeps the current stream busy for about ``micros`` microseconds (at most 200,000); for measurements that
     want a step's launches queued before the GPU starts on them."""
-    global _launches
     code = lib().nv_delay(c_int(int(micros)), _stream())
     if code:
         raise KernelError(f"delay: {_ERR.get(code, code)}")

@@ -237,6 +237,8 @@ class SparseMoeSwiGLU(FeedForward):
         if many:
             if self._counters is None:
                 self._counters = torch.zeros(2, dtype=torch.int32, device=dev)
+            else:       # (a product sets its counter back itself; one that gave up on a wait may not have)
+                self._counters.zero_()
             c0, c1 = self._counters[0:1], self._counters[1:2]
         x_sorted = ops.permute_rows(h, al.sorted_token, T * K)
         ops.gemm_fast_grouped(x_sorted, self.w_gate_up, act, al, swiglu=True, err=ctx.err, tiles_ready=True, counter=c0)
