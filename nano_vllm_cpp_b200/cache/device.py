@@ -52,11 +52,20 @@ class DeviceCache:
                 out[g] += 2 * s.num_kv_heads * self.page_size * s.head_dim * item
         return out
 
-    def allocate(self, num_pages) -> None:
+    def allocate(self, num_pages, max_blocks: int = 0) -> None:
+        """``max_blocks`` > 0: also the block tables, per group one of every state slot's request
+        (``tables[g]`` [slots, max_blocks], kept up to date step by step with what changed) and one of the running
+        step's entries (``step_tables[g]`` [slots, max_blocks], the one the kernels read): see ``sync_tables``."""
         if isinstance(num_pages, int):
             num_pages = [num_pages] * len(self.windows)
         self.num_pages = list(num_pages)
         self.views = []
+        self.max_blocks = max_blocks
+        self.tables = self.step_tables = None
+        if max_blocks > 0:
+            shape = (max(1, self.max_slots), max_blocks)
+            self.tables = [torch.full(shape, -1, dtype=torch.int32, device=self.device) for _ in self.windows]
+            self.step_tables = [torch.full(shape, -1, dtype=torch.int32, device=self.device) for _ in self.windows]
         for s, g in zip(self.specs, self.entry_group):
             if isinstance(s, KVCacheSpec):
                 shape = (max(1, num_pages[g]), s.num_kv_heads, self.page_size, s.head_dim)
@@ -81,6 +90,17 @@ class DeviceCache:
     @property
     def has_state(self) -> bool:
         return any(isinstance(s, StateCacheSpec) for s in self.specs)
+
+    def sync_tables(self, batch) -> None:
+        """Before a step runs: the block tables of its entries, in entry order, are put together on the device
+        (``batch.block_tables``) from the tables kept per state slot, after the rows that travelled with the step
+        (the tables that changed since they last did) have been taken in.  The reference writes every table of a
+        step again on the host (src/model_runner.cpp:29-41)."""
+        from ..csrc import ops
+        if batch.table_updates is None:
+            return
+        for g, (src, lens, rows) in enumerate(batch.table_updates):
+            ops.sync_block_tables(src, lens, rows, batch.entry_slot, self.tables[g], self.step_tables[g], batch.S)
 
     def reset_fresh(self, batch) -> None:
         """Before a step runs: the state of every entry that starts its request (first position 0) is zeroed, on

@@ -192,11 +192,15 @@ class CacheManager:
             raise KeyError(rid)
         return int(n)
 
-    def prepare_step(self, entries: list, max_blocks: int, max_model_len: int, sampling: bool, buf: np.ndarray):
+    def prepare_step(self, entries: list, max_blocks: int, max_model_len: int, sampling: bool, buf: np.ndarray,
+                     fixed_rows: int = 0):
         """Takes the pages that the entries' next rows need and writes the step's index arrays into ``buf`` (int32)
         in the layout of ``engine.batch.batch_layout``.  ``entries``: objects with ``rid``, ``tokens``, ``want`` of
-        open requests.  Returns (ints used, [(slot, first position)] per entry, native ids)."""
+        open requests.  A request's block table travels only if it has changed since it last did; ``fixed_rows``
+        > 0 keeps room for that many tables per group whatever the step needs (the layout of a captured step).
+        Returns (ints used, [(slot, first position)] per entry, native ids, tables sent per group)."""
         S = len(entries)
+        G = len(self.pools)
         rids = (ctypes.c_int64 * max(S, 1))(*[self._native(e.rid) for e in entries])
         lens = (ctypes.c_int * max(S, 1))(*[len(e.tokens) for e in entries])
         flat = [t for e in entries for t in e.tokens]
@@ -208,13 +212,20 @@ class CacheManager:
         wants_cu = (ctypes.c_int * (S + 1))(*cu)
         wants_a = (ctypes.c_int * max(len(wants), 1))(*wants)
         info = (ctypes.c_int * max(2 * S, 1))()
+        sent = (ctypes.c_int * max(G, 1))()
         n = host.lib().nvh_prepare_step(self._h, S, rids, lens, tokens, wants_cu, wants_a, max_blocks, max_model_len,
-                                        1 if sampling else 0, buf.ctypes.data_as(ctypes.c_void_p), buf.shape[0], info)
+                                        1 if sampling else 0, fixed_rows, buf.ctypes.data_as(ctypes.c_void_p),
+                                        buf.shape[0], info, None, sent)
         if n < 0:
             if n == host.ERR_STATE:
                 raise ValueError(host.last_error())
             self._raise(n)
-        return int(n), [(info[2 * i], info[2 * i + 1]) for i in range(S)], rids
+        return int(n), [(info[2 * i], info[2 * i + 1]) for i in range(S)], rids, [int(sent[g]) for g in range(G)]
+
+    def invalidate_tables(self) -> None:
+        """The device's copies of the block tables are no longer to be trusted (a prepared step never ran): every
+        request's tables travel again with its next step."""
+        host.lib().nvh_touch_tables(self._h)
 
     def commit_many(self, native_ids, ends: list) -> None:
         """``commit`` for many requests at once (``native_ids`` as returned by ``prepare_step``); no page hashing."""

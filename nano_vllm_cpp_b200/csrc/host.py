@@ -50,8 +50,10 @@ _PROTOS = {
     "nvh_new_pages_for": (c_int, [c_void_p, c_int, _IP, c_int]),
     "nvh_manager_check": (c_int, [c_void_p]),
     "nvh_commit_many": (c_int, [c_void_p, c_int, _LP, _IP]),
-    "nvh_step_layout": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, _IP]),
-    "nvh_prepare_step": (c_int, [c_void_p, c_int, _LP, _IP, _IP, _IP, _IP, c_int, c_int, c_int, c_void_p, c_int, _IP]),
+    "nvh_step_layout": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, _IP, _IP]),
+    "nvh_prepare_step": (c_int, [c_void_p, c_int, _LP, _IP, _IP, _IP, _IP, c_int, c_int, c_int, c_int, c_void_p, c_int,
+                                 _IP, _IP, _IP]),
+    "nvh_touch_tables": (None, [c_void_p]),
     "nvs_create": (c_void_p, [c_void_p, c_int, c_int, c_int, c_int, c_int]),
     "nvs_destroy": (None, [c_void_p]),
     "nvs_add": (c_int, [c_void_p, c_int64, _IP, c_int, c_int, c_int, c_int]),

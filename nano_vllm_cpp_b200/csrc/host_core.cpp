@@ -156,6 +156,7 @@ struct RequestCache {
   int64_t rid = 0;
   int slot = 0;
   std::vector<std::vector<int>> tables;   // per group: page ids, -1 where given back
+  std::vector<uint8_t> dirty;             // per group: the table has changed since it last went to the device
   int num_tokens = 0;                     // tokens whose keys/values (or state) are in the cache
   int hashed_pages = 0;                   // leading full pages that carry a hash
   bool has_last = false;
@@ -193,6 +194,7 @@ class CacheManager {
     rc.slot = free_slots.back();
     free_slots.pop_back();
     rc.tables.resize(pools.size());
+    rc.dirty.assign(pools.size(), 1);
     const int slot = rc.slot;
     requests.emplace(rid, std::move(rc));
     return slot;
@@ -252,13 +254,17 @@ class CacheManager {
           int r = pools[g].release(table[i]);
           if (r) return r;
           table[i] = -1;
+          rc->dirty[g] = 1;
         }
     }
     if (!can_extend(*rc, start, end)) return fail(ERR_NO_PAGES, "no free blocks");
     for (size_t g = 0; g < pools.size(); ++g) {
       auto& table = rc->tables[g];
       const int total = (end + page_size - 1) / page_size;
-      while ((int)table.size() < total) table.push_back(pools[g].allocate());
+      while ((int)table.size() < total) {
+        table.push_back(pools[g].allocate());
+        rc->dirty[g] = 1;
+      }
     }
     return OK;
   }
@@ -313,6 +319,7 @@ class CacheManager {
       int r = pools[0].share(pages[i]);
       if (r) return r;
       rc->tables[0].push_back(pages[i]);
+      rc->dirty[0] = 1;
       rc->has_last = true;
       rc->last_hash = hashes[i];
     }
@@ -328,6 +335,11 @@ class CacheManager {
     for (int i = 0; i < n; ++i)
       if (pools[0].ref_count[pages[i]] == 0) ++revived;
     return total - n + revived;
+  }
+  // The device's copies of the block tables can no longer be trusted (a step was prepared but never ran): every
+  // request's tables travel again with its next step.
+  void touch_all() {
+    for (auto& kv : requests) std::fill(kv.second.dirty.begin(), kv.second.dirty.end(), 1);
   }
   int check() const {
     std::vector<uint8_t> used(max_requests, 0);
@@ -626,55 +638,95 @@ NVH_API int nvh_commit_many(void* m, int S, const int64_t* rids, const int* ends
 // ---- the index arrays of one step
 // Layout of the one int32 buffer that carries a step's index arrays to the device, every segment starting on a
 // multiple of four ints: ids[T] pos[T] row_entry[T] cu[S+1] pos0[S] slot[S] want[W] single[S] (the batch rows of
-// the entries that have one row, in entry order, then -1), one block table [S][max_blocks] per group, and with
-// `sampling` temp[W] (float bits) and u[2W] (doubles).  offsets[] receives the 8 + groups (+ 2) segment starts; the
-// return value is the buffer's length in ints.
+// the entries that have one row, in entry order, then -1); per group table_src[S] (which uploaded row holds the
+// entry's block table, -1: the device's copy is current) and table_len[S] (pages in the entry's table); with
+// `sampling` temp[W] (float bits) and u[2W] (doubles); and last, per group, the uploaded rows
+// [rows[g]][max_blocks] (rows == nullptr: S rows per group, the most a step can need).  offsets[] receives the
+// 8 + 2 * groups (+ 2) + groups segment starts; the return value is the buffer's length in ints.
 static inline int align4(int n) { return (n + 3) & ~3; }
-NVH_API int nvh_step_layout(int S, int T, int W, int groups, int max_blocks, int sampling, int* offsets) {
+NVH_API int nvh_step_layout(int S, int T, int W, int groups, int max_blocks, int sampling, const int* rows,
+                            int* offsets) {
   int off = 0, k = 0;
+  auto seg = [&](long long len) {
+    if (offsets) offsets[k] = off;
+    ++k;
+    off = align4(off + (int)len);
+  };
   const int lens[8] = {T, T, T, S + 1, S, S, W, S};
-  for (int i = 0; i < 8; ++i) {
-    if (offsets) offsets[k] = off;
-    ++k;
-    off = align4(off + lens[i]);
-  }
+  for (int i = 0; i < 8; ++i) seg(lens[i]);
   for (int g = 0; g < groups; ++g) {
-    if (offsets) offsets[k] = off;
-    ++k;
-    off = align4(off + S * max_blocks);
+    seg(S);
+    seg(S);
   }
   if (sampling) {
-    if (offsets) offsets[k] = off;
-    ++k;
-    off = align4(off + W);
-    if (offsets) offsets[k] = off;
-    ++k;
-    off = align4(off + 2 * W);
+    seg(W);
+    seg(2 * W);
   }
+  for (int g = 0; g < groups; ++g) seg((long long)(rows ? rows[g] : S) * max_blocks);
   return off < 4 ? 4 : off;
 }
 
-// Takes the pages that the entries' next rows need and writes the step's arrays into `buf` (cap ints, filled
-// with -1 first).  Entry i is request rids[i] with lens[i] next tokens (tokens[] holds them back to back) whose
-// wanted places are wants[wants_cu[i] .. wants_cu[i+1]).  info[2i], info[2i+1] receive the entry's state slot and
-// first position.  Requests must be open.  Returns the length used, or an error (the entries before the failing
-// one keep the pages they took: taking them again is harmless).
+// Takes the pages that the entries' next rows need and writes the step's arrays into `buf` (cap ints).  Entry i is
+// request rids[i] with lens[i] next tokens (tokens[] holds them back to back) whose wanted places are
+// wants[wants_cu[i] .. wants_cu[i+1]).  info[2i], info[2i+1] receive the entry's state slot and first position.
+// Requests must be open.  A request's block table travels only if it has changed since it last did (a page taken
+// or given back, a new request): the device keeps the tables of all live requests by state slot.  `fixed_rows` = 0:
+// the uploaded rows are packed (as many as there are); > 0: every group has room for that many (the layout of a
+// captured step, which must not depend on the step).  offsets[] receives the segment starts (see
+// nvh_step_layout), uploaded[g] the number of rows that travel for group g.  Returns the length used, or an error:
+// then nothing was written and no table counts as sent (the entries before the failing one keep the pages they
+// took: taking them again is harmless).
 NVH_API int nvh_prepare_step(void* m, int S, const int64_t* rids, const int* lens, const int* tokens,
                              const int* wants_cu, const int* wants, int max_blocks, int max_model_len, int sampling,
-                             int* buf, int cap, int* info) {
+                             int fixed_rows, int* buf, int cap, int* info, int* offsets, int* uploaded) {
   CacheManager* cm = (CacheManager*)m;
   const int G = (int)cm->pools.size();
+  if (G > 64) return fail(ERR_STATE, "too many cache groups");
   int T = 0;
   for (int i = 0; i < S; ++i) {
     if (lens[i] < 1) return fail(ERR_STATE, "an entry needs at least one token");
     T += lens[i];
   }
   const int W = wants_cu[S];
-  int off[8 + 64 + 2];
-  if (G > 64) return fail(ERR_STATE, "too many cache groups");
-  const int total = nvh_step_layout(S, T, W, G, max_blocks, sampling, off);
-  if (total > cap) return fail(ERR_STATE, "the step's arrays do not fit the staging buffer");
-  std::fill(buf, buf + total, -1);
+  // first everything that can fail: the pages, the places, the widths
+  std::vector<RequestCache*> rcs(S);
+  int n_up[64] = {0};
+  for (int i = 0; i < S; ++i) {
+    RequestCache* rc = cm->find(rids[i]);
+    if (!rc) return fail(ERR_STATE, "request is not open");
+    for (int j = 0; j < i; ++j)
+      if (rcs[j] == rc) return fail(ERR_STATE, "a request appears twice in one step");
+    rcs[i] = rc;
+    const int start = rc->num_tokens, n = lens[i], end = start + n;
+    if (end > max_model_len)
+      return fail(ERR_STATE, "request " + std::to_string(rids[i]) + ": " + std::to_string(end) +
+                                 " tokens exceed the longest sequence " + std::to_string(max_model_len));
+    for (int w = wants_cu[i]; w < wants_cu[i + 1]; ++w)
+      if (wants[w] < 0 || wants[w] >= n)
+        return fail(ERR_STATE, "wanted place " + std::to_string(wants[w]) + " is not among the entry's " +
+                                   std::to_string(n) + " tokens");
+    const int r = cm->extend(rids[i], start, end);
+    if (r) return r;
+    for (int g = 0; g < G; ++g)
+      if ((int)rc->tables[g].size() > max_blocks)
+        return fail(ERR_STATE, "a request holds more pages than the block table is wide");
+  }
+  for (int i = 0; i < S; ++i)
+    for (int g = 0; g < G; ++g) n_up[g] += rcs[i]->dirty[g] ? 1 : 0;
+  int rows[64];
+  for (int g = 0; g < G; ++g) {
+    if (fixed_rows > 0 && n_up[g] > fixed_rows) return fail(ERR_STATE, "more block tables to send than the step has room for");
+    rows[g] = fixed_rows > 0 ? fixed_rows : n_up[g];
+  }
+  int off[8 + 3 * 64 + 2];
+  const int total = nvh_step_layout(S, T, W, G, max_blocks, sampling, rows, off);
+  const int rows_at = 8 + 2 * G + (sampling ? 2 : 0);        // index of the first group's uploaded rows in off[]
+  int used = G == 0 ? total : off[rows_at];                   // what travels ends with the last row that does
+  for (int g = 0; g < G; ++g)
+    if (n_up[g] > 0) used = align4(off[rows_at + g] + n_up[g] * max_blocks);
+  if (used < 4) used = 4;
+  if (used > cap || total > cap) return fail(ERR_STATE, "the step's arrays do not fit the staging buffer");
+  std::fill(buf, buf + used, -1);
   int* ids = buf + off[0];
   int* pos = buf + off[1];
   int* row_entry = buf + off[2];
@@ -684,27 +736,17 @@ NVH_API int nvh_prepare_step(void* m, int S, const int64_t* rids, const int* len
   int* want = buf + off[6];
   int* single = buf + off[7];
   int row = 0, n_single = 0;
+  int next_up[64] = {0};
   cu[0] = 0;
   for (int i = 0; i < S; ++i) {
-    RequestCache* rc = cm->find(rids[i]);
-    if (!rc) return fail(ERR_STATE, "request is not open");
-    const int start = rc->num_tokens, n = lens[i], end = start + n;
-    if (end > max_model_len)
-      return fail(ERR_STATE, "request " + std::to_string(rids[i]) + ": " + std::to_string(end) +
-                                 " tokens exceed the longest sequence " + std::to_string(max_model_len));
-    const int r = cm->extend(rids[i], start, end);
-    if (r) return r;
+    RequestCache* rc = rcs[i];
+    const int start = rc->num_tokens, n = lens[i];
     for (int j = 0; j < n; ++j) {
       ids[row + j] = tokens[row + j];
       pos[row + j] = start + j;
       row_entry[row + j] = i;
     }
-    for (int w = wants_cu[i]; w < wants_cu[i + 1]; ++w) {
-      if (wants[w] < 0 || wants[w] >= n)
-        return fail(ERR_STATE, "wanted place " + std::to_string(wants[w]) + " is not among the entry's " +
-                                   std::to_string(n) + " tokens");
-      want[w] = row + wants[w];
-    }
+    for (int w = wants_cu[i]; w < wants_cu[i + 1]; ++w) want[w] = row + wants[w];
     if (n == 1) single[n_single++] = row;
     pos0[i] = start;
     slot[i] = rc->slot;
@@ -712,14 +754,21 @@ NVH_API int nvh_prepare_step(void* m, int S, const int64_t* rids, const int* len
     info[2 * i + 1] = start;
     for (int g = 0; g < G; ++g) {
       const auto& t = rc->tables[g];
-      if ((int)t.size() > max_blocks) return fail(ERR_STATE, "a request holds more pages than the block table is wide");
-      std::memcpy(buf + off[8 + g] + (size_t)i * max_blocks, t.data(), sizeof(int) * t.size());
+      buf[off[8 + 2 * g + 1] + i] = (int)t.size();
+      if (!rc->dirty[g]) continue;              // table_src stays -1
+      const int r = next_up[g]++;
+      buf[off[8 + 2 * g] + i] = r;
+      std::memcpy(buf + off[rows_at + g] + (size_t)r * max_blocks, t.data(), sizeof(int) * t.size());
+      rc->dirty[g] = 0;
     }
     row += n;
     cu[i + 1] = row;
   }
-  return total;
+  if (offsets) std::memcpy(offsets, off, sizeof(int) * (size_t)(rows_at + G));
+  if (uploaded) std::memcpy(uploaded, n_up, sizeof(int) * (size_t)G);
+  return used;
 }
+NVH_API void nvh_touch_tables(void* m) { ((CacheManager*)m)->touch_all(); }
 
 // ---- the scheduler
 NVH_API void* nvs_create(void* manager, int max_num_seqs, int max_batched_tokens, int max_model_len, int eos,

@@ -570,6 +570,18 @@ def reset_fresh_state(state, entry_slot, entry_pos0) -> None:
                                       c_int(entry_slot.numel()), _stream()), "reset_fresh_state")
 
 
+def sync_block_tables(src, lens, rows, entry_slot, tables, step_tables, S: int) -> None:
+    """``tables`` [slots, max_blocks] takes in the rows that travelled with the step (``rows[src[e]]`` for the
+    entries with ``src[e]`` >= 0) and ``step_tables[e, :lens[e]]`` becomes entry e's table, for e < S."""
+    _cuda_contig(src, lens, rows, entry_slot, tables, step_tables)
+    _i32(src, lens, rows, entry_slot, tables, step_tables)
+    slots, max_blocks = tables.shape
+    _need(step_tables.shape == tables.shape and src.numel() >= S and lens.numel() >= S and entry_slot.numel() >= S,
+          "sync_block_tables: shapes")
+    _check(lib().nv_sync_block_tables(_p(src), _p(lens), _p(rows), _p(entry_slot), _p(tables), _p(step_tables),
+                                      c_int(S), c_int(max_blocks), c_int(slots), _stream()), "sync_block_tables")
+
+
 def delay(micros: int) -> None:
     """Keeps the current stream busy for about ``micros`` microseconds (at most 200,000); for measurements that
     want a step's launches queued before the GPU starts on them."""

@@ -675,6 +675,47 @@ NV_API int nv_reset_fresh_state(void* state, long long slot_bytes, int num_slots
   NV_RETURN_LAST();
 }
 
+// The block tables of a step's entries, put together on the device.  tables: [slots][max_blocks], the table of
+// every state slot's request as the device knows it; rows: the tables that travelled with this step (those that
+// have changed since they last did); src[e]: which of them is entry e's, or -1; lens[e]: pages in entry e's table.
+// Entry e's table is taken into tables[slot[e]] if it travelled, and tables[slot[e]][0 .. lens[e]) is copied to
+// step[e], which the step's kernels read.  (What lies beyond lens[e] in step[e] is left as it was: no kernel reads
+// beyond the pages of its rows.)  One block row per entry.  The reference builds the whole [S][max_blocks] array on
+// the host for every step (src/model_runner.cpp:29-41).
+__global__ void sync_block_tables_kernel(const int* __restrict__ src, const int* __restrict__ lens,
+                                         const int* __restrict__ rows, const int* __restrict__ entry_slot,
+                                         int* __restrict__ tables, int* __restrict__ step, int max_blocks,
+                                         int num_slots) {
+  const int e = blockIdx.x;
+  const int slot = entry_slot[e];
+  if (slot < 0 || slot >= num_slots) return;
+  const int n = min(lens[e], max_blocks), s = src[e];
+  int* mine = tables + (size_t)slot * max_blocks;
+  int* out = step + (size_t)e * max_blocks;
+  const int* sent = s >= 0 ? rows + (size_t)s * max_blocks : nullptr;
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < n; i += gridDim.y * blockDim.x) {
+    int v;
+    if (sent) {
+      v = sent[i];
+      mine[i] = v;
+    } else {
+      v = mine[i];
+    }
+    out[i] = v;
+  }
+}
+
+NV_API int nv_sync_block_tables(const int* src, const int* lens, const int* rows, const int* entry_slot, int* tables,
+                                int* step, int S, int max_blocks, int num_slots, cudaStream_t s) {
+  if (S == 0 || max_blocks <= 0) return NV_OK;
+  if (S > num_slots) return NV_ERR_BAD_SIZE;       // step[] has one row per slot
+  int chunks = (max_blocks + 1023) / 1024;
+  if (chunks > 32) chunks = 32;
+  sync_block_tables_kernel<<<dim3((unsigned)S, (unsigned)chunks), 256, 0, s>>>(src, lens, rows, entry_slot, tables, step,
+                                                                              max_blocks, num_slots);
+  NV_RETURN_LAST();
+}
+
 // Keeps the stream busy for about `micros` microseconds (at most 200,000) and does nothing else: a measurement queues
 // it before a step, so that the host has launched the whole step by the time the GPU starts on it and the times
 // between the step's kernels hold no waits for the host.

@@ -52,6 +52,7 @@ class StepBatch:
     temperatures: torch.Tensor = None   # [n_want] float32, when the step also samples
     uniforms: torch.Tensor = None       # [n_want] float64
     native_ids: object = None           # the entries' request ids as the native cache manager knows them
+    table_updates: list = None          # per group (src [S], len [S], rows [n, max_blocks]): see batch_layout
 
 
 def _align4(n: int) -> int:
@@ -108,30 +109,40 @@ class BatchStager:
         return self.submit(ticket, n, static_dev)
 
 
-def batch_layout(S: int, T: int, n_want: int, G: int, max_blocks: int, sampling: bool = False):
-    """Offsets of the index arrays inside the one int32 buffer of a step: name -> (offset, length).  With
+def batch_layout(S: int, T: int, n_want: int, G: int, max_blocks: int, sampling: bool = False, table_rows=None):
+    """Offsets of the index arrays inside the one int32 buffer of a step: name -> (offset, length).  Per cache
+    group: ``tsrc{g}`` [S] (which uploaded row holds the entry's block table; -1: the device's copy is current),
+    ``tlen{g}`` [S] (pages in the entry's table) and, at the end of the buffer, the uploaded rows ``trows{g}``
+    [``table_rows[g]``, max_blocks] (``table_rows`` None: S rows per group, the most a step can need).  With
     ``sampling`` the buffer also carries a temperature (float32) and a uniform number (float64) per wanted row.
     The native ``nvh_step_layout`` computes the same layout."""
     seg = {}
     off = 0
-    for name, n in (("ids", T), ("pos", T), ("row_entry", T), ("cu", S + 1), ("pos0", S), ("slot", S),
-                    ("want", n_want), ("single", S)):
+
+    def put(name, n):
+        nonlocal off
         seg[name] = (off, n)
         off = _align4(off + n)
+
+    for name, n in (("ids", T), ("pos", T), ("row_entry", T), ("cu", S + 1), ("pos0", S), ("slot", S),
+                    ("want", n_want), ("single", S)):
+        put(name, n)
     for g in range(G):
-        seg[f"bt{g}"] = (off, S * max_blocks)
-        off = _align4(off + S * max_blocks)
+        put(f"tsrc{g}", S)
+        put(f"tlen{g}", S)
     if sampling:
-        seg["temp"] = (off, n_want)
-        off = _align4(off + n_want)
-        seg["u"] = (off, 2 * n_want)
-        off = _align4(off + 2 * n_want)
+        put("temp", n_want)
+        put("u", 2 * n_want)
+    for g in range(G):
+        put(f"trows{g}", (S if table_rows is None else table_rows[g]) * max_blocks)
     return seg, max(off, 4)
 
 
 def batch_from_buffer(dev: torch.Tensor, seg: dict, infos: list, S: int, T: int, G: int, max_blocks: int,
-                      h2d_bytes: int) -> StepBatch:
-    """The views of a step's arrays inside the device copy ``dev`` of its buffer."""
+                      h2d_bytes: int, block_tables: list) -> StepBatch:
+    """The views of a step's arrays inside the device copy ``dev`` of its buffer.  ``block_tables``: per group the
+    [S, max_blocks] table that the kernels read (the device cache's, brought up to date from the buffer's
+    ``tsrc`` / ``tlen`` / ``trows`` segments by ``DeviceCache.sync_tables`` before the model runs)."""
     def view(name):
         o, n = seg[name]
         return dev[o:o + n]
@@ -141,12 +152,13 @@ def batch_from_buffer(dev: torch.Tensor, seg: dict, infos: list, S: int, T: int,
         temps = view("temp").view(torch.float32)
         us = view("u").view(torch.float64)
     n_single = sum(1 for i in infos if i.length == 1)
+    updates = [(view(f"tsrc{g}"), view(f"tlen{g}"), view(f"trows{g}")) for g in range(G)] if "tsrc0" in seg else None
     return StepBatch(
         T=T, S=S, input_ids=view("ids"), positions=view("pos"), row_entry=view("row_entry"), cu_rows=view("cu"),
         entry_pos0=view("pos0"), entry_slot=view("slot"), want_rows=view("want"),
-        block_tables=[view(f"bt{g}").view(S, max_blocks) for g in range(G)], entries=list(infos),
+        block_tables=block_tables, entries=list(infos),
         max_rows=max((i.length for i in infos), default=0),
         max_context=max((i.pos0 + i.length for i in infos), default=0),
         decode_only=n_single == len(infos), single_rows=view("single")[:n_single], n_single=n_single,
         max_single_context=max((i.pos0 + 1 for i in infos if i.length == 1), default=0),
-        h2d_bytes=h2d_bytes, temperatures=temps, uniforms=us)
+        h2d_bytes=h2d_bytes, temperatures=temps, uniforms=us, table_updates=updates)

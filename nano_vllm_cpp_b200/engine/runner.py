@@ -69,7 +69,7 @@ class ModelRunner:
             max_model_len = num_pages * page_size if paged else (max_tokens or 1 << 30)
         self.max_model_len = max_model_len
         self.max_blocks = max(1, (max_model_len + page_size - 1) // page_size) if paged else 1
-        self.cache.allocate(num_pages)
+        self.cache.allocate(num_pages, self.max_blocks if paged else 0)
         # prefix sharing only where every layer's cache is pages without a window (the manager refuses it otherwise)
         self.manager = CacheManager(self.cache.windows, num_pages, page_size, max_requests,
                                     prefix_caching=prefix_caching, has_state=self.cache.has_state)
@@ -125,41 +125,54 @@ class ModelRunner:
             if not self.manager.has(e.rid):
                 self.open(e.rid)
         S = len(entries)
+        if S > self.cache.max_slots:
+            raise StepError(f"a step takes at most {self.cache.max_slots} requests, found {S}")
         T = sum(len(e.tokens) for e in entries)
         W = sum(len(e.want) for e in entries)
         G = len(self.manager.pools)
-        seg, total = batch_layout(S, T, W, G, self.max_blocks, sampling is not None)
-        ticket, buf = self.stager.acquire(total)
+        if sampling is not None and (len(sampling[0]) != W or len(sampling[1]) != W):
+            raise StepError("one temperature and one uniform number per wanted row")
+        fixed = S if static_dev is not None else 0          # a captured step's layout does not depend on the step
+        _, most = batch_layout(S, T, W, G, self.max_blocks, sampling is not None)
+        ticket, buf = self.stager.acquire(most)
         try:
-            used, slots, native_ids = self.manager.prepare_step(entries, self.max_blocks, self.max_model_len,
-                                                               sampling is not None, buf)
+            used, slots, native_ids, sent = self.manager.prepare_step(entries, self.max_blocks, self.max_model_len,
+                                                                     sampling is not None, buf, fixed)
         except ValueError as e:
             raise StepError(str(e)) from None
-        assert used == total
-        if sampling is not None:
-            temps, us = sampling
-            if len(temps) != W or len(us) != W:
-                raise StepError("one temperature and one uniform number per wanted row")
-            o, n = seg["temp"]
-            buf[o:o + n].view(np.float32)[:] = temps
-            o, n = seg["u"]
-            buf[o:o + n].view(np.float64)[:] = us
-        dev = self.stager.submit(ticket, total, static_dev)
-        self.last_h2d_bytes = total * 4
+        try:
+            seg, total = batch_layout(S, T, W, G, self.max_blocks, sampling is not None, None if fixed else sent)
+            assert used <= total <= most
+            if sampling is not None:
+                temps, us = sampling
+                o, n = seg["temp"]
+                buf[o:o + n].view(np.float32)[:] = temps
+                o, n = seg["u"]
+                buf[o:o + n].view(np.float64)[:] = us
+            dev = self.stager.submit(ticket, used, static_dev)
+        except BaseException:
+            self.manager.invalidate_tables()       # the tables that were to travel with this step never did
+            raise
+        self.last_h2d_bytes = used * 4
         if views is False:          # a replayed graph has its views already: only what the commit needs
             return _Prepared(native_ids, [pos0 + len(e.tokens) for e, (_, pos0) in zip(entries, slots)])
         infos, row0 = [], 0
         for e, (slot, pos0) in zip(entries, slots):
             infos.append(EntryInfo(e.rid, slot, pos0, len(e.tokens), row0))
             row0 += len(e.tokens)
-        batch = batch_from_buffer(dev, seg, infos, S, T, G, self.max_blocks, total * 4)
+        tables = [t[:S] for t in self.cache.step_tables] if G else []
+        batch = batch_from_buffer(dev, seg, infos, S, T, G, self.max_blocks, used * 4, tables)
         batch.native_ids = native_ids
-        self.last_h2d_bytes = batch.h2d_bytes
         return batch
 
     def _forward(self, batch):
-        self.cache.reset_fresh(batch)
-        return self.model.forward(batch, self.cache)
+        try:
+            self.cache.sync_tables(batch)
+            self.cache.reset_fresh(batch)
+            return self.model.forward(batch, self.cache)
+        except BaseException:
+            self.manager.invalidate_tables()       # the step may not have run: its tables travel again
+            raise
 
     def _commit(self, batch) -> None:
         ends = batch.ends if isinstance(batch, _Prepared) else [i.pos0 + i.length for i in batch.entries]

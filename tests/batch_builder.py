@@ -10,13 +10,15 @@ def build_batch(entries: list, infos: list, tables, max_blocks: int, device, sta
                 static_dev=None, table_filler=None, num_groups=None) -> StepBatch:
     """``infos``: EntryInfo per entry; ``tables``: per group, per entry, the list of page ids — or None with
     ``table_filler(group, entry, dst)``, which writes an entry's block table into an int32 array view.
-    With ``static_dev`` the arrays are written into that device buffer (whose layout must be the one
-    of ``batch_layout`` for these sizes) instead of a fresh one."""
+    The block tables are written whole, [S, max_blocks] per group behind the other arrays (the product sends only
+    the tables that changed and keeps the rest on the device).  With ``static_dev`` the arrays are written into that
+    device buffer (at least as long) instead of a fresh one."""
     S = len(entries)
     T = sum(len(e.tokens) for e in entries)
     n_want = sum(len(e.want) for e in entries)
     G = len(tables) if tables is not None else num_groups
-    seg, total = batch_layout(S, T, n_want, G, max_blocks)
+    seg, fixed = batch_layout(S, T, n_want, G, max_blocks, table_rows=[0] * G)    # no tables travel: dense ones follow
+    total = fixed + G * S * max_blocks
     host = np.full(total, -1, dtype=np.int32)
 
     def put(name, values):
@@ -39,7 +41,7 @@ def build_batch(entries: list, infos: list, tables, max_blocks: int, device, sta
     single = [i.row0 for i in infos if i.length == 1]
     put("single", single + [-1] * (S - len(single)))
     for g in range(G):
-        o, _ = seg[f"bt{g}"]
+        o = fixed + g * S * max_blocks
         if tables is None:
             for i in range(S):
                 if table_filler(g, i, host[o + i * max_blocks:o + (i + 1) * max_blocks]) > max_blocks:
@@ -53,4 +55,7 @@ def build_batch(entries: list, infos: list, tables, max_blocks: int, device, sta
         stager = BatchStager(device, depth=1)
     dev = stager.stage(host, static_dev)
 
-    return batch_from_buffer(dev, seg, infos, S, T, G, max_blocks, int(host.nbytes))
+    dense = [dev[fixed + g * S * max_blocks:fixed + (g + 1) * S * max_blocks].view(S, max_blocks) for g in range(G)]
+    batch = batch_from_buffer(dev, seg, infos, S, T, G, max_blocks, int(host.nbytes), dense)
+    batch.table_updates = None              # the tables above are complete: nothing is to be taken in
+    return batch

@@ -476,23 +476,29 @@ def test_native_pool_and_hash_against_the_plain_restatement():
 
 
 def test_native_step_arrays_match_the_python_builder():
-    """The native fill of a step's index arrays against ``build_batch`` on the same requests."""
+    """The native fill of a step's index arrays against ``build_batch`` on the same requests.  Block tables travel
+    only when they have changed: the test keeps the tables by state slot as the device does, takes in what a step
+    brings, and holds the result to the manager's own tables."""
     import numpy as np
     from nano_vllm_cpp_b200.engine.batch import StepEntry, EntryInfo, batch_layout
     from batch_builder import build_batch
     rng = random.Random(5)
+    sent_total = entries_total = 0
     for trial in range(30):
         windows = rng.choice([(0,), (0, 16)])
+        G = len(windows)
         m = CacheManager(list(windows), 64, 16, max_requests=6)
         max_blocks = 12
         live = {}
-        for step in range(6):
+        device_tables = [dict() for _ in range(G)]          # per group: slot -> the table as the device has it
+        last_sent = [dict() for _ in range(G)]              # per group: rid -> the table when it last travelled
+        for step in range(8):
             entries = []
             for rid in rng.sample(["a", "b", 3, 4, "e"], rng.randrange(1, 5)):
                 if not m.has(rid):
                     m.open(rid)
                     live[rid] = 0
-                n = rng.choice([1, 1, 2, 5, 17])
+                n = rng.choice([1, 1, 1, 2, 5, 17])
                 if live[rid] + n > 150:
                     continue
                 toks = [rng.randrange(1000) for _ in range(n)]
@@ -501,18 +507,22 @@ def test_native_step_arrays_match_the_python_builder():
             if not entries:
                 continue
             sampling = rng.random() < 0.5
+            fixed_rows = len(entries) if rng.random() < 0.3 else 0
             S, T = len(entries), sum(len(e.tokens) for e in entries)
             W = sum(len(e.want) for e in entries)
-            seg, total = batch_layout(S, T, W, len(windows), max_blocks, sampling)
-            buf = np.full(total + 7, 12345, dtype=np.int32)
-            used, slots, ids = m.prepare_step(entries, max_blocks, 160, sampling, buf)
-            assert used == total and (buf[total:] == 12345).all()
+            _, most = batch_layout(S, T, W, G, max_blocks, sampling)
+            buf = np.full(most + 7, 12345, dtype=np.int32)
+            used, slots, ids, sent = m.prepare_step(entries, max_blocks, 160, sampling, buf, fixed_rows)
+            seg, total = batch_layout(S, T, W, G, max_blocks, sampling, None if fixed_rows else sent)
+            assert used <= total <= most and (buf[used:] == 12345).all()
+            if not fixed_rows:
+                assert used == total
             infos, row0 = [], 0
             for e, (slot, pos0) in zip(entries, slots):
                 assert (slot, pos0) == (m.get(e.rid).slot, live[e.rid])
                 infos.append(EntryInfo(e.rid, slot, pos0, len(e.tokens), row0))
                 row0 += len(e.tokens)
-            tables = [[m.get(e.rid).tables[g] for e in entries] for g in range(len(windows))]
+            tables = [[m.get(e.rid).tables[g] for e in entries] for g in range(G)]
             ref = build_batch(entries, infos, tables, max_blocks, "cpu")
             for name, t in (("ids", ref.input_ids), ("pos", ref.positions), ("row_entry", ref.row_entry),
                             ("cu", ref.cu_rows), ("pos0", ref.entry_pos0), ("slot", ref.entry_slot),
@@ -523,14 +533,50 @@ def test_native_step_arrays_match_the_python_builder():
             singles = [i.row0 for i in infos if i.length == 1]
             assert buf[o:o + n].tolist() == singles + [-1] * (S - len(singles))
             assert ref.single_rows.tolist() == singles and ref.n_single == len(singles)
-            for g in range(len(windows)):
-                o, n = seg[f"bt{g}"]
-                assert buf[o:o + n].tolist() == ref.block_tables[g].flatten().tolist()
+            for g in range(G):
+                src = buf[seg[f"tsrc{g}"][0]:][:S].tolist()
+                lens = buf[seg[f"tlen{g}"][0]:][:S].tolist()
+                rows = buf[seg[f"trows{g}"][0]:]
+                assert sorted(x for x in src if x >= 0) == list(range(sent[g]))      # packed, each row used once
+                for i, (e, info) in enumerate(zip(entries, infos)):
+                    table = list(m.get(e.rid).tables[g])
+                    assert lens[i] == len(table)
+                    assert (src[i] >= 0) == (last_sent[g].get(e.rid) != table), (trial, step, e.rid)
+                    if src[i] >= 0:
+                        row = rows[src[i] * max_blocks:(src[i] + 1) * max_blocks].tolist()
+                        assert row == table + [-1] * (max_blocks - len(table))
+                        device_tables[g][info.slot] = row
+                        last_sent[g][e.rid] = table
+                    assert device_tables[g][info.slot][:lens[i]] == ref.block_tables[g][i, :lens[i]].tolist()
+                sent_total += sent[g]
+                entries_total += S
             m.commit_many(ids, [i.pos0 + i.length for i in infos])
             for e in entries:
                 live[e.rid] += len(e.tokens)
                 assert m.get(e.rid).num_tokens == live[e.rid]
+            if rng.random() < 0.15:                      # a request ends; its slot goes to whoever opens next
+                gone = rng.choice(sorted(live, key=str))
+                m.close(gone)
+                del live[gone]
+                for g in range(G):
+                    last_sent[g].pop(gone, None)
+            if rng.random() < 0.1:                       # a prepared step never ran: everything travels again
+                m.invalidate_tables()
+                for g in range(G):
+                    last_sent[g].clear()
         m.check()
+    assert 0 < sent_total < entries_total                # some tables stayed at home
+    # a step that fails sends nothing and leaves every table still to be sent
+    m = CacheManager([0], 4, 16, max_requests=2)
+    m.open("p"), m.open("q")
+    buf = np.zeros(512, dtype=np.int32)
+    with pytest.raises(Exception):
+        m.prepare_step([StepEntry("p", [1] * 20, []), StepEntry("q", [1] * 60, [])], 8, 1000, False, buf)
+    used, _, ids, sent = m.prepare_step([StepEntry("p", [1] * 20, [])], 8, 1000, False, buf)
+    assert sent == [1]
+    m.commit_many(ids, [20])
+    used, _, ids, sent = m.prepare_step([StepEntry("p", [1], [])], 8, 1000, False, buf)
+    assert sent == [0]                                   # position 20 lies in a page that the request holds already
     # errors: a place that is not among the tokens, an entry without tokens, too long a sequence
     m = CacheManager([0], 8, 16, max_requests=2)
     m.open("x")

@@ -704,3 +704,28 @@ def test_attention_prefill_against_plain(Hq, Hkv, D, page, window):
         e = int(row_entry[r])
         want = attention_reference(qkv[r, :Hq * D].reshape(Hq, D).cpu(), ks[e], vs[e], int(pos[r]), scale, window)
         close(out[r], want.reshape(-1), 1.5e-2, f"row {r}")
+
+
+def test_block_tables_are_put_together_on_the_device():
+    """``sync_block_tables``: a step's tables come from the tables kept by state slot, after the rows that travel
+    with the step have been taken in; what lies beyond an entry's pages is left alone."""
+    from nano_vllm_cpp_b200.csrc import ops
+    g = torch.Generator().manual_seed(3)
+    slots, max_blocks = 7, 2100                   # more than one chunk of the kernel's walk along a table
+    kept = torch.randint(0, 5000, (slots, max_blocks), generator=g, dtype=torch.int32)
+    step = torch.full((slots, max_blocks), -7, dtype=torch.int32)
+    entry_slot = torch.tensor([4, 0, 6, 2], dtype=torch.int32)
+    lens = torch.tensor([2100, 3, 0, 1500], dtype=torch.int32)
+    src = torch.tensor([1, -1, -1, 0], dtype=torch.int32)
+    rows = torch.randint(5000, 9000, (2, max_blocks), generator=g, dtype=torch.int32)
+    want_kept, want_step = kept.clone(), step.clone()
+    for e in range(4):
+        s, n = int(entry_slot[e]), int(lens[e])
+        if src[e] >= 0:
+            want_kept[s, :n] = rows[int(src[e]), :n]
+        want_step[e, :n] = want_kept[s, :n]
+    d = [t.to(DEV) for t in (src, lens, rows, entry_slot, kept, step)]
+    ops.sync_block_tables(*d, 4)
+    assert torch.equal(d[4].cpu(), want_kept) and torch.equal(d[5].cpu(), want_step)
+    ops.sync_block_tables(*d, 4)                   # the same step again changes nothing
+    assert torch.equal(d[4].cpu(), want_kept) and torch.equal(d[5].cpu(), want_step)

@@ -127,6 +127,41 @@ def test_float32_logits_are_bit_equal_however_the_work_is_cut(case, folders):
     rp.step([], end=["x", "o"])
 
 
+def test_block_tables_travel_only_when_they_change(folders):
+    """A request's block table goes to the device when it has changed (a page taken or given back, a new request)
+    and stays there otherwise: decode steps inside a page send no table, the logits are those of a runner whose
+    tables all travel with every step, and after a step that was prepared but never ran everything travels again."""
+    from nano_vllm_cpp_b200.engine.batch import StepEntry
+    case = "C"                                     # one group with a window, one without: pages are given back too
+    lazy = make_runner(folders[case], "float32", 64 * 4)
+    eager = make_runner(folders[case], "float32", 64 * 4)
+    ids = {r: prompt(case, 70, salt=60 + r) for r in range(3)}
+    sent_bytes = []
+    for step in range(40):
+        entries = []
+        for r in range(3):
+            at = 0 if step == 0 else 30 + step - 1          # 30 tokens at once, then one by one
+            n = 30 if step == 0 else 1
+            entries.append(StepEntry(r, ids[r][at:at + n], [n - 1]))
+        eager.manager.invalidate_tables()
+        a = lazy.step(entries).clone()
+        sent_bytes.append(lazy.last_h2d_bytes)
+        b = eager.step(entries)
+        assert torch.equal(a, b), step
+        assert eager.last_h2d_bytes >= lazy.last_h2d_bytes
+    G, S, mb = len(lazy.manager.pools), 3, lazy.max_blocks
+    assert G == 2
+    # positions 30..68: pages are taken at 32, 48 and 64 and one is given back at 63; the other steps carry no table
+    quiet = min(sent_bytes[1:])
+    assert sent_bytes.count(quiet) >= 30 and max(sent_bytes[1:]) >= quiet + 4 * S * mb
+    # a prepared step that does not run: the next one brings every table again, and the logits stay right
+    entries = [StepEntry(r, ids[r][69:70], [0]) for r in range(3)]
+    lazy.prepare([StepEntry(0, ids[0][69:70], [0])])
+    lazy.manager.invalidate_tables()
+    a, b = lazy.step(entries).clone(), eager.step(entries)
+    assert torch.equal(a, b) and lazy.last_h2d_bytes >= quiet + 4 * G * S * mb
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_first_tokens_and_long_decoding(dtype, folders):
     """Positions 0, 1, 2 alone, then 150 tokens one by one (beyond several pages and the window)."""
