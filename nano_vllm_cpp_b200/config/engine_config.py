@@ -24,6 +24,7 @@ class EngineConfig:
     run_ahead: bool = True                # launch a step before the host has read the tokens of the one before
     device: str = "cuda:0"
     log_stats: bool = True                # at start-up, on stderr: device memory after loading, size of the page pool
+    warm_up: bool = True                  # at start-up, one step of max_num_batched_tokens tokens: sizes the workspace
 
     def validate(self) -> None:
         self.dtype = {"bf16": "bfloat16", "fp32": "float32"}.get(self.dtype, self.dtype)

@@ -69,8 +69,24 @@ class LLMEngine:
                                    max_num_batched_tokens=cfg.max_num_batched_tokens,
                                    max_model_len=cfg.max_model_len, eos=cfg.eos, prefill_chunk=cfg.prefill_chunk)
         self.sampler = Sampler(self.runner.device)
+        if cfg.warm_up:
+            self._warm_up()
         self._pending = None
         self._nucleus_live = set()      # ids of live requests that are sampled by the nucleus rule
+
+    def _warm_up(self) -> None:
+        """The largest step the scheduler can ask for runs once before the first request: what its activations
+        take is the engine's workspace from then on (the allocator keeps it), so that serving allocates no device
+        memory for a step (the reference allocates per step: src/model.cpp:719-754)."""
+        import sys
+        import torch
+        cfg = self.config
+        before = torch.cuda.memory_reserved(self.runner.device)
+        n = self.runner.warm_up(min(cfg.max_num_batched_tokens, cfg.max_num_seqs * cfg.max_model_len))
+        if cfg.log_stats:
+            held = torch.cuda.memory_reserved(self.runner.device) - before
+            print(f"[nanovllm] workspace: {max(held, 0) / 2**30:.2f} GiB more held after a step of {n} tokens "
+                  f"(max_num_batched_tokens {cfg.max_num_batched_tokens})", file=sys.stderr, flush=True)
 
     @staticmethod
     def _eos_from_files(model_dir: str, from_config: int) -> int:

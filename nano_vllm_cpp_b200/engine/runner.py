@@ -111,6 +111,35 @@ class ModelRunner:
     def num_cached(self, rid) -> int:
         return self.manager.get(rid).num_tokens
 
+    def warm_up(self, num_tokens: int) -> int:
+        """Runs one step of up to ``num_tokens`` tokens with the sampling kernel behind it (as few requests as the
+        longest sequence allows, as many tokens as the free pages hold) and gives every page and slot back.  It is
+        the largest step the scheduler will ask for, so the memory its activations take is held from now on and
+        the steps that follow allocate nothing on the device (the reference allocates and frees its activations in
+        every step, src/model.cpp:719-754).  Returns the number of tokens run."""
+        pages_left = min((p.num_free() for p in self.manager.pools), default=None)
+        slots_left = self.manager.free_slots()
+        entries, left = [], num_tokens
+        while left > 0 and slots_left > 0:
+            k = min(left, self.max_model_len)
+            if pages_left is not None:
+                k = min(k, pages_left * self.page_size)
+                pages_left -= (k + self.page_size - 1) // self.page_size
+            if k < 1:
+                break
+            entries.append(StepEntry(("warm-up", len(entries)), [0] * k, [k - 1]))
+            left -= k
+            slots_left -= 1
+        if not entries:
+            return 0
+        try:
+            self.step_tokens(entries, [0.0] * len(entries), [0.0] * len(entries))
+        finally:
+            for e in entries:
+                if self.manager.has(e.rid):
+                    self.close(e.rid)
+        return num_tokens - left
+
     # ------------------------------------------------------------------ the step
     def prepare(self, entries: list, static_dev=None, sampling=None, views: bool = True):
         """Takes pages for the entries' positions and builds the batch arrays (natively, straight into a pinned

@@ -353,7 +353,31 @@ def test_command_line_with_a_config_file_and_the_start_up_lines(tmp_path):
         assert r.returncode == 0, r.stderr[-2000:]
         runs.append([l for l in r.stdout.splitlines() if l.startswith("token_ids:")][0])
         assert "[nanovllm] weights loaded:" in r.stderr and "[nanovllm] cache pool: 8 pages of 16 tokens" in r.stderr
+        assert "[nanovllm] workspace:" in r.stderr and "after a step of 128 tokens" in r.stderr      # all 8 pages
     assert runs[0] == runs[1] and len(runs[0].split()) == 6          # the seed fixes the weights
+
+
+def test_the_start_up_step_sizes_the_workspace(folders):
+    """The engine runs the largest step its scheduler can ask for once at start-up; what the allocator holds after
+    it serves every later step: prompts that fill the token budget, decoding, sampling, without more device
+    memory being taken (captured decode steps keep memory of their own and are left out here)."""
+    from nano_vllm_cpp_b200 import SamplingParams
+    case = "C"
+    prompts = [prompt(case, n, salt=70 + i) for i, n in enumerate((90, 60, 33, 7, 120, 2))]
+    sp = [SamplingParams(temperature=0.8 if i % 2 else 0.0, max_tokens=12, ignore_eos=True, seed=i) for i in range(6)]
+    grew = {}
+    for warm in (True, False):
+        torch.cuda.synchronize()
+        torch.cuda.empty_cache()
+        eng = engine(folders[case], dtype="bfloat16", max_model_len=160, num_kv_blocks=48, max_num_batched_tokens=256,
+                     cuda_graphs=False, warm_up=warm, log_stats=False)
+        assert all(p.num_free() == p.num_pages for p in eng.runner.manager.pools) and eng.runner.manager.free_slots() == 8
+        before = torch.cuda.memory_reserved()
+        outs = eng.generate(prompts, sp)
+        assert all(len(o["token_ids"]) == 12 for o in outs)
+        grew[warm] = torch.cuda.memory_reserved() - before
+        del eng
+    assert grew[True] <= 2 << 20 and grew[True] < grew[False]       # at most one more small segment of the allocator's
 
 
 def test_kernel_times():
