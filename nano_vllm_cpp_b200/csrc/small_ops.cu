@@ -113,6 +113,9 @@ __global__ void __launch_bounds__(256) rowdot_wide_kernel(const float* __restric
 #pragma unroll
     for (int i = 0; i < 4; ++i) wr[i] = w + (size_t)min(n0 + i, N - 1) * K;
     if (vec) {
+      // (few rows per block: unrolled, so that a warp has the weight loads of several steps under way; with four or
+      // eight rows the accumulators leave no registers for that and the unrolled loop was slower)
+#pragma unroll (WT <= 2 ? 8 : 1)
       for (int k = lane * 4; k < K; k += 128) {
         float4 av[WT];
 #pragma unroll
@@ -207,31 +210,39 @@ NV_API int nv_rowdot(const float* a, long long lda, const void* w, int w_dt, flo
                      int N, int K, int wide, cudaStream_t s) {
   if (!dt_ok(w_dt)) return NV_ERR_BAD_DTYPE;
   if (T == 0 || N == 0) return NV_OK;
-  // many rows: eight per block where they fit the shared memory (every block reads the whole matrix, so
-  // fewer, fatter blocks halve what comes out of L2), else four
-  if (wide && T >= 1024 && (size_t)8 * K * 4 <= 96 * 1024) {
-    static bool attr_done = false;
-    if (!attr_done) {
-      cudaError_t e = cudaFuncSetAttribute(rowdot_wide_kernel<float, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-      if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(rowdot_wide_kernel<bf16, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-      if (e != cudaSuccess) return (int)e;
-      attr_done = true;
+  // many rows: WT of them per block in shared memory.  Every block reads the whole matrix (from L2), so fat blocks
+  // save traffic, but a block's eight warps each walk all of k alone, so there must be blocks enough to hide that:
+  // WT = T / 256 (1, 2, 4 or 8), i.e. 256 blocks or more.  (Measured at 256 rows, 61 outputs, K = 2,048: 60 us with
+  // 64 blocks of four rows.)  A row's sum does not depend on WT.
+  if (wide) {
+    int wt = 8;
+    while (wt > 1 && (T < 256 * wt || (size_t)wt * K * 4 > 96 * 1024)) wt >>= 1;
+    const size_t smem = (size_t)wt * K * 4;
+    if (smem <= 96 * 1024) {
+      static bool attr_done = false;
+      if (!attr_done) {
+        const void* fns[8] = {(const void*)rowdot_wide_kernel<float, 1>, (const void*)rowdot_wide_kernel<bf16, 1>,
+                              (const void*)rowdot_wide_kernel<float, 2>, (const void*)rowdot_wide_kernel<bf16, 2>,
+                              (const void*)rowdot_wide_kernel<float, 4>, (const void*)rowdot_wide_kernel<bf16, 4>,
+                              (const void*)rowdot_wide_kernel<float, 8>, (const void*)rowdot_wide_kernel<bf16, 8>};
+        for (const void* f : fns) {
+          const cudaError_t e = cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+          if (e != cudaSuccess) return (int)e;
+        }
+        attr_done = true;
+      }
+      const unsigned blocks = (unsigned)((T + wt - 1) / wt);
+      const bool f32 = w_dt == NV_DT_F32;
+#define NV_ROWDOT_WIDE(WT)                                                                                          \
+  if (f32) rowdot_wide_kernel<float, WT><<<blocks, 256, smem, s>>>(a, lda, (const float*)w, out, ldo, T, N, K);     \
+  else rowdot_wide_kernel<bf16, WT><<<blocks, 256, smem, s>>>(a, lda, (const bf16*)w, out, ldo, T, N, K)
+      if (wt == 8) { NV_ROWDOT_WIDE(8); }
+      else if (wt == 4) { NV_ROWDOT_WIDE(4); }
+      else if (wt == 2) { NV_ROWDOT_WIDE(2); }
+      else { NV_ROWDOT_WIDE(1); }
+#undef NV_ROWDOT_WIDE
+      NV_RETURN_LAST();
     }
-    const unsigned blocks = (unsigned)((T + 7) / 8);
-    if (w_dt == NV_DT_F32)
-      rowdot_wide_kernel<float, 8><<<blocks, 256, (size_t)8 * K * 4, s>>>(a, lda, (const float*)w, out, ldo, T, N, K);
-    else
-      rowdot_wide_kernel<bf16, 8><<<blocks, 256, (size_t)8 * K * 4, s>>>(a, lda, (const bf16*)w, out, ldo, T, N, K);
-    NV_RETURN_LAST();
-  }
-  if (wide && (size_t)4 * K * 4 <= 48 * 1024) {
-    const unsigned blocks = (unsigned)((T + 3) / 4);
-    if (w_dt == NV_DT_F32)
-      rowdot_wide_kernel<float, 4><<<blocks, 256, (size_t)4 * K * 4, s>>>(a, lda, (const float*)w, out, ldo, T, N, K);
-    else
-      rowdot_wide_kernel<bf16, 4><<<blocks, 256, (size_t)4 * K * 4, s>>>(a, lda, (const bf16*)w, out, ldo, T, N, K);
-    NV_RETURN_LAST();
   }
   if ((N + 3) / 4 > 65535) return NV_ERR_BAD_SIZE;
   dim3 grid(T, (N + 3) / 4);

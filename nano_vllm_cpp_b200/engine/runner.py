@@ -196,6 +196,7 @@ class ModelRunner:
 
     def _forward(self, batch):
         try:
+            ops.mark_step()                        # (per-kernel timers: the step's kernels begin here)
             self.cache.sync_tables(batch)
             self.cache.reset_fresh(batch)
             return self.model.forward(batch, self.cache)

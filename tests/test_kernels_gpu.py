@@ -318,7 +318,8 @@ def test_skinny_gemm_dense(R, N, K, swiglu, out_dtype):
         o.skinny_gemm(a[:, :K - 8].contiguous(), w[:, :K - 8].contiguous(), out, swiglu=swiglu, rows=R)
 
 
-@pytest.mark.parametrize("T,N,K", [(1, 1, 64), (8, 60, 2048), (33, 7, 100), (5, 64, 3000), (1030, 61, 520), (1025, 9, 2050)])
+@pytest.mark.parametrize("T,N,K", [(1, 1, 64), (8, 60, 2048), (33, 7, 100), (5, 64, 3000), (1030, 61, 520), (1025, 9, 2050),
+                                   (300, 61, 2048), (600, 61, 1032), (2100, 5, 264)])
 @pytest.mark.parametrize("tw", [torch.float32, torch.bfloat16])
 def test_rowdot(T, N, K, tw):
     o = ops()
@@ -329,6 +330,10 @@ def test_rowdot(T, N, K, tw):
     wide = torch.empty(T, N, device=DEV)
     o.rowdot(a, w, wide, wide=True)                  # the many-rows kernel: same values up to rounding
     close(wide, a.double() @ w.double().T, 2e-6, "rowdot wide")
+    if T >= 4:                                       # ... and a row's value does not depend on how many rows a block takes
+        part = torch.empty(T // 4, N, device=DEV)
+        o.rowdot(a[:T // 4].contiguous(), w, part, wide=True)
+        assert torch.equal(part, wide[:T // 4])
     one = torch.empty(1, N, device=DEV)
     o.rowdot(a[T - 1:T].contiguous(), w, one)
     assert torch.equal(one[0], out[T - 1])          # a row does not depend on the batch
