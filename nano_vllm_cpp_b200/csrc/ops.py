@@ -644,26 +644,26 @@ def gemm_fast_usable(a, w, out, *, bias=None, a_rows=None, swiglu=False, grouped
     return True
 
 
-SKINNY_MAX_ROWS = 8
+SKINNY_MAX_ROWS = 32               # without SwiGLU; 8 with it
 GROUPED_SPLIT_MAX_PAIRS = 16       # grouped products of at most this many (row, expert) pairs may split K
 
 
-def skinny_usable(a, w, rows: int) -> bool:
+def skinny_usable(a, w, rows: int, swiglu: bool = False) -> bool:
     """Whether the weight-streaming product for a handful of rows (skinny_gemm.cu) takes these operands."""
-    return (1 <= rows <= SKINNY_MAX_ROWS and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+    return (1 <= rows <= (8 if swiglu else SKINNY_MAX_ROWS) and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
             and a.stride(-1) == 1 and w.is_contiguous() and a.shape[-1] % 32 == 0 and a.stride(0) % 8 == 0
             and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
 def skinny_gemm(a, w, out, *, bias=None, swiglu=False, rows=None, err=None) -> None:
-    """``out[:rows] = a[:rows] @ w.T (+ bias)`` for at most eight rows (default: all rows of ``a``), by streaming
-    ``w`` once; ``swiglu`` as in ``gemm_plain``."""
+    """``out[:rows] = a[:rows] @ w.T (+ bias)`` for at most 32 rows (8 with ``swiglu``; default: all rows of ``a``),
+    by streaming ``w`` once; ``swiglu`` as in ``gemm_plain``."""
     _cuda_contig(w, bias)
     K = a.shape[-1]
     rows_w = w.shape[0]
     N = rows_w // 2 if swiglu else rows_w
     R = a.shape[0] if rows is None else rows
-    _need(skinny_usable(a, w, R), "skinny product: operands or row count not supported")
+    _need(skinny_usable(a, w, R, swiglu), "skinny product: operands or row count not supported")
     _need(w.dim() == 2 and w.shape[1] == K and out.shape[1] == N and out.stride(1) == 1 and out.shape[0] >= R,
           "skinny product: shapes")
     _need(bias is None or (not swiglu and bias.numel() == N), "skinny product: bias")

@@ -1,4 +1,5 @@
-// Dense products of a handful of rows with bfloat16 weights: out[r, n] = sum_k x[r, k] * W[n, k], r < 8.
+// Dense products of a handful of rows with bfloat16 weights: out[r, n] = sum_k x[r, k] * W[n, k], r < 8 (r < 32
+// without SwiGLU).
 //
 // With one to eight rows a product is nothing but a stream of W from memory, and what decides its time is how soon
 // the whole matrix is on its way.  The tcgen05 kernel (tc_gemm.cu) pays for its set-up here: a weight tile of 128
@@ -12,7 +13,10 @@
 // slots of two instructions' A fragments, and the lane's 16 bytes of the x row at the same k as its B slots, so each
 // instruction sums 16 values of k that are not the 16 the fragment layout names, but the same 16 in A and in B, and
 // all of them exactly once.  Warps' partial sums are added in warp order in shared memory.  A row's result depends
-// on no other row.  Options: bias; swiglu (W holds gate rows [0, N) and up rows [N, 2N); out = silu(gate) * up).
+// on no other row.  More than eight rows (up to 32, without SwiGLU) are NT groups of eight: the same weight
+// fragments go through NT instructions, each with its own eight rows of x, which come from the first-level cache (x is
+// a few hundred KB at most) while the weights come from memory.
+// Options: bias; swiglu (W holds gate rows [0, N) and up rows [N, 2N); out = silu(gate) * up).
 //
 // It is for small streams: one block per multiprocessor with a round of loads ahead tops out near 4.5 TB/s, so
 // matrices beyond about a hundred MB stay with the tcgen05 kernel, whose ring is deeper; and inside a decode step
@@ -25,7 +29,8 @@
 namespace {
 
 constexpr int SK_WARPS = 16;          // warps per block: the block's share of K is cut into this many
-constexpr int SK_MAX_ROWS = 8;
+constexpr int SK_MAX_ROWS = 32;        // without SwiGLU; 8 with it.  (64 rows as eight groups were slower inside a step
+                                       // than the tcgen05 kernel: batch 64 6,209 -> 6,030 tokens/s; 16 and 32 rows gain 1.5 %)
 constexpr int SK_LOADS = 8;           // 16-byte weight loads of a lane per round; two rounds are in flight
 
 struct SkArgs {
@@ -45,11 +50,12 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint3
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-template <bool SWIGLU>
+template <bool SWIGLU, int NT>
 __global__ void __launch_bounds__(SK_WARPS * 32, 1) skinny_kernel(SkArgs a) {
   constexpr int NA = SWIGLU ? 2 : 1;                  // accumulators: gate and up
   constexpr int SK_BATCH = SK_LOADS / (2 * NA);       // steps of 32 elements of K per round of loads
-  __shared__ float part[2][SK_WARPS][NA][32][4];
+  extern __shared__ __align__(16) float part_s[];     // [2][SK_WARPS][NA][NT][32][4]
+  typedef float (*PartPtr)[NA][NT][32][4];
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const int g = lane / 4, c = lane % 4;               // fragment row / column group of this lane
   const int total = a.groups_n;                       // groups of sixteen features
@@ -74,57 +80,86 @@ __global__ void __launch_bounds__(SK_WARPS * 32, 1) skinny_kernel(SkArgs a) {
       }
     }
   };
-  float acc[NA][4];
+  float acc[NA][NT][4];
   auto clear = [&]() {
 #pragma unroll
-    for (int s = 0; s < NA; ++s) acc[s][0] = acc[s][1] = acc[s][2] = acc[s][3] = 0.f;
+    for (int s = 0; s < NA; ++s)
+#pragma unroll
+      for (int t = 0; t < NT; ++t) acc[s][t][0] = acc[s][t][1] = acc[s][t][2] = acc[s][t][3] = 0.f;
   };
-  // this lane's row of x (column g of the B operand); lanes beyond the rows multiply zeros
+  // this lane's rows of x (column g of the B operand of each group of eight rows); lanes beyond the rows multiply zeros
   const uint4* xp = (const uint4*)(a.x + (size_t)(g < a.R ? g : 0) * a.ldx) + c;
+  const size_t x_tile = (size_t)8 * a.ldx / 8;        // uint4s from one group of eight rows to the next
   int done = 0;                                       // groups this block has finished: which half of `part` is next
   auto compute = [&](int n0, int r, const uint4 (&wl)[SK_BATCH][NA], const uint4 (&wh)[SK_BATCH][NA]) {
-    uint4 xv[SK_BATCH];
+    if (NT == 1) {
+      uint4 xv[SK_BATCH];
 #pragma unroll
-    for (int b = 0; b < SK_BATCH; ++b) {
-      const int i = r * SK_BATCH + b;
-      xv[b] = (i < my_steps && g < a.R) ? __ldg(xp + (warp + i * SK_WARPS) * 4) : make_uint4(0, 0, 0, 0);
-    }
+      for (int b = 0; b < SK_BATCH; ++b) {
+        const int i = r * SK_BATCH + b;
+        xv[b] = (i < my_steps && g < a.R) ? __ldg(xp + (warp + i * SK_WARPS) * 4) : make_uint4(0, 0, 0, 0);
+      }
 #pragma unroll
-    for (int b = 0; b < SK_BATCH; ++b) {
-      if (r * SK_BATCH + b < my_steps) {
+      for (int b = 0; b < SK_BATCH; ++b) {
+        if (r * SK_BATCH + b < my_steps) {
 #pragma unroll
-        for (int s = 0; s < NA; ++s) {
-          mma_bf16_16816(acc[s], wl[b][s].x, wh[b][s].x, wl[b][s].y, wh[b][s].y, xv[b].x, xv[b].y);
-          mma_bf16_16816(acc[s], wl[b][s].z, wh[b][s].z, wl[b][s].w, wh[b][s].w, xv[b].z, xv[b].w);
+          for (int s = 0; s < NA; ++s) {
+            mma_bf16_16816(acc[s][0], wl[b][s].x, wh[b][s].x, wl[b][s].y, wh[b][s].y, xv[b].x, xv[b].y);
+            mma_bf16_16816(acc[s][0], wl[b][s].z, wh[b][s].z, wl[b][s].w, wh[b][s].w, xv[b].z, xv[b].w);
+          }
+        }
+      }
+    } else {
+#pragma unroll
+      for (int b = 0; b < SK_BATCH; ++b) {
+        const int i = r * SK_BATCH + b;
+        if (i < my_steps) {
+          constexpr int XT = NT < 4 ? NT : 4;         // row groups whose x is in registers at a time
+#pragma unroll
+          for (int t0 = 0; t0 < NT; t0 += XT) {
+            uint4 xv[XT];
+#pragma unroll
+            for (int t = 0; t < XT; ++t)
+              xv[t] = ((t0 + t) * 8 + g < a.R) ? __ldg(xp + (t0 + t) * x_tile + (warp + i * SK_WARPS) * 4)
+                                               : make_uint4(0, 0, 0, 0);
+#pragma unroll
+            for (int t = 0; t < XT; ++t)
+#pragma unroll
+              for (int s = 0; s < NA; ++s) {
+                mma_bf16_16816(acc[s][t0 + t], wl[b][s].x, wh[b][s].x, wl[b][s].y, wh[b][s].y, xv[t].x, xv[t].y);
+                mma_bf16_16816(acc[s][t0 + t], wl[b][s].z, wh[b][s].z, wl[b][s].w, wh[b][s].w, xv[t].z, xv[t].w);
+              }
+          }
         }
       }
     }
     if (r + 1 < rounds) return;
     // the group is complete: the warps' sums are added in warp order.  The halves of `part` take turns, so one
     // barrier per group is enough: a half is written again only after the barrier of the group in between.
-    float (*p)[NA][32][4] = part[done & 1];
+    PartPtr p = (PartPtr)(part_s + (size_t)(done & 1) * SK_WARPS * NA * NT * 32 * 4);
     ++done;
 #pragma unroll
     for (int s = 0; s < NA; ++s)
 #pragma unroll
-      for (int j = 0; j < 4; ++j) p[warp][s][lane][j] = acc[s][j];
+      for (int t = 0; t < NT; ++t)
+        *(float4*)p[warp][s][t][lane] = make_float4(acc[s][t][0], acc[s][t][1], acc[s][t][2], acc[s][t][3]);
     clear();
     __syncthreads();
-    if (threadIdx.x < 128) {
-      const int l = threadIdx.x / 4, j = threadIdx.x % 4;
+    // accumulator element j of lane l of row group t: feature (l / 4) + 8 * (j / 2), row 8 * t + 2 * (l % 4) + (j % 2)
+    for (int o = threadIdx.x; o < 128 * NT; o += SK_WARPS * 32) {
+      const int t = o / 128, l = (o % 128) / 4, j = o % 4;
       float v[NA];
 #pragma unroll
       for (int s = 0; s < NA; ++s) {
         v[s] = 0.f;
 #pragma unroll
-        for (int wi = 0; wi < SK_WARPS; ++wi) v[s] += p[wi][s][l][j];
+        for (int wi = 0; wi < SK_WARPS; ++wi) v[s] += p[wi][s][t][l][j];
       }
-      // accumulator element j of lane l: feature (l / 4) + 8 * (j / 2), row 2 * (l % 4) + (j % 2)
-      const int feat = n0 + l / 4 + 8 * (j / 2), row = 2 * (l % 4) + (j % 2);
+      const int feat = n0 + l / 4 + 8 * (j / 2), row = 8 * t + 2 * (l % 4) + (j % 2);
       if (feat < a.N && row < a.R) {
-        float o = SWIGLU ? silu_mul(v[0], v[NA - 1]) : v[0];
-        if (!SWIGLU && a.bias) o += ld_dt(a.bias, a.bias_dt, feat);
-        st_dt(a.out, a.out_dt, (size_t)row * a.ldo + feat, o);
+        float out = SWIGLU ? silu_mul(v[0], v[NA - 1]) : v[0];
+        if (!SWIGLU && a.bias) out += ld_dt(a.bias, a.bias_dt, feat);
+        st_dt(a.out, a.out_dt, (size_t)row * a.ldo + feat, out);
       }
     }
   };
@@ -153,9 +188,21 @@ __global__ void __launch_bounds__(SK_WARPS * 32, 1) skinny_kernel(SkArgs a) {
   }
 }
 
+template <bool SWIGLU, int NT>
+cudaError_t launch_skinny(const SkArgs& a, int blocks, cudaStream_t stream) {
+  constexpr size_t smem = (size_t)2 * SK_WARPS * (SWIGLU ? 2 : 1) * NT * 32 * 4 * sizeof(float);
+  static bool attr_done = false;
+  if (!attr_done && smem > 48 * 1024) {
+    const cudaError_t e = cudaFuncSetAttribute(skinny_kernel<SWIGLU, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    attr_done = true;
+  }
+  return launch_dep(skinny_kernel<SWIGLU, NT>, dim3(blocks), dim3(SK_WARPS * 32), smem, stream, a);
+}
+
 }  // namespace
 
-NV_API int nv_skinny_gemm_max_rows() { return SK_MAX_ROWS; }
+NV_API int nv_skinny_gemm_max_rows(int swiglu) { return swiglu ? 8 : SK_MAX_ROWS; }
 
 // Whether the kernel takes these sizes: K a multiple of 32 (a warp's step), rows of x and W 16-byte aligned.
 NV_API int nv_skinny_gemm_usable(int rows, int K, long long ldx, const void* x, const void* w) {
@@ -163,11 +210,11 @@ NV_API int nv_skinny_gemm_usable(int rows, int K, long long ldx, const void* x, 
          !((uintptr_t)w & 15);
 }
 
-// out[r, :] for rows r < R <= 8 of x; W is [N, K], or [2N, K] with swiglu.
+// out[r, :] for rows r < R of x (R <= 32, or 8 with swiglu); W is [N, K], or [2N, K] with swiglu.
 NV_API int nv_skinny_gemm(const void* x, long long ldx, int R, const void* w, int N, int K, const void* bias, int bias_dt,
                           void* out, int out_dt, long long ldo, int swiglu, cudaStream_t stream) {
   if (!dt_ok(out_dt) || (bias && !dt_ok(bias_dt))) return NV_ERR_BAD_DTYPE;
-  if (!nv_skinny_gemm_usable(R, K, ldx, x, w) || N <= 0) return NV_ERR_UNSUPPORTED;
+  if (!nv_skinny_gemm_usable(R, K, ldx, x, w) || N <= 0 || R > nv_skinny_gemm_max_rows(swiglu)) return NV_ERR_UNSUPPORTED;
   if (bias && swiglu) return NV_ERR_BAD_SIZE;
   SkArgs a;
   a.x = (const bf16*)x; a.w = (const bf16*)w; a.bias = bias; a.out = out;
@@ -181,8 +228,11 @@ NV_API int nv_skinny_gemm(const void* x, long long ldx, int R, const void* w, in
       num_sms = 148;
   }
   const int blocks = a.groups_n < num_sms ? a.groups_n : num_sms;   // one block per multiprocessor walks the groups
-  const cudaError_t e = swiglu ? launch_dep(skinny_kernel<true>, dim3(blocks), dim3(SK_WARPS * 32), 0, stream, a)
-                               : launch_dep(skinny_kernel<false>, dim3(blocks), dim3(SK_WARPS * 32), 0, stream, a);
+  cudaError_t e;
+  if (swiglu) e = launch_skinny<true, 1>(a, blocks, stream);
+  else if (R <= 8) e = launch_skinny<false, 1>(a, blocks, stream);
+  else if (R <= 16) e = launch_skinny<false, 2>(a, blocks, stream);
+  else e = launch_skinny<false, 4>(a, blocks, stream);
   NV_RETURN_IF(e);
   NV_RETURN_LAST();
 }

@@ -28,7 +28,7 @@ def linear(ctx, a, w, out_dtype, *, bias=None, a_rows=None, swiglu=False, M=None
     if M == 0:
         return out
     if (ctx.fast_kernels and M <= SKINNY_ROWS and w.numel() * w.element_size() <= SKINNY_MAX_BYTES
-            and ops.skinny_usable(a, w, M)):
+            and ops.skinny_usable(a, w, M, swiglu)):
         # a handful of rows: the product is a stream of w, and the kernel without tiles starts it soonest
         if a_rows is not None:
             a = ops.permute_rows(a, a_rows, M)

@@ -291,11 +291,19 @@ def test_always_on_experts_run_before_the_routing(T, E, K, C):
 # ------------------------------------------------------------------------------- small products, router
 # ------------------------------------------------------------------------------- products of a handful of rows
 @pytest.mark.parametrize("R,N,K", [(1, 5, 32), (1, 6144, 2048), (2, 130, 288), (3, 2048, 1408), (5, 61, 544), (8, 200, 3584),
-                                   (8, 4, 64), (7, 1000, 96), (4, 33, 20480)])
+                                   (8, 4, 64), (7, 1000, 96), (4, 33, 20480), (9, 130, 288), (16, 2048, 2048), (17, 61, 544),
+                                   (31, 6144, 2048), (32, 40, 96), (25, 200, 3584)])
 @pytest.mark.parametrize("swiglu", [False, True])
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 def test_skinny_gemm_dense(R, N, K, swiglu, out_dtype):
     o = ops()
+    if swiglu and R > 8:                                                  # SwiGLU: eight rows at most, refused beyond
+        a = rnd(R, K, dtype=torch.bfloat16, seed=1)
+        w = rnd(2 * N, K, dtype=torch.bfloat16, scale=0.1, seed=2)
+        assert not o.skinny_usable(a, w, R, True)
+        with pytest.raises(o.KernelError):
+            o.skinny_gemm(a, w, torch.empty((R, N), dtype=out_dtype, device=DEV), swiglu=True)
+        return
     a = rnd(R + 2, K, dtype=torch.bfloat16, seed=1)                       # two more rows than are used
     w = rnd(2 * N if swiglu else N, K, dtype=torch.bfloat16, scale=0.1, seed=2)
     bias = None if swiglu else rnd(N, seed=3)
@@ -313,7 +321,8 @@ def test_skinny_gemm_dense(R, N, K, swiglu, out_dtype):
         o.skinny_gemm(a[R - 1:R], w, one, bias=bias, swiglu=swiglu, rows=1)
         assert torch.equal(one[0], out[R - 1])
     # sizes it does not take are refused, not guessed at
-    assert not o.skinny_usable(a[:, :K - 8], w[:, :K - 8].contiguous(), R) and not o.skinny_usable(a, w, 9)
+    assert not o.skinny_usable(a[:, :K - 8], w[:, :K - 8].contiguous(), R) and not o.skinny_usable(a, w, 33)
+    assert not o.skinny_usable(a, w, 9, True)
     with pytest.raises(o.KernelError):
         o.skinny_gemm(a[:, :K - 8].contiguous(), w[:, :K - 8].contiguous(), out, swiglu=swiglu, rows=R)
 
