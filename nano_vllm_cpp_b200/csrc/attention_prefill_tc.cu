@@ -41,6 +41,7 @@ struct PtArgs {
   float scale_log2;         // scale * log2(e)
   int S, max_blocks, window, Hq, Hkv, page;
   int min_rows;             // entries with fewer rows are left to another kernel
+  int first_wave;           // CTAs that start alone on a multiprocessor (their number), before the second ones join them
 };
 
 // 2^x by the special-function unit; exp2(-inf) = 0.
@@ -69,7 +70,17 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
   uint8_t* Ps = Vs + SL * KV_SLAB;                 // [128 rows][64 keys] bf16
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
-  const int h = blockIdx.y, kvh = h / (a.Hq / a.Hkv);
+  // Which (tile, head) is this CTA's.  A causal tile's work grows with its place in the request, and two CTAs share
+  // a multiprocessor: the CTAs that start alone on one (the first `first_wave` in launch order) take the tiles in
+  // descending order of work, later tiles first and the heads of a tile side by side, and the CTAs that join them
+  // take the rest in ascending order, so that a heavy tile shares its multiprocessor with a light one.  (Where a CTA
+  // lands is the hardware's choice; the order only makes the even spread likely.  In launch order, tile by tile from
+  // the heaviest, the 2,048-token prompt's attention took the time of its heaviest pair: 51 us a layer.)
+  const int n_cta = (int)(gridDim.x * gridDim.y), cta = (int)(blockIdx.y * gridDim.x + blockIdx.x);
+  // (more CTAs than fit at once: plain descending order, the heaviest first, is the better schedule then)
+  const int alone = n_cta <= 2 * a.first_wave ? min(n_cta, a.first_wave) : n_cta;
+  const int rank = cta < alone ? cta : n_cta - 1 - (cta - alone);          // 0: the heaviest
+  const int h = rank % a.Hq, kvh = h / (a.Hq / a.Hkv);
 
   if (tid == 0) {
     asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&tm_q) : "memory");
@@ -95,7 +106,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
   grid_dep_wait();              // queries, and this step's keys and values, come from the kernel before
   grid_dep_launch();
   if (tid == 0) {               // which (entry, tile of 128 rows) is this CTA's?  later tiles (more keys) first
-    int left = (int)(gridDim.x - 1 - blockIdx.x), e = 0, found = -1;
+    int left = (int)gridDim.x - 1 - rank / a.Hq, e = 0, found = -1;
     for (; e < a.S; ++e) {
       const int n = a.cu_rows[e + 1] - a.cu_rows[e];
       const int tiles = n >= a.min_rows ? (n + TQ - 1) / TQ : 0;
@@ -364,6 +375,14 @@ NV_API int nv_attention_prefill_tc(const void* qkv, int q_stride, int T, const v
   a.scale_log2 = scale * 1.4426950408889634f;
   a.S = S; a.max_blocks = max_blocks; a.window = window; a.Hq = Hq; a.Hkv = Hkv; a.page = page;
   a.min_rows = min_rows;
+  static int num_sms = 0;
+  if (!num_sms) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || num_sms <= 0)
+      num_sms = 148;
+  }
+  a.first_wave = num_sms;
   const int tiles = (max_tiles + S + 1) / 2;
   if (D == 64) return launch_prefill_tc<64>(a, qkv, q_stride, T, kc, vc, num_pages, tiles, stream);
   return launch_prefill_tc<128>(a, qkv, q_stride, T, kc, vc, num_pages, tiles, stream);
