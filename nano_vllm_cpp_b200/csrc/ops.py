@@ -300,8 +300,14 @@ def rowdot(a, w, out, wide: bool = False) -> None:
     T, K = a.shape
     N = w.shape[0]
     _need(w.shape[1] == K and out.shape == (T, N), "rowdot: shapes")
+    scratch = None
+    if wide:        # a long K is cut into ranges whose sums a second kernel adds
+        lib().nv_rowdot_scratch_floats.restype = c_longlong
+        n = int(lib().nv_rowdot_scratch_floats(c_int(T), c_int(N), c_int(K), c_int(1)))
+        if n:
+            scratch = torch.empty(n, dtype=torch.float32, device=a.device)
     _check(lib().nv_rowdot(_p(a), c_longlong(a.stride(0)), _p(w), c_int(dt(w)), _p(out), c_longlong(out.stride(0)),
-                           c_int(T), c_int(N), c_int(K), c_int(1 if wide else 0), _stream()), "rowdot")
+                           c_int(T), c_int(N), c_int(K), c_int(1 if wide else 0), _p(scratch), _stream()), "rowdot")
 
 
 def attention_decode_usable(k_cache, D: int) -> bool:

@@ -66,19 +66,37 @@ __global__ void __launch_bounds__(256) rowdot_kernel(const float* __restrict__ a
 }
 
 // The same product for many rows: one block keeps WT rows in shared memory and its 8 warps walk the outputs
-// four at a time, each warp summing all of k itself for the WT rows at once, so a weight row is read once per
+// four at a time, each warp summing its k for the WT rows at once, so a weight row is read once per
 // WT rows.  Fewer, fatter blocks and a fraction of the loads; the order of the sum differs from
 // rowdot_kernel's, so a run uses one of the two for a given op and batch shape only where rounding-level
 // differences between batch shapes are accepted (bfloat16 runs).
+// A warp's walk along k is a chain of trips to L2 for the weights, one per 128 elements, so a long K is cut into
+// ranges of ROWDOT_K_RANGE elements (blockIdx.y): every range is a block of its own, writes its sums to part[range],
+// and rowdot_finish_kernel adds the ranges in order.  The cut depends on K alone, so a row's value does not depend
+// on the batch.  Measured for 2,048 rows: K = 3,584 and 65 outputs, 147 us in one range (84 trips one after the
+// other) and 72 us in seven; K = 2,048 and 61 outputs, 31 us in one range and 40 us in four (the second kernel and
+// the blocks' set-up cost more than the shorter chain gains): K is cut from ROWDOT_CUT_FROM elements on.
+constexpr int ROWDOT_K_RANGE = 512;
+constexpr int ROWDOT_CUT_FROM = 3072;
 template <typename TW, int WT>
 __global__ void __launch_bounds__(256) rowdot_wide_kernel(const float* __restrict__ a, long long lda,
                                                           const TW* __restrict__ w, float* __restrict__ out,
-                                                          long long ldo, int T, int N, int K) {
+                                                          long long ldo, int T, int N, int K_all,
+                                                          float* __restrict__ part) {
   extern __shared__ float row_s[];                 // [WT][K]
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const int t0 = blockIdx.x * WT;
   const int nt = min(WT, T - t0);
-  if (K % 4 == 0 && lda % 4 == 0 && ((uintptr_t)a & 15) == 0) {
+  // this block's range of k; from here on a, w and K are the range's
+  const int kb = gridDim.y > 1 ? (int)blockIdx.y * ROWDOT_K_RANGE : 0;
+  const int K = gridDim.y > 1 ? min(ROWDOT_K_RANGE, K_all - kb) : K_all;
+  a += kb;
+  w += kb;
+  if (gridDim.y > 1) {
+    out = part + (size_t)blockIdx.y * T * N;
+    ldo = N;
+  }
+  if (K_all % 4 == 0 && lda % 4 == 0 && ((uintptr_t)a & 15) == 0) {
     // 16-byte loads, four in flight per thread: one scalar load at a time made this copy the kernel's time
     // (the rows of the tile are walked as one run of WT * K / 4 loads, eight in flight per thread: row by row a
     // thread had only K / 1024 loads under way at a time)
@@ -104,14 +122,14 @@ __global__ void __launch_bounds__(256) rowdot_wide_kernel(const float* __restric
     }
   }
   __syncthreads();
-  const bool vec = K % 4 == 0 && ((uintptr_t)w & 15) == 0;
+  const bool vec = K_all % 4 == 0 && ((uintptr_t)w & 15) == 0;
   for (int n0 = warp * 4; n0 < N; n0 += 32) {
     float s[WT][4];
 #pragma unroll
     for (int r = 0; r < WT; ++r) s[r][0] = s[r][1] = s[r][2] = s[r][3] = 0.f;
     const TW* wr[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) wr[i] = w + (size_t)min(n0 + i, N - 1) * K;
+    for (int i = 0; i < 4; ++i) wr[i] = w + (size_t)min(n0 + i, N - 1) * K_all;
     if (vec) {
       // (few rows per block: unrolled, so that a warp has the weight loads of several steps under way; with four or
       // eight rows the accumulators leave no registers for that and the unrolled loop was slower)
@@ -157,6 +175,18 @@ __global__ void __launch_bounds__(256) rowdot_wide_kernel(const float* __restric
         if (lane == 0 && r < nt && n0 + i < N) out[(size_t)(t0 + r) * ldo + n0 + i] = v;
       }
   }
+}
+
+// out[t, n] = part[0][t][n] + part[1][t][n] + ... in that order.
+__global__ void rowdot_finish_kernel(const float* __restrict__ part, int ranges, float* __restrict__ out, long long ldo,
+                                     int T, int N) {
+  grid_dep_wait();
+  grid_dep_launch();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)T * N) return;
+  float v = 0.f;
+  for (int r = 0; r < ranges; ++r) v += part[(size_t)r * T * N + i];
+  out[(i / N) * ldo + i % N] = v;
 }
 
 // Routing of a small batch in one launch: top-k of every row, the expert permutation, and the
@@ -206,19 +236,28 @@ __global__ void __launch_bounds__(1024) moe_route_small_kernel(
 
 }  // namespace
 
+// Floats of scratch that the many-rows kernel needs for its ranges of k (0: it does not cut K).
+NV_API long long nv_rowdot_scratch_floats(int T, int N, int K, int wide) {
+  if (!wide || K < ROWDOT_CUT_FROM) return 0;
+  return (long long)((K + ROWDOT_K_RANGE - 1) / ROWDOT_K_RANGE) * T * N;
+}
+
 NV_API int nv_rowdot(const float* a, long long lda, const void* w, int w_dt, float* out, long long ldo, int T,
-                     int N, int K, int wide, cudaStream_t s) {
+                     int N, int K, int wide, float* scratch, cudaStream_t s) {
   if (!dt_ok(w_dt)) return NV_ERR_BAD_DTYPE;
   if (T == 0 || N == 0) return NV_OK;
-  // many rows: WT of them per block in shared memory.  Every block reads the whole matrix (from L2), so fat blocks
-  // save traffic, but a block's eight warps each walk all of k alone, so there must be blocks enough to hide that:
-  // WT = T / 256 (1, 2, 4 or 8), i.e. 256 blocks or more.  (Measured at 256 rows, 61 outputs, K = 2,048: 60 us with
+  // many rows: WT of them per block in shared memory.  Every block reads the matrix's columns of its range of k (from
+  // L2), so fat blocks save traffic, but there must be blocks enough to hide a warp's chain of loads: WT = T / 256
+  // (1, 2, 4 or 8), i.e. 256 blocks or more per range.  (Measured at 256 rows, 61 outputs, K = 2,048: 60 us with
   // 64 blocks of four rows.)  A row's sum does not depend on WT.
   if (wide) {
+    const int ranges = scratch && K >= ROWDOT_CUT_FROM ? (K + ROWDOT_K_RANGE - 1) / ROWDOT_K_RANGE : 1;
+    if (ranges > 1 && nv_rowdot_scratch_floats(T, N, K, 1) == 0) return NV_ERR_BAD_SIZE;
+    const int k_block = ranges > 1 ? ROWDOT_K_RANGE : K;
     int wt = 8;
-    while (wt > 1 && (T < 256 * wt || (size_t)wt * K * 4 > 96 * 1024)) wt >>= 1;
-    const size_t smem = (size_t)wt * K * 4;
-    if (smem <= 96 * 1024) {
+    while (wt > 1 && (T < 256 * wt || (size_t)wt * k_block * 4 > 96 * 1024)) wt >>= 1;
+    const size_t smem = (size_t)wt * k_block * 4;
+    if (smem <= 96 * 1024 && ranges <= 65535) {
       static bool attr_done = false;
       if (!attr_done) {
         const void* fns[8] = {(const void*)rowdot_wide_kernel<float, 1>, (const void*)rowdot_wide_kernel<bf16, 1>,
@@ -231,16 +270,24 @@ NV_API int nv_rowdot(const float* a, long long lda, const void* w, int w_dt, flo
         }
         attr_done = true;
       }
-      const unsigned blocks = (unsigned)((T + wt - 1) / wt);
+      const dim3 blocks((unsigned)((T + wt - 1) / wt), (unsigned)ranges);
       const bool f32 = w_dt == NV_DT_F32;
-#define NV_ROWDOT_WIDE(WT)                                                                                          \
-  if (f32) rowdot_wide_kernel<float, WT><<<blocks, 256, smem, s>>>(a, lda, (const float*)w, out, ldo, T, N, K);     \
-  else rowdot_wide_kernel<bf16, WT><<<blocks, 256, smem, s>>>(a, lda, (const bf16*)w, out, ldo, T, N, K)
+#define NV_ROWDOT_WIDE(WT)                                                                                           \
+  if (f32)                                                                                                           \
+    rowdot_wide_kernel<float, WT><<<blocks, 256, smem, s>>>(a, lda, (const float*)w, out, ldo, T, N, K, scratch);   \
+  else                                                                                                               \
+    rowdot_wide_kernel<bf16, WT><<<blocks, 256, smem, s>>>(a, lda, (const bf16*)w, out, ldo, T, N, K, scratch)
       if (wt == 8) { NV_ROWDOT_WIDE(8); }
       else if (wt == 4) { NV_ROWDOT_WIDE(4); }
       else if (wt == 2) { NV_ROWDOT_WIDE(2); }
       else { NV_ROWDOT_WIDE(1); }
 #undef NV_ROWDOT_WIDE
+      NV_RETURN_IF(cudaGetLastError());
+      if (ranges > 1) {
+        const long long outputs = (long long)T * N;
+        NV_RETURN_IF(launch_dep(rowdot_finish_kernel, dim3((unsigned)((outputs + 255) / 256)), dim3(256), 0, s,
+                                (const float*)scratch, ranges, out, ldo, T, N));
+      }
       NV_RETURN_LAST();
     }
   }

@@ -328,7 +328,7 @@ def test_skinny_gemm_dense(R, N, K, swiglu, out_dtype):
 
 
 @pytest.mark.parametrize("T,N,K", [(1, 1, 64), (8, 60, 2048), (33, 7, 100), (5, 64, 3000), (1030, 61, 520), (1025, 9, 2050),
-                                   (300, 61, 2048), (600, 61, 1032), (2100, 5, 264)])
+                                   (300, 61, 2048), (600, 61, 1032), (2100, 5, 264), (520, 65, 3584), (9, 3, 3076)])
 @pytest.mark.parametrize("tw", [torch.float32, torch.bfloat16])
 def test_rowdot(T, N, K, tw):
     o = ops()
