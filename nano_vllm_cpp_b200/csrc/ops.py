@@ -374,15 +374,26 @@ def gemm_plain_tile_m() -> int:
 
 
 def rope_store(qkv, positions, inv_freq, rotary_dim: int, k_cache, v_cache, block_table, row_entry,
-               Hq: int, Hkv: int, D: int, write_kv: bool, err: ErrorFlag) -> None:
-    _cuda_contig(qkv, positions, inv_freq, k_cache, v_cache, block_table, row_entry)
-    _i32(positions, block_table, row_entry)
+               Hq: int, Hkv: int, D: int, write_kv: bool, err: ErrorFlag, rot_positions=None, pair_axis=None) -> None:
+    """Turns q and k by their positions and writes k and v to their pages.  ``positions`` [T] are the rows' places
+    in their sequences (they pick the cache slot, and the angle unless ``rot_positions`` is given).
+    ``rot_positions`` [T] or [T, axes] int32: the coordinates that the pairs are turned by instead, and
+    ``pair_axis`` [rotary_dim / 2] int32: which coordinate turns which pair (None: the first)."""
+    _cuda_contig(qkv, positions, inv_freq, k_cache, v_cache, block_table, row_entry, rot_positions, pair_axis)
+    _i32(positions, block_table, row_entry, rot_positions, pair_axis)
     T = qkv.shape[0]
+    axes = 0
+    if rot_positions is not None:
+        axes = 1 if rot_positions.dim() == 1 else rot_positions.shape[1]
+        _need(rot_positions.shape[0] == T and axes >= 1, "rope_store: one row of coordinates per row")
+    _need(pair_axis is None or (rot_positions is not None and pair_axis.numel() >= rotary_dim // 2),
+          "rope_store: pair_axis needs rot_positions and one entry per pair")
     _need(qkv.shape[1] == (Hq + 2 * Hkv) * D, "rope_store: qkv width")
     _need(inv_freq.dtype == torch.float32 and inv_freq.numel() >= rotary_dim // 2, "rope_store: inv_freq")
     page = k_cache.shape[2]
     _need(k_cache.shape[1:] == (Hkv, page, D) and v_cache.shape == k_cache.shape, "rope_store: cache shape")
-    _check(lib().nv_rope_store(_p(qkv), c_int(dt(qkv)), _p(positions), _p(inv_freq), c_int(rotary_dim),
+    _check(lib().nv_rope_store(_p(qkv), c_int(dt(qkv)), _p(positions), _p(rot_positions), c_int(axes), _p(pair_axis),
+                               _p(inv_freq), c_int(rotary_dim),
                                _p(k_cache), _p(v_cache), c_int(dt(k_cache)), _p(block_table),
                                c_int(block_table.shape[1]), _p(row_entry), c_int(T), c_int(Hq), c_int(Hkv),
                                c_int(D), c_int(page), c_int(1 if write_kv else 0), _p(err.t), _stream()),

@@ -203,8 +203,12 @@ __global__ void __launch_bounds__(NORM_THREADS) add_rmsnorm_kernel(NormArgs a) {
 // (src/hip_ops.hip:431-450).  q is rotated in place; k is rotated and written to its page; v is
 // copied to its page (src/hip_ops.hip:452-466).  
 // Cache layout: [page][kv head][slot in page][D].
+// The position that turns pair d need not be the row's place in its sequence: rot_pos is [T][axes] (the row's
+// coordinates, e.g. a place in the text and a row and a column of an image) and pair_axis[d] says which of them pair
+// d is turned by (nullptr: the first).  The cache slot always comes from `positions`, the place in the sequence.
 // One block per (row, group of `hpb` heads in the order q.., k.., v..): the angles are taken once per block.
 __global__ void __launch_bounds__(256) rope_store_kernel(void* __restrict__ qkv, int dt, const int* __restrict__ positions,
+                                  const int* __restrict__ rot_pos, int axes, const int* __restrict__ pair_axis,
                                   const float* __restrict__ inv_freq, int rotary_dim,
                                   void* __restrict__ kc, void* __restrict__ vc, int cache_dt,
                                   const int* __restrict__ block_table, int max_blocks,
@@ -222,7 +226,8 @@ __global__ void __launch_bounds__(256) rope_store_kernel(void* __restrict__ qkv,
   const int half = rotary_dim / 2;
   if (h_begin < Hq + Hkv)
     for (int f = threadIdx.x; f < half; f += blockDim.x) {
-      float ang = (float)pos * inv_freq[f];
+      const int pf = rot_pos ? rot_pos[(size_t)t * axes + (pair_axis ? pair_axis[f] : 0)] : pos;
+      float ang = (float)pf * inv_freq[f];
       cs[f] = cosf(ang);
       sn[f] = sinf(ang);
     }
@@ -571,20 +576,25 @@ NV_API int nv_add_rmsnorm(float* x, const float* branch, const void* w, int w_dt
   NV_RETURN_LAST();
 }
 
-NV_API int nv_rope_store(void* qkv, int dt, const int* positions, const float* inv_freq, int rotary_dim,
+// rot_pos [T][axes] and pair_axis [rotary_dim / 2] (entries in [0, axes)) may be nullptr: every pair is then turned
+// by `positions`.
+NV_API int nv_rope_store(void* qkv, int dt, const int* positions, const int* rot_pos, int axes, const int* pair_axis,
+                         const float* inv_freq, int rotary_dim,
                          void* kc, void* vc, int cache_dt, const int* block_table, int max_blocks,
                          const int* row_entry, int T, int Hq, int Hkv, int D, int page, int write_kv, int* err,
                          cudaStream_t s) {
   if (!dt_ok(dt) || !dt_ok(cache_dt)) return NV_ERR_BAD_DTYPE;
   if (rotary_dim < 0 || rotary_dim > D || rotary_dim % 2) return NV_ERR_BAD_SIZE;
+  if (rot_pos && axes < 1) return NV_ERR_BAD_SIZE;
+  if (!rot_pos && pair_axis) return NV_ERR_BAD_SIZE;
   if (T == 0) return NV_OK;
   if (D > 256 || D % 2) return NV_ERR_UNSUPPORTED;
   // few rows: many small blocks (latency); many rows: one block per row does all heads (the angles once)
   const int heads = Hq + 2 * Hkv;
   const int hpb = T >= 256 ? heads : 4;
   dim3 grid(T, (heads + hpb - 1) / hpb);
-  NV_RETURN_IF(launch_dep(rope_store_kernel, grid, dim3(T >= 256 ? 256 : 128), 0, s, qkv, dt, positions, inv_freq,
-                          rotary_dim, kc, vc, cache_dt, block_table, max_blocks, row_entry, Hq, Hkv, D, page, write_kv,
+  NV_RETURN_IF(launch_dep(rope_store_kernel, grid, dim3(T >= 256 ? 256 : 128), 0, s, qkv, dt, positions, rot_pos, axes,
+                          pair_axis, inv_freq, rotary_dim, kc, vc, cache_dt, block_table, max_blocks, row_entry, Hq, Hkv, D, page, write_kv,
                           hpb, err));
   NV_RETURN_LAST();
 }

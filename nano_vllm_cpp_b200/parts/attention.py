@@ -65,7 +65,8 @@ class PagedAttention(Mixer):
         qkv = linear(ctx, h, self.qkv_weight, ctx.act_dtype, bias=self.qkv_bias)
         bt = batch.block_tables[cache.group]
         ops.rope_store(qkv, batch.positions, self.position.inv_freq(), self.position.rotary_dim, cache.k, cache.v,
-                       bt, batch.row_entry, self.Hq, self.Hkv, self.D, cache.write, ctx.err)
+                       bt, batch.row_entry, self.Hq, self.Hkv, self.D, cache.write, ctx.err,
+                       rot_positions=self.position.rotation_positions(batch), pair_axis=self.position.pair_axis())
         att = torch.empty((T, self.Hq * self.D), dtype=ctx.act_dtype, device=h.device)
         self._attend(qkv, cache, bt, batch, att)
         return linear(ctx, att, self.o_weight, torch.float32)

@@ -120,10 +120,20 @@ def resolve_branch(norm: Norm, branch):
 
 
 class PositionEncoding(Part):
+    """What the rotation kernel needs: ``rotary_dim`` (the first so many elements of a head are turned, in pairs
+    ``(d, d + rotary_dim / 2)``), ``inv_freq()`` (float32 [rotary_dim / 2]) and, for encodings whose pairs are not
+    all turned by the row's place in its sequence, ``rotation_positions(batch)`` (int32 [T] or [T, axes]: the rows'
+    coordinates) with ``pair_axis()`` (int32 [rotary_dim / 2]: which coordinate turns which pair)."""
     rotary_dim: int = 0
 
     def inv_freq(self):
         raise NotImplementedError
+
+    def rotation_positions(self, batch):
+        return None                 # the rows' places in their sequences (batch.positions)
+
+    def pair_axis(self):
+        return None                 # every pair is turned by the first (or only) coordinate
 
 
 class Mixer(Part):

@@ -577,6 +577,49 @@ def test_rope_store(Hq, Hkv, D, rot, dtype):
         err.check("rope")
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rope_store_with_coordinates_per_pair(dtype):
+    """Pairs turned by other numbers than the row's place in its sequence: every row has three coordinates and every
+    pair names the one it is turned by; the cache slot still comes from the place in the sequence."""
+    o = ops()
+    Hq, Hkv, D, rot, page, T = 3, 1, 32, 24, 16, 5
+    positions = [0, 3, 17, 40, 41]
+    coords = torch.tensor([[0, 0, 0], [3, 1, 2], [17, 5, 0], [9, 7, 7], [40, 2, 300]], dtype=torch.int32)
+    axis = torch.tensor([0, 0, 1, 2, 1, 2, 0, 1, 2, 2, 1, 0], dtype=torch.int32)          # rot / 2 = 12 pairs
+    qkv = rnd(T, (Hq + 2 * Hkv) * D, dtype=dtype)
+    orig = qkv.clone()
+    inv = torch.tensor([1.0 / (50.0 ** (2.0 * i / rot)) for i in range(rot // 2)], dtype=torch.float64).float().to(DEV)
+    n_pages = 4
+    kc = torch.zeros(n_pages, Hkv, page, D, dtype=dtype, device=DEV)
+    vc = torch.zeros_like(kc)
+    bt = torch.tensor([[2, 0, 3, 1]], dtype=torch.int32, device=DEV)
+    ent = torch.zeros(T, dtype=torch.int32, device=DEV)
+    err = o.ErrorFlag(DEV)
+    o.rope_store(qkv, torch.tensor(positions, dtype=torch.int32, device=DEV), inv, rot, kc, vc, bt, ent, Hq, Hkv, D,
+                 True, err, rot_positions=coords.to(DEV), pair_axis=axis.to(DEV))
+    err.check("rope")
+    tol = 3e-6 if dtype == torch.float32 else 2 ** -8
+    for i, p in enumerate(positions):
+        heads = orig[i].reshape(Hq + 2 * Hkv, D).cpu().double()
+        ang = (coords[i][axis.long()].float() * inv.cpu()).double()
+        c, sn = torch.cos(ang), torch.sin(ang)
+        x1, x2 = heads[:, :rot // 2], heads[:, rot // 2:rot]
+        want = torch.cat([x1 * c - x2 * sn, x2 * c + x1 * sn, heads[:, rot:]], -1)
+        close(qkv[i, :Hq * D].reshape(Hq, D), want[:Hq], tol, "q")
+        page_id = int(bt[0, p // page])
+        close(kc[page_id, :, p % page], want[Hq:Hq + Hkv], tol, "k")
+        assert torch.equal(vc[page_id, :, p % page].cpu().double(), heads[Hq + Hkv:])
+    # one coordinate per row and no table of axes: the same as positions of their own
+    a, b = orig.clone(), orig.clone()
+    other = torch.tensor([7, 7, 0, 100, 3], dtype=torch.int32, device=DEV)
+    o.rope_store(a, torch.tensor(positions, dtype=torch.int32, device=DEV), inv, rot, kc, vc, bt, ent, Hq, Hkv, D,
+                 False, err, rot_positions=other)
+    o.rope_store(b, other, inv, rot, kc, vc, bt, ent, Hq, Hkv, D, False, err)
+    assert torch.equal(a, b)
+    with pytest.raises(o.KernelError):
+        o.rope_store(a, other, inv, rot, kc, vc, bt, ent, Hq, Hkv, D, False, err, pair_axis=axis.to(DEV))
+
+
 @pytest.mark.parametrize("D,window,ctx,new", [(128, 0, 0, 1100), (64, 300, 500, 700), (128, 0, 16000, 900), (128, 5000, 0, 17000)])
 def test_attention_prefill_tc_long(D, window, ctx, new):
     """Long portions on the tcgen05 kernel against the mma.sync kernel on the same cache: many row tiles, a

@@ -603,6 +603,107 @@ def test_toy_position_encoding_and_routing_feed_forward(tmp_path):
         helpers.assert_close(got, want, "float32", f"toy switch request {r}")
 
 
+# ------------------------------------------------------------------------------- a position encoding with two coordinates
+def define_toy_grid_position():
+    """A position encoding that turns half of its pairs by the row's place in the sequence and the other half by a
+    second coordinate of the row (here the place divided by four, as if the tokens were laid out in rows of four):
+    it gives the rotation kernel the coordinates of every row and says which pair follows which."""
+    from nano_vllm_cpp_b200.parts import PositionEncoding, PartSpec, LayerSpec, ModelSpec, register_part
+    from nano_vllm_cpp_b200.config import register_architecture
+
+    class GridRotary(PositionEncoding):
+        def __init__(self, rotary_dim, theta):
+            self.rotary_dim, self.theta = rotary_dim, theta
+
+        def load(self, fetch, ctx):
+            half = self.rotary_dim // 2
+            inv = [1.0 / (self.theta ** ((2.0 * (i % (half // 2))) / half)) for i in range(half)]
+            self._inv = torch.tensor(inv, dtype=torch.float64).float().to(ctx.device)
+            self._axis = torch.tensor([i // (half // 2) for i in range(half)], dtype=torch.int32, device=ctx.device)
+
+        def inv_freq(self):
+            return self._inv
+
+        def rotation_positions(self, batch):
+            pos = batch.positions
+            return torch.stack([pos, pos // 4], dim=1).contiguous()
+
+        def pair_axis(self):
+            return self._axis
+
+    register_part("position", "toy_grid_rotary", GridRotary)
+
+    def build(cfg):
+        H = cfg["hidden_size"]
+        norm = PartSpec("rmsnorm", dict(size=H, eps=cfg["rms_norm_eps"]))
+        att = PartSpec("paged_attention", dict(
+            hidden_size=H, num_heads=cfg["num_heads"], num_kv_heads=cfg["num_kv_heads"], head_dim=cfg["head_dim"],
+            bias=False, position=PartSpec("toy_grid_rotary", dict(rotary_dim=cfg["head_dim"], theta=cfg["theta"]))))
+        mlp = PartSpec("dense_swiglu", dict(hidden_size=H, intermediate_size=cfg["intermediate_size"]))
+        layers = [LayerSpec(norm1=norm, mixer=att, norm2=norm, feed_forward=mlp) for _ in range(2)]
+        return ModelSpec(vocab_size=cfg["vocab_size"], hidden_size=H, layers=layers, final_norm=norm,
+                         tie_word_embeddings=True, init_std=0.1)
+
+    register_architecture("ToyGridForCausalLM", dict, build)
+
+
+def toy_grid_plain(cfg, W, ids):
+    T, Hq, Hkv, D = len(ids), cfg["num_heads"], cfg["num_kv_heads"], cfg["head_dim"]
+    half = D // 2
+    inv = torch.tensor([1.0 / (cfg["theta"] ** ((2.0 * (i % (half // 2))) / half)) for i in range(half)],
+                       dtype=torch.float64).float().double()
+    pos = torch.arange(T)
+    coord = torch.stack([pos, pos // 4], 1)
+    axis = torch.tensor([i // (half // 2) for i in range(half)])
+    ang = (coord[:, axis].float() * inv.float()).double()                     # [T, half], the product in float32
+    c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+
+    def turn(x):                                                              # [T, heads, D]
+        x1, x2 = x[..., :half], x[..., half:]
+        return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], -1)
+
+    x = pm.embedding(W["model.embed_tokens.weight"], ids)
+    for l in range(2):
+        p = f"model.layers.{l}."
+        h = pm.rms_norm(x, W[p + "input_layernorm.weight"], cfg["rms_norm_eps"])
+        q, k, v = (h @ W[p + f"self_attn.{n}_proj.weight"].double().T for n in "qkv")
+        q, k, v = turn(q.reshape(T, Hq, D)), turn(k.reshape(T, Hkv, D)), v.reshape(T, Hkv, D)
+        out = torch.zeros(T, Hq, D, dtype=torch.float64)
+        for hh in range(Hq):
+            sc = (q[:, hh] @ k[:, hh // (Hq // Hkv)].T) / (D ** 0.5)
+            sc = sc.masked_fill(torch.triu(torch.ones(T, T, dtype=torch.bool), 1), float("-inf"))
+            out[:, hh] = torch.softmax(sc, -1) @ v[:, hh // (Hq // Hkv)]
+        x = x + out.reshape(T, Hq * D) @ W[p + "self_attn.o_proj.weight"].double().T
+        h = pm.rms_norm(x, W[p + "post_attention_layernorm.weight"], cfg["rms_norm_eps"])
+        x = x + pm.dense_mlp(h, W, p + "mlp.")
+    return pm.rms_norm(x, W["model.norm.weight"], cfg["rms_norm_eps"]) @ W["model.embed_tokens.weight"].double().T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_position_encoding_with_two_coordinates(dtype, tmp_path):
+    """A position encoding whose pairs follow two different coordinates of a row, registered from outside the
+    package: the model is built, loaded and stepped whole, in portions and one by one, also in a captured step."""
+    from nano_vllm_cpp_b200.weights import write_model_folder
+    from nano_vllm_cpp_b200.engine.runner import ModelRunner
+    define_toy_grid_position()
+    cfg = dict(architectures=["ToyGridForCausalLM"], vocab_size=80, hidden_size=48, num_heads=4, num_kv_heads=2,
+               head_dim=16, intermediate_size=40, rms_norm_eps=1e-5, theta=100.0)
+    mdir = write_model_folder(cfg, str(tmp_path / "grid"), seed=11, norm_std=0.1, dtype="bfloat16")
+    _, W = pm.read_folder(mdir)
+    runner = ModelRunner(mdir, dtype=dtype, max_tokens=128, max_requests=2)
+    ids = [int(t) for t in np.random.RandomState(2).randint(0, 80, size=37)]
+    want = toy_grid_plain(cfg, W, ids)
+    rp = helpers.Replay(runner)
+    rp.step([("w", ids, True)], end=["w"])
+    rp.step([("c", ids[:9], True)])
+    rp.step([("c", ids[9:22], True)])
+    for t in range(22, 37):
+        rp.step([("c", ids[t:t + 1], True)])
+    for r in ("w", "c"):
+        got = torch.stack([rp.logits[(r, p)] for p in range(len(ids))])
+        helpers.assert_close(got, want, dtype, f"toy grid position, request {r}")
+
+
 # ------------------------------------------------------------------------------- toy arrangements
 def define_toy_arrangements():
     """Two arrangements that the package does not have: a parallel block (one norm feeds the mixer and the
