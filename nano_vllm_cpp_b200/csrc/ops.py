@@ -480,10 +480,12 @@ class MoeAlignment:
         return self.primary
 
 
-def moe_align(idx, K: int, al: MoeAlignment, err: ErrorFlag, spread_last: int = 0, static_last: int = 0) -> None:
+def moe_align(idx, K: int, al: MoeAlignment, err: ErrorFlag, spread_last: int = 0, static_last: int = 0,
+              zero=None) -> None:
     """``spread_last``: the tiles of the last so many experts (ones that every row visits) are spread evenly through
     the tile lists instead of standing at their end.  ``static_last`` instead: those experts' pairs sit in row order
-    at the end of the permutation and get no tiles (``StaticTiles`` lists them; they can run before the routing)."""
+    at the end of the permutation and get no tiles (``StaticTiles`` lists them; they can run before the routing).
+    ``zero``: a few int32 that the kernel also sets to 0 (the tile counters of the products that follow it)."""
     _cuda_contig(idx)
     _i32(idx)
     T = idx.numel() // K
@@ -494,7 +496,7 @@ def moe_align(idx, K: int, al: MoeAlignment, err: ErrorFlag, spread_last: int = 
                               _p(al.tile_expert), _p(al.tile_row0), _p(al.tile_rows), _p(al.num_tiles), _p(err.t),
                               c_int(s2.tile_m if s2 else 0), _p(s2.tile_expert if s2 else None), _p(s2.tile_row0 if s2 else None),
                               _p(s2.tile_rows if s2 else None), _p(s2.num_tiles if s2 else None), c_int(spread_last),
-                              c_int(static_last), _stream()),
+                              c_int(static_last), _p(zero), c_int(zero.numel() if zero is not None else 0), _stream()),
            "moe_align")
 
 

@@ -422,8 +422,10 @@ __global__ void __launch_bounds__(1024) moe_align_kernel(const int* __restrict__
                                                          int* __restrict__ err, int tile_m2,
                                                          int* __restrict__ t2_expert, int* __restrict__ t2_row0,
                                                          int* __restrict__ t2_rows, int* __restrict__ num_tiles2,
-                                                         int n_spread, int n_static) {
+                                                         int n_spread, int n_static, int* __restrict__ zero,
+                                                         int n_zero) {
   extern __shared__ int al_s[];
+  if ((int)threadIdx.x < n_zero) zero[threadIdx.x] = 0;      // (tile counters of the products that follow)
   align_block(idx, TK, K, E, tile_m, counts, offsets, sorted_token, pair_pos, tile_expert, tile_row0, tile_rows,
               num_tiles, err, al_s, tile_m2, t2_expert, t2_row0, t2_rows, num_tiles2, n_static, n_spread);
 }
@@ -628,14 +630,15 @@ NV_API int nv_router_topk(const float* logits, long long ld, int T, int E, int K
 NV_API int nv_moe_align(const int* idx, int T, int K, int E, int tile_m, int* counts, int* offsets,
                         int* sorted_token, int* pair_pos, int* tile_expert, int* tile_row0, int* tile_rows,
                         int* num_tiles, int* err, int tile_m2, int* t2_expert, int* t2_row0, int* t2_rows,
-                        int* num_tiles2, int n_spread, int n_static, cudaStream_t s) {
+                        int* num_tiles2, int n_spread, int n_static, int* zero, int n_zero, cudaStream_t s) {
   if (tile_m <= 0 || K <= 0 || E <= 0 || tile_m2 < 0 || n_spread < 0 || n_spread > E) return NV_ERR_BAD_SIZE;
+  if (n_zero < 0 || n_zero > 1024 || (n_zero && !zero)) return NV_ERR_BAD_SIZE;
   if (n_static < 0 || n_static > E || (n_static && n_spread)) return NV_ERR_BAD_SIZE;
   if (E > 3000) return NV_ERR_UNSUPPORTED;   // four int arrays of E in shared memory
   moe_align_kernel<<<1, 1024, 4 * E * sizeof(int), s>>>(idx, T * K, K, E, tile_m, counts, offsets, sorted_token,
                                                         pair_pos, tile_expert, tile_row0, tile_rows, num_tiles, err,
                                                         tile_m2, t2_expert, t2_row0, t2_rows, num_tiles2, n_spread,
-                                                        n_static);
+                                                        n_static, zero, n_zero);
   NV_RETURN_LAST();
 }
 

@@ -225,21 +225,19 @@ class SparseMoeSwiGLU(FeedForward):
                                   x_rows=st.x_rows, max_ctas=cap)
             ops.gemm_fast_grouped(act, self.w_down, y, al, err=ctx.err, tiles=st, tiles_ready=True, max_ctas=cap)
             join.record(side)
-        if many:
-            ops.router_topk(logits, K, self.renorm, idx, score, C, gate_logit)
-            ops.moe_align(idx, KT, al, ctx.err, static_last=C)
-        else:
-            ops.moe_route_small(logits, K, self.renorm, C, gate_logit, idx, score, al, ctx.err, x=None, static=True)
-        self.last_alignment = al
         # (a prompt's routed products start while the side products still hold most multiprocessors: their CTAs take
-        # tiles from a counter, so the ones that start early do more of the work)
+        # tiles from a counter, so the ones that start early do more of the work.  A product sets its counter back
+        # itself; one that gave up on a wait may not have, so the permutation kernel zeroes both.)
         c0 = c1 = None
         if many:
             if self._counters is None:
                 self._counters = torch.zeros(2, dtype=torch.int32, device=dev)
-            else:       # (a product sets its counter back itself; one that gave up on a wait may not have)
-                self._counters.zero_()
             c0, c1 = self._counters[0:1], self._counters[1:2]
+            ops.router_topk(logits, K, self.renorm, idx, score, C, gate_logit)
+            ops.moe_align(idx, KT, al, ctx.err, static_last=C, zero=self._counters)
+        else:
+            ops.moe_route_small(logits, K, self.renorm, C, gate_logit, idx, score, al, ctx.err, x=None, static=True)
+        self.last_alignment = al
         x_sorted = ops.permute_rows(h, al.sorted_token, T * K)
         ops.gemm_fast_grouped(x_sorted, self.w_gate_up, act, al, swiglu=True, err=ctx.err, tiles_ready=True, counter=c0)
         ops.gemm_fast_grouped(act, self.w_down, y, al, err=ctx.err, tiles_ready=True, counter=c1)
