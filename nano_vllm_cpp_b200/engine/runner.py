@@ -29,6 +29,14 @@ class StepError(RuntimeError):
     pass
 
 
+# Steps of up to this many tokens may be captured as CUDA graphs: the host needs several milliseconds to launch a
+# step's four hundred kernels one by one, which is longer than the GPU takes for a step of a few hundred tokens.
+# A larger step keeps the GPU busy for longer than its launches take.
+GRAPH_MAX_TOKENS = 1024
+MAX_GRAPHS = 48             # captured steps kept; further shapes run launch by launch
+GRAPH_MAX_LOGIT_BYTES = 64 << 20
+
+
 class _Prepared:
     """What is left of a step's preparation when nobody needs its arrays on the host side."""
     __slots__ = ("native_ids", "ends")
@@ -85,7 +93,8 @@ class ModelRunner:
         self.last_h2d_bytes = 0
         self.stager = BatchStager(self.device)
         self.cuda_graphs = cuda_graphs and self.model.graph_safe
-        self._graphs: dict = {}        # (decode batch size, with sampling) -> captured step
+        self._graphs: dict = {}        # a step's shape (see _graph_key) -> captured step
+        self._graph_pool = None        # one memory pool for all captured steps: they run one after the other
         self._out_ring: list = [None, None, None]     # pinned [tokens..., error flag] of the launches in flight
         self._out_at = 0
         self._seen: dict = {}
@@ -215,8 +224,9 @@ class ModelRunner:
         if not entries:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
         logits = batch = None
-        if self.cuda_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
-            logits, batch = self._graph_step(entries, None)
+        key = self._graph_key(entries, None)
+        if key is not None:
+            logits, batch = self._graph_step(entries, None, key)
         if batch is None:
             batch = self.prepare(entries)
             logits = self._forward(batch)
@@ -247,8 +257,9 @@ class ModelRunner:
         sampling = (temperatures, uniforms)
         batch = None
         picked = [r for r, x in enumerate(nucleus or []) if x is not None]
-        if not picked and self.cuda_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
-            _, batch = self._graph_step(entries, sampling)
+        key = None if picked else self._graph_key(entries, sampling)
+        if key is not None:
+            _, batch = self._graph_step(entries, sampling, key)
         if batch is None:
             batch = self.prepare(entries, sampling=sampling)
             logits = self._forward(batch)
@@ -301,35 +312,56 @@ class ModelRunner:
                            torch.tensor(off, dtype=torch.int32).to(dev), out)
         self.feed.index_copy_(0, rows, out)
 
-    # ------------------------------------------------------------------ decode steps as CUDA graphs
-    def _graph_step(self, entries: list, sampling):
-        """A batch of single rows that all want their logits always launches the same kernels with the
-        same sizes; only the index arrays differ.  Such a step is captured once per batch size (and once more
-        with the sampling kernel behind it) and replayed afterwards: the arrays are copied into the buffer the
-        graph reads, and the graph's logits tensor is returned, valid until the next step of the same size."""
+    # ------------------------------------------------------------------ steps as CUDA graphs
+    def _graph_key(self, entries: list, sampling):
+        """What fixes a step's kernels and their sizes: how many rows every entry brings, which of them are wanted,
+        and whether the sampling kernel follows.  None for a step that is not to be captured."""
+        if not self.cuda_graphs:
+            return None
+        lens = tuple(len(e.tokens) for e in entries)
+        if sum(lens) > GRAPH_MAX_TOKENS:
+            return None
+        wants = tuple(tuple(e.want) for e in entries)
+        if sum(len(w) for w in wants) * self.vocab_size * 4 > GRAPH_MAX_LOGIT_BYTES:
+            return None                        # (a captured step keeps its logits tensor for good)
+        return (lens, wants, sampling is not None)
+
+    def _graph_step(self, entries: list, sampling, key):
+        """Two steps of the same shape (see ``_graph_key``) launch the same kernels with the same sizes; only the
+        index arrays differ (every kernel takes positions, lengths and tables from them, on the device).  A shape
+        seen for the second time is captured and replayed from then on: the arrays are copied into the buffer the
+        graph reads, and the graph's logits tensor is returned, valid until the next captured step.  Decode steps
+        are such shapes (one per batch size), and so are the mixed steps of a server that cuts prompts into
+        portions of a fixed size."""
         S = len(entries)
-        key = (S, sampling is not None)
         g = self._graphs.get(key)
         if g is None:
-            self._seen[key] = self._seen.get(key, 0) + 1
-            if self._seen[key] < 2 or len(self._graphs) >= 24:
-                return None, None          # a size seen once is not worth a capture
-            seg, total = batch_layout(S, S, S, len(self.manager.pools), self.max_blocks, sampling is not None)
+            seen = self._seen.pop(key, 0) + 1
+            if len(self._seen) >= 512:                       # (shapes seen once come and go: forget the oldest)
+                self._seen.pop(next(iter(self._seen)))
+            self._seen[key] = seen
+            if seen < 2 or len(self._graphs) >= MAX_GRAPHS:
+                return None, None          # a shape seen once is not worth a capture
+            T, W = sum(key[0]), sum(len(w) for w in key[1])
+            seg, total = batch_layout(S, T, W, len(self.manager.pools), self.max_blocks, sampling is not None)
             static_dev = torch.full((total,), -1, dtype=torch.int32, device=self.device)
             batch = self.prepare(entries, static_dev, sampling)
-            batch.max_context = self.max_model_len        # the split of the keys must not depend on the step
+            # the split of the keys of single rows must not depend on the step
+            batch.max_context = batch.max_single_context = self.max_model_len
             logits = self._forward(batch)       # warms up; also this step's result
             if sampling is not None:
                 self._sample_into_feed(logits, batch)
             torch.cuda.synchronize(self.device)
             before = ops.launch_count()
             graph = torch.cuda.CUDAGraph()
+            if self._graph_pool is None:
+                self._graph_pool = torch.cuda.graph_pool_handle()
             # The collector stays off while the stream is capturing: an old engine's graphs or buffers that it
             # happened to free in the middle would be CUDA calls that a capture does not permit.
             collecting = gc.isenabled()
             gc.disable()
             try:
-                with torch.cuda.graph(graph):
+                with torch.cuda.graph(graph, pool=self._graph_pool):
                     static_logits = self._forward(batch)
                     if sampling is not None:
                         self._sample_into_feed(static_logits, batch)

@@ -64,6 +64,7 @@ class SparseMoeSwiGLU(FeedForward):
         self._counters = None
         self._captured = {}
         self._static = {}
+        self._static_kept = set()
         self.router_and_gate = None
         self.last_alignment = None      # the permutation buffers of the latest forward (for statistics)
 
@@ -209,10 +210,12 @@ class SparseMoeSwiGLU(FeedForward):
         key = (T, dev)
         st = self._static.get(key)
         if st is None:
-            big = [k for k in self._static if k[0] > SIDE_MAX_ROWS]      # (small ones may belong to captured steps)
-            if len(big) >= MAX_ALIGNMENTS:
-                self._static.pop(big[0])
+            loose = [k for k in self._static if k not in self._static_kept]
+            if len(loose) >= MAX_ALIGNMENTS:
+                self._static.pop(loose[0])
             st = self._static[key] = ops.StaticTiles(T, K, self.E, C, dev)
+        if torch.cuda.is_current_stream_capturing():       # a captured step names these buffers by address
+            self._static_kept.add(key)
         act = torch.empty((T * KT, self.inter), dtype=ctx.act_dtype, device=dev)
         y = torch.empty((T * KT, self.hidden), dtype=torch.float32, device=dev)
         main, side = torch.cuda.current_stream(dev), _side_stream(dev)

@@ -127,6 +127,48 @@ def test_float32_logits_are_bit_equal_however_the_work_is_cut(case, folders):
     rp.step([], end=["x", "o"])
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("case", ["B", "C"])
+def test_a_repeated_mixed_step_is_captured_and_replayed(case, dtype, folders):
+    """A step's shape (rows per entry, wanted places) seen for the second time is captured as a CUDA graph and
+    replayed from then on, whatever it holds: here two decoding requests beside a 24-token portion of a third, five
+    times over, then portions alone.  The logits are those of a runner that launches every step kernel by kernel
+    (float32: bit for bit; bfloat16: the decode kernel cuts the keys of single rows by the longest sequence allowed
+    instead of by the step's longest, so rounding differs)."""
+    from nano_vllm_cpp_b200.engine.runner import ModelRunner
+    from nano_vllm_cpp_b200.engine.batch import StepEntry
+    graphs = ModelRunner(folders[case], dtype=dtype, max_tokens=512, max_requests=4)
+    plain = ModelRunner(folders[case], dtype=dtype, max_tokens=512, max_requests=4, cuda_graphs=False)
+    ids = {r: prompt(case, 200, salt=80 + i) for i, r in enumerate("abc")}
+    at = {"a": 0, "b": 0, "c": 0}
+
+    def step(parts):
+        entries = []
+        for r, n in parts:
+            entries.append(StepEntry(r, ids[r][at[r]:at[r] + n], [n - 1]))
+            at[r] += n
+        got, want = graphs.step(entries).clone(), plain.step(entries)
+        if dtype == "float32":
+            assert torch.equal(got, want), parts
+        else:
+            helpers.assert_close(got, want, dtype, f"captured step {parts}")
+
+    step([("a", 20), ("b", 7)])
+    for _ in range(5):
+        step([("a", 1), ("b", 1), ("c", 24)])
+    mixed = ((1, 1, 24), ((0,), (0,), (23,)), False)
+    assert mixed in graphs._graphs and not plain._graphs
+    for _ in range(3):
+        step([("c", 13)])
+    assert ((13,), ((12,),), False) in graphs._graphs
+    for _ in range(3):                                   # ... and decode steps as before
+        step([("a", 1), ("b", 1), ("c", 1)])
+    assert ((1, 1, 1), ((0,), (0,), (0,)), False) in graphs._graphs
+    for r in "abc":
+        graphs.close(r), plain.close(r)
+    graphs.manager.check()
+
+
 def test_block_tables_travel_only_when_they_change(folders):
     """A request's block table goes to the device when it has changed (a page taken or given back, a new request)
     and stays there otherwise: decode steps inside a page send no table, the logits are those of a runner whose
