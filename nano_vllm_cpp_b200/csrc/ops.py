@@ -8,11 +8,50 @@ build it) importing the ops fails with the reason.
 from __future__ import annotations
 
 import ctypes
-from ctypes import c_int, c_float, c_longlong, c_void_p
+import os
+import re
 
 import torch
 
 from . import build as _build
+
+
+# The launchers' prototypes are read from the sources (every ``NV_API`` function of csrc/*.cu) and given to ctypes,
+# which then converts plain Python numbers and addresses itself and refuses a call with the wrong number of arguments.
+_C_TYPES = {"int": ctypes.c_int, "long long": ctypes.c_longlong, "unsigned long long": ctypes.c_ulonglong,
+            "float": ctypes.c_float, "double": ctypes.c_double, "void": None, "cudaStream_t": ctypes.c_void_p,
+            "const char*": ctypes.c_char_p}
+
+
+def _c_type(text: str):
+    text = " ".join(text.replace("*", " * ").split())
+    if "*" in text:
+        return ctypes.c_char_p if text.replace("const ", "").startswith("char") else ctypes.c_void_p
+    text = text.replace("const ", "")
+    try:
+        return _C_TYPES[text]
+    except KeyError:
+        raise KernelError(f"cannot read the C type {text!r} of a launcher's prototype") from None
+
+
+def _declare(lib: ctypes.CDLL) -> None:
+    """Sets ``argtypes`` and ``restype`` of every exported launcher from its definition in the sources."""
+    proto = re.compile(r"NV_API\s+([\w\s\*]+?)\s*\b(nv_\w+)\s*\(([^)]*)\)\s*\{", re.S)
+    for name in sorted(os.listdir(_build.CSRC)):
+        if not name.endswith(".cu"):
+            continue
+        with open(os.path.join(_build.CSRC, name)) as f:
+            text = f.read()
+        for ret, fn, args in proto.findall(text):
+            types = []
+            for a in (x.strip() for x in args.split(",")):
+                if not a or a == "void":
+                    continue
+                m = re.match(r"(.*?)(\w+)$", a, re.S)              # the type is what stands before the name
+                types.append(_c_type(m.group(1)))
+            f_ = getattr(lib, fn)
+            f_.argtypes = types
+            f_.restype = _c_type(ret)
 
 F32, BF16 = 0, 1
 _DT = {torch.float32: F32, torch.bfloat16: BF16}
@@ -35,7 +74,8 @@ def lib() -> ctypes.CDLL:
             _lib = ctypes.CDLL(path)
         except OSError as e:
             raise KernelError(f"cannot load the CUDA library {path}: {e}") from None
-        _lib.nv_set_dependent_launch(c_int(_early()))
+        _declare(_lib)
+        _lib.nv_set_dependent_launch(_early())
     return _lib
 
 
@@ -140,7 +180,7 @@ def _cuda_error_name(code: int) -> str:
     try:
         f = lib().nv_error_string
         f.restype = ctypes.c_char_p
-        return f(c_int(code)).decode()
+        return f(code).decode()
     except Exception:
         return "?"
 
@@ -151,16 +191,15 @@ _raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
 _raw_device = getattr(torch._C, "_cuda_getDevice", None)
 
 
-def _stream() -> c_void_p:
+def _stream() -> int:
     if _raw_stream is not None and _raw_device is not None:
-        return c_void_p(_raw_stream(_raw_device()))
-    return c_void_p(torch.cuda.current_stream().cuda_stream)
+        return _raw_stream(_raw_device())
+    return torch.cuda.current_stream().cuda_stream
 
 
-def _p(t) -> c_void_p:
-    if t is None:
-        return c_void_p(0)
-    return c_void_p(t.data_ptr())
+def _p(t):
+    """The address of a tensor's first element (None: a null pointer)."""
+    return None if t is None else t.data_ptr()
 
 
 def dt(t: torch.Tensor) -> int:
@@ -210,8 +249,8 @@ def random_fill(out, key: int, mean: float, std: float) -> None:
     """``out[i] = mean + z_i * std`` with z_i a function of (key, i) alone (see weights/random_values.py, whose
     host function gives the same bits)."""
     _cuda_contig(out)
-    _check(lib().nv_random_fill(_p(out), c_int(dt(out)), c_longlong(out.numel()), ctypes.c_ulonglong(key & (2**64 - 1)),
-                                c_float(mean), c_float(std), _stream()), "random_fill")
+    _check(lib().nv_random_fill(_p(out), dt(out), out.numel(), ctypes.c_ulonglong(key & (2**64 - 1)),
+                                mean, std, _stream()), "random_fill")
 
 
 def embedding(ids, table, out, err: ErrorFlag, feed=None) -> None:
@@ -220,7 +259,7 @@ def embedding(ids, table, out, err: ErrorFlag, feed=None) -> None:
     _i32(ids, feed)
     T, (V, H) = ids.numel(), table.shape
     _need(out.dtype == torch.float32 and out.shape == (T, H), "embedding: out must be float32 [T, H]")
-    _check(lib().nv_embedding(_p(ids), _p(feed), _p(table), c_int(dt(table)), _p(out), c_int(T), c_int(H), c_int(V),
+    _check(lib().nv_embedding(_p(ids), _p(feed), _p(table), dt(table), _p(out), T, H, V,
                               _p(err.t), _stream()), "embedding")
 
 
@@ -255,9 +294,9 @@ def add_rmsnorm(x, branch, w, eps: float, out, out32=None, *, mix=None) -> None:
     if H % 4 == 0:
         for t_ in (x, branch, out, out32, rows, dense):
             _need(t_ is None or t_.data_ptr() % 16 == 0, "add_rmsnorm: rows must start on 16-byte boundaries")
-    _check(lib().nv_add_rmsnorm(_p(x), _p(branch), _p(w), c_int(dt(w)), c_float(eps), _p(out), c_int(dt(out)),
-                                _p(out32), c_int(T), c_int(H), _p(rows), _p(index), _p(weight), c_int(R), _p(dense),
-                                _p(gate), c_longlong(gate_ld), _stream()), "add_rmsnorm")
+    _check(lib().nv_add_rmsnorm(_p(x), _p(branch), _p(w), dt(w), eps, _p(out), dt(out),
+                                _p(out32), T, H, _p(rows), _p(index), _p(weight), R, _p(dense),
+                                _p(gate), gate_ld, _stream()), "add_rmsnorm")
 
 
 ADD_RMSNORM_MAX_MIX = 64
@@ -291,12 +330,12 @@ def gemm_plain(a, w, out, *, bias=None, a_rows=None, swiglu=False, M=None, tiles
         max_tiles = 0
     if bias is not None:
         _need(bias.numel() == N, "gemm: bias length")
-    _check(lib().nv_gemm_plain(_p(a), c_int(dt(a)), c_longlong(a.stride(0)), _p(a_rows),
-                               _p(w), c_int(dt(w)), c_longlong(stride),
-                               _p(bias), c_int(dt(bias) if bias is not None else 0),
-                               _p(out), c_int(dt(out)), c_longlong(out.stride(0)),
-                               c_int(M), c_int(N), c_int(K), c_int(1 if swiglu else 0),
-                               _p(te), _p(tr0), _p(tr), _p(nt), c_int(max_tiles), _stream()), "gemm_plain")
+    _check(lib().nv_gemm_plain(_p(a), dt(a), a.stride(0), _p(a_rows),
+                               _p(w), dt(w), stride,
+                               _p(bias), (dt(bias) if bias is not None else 0),
+                               _p(out), dt(out), out.stride(0),
+                               M, N, K, (1 if swiglu else 0),
+                               _p(te), _p(tr0), _p(tr), _p(nt), max_tiles, _stream()), "gemm_plain")
 
 
 def rowdot(a, w, out, wide: bool = False) -> None:
@@ -310,16 +349,15 @@ def rowdot(a, w, out, wide: bool = False) -> None:
     _need(w.shape[1] == K and out.shape == (T, N), "rowdot: shapes")
     scratch = None
     if wide:        # a long K is cut into ranges whose sums a second kernel adds
-        lib().nv_rowdot_scratch_floats.restype = c_longlong
-        n = int(lib().nv_rowdot_scratch_floats(c_int(T), c_int(N), c_int(K), c_int(1)))
+        n = int(lib().nv_rowdot_scratch_floats(T, N, K, 1))
         if n:
             scratch = torch.empty(n, dtype=torch.float32, device=a.device)
-    _check(lib().nv_rowdot(_p(a), c_longlong(a.stride(0)), _p(w), c_int(dt(w)), _p(out), c_longlong(out.stride(0)),
-                           c_int(T), c_int(N), c_int(K), c_int(1 if wide else 0), _p(scratch), _stream()), "rowdot")
+    _check(lib().nv_rowdot(_p(a), a.stride(0), _p(w), dt(w), _p(out), out.stride(0),
+                           T, N, K, (1 if wide else 0), _p(scratch), _stream()), "rowdot")
 
 
 def attention_decode_usable(k_cache, D: int) -> bool:
-    return bool(lib().nv_attention_decode_usable(c_int(D), c_int(k_cache.shape[2]), c_int(dt(k_cache))))
+    return bool(lib().nv_attention_decode_usable(D, k_cache.shape[2], dt(k_cache)))
 
 
 def attention_decode(qkv, k_cache, v_cache, block_table, row_entry, positions, scale: float, window: int, out,
@@ -330,15 +368,15 @@ def attention_decode(qkv, k_cache, v_cache, block_table, row_entry, positions, s
     R = qkv.shape[0] if rows is None else rows.numel()
     page = k_cache.shape[2]
     L = lib()
-    splits = L.nv_attention_decode_splits(c_int(R), c_int(Hq), c_int(Hkv), c_int(max_context), c_int(num_sms()))
+    splits = L.nv_attention_decode_splits(R, Hq, Hkv, max_context, num_sms())
     scratch = None
     if splits > 1:
         scratch = torch.empty(R * Hq * splits * (D + 2), dtype=torch.float32, device=qkv.device)
-    _check(L.nv_attention_decode(_p(qkv), c_int(dt(qkv)), c_int(qkv.shape[1]), _p(k_cache), _p(v_cache),
-                                 c_int(dt(k_cache)), _p(block_table), c_int(block_table.shape[1]), _p(row_entry),
-                                 _p(positions), _p(rows), c_int(R), c_float(scale), c_int(window), _p(out),
-                                 c_int(dt(out)), c_int(Hq), c_int(Hkv), c_int(D), c_int(page), c_int(k_cache.shape[0]),
-                                 c_int(splits), _p(scratch), _p(err.t if err is not None else _global_err().t),
+    _check(L.nv_attention_decode(_p(qkv), dt(qkv), qkv.shape[1], _p(k_cache), _p(v_cache),
+                                 dt(k_cache), _p(block_table), block_table.shape[1], _p(row_entry),
+                                 _p(positions), _p(rows), R, scale, window, _p(out),
+                                 dt(out), Hq, Hkv, D, page, k_cache.shape[0],
+                                 splits, _p(scratch), _p(err.t if err is not None else _global_err().t),
                                  _stream()),
            "attention_decode")
 
@@ -362,19 +400,19 @@ def attention_prefill(qkv, k_cache, v_cache, block_table, cu_rows, entry_pos0, m
     L = lib()
     page = k_cache.shape[2]
     _need(kernel in ("auto", "mma"), "attention_prefill: kernel is 'auto' or 'mma'")
-    if kernel == "auto" and L.nv_attention_prefill_tc_usable(c_int(D), c_int(page)):
-        _check(L.nv_attention_prefill_tc(_p(qkv), c_int(qkv.shape[1]), c_int(qkv.shape[0]), _p(k_cache), _p(v_cache),
-                                         c_int(k_cache.shape[0]), _p(block_table), c_int(block_table.shape[1]),
-                                         _p(cu_rows), _p(entry_pos0), c_int(S), c_int(max_tiles), c_float(scale),
-                                         c_int(window), _p(out), c_int(Hq), c_int(Hkv), c_int(D), c_int(page),
-                                         c_int(min_rows), _p(err.t if err is not None else _global_err().t),
+    if kernel == "auto" and L.nv_attention_prefill_tc_usable(D, page):
+        _check(L.nv_attention_prefill_tc(_p(qkv), qkv.shape[1], qkv.shape[0], _p(k_cache), _p(v_cache),
+                                         k_cache.shape[0], _p(block_table), block_table.shape[1],
+                                         _p(cu_rows), _p(entry_pos0), S, max_tiles, scale,
+                                         window, _p(out), Hq, Hkv, D, page,
+                                         min_rows, _p(err.t if err is not None else _global_err().t),
                                          _stream()),
                "attention_prefill_tc")
         return
-    _check(L.nv_attention_prefill(_p(qkv), c_int(qkv.shape[1]), _p(k_cache), _p(v_cache), _p(block_table),
-                                  c_int(block_table.shape[1]), _p(cu_rows), _p(entry_pos0), c_int(S),
-                                  c_int(max_tiles), c_float(scale), c_int(window), _p(out), c_int(Hq), c_int(Hkv),
-                                  c_int(D), c_int(page), c_int(min_rows), _stream()), "attention_prefill")
+    _check(L.nv_attention_prefill(_p(qkv), qkv.shape[1], _p(k_cache), _p(v_cache), _p(block_table),
+                                  block_table.shape[1], _p(cu_rows), _p(entry_pos0), S,
+                                  max_tiles, scale, window, _p(out), Hq, Hkv,
+                                  D, page, min_rows, _stream()), "attention_prefill")
 
 
 def gemm_plain_tile_m() -> int:
@@ -400,11 +438,11 @@ def rope_store(qkv, positions, inv_freq, rotary_dim: int, k_cache, v_cache, bloc
     _need(inv_freq.dtype == torch.float32 and inv_freq.numel() >= rotary_dim // 2, "rope_store: inv_freq")
     page = k_cache.shape[2]
     _need(k_cache.shape[1:] == (Hkv, page, D) and v_cache.shape == k_cache.shape, "rope_store: cache shape")
-    _check(lib().nv_rope_store(_p(qkv), c_int(dt(qkv)), _p(positions), _p(rot_positions), c_int(axes), _p(pair_axis),
-                               _p(inv_freq), c_int(rotary_dim),
-                               _p(k_cache), _p(v_cache), c_int(dt(k_cache)), _p(block_table),
-                               c_int(block_table.shape[1]), _p(row_entry), c_int(T), c_int(Hq), c_int(Hkv),
-                               c_int(D), c_int(page), c_int(1 if write_kv else 0), _p(err.t), _stream()),
+    _check(lib().nv_rope_store(_p(qkv), dt(qkv), _p(positions), _p(rot_positions), axes, _p(pair_axis),
+                               _p(inv_freq), rotary_dim,
+                               _p(k_cache), _p(v_cache), dt(k_cache), _p(block_table),
+                               block_table.shape[1], _p(row_entry), T, Hq, Hkv,
+                               D, page, (1 if write_kv else 0), _p(err.t), _stream()),
            "rope_store")
 
 
@@ -415,10 +453,10 @@ def paged_attention_plain(qkv, k_cache, v_cache, block_table, row_entry, positio
     T = qkv.shape[0]
     page = k_cache.shape[2]
     _need(out.shape == (T, Hq * D), "attention: out shape")
-    _check(lib().nv_paged_attention_plain(_p(qkv), c_int(dt(qkv)), c_int(qkv.shape[1]), _p(k_cache), _p(v_cache),
-                                          c_int(dt(k_cache)), _p(block_table), c_int(block_table.shape[1]),
-                                          _p(row_entry), _p(positions), c_float(scale), c_int(window), _p(out),
-                                          c_int(dt(out)), c_int(T), c_int(Hq), c_int(Hkv), c_int(D), c_int(page),
+    _check(lib().nv_paged_attention_plain(_p(qkv), dt(qkv), qkv.shape[1], _p(k_cache), _p(v_cache),
+                                          dt(k_cache), _p(block_table), block_table.shape[1],
+                                          _p(row_entry), _p(positions), scale, window, _p(out),
+                                          dt(out), T, Hq, Hkv, D, page,
                                           _stream()), "paged_attention_plain")
 
 
@@ -432,9 +470,9 @@ def router_topk(logits, K: int, renorm: bool, idx, score, C: int = 0, gate_logit
     _i32(idx)
     _need(idx.shape == (T, K + C) and score.shape == (T, K + C), "router: output shapes")
     _need(C == 0 or (gate_logit is not None and gate_logit.dtype == torch.float32), "router: gate logits")
-    _check(lib().nv_router_topk(_p(logits), c_longlong(logits.stride(0)), c_int(T), c_int(E), c_int(K),
-                                c_int(1 if renorm else 0), _p(idx), _p(score), c_int(C), _p(gate_logit),
-                                c_longlong(gate_logit.stride(0) if gate_logit is not None else 0), _stream()),
+    _check(lib().nv_router_topk(_p(logits), logits.stride(0), T, E, K,
+                                (1 if renorm else 0), _p(idx), _p(score), C, _p(gate_logit),
+                                (gate_logit.stride(0) if gate_logit is not None else 0), _stream()),
            "router_topk")
 
 
@@ -499,17 +537,17 @@ def moe_align(idx, K: int, al: MoeAlignment, err: ErrorFlag, spread_last: int = 
     T = idx.numel() // K
     _need(T * K == al.TK, "moe_align: buffers were sized for another batch")
     s2 = al.secondary
-    _check(lib().nv_moe_align(_p(idx), c_int(T), c_int(K), c_int(al.E), c_int(al.tile_m), _p(al.counts),
+    _check(lib().nv_moe_align(_p(idx), T, K, al.E, al.tile_m, _p(al.counts),
                               _p(al.offsets), _p(al.sorted_token), _p(al.pair_pos),
                               _p(al.tile_expert), _p(al.tile_row0), _p(al.tile_rows), _p(al.num_tiles), _p(err.t),
-                              c_int(s2.tile_m if s2 else 0), _p(s2.tile_expert if s2 else None), _p(s2.tile_row0 if s2 else None),
-                              _p(s2.tile_rows if s2 else None), _p(s2.num_tiles if s2 else None), c_int(spread_last),
-                              c_int(static_last), _p(zero), c_int(zero.numel() if zero is not None else 0), _stream()),
+                              (s2.tile_m if s2 else 0), _p(s2.tile_expert if s2 else None), _p(s2.tile_row0 if s2 else None),
+                              _p(s2.tile_rows if s2 else None), _p(s2.num_tiles if s2 else None), spread_last,
+                              static_last, _p(zero), (zero.numel() if zero is not None else 0), _stream()),
            "moe_align")
 
 
 def moe_route_small_usable(T: int, E: int, K: int, C: int, H: int) -> bool:
-    return bool(lib().nv_moe_route_small_usable(c_int(T), c_int(E), c_int(K), c_int(C), c_int(H)))
+    return bool(lib().nv_moe_route_small_usable(T, E, K, C, H))
 
 
 def moe_route_small(logits, K: int, renorm: bool, C: int, gate_logit, idx, score, al: "MoeAlignment", err, x=None,
@@ -527,12 +565,12 @@ def moe_route_small(logits, K: int, renorm: bool, C: int, gate_logit, idx, score
         _need(x.dtype == torch.bfloat16 and x.is_contiguous(), "route: bfloat16 rows")
         H = x.shape[1]
         xs = torch.empty((T * KT, H), dtype=x.dtype, device=x.device)
-    _check(lib().nv_moe_route_small(_p(logits), c_longlong(logits.stride(0)), c_int(T), c_int(E), c_int(K),
-                                    c_int(1 if renorm else 0), c_int(C), _p(gate_logit),
-                                    c_longlong(gate_logit.stride(0) if gate_logit is not None else 0), _p(idx),
-                                    _p(score), c_int(al.tile_m), _p(al.counts), _p(al.offsets), _p(al.sorted_token),
+    _check(lib().nv_moe_route_small(_p(logits), logits.stride(0), T, E, K,
+                                    (1 if renorm else 0), C, _p(gate_logit),
+                                    (gate_logit.stride(0) if gate_logit is not None else 0), _p(idx),
+                                    _p(score), al.tile_m, _p(al.counts), _p(al.offsets), _p(al.sorted_token),
                                     _p(al.pair_pos), _p(al.tile_expert), _p(al.tile_row0), _p(al.tile_rows),
-                                    _p(al.num_tiles), _p(err.t), _p(x), _p(xs), c_int(H), c_int(C if static else 0),
+                                    _p(al.num_tiles), _p(err.t), _p(x), _p(xs), H, (C if static else 0),
                                     _stream()), "moe_route_small")
     return xs
 
@@ -566,15 +604,15 @@ def moe_combine(y, pair_pos, score, shared, gate_logit, out) -> None:
     H = out.shape[1]
     for t in (y, score, shared, gate_logit, out):
         _need(t is None or t.dtype == torch.float32, "moe_combine: float32 tensors")
-    _check(lib().nv_moe_combine(_p(y), _p(pair_pos), _p(score), _p(shared), _p(gate_logit), c_longlong(gate_ld),
-                                _p(out), c_int(T), c_int(K), c_int(H), _stream()), "moe_combine")
+    _check(lib().nv_moe_combine(_p(y), _p(pair_pos), _p(score), _p(shared), _p(gate_logit), gate_ld,
+                                _p(out), T, K, H, _stream()), "moe_combine")
 
 
 def silu_mul(gu, out) -> None:
     _cuda_contig(gu, out)
     rows, I2 = gu.shape
     _need(out.shape == (rows, I2 // 2), "silu_mul: out shape")
-    _check(lib().nv_silu_mul(_p(gu), c_int(dt(gu)), _p(out), c_int(dt(out)), c_longlong(rows), c_int(I2 // 2),
+    _check(lib().nv_silu_mul(_p(gu), dt(gu), _p(out), dt(out), rows, I2 // 2,
                              _stream()), "silu_mul")
 
 
@@ -582,8 +620,8 @@ def gather_rows(src, rows, dst) -> None:
     _cuda_contig(src, rows, dst)
     _i32(rows)
     _need(src.dtype == dst.dtype and dst.shape == (rows.numel(), src.shape[1]), "gather_rows: shapes")
-    _check(lib().nv_gather_rows(_p(src), c_int(dt(src)), _p(rows), _p(dst), c_int(rows.numel()),
-                                c_int(src.shape[1]), _stream()), "gather_rows")
+    _check(lib().nv_gather_rows(_p(src), dt(src), _p(rows), _p(dst), rows.numel(),
+                                src.shape[1], _stream()), "gather_rows")
 
 
 def reset_fresh_state(state, entry_slot, entry_pos0) -> None:
@@ -593,8 +631,8 @@ def reset_fresh_state(state, entry_slot, entry_pos0) -> None:
     slots = state.shape[0]
     slot_bytes = (state.numel() // max(slots, 1)) * state.element_size()
     _need(slot_bytes % 4 == 0, "reset_fresh_state: a slot's bytes must be a multiple of four")
-    _check(lib().nv_reset_fresh_state(_p(state), c_longlong(slot_bytes), c_int(slots), _p(entry_slot), _p(entry_pos0),
-                                      c_int(entry_slot.numel()), _stream()), "reset_fresh_state")
+    _check(lib().nv_reset_fresh_state(_p(state), slot_bytes, slots, _p(entry_slot), _p(entry_pos0),
+                                      entry_slot.numel(), _stream()), "reset_fresh_state")
 
 
 def sync_block_tables(src, lens, rows, entry_slot, tables, step_tables, S: int) -> None:
@@ -606,13 +644,13 @@ def sync_block_tables(src, lens, rows, entry_slot, tables, step_tables, S: int) 
     _need(step_tables.shape == tables.shape and src.numel() >= S and lens.numel() >= S and entry_slot.numel() >= S,
           "sync_block_tables: shapes")
     _check(lib().nv_sync_block_tables(_p(src), _p(lens), _p(rows), _p(entry_slot), _p(tables), _p(step_tables),
-                                      c_int(S), c_int(max_blocks), c_int(slots), _stream()), "sync_block_tables")
+                                      S, max_blocks, slots, _stream()), "sync_block_tables")
 
 
 def delay(micros: int) -> None:
     """Keeps the current stream busy for about ``micros`` microseconds (at most 200,000); for measurements that
     want a step's launches queued before the GPU starts on them."""
-    code = lib().nv_delay(c_int(int(micros)), _stream())
+    code = lib().nv_delay(int(micros), _stream())
     if code:
         raise KernelError(f"delay: {_ERR.get(code, code)}")
 
@@ -625,7 +663,7 @@ def sample(logits, temperature, u, out) -> None:
           "sample: logits/temperature float32, u float64")
     _i32(out)
     _need(temperature.numel() == R and u.numel() == R and out.numel() == R, "sample: one entry per row")
-    _check(lib().nv_sample(_p(logits), c_int(R), c_int(V), _p(temperature), _p(u), _p(out), _stream()), "sample")
+    _check(lib().nv_sample(_p(logits), R, V, _p(temperature), _p(u), _p(out), _stream()), "sample")
 
 
 def sample_nucleus(logits, params, recent, recent_off, out) -> None:
@@ -639,7 +677,7 @@ def sample_nucleus(logits, params, recent, recent_off, out) -> None:
     _i32(recent, recent_off, out)
     _need(recent_off.numel() == R + 1 and out.numel() == R, "sample_nucleus: one entry per row")
     work = torch.empty_like(logits)
-    _check(lib().nv_sample_nucleus(_p(logits), _p(work), c_int(R), c_int(V), _p(params), _p(recent), _p(recent_off),
+    _check(lib().nv_sample_nucleus(_p(logits), _p(work), R, V, _p(params), _p(recent), _p(recent_off),
                                    _p(out), _stream()), "sample_nucleus")
 
 
@@ -694,9 +732,9 @@ def skinny_gemm(a, w, out, *, bias=None, swiglu=False, rows=None, err=None) -> N
     _need(w.dim() == 2 and w.shape[1] == K and out.shape[1] == N and out.stride(1) == 1 and out.shape[0] >= R,
           "skinny product: shapes")
     _need(bias is None or (not swiglu and bias.numel() == N), "skinny product: bias")
-    _check(lib().nv_skinny_gemm(_p(a), c_longlong(a.stride(0)), c_int(R), _p(w), c_int(N), c_int(K),
-                                _p(bias), c_int(dt(bias) if bias is not None else 0), _p(out), c_int(dt(out)),
-                                c_longlong(out.stride(0)), c_int(1 if swiglu else 0), _stream()),
+    _check(lib().nv_skinny_gemm(_p(a), a.stride(0), R, _p(w), N, K,
+                                _p(bias), (dt(bias) if bias is not None else 0), _p(out), dt(out),
+                                out.stride(0), (1 if swiglu else 0), _stream()),
            f"skinny_gemm N={rows_w} K={K}", 0.0, float(w.element_size() * rows_w * K))
 
 
@@ -718,7 +756,7 @@ def permute_rows(src, rows, R=None):
     """bfloat16 rows of ``src`` gathered in the order of ``rows``."""
     R = rows.numel() if R is None else R
     dst = torch.empty((R, src.shape[1]), dtype=src.dtype, device=src.device)
-    _check(lib().nv_permute_rows_bf16(_p(src), _p(rows), _p(dst), c_int(R), c_int(src.shape[1]), _stream()),
+    _check(lib().nv_permute_rows_bf16(_p(src), _p(rows), _p(dst), R, src.shape[1], _stream()),
            "permute_rows")
     return dst
 
@@ -732,18 +770,18 @@ def gemm_fast(a, w, out, *, bias=None, a_rows=None, swiglu=False, M=None, err=No
     rows_w = w.shape[0]
     N = rows_w // 2 if swiglu else rows_w
     L = lib()
-    n_tile = L.nv_tc_gemm_token_tile(c_int(M), c_int(1 if swiglu else 0))
+    n_tile = L.nv_tc_gemm_token_tile(M, (1 if swiglu else 0))
     if splits is None:
-        splits = L.nv_tc_gemm_splits(c_int(M), c_int(N), c_int(K), c_int(n_tile), c_int(num_sms()))
+        splits = L.nv_tc_gemm_splits(M, N, K, n_tile, num_sms())
     scratch = None
     if splits > 1:
         scratch = torch.empty((splits, M, 2 * N if swiglu else N), dtype=torch.float32, device=a.device)
-    _check(L.nv_tc_gemm(_p(a), c_longlong(a.stride(0)), c_int(M), _p(w), c_int(rows_w), c_int(N), c_int(K),
-                        _p(bias), c_int(dt(bias) if bias is not None else 0), _p(out), c_int(dt(out)),
-                        c_longlong(out.stride(0)), c_int(1 if swiglu else 0), c_int(n_tile), c_int(splits),
-                        _p(scratch), _p(None), _p(None), _p(None), _p(None), c_int(0), c_int(0),
-                        _p(err.t if err is not None else _global_err().t), c_int(_early()), c_int(0), c_int(0),
-                        c_int(0), _p(None), c_int(0), _stream()), f"tc_gemm N={rows_w} K={K}", 2.0 * M * rows_w * K,
+    _check(L.nv_tc_gemm(_p(a), a.stride(0), M, _p(w), rows_w, N, K,
+                        _p(bias), (dt(bias) if bias is not None else 0), _p(out), dt(out),
+                        out.stride(0), (1 if swiglu else 0), n_tile, splits,
+                        _p(scratch), _p(None), _p(None), _p(None), _p(None), 0, 0,
+                        _p(err.t if err is not None else _global_err().t), _early(), 0, 0,
+                        0, _p(None), 0, _stream()), f"tc_gemm N={rows_w} K={K}", 2.0 * M * rows_w * K,
            w.element_size() * rows_w * K + a.element_size() * M * K + out.element_size() * M * N)
 
 
@@ -783,13 +821,13 @@ def gemm_fast_grouped(a, w, out, align, *, a_rows=None, swiglu=False, err=None, 
         splits = max(1, min(2 * num_sms() // ctas, k_steps // 4, 16))
         if splits > 1:
             scratch = torch.empty((splits, align.TK, 2 * N if swiglu else N), dtype=torch.float32, device=a.device)
-    _check(lib().nv_tc_gemm(_p(a), c_longlong(a.stride(0)), c_int(a.shape[0]), _p(w), c_int(E * rows_w), c_int(N),
-                            c_int(K), _p(None), c_int(0), _p(out), c_int(dt(out)), c_longlong(out.stride(0)),
-                            c_int(1 if swiglu else 0), c_int(tl.tile_m), c_int(splits), _p(scratch), _p(tl.tile_expert),
-                            _p(tl.tile_row0), _p(tl.tile_rows), _p(tl.num_tiles), c_int(tl.max_tiles),
-                            c_int(rows_w), _p(err.t if err is not None else _global_err().t),
-                            c_int(_early() if tiles_ready else 0), c_int(x_sub), c_int(x_mod), c_int(max_ctas),
-                            _p(counter), c_int(align.TK), _stream()),
+    _check(lib().nv_tc_gemm(_p(a), a.stride(0), a.shape[0], _p(w), E * rows_w, N,
+                            K, _p(None), 0, _p(out), dt(out), out.stride(0),
+                            (1 if swiglu else 0), tl.tile_m, splits, _p(scratch), _p(tl.tile_expert),
+                            _p(tl.tile_row0), _p(tl.tile_rows), _p(tl.num_tiles), tl.max_tiles,
+                            rows_w, _p(err.t if err is not None else _global_err().t),
+                            (_early() if tiles_ready else 0), x_sub, x_mod, max_ctas,
+                            _p(counter), align.TK, _stream()),
            f"tc_gemm_grouped N={rows_w} K={K}")
 
 
@@ -801,7 +839,7 @@ def set_dependent_launch(on: bool) -> None:
     ordinary way; for comparisons."""
     global _dependent_launch
     _dependent_launch = 1 if on else 0
-    lib().nv_set_dependent_launch(c_int(_dependent_launch))
+    lib().nv_set_dependent_launch(_dependent_launch)
 
 
 def _early() -> int:
