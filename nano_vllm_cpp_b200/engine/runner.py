@@ -314,15 +314,16 @@ class ModelRunner:
 
     # ------------------------------------------------------------------ steps as CUDA graphs
     def _graph_key(self, entries: list, sampling):
-        """What fixes a step's kernels and their sizes: how many rows every entry brings, which of them are wanted,
-        and whether the sampling kernel follows.  None for a step that is not to be captured."""
+        """What fixes a step's kernels and their sizes: how many rows every entry brings, how many of them are
+        wanted (which ones is data: the kernels read the places from the step's arrays), and whether the sampling
+        kernel follows.  None for a step that is not to be captured."""
         if not self.cuda_graphs:
             return None
         lens = tuple(len(e.tokens) for e in entries)
         if sum(lens) > GRAPH_MAX_TOKENS:
             return None
-        wants = tuple(tuple(e.want) for e in entries)
-        if sum(len(w) for w in wants) * self.vocab_size * 4 > GRAPH_MAX_LOGIT_BYTES:
+        wants = tuple(len(e.want) for e in entries)
+        if sum(wants) * self.vocab_size * 4 > GRAPH_MAX_LOGIT_BYTES:
             return None                        # (a captured step keeps its logits tensor for good)
         return (lens, wants, sampling is not None)
 
@@ -342,7 +343,7 @@ class ModelRunner:
             self._seen[key] = seen
             if seen < 2 or len(self._graphs) >= MAX_GRAPHS:
                 return None, None          # a shape seen once is not worth a capture
-            T, W = sum(key[0]), sum(len(w) for w in key[1])
+            T, W = sum(key[0]), sum(key[1])
             seg, total = batch_layout(S, T, W, len(self.manager.pools), self.max_blocks, sampling is not None)
             static_dev = torch.full((total,), -1, dtype=torch.int32, device=self.device)
             batch = self.prepare(entries, static_dev, sampling)
