@@ -33,7 +33,8 @@ class StepError(RuntimeError):
 # step's four hundred kernels one by one, which is longer than the GPU takes for a step of a few hundred tokens.
 # A larger step keeps the GPU busy for longer than its launches take.
 GRAPH_MAX_TOKENS = 1024
-MAX_GRAPHS = 48             # captured steps kept; further shapes run launch by launch
+MAX_GRAPHS = 48             # captured steps with a portion among their entries; further such shapes run launch by launch
+MAX_DECODE_GRAPHS = 64      # captured steps of single rows only (one per batch size, with and without sampling)
 GRAPH_MAX_LOGIT_BYTES = 64 << 20
 
 
@@ -341,7 +342,9 @@ class ModelRunner:
             if len(self._seen) >= 512:                       # (shapes seen once come and go: forget the oldest)
                 self._seen.pop(next(iter(self._seen)))
             self._seen[key] = seen
-            if seen < 2 or len(self._graphs) >= MAX_GRAPHS:
+            decode = max(key[0]) == 1
+            kept = sum(1 for k in self._graphs if (max(k[0]) == 1) == decode)
+            if seen < 2 or kept >= (MAX_DECODE_GRAPHS if decode else MAX_GRAPHS):
                 return None, None          # a shape seen once is not worth a capture
             T, W = sum(key[0]), sum(key[1])
             seg, total = batch_layout(S, T, W, len(self.manager.pools), self.max_blocks, sampling is not None)
