@@ -315,22 +315,23 @@ class ModelRunner:
 
     # ------------------------------------------------------------------ steps as CUDA graphs
     def _graph_key(self, entries: list, sampling):
-        """What fixes a step's kernels and their sizes: how many rows every entry brings, how many of them are
-        wanted (which ones is data: the kernels read the places from the step's arrays), and whether the sampling
-        kernel follows.  None for a step that is not to be captured."""
+        """What fixes a step's kernels and their sizes: the number of entries, of rows, of entries with a single row
+        (they go to another attention kernel) and of wanted rows, and whether the sampling kernel follows.  How the
+        rows are cut into entries and which rows are wanted is data: the kernels read it from the step's arrays.
+        None for a step that is not to be captured."""
         if not self.cuda_graphs:
             return None
-        lens = tuple(len(e.tokens) for e in entries)
-        if sum(lens) > GRAPH_MAX_TOKENS:
+        T = sum(len(e.tokens) for e in entries)
+        if T > GRAPH_MAX_TOKENS:
             return None
-        wants = tuple(len(e.want) for e in entries)
-        if sum(wants) * self.vocab_size * 4 > GRAPH_MAX_LOGIT_BYTES:
+        W = sum(len(e.want) for e in entries)
+        if W * self.vocab_size * 4 > GRAPH_MAX_LOGIT_BYTES:
             return None                        # (a captured step keeps its logits tensor for good)
-        return (lens, wants, sampling is not None)
+        return (len(entries), T, sum(1 for e in entries if len(e.tokens) == 1), W, sampling is not None)
 
     def _graph_step(self, entries: list, sampling, key):
         """Two steps of the same shape (see ``_graph_key``) launch the same kernels with the same sizes; only the
-        index arrays differ (every kernel takes positions, lengths and tables from them, on the device).  A shape
+        index arrays differ (every kernel takes positions, entry lengths and tables from them, on the device).  A shape
         seen for the second time is captured and replayed from then on: the arrays are copied into the buffer the
         graph reads, and the graph's logits tensor is returned, valid until the next captured step.  Decode steps
         are such shapes (one per batch size), and so are the mixed steps of a server that cuts prompts into
@@ -342,11 +343,11 @@ class ModelRunner:
             if len(self._seen) >= 512:                       # (shapes seen once come and go: forget the oldest)
                 self._seen.pop(next(iter(self._seen)))
             self._seen[key] = seen
-            decode = max(key[0]) == 1
-            kept = sum(1 for k in self._graphs if (max(k[0]) == 1) == decode)
+            decode = key[2] == key[0]
+            kept = sum(1 for k in self._graphs if (k[2] == k[0]) == decode)
             if seen < 2 or kept >= (MAX_DECODE_GRAPHS if decode else MAX_GRAPHS):
                 return None, None          # a shape seen once is not worth a capture
-            T, W = sum(key[0]), sum(key[1])
+            T, W = key[1], key[3]
             seg, total = batch_layout(S, T, W, len(self.manager.pools), self.max_blocks, sampling is not None)
             static_dev = torch.full((total,), -1, dtype=torch.int32, device=self.device)
             batch = self.prepare(entries, static_dev, sampling)

@@ -89,7 +89,9 @@ class PagedAttention(Mixer):
         if single < batch.S:
             tm = ops.attention_prefill_tile_rows()
             min_rows = 2 if single else 1
-            tiles = sum((e.length + tm - 1) // tm for e in batch.entries if e.length >= min_rows)
+            # an upper bound of the entries' tiles that depends on the step's totals only (CTAs without a tile leave
+            # at once): a captured step serves every step with the same totals, however its rows are cut
+            tiles = (batch.T - single) // tm + (batch.S - single)
             ops.attention_prefill(qkv, cache.k, cache.v, bt, batch.cu_rows, batch.entry_pos0, tiles, self.scale,
                                   self.window, att, self.Hq, self.Hkv, self.D, err=ctx.err, min_rows=min_rows)
 

@@ -132,14 +132,14 @@ def test_float32_logits_are_bit_equal_however_the_work_is_cut(case, folders):
 def test_a_repeated_mixed_step_is_captured_and_replayed(case, dtype, folders):
     """A step's shape (rows per entry, wanted places) seen for the second time is captured as a CUDA graph and
     replayed from then on, whatever it holds: here two decoding requests beside a 24-token portion of a third, five
-    times over, then portions alone.  The logits are those of a runner that launches every step kernel by kernel
+    times over, then the same totals cut otherwise, then portions alone.  The logits are those of a runner that launches every step kernel by kernel
     (float32: bit for bit; bfloat16: the decode kernel cuts the keys of single rows by the longest sequence allowed
     instead of by the step's longest, so rounding differs)."""
     from nano_vllm_cpp_b200.engine.runner import ModelRunner
     from nano_vllm_cpp_b200.engine.batch import StepEntry
     graphs = ModelRunner(folders[case], dtype=dtype, max_tokens=512, max_requests=4)
     plain = ModelRunner(folders[case], dtype=dtype, max_tokens=512, max_requests=4, cuda_graphs=False)
-    ids = {r: prompt(case, 200, salt=80 + i) for i, r in enumerate("abc")}
+    ids = {r: prompt(case, 260, salt=80 + i) for i, r in enumerate("abc")}
     at = {"a": 0, "b": 0, "c": 0}
 
     def step(parts):
@@ -156,14 +156,20 @@ def test_a_repeated_mixed_step_is_captured_and_replayed(case, dtype, folders):
     step([("a", 20), ("b", 7)])
     for _ in range(5):
         step([("a", 1), ("b", 1), ("c", 24)])
-    mixed = ((1, 1, 24), (1, 1, 1), False)
+    mixed = (3, 26, 2, 3, False)                         # entries, rows, single rows, wanted rows, no sampling
     assert mixed in graphs._graphs and not plain._graphs
+    step([("a", 24), ("b", 1), ("c", 1)])                # the same totals, the portion first: the same captured step
+    assert len(graphs._graphs) == 1
+    step([("a", 2), ("b", 1), ("c", 23)])                # one single row and two portions, cut three ways
+    step([("a", 12), ("b", 1), ("c", 13)])
+    step([("a", 7), ("b", 1), ("c", 18)])
+    assert (3, 26, 1, 3, False) in graphs._graphs and len(graphs._graphs) == 2
     for _ in range(3):
         step([("c", 13)])
-    assert ((13,), (1,), False) in graphs._graphs
+    assert (1, 13, 0, 1, False) in graphs._graphs
     for _ in range(3):                                   # ... and decode steps as before
         step([("a", 1), ("b", 1), ("c", 1)])
-    assert ((1, 1, 1), (1, 1, 1), False) in graphs._graphs
+    assert (3, 3, 3, 3, False) in graphs._graphs
     for r in "abc":
         graphs.close(r), plain.close(r)
     graphs.manager.check()
