@@ -551,10 +551,11 @@ def moe_route_small_usable(T: int, E: int, K: int, C: int, H: int) -> bool:
 
 
 def moe_route_small(logits, K: int, renorm: bool, C: int, gate_logit, idx, score, al: "MoeAlignment", err, x=None,
-                    static: bool = False):
+                    static: bool = False, zero=None):
     """Top-k, expert permutation and (with ``x``, bfloat16 rows) the expert-sorted copy of x, in one launch.
     Returns the sorted copy or None.  ``static``: the C always-on experts' pairs sit in row order at the end of
-    the permutation and get no tiles (``static_tiles`` lists them; they can then run before the routing)."""
+    the permutation and get no tiles (``static_tiles`` lists them; they can then run before the routing).
+    ``zero``: a few int32 that the kernel also sets to 0 (the tile counters of the products that follow it)."""
     T, E = logits.shape
     KT = K + C
     _need(idx.shape == (T, KT) and score.shape == (T, KT) and al.TK == T * KT and al.E == E + C, "route: sizes")
@@ -571,7 +572,7 @@ def moe_route_small(logits, K: int, renorm: bool, C: int, gate_logit, idx, score
                                     _p(score), al.tile_m, _p(al.counts), _p(al.offsets), _p(al.sorted_token),
                                     _p(al.pair_pos), _p(al.tile_expert), _p(al.tile_row0), _p(al.tile_rows),
                                     _p(al.num_tiles), _p(err.t), _p(x), _p(xs), H, (C if static else 0),
-                                    _stream()), "moe_route_small")
+                                    _p(zero), (zero.numel() if zero is not None else 0), _stream()), "moe_route_small")
     return xs
 
 

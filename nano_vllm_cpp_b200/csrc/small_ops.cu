@@ -198,10 +198,12 @@ __global__ void __launch_bounds__(1024) moe_route_small_kernel(
     int tile_m, int* __restrict__ counts, int* __restrict__ offsets, int* __restrict__ sorted_token,
     int* __restrict__ pair_pos, int* __restrict__ tile_expert, int* __restrict__ tile_row0,
     int* __restrict__ tile_rows, int* __restrict__ num_tiles, int* __restrict__ err,
-    const bf16* __restrict__ x, bf16* __restrict__ x_sorted, int H, int n_static) {
+    const bf16* __restrict__ x, bf16* __restrict__ x_sorted, int H, int n_static, int* __restrict__ zero,
+    int n_zero) {
   extern __shared__ double rs_smem[];
   grid_dep_wait();
   grid_dep_launch();
+  if ((int)threadIdx.x < n_zero) zero[threadIdx.x] = 0;      // (tile counters of the products that follow)
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const int KT = K + C;
   for (int t = warp; t < T; t += 32)
@@ -308,13 +310,15 @@ NV_API int nv_moe_route_small(const float* logits, long long ld, int T, int E, i
                               const float* gate_logit, long long gate_ld, int* idx, float* score, int tile_m,
                               int* counts, int* offsets, int* sorted_token, int* pair_pos, int* tile_expert,
                               int* tile_row0, int* tile_rows, int* num_tiles, int* err, const void* x,
-                              void* x_sorted, int H, int n_static, cudaStream_t s) {
+                              void* x_sorted, int H, int n_static, int* zero, int n_zero, cudaStream_t s) {
   if (!nv_moe_route_small_usable(T, E, K, C, H) || K < 1 || K > E || (C > 0 && !gate_logit)) return NV_ERR_UNSUPPORTED;
+  if (n_zero < 0 || n_zero > 1024 || (n_zero && !zero)) return NV_ERR_BAD_SIZE;
   if (n_static != 0 && n_static != C) return NV_ERR_UNSUPPORTED;
   if (T == 0) return NV_OK;
   const size_t smem = (size_t)32 * E * sizeof(double) + (size_t)4 * (E + C) * sizeof(int);
   NV_RETURN_IF(launch_dep(moe_route_small_kernel, dim3(1), dim3(1024), smem, s, logits, ld, T, E, K, renorm, C,
                           gate_logit, gate_ld, idx, score, tile_m, counts, offsets, sorted_token, pair_pos, tile_expert,
-                          tile_row0, tile_rows, num_tiles, err, (const bf16*)x, (bf16*)x_sorted, H, n_static));
+                          tile_row0, tile_rows, num_tiles, err, (const bf16*)x, (bf16*)x_sorted, H, n_static, zero,
+                          n_zero));
   NV_RETURN_LAST();
 }

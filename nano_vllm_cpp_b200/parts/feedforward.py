@@ -174,21 +174,27 @@ class SparseMoeSwiGLU(FeedForward):
             return self._forward_beside(h, logits, gate_logit, idx, score, al)
         if fast and C and T >= 256 and al.secondary is None:
             return self._forward_beside(h, logits, gate_logit, idx, score, al, many=True)
+        # (the products' CTAs take their tiles from a counter, as in _forward_beside, unless a handful of pairs split K)
+        c0 = c1 = zero = None
+        if fast and al.TK > ops.GROUPED_SPLIT_MAX_PAIRS:
+            if self._counters is None:
+                self._counters = torch.zeros(2, dtype=torch.int32, device=dev)
+            zero, c0, c1 = self._counters, self._counters[0:1], self._counters[1:2]
         if fast and al.secondary is None and ops.moe_route_small_usable(T, self.E, self.K, C, self.hidden):
             x_sorted = ops.moe_route_small(logits, self.K, self.renorm, C, gate_logit, idx, score, al, ctx.err,
-                                           x=None)   # one block copies rows slower than the copy kernel does
+                                           x=None, zero=zero)   # one block copies rows slower than the copy kernel does
         else:
             ops.router_topk(logits, self.K, self.renorm, idx, score, C, gate_logit)
-            ops.moe_align(idx, KT, al, ctx.err, spread_last=C if fast else 0)
+            ops.moe_align(idx, KT, al, ctx.err, spread_last=C if fast else 0, zero=zero)
         self.last_alignment = al
         wide = al.secondary                      # the tile list of the SwiGLU product, if it has one of its own
         if x_sorted is not None:
-            act = grouped_linear(ctx, x_sorted, self.w_gate_up, ctx.act_dtype, al, swiglu=True, tiles=wide)
+            act = grouped_linear(ctx, x_sorted, self.w_gate_up, ctx.act_dtype, al, swiglu=True, tiles=wide, counter=c0)
         else:
             act = grouped_linear(ctx, h, self.w_gate_up, ctx.act_dtype, al, a_rows=al.sorted_token, swiglu=True,
-                                 tiles=wide)
+                                 tiles=wide, counter=c0)
         # the tile lists were final before the first product started: the second may start beside it
-        y = grouped_linear(ctx, act, self.w_down, torch.float32, al, tiles_ready=True)
+        y = grouped_linear(ctx, act, self.w_down, torch.float32, al, tiles_ready=True, counter=c1)
         shared = None
         if self.shared_inter > 0 and not C:
             sact = linear(ctx, h, self.sh_gate_up, ctx.act_dtype, swiglu=True)
@@ -228,18 +234,23 @@ class SparseMoeSwiGLU(FeedForward):
                                   x_rows=st.x_rows, max_ctas=cap)
             ops.gemm_fast_grouped(act, self.w_down, y, al, err=ctx.err, tiles=st, tiles_ready=True, max_ctas=cap)
             join.record(side)
-        # (a prompt's routed products start while the side products still hold most multiprocessors: their CTAs take
-        # tiles from a counter, so the ones that start early do more of the work.  A product sets its counter back
-        # itself; one that gave up on a wait may not have, so the permutation kernel zeroes both.)
+        # The routed products' CTAs take their tiles from a counter: a prompt's start while the side products still hold
+        # most multiprocessors, so the ones that start early do more of the work; a decode step's tiles are one to
+        # three per CTA, and CTAs that are through with theirs take what is left (measured per decode step: batch 8
+        # 3.70 -> 3.63 ms, batch 16 5.42 -> 5.23, batch 32 7.77 -> 7.52, batch 64 10.24 -> 10.18).  A handful of pairs
+        # go without: their products split K instead.  A product sets its counter back itself; one that gave up on a
+        # wait may not have, so the routing kernel zeroes both.
         c0 = c1 = None
-        if many:
+        if many or al.TK > ops.GROUPED_SPLIT_MAX_PAIRS:
             if self._counters is None:
                 self._counters = torch.zeros(2, dtype=torch.int32, device=dev)
             c0, c1 = self._counters[0:1], self._counters[1:2]
+        if many:
             ops.router_topk(logits, K, self.renorm, idx, score, C, gate_logit)
             ops.moe_align(idx, KT, al, ctx.err, static_last=C, zero=self._counters)
         else:
-            ops.moe_route_small(logits, K, self.renorm, C, gate_logit, idx, score, al, ctx.err, x=None, static=True)
+            ops.moe_route_small(logits, K, self.renorm, C, gate_logit, idx, score, al, ctx.err, x=None, static=True,
+                                zero=self._counters if c0 is not None else None)
         self.last_alignment = al
         x_sorted = ops.permute_rows(h, al.sorted_token, T * K)
         ops.gemm_fast_grouped(x_sorted, self.w_gate_up, act, al, swiglu=True, err=ctx.err, tiles_ready=True, counter=c0)

@@ -50,9 +50,11 @@ def small_linear(ctx, a32, w):
     return out
 
 
-def grouped_linear(ctx, a, w, out_dtype, align, *, a_rows=None, swiglu=False, tiles=None, tiles_ready=False, out=None):
+def grouped_linear(ctx, a, w, out_dtype, align, *, a_rows=None, swiglu=False, tiles=None, tiles_ready=False, out=None,
+                   counter=None):
     """Per-expert product over an expert-sorted row list: row r of the output belongs to the expert
-    whose segment of ``align`` holds r and is ``a[a_rows[r]] @ w[expert].T``."""
+    whose segment of ``align`` holds r and is ``a[a_rows[r]] @ w[expert].T``.  ``counter``: see
+    ``ops.gemm_fast_grouped`` (tensor-core path only)."""
     rows_w = w.shape[1]
     N = rows_w // 2 if swiglu else rows_w
     if out is None:
@@ -61,7 +63,7 @@ def grouped_linear(ctx, a, w, out_dtype, align, *, a_rows=None, swiglu=False, ti
         return out
     if ctx.fast_kernels and ops.gemm_fast_usable(a, w, out, a_rows=a_rows, swiglu=swiglu, grouped=True):
         ops.gemm_fast_grouped(a, w, out, align, a_rows=a_rows, swiglu=swiglu, err=ctx.err, tiles=tiles,
-                              tiles_ready=tiles_ready)
+                              tiles_ready=tiles_ready, counter=counter)
     else:
         ops.gemm_plain(a, w, out, a_rows=a_rows, swiglu=swiglu, M=align.TK, tiles=align.tiles)
     return out
