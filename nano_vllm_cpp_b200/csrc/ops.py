@@ -369,16 +369,29 @@ def attention_decode(qkv, k_cache, v_cache, block_table, row_entry, positions, s
     page = k_cache.shape[2]
     L = lib()
     splits = L.nv_attention_decode_splits(R, Hq, Hkv, max_context, num_sms())
-    scratch = None
+    scratch = counts = None
     if splits > 1:
         scratch = torch.empty(R * Hq * splits * (D + 2), dtype=torch.float32, device=qkv.device)
+        counts = _split_counts(qkv.device)
     _check(L.nv_attention_decode(_p(qkv), dt(qkv), qkv.shape[1], _p(k_cache), _p(v_cache),
                                  dt(k_cache), _p(block_table), block_table.shape[1], _p(row_entry),
                                  _p(positions), _p(rows), R, scale, window, _p(out),
                                  dt(out), Hq, Hkv, D, page, k_cache.shape[0],
                                  splits, _p(scratch), _p(err.t if err is not None else _global_err().t),
-                                 _stream()),
+                                 _p(counts), (counts.numel() if counts is not None else 0), _stream()),
            "attention_decode")
+
+
+_counts = {}
+
+
+def _split_counts(device):
+    """Zeros that the decode attention kernel counts finished splits in (and sets back to zero itself): one array
+    per device, for kernels that run one after the other, as a step's do."""
+    key = torch.device(device)
+    if key not in _counts:
+        _counts[key] = torch.zeros(1 << 16, dtype=torch.int32, device=key)
+    return _counts[key]
 
 
 def attention_prefill_tile_rows() -> int:

@@ -46,6 +46,7 @@ def _call(lib, name, qkv, kc, vc, bt, ent, pos, out, Hq, Hkv, D, page, splits, s
     if scratch is not None:
         args.append(c_void_p(scratch.data_ptr()))
         args.append(c_void_p(0))            # the ordinary entry point also takes an error flag; none here
+        args += [c_void_p(0), c_int(0)]     # ... and counters for adding the splits up in the kernel itself; none
     args.append(stream)
     return fn(*args)
 
